@@ -1,0 +1,306 @@
+"""ctypes bindings for the two CPU checkers.  TEST INFRASTRUCTURE ONLY.
+
+* ``Oracle``     -> oracle/libmarmot_oracle.so, the plain-C restatement.
+* ``Reference``  -> oracle/_ref/libmarmot_ref.so, the reference's own CPU
+  backend compiled from its sources (marmot_init(CPU) -> marmot_linear /
+  marmot_moe_experts / marmot_quantize_* / marmot_dequantize_*).
+
+Only tests, the smoke check and the CPU-baseline legs of the benchmark import
+this module; nothing under marmot_b200/ does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+ORACLE_LIB = HERE / "libmarmot_oracle.so"
+REF_LIB = HERE / "_ref" / "libmarmot_ref.so"
+
+KIND_Q8_0, KIND_Q4_K, KIND_Q6_K = 5, 9, 11
+KIND_BY_NAME = {"q8_0": KIND_Q8_0, "q4_k": KIND_Q4_K, "q6_k": KIND_Q6_K}
+BLOCK_VALUES = {KIND_Q8_0: 32, KIND_Q4_K: 256, KIND_Q6_K: 256}
+BLOCK_BYTES = {KIND_Q8_0: 34, KIND_Q4_K: 144, KIND_Q6_K: 210}
+POLICY_SOFTMAX_SELECTED, POLICY_RENORMALIZE_SELECTED = 0, 2
+FFN_SWIGLU, FFN_GEGLU = 0, 2
+
+
+def row_bytes(kind: int, K: int) -> int:
+    bv = BLOCK_VALUES[kind]
+    return (K + bv - 1) // bv * BLOCK_BYTES[kind]
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+class Oracle:
+    def __init__(self, path: Path = ORACLE_LIB):
+        if not path.exists():
+            raise FileNotFoundError(f"{path} missing: run oracle/build_oracle.py")
+        self.lib = L = C.CDLL(str(path))
+        L.mo_dequantize.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.mo_pack_q8_k_f32.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+        L.mo_pack_q8_0_f32.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+        for n in ("mo_vec_dot_q4_k_q8_k", "mo_vec_dot_q6_k_q8_k", "mo_vec_dot_q8_0_q8_0"):
+            f = getattr(L, n)
+            f.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+            f.restype = C.c_float
+        L.mo_linear.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
+                                C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+        L.mo_topk.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p]
+        L.mo_moe_experts.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
+                                     C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                     C.c_size_t, C.c_int, C.c_float, C.c_int, C.c_void_p, C.c_int]
+
+    def dequantize(self, kind: int, blocks: np.ndarray, n_values: int) -> np.ndarray:
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        out = np.empty(n_values, dtype=np.float32)
+        assert self.lib.mo_dequantize(kind, _p(blocks), n_values, _p(out)) == 0
+        return out
+
+    def pack_q8_k(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.zeros(((x.size + 255) // 256) * 292, dtype=np.uint8)
+        self.lib.mo_pack_q8_k_f32(_p(x), x.size, _p(out))
+        return out
+
+    def pack_q8_0(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.zeros(((x.size + 31) // 32) * 34, dtype=np.uint8)
+        self.lib.mo_pack_q8_0_f32(_p(x), x.size, _p(out))
+        return out
+
+    def vec_dot(self, kind: int, w: np.ndarray, a: np.ndarray, n_blocks: int) -> float:
+        fn = {KIND_Q4_K: self.lib.mo_vec_dot_q4_k_q8_k, KIND_Q6_K: self.lib.mo_vec_dot_q6_k_q8_k,
+              KIND_Q8_0: self.lib.mo_vec_dot_q8_0_q8_0}[kind]
+        w = np.ascontiguousarray(w, dtype=np.uint8)
+        a = np.ascontiguousarray(a, dtype=np.uint8)
+        return float(fn(_p(w), _p(a), n_blocks))
+
+    def linear(self, kind: int, x: np.ndarray, W: np.ndarray, F: int, bias: np.ndarray | None = None,
+               threads: int | None = None) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        W = np.ascontiguousarray(W, dtype=np.uint8)
+        T, K = x.shape
+        assert W.size == F * row_bytes(kind, K), (W.size, F, K)
+        out = np.empty((T, F), dtype=np.float32)
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        rc = self.lib.mo_linear(kind, _p(x), K, _p(W), T, K, F, None if b is None else _p(b), _p(out), F,
+                                threads or os.cpu_count() or 1)
+        assert rc == 0
+        return out
+
+    def topk(self, x: np.ndarray, k: int):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        rows, cols = x.shape
+        vals = np.empty((rows, k), dtype=np.float32)
+        idx = np.empty((rows, k), dtype=np.int32)
+        self.lib.mo_topk(_p(x), rows, cols, cols, k, _p(vals), _p(idx))
+        return vals, idx
+
+    def moe_experts(self, kinds, hidden, gate, up, down, topk_ids, topk_weights, FF: int, E: int,
+                    ffn_type: int = FFN_SWIGLU, weights_scale: float = 1.0,
+                    policy: int = POLICY_RENORMALIZE_SELECTED, threads: int | None = None) -> np.ndarray:
+        hidden = np.ascontiguousarray(hidden, dtype=np.float32)
+        ids = np.ascontiguousarray(topk_ids, dtype=np.int32)
+        wts = np.ascontiguousarray(topk_weights, dtype=np.float32)
+        T, H = hidden.shape
+        k = ids.shape[1]
+        out = np.empty((T, H), dtype=np.float32)
+        gate, up, down = (np.ascontiguousarray(a, dtype=np.uint8) for a in (gate, up, down))
+        rc = self.lib.mo_moe_experts(kinds[0], kinds[1], kinds[2], _p(hidden), T, H, FF, E, _p(gate), _p(up), _p(down),
+                                     _p(ids), _p(wts), k, ffn_type, weights_scale, policy, _p(out),
+                                     threads or os.cpu_count() or 1)
+        assert rc == 0, rc
+        return out
+
+
+# ---------------------------------------------------------------------------
+# The reference library itself
+# ---------------------------------------------------------------------------
+
+MAX_DIMS = 8
+DT_F32, DT_F16, DT_I32, DT_I8, DT_U8 = 0, 1, 3, 5, 6
+
+
+class _Shape(C.Structure):
+    _fields_ = [("ndim", C.c_size_t), ("shape", C.c_size_t * MAX_DIMS), ("strides", C.c_size_t * MAX_DIMS)]
+
+
+class _Tensor(C.Structure):
+    """struct marmot_tensor, include/marmot/tensor.h:20-38."""
+    _fields_ = [
+        ("shape", _Shape), ("dtype", C.c_int), ("data", C.c_void_p), ("capacity_bytes", C.c_size_t),
+        ("owns_data", C.c_bool), ("quant_params", C.c_void_p), ("quant_kind", C.c_int), ("quant_layout", C.c_int),
+        ("backend", C.c_int), ("ctx", C.c_void_p), ("memory_location", C.c_int), ("needs_sync", C.c_bool),
+        ("packed_data", C.c_void_p), ("packed_src_data", C.c_void_p), ("packed_bytes", C.c_size_t),
+        ("packed_row_bytes", C.c_size_t), ("packed_rows", C.c_size_t),
+    ]
+
+
+class _MoeDesc(C.Structure):
+    """struct marmot_moe_experts_desc, include/marmot/ops_types.h:203-214."""
+    _fields_ = [
+        ("hidden_states", C.POINTER(_Tensor)), ("gate_exps", C.POINTER(_Tensor)), ("up_exps", C.POINTER(_Tensor)),
+        ("down_exps", C.POINTER(_Tensor)), ("topk_ids", C.POINTER(_Tensor)), ("topk_weights", C.POINTER(_Tensor)),
+        ("out", C.POINTER(_Tensor)), ("ffn_type", C.c_int), ("weights_scale", C.c_float),
+        ("router_weight_policy", C.c_int),
+    ]
+
+
+class _TopkDesc(C.Structure):
+    _fields_ = [("x", C.POINTER(_Tensor)), ("values_out", C.POINTER(_Tensor)), ("indices_out", C.POINTER(_Tensor)),
+                ("axis", C.c_int32), ("k", C.c_uint32)]
+
+
+class Reference:
+    """The reference CPU backend, driven through its public C API."""
+
+    def __init__(self, path: Path = REF_LIB, threads: int | None = None):
+        if not path.exists():
+            raise FileNotFoundError(f"{path} missing: run oracle/build_ref.py on a machine with the reference tree")
+        if threads is not None:
+            os.environ["MARMOT_NUM_THREADS"] = str(threads)
+        self.lib = L = C.CDLL(str(path))
+        TP = C.POINTER(_Tensor)
+        L.marmot_init.restype = C.c_void_p
+        L.marmot_init.argtypes = [C.c_int]
+        L.marmot_destroy.argtypes = [C.c_void_p]
+        L.marmot_tensor_create.restype = TP
+        L.marmot_tensor_create.argtypes = [C.c_void_p, C.POINTER(C.c_size_t), C.c_size_t, C.c_int]
+        L.marmot_tensor_create_quantized.restype = TP
+        L.marmot_tensor_create_quantized.argtypes = [C.c_void_p, C.POINTER(C.c_size_t), C.c_size_t, C.c_int]
+        L.marmot_tensor_destroy.argtypes = [TP]
+        L.marmot_tensor_copy_from_host_buffer.argtypes = [C.c_void_p, TP, C.c_void_p, C.c_size_t]
+        L.marmot_tensor_copy_to_host_buffer.argtypes = [C.c_void_p, TP, C.c_void_p, C.c_size_t]
+        L.marmot_tensor_size_bytes.restype = C.c_size_t
+        L.marmot_tensor_size_bytes.argtypes = [TP]
+        L.marmot_linear.argtypes = [C.c_void_p, TP, TP, C.c_void_p, TP]
+        L.marmot_moe_experts.argtypes = [C.c_void_p, C.POINTER(_MoeDesc)]
+        L.marmot_get_last_error_detail.restype = C.c_char_p
+        for n in ("q4_k", "q6_k", "q8_0"):
+            getattr(L, f"marmot_quantize_{n}").argtypes = [C.c_void_p, TP, TP]
+            getattr(L, f"marmot_dequantize_{n}").argtypes = [C.c_void_p, TP, TP]
+        self.ctx = L.marmot_init(0)
+        if not self.ctx:
+            raise RuntimeError("marmot_init(MARMOT_BACKEND_CPU) failed")
+
+    def close(self):
+        if self.ctx:
+            self.lib.marmot_destroy(self.ctx)
+            self.ctx = None
+
+    def _check(self, rc, what):
+        if rc != 0:
+            detail = self.lib.marmot_get_last_error_detail()
+            raise RuntimeError(f"{what} failed ({rc}): {detail.decode() if detail else ''}")
+
+    def _tensor(self, shape, dtype, src: np.ndarray | None = None):
+        arr = (C.c_size_t * len(shape))(*shape)
+        t = self.lib.marmot_tensor_create(self.ctx, arr, len(shape), dtype)
+        assert t, "tensor_create"
+        if src is not None:
+            src = np.ascontiguousarray(src)
+            self._check(self.lib.marmot_tensor_copy_from_host_buffer(self.ctx, t, _p(src), src.nbytes), "copy_from")
+        return t
+
+    def _qtensor(self, shape, kind, blocks: np.ndarray):
+        arr = (C.c_size_t * len(shape))(*shape)
+        t = self.lib.marmot_tensor_create_quantized(self.ctx, arr, len(shape), kind)
+        assert t, "tensor_create_quantized"
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        assert self.lib.marmot_tensor_size_bytes(t) == blocks.nbytes, (self.lib.marmot_tensor_size_bytes(t), blocks.nbytes)
+        self._check(self.lib.marmot_tensor_copy_from_host_buffer(self.ctx, t, _p(blocks), blocks.nbytes), "copy_from")
+        return t
+
+    def _read(self, t, shape, dtype) -> np.ndarray:
+        out = np.empty(shape, dtype=dtype)
+        self._check(self.lib.marmot_tensor_copy_to_host_buffer(self.ctx, t, _p(out), out.nbytes), "copy_to")
+        return out
+
+    def linear(self, kind: int, x: np.ndarray, W: np.ndarray, F: int) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        T, K = x.shape
+        tx = self._tensor((T, K), DT_F32, x)
+        tw = self._qtensor((F, K), kind, W)
+        to = self._tensor((T, F), DT_F32)
+        try:
+            self._check(self.lib.marmot_linear(self.ctx, tx, tw, None, to), "marmot_linear")
+            return self._read(to, (T, F), np.float32)
+        finally:
+            for t in (to, tw, tx):
+                self.lib.marmot_tensor_destroy(t)
+
+    def quantize(self, kind: int, w: np.ndarray) -> np.ndarray:
+        """Row-wise weight quantisation: w [rows, K] f32 -> packed rows (uint8)."""
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        rows, K = w.shape
+        rb = row_bytes(kind, K)
+        name = {KIND_Q4_K: "q4_k", KIND_Q6_K: "q6_k", KIND_Q8_0: "q8_0"}[kind]
+        fn = getattr(self.lib, f"marmot_quantize_{name}")
+        store_dt = DT_I8 if kind == KIND_Q8_0 else DT_U8
+        out = np.empty((rows, rb), dtype=np.uint8)
+        tin = self._tensor((K,), DT_F32)
+        tq = self._tensor((rb,), store_dt)
+        try:
+            for r in range(rows):
+                self._check(self.lib.marmot_tensor_copy_from_host_buffer(self.ctx, tin, _p(w[r]), K * 4), "copy_from")
+                self._check(fn(self.ctx, tin, tq), f"quantize_{name}")
+                self._check(self.lib.marmot_tensor_copy_to_host_buffer(self.ctx, tq, _p(out[r]), rb), "copy_to")
+        finally:
+            self.lib.marmot_tensor_destroy(tq)
+            self.lib.marmot_tensor_destroy(tin)
+        return out.reshape(-1)
+
+    def dequantize(self, kind: int, blocks: np.ndarray, n_values: int) -> np.ndarray:
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        name = {KIND_Q4_K: "q4_k", KIND_Q6_K: "q6_k", KIND_Q8_0: "q8_0"}[kind]
+        store_dt = DT_I8 if kind == KIND_Q8_0 else DT_U8
+        tq = self._tensor((blocks.nbytes,), store_dt, blocks)
+        to = self._tensor((n_values,), DT_F32)
+        try:
+            self._check(getattr(self.lib, f"marmot_dequantize_{name}")(self.ctx, tq, to), f"dequantize_{name}")
+            return self._read(to, (n_values,), np.float32)
+        finally:
+            self.lib.marmot_tensor_destroy(to)
+            self.lib.marmot_tensor_destroy(tq)
+
+    def _expert_tensor(self, kind: int, blocks: np.ndarray, rows: int, cols: int, experts: int):
+        """3-D expert weight in GGUF ne order {cols, rows, experts}, as tests/backend/test_backend_moe.c:77-124."""
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        store_dt = DT_I8 if kind == KIND_Q8_0 else DT_U8
+        t = self._tensor((blocks.nbytes,), store_dt, blocks)
+        s = t.contents
+        s.shape.ndim = 3
+        s.shape.shape[0], s.shape.shape[1], s.shape.shape[2] = cols, rows, experts
+        s.shape.strides[2], s.shape.strides[1], s.shape.strides[0] = 1, experts, rows * experts
+        s.quant_kind = kind
+        s.quant_layout = 1  # MARMOT_QUANT_LAYOUT_GGUF
+        return t
+
+    def moe_experts(self, kinds, hidden, gate, up, down, topk_ids, topk_weights, FF: int, E: int,
+                    ffn_type: int = FFN_SWIGLU, weights_scale: float = 1.0,
+                    policy: int = POLICY_RENORMALIZE_SELECTED) -> np.ndarray:
+        hidden = np.ascontiguousarray(hidden, dtype=np.float32)
+        ids = np.ascontiguousarray(topk_ids, dtype=np.int32)
+        wts = np.ascontiguousarray(topk_weights, dtype=np.float32)
+        T, H = hidden.shape
+        k = ids.shape[1]
+        th = self._tensor((T, H), DT_F32, hidden)
+        tg = self._expert_tensor(kinds[0], gate, FF, H, E)
+        tu = self._expert_tensor(kinds[1], up, FF, H, E)
+        td = self._expert_tensor(kinds[2], down, H, FF, E)
+        ti = self._tensor((T, k), DT_I32, ids)
+        tw = self._tensor((T, k), DT_F32, wts)
+        to = self._tensor((T, H), DT_F32)
+        desc = _MoeDesc(th, tg, tu, td, ti, tw, to, ffn_type, weights_scale, policy)
+        try:
+            self._check(self.lib.marmot_moe_experts(self.ctx, C.byref(desc)), "marmot_moe_experts")
+            return self._read(to, (T, H), np.float32)
+        finally:
+            for t in (to, tw, ti, td, tu, tg, th):
+                self.lib.marmot_tensor_destroy(t)
