@@ -1,0 +1,301 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized-matmul hot path.
+
+Workload (default): the single-token Q4_K GEMV, K = 4096, F = 4096, f32 activations drawn from
+N(0,1), weights drawn in block space (fp16 d, dmin = |N(0,0.02)|, 6-bit scales / mins and 4-bit
+quants uniform).  One *step* is one pass over a rotation of ``--copies`` distinct weight matrices
+(default 32 x 9.4 MB = 302 MB, larger than twice the 126 MB L2, so every pass streams from HBM);
+each GEMV in the pass is one call of the library's ``mcu_linear``.
+
+Printed on rank 0 as one JSON line:
+  value     GB/s of algorithmic bytes (packed weights + x + y = 9 469 952 B per GEMV) over the timed
+            region, inputs resident in HBM, summed over ranks
+  e2e       the same through ``mcu_linear_host``: activations start in pinned host memory and the
+            result is copied back to the host inside the timed region (weights stay resident)
+  roofline  the GEMV kernel against the measured HBM copy bandwidth
+  cpu_baseline  the reference CPU backend (or the oracle port) on the host cores, bounded sample
+
+``--impl reference`` times the reference's own CPU implementation instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+KIND_Q4_K = 9
+K_DIM, F_DIM, T_TOK = 4096, 4096, 1
+W_BYTES = F_DIM * (K_DIM // 256) * 144
+ALG_BYTES = W_BYTES + T_TOK * K_DIM * 4 + T_TOK * F_DIM * 4  # 9 469 952
+METRIC = "q4k_gemv_hbm_gbps"
+UNIT = "GB/s"
+WORKLOAD = "Q4_K GEMV T=1 K=4096 F=4096 (BASELINE config 1), rotation of distinct weight matrices"
+
+
+def measured_peaks():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_weights(seed: int) -> np.ndarray:
+    from tests.util import random_blocks
+
+    return random_blocks(KIND_Q4_K, F_DIM, K_DIM, np.random.default_rng(seed))
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_gemv_time(copies: int, iters: int, threads: int):
+    """Seconds per GEMV of the CPU checker on this host (reference library when present)."""
+    from oracle.bindings import REF_LIB, Oracle, Reference
+
+    ws = [make_weights(1000 + i) for i in range(copies)]
+    x = np.random.default_rng(5).normal(0, 1, (T_TOK, K_DIM)).astype(np.float32)
+    if REF_LIB.exists():
+        ref = Reference(threads=threads)
+        # keep the weight tensors alive across calls, as a model would
+        import ctypes as C
+        tw = [ref._qtensor((F_DIM, K_DIM), KIND_Q4_K, w) for w in ws]
+        tx = ref._tensor((T_TOK, K_DIM), 0, x)
+        to = ref._tensor((T_TOK, F_DIM), 0)
+        run = lambda i: ref._check(ref.lib.marmot_linear(ref.ctx, tx, tw[i % copies], None, to), "marmot_linear")
+        kind = "reference"
+    else:
+        from oracle import build_oracle
+
+        build_oracle.build()
+        orc = Oracle()
+        run = lambda i: orc.linear(KIND_Q4_K, x, ws[i % copies], F_DIM, threads=threads)
+        kind = "port"
+    for i in range(3):
+        run(i)
+    t0 = time.perf_counter()
+    for i in range(iters):
+        run(i)
+    dt = (time.perf_counter() - t0) / iters
+    return dt, kind
+
+
+def run_reference_arm(args, rank: int):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    per_step = 8  # GEMVs per step: a bounded sample of the rotation
+    copies = 4
+    from oracle.bindings import REF_LIB
+
+    times = []
+    # warm-up + timed steps share one loop helper; each step = per_step GEMVs
+    dt, kind = cpu_gemv_time(copies, per_step * max(1, args.warmup), threads)
+    for _ in range(args.steps):
+        dt, kind = cpu_gemv_time(copies, per_step, threads)
+        times.append(dt * per_step)
+    total = sum(times)
+    value = args.steps * per_step * ALG_BYTES / total / 1e9
+    sample = f"{per_step} GEMVs per step over {copies} weight copies, {threads} host threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 dot, f32 scale", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "T": T_TOK, "K": K_DIM, "F": F_DIM, "quant": "Q4_K"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--copies", type=int, default=32)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from marmot_b200 import Context
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank)
+    ctx = Context(local_rank)
+
+    R = args.copies
+    weights = [ctx.upload(make_weights(1000 * rank + i)) for i in range(R)]
+    rng = np.random.default_rng(7 + rank)
+    xs_host = torch.from_numpy(rng.normal(0, 1, (R, T_TOK, K_DIM)).astype(np.float32)).pin_memory()
+    xs = xs_host.to(dev)
+    outs = torch.empty((R, T_TOK, F_DIM), dtype=torch.float32, device=dev)
+    outs_host = torch.empty((R, T_TOK, F_DIM), dtype=torch.float32).pin_memory()
+
+    def step_device():
+        for i in range(R):
+            ctx.linear(KIND_Q4_K, xs[i], weights[i], F_DIM, out=outs[i])
+
+    xh_np = xs_host.numpy()
+    oh_np = outs_host.numpy()
+
+    def step_host():
+        for i in range(R):
+            ctx.linear_host(KIND_Q4_K, xh_np[i], weights[i], F_DIM, out_host=oh_np[i])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, steps):
+        for _ in range(args.warmup):
+            step_fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = ctx.launch_count()
+        e0.record()
+        for _ in range(steps):
+            step_fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        launches = ctx.launch_count() - l0
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, launches
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms_dev, launches = timed(step_device, args.steps)
+    clocks = sampler.stop() if sampler else None
+
+    # end to end through the host-buffer entry point (host wall clock == device time here: every call
+    # returns only after its result is in host memory)
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(args.warmup):
+        step_host()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        step_host()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    n_gemv = args.steps * R
+    value = world * n_gemv * ALG_BYTES / (ms_dev * 1e-3) / 1e9
+    e2e_value = world * e2e_steps * R * ALG_BYTES / e2e_s / 1e9
+    peak, peak_kind = measured_peaks()
+    # dominant kernel: the GEMV; its launches in the region == n_gemv.  Region time / launches is an
+    # upper bound of its duration (it includes the small activation-quantisation kernel and launch gaps).
+    per_launch_s = ms_dev * 1e-3 / n_gemv
+    achieved = ALG_BYTES / per_launch_s / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 dot, f32 scale", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "T": T_TOK, "K": K_DIM, "F": F_DIM, "quant": "Q4_K", "weight_copies": R,
+                   "l2_policy": f"inputs larger than L2: rotation over {R * W_BYTES / 1e6:.0f} MB of weights",
+                   "multi_gpu": "replicas only (independent GEMVs per rank, no collective)"},
+        "gpu_launches": int(launches),
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": R * T_TOK * K_DIM * 4,
+                "d2h_bytes_per_step": R * T_TOK * F_DIM * 4, "steps": e2e_steps,
+                "note": "weights device resident; activations from pinned host memory, result read back to host"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_kind, "frac_of_nominal_8TBs": achieved / 8000.0,
+                     "kernel": "gemv_q4_k_kernel<1>", "us_per_launch": per_launch_s * 1e6},
+        "clocks": clocks,
+    }
+    if not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        iters = 200
+        dt, kind = cpu_gemv_time(4, iters, threads)
+        line["cpu_baseline"] = {"value": ALG_BYTES / dt / 1e9, "unit": UNIT, "cores": threads, "kind": kind,
+                                "sample": f"{iters} GEMVs over 4 weight copies ({dt * 1e3:.3f} ms each)"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

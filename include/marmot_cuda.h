@@ -1,0 +1,140 @@
+/*
+ * libmarmot_cuda: hand-written sm_100a kernels for marmot's quantized GGUF matmul path behind a
+ * thin C ABI.  Plain pointers and sizes only; no marmot, torch or C++ types cross this boundary.
+ *
+ * This is the layer the reference's generated CUDA dispatch entries call.  In the reference the
+ * same position is held by the CPU backend's implementation functions named by the kernel-DSL
+ * `.def` files (IMPL_FUNCTION), which the generated `*_exec` wrappers invoke; each declaration
+ * below cites the reference function it stands in for (paths relative to the reference tree).
+ *
+ * Conventions
+ *   - T = tokens (rows of the activation), K = reduction length, F = output features.  The
+ *     reference calls these N, K, M (include/marmot/ops/matmul.h:11).
+ *   - `kind` is the numeric marmot_quant_kind_t (include/marmot/types.h:373-387):
+ *     Q8_0 = 5, Q4_K = 9, Q6_K = 11.  Weights are raw GGUF blocks, row-major [F][ceil(K/bv)].
+ *   - Return value: 0 on success, otherwise the negative marmot_error_t code
+ *     (include/marmot/types.h:210-220).  A message is kept per thread, see
+ *     mcu_last_error_message().
+ *   - Functions taking `*_dev` pointers expect device memory and only enqueue work on the
+ *     context's stream; functions with `_host` in the name take host memory, copy in and out on
+ *     that stream and return after the result is in host memory.
+ *   - There is no CPU fallback: every entry point fails with MCU_ERROR_DEVICE_NOT_AVAILABLE when
+ *     no CUDA device can be used.
+ */
+#ifndef MARMOT_CUDA_H
+#define MARMOT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    MCU_SUCCESS = 0,
+    MCU_ERROR_INVALID_ARGUMENT = -1,
+    MCU_ERROR_OUT_OF_MEMORY = -2,
+    MCU_ERROR_DEVICE_NOT_AVAILABLE = -3,
+    MCU_ERROR_BACKEND_INIT_FAILED = -4,
+    MCU_ERROR_INVALID_OPERATION = -5,
+    MCU_ERROR_UNSUPPORTED_DTYPE = -6,
+    MCU_ERROR_DIMENSION_MISMATCH = -7,
+    MCU_ERROR_NOT_IMPLEMENTED = -8,
+};
+
+enum { MCU_KIND_Q8_0 = 5, MCU_KIND_Q4_K = 9, MCU_KIND_Q6_K = 11 };
+
+/* marmot_router_weight_policy_t / marmot_ffn_type_t values (include/marmot/types.h:281-293) */
+enum { MCU_ROUTER_SOFTMAX_SELECTED = 0, MCU_ROUTER_SOFTMAX_SELECTED_SCALED = 1, MCU_ROUTER_RENORMALIZE_SELECTED = 2 };
+enum { MCU_FFN_SWIGLU = 0, MCU_FFN_GELU = 1, MCU_FFN_GEGLU = 2 };
+
+/* Regime override for mcu_linear*: the analogue of the reference's MARMOT_METAL_FORCE_{MV,MM}
+ * switches (src/backends/metal/ops/matmul_quant_dispatch.mm:41). */
+enum { MCU_REGIME_AUTO = 0, MCU_REGIME_GEMV = 1, MCU_REGIME_GEMM = 2 };
+
+typedef struct mcu_context mcu_context_t;
+
+/* ---- context: the device half of marmot_device_ops (include/marmot/device.h:43-66);
+ *      stands in for cpu_init / cpu_destroy / cpu_synchronize
+ *      (src/backends/cpu/runtime/runtime.c:1409-1443, src/backends/cpu/dispatch/device_ops.c:12-30). ---- */
+int mcu_context_create(int device, mcu_context_t **out);
+void mcu_context_destroy(mcu_context_t *ctx);
+/* Use a stream owned by the caller (cudaStream_t passed as void*); NULL restores the context's own. */
+int mcu_context_set_stream(mcu_context_t *ctx, void *cuda_stream);
+void *mcu_context_get_stream(mcu_context_t *ctx);
+int mcu_context_set_regime(mcu_context_t *ctx, int regime);
+int mcu_synchronize(mcu_context_t *ctx);
+const char *mcu_last_error_message(void);
+/* Number of kernels this context has launched so far. */
+uint64_t mcu_kernel_launch_count(const mcu_context_t *ctx);
+
+/* ---- device memory: alloc / free / memcpy slots of marmot_device_ops (include/marmot/device.h:47-56) ---- */
+int mcu_malloc(mcu_context_t *ctx, size_t bytes, void **out_dev);
+int mcu_free(mcu_context_t *ctx, void *dev);
+int mcu_memcpy_to_device(mcu_context_t *ctx, void *dst_dev, const void *src_host, size_t bytes);
+int mcu_memcpy_to_host(mcu_context_t *ctx, void *dst_host, const void *src_dev, size_t bytes);
+
+size_t mcu_row_bytes(int kind, size_t K);
+
+/* ---- dequantize: cpu_dequantize_{q4_k,q6_k,q8_0}
+ *      (src/backends/cpu/quantization/formats/q4k_gguf.c:133-166, q6k_gguf.c:63-99,
+ *       q8_gguf.c:110-114,189-200; row loop quantization/ops/quantize_core.c:267-331). Bit-exact. ---- */
+int mcu_dequantize(mcu_context_t *ctx, int kind, const void *blocks_dev, size_t n_values, float *out_dev);
+
+/* ---- activation packers: cpu_matmul_quant_pack_q8_k_f32 / cpu_matmul_quant_pack_q8_0_f32
+ *      (src/backends/cpu/ops/matmul/quantized/matmul_quant_pack.c:106-169, :23-62). Bit-exact values in a
+ *      structure-of-arrays layout: qs[T][kp] int8 (kp = K rounded up to the block size; within each
+ *      256-value Q8_K block the value 64g+32b+i is stored at b*128+g*32+i), d[T][nb] f32,
+ *      bsums[T][nb*16] int16 (Q8_K only, may be NULL for Q8_0). ---- */
+int mcu_quantize_activations(
+    mcu_context_t *ctx, int weight_kind, const float *x_dev, size_t ldx, size_t T, size_t K, int8_t *qs_dev,
+    float *d_dev, int16_t *bsums_dev
+);
+
+/* ---- quantized linear: cpu_matmul_quantized_{q4_k,q6_k,q8_0} -> cpu_matmul_quantized_impl
+ *      (src/backends/cpu/ops/matmul/quantized/matmul_quant_dispatch.c:373-591,905-960) with the bias epilogue of
+ *      cpu_matmul_apply_epilogue (src/backends/cpu/ops/matmul/matmul_epilogue.c).
+ *      out[t*ldo + f] = sum_k x[t*ldx + k] * W[f][k] (+ bias[f]); f32 in, f32 out. ---- */
+int mcu_linear(
+    mcu_context_t *ctx, int kind, const float *x_dev, size_t ldx, const void *w_dev, size_t T, size_t K, size_t F,
+    const float *bias_dev, float *out_dev, size_t ldo
+);
+
+/* ---- two weights, one activation read: cpu_matmul_quantized_dual_output
+ *      (matmul_quant_dispatch.c:593-856); gate/up of the FFN and of MoE experts. ---- */
+int mcu_linear_dual(
+    mcu_context_t *ctx, int kind, const float *x_dev, size_t ldx, const void *w_a_dev, const void *w_b_dev, size_t T,
+    size_t K, size_t F, float *out_a_dev, float *out_b_dev, size_t ldo
+);
+
+/* Same as mcu_linear with host activations / bias / output; weights stay device resident (made so once
+ * with mcu_malloc + mcu_memcpy_to_device, the residency contract of marmot_tensor_to_device,
+ * src/core/tensor/transfer.c:22). */
+int mcu_linear_host(
+    mcu_context_t *ctx, int kind, const float *x_host, size_t ldx, const void *w_dev, size_t T, size_t K, size_t F,
+    const float *bias_host, float *out_host, size_t ldo
+);
+
+/* ---- top-k over the last axis, ties to the lower index: cpu_topk_impl
+ *      (src/backends/cpu/ops/moe/moe_ops.c:789-889). ---- */
+int mcu_topk(
+    mcu_context_t *ctx, const float *x_dev, size_t rows, size_t cols, size_t ldx, size_t k, float *values_dev,
+    int32_t *indices_dev
+);
+
+/* ---- MoE expert FFN: cpu_moe_experts_impl -> cpu_moe_execute_grouped / cpu_moe_execute_decode
+ *      (src/backends/cpu/ops/moe/moe_ops.c:1069-1178, 891-1049, 622-787).
+ *      hidden [T][H] f32; gate/up: E contiguous [FF][H] quantized matrices; down: E contiguous [H][FF];
+ *      topk_ids [T][k] int32, topk_weights [T][k] f32; out [T][H] f32. ---- */
+int mcu_moe_experts(
+    mcu_context_t *ctx, int gate_kind, int up_kind, int down_kind, const float *hidden_dev, size_t T, size_t H,
+    size_t FF, size_t E, const void *gate_dev, const void *up_dev, const void *down_dev, const int32_t *topk_ids_dev,
+    const float *topk_weights_dev, size_t k, int ffn_type, float weights_scale, int router_weight_policy,
+    float *out_dev
+);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,423 @@
+// extern "C" entry points of libmarmot_cuda.so (declared in include/marmot_cuda.h): context,
+// device memory, regime selection and workspace handling around the kernels.  No CPU fallback:
+// every operation either enqueues CUDA kernels or returns an error.
+#include "../../include/marmot_cuda.h"
+
+#include "common.cuh"
+#include "kernels.h"
+#include "moe.h"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+namespace mcu {
+
+std::atomic<uint64_t> g_kernel_launches{0};
+void count_launches(int n) { g_kernel_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+static thread_local char g_err[512] = "";
+
+static int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+static int cuda_fail(cudaError_t e, const char *what) {
+    const int code = e == cudaErrorMemoryAllocation ? MCU_ERROR_OUT_OF_MEMORY
+        : (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver || e == cudaErrorInvalidDevice)
+        ? MCU_ERROR_DEVICE_NOT_AVAILABLE
+        : MCU_ERROR_INVALID_OPERATION;
+    return fail(code, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define MCU_CUDA(expr)                                              \
+    do {                                                            \
+        cudaError_t e__ = (expr);                                   \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #expr);       \
+    } while (0)
+
+static int g_sm_count = 0;
+int device_sm_count() { return g_sm_count > 0 ? g_sm_count : 148; }
+
+struct Buffer {
+    void *ptr = nullptr;
+    size_t cap = 0;
+};
+
+}  // namespace mcu
+
+using namespace mcu;
+
+struct mcu_context {
+    int device = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    int regime = MCU_REGIME_AUTO;
+    std::mutex mu;  // guards the workspace; calls on one context are serialised
+    // workspace (grows on demand, never shrinks)
+    Buffer act_qs, act_d, act_bsums, act_half, x_stage, out_stage, bias_stage;
+    Buffer moe_meta, moe_hidden, moe_gate, moe_up, moe_down;
+    std::vector<int> host_counts;
+};
+
+static int ensure(mcu_context *ctx, Buffer &b, size_t bytes) {
+    if (bytes <= b.cap) return MCU_SUCCESS;
+    // Kernels already enqueued may still read the old allocation.
+    MCU_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (b.ptr != nullptr) MCU_CUDA(cudaFree(b.ptr));
+    b.ptr = nullptr;
+    b.cap = 0;
+    const size_t want = (bytes + 255) & ~(size_t)255;
+    MCU_CUDA(cudaMalloc(&b.ptr, want));
+    b.cap = want;
+    return MCU_SUCCESS;
+}
+
+static int check_ctx(mcu_context *ctx) {
+    if (ctx == nullptr) return fail(MCU_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+    MCU_CUDA(cudaSetDevice(ctx->device));
+    return MCU_SUCCESS;
+}
+
+extern "C" {
+
+const char *mcu_last_error_message(void) { return g_err; }
+
+uint64_t mcu_kernel_launch_count(const mcu_context_t *) { return g_kernel_launches.load(); }
+
+int mcu_context_create(int device, mcu_context_t **out) {
+    if (out == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0)
+        return fail(MCU_ERROR_DEVICE_NOT_AVAILABLE, "no CUDA device: %s", cudaGetErrorString(e));
+    if (device < 0 || device >= n) return fail(MCU_ERROR_DEVICE_NOT_AVAILABLE, "device %d out of range (%d)", device, n);
+    MCU_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    MCU_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(MCU_ERROR_BACKEND_INIT_FAILED, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                    prop.major, prop.minor);
+    g_sm_count = prop.multiProcessorCount;
+    mcu_context *ctx = new (std::nothrow) mcu_context();
+    if (ctx == nullptr) return fail(MCU_ERROR_OUT_OF_MEMORY, "context allocation failed");
+    ctx->device = device;
+    e = cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        delete ctx;
+        return cuda_fail(e, "cudaStreamCreate");
+    }
+    ctx->stream = ctx->own_stream;
+    const char *env = getenv("MARMOT_CUDA_FORCE_GEMV");
+    if (env != nullptr && env[0] == '1') ctx->regime = MCU_REGIME_GEMV;
+    env = getenv("MARMOT_CUDA_FORCE_GEMM");
+    if (env != nullptr && env[0] == '1') ctx->regime = MCU_REGIME_GEMM;
+    *out = ctx;
+    return MCU_SUCCESS;
+}
+
+void mcu_context_destroy(mcu_context_t *ctx) {
+    if (ctx == nullptr) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    Buffer *bufs[] = {&ctx->act_qs,   &ctx->act_d,      &ctx->act_bsums, &ctx->act_half, &ctx->x_stage, &ctx->out_stage,
+                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down};
+    for (Buffer *b : bufs)
+        if (b->ptr != nullptr) cudaFree(b->ptr);
+    if (ctx->own_stream != nullptr) cudaStreamDestroy(ctx->own_stream);
+    delete ctx;
+}
+
+int mcu_context_set_stream(mcu_context_t *ctx, void *cuda_stream) {
+    if (int rc = check_ctx(ctx)) return rc;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    MCU_CUDA(cudaStreamSynchronize(ctx->stream));
+    ctx->stream = cuda_stream != nullptr ? (cudaStream_t)cuda_stream : ctx->own_stream;
+    return MCU_SUCCESS;
+}
+
+void *mcu_context_get_stream(mcu_context_t *ctx) { return ctx != nullptr ? (void *)ctx->stream : nullptr; }
+
+int mcu_context_set_regime(mcu_context_t *ctx, int regime) {
+    if (ctx == nullptr) return fail(MCU_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+    if (regime < MCU_REGIME_AUTO || regime > MCU_REGIME_GEMM) return fail(MCU_ERROR_INVALID_ARGUMENT, "bad regime");
+    ctx->regime = regime;
+    return MCU_SUCCESS;
+}
+
+int mcu_synchronize(mcu_context_t *ctx) {
+    if (int rc = check_ctx(ctx)) return rc;
+    MCU_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MCU_SUCCESS;
+}
+
+int mcu_malloc(mcu_context_t *ctx, size_t bytes, void **out_dev) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (out_dev == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "out_dev is null");
+    *out_dev = nullptr;
+    MCU_CUDA(cudaMalloc(out_dev, bytes > 0 ? bytes : 1));
+    return MCU_SUCCESS;
+}
+
+int mcu_free(mcu_context_t *ctx, void *dev) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (dev == nullptr) return MCU_SUCCESS;
+    MCU_CUDA(cudaStreamSynchronize(ctx->stream));
+    MCU_CUDA(cudaFree(dev));
+    return MCU_SUCCESS;
+}
+
+int mcu_memcpy_to_device(mcu_context_t *ctx, void *dst_dev, const void *src_host, size_t bytes) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (bytes == 0) return MCU_SUCCESS;
+    if (dst_dev == nullptr || src_host == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "null pointer");
+    MCU_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    MCU_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MCU_SUCCESS;
+}
+
+int mcu_memcpy_to_host(mcu_context_t *ctx, void *dst_host, const void *src_dev, size_t bytes) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (bytes == 0) return MCU_SUCCESS;
+    if (dst_host == nullptr || src_dev == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "null pointer");
+    MCU_CUDA(cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    MCU_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MCU_SUCCESS;
+}
+
+size_t mcu_row_bytes(int kind, size_t K) {
+    if (!kind_supported(kind)) return 0;
+    const size_t bv = (size_t)block_values(kind);
+    return (K + bv - 1) / bv * (size_t)block_bytes(kind);
+}
+
+int mcu_dequantize(mcu_context_t *ctx, int kind, const void *blocks_dev, size_t n_values, float *out_dev) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (!kind_supported(kind)) return fail(MCU_ERROR_NOT_IMPLEMENTED, "quant kind %d has no CUDA kernel", kind);
+    if (n_values == 0) return MCU_SUCCESS;
+    if (blocks_dev == nullptr || out_dev == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "null tensor data");
+    if (kind == MCU_KIND_Q4_K && ((uintptr_t)blocks_dev & 3)) return fail(MCU_ERROR_INVALID_ARGUMENT, "Q4_K blocks must be 4-byte aligned");
+    if ((uintptr_t)blocks_dev & 1) return fail(MCU_ERROR_INVALID_ARGUMENT, "blocks must be 2-byte aligned");
+    MCU_CUDA(launch_dequantize(kind, blocks_dev, n_values, out_dev, ctx->stream));
+    count_launches(1);
+    return MCU_SUCCESS;
+}
+
+static int validate_linear(int kind, const void *x, const void *w, const void *out, size_t T, size_t K, size_t F,
+                           size_t ldx, size_t ldo) {
+    if (!kind_supported(kind)) return fail(MCU_ERROR_NOT_IMPLEMENTED, "quant kind %d has no CUDA kernel", kind);
+    if (x == nullptr || w == nullptr || out == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "Tensor argument must not be null");
+    if (K == 0) return fail(MCU_ERROR_DIMENSION_MISMATCH, "K must be positive");
+    if (ldx < K || ldo < F) return fail(MCU_ERROR_DIMENSION_MISMATCH, "row stride smaller than the row");
+    if (T > (size_t)1 << 30 || F > (size_t)1 << 30 || K > (size_t)1 << 30)
+        return fail(MCU_ERROR_INVALID_ARGUMENT, "dimension too large");
+    const uintptr_t align = kind == MCU_KIND_Q4_K ? 15 : 1;
+    if ((uintptr_t)w & align)
+        return fail(MCU_ERROR_INVALID_ARGUMENT, "weight blocks must be %d-byte aligned", (int)align + 1);
+    return MCU_SUCCESS;
+}
+
+// Quantize the activations into the context workspace.
+static int pack_activations(mcu_context *ctx, int kind, const float *x, size_t ldx, size_t T, size_t K, bool want_half,
+                            ActBuffers &ab) {
+    const size_t bv = (size_t)block_values(kind);
+    const size_t nb = (K + bv - 1) / bv, kp = nb * bv;
+    if (int rc = ensure(ctx, ctx->act_qs, T * kp)) return rc;
+    if (int rc = ensure(ctx, ctx->act_d, T * nb * sizeof(float))) return rc;
+    if (kind != MCU_KIND_Q8_0)
+        if (int rc = ensure(ctx, ctx->act_bsums, T * nb * 16 * sizeof(int16_t))) return rc;
+    if (want_half)
+        if (int rc = ensure(ctx, ctx->act_half, T * kp * sizeof(__half))) return rc;
+    ab.qs = (int8_t *)ctx->act_qs.ptr;
+    ab.d = (float *)ctx->act_d.ptr;
+    ab.bsums = (int16_t *)ctx->act_bsums.ptr;
+    MCU_CUDA(launch_quantize_act(kind, x, (int)ldx, (int)T, (int)K, ab, want_half ? (__half *)ctx->act_half.ptr : nullptr,
+                                 ctx->stream));
+    count_launches(1);
+    return MCU_SUCCESS;
+}
+
+// Core of mcu_linear / mcu_linear_dual on device pointers; ctx->mu is held by the caller.
+static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx, const void *w, const void *w2, size_t T,
+                         size_t K, size_t F, const float *bias, float *out, float *out2, size_t ldo) {
+    if (T == 0 || F == 0) return MCU_SUCCESS;
+    const bool gemm = ctx->regime == MCU_REGIME_GEMM || (ctx->regime == MCU_REGIME_AUTO && T > (size_t)GEMV_MAX_T);
+    ActBuffers ab;
+    if (gemm) {
+        if (gemm_tc_supported(kind, (int)T, (int)K, (int)F)) {
+            if (int rc = pack_activations(ctx, kind, x, ldx, T, K, true, ab)) return rc;
+            const size_t bv = (size_t)block_values(kind);
+            const size_t kp = (K + bv - 1) / bv * bv;
+            int launches = 0;
+            MCU_CUDA(launch_gemm_tc(kind, w, w2, (const __half *)ctx->act_half.ptr, (int)kp, (int)T, (int)K, (int)F, bias,
+                                    out, out2, (int)ldo, ctx->stream, &launches));
+            count_launches(launches);
+            return MCU_SUCCESS;
+        }
+        if (ctx->regime == MCU_REGIME_GEMM)
+            return fail(MCU_ERROR_NOT_IMPLEMENTED, "tensor-core GEMM does not cover kind %d T=%zu K=%zu F=%zu", kind, T, K, F);
+    }
+    if (int rc = pack_activations(ctx, kind, x, ldx, T, K, false, ab)) return rc;
+    const size_t bv = (size_t)block_values(kind);
+    const size_t nb = (K + bv - 1) / bv, kp = nb * bv;
+    for (size_t t0 = 0; t0 < T; t0 += GEMV_MAX_T) {
+        const size_t tc = T - t0 < (size_t)GEMV_MAX_T ? T - t0 : (size_t)GEMV_MAX_T;
+        ActBuffers sub = ab;
+        sub.qs += t0 * kp;
+        sub.d += t0 * nb;
+        if (sub.bsums != nullptr) sub.bsums += t0 * nb * 16;
+        MCU_CUDA(launch_gemv(kind, w, w2, sub, (int)tc, (int)K, (int)F, bias, out + t0 * ldo,
+                             out2 != nullptr ? out2 + t0 * ldo : nullptr, (int)ldo, ctx->stream));
+        count_launches(1);
+    }
+    return MCU_SUCCESS;
+}
+
+int mcu_quantize_activations(mcu_context_t *ctx, int weight_kind, const float *x_dev, size_t ldx, size_t T, size_t K,
+                             int8_t *qs_dev, float *d_dev, int16_t *bsums_dev) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (!kind_supported(weight_kind)) return fail(MCU_ERROR_NOT_IMPLEMENTED, "quant kind %d has no CUDA kernel", weight_kind);
+    if (T == 0) return MCU_SUCCESS;
+    if (x_dev == nullptr || qs_dev == nullptr || d_dev == nullptr || (weight_kind != MCU_KIND_Q8_0 && bsums_dev == nullptr))
+        return fail(MCU_ERROR_INVALID_ARGUMENT, "null tensor data");
+    if (K == 0 || ldx < K) return fail(MCU_ERROR_DIMENSION_MISMATCH, "bad K / ldx");
+    ActBuffers ab{qs_dev, d_dev, bsums_dev};
+    MCU_CUDA(launch_quantize_act(weight_kind, x_dev, (int)ldx, (int)T, (int)K, ab, nullptr, ctx->stream));
+    count_launches(1);
+    return MCU_SUCCESS;
+}
+
+int mcu_linear(mcu_context_t *ctx, int kind, const float *x_dev, size_t ldx, const void *w_dev, size_t T, size_t K,
+               size_t F, const float *bias_dev, float *out_dev, size_t ldo) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = validate_linear(kind, x_dev, w_dev, out_dev, T, K, F, ldx, ldo)) return rc;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    return linear_locked(ctx, kind, x_dev, ldx, w_dev, nullptr, T, K, F, bias_dev, out_dev, nullptr, ldo);
+}
+
+int mcu_linear_dual(mcu_context_t *ctx, int kind, const float *x_dev, size_t ldx, const void *w_a_dev,
+                    const void *w_b_dev, size_t T, size_t K, size_t F, float *out_a_dev, float *out_b_dev, size_t ldo) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (w_b_dev == nullptr || out_b_dev == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "Tensor argument must not be null");
+    if (int rc = validate_linear(kind, x_dev, w_a_dev, out_a_dev, T, K, F, ldx, ldo)) return rc;
+    if (int rc = validate_linear(kind, x_dev, w_b_dev, out_b_dev, T, K, F, ldx, ldo)) return rc;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    return linear_locked(ctx, kind, x_dev, ldx, w_a_dev, w_b_dev, T, K, F, nullptr, out_a_dev, out_b_dev, ldo);
+}
+
+int mcu_linear_host(mcu_context_t *ctx, int kind, const float *x_host, size_t ldx, const void *w_dev, size_t T,
+                    size_t K, size_t F, const float *bias_host, float *out_host, size_t ldo) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = validate_linear(kind, x_host, w_dev, out_host, T, K, F, ldx, ldo)) return rc;
+    if (T == 0 || F == 0) return MCU_SUCCESS;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (int rc = ensure(ctx, ctx->x_stage, T * K * sizeof(float))) return rc;
+    if (int rc = ensure(ctx, ctx->out_stage, T * F * sizeof(float))) return rc;
+    float *xd = (float *)ctx->x_stage.ptr, *od = (float *)ctx->out_stage.ptr, *bd = nullptr;
+    MCU_CUDA(cudaMemcpy2DAsync(xd, K * sizeof(float), x_host, ldx * sizeof(float), K * sizeof(float), T,
+                               cudaMemcpyHostToDevice, ctx->stream));
+    if (bias_host != nullptr) {
+        if (int rc = ensure(ctx, ctx->bias_stage, F * sizeof(float))) return rc;
+        bd = (float *)ctx->bias_stage.ptr;
+        MCU_CUDA(cudaMemcpyAsync(bd, bias_host, F * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    }
+    if (int rc = linear_locked(ctx, kind, xd, K, w_dev, nullptr, T, K, F, bd, od, nullptr, F)) return rc;
+    MCU_CUDA(cudaMemcpy2DAsync(out_host, ldo * sizeof(float), od, F * sizeof(float), F * sizeof(float), T,
+                               cudaMemcpyDeviceToHost, ctx->stream));
+    MCU_CUDA(cudaStreamSynchronize(ctx->stream));
+    return MCU_SUCCESS;
+}
+
+int mcu_topk(mcu_context_t *ctx, const float *x_dev, size_t rows, size_t cols, size_t ldx, size_t k, float *values_dev,
+             int32_t *indices_dev) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (x_dev == nullptr || values_dev == nullptr || indices_dev == nullptr)
+        return fail(MCU_ERROR_INVALID_ARGUMENT, "TopK descriptor is incomplete");
+    if (k == 0 || k > cols || ldx < cols) return fail(MCU_ERROR_DIMENSION_MISMATCH, "TopK shapes do not match");
+    MCU_CUDA(launch_topk(x_dev, (int)rows, (int)cols, ldx, (int)k, values_dev, indices_dev, ctx->stream));
+    count_launches(1);
+    return MCU_SUCCESS;
+}
+
+int mcu_moe_experts(mcu_context_t *ctx, int gate_kind, int up_kind, int down_kind, const float *hidden_dev, size_t T,
+                    size_t H, size_t FF, size_t E, const void *gate_dev, const void *up_dev, const void *down_dev,
+                    const int32_t *topk_ids_dev, const float *topk_weights_dev, size_t k, int ffn_type,
+                    float weights_scale, int router_weight_policy, float *out_dev) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (hidden_dev == nullptr || gate_dev == nullptr || up_dev == nullptr || down_dev == nullptr ||
+        topk_ids_dev == nullptr || topk_weights_dev == nullptr || out_dev == nullptr)
+        return fail(MCU_ERROR_INVALID_ARGUMENT, "MoE experts descriptor is incomplete");
+    if (!kind_supported(gate_kind) || !kind_supported(up_kind) || !kind_supported(down_kind))
+        return fail(MCU_ERROR_NOT_IMPLEMENTED, "MoE expert quant kind has no CUDA kernel");
+    if (ffn_type != MCU_FFN_SWIGLU && ffn_type != MCU_FFN_GEGLU)
+        return fail(MCU_ERROR_NOT_IMPLEMENTED, "MoE experts supports SWIGLU and GEGLU only");
+    if (k == 0 || k > (size_t)MOE_MAX_TOPK || E == 0 || H == 0 || FF == 0)
+        return fail(MCU_ERROR_DIMENSION_MISMATCH, "MoE experts shapes do not match");
+    if (T == 0) return MCU_SUCCESS;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    const size_t routes = T * k;
+    // routing metadata: counts[E+1] | offsets[E+1] | sorted_tok | sorted_w | route_pos
+    const size_t meta_bytes = (2 * (E + 1) + 3 * routes) * sizeof(int32_t);
+    if (int rc = ensure(ctx, ctx->moe_meta, meta_bytes)) return rc;
+    if (int rc = ensure(ctx, ctx->moe_hidden, routes * H * sizeof(float))) return rc;
+    if (int rc = ensure(ctx, ctx->moe_gate, routes * FF * sizeof(float))) return rc;
+    if (int rc = ensure(ctx, ctx->moe_up, routes * FF * sizeof(float))) return rc;
+    if (int rc = ensure(ctx, ctx->moe_down, routes * H * sizeof(float))) return rc;
+    MoeRouteBuffers rb;
+    rb.counts = (int *)ctx->moe_meta.ptr;
+    rb.offsets = rb.counts + (E + 1);
+    rb.sorted_tok = (int32_t *)(rb.offsets + (E + 1));
+    rb.sorted_w = (float *)(rb.sorted_tok + routes);
+    rb.route_pos = (int32_t *)(rb.sorted_w + routes);
+    cudaStream_t s = ctx->stream;
+    const int renorm = router_weight_policy == MCU_ROUTER_RENORMALIZE_SELECTED;
+    MCU_CUDA(launch_moe_route(topk_ids_dev, topk_weights_dev, (int)T, (int)k, (int)E, weights_scale, renorm, rb, s));
+    count_launches(3);
+    float *route_hidden = (float *)ctx->moe_hidden.ptr, *gate_out = (float *)ctx->moe_gate.ptr;
+    float *up_out = (float *)ctx->moe_up.ptr, *route_down = (float *)ctx->moe_down.ptr;
+    MCU_CUDA(launch_moe_gather(hidden_dev, H, rb.sorted_tok, (int)routes, (int)H, route_hidden, s));
+    count_launches(1);
+    // The per-expert launches need the group sizes on the host.
+    ctx->host_counts.resize(2 * (E + 1));
+    MCU_CUDA(cudaMemcpyAsync(ctx->host_counts.data(), rb.counts, 2 * (E + 1) * sizeof(int), cudaMemcpyDeviceToHost, s));
+    MCU_CUDA(cudaStreamSynchronize(s));
+    if (ctx->host_counts[E] != 0) return fail(MCU_ERROR_INVALID_ARGUMENT, "MoE expert id is out of range");
+    const int *counts = ctx->host_counts.data();
+    const int *offsets = counts + (E + 1);
+    const size_t gate_slice = FF * mcu_row_bytes(gate_kind, H), up_slice = FF * mcu_row_bytes(up_kind, H);
+    const size_t down_slice = H * mcu_row_bytes(down_kind, FF);
+    for (size_t e = 0; e < E; ++e) {
+        const size_t cnt = (size_t)counts[e], off = (size_t)offsets[e];
+        if (cnt == 0) continue;
+        const float *hx = route_hidden + off * H;
+        const uint8_t *ge = (const uint8_t *)gate_dev + e * gate_slice, *ue = (const uint8_t *)up_dev + e * up_slice;
+        int rc;
+        if (gate_kind == up_kind) {
+            rc = linear_locked(ctx, gate_kind, hx, H, ge, ue, cnt, H, FF, nullptr, gate_out + off * FF, up_out + off * FF, FF);
+        } else {
+            rc = linear_locked(ctx, gate_kind, hx, H, ge, nullptr, cnt, H, FF, nullptr, gate_out + off * FF, nullptr, FF);
+            if (rc == 0)
+                rc = linear_locked(ctx, up_kind, hx, H, ue, nullptr, cnt, H, FF, nullptr, up_out + off * FF, nullptr, FF);
+        }
+        if (rc != 0) return rc;
+        MCU_CUDA(launch_moe_glu(gate_out + off * FF, up_out + off * FF, cnt * FF, ffn_type == MCU_FFN_GEGLU, s));
+        count_launches(1);
+        rc = linear_locked(ctx, down_kind, gate_out + off * FF, FF, (const uint8_t *)down_dev + e * down_slice, nullptr,
+                           cnt, FF, H, nullptr, route_down + off * H, nullptr, H);
+        if (rc != 0) return rc;
+    }
+    MCU_CUDA(launch_moe_combine(route_down, rb.sorted_w, rb.route_pos, (int)T, (int)k, (int)H, out_dev, H, s));
+    count_launches(1);
+    return MCU_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,130 @@
+// Activation quantizers: f32 rows -> Q8_K / Q8_0 values, bit-identical to the reference's
+// matmul packers (src/backends/cpu/ops/matmul/quantized/matmul_quant_pack.c:23-62,106-169,
+// scalar helpers src/backends/cpu/quantization/common/block.c:175-183,221-232).
+#include "common.cuh"
+#include "kernels.h"
+
+#include <float.h>
+
+namespace mcu {
+
+// round-to-nearest-even through the 1.5*2^23 bit trick, as cpu_quant_matmul_nearest_int
+// (matmul_quant_pack.c:11-21)
+__device__ __forceinline__ int nearest_int(float v) {
+    v = fminf(fmaxf(v, -4194303.0f), 4194303.0f);
+    const float shifted = __fadd_rn(v, 12582912.0f);
+    return (__float_as_int(shifted) & 0x007fffff) - 0x00400000;
+}
+
+// One warp per (token, 256-value block).  Lane l owns values l, l+32, ..., l+224.
+__global__ void __launch_bounds__(256)
+quantize_q8_k_kernel(const float *__restrict__ x, int ldx, int T, int K, int nb, int8_t *__restrict__ qs,
+                     float *__restrict__ dq, int16_t *__restrict__ bsums, __half *__restrict__ xh) {
+    const int lane = threadIdx.x & 31;
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= T * nb) return;
+    const int t = w / nb, blk = w - t * nb;
+    const float *row = x + (size_t)t * ldx + (size_t)blk * QK_K;
+    const int len = min(QK_K, K - blk * QK_K);
+
+    float v[8];
+    float best_abs = 0.0f, best_val = 0.0f;
+    int best_idx = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = lane + 32 * i;
+        v[i] = idx < len ? row[idx] : 0.0f;
+        const float a = fabsf(v[i]);
+        if (a > best_abs) {  // strict: the first occurrence wins
+            best_abs = a;
+            best_val = v[i];
+            best_idx = idx;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, best_abs, o);
+        const float ov = __shfl_xor_sync(0xffffffffu, best_val, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_idx, o);
+        if (oa > best_abs || (oa == best_abs && oi < best_idx)) {
+            best_abs = oa;
+            best_val = ov;
+            best_idx = oi;
+        }
+    }
+    int8_t *qrow = qs + (size_t)t * nb * QK_K + (size_t)blk * QK_K;
+    int16_t *brow = bsums + ((size_t)t * nb + blk) * 16;
+    __half *hrow = xh != nullptr ? xh + (size_t)t * nb * QK_K + (size_t)blk * QK_K : nullptr;
+    if (!(best_abs > 0.0f)) {
+        // all-zero block: d = 0, zero quants (matmul_quant_pack.c:121-126)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            qrow[(i & 1) * 128 + (i >> 1) * 32 + lane] = 0;
+            if (hrow != nullptr) hrow[lane + 32 * i] = __float2half_rn(0.0f);
+        }
+        if (lane < 16) brow[lane] = 0;
+        if (lane == 0) dq[(size_t)t * nb + blk] = 0.0f;
+        return;
+    }
+    const float iscale = __fdiv_rn(-127.0f, best_val);
+    const float d = __fdiv_rn(1.0f, iscale);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        int q = nearest_int(__fmul_rn(iscale, v[i]));
+        q = min(q, 127);
+        qrow[(i & 1) * 128 + (i >> 1) * 32 + lane] = (int8_t)q;
+        if (hrow != nullptr) hrow[lane + 32 * i] = __float2half_rn(__fmul_rn(d, (float)q));
+        // sums over 16 consecutive values: the 16 lanes of a half warp
+        int s = q;
+        s += __shfl_xor_sync(0xffffffffu, s, 8);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        if ((lane & 15) == 0) brow[2 * i + (lane >> 4)] = (int16_t)s;
+    }
+    if (lane == 0) dq[(size_t)t * nb + blk] = d;
+}
+
+// One warp per (token, 32-value block); lane = value.
+__global__ void __launch_bounds__(256)
+quantize_q8_0_kernel(const float *__restrict__ x, int ldx, int T, int K, int nb, int8_t *__restrict__ qs,
+                     float *__restrict__ dq, __half *__restrict__ xh) {
+    const int lane = threadIdx.x & 31;
+    const int wpb = blockDim.x >> 5;
+    const long total = (long)T * nb;
+    for (long w = (long)blockIdx.x * wpb + (threadIdx.x >> 5); w < total; w += (long)gridDim.x * wpb) {
+        const int t = (int)(w / nb), blk = (int)(w - (long)t * nb);
+        const int k = blk * Q8_0_VALUES + lane;
+        const float v = k < K ? x[(size_t)t * ldx + k] : 0.0f;
+        float amax = fabsf(v);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        float scale = __fdiv_rn(amax, 127.0f);
+        if (scale < FLT_MIN) scale = 1.0f;
+        const float inv = __fdiv_rn(1.0f, scale);
+        int q = (int)roundf(__fmul_rn(v, inv));
+        q = max(-127, min(127, q));
+        const float d_stored = __half2float(__float2half_rn(scale));
+        qs[(size_t)t * nb * Q8_0_VALUES + k] = (int8_t)q;
+        if (xh != nullptr) xh[(size_t)t * nb * Q8_0_VALUES + k] = __float2half_rn(__fmul_rn(d_stored, (float)q));
+        if (lane == 0) dq[(size_t)t * nb + blk] = d_stored;
+    }
+}
+
+cudaError_t launch_quantize_act(int kind, const float *x, int ldx, int T, int K, const ActBuffers &a, __half *xh,
+                                cudaStream_t s) {
+    if (T <= 0) return cudaSuccess;
+    if (kind == KIND_Q8_0) {
+        const int nb = (K + Q8_0_VALUES - 1) / Q8_0_VALUES;
+        const long warps = (long)T * nb;
+        const int blocks = (int)min((warps + 7) / 8, (long)148 * 16);
+        quantize_q8_0_kernel<<<blocks, 256, 0, s>>>(x, ldx, T, K, nb, a.qs, a.d, xh);
+    } else {
+        const int nb = (K + QK_K - 1) / QK_K;
+        const long warps = (long)T * nb;
+        quantize_q8_k_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(x, ldx, T, K, nb, a.qs, a.d, a.bsums, xh);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace mcu

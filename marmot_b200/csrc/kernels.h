@@ -1,0 +1,41 @@
+// Internal launcher declarations shared by the translation units of libmarmot_cuda.so.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace mcu {
+
+// Device buffers holding quantized activations (structure of arrays).
+struct ActBuffers {
+    int8_t *qs;      // [T][kp]
+    float *d;        // [T][nb]
+    int16_t *bsums;  // [T][nb*16], Q8_K only
+};
+
+// f32 activations -> Q8_K (K-quant weights) or Q8_0 (Q8_0 weights); xh (optional) receives the
+// dequantised activations d*q as fp16, row stride kp.
+cudaError_t launch_quantize_act(int kind, const float *x, int ldx, int T, int K, const ActBuffers &a, __half *xh,
+                                cudaStream_t s);
+
+// blocks -> f32 (bit-exact with the reference dequantizers)
+cudaError_t launch_dequantize(int kind, const void *blocks, size_t n_values, float *out, cudaStream_t s);
+
+// Decode-regime matmul, T <= GEMV_MAX_T tokens: out[t*ldo + f] = dot(W[f], act[t]) (+ bias[f]).
+// W2/out2 non-null computes a second weight matrix of the same shape from the same activations.
+constexpr int GEMV_MAX_T = 8;
+cudaError_t launch_gemv(int kind, const void *W, const void *W2, const ActBuffers &a, int T, int K, int F,
+                        const float *bias, float *out, float *out2, int ldo, cudaStream_t s);
+
+// Prefill / batched regime on the tcgen05 tensor cores: weights dequantised to fp16 tiles in shared
+// memory, activations given as fp16 (d*q of the quantized activations, row stride ldxh), f32
+// accumulation in tensor memory.
+bool gemm_tc_supported(int kind, int T, int K, int F);
+cudaError_t launch_gemm_tc(int kind, const void *W, const void *W2, const __half *xh, int ldxh, int T, int K, int F,
+                           const float *bias, float *out, float *out2, int ldo, cudaStream_t s, int *launches);
+
+int device_sm_count();
+
+}  // namespace mcu

@@ -1,0 +1,189 @@
+// Device-side MoE routing and glue: top-k, per-expert histogram, exclusive prefix, stable scatter
+// of (token, weight*norm), hidden-row gather, act(gate)*up, and the weighted combine.
+// Order and arithmetic follow the reference's grouped path
+// (src/backends/cpu/ops/moe/moe_ops.c:789-889 top-k, :891-1049 grouped execution).
+#include "common.cuh"
+#include "kernels.h"
+#include "moe.h"
+
+#include <float.h>
+
+namespace mcu {
+
+// One thread per row; insertion top-k, equal values keep the lower column first (moe_ops.c:851-875).
+__global__ void topk_kernel(const float *__restrict__ x, int rows, int cols, size_t ldx, int k,
+                            float *__restrict__ values, int32_t *__restrict__ indices) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    float *bv = values + (size_t)r * k;
+    int32_t *bi = indices + (size_t)r * k;
+    for (int i = 0; i < k; ++i) {
+        bv[i] = -FLT_MAX;
+        bi[i] = -1;
+    }
+    for (int c = 0; c < cols; ++c) {
+        const float v = x[(size_t)r * ldx + c];
+        int pos = k;
+        for (int i = 0; i < k; ++i) {
+            if (v > bv[i] || (v == bv[i] && c < bi[i])) {
+                pos = i;
+                break;
+            }
+        }
+        if (pos == k) continue;
+        for (int i = k - 1; i > pos; --i) {
+            bv[i] = bv[i - 1];
+            bi[i] = bi[i - 1];
+        }
+        bv[pos] = v;
+        bi[pos] = c;
+    }
+}
+
+// counts[e] = number of routes to expert e; bad_flag set when an id is out of range.
+__global__ void moe_count_kernel(const int32_t *__restrict__ ids, int routes, int E, int *__restrict__ counts,
+                                 int *__restrict__ bad_flag) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= routes) return;
+    const int e = ids[i];
+    if (e < 0 || e >= E) {
+        atomicExch(bad_flag, 1);
+        return;
+    }
+    atomicAdd(&counts[e], 1);
+}
+
+// Single block: exclusive prefix over the experts (offsets[E] = routes).
+__global__ void moe_prefix_kernel(const int *__restrict__ counts, int E, int *__restrict__ offsets) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        int p = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = p;
+            p += counts[e];
+        }
+        offsets[E] = p;
+    }
+}
+
+// One warp per expert walks the routes in order (token-major, slot-minor) and assigns stable
+// positions with ballots; writes the sorted token ids, the normalised weights
+// (renormalise policy: weight * (scale / sum of the token's weights), 0 when the sum <= FLT_MIN,
+// moe_ops.c:960-967) and the inverse map route -> position.
+__global__ void moe_scatter_kernel(const int32_t *__restrict__ ids, const float *__restrict__ weights, int T, int k,
+                                   const int *__restrict__ offsets, float weights_scale, int renormalize,
+                                   int32_t *__restrict__ sorted_tok, float *__restrict__ sorted_w,
+                                   int32_t *__restrict__ route_pos) {
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x;
+    const int routes = T * k;
+    int cursor = offsets[e];
+    for (int base = 0; base < routes; base += 32) {
+        const int i = base + lane;
+        const bool mine = i < routes && ids[i] == e;
+        const unsigned m = __ballot_sync(0xffffffffu, mine);
+        if (mine) {
+            const int pos = cursor + __popc(m & ((1u << lane) - 1u));
+            const int t = i / k;
+            float norm = weights_scale;
+            if (renormalize) {
+                float s = 0.0f;
+                for (int j = 0; j < k; ++j) s = __fadd_rn(s, weights[(size_t)t * k + j]);
+                norm = s > FLT_MIN ? __fdiv_rn(weights_scale, s) : 0.0f;
+            }
+            sorted_tok[pos] = t;
+            sorted_w[pos] = __fmul_rn(weights[i], norm);
+            route_pos[i] = pos;
+        }
+        cursor += __popc(m);
+    }
+}
+
+// route_hidden[r][:] = hidden[sorted_tok[r]][:]
+__global__ void moe_gather_kernel(const float *__restrict__ hidden, size_t ldh, const int32_t *__restrict__ sorted_tok,
+                                  int H, float *__restrict__ route_hidden) {
+    const int r = blockIdx.x;
+    const float *src = hidden + (size_t)sorted_tok[r] * ldh;
+    float *dst = route_hidden + (size_t)r * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = src[c];
+}
+
+// gate <- act(gate) * up; silu(x) = x / (1 + expf(-x)), gelu(x) = 0.5 x (1 + erff(x / sqrt 2))
+// (moe_ops.c:318-324,552-556)
+__global__ void moe_glu_kernel(float *__restrict__ gate, const float *__restrict__ up, size_t n, int geglu) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g = gate[i];
+    float a;
+    if (geglu) a = __fmul_rn(__fmul_rn(0.5f, g), __fadd_rn(1.0f, erff(__fmul_rn(g, 0.7071067811865475f))));
+    else a = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+    gate[i] = __fmul_rn(a, up[i]);
+}
+
+// out[t][c] = sum over the token's routes, in ascending sorted position (= the reference's route
+// order, moe_ops.c:1034-1042), of w * down[pos][c]; products and sums rounded separately.
+template <int MAXK>
+__global__ void moe_combine_kernel(const float *__restrict__ route_down, const float *__restrict__ sorted_w,
+                                   const int32_t *__restrict__ route_pos, int k, int H, float *__restrict__ out,
+                                   size_t ldo) {
+    const int t = blockIdx.x;
+    int pos[MAXK];
+    float w[MAXK];
+    for (int j = 0; j < k; ++j) pos[j] = route_pos[(size_t)t * k + j];
+    for (int i = 1; i < k; ++i) {  // insertion sort, k is tiny
+        const int p = pos[i];
+        int j = i;
+        while (j > 0 && pos[j - 1] > p) {
+            pos[j] = pos[j - 1];
+            --j;
+        }
+        pos[j] = p;
+    }
+    for (int j = 0; j < k; ++j) w[j] = sorted_w[pos[j]];
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < k; ++j) acc = __fadd_rn(acc, __fmul_rn(w[j], route_down[(size_t)pos[j] * H + c]));
+        out[(size_t)t * ldo + c] = acc;
+    }
+}
+
+cudaError_t launch_topk(const float *x, int rows, int cols, size_t ldx, int k, float *values, int32_t *indices,
+                        cudaStream_t s) {
+    if (rows <= 0) return cudaSuccess;
+    topk_kernel<<<(rows + 127) / 128, 128, 0, s>>>(x, rows, cols, ldx, k, values, indices);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_route(const int32_t *ids, const float *weights, int T, int k, int E, float weights_scale,
+                             int renormalize, const MoeRouteBuffers &b, cudaStream_t s) {
+    const int routes = T * k;
+    cudaError_t err = cudaMemsetAsync(b.counts, 0, (size_t)(E + 1) * sizeof(int), s);
+    if (err != cudaSuccess) return err;
+    moe_count_kernel<<<(routes + 255) / 256, 256, 0, s>>>(ids, routes, E, b.counts, b.counts + E);
+    moe_prefix_kernel<<<1, 32, 0, s>>>(b.counts, E, b.offsets);
+    moe_scatter_kernel<<<E, 32, 0, s>>>(ids, weights, T, k, b.offsets, weights_scale, renormalize, b.sorted_tok,
+                                        b.sorted_w, b.route_pos);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_gather(const float *hidden, size_t ldh, const int32_t *sorted_tok, int routes, int H,
+                              float *route_hidden, cudaStream_t s) {
+    if (routes <= 0) return cudaSuccess;
+    moe_gather_kernel<<<routes, 256, 0, s>>>(hidden, ldh, sorted_tok, H, route_hidden);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_glu(float *gate, const float *up, size_t n, int geglu, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    moe_glu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(gate, up, n, geglu);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_combine(const float *route_down, const float *sorted_w, const int32_t *route_pos, int T, int k,
+                               int H, float *out, size_t ldo, cudaStream_t s) {
+    if (T <= 0) return cudaSuccess;
+    if (k > MOE_MAX_TOPK) return cudaErrorInvalidValue;
+    moe_combine_kernel<MOE_MAX_TOPK><<<T, 256, 0, s>>>(route_down, sorted_w, route_pos, k, H, out, ldo);
+    return cudaGetLastError();
+}
+
+}  // namespace mcu

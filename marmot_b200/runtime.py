@@ -1,0 +1,198 @@
+"""ctypes binding of libmarmot_cuda.so.  Plumbing only: device buffers are torch tensors, every
+operation is one call through the C ABI declared in include/marmot_cuda.h."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libmarmot_cuda.so"
+
+KIND_Q8_0, KIND_Q4_K, KIND_Q6_K = 5, 9, 11
+KIND_BY_NAME = {"q8_0": KIND_Q8_0, "q4_k": KIND_Q4_K, "q6_k": KIND_Q6_K}
+BLOCK_VALUES = {KIND_Q8_0: 32, KIND_Q4_K: 256, KIND_Q6_K: 256}
+BLOCK_BYTES = {KIND_Q8_0: 34, KIND_Q4_K: 144, KIND_Q6_K: 210}
+REGIME_AUTO, REGIME_GEMV, REGIME_GEMM = 0, 1, 2
+ROUTER_SOFTMAX_SELECTED, ROUTER_RENORMALIZE_SELECTED = 0, 2
+FFN_SWIGLU, FFN_GEGLU = 0, 2
+
+# Every symbol include/marmot_cuda.h declares.
+EXPORTS = (
+    "mcu_context_create", "mcu_context_destroy", "mcu_context_set_stream", "mcu_context_get_stream",
+    "mcu_context_set_regime", "mcu_synchronize", "mcu_last_error_message", "mcu_kernel_launch_count",
+    "mcu_malloc", "mcu_free", "mcu_memcpy_to_device", "mcu_memcpy_to_host", "mcu_row_bytes", "mcu_dequantize",
+    "mcu_quantize_activations", "mcu_linear", "mcu_linear_dual", "mcu_linear_host", "mcu_topk", "mcu_moe_experts",
+)
+
+
+class MarmotCudaError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"marmot_cuda error {code}: {message}")
+        self.code = code
+
+
+def row_bytes(kind: int, K: int) -> int:
+    bv = BLOCK_VALUES[kind]
+    return (K + bv - 1) // bv * BLOCK_BYTES[kind]
+
+
+_lib = None
+
+
+def load_library() -> C.CDLL:
+    """Load libmarmot_cuda.so; there is no fallback if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise FileNotFoundError(
+            f"{LIB_PATH} is missing: build it with `python -m marmot_b200.build` (needs nvcc); "
+            "marmot_b200 has no CPU or PyTorch fallback"
+        )
+    L = C.CDLL(str(LIB_PATH))
+    vp, sz, i32, f32 = C.c_void_p, C.c_size_t, C.c_int, C.c_float
+    L.mcu_context_create.argtypes = [i32, C.POINTER(vp)]
+    L.mcu_context_destroy.argtypes = [vp]
+    L.mcu_context_destroy.restype = None
+    L.mcu_context_set_stream.argtypes = [vp, vp]
+    L.mcu_context_get_stream.argtypes = [vp]
+    L.mcu_context_get_stream.restype = vp
+    L.mcu_context_set_regime.argtypes = [vp, i32]
+    L.mcu_synchronize.argtypes = [vp]
+    L.mcu_last_error_message.restype = C.c_char_p
+    L.mcu_kernel_launch_count.argtypes = [vp]
+    L.mcu_kernel_launch_count.restype = C.c_uint64
+    L.mcu_malloc.argtypes = [vp, sz, C.POINTER(vp)]
+    L.mcu_free.argtypes = [vp, vp]
+    L.mcu_memcpy_to_device.argtypes = [vp, vp, vp, sz]
+    L.mcu_memcpy_to_host.argtypes = [vp, vp, vp, sz]
+    L.mcu_row_bytes.argtypes = [i32, sz]
+    L.mcu_row_bytes.restype = sz
+    L.mcu_dequantize.argtypes = [vp, i32, vp, sz, vp]
+    L.mcu_quantize_activations.argtypes = [vp, i32, vp, sz, sz, sz, vp, vp, vp]
+    L.mcu_linear.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
+    L.mcu_linear_dual.argtypes = [vp, i32, vp, sz, vp, vp, sz, sz, sz, vp, vp, sz]
+    L.mcu_linear_host.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
+    L.mcu_topk.argtypes = [vp, vp, sz, sz, sz, sz, vp, vp]
+    L.mcu_moe_experts.argtypes = [vp, i32, i32, i32, vp, sz, sz, sz, sz, vp, vp, vp, vp, vp, sz, i32, f32, i32, vp]
+    _lib = L
+    return L
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else int(t.data_ptr())
+
+
+class Context:
+    """One mcu_context_t on one device.  Tensors passed in must live on that device."""
+
+    def __init__(self, device: int = 0, use_torch_stream: bool = True):
+        import torch
+
+        self.torch = torch
+        self.lib = load_library()
+        self.device = device
+        h = C.c_void_p()
+        self._check(self.lib.mcu_context_create(device, C.byref(h)))
+        self.handle = h
+        if use_torch_stream:
+            with torch.cuda.device(device):
+                stream = torch.cuda.current_stream().cuda_stream
+            self._check(self.lib.mcu_context_set_stream(self.handle, C.c_void_p(stream)))
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.mcu_context_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc != 0:
+            raise MarmotCudaError(rc, self.lib.mcu_last_error_message().decode())
+
+    # -- helpers -----------------------------------------------------------
+    def upload(self, host: np.ndarray):
+        """Host bytes -> device tensor (uint8), the one-time residency step for weights."""
+        t = self.torch.from_numpy(np.ascontiguousarray(host).view(np.uint8).reshape(-1))
+        return t.to(f"cuda:{self.device}")
+
+    def set_regime(self, regime: int):
+        self._check(self.lib.mcu_context_set_regime(self.handle, regime))
+
+    def synchronize(self):
+        self._check(self.lib.mcu_synchronize(self.handle))
+
+    def launch_count(self) -> int:
+        return int(self.lib.mcu_kernel_launch_count(self.handle))
+
+    # -- operations ----------------------------------------------------------
+    def dequantize(self, kind: int, blocks, n_values: int):
+        out = self.torch.empty(n_values, dtype=self.torch.float32, device=blocks.device)
+        self._check(self.lib.mcu_dequantize(self.handle, kind, _ptr(blocks), n_values, _ptr(out)))
+        return out
+
+    def quantize_activations(self, weight_kind: int, x):
+        T, K = x.shape
+        bv = BLOCK_VALUES[weight_kind]
+        nb = (K + bv - 1) // bv
+        tc = self.torch
+        qs = tc.empty((T, nb * bv), dtype=tc.int8, device=x.device)
+        d = tc.empty((T, nb), dtype=tc.float32, device=x.device)
+        bs = tc.empty((T, nb * 16), dtype=tc.int16, device=x.device) if weight_kind != KIND_Q8_0 else None
+        self._check(self.lib.mcu_quantize_activations(self.handle, weight_kind, _ptr(x), x.stride(0), T, K, _ptr(qs),
+                                                      _ptr(d), _ptr(bs)))
+        return qs, d, bs
+
+    def linear(self, kind: int, x, w, F: int, bias=None, out=None):
+        T, K = x.shape
+        assert x.stride(1) == 1 and w.numel() * w.element_size() >= F * row_bytes(kind, K)
+        if out is None:
+            out = self.torch.empty((T, F), dtype=self.torch.float32, device=x.device)
+        self._check(self.lib.mcu_linear(self.handle, kind, _ptr(x), x.stride(0), _ptr(w), T, K, F, _ptr(bias), _ptr(out),
+                                        out.stride(0)))
+        return out
+
+    def linear_dual(self, kind: int, x, w_a, w_b, F: int):
+        T, K = x.shape
+        tc = self.torch
+        oa = tc.empty((T, F), dtype=tc.float32, device=x.device)
+        ob = tc.empty((T, F), dtype=tc.float32, device=x.device)
+        self._check(self.lib.mcu_linear_dual(self.handle, kind, _ptr(x), x.stride(0), _ptr(w_a), _ptr(w_b), T, K, F,
+                                             _ptr(oa), _ptr(ob), F))
+        return oa, ob
+
+    def linear_host(self, kind: int, x_host: np.ndarray, w, F: int, bias_host: np.ndarray | None = None,
+                    out_host: np.ndarray | None = None) -> np.ndarray:
+        """Host activations in, host result out; weights device resident."""
+        T, K = x_host.shape
+        if out_host is None:
+            out_host = np.empty((T, F), dtype=np.float32)
+        bp = None if bias_host is None else bias_host.ctypes.data
+        self._check(self.lib.mcu_linear_host(self.handle, kind, x_host.ctypes.data, x_host.strides[0] // 4, _ptr(w), T, K,
+                                             F, bp, out_host.ctypes.data, out_host.strides[0] // 4))
+        return out_host
+
+    def topk(self, x, k: int):
+        rows, cols = x.shape
+        tc = self.torch
+        vals = tc.empty((rows, k), dtype=tc.float32, device=x.device)
+        idx = tc.empty((rows, k), dtype=tc.int32, device=x.device)
+        self._check(self.lib.mcu_topk(self.handle, _ptr(x), rows, cols, x.stride(0), k, _ptr(vals), _ptr(idx)))
+        return vals, idx
+
+    def moe_experts(self, kinds, hidden, gate, up, down, topk_ids, topk_weights, FF: int, E: int,
+                    ffn_type: int = FFN_SWIGLU, weights_scale: float = 1.0, policy: int = ROUTER_RENORMALIZE_SELECTED):
+        T, H = hidden.shape
+        k = topk_ids.shape[1]
+        out = self.torch.empty((T, H), dtype=self.torch.float32, device=hidden.device)
+        self._check(self.lib.mcu_moe_experts(self.handle, kinds[0], kinds[1], kinds[2], _ptr(hidden), T, H, FF, E,
+                                             _ptr(gate), _ptr(up), _ptr(down), _ptr(topk_ids), _ptr(topk_weights), k,
+                                             ffn_type, weights_scale, policy, _ptr(out)))
+        return out

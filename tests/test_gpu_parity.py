@@ -1,0 +1,291 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle, the reference's golden vectors
+and fixtures produced by the reference library.  Integer / bit-level work is compared exactly;
+matmul outputs within the tolerances in tests/util.py."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from tests.util import (BLOCK_VALUES, KIND_Q4_K, KIND_Q6_K, KIND_Q8_0, KINDS, TOL_FP32, cosine, max_rel_err,
+                        random_blocks, row_bytes, unpack_q8_0, unpack_q8_k, unsplit_q8_k)
+
+pytestmark = pytest.mark.gpu
+
+NAMES = ["q4_k", "q6_k", "q8_0"]
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from marmot_b200 import Context
+
+    c = Context(0)
+    yield c
+    c.close()
+
+
+def dev(ctx, a):
+    import torch
+
+    return torch.from_numpy(np.ascontiguousarray(a)).to("cuda:0")
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+# ---------------------------------------------------------------- dequantize (bit-exact)
+@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("rows,K", [(1, 256), (3, 768), (64, 4096)])
+def test_dequantize_bit_exact(ctx, oracle, name, rows, K):
+    kind = KINDS[name]
+    rng = np.random.default_rng(rows * 1000 + K)
+    W = random_blocks(kind, rows, K, rng)
+    n = rows * K
+    got = ctx.dequantize(kind, ctx.upload(W), n).cpu().numpy()
+    assert np.array_equal(bits(got), bits(oracle.dequantize(kind, W, n)))
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_dequantize_ragged_tail_and_golden(ctx, oracle, llama_goldens, name):
+    kind = KINDS[name]
+    rng = np.random.default_rng(5)
+    W = random_blocks(kind, 1, 2 * BLOCK_VALUES[kind], rng)
+    n = 2 * BLOCK_VALUES[kind] - 7  # count not a multiple of the block size
+    got = ctx.dequantize(kind, ctx.upload(W), n).cpu().numpy()
+    assert np.array_equal(bits(got), bits(oracle.dequantize(kind, W, n)))
+    exp = llama_goldens[f"llama_{name}_dequant"]
+    got = ctx.dequantize(kind, ctx.upload(llama_goldens[f"llama_{name}"]), exp.size).cpu().numpy()
+    assert np.max(np.abs(got - exp)) <= 5e-4  # tolerance of tests/backend/test_backend_quantization.c
+
+
+# ---------------------------------------------------------------- activation packers (bit-exact)
+@pytest.mark.parametrize("T,K", [(1, 256), (3, 700), (5, 4096), (2, 31)])
+def test_quantize_activations_q8_k_bit_exact(ctx, oracle, T, K):
+    rng = np.random.default_rng(T * 31 + K)
+    x = rng.normal(0, 1, (T, K)).astype(np.float32)
+    x[0, : min(K, 256)] = 0.0  # an all-zero block
+    if K > 300:
+        x[T - 1, 260] = -x[T - 1, 270] if x[T - 1, 270] != 0 else 1.0
+        x[T - 1, 260:272] = np.float32(3.5)  # ties on |x|: the first one decides the sign
+        x[T - 1, 265] = np.float32(-3.5)
+    qs, d, bs = ctx.quantize_activations(KIND_Q4_K, dev(ctx, x))
+    nb = (K + 255) // 256
+    ref = np.concatenate([oracle.pack_q8_k(x[t]) for t in range(T)])
+    rq, rd, rb = unpack_q8_k(ref, T, nb)
+    assert np.array_equal(unsplit_q8_k(qs.cpu().numpy()), rq)
+    assert np.array_equal(bits(d.cpu().numpy()), bits(rd))
+    assert np.array_equal(bs.cpu().numpy(), rb)
+
+
+@pytest.mark.parametrize("T,K", [(1, 32), (4, 100), (3, 4096)])
+def test_quantize_activations_q8_0_bit_exact(ctx, oracle, T, K):
+    rng = np.random.default_rng(T * 77 + K)
+    x = rng.normal(0, 1, (T, K)).astype(np.float32)
+    x[0, :32] = 0.0
+    x[T - 1, :8] = np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 126.5, -126.5], dtype=np.float32)  # round half away
+    if K >= 8:
+        x[T - 1, 7 if K < 32 else 31] = np.float32(127.0)  # makes the scale exactly 1
+    qs, d, _ = ctx.quantize_activations(KIND_Q8_0, dev(ctx, x))
+    nb = (K + 31) // 32
+    ref = np.concatenate([oracle.pack_q8_0(x[t]) for t in range(T)])
+    rq, rd = unpack_q8_0(ref, T, nb)
+    assert np.array_equal(qs.cpu().numpy(), rq)
+    assert np.array_equal(bits(d.cpu().numpy()), bits(rd))
+
+
+# ---------------------------------------------------------------- linear
+SHAPES = [(1, 256, 1), (1, 4096, 64), (2, 768, 13), (3, 1024, 40), (5, 2304, 9), (8, 512, 33), (9, 512, 17),
+          (17, 1280, 24), (33, 256, 65)]
+
+
+@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("T,K,F", SHAPES)
+def test_linear_vs_oracle(ctx, oracle, name, T, K, F):
+    kind = KINDS[name]
+    rng = np.random.default_rng(kind * 1000003 + T * 100003 + K * 101 + F)
+    W = random_blocks(kind, F, K, rng)
+    x = rng.normal(0, 1, (T, K)).astype(np.float32)
+    got = ctx.linear(kind, dev(ctx, x), ctx.upload(W), F).cpu().numpy()
+    ref = oracle.linear(kind, x, W, F)
+    assert max_rel_err(got, ref) <= TOL_FP32
+    assert cosine(got, ref) >= 0.999
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_linear_ragged_k_strided_input_and_bias(ctx, oracle, name):
+    kind = KINDS[name]
+    bv = BLOCK_VALUES[kind]
+    T, K, F = 3, 2 * bv + bv // 2 + 3, 11  # K not a multiple of the block size
+    rng = np.random.default_rng(11)
+    W = random_blocks(kind, F, K, rng)
+    xfull = rng.normal(0, 1, (T, K + 5)).astype(np.float32)
+    x = xfull[:, :K]
+    bias = rng.normal(0, 1, F).astype(np.float32)
+    xd = dev(ctx, xfull)[:, :K]  # row stride K+5
+    got = ctx.linear(kind, xd, ctx.upload(W), F, bias=dev(ctx, bias)).cpu().numpy()
+    ref = oracle.linear(kind, np.ascontiguousarray(x), W, F, bias=bias)
+    assert max_rel_err(got, ref) <= TOL_FP32
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_linear_llama_golden(ctx, llama_goldens, name):
+    T, K, F = (int(v) for v in llama_goldens[f"matmul_{name}_dims"])
+    x = llama_goldens[f"matmul_{name}_input_f32"].reshape(T, K)
+    got = ctx.linear(KINDS[name], dev(ctx, x), ctx.upload(llama_goldens[f"matmul_{name}_weight"]), F).cpu().numpy()
+    exp = llama_goldens[f"matmul_{name}_output_from_f32"].reshape(T, F)
+    # the reference's own tolerance, tests/backend/test_matmul_quantized.c:163-166
+    assert np.all(np.abs(got - exp) <= np.abs(exp) * 5e-5 + 2e-5)
+
+
+@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("case", [0, 1, 2])
+def test_linear_reference_fixture(ctx, ref_cases, name, case):
+    kind = KINDS[name]
+    x, W = ref_cases[f"{name}_{case}_x"], ref_cases[f"{name}_{case}_w"]
+    T, K = x.shape
+    F = W.size // row_bytes(kind, K)
+    wd = ctx.upload(W)
+    deq = ctx.dequantize(kind, wd, F * K).cpu().numpy()
+    assert np.array_equal(bits(deq), bits(ref_cases[f"{name}_{case}_deq"]))
+    got = ctx.linear(kind, dev(ctx, x), wd, F).cpu().numpy()
+    assert max_rel_err(got, ref_cases[f"{name}_{case}_y"]) <= TOL_FP32
+
+
+@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("T", [1, 4, 12])
+def test_dual_output_equals_two_singles(ctx, name, T):
+    # tests/backend/test_matmul_quantized.c:202-298: dual-output == two single calls
+    kind = KINDS[name]
+    K, F = 1024, 48
+    rng = np.random.default_rng(T)
+    Wa, Wb = ctx.upload(random_blocks(kind, F, K, rng)), ctx.upload(random_blocks(kind, F, K, rng))
+    x = dev(ctx, rng.normal(0, 1, (T, K)).astype(np.float32))
+    oa, ob = ctx.linear_dual(kind, x, Wa, Wb, F)
+    assert np.array_equal(bits(oa.cpu().numpy()), bits(ctx.linear(kind, x, Wa, F).cpu().numpy()))
+    assert np.array_equal(bits(ob.cpu().numpy()), bits(ctx.linear(kind, x, Wb, F).cpu().numpy()))
+
+
+def test_linear_host_buffers(ctx, oracle):
+    kind, T, K, F = KIND_Q4_K, 2, 1024, 96
+    rng = np.random.default_rng(3)
+    W = random_blocks(kind, F, K, rng)
+    x = rng.normal(0, 1, (T, K)).astype(np.float32)
+    bias = rng.normal(0, 1, F).astype(np.float32)
+    got = ctx.linear_host(kind, x, ctx.upload(W), F, bias_host=bias)
+    assert max_rel_err(got, oracle.linear(kind, x, W, F, bias=bias)) <= TOL_FP32
+
+
+def test_config_q4k_gemv_full_size(ctx, oracle):
+    """The single-token Q4_K GEMV at 4096 x 4096 with the benchmark's value distributions."""
+    kind, T, K, F = KIND_Q4_K, 1, 4096, 4096
+    rng = np.random.default_rng(0xB200)
+    W = random_blocks(kind, F, K, rng)
+    x = rng.normal(0, 1, (T, K)).astype(np.float32)
+    got = ctx.linear(kind, dev(ctx, x), ctx.upload(W), F).cpu().numpy()
+    ref = oracle.linear(kind, x, W, F)
+    assert max_rel_err(got, ref) <= TOL_FP32 and cosine(got, ref) >= 0.999
+
+
+def test_linearity_in_the_dequantised_weights(ctx):
+    """Size-independent property: the matmul is linear in the output rows, so stacking two weight
+    matrices stacks the outputs (checked bit for bit)."""
+    kind, T, K, F = KIND_Q6_K, 4, 2048, 256
+    rng = np.random.default_rng(9)
+    Wa, Wb = random_blocks(kind, F, K, rng), random_blocks(kind, F, K, rng)
+    x = dev(ctx, rng.normal(0, 1, (T, K)).astype(np.float32))
+    both = ctx.linear(kind, x, ctx.upload(np.concatenate([Wa, Wb])), 2 * F).cpu().numpy()
+    a = ctx.linear(kind, x, ctx.upload(Wa), F).cpu().numpy()
+    b = ctx.linear(kind, x, ctx.upload(Wb), F).cpu().numpy()
+    assert np.array_equal(bits(both[:, :F]), bits(a)) and np.array_equal(bits(both[:, F:]), bits(b))
+
+
+def test_zero_sized_inputs(ctx):
+    import torch
+
+    x = torch.empty((0, 256), dtype=torch.float32, device="cuda:0")
+    W = ctx.upload(random_blocks(KIND_Q4_K, 4, 256, np.random.default_rng(0)))
+    assert ctx.linear(KIND_Q4_K, x, W, 4).shape == (0, 4)
+
+
+def test_error_codes(ctx):
+    import torch
+    from marmot_b200 import MarmotCudaError
+
+    x = torch.zeros((1, 256), dtype=torch.float32, device="cuda:0")
+    W = ctx.upload(random_blocks(KIND_Q4_K, 4, 256, np.random.default_rng(0)))
+    with pytest.raises(MarmotCudaError) as e:
+        ctx.linear(4, x, W, 4)  # Q5_1 has no CUDA kernel
+    assert e.value.code == -8
+    lib = ctx.lib
+    assert lib.mcu_linear(ctx.handle, KIND_Q4_K, None, 256, W.data_ptr(), 1, 256, 4, None, x.data_ptr(), 4) == -1
+    assert lib.mcu_linear(ctx.handle, KIND_Q4_K, x.data_ptr(), 100, W.data_ptr(), 1, 256, 4, None, x.data_ptr(), 4) == -7
+    # a misaligned Q4_K weight pointer is rejected rather than read with vector loads
+    assert lib.mcu_linear(ctx.handle, KIND_Q4_K, x.data_ptr(), 256, W.data_ptr() + 2, 1, 256, 1, None, x.data_ptr(), 4) == -1
+
+
+# ---------------------------------------------------------------- MoE
+def test_topk_matches_oracle_with_ties(ctx, oracle):
+    rng = np.random.default_rng(1)
+    x = rng.integers(0, 4, (257, 8)).astype(np.float32)  # many ties
+    vals, idx = ctx.topk(dev(ctx, x), 3)
+    rv, ri = oracle.topk(x, 3)
+    assert np.array_equal(idx.cpu().numpy(), ri) and np.array_equal(bits(vals.cpu().numpy()), bits(rv))
+
+
+def _moe_case(rng, T, H, FF, E, k, kinds):
+    hid = rng.normal(0, 1, (T, H)).astype(np.float32)
+    gate = np.concatenate([random_blocks(kinds[0], FF, H, rng) for _ in range(E)])
+    up = np.concatenate([random_blocks(kinds[1], FF, H, rng) for _ in range(E)])
+    down = np.concatenate([random_blocks(kinds[2], H, FF, rng, d_sigma=0.0005) for _ in range(E)])
+    logits = rng.normal(0, 1, (T, E)).astype(np.float32)
+    p = np.exp(logits - logits.max(1, keepdims=True))
+    p = (p / p.sum(1, keepdims=True)).astype(np.float32)
+    return hid, gate, up, down, p
+
+
+@pytest.mark.parametrize("T,k,policy,scale", [(37, 2, 2, 1.0), (3, 2, 2, 1.0), (20, 3, 0, 0.5), (9, 1, 2, 1.0)])
+def test_moe_experts_vs_oracle(ctx, oracle, T, k, policy, scale):
+    H, FF, E = 256, 512, 4
+    kinds = (KIND_Q4_K, KIND_Q4_K, KIND_Q6_K)
+    rng = np.random.default_rng(T * 10 + k)
+    hid, gate, up, down, p = _moe_case(rng, T, H, FF, E, k, kinds)
+    vals, ids = oracle.topk(p, k)
+    ref = oracle.moe_experts(kinds, hid, gate, up, down, ids, vals, FF, E, weights_scale=scale, policy=policy)
+    got = ctx.moe_experts(kinds, dev(ctx, hid), ctx.upload(gate), ctx.upload(up), ctx.upload(down), dev(ctx, ids),
+                          dev(ctx, vals), FF, E, weights_scale=scale, policy=policy).cpu().numpy()
+    assert max_rel_err(got, ref) <= TOL_FP32 and cosine(got, ref) >= 0.999
+
+
+def test_moe_reference_fixture(ctx, ref_cases):
+    T, H, FF, E, k = (int(v) for v in ref_cases["moe_dims"])
+    kinds = (KIND_Q4_K, KIND_Q4_K, KIND_Q6_K)
+    got = ctx.moe_experts(kinds, dev(ctx, ref_cases["moe_hidden"]), ctx.upload(ref_cases["moe_gate"]),
+                          ctx.upload(ref_cases["moe_up"]), ctx.upload(ref_cases["moe_down"]),
+                          dev(ctx, ref_cases["moe_ids"]), dev(ctx, ref_cases["moe_weights"]), FF, E).cpu().numpy()
+    assert max_rel_err(got, ref_cases["moe_out_renorm"]) <= TOL_FP32
+
+
+def test_moe_duplicate_routes_and_unused_experts(ctx, oracle):
+    # tests/backend/test_backend_moe.c: duplicate expert ids for one token; experts nobody selects
+    H, FF, E, k, T = 256, 256, 6, 2, 5
+    kinds = (KIND_Q8_0, KIND_Q8_0, KIND_Q8_0)
+    rng = np.random.default_rng(2)
+    hid, gate, up, down, _ = _moe_case(rng, T, H, FF, E, k, kinds)
+    ids = np.array([[1, 1], [4, 1], [1, 4], [4, 4], [1, 4]], dtype=np.int32)
+    wts = rng.uniform(0.1, 1.0, (T, k)).astype(np.float32)
+    ref = oracle.moe_experts(kinds, hid, gate, up, down, ids, wts, FF, E)
+    got = ctx.moe_experts(kinds, dev(ctx, hid), ctx.upload(gate), ctx.upload(up), ctx.upload(down), dev(ctx, ids),
+                          dev(ctx, wts), FF, E).cpu().numpy()
+    assert max_rel_err(got, ref) <= TOL_FP32
+    from marmot_b200 import MarmotCudaError
+
+    bad = ids.copy()
+    bad[0, 0] = E
+    with pytest.raises(MarmotCudaError) as e:
+        ctx.moe_experts(kinds, dev(ctx, hid), ctx.upload(gate), ctx.upload(up), ctx.upload(down), dev(ctx, bad),
+                        dev(ctx, wts), FF, E)
+    assert e.value.code == -1
