@@ -51,7 +51,12 @@ enum { MCU_FFN_SWIGLU = 0, MCU_FFN_GELU = 1, MCU_FFN_GEGLU = 2 };
 
 /* Regime override for mcu_linear*: the analogue of the reference's MARMOT_METAL_FORCE_{MV,MM}
  * switches (src/backends/metal/ops/matmul_quant_dispatch.mm:41). */
-enum { MCU_REGIME_AUTO = 0, MCU_REGIME_GEMV = 1, MCU_REGIME_GEMM = 2 };
+enum {
+    MCU_REGIME_AUTO = 0,
+    MCU_REGIME_GEMV = 1,       /* decode kernels for every T (tokens processed eight at a time) */
+    MCU_REGIME_GEMM = 2,       /* tensor-core kernel for every T */
+    MCU_REGIME_GEMV_PLAIN = 3, /* decode kernels without the shared-memory streaming variant */
+};
 
 typedef struct mcu_context mcu_context_t;
 
@@ -60,7 +65,8 @@ typedef struct mcu_context mcu_context_t;
  *      (src/backends/cpu/runtime/runtime.c:1409-1443, src/backends/cpu/dispatch/device_ops.c:12-30). ---- */
 int mcu_context_create(int device, mcu_context_t **out);
 void mcu_context_destroy(mcu_context_t *ctx);
-/* Use a stream owned by the caller (cudaStream_t passed as void*); NULL restores the context's own. */
+/* Use a stream owned by the caller (cudaStream_t passed as void*); NULL restores the context's own
+ * non-blocking stream.  To run on the legacy default stream pass cudaStreamLegacy ((void*)0x1). */
 int mcu_context_set_stream(mcu_context_t *ctx, void *cuda_stream);
 void *mcu_context_get_stream(mcu_context_t *ctx);
 int mcu_context_set_regime(mcu_context_t *ctx, int regime);

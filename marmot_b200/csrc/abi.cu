@@ -66,6 +66,7 @@ struct mcu_context {
     Buffer act_qs, act_d, act_bsums, act_half, x_stage, out_stage, bias_stage;
     Buffer moe_meta, moe_hidden, moe_gate, moe_up, moe_down;
     std::vector<int> host_counts;
+    int *dev_err = nullptr;  // set by kernels whose bounded device-side waits ran out
 };
 
 static int ensure(mcu_context *ctx, Buffer &b, size_t bytes) {
@@ -78,6 +79,17 @@ static int ensure(mcu_context *ctx, Buffer &b, size_t bytes) {
     const size_t want = (bytes + 255) & ~(size_t)255;
     MCU_CUDA(cudaMalloc(&b.ptr, want));
     b.cap = want;
+    return MCU_SUCCESS;
+}
+
+// After a synchronize: did a kernel give up on a bounded wait?
+static int check_device_error(mcu_context *ctx) {
+    int flag = 0;
+    MCU_CUDA(cudaMemcpy(&flag, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (flag != 0) {
+        cudaMemset(ctx->dev_err, 0, sizeof(int));
+        return fail(MCU_ERROR_INVALID_OPERATION, "a device-side wait timed out (code %d)", flag);
+    }
     return MCU_SUCCESS;
 }
 
@@ -117,6 +129,13 @@ int mcu_context_create(int device, mcu_context_t **out) {
         return cuda_fail(e, "cudaStreamCreate");
     }
     ctx->stream = ctx->own_stream;
+    e = cudaMalloc(&ctx->dev_err, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->dev_err, 0, sizeof(int));
+    if (e != cudaSuccess) {
+        cudaStreamDestroy(ctx->own_stream);
+        delete ctx;
+        return cuda_fail(e, "cudaMalloc(error flag)");
+    }
     const char *env = getenv("MARMOT_CUDA_FORCE_GEMV");
     if (env != nullptr && env[0] == '1') ctx->regime = MCU_REGIME_GEMV;
     env = getenv("MARMOT_CUDA_FORCE_GEMM");
@@ -133,6 +152,7 @@ void mcu_context_destroy(mcu_context_t *ctx) {
                       &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down};
     for (Buffer *b : bufs)
         if (b->ptr != nullptr) cudaFree(b->ptr);
+    if (ctx->dev_err != nullptr) cudaFree(ctx->dev_err);
     if (ctx->own_stream != nullptr) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
 }
@@ -149,7 +169,7 @@ void *mcu_context_get_stream(mcu_context_t *ctx) { return ctx != nullptr ? (void
 
 int mcu_context_set_regime(mcu_context_t *ctx, int regime) {
     if (ctx == nullptr) return fail(MCU_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
-    if (regime < MCU_REGIME_AUTO || regime > MCU_REGIME_GEMM) return fail(MCU_ERROR_INVALID_ARGUMENT, "bad regime");
+    if (regime < MCU_REGIME_AUTO || regime > MCU_REGIME_GEMV_PLAIN) return fail(MCU_ERROR_INVALID_ARGUMENT, "bad regime");
     ctx->regime = regime;
     return MCU_SUCCESS;
 }
@@ -157,7 +177,7 @@ int mcu_context_set_regime(mcu_context_t *ctx, int regime) {
 int mcu_synchronize(mcu_context_t *ctx) {
     if (int rc = check_ctx(ctx)) return rc;
     MCU_CUDA(cudaStreamSynchronize(ctx->stream));
-    return MCU_SUCCESS;
+    return check_device_error(ctx);
 }
 
 int mcu_malloc(mcu_context_t *ctx, size_t bytes, void **out_dev) {
@@ -266,6 +286,13 @@ static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx,
         if (ctx->regime == MCU_REGIME_GEMM)
             return fail(MCU_ERROR_NOT_IMPLEMENTED, "tensor-core GEMM does not cover kind %d T=%zu K=%zu F=%zu", kind, T, K, F);
     }
+    if (ctx->regime != MCU_REGIME_GEMV_PLAIN && T <= (size_t)GEMV_MAX_T &&
+        gemv_stream_supported(kind, w, w2, (int)T, (int)K, (int)F)) {
+        MCU_CUDA(launch_gemv_stream(kind, w, w2, x, (int)ldx, (int)T, (int)K, (int)F, bias, out, out2, (int)ldo,
+                                    ctx->dev_err, ctx->stream));
+        count_launches(1);
+        return MCU_SUCCESS;
+    }
     if (int rc = pack_activations(ctx, kind, x, ldx, T, K, false, ab)) return rc;
     const size_t bv = (size_t)block_values(kind);
     const size_t nb = (K + bv - 1) / bv, kp = nb * bv;
@@ -299,6 +326,8 @@ int mcu_quantize_activations(mcu_context_t *ctx, int weight_kind, const float *x
 int mcu_linear(mcu_context_t *ctx, int kind, const float *x_dev, size_t ldx, const void *w_dev, size_t T, size_t K,
                size_t F, const float *bias_dev, float *out_dev, size_t ldo) {
     if (int rc = check_ctx(ctx)) return rc;
+    if (!kind_supported(kind)) return fail(MCU_ERROR_NOT_IMPLEMENTED, "quant kind %d has no CUDA kernel", kind);
+    if (T == 0 || F == 0) return MCU_SUCCESS;
     if (int rc = validate_linear(kind, x_dev, w_dev, out_dev, T, K, F, ldx, ldo)) return rc;
     std::lock_guard<std::mutex> lock(ctx->mu);
     return linear_locked(ctx, kind, x_dev, ldx, w_dev, nullptr, T, K, F, bias_dev, out_dev, nullptr, ldo);
@@ -334,7 +363,7 @@ int mcu_linear_host(mcu_context_t *ctx, int kind, const float *x_host, size_t ld
     MCU_CUDA(cudaMemcpy2DAsync(out_host, ldo * sizeof(float), od, F * sizeof(float), F * sizeof(float), T,
                                cudaMemcpyDeviceToHost, ctx->stream));
     MCU_CUDA(cudaStreamSynchronize(ctx->stream));
-    return MCU_SUCCESS;
+    return check_device_error(ctx);
 }
 
 int mcu_topk(mcu_context_t *ctx, const float *x_dev, size_t rows, size_t cols, size_t ldx, size_t k, float *values_dev,

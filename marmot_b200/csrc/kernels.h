@@ -29,6 +29,13 @@ constexpr int GEMV_MAX_T = 8;
 cudaError_t launch_gemv(int kind, const void *W, const void *W2, const ActBuffers &a, int T, int K, int F,
                         const float *bias, float *out, float *out2, int ldo, cudaStream_t s);
 
+// Streaming variant of the decode-regime matmul: activation quantisation fused in, weights streamed through
+// shared memory with bulk asynchronous copies, launched with programmatic stream serialization.
+// *err_flag (device int) receives a non-zero code if a bounded device-side wait ran out.
+bool gemv_stream_supported(int kind, const void *W, const void *W2, int T, int K, int F);
+cudaError_t launch_gemv_stream(int kind, const void *W, const void *W2, const float *x, int ldx, int T, int K, int F,
+                               const float *bias, float *out, float *out2, int ldo, int *err_flag, cudaStream_t s);
+
 // Prefill / batched regime on the tcgen05 tensor cores: weights dequantised to fp16 tiles in shared
 // memory, activations given as fp16 (d*q of the quantized activations, row stride ldxh), f32
 // accumulation in tensor memory.

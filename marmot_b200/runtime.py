@@ -14,7 +14,7 @@ KIND_Q8_0, KIND_Q4_K, KIND_Q6_K = 5, 9, 11
 KIND_BY_NAME = {"q8_0": KIND_Q8_0, "q4_k": KIND_Q4_K, "q6_k": KIND_Q6_K}
 BLOCK_VALUES = {KIND_Q8_0: 32, KIND_Q4_K: 256, KIND_Q6_K: 256}
 BLOCK_BYTES = {KIND_Q8_0: 34, KIND_Q4_K: 144, KIND_Q6_K: 210}
-REGIME_AUTO, REGIME_GEMV, REGIME_GEMM = 0, 1, 2
+REGIME_AUTO, REGIME_GEMV, REGIME_GEMM, REGIME_GEMV_PLAIN = 0, 1, 2, 3
 ROUTER_SOFTMAX_SELECTED, ROUTER_RENORMALIZE_SELECTED = 0, 2
 FFN_SWIGLU, FFN_GEGLU = 0, 2
 
@@ -99,7 +99,9 @@ class Context:
         self.handle = h
         if use_torch_stream:
             with torch.cuda.device(device):
-                stream = torch.cuda.current_stream().cuda_stream
+                # torch reports the legacy default stream as handle 0, which this ABI reads as
+                # "use the context's own stream"; cudaStreamLegacy (0x1) names it explicitly.
+                stream = torch.cuda.current_stream().cuda_stream or 1
             self._check(self.lib.mcu_context_set_stream(self.handle, C.c_void_p(stream)))
 
     def close(self):
@@ -122,6 +124,10 @@ class Context:
         """Host bytes -> device tensor (uint8), the one-time residency step for weights."""
         t = self.torch.from_numpy(np.ascontiguousarray(host).view(np.uint8).reshape(-1))
         return t.to(f"cuda:{self.device}")
+
+    def set_stream(self, cuda_stream: int):
+        """Run on the given cudaStream_t handle (0 is mapped to cudaStreamLegacy)."""
+        self._check(self.lib.mcu_context_set_stream(self.handle, C.c_void_p(cuda_stream or 1)))
 
     def set_regime(self, regime: int):
         self._check(self.lib.mcu_context_set_regime(self.handle, regime))

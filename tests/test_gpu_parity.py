@@ -102,21 +102,33 @@ SHAPES = [(1, 256, 1), (1, 4096, 64), (2, 768, 13), (3, 1024, 40), (5, 2304, 9),
           (17, 1280, 24), (33, 256, 65)]
 
 
+@pytest.fixture(params=["auto", "plain"])
+def variant(request, ctx):
+    """Decode kernels: the shared-memory streaming variant (picked automatically when the shape allows)
+    and the plain-load variant."""
+    from marmot_b200.runtime import REGIME_AUTO, REGIME_GEMV_PLAIN
+
+    ctx.set_regime(REGIME_GEMV_PLAIN if request.param == "plain" else REGIME_AUTO)
+    yield request.param
+    ctx.set_regime(REGIME_AUTO)
+
+
 @pytest.mark.parametrize("name", NAMES)
-@pytest.mark.parametrize("T,K,F", SHAPES)
-def test_linear_vs_oracle(ctx, oracle, name, T, K, F):
+@pytest.mark.parametrize("T,K,F", SHAPES + [(4, 14336, 40), (7, 2048, 296), (1, 4096, 1184)])
+def test_linear_vs_oracle(ctx, oracle, variant, name, T, K, F):
     kind = KINDS[name]
     rng = np.random.default_rng(kind * 1000003 + T * 100003 + K * 101 + F)
     W = random_blocks(kind, F, K, rng)
     x = rng.normal(0, 1, (T, K)).astype(np.float32)
     got = ctx.linear(kind, dev(ctx, x), ctx.upload(W), F).cpu().numpy()
+    ctx.synchronize()
     ref = oracle.linear(kind, x, W, F)
     assert max_rel_err(got, ref) <= TOL_FP32
     assert cosine(got, ref) >= 0.999
 
 
 @pytest.mark.parametrize("name", NAMES)
-def test_linear_ragged_k_strided_input_and_bias(ctx, oracle, name):
+def test_linear_ragged_k_strided_input_and_bias(ctx, oracle, variant, name):
     kind = KINDS[name]
     bv = BLOCK_VALUES[kind]
     T, K, F = 3, 2 * bv + bv // 2 + 3, 11  # K not a multiple of the block size
@@ -157,7 +169,7 @@ def test_linear_reference_fixture(ctx, ref_cases, name, case):
 
 @pytest.mark.parametrize("name", NAMES)
 @pytest.mark.parametrize("T", [1, 4, 12])
-def test_dual_output_equals_two_singles(ctx, name, T):
+def test_dual_output_equals_two_singles(ctx, variant, name, T):
     # tests/backend/test_matmul_quantized.c:202-298: dual-output == two single calls
     kind = KINDS[name]
     K, F = 1024, 48
@@ -217,10 +229,12 @@ def test_error_codes(ctx):
 
     x = torch.zeros((1, 256), dtype=torch.float32, device="cuda:0")
     W = ctx.upload(random_blocks(KIND_Q4_K, 4, 256, np.random.default_rng(0)))
-    with pytest.raises(MarmotCudaError) as e:
-        ctx.linear(4, x, W, 4)  # Q5_1 has no CUDA kernel
-    assert e.value.code == -8
     lib = ctx.lib
+    # Q5_1 (kind 4) has no CUDA kernel: reported as not implemented, never computed some other way
+    assert lib.mcu_linear(ctx.handle, 4, x.data_ptr(), 256, W.data_ptr(), 1, 256, 4, None, x.data_ptr(), 4) == -8
+    with pytest.raises(MarmotCudaError) as e:
+        ctx.dequantize(4, W, 256)
+    assert e.value.code == -8
     assert lib.mcu_linear(ctx.handle, KIND_Q4_K, None, 256, W.data_ptr(), 1, 256, 4, None, x.data_ptr(), 4) == -1
     assert lib.mcu_linear(ctx.handle, KIND_Q4_K, x.data_ptr(), 100, W.data_ptr(), 1, 256, 4, None, x.data_ptr(), 4) == -7
     # a misaligned Q4_K weight pointer is rejected rather than read with vector loads
