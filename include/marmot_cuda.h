@@ -122,6 +122,28 @@ int mcu_linear_host(
     const float *bias_host, float *out_host, size_t ldo
 );
 
+/* ---- mcu_linear without any allocation.  No counterpart in the reference: it exists for callers of this
+ *      library that cannot call cudaMalloc at the time they need a matmul, for example code running after a
+ *      serving engine or a caching allocator has reserved all of the device memory (a further cudaMalloc
+ *      would fail), or a latency-critical thread that cannot afford the device-wide synchronisation a
+ *      cudaMalloc / cudaFree implies.  Same arithmetic as mcu_linear's decode kernels (f32 activations packed to
+ *      Q8_K / Q8_0, integer dots, per-block f32 scaling), limited to T <= MCU_STATIC_SCRATCH_MAX_T tokens and
+ *      K <= MCU_STATIC_SCRATCH_MAX_K; larger sizes are rejected with MCU_ERROR_INVALID_ARGUMENT.
+ *      The packed activations go to a fixed 160 KiB array inside the library's device image (each GPU that
+ *      loads the library holds it until the process exits).  The call takes no context and performs no
+ *      cudaMalloc, cudaFree or other allocating call; it enqueues two kernels on `cuda_stream` (a cudaStream_t,
+ *      NULL = default stream) of the current device.  The first call on each device looks up the array's
+ *      device address (cudaGetSymbolAddress); make that first call outside of any stream capture.
+ *      All calls share the one array and it keeps the last call's contents.  Nothing in it needs clearing
+ *      (each call rewrites every byte it later reads), but two calls that overlap on the GPU, e.g. on
+ *      different streams, race on it: serialise them. ---- */
+#define MCU_STATIC_SCRATCH_MAX_T 8
+#define MCU_STATIC_SCRATCH_MAX_K 16384
+int mcu_linear_static_scratch(
+    void *cuda_stream, int kind, const float *x_dev, size_t ldx, const void *w_dev, size_t T, size_t K, size_t F,
+    const float *bias_dev, float *out_dev, size_t ldo
+);
+
 /* ---- top-k over the last axis, ties to the lower index: cpu_topk_impl
  *      (src/backends/cpu/ops/moe/moe_ops.c:789-889). ---- */
 int mcu_topk(

@@ -30,6 +30,8 @@ static int fail(int code, const char *fmt, ...) {
     return code;
 }
 
+int set_error(int code, const char *message) { return fail(code, "%s", message); }
+
 static int cuda_fail(cudaError_t e, const char *what) {
     const int code = e == cudaErrorMemoryAllocation ? MCU_ERROR_OUT_OF_MEMORY
         : (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver || e == cudaErrorInvalidDevice)

@@ -45,4 +45,8 @@ cudaError_t launch_gemm_tc(int kind, const void *W, const void *W2, const __half
 
 int device_sm_count();
 
+// Record the calling thread's error message (read back by mcu_last_error_message) and return `code`.
+int set_error(int code, const char *message);
+void count_launches(int n);
+
 }  // namespace mcu

@@ -24,6 +24,7 @@ EXPORTS = (
     "mcu_context_set_regime", "mcu_synchronize", "mcu_last_error_message", "mcu_kernel_launch_count",
     "mcu_malloc", "mcu_free", "mcu_memcpy_to_device", "mcu_memcpy_to_host", "mcu_row_bytes", "mcu_dequantize",
     "mcu_quantize_activations", "mcu_linear", "mcu_linear_dual", "mcu_linear_host", "mcu_topk", "mcu_moe_experts",
+    "mcu_linear_static_scratch",
 )
 
 
@@ -75,6 +76,7 @@ def load_library() -> C.CDLL:
     L.mcu_linear.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_linear_dual.argtypes = [vp, i32, vp, sz, vp, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_linear_host.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
+    L.mcu_linear_static_scratch.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_topk.argtypes = [vp, vp, sz, sz, sz, sz, vp, vp]
     L.mcu_moe_experts.argtypes = [vp, i32, i32, i32, vp, sz, sz, sz, sz, vp, vp, vp, vp, vp, sz, i32, f32, i32, vp]
     _lib = L
