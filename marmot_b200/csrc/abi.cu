@@ -281,7 +281,7 @@ static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx,
             const size_t kp = (K + bv - 1) / bv * bv;
             int launches = 0;
             MCU_CUDA(launch_gemm_tc(kind, w, w2, (const __half *)ctx->act_half.ptr, (int)kp, (int)T, (int)K, (int)F, bias,
-                                    out, out2, (int)ldo, ctx->stream, &launches));
+                                    out, out2, (int)ldo, ctx->dev_err, ctx->stream, &launches));
             count_launches(launches);
             return MCU_SUCCESS;
         }

@@ -41,7 +41,8 @@ cudaError_t launch_gemv_stream(int kind, const void *W, const void *W2, const fl
 // accumulation in tensor memory.
 bool gemm_tc_supported(int kind, int T, int K, int F);
 cudaError_t launch_gemm_tc(int kind, const void *W, const void *W2, const __half *xh, int ldxh, int T, int K, int F,
-                           const float *bias, float *out, float *out2, int ldo, cudaStream_t s, int *launches);
+                           const float *bias, float *out, float *out2, int ldo, int *err_flag, cudaStream_t s,
+                           int *launches);
 
 int device_sm_count();
 

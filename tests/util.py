@@ -13,6 +13,9 @@ BLOCK_BYTES = {KIND_Q8_0: 34, KIND_Q4_K: 144, KIND_Q6_K: 210}
 TOL_FP32 = 2e-3
 # tensor-core kernels (fp16 operands, f32 accumulation): max relative error 1e-2
 TOL_MMA = 1e-2
+# MoE expert FFN: two chained matmuls with a GLU in between; the reference's own quantized MoE tests accept
+# 3e-2 and more (tests/backend/test_backend_moe.c:496-620)
+TOL_MOE = 3e-2
 
 
 def row_bytes(kind: int, K: int) -> int:
