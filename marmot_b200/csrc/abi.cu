@@ -65,7 +65,7 @@ struct mcu_context {
     int regime = MCU_REGIME_AUTO;
     std::mutex mu;  // guards the workspace; calls on one context are serialised
     // workspace (grows on demand, never shrinks)
-    Buffer act_qs, act_d, act_bsums, act_half, x_stage, out_stage, bias_stage;
+    Buffer act_qs, act_d, act_bsums, act_half, act_rowscale, x_stage, out_stage, bias_stage;
     Buffer moe_meta, moe_hidden, moe_gate, moe_up, moe_down;
     std::vector<int> host_counts;
     int *dev_err = nullptr;  // set by kernels whose bounded device-side waits ran out
@@ -150,7 +150,7 @@ void mcu_context_destroy(mcu_context_t *ctx) {
     if (ctx == nullptr) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    Buffer *bufs[] = {&ctx->act_qs,   &ctx->act_d,      &ctx->act_bsums, &ctx->act_half, &ctx->x_stage, &ctx->out_stage,
+    Buffer *bufs[] = {&ctx->act_qs,   &ctx->act_d,      &ctx->act_bsums, &ctx->act_half, &ctx->act_rowscale, &ctx->x_stage, &ctx->out_stage,
                       &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down};
     for (Buffer *b : bufs)
         if (b->ptr != nullptr) cudaFree(b->ptr);
@@ -257,14 +257,20 @@ static int pack_activations(mcu_context *ctx, int kind, const float *x, size_t l
     if (int rc = ensure(ctx, ctx->act_d, T * nb * sizeof(float))) return rc;
     if (kind != MCU_KIND_Q8_0)
         if (int rc = ensure(ctx, ctx->act_bsums, T * nb * 16 * sizeof(int16_t))) return rc;
-    if (want_half)
+    if (want_half) {
         if (int rc = ensure(ctx, ctx->act_half, T * kp * sizeof(__half))) return rc;
+        if (int rc = ensure(ctx, ctx->act_rowscale, T * sizeof(float))) return rc;
+    }
     ab.qs = (int8_t *)ctx->act_qs.ptr;
     ab.d = (float *)ctx->act_d.ptr;
     ab.bsums = (int16_t *)ctx->act_bsums.ptr;
-    MCU_CUDA(launch_quantize_act(kind, x, (int)ldx, (int)T, (int)K, ab, want_half ? (__half *)ctx->act_half.ptr : nullptr,
-                                 ctx->stream));
+    MCU_CUDA(launch_quantize_act(kind, x, (int)ldx, (int)T, (int)K, ab, nullptr, ctx->stream));
     count_launches(1);
+    if (want_half) {
+        MCU_CUDA(launch_half_acts(kind, ab, (int)T, (int)K, (__half *)ctx->act_half.ptr, (float *)ctx->act_rowscale.ptr,
+                                  ctx->stream));
+        count_launches(1);
+    }
     return MCU_SUCCESS;
 }
 
@@ -280,8 +286,14 @@ static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx,
             const size_t bv = (size_t)block_values(kind);
             const size_t kp = (K + bv - 1) / bv * bv;
             int launches = 0;
-            MCU_CUDA(launch_gemm_tc(kind, w, w2, (const __half *)ctx->act_half.ptr, (int)kp, (int)T, (int)K, (int)F, bias,
-                                    out, out2, (int)ldo, ctx->dev_err, ctx->stream, &launches));
+            if (gemm_tma_supported(kind, w, w2, (int)T, (int)K, (int)F))
+                MCU_CUDA(launch_gemm_tma(kind, w, w2, (const __half *)ctx->act_half.ptr,
+                                         (const float *)ctx->act_rowscale.ptr, (int)kp, (int)T, (int)K, (int)F,
+                                         bias, out, out2, (int)ldo, ctx->dev_err, ctx->stream, &launches));
+            else
+                MCU_CUDA(launch_gemm_tc(kind, w, w2, (const __half *)ctx->act_half.ptr,
+                                        (const float *)ctx->act_rowscale.ptr, (int)kp, (int)T, (int)K, (int)F,
+                                        bias, out, out2, (int)ldo, ctx->dev_err, ctx->stream, &launches));
             count_launches(launches);
             return MCU_SUCCESS;
         }

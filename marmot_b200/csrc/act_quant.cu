@@ -111,6 +111,55 @@ quantize_q8_0_kernel(const float *__restrict__ x, int ldx, int T, int K, int nb,
     }
 }
 
+// fp16 operands for the tensor-core path: xh[t][k] = (d*q) * 2^-e_t, with one exponent per token chosen so
+// that the largest magnitude of the row is about 2^14.  The power-of-two scale is exact, keeps large
+// activations inside the fp16 range (and tiny ones out of the subnormals); the matmul epilogue multiplies
+// the row back by rowscale[t] = 2^e_t.  One CTA per token.
+__global__ void __launch_bounds__(256)
+half_acts_kernel(int kq, const int8_t *__restrict__ qs, const float *__restrict__ dq, int nb, int kp,
+                 __half *__restrict__ xh, float *__restrict__ rowscale) {
+    __shared__ float red[8];
+    __shared__ float inv_s;
+    const int t = blockIdx.x;
+    const float *drow = dq + (size_t)t * nb;
+    float m = 0.0f;
+    for (int b = threadIdx.x; b < nb; b += blockDim.x) m = fmaxf(m, fabsf(drow[b]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float mm = 0.0f;
+        for (int i = 0; i < 8; ++i) mm = fmaxf(mm, red[i]);
+        mm *= 127.0f;  // bound of |d*q| over the row
+        int e = 0;
+        if (mm > 0.0f && mm < 3.0e38f) {
+            (void)frexpf(mm, &e);  // mm = f * 2^e, f in [0.5, 1)
+            e -= 14;
+            e = max(-100, min(100, e));
+        }
+        inv_s = ldexpf(1.0f, -e);
+        rowscale[t] = ldexpf(1.0f, e);
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    const int8_t *qrow = qs + (size_t)t * kp;
+    __half *hrow = xh + (size_t)t * kp;
+    const int bv = kq ? QK_K : Q8_0_VALUES;
+    for (int k = threadIdx.x; k < kp; k += blockDim.x) {
+        const int blk = k / bv;
+        const int pos = kq ? blk * QK_K + q8k_split_pos(k - blk * QK_K) : k;
+        hrow[k] = __float2half_rn(__fmul_rn(__fmul_rn(drow[blk], inv), (float)qrow[pos]));
+    }
+}
+
+cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, __half *xh, float *rowscale, cudaStream_t s) {
+    if (T <= 0) return cudaSuccess;
+    const int bv = block_values(kind), nb = (K + bv - 1) / bv;
+    half_acts_kernel<<<T, 256, 0, s>>>(kind != KIND_Q8_0, a.qs, a.d, nb, nb * bv, xh, rowscale);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_quantize_act(int kind, const float *x, int ldx, int T, int K, const ActBuffers &a, __half *xh,
                                 cudaStream_t s) {
     if (T <= 0) return cudaSuccess;

@@ -34,6 +34,7 @@ struct GemmTcParams {
     const uint8_t *W;
     const __half *xh;
     const float *bias;
+    const float *rowscale;  // per-token power-of-two factor undone in the epilogue
     float *out;
     int *err;
     int ldxh, ldo, T, K, F, nb;
@@ -429,7 +430,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcPara
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int t = t0 + col0 + cb + j;
-                        if (t < p.T) p.out[(size_t)t * p.ldo + f] = __uint_as_float(v[j]) + bias;
+                        if (t < p.T) p.out[(size_t)t * p.ldo + f] = __uint_as_float(v[j]) * p.rowscale[t] + bias;
                     }
                 }
             }
@@ -478,12 +479,13 @@ static cudaError_t launch_kind(const GemmTcParams &p, cudaStream_t s) {
     return launch_bn<KIND, 256>(p, s);
 }
 
-cudaError_t launch_gemm_tc(int kind, const void *W, const void *W2, const __half *xh, int ldxh, int T, int K, int F,
-                           const float *bias, float *out, float *out2, int ldo, int *err_flag, cudaStream_t s,
-                           int *launches) {
+cudaError_t launch_gemm_tc(int kind, const void *W, const void *W2, const __half *xh, const float *rowscale, int ldxh,
+                           int T, int K, int F, const float *bias, float *out, float *out2, int ldo, int *err_flag,
+                           cudaStream_t s, int *launches) {
     GemmTcParams p;
     p.xh = xh;
     p.bias = bias;
+    p.rowscale = rowscale;
     p.err = err_flag;
     p.ldxh = ldxh;
     p.ldo = ldo;

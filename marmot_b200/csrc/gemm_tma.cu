@@ -1,0 +1,669 @@
+// TMA-fed variant of the tensor-core quantized matmul (tcgen05 + TMEM), used when the weight rows are
+// 16-byte multiples (K % 2048 == 0 for Q6_K, K % 256 == 0 for Q8_0, always for Q4_K).
+//
+//   warp 18     one thread streams slabs of RAW packed weight blocks (rows_box rows x one super-block
+//               column, no swizzle) from HBM into a ring with cp.async.bulk.tensor.
+//   warp 17     one thread loads the BN x 64 fp16 activation tile of every K step (SWIZZLE_128B) straight
+//               into the MMA stage, also with cp.async.bulk.tensor.
+//   warps 0..15 converters, two groups that alternate K steps: read the packed blocks from shared memory,
+//               dequantise 32 values per thread with packed-half arithmetic (byte -> 1024+q by PRMT,
+//               -1024, one HFMA2 per two values) and store the fp16 A tile in the canonical K-major
+//               SWIZZLE_128B layout; group 0 later runs the epilogue (tcgen05.ld, + bias, coalesced stores).
+//   warp 16     one thread issues tcgen05.mma (M = 128, N = BN, K = 16) and tcgen05.commit; owns TMEM.
+//
+// For few tokens (T <= 64) the matmul is bound by the weight stream, so the CTAs take fewer than 128
+// weight rows each (F split evenly over the SMs, rounded up to 8) instead of full 128-row tiles that
+// would leave SMs idle; the unused accumulator lanes are simply not read back.
+// No TMA multicast anywhere; every mbarrier wait is bounded.
+#include "common.cuh"
+#include "kernels.h"
+
+#include <cuda.h>
+
+#include <cstdlib>
+#include <mutex>
+#include <type_traits>
+
+namespace mcu {
+
+constexpr int TM_BM = 128;
+constexpr int TM_BK = 64;
+constexpr int TM_CONV_WARPS = 8;   // warps per converter group: one K step needs 256 threads (row, 32-value half)
+constexpr int TM_CONV_GROUPS = 2;  // the groups alternate K steps
+constexpr int TM_ALL_CONV = TM_CONV_WARPS * TM_CONV_GROUPS;
+constexpr int TM_THREADS = (TM_ALL_CONV + 3) * 32;  // + MMA issuer, activation-tile producer, weight-slab producer
+constexpr int TM_A_BYTES = TM_BM * TM_BK * 2;
+constexpr int TM_MAX_RING = 8;
+constexpr uint32_t TM_SPIN_LIMIT = 1u << 22;
+
+template <int KIND>
+struct RawCfg;
+template <>
+struct RawCfg<KIND_Q4_K> {
+    static constexpr int KR = 4;         // K steps per raw slab (one 256-value super-block)
+    static constexpr int UNIT = 144;     // bytes of packed data per slab and row
+    static constexpr int BOX_W = 144;    // bytes fetched per row (16-byte aligned window covering UNIT)
+};
+template <>
+struct RawCfg<KIND_Q6_K> {
+    static constexpr int KR = 4;
+    static constexpr int UNIT = 210;
+    static constexpr int BOX_W = 224;
+};
+template <>
+struct RawCfg<KIND_Q8_0> {
+    static constexpr int KR = 2;         // four 32-value blocks
+    static constexpr int UNIT = 136;
+    static constexpr int BOX_W = 144;
+};
+
+struct GemmTmaParams {
+    const float *bias;
+    const float *rowscale;  // per-token power-of-two factor undone in the epilogue
+    float *out;
+    int *err;
+    int ldo, T, F, nb;
+    int ksteps;
+    int rows_per_cta;  // weight rows per CTA (= tensor-map box rows), <= 128
+    int stages;        // MMA stage ring depth
+    int raw_stages;    // raw slab ring depth
+#ifdef MCU_TRACE
+    long long *trace;  // development aid: clock64 samples of CTA 0, [agent][step][point]
+#endif
+};
+
+#ifdef MCU_TRACE
+#define MCU_TRACE_POINT(agent, step, point)                                                          \
+    do {                                                                                             \
+        if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (step) < 64)                 \
+            p.trace[((agent) * 64 + (step)) * 4 + (point)] = clock64();                               \
+    } while (0)
+#else
+#define MCU_TRACE_POINT(agent, step, point) do { } while (0)
+#endif
+
+__device__ __forceinline__ uint32_t tm_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tm_mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void tm_mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tm_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool tm_mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < TM_SPIN_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+// Same, for the agents that have slack (converters, producers): sleep between polls so that waiting warps
+// do not take issue slots from the single thread that feeds the tensor core.
+__device__ __forceinline__ bool tm_mbar_wait_relaxed(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < TM_SPIN_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        __nanosleep(40);
+    }
+    return false;
+}
+// 2-D tiled tensor load, completion counted in bytes on an mbarrier of this CTA (no multicast).
+__device__ __forceinline__ void tm_tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ uint64_t tm_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__host__ __device__ constexpr uint32_t tm_idesc(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TM_BM >> 4) << 24);
+}
+__device__ __forceinline__ void tm_mma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void tm_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// N words from a 2-byte aligned shared-memory address (reads one aligned word beyond the last).
+template <int N>
+__device__ __forceinline__ void tm_lds_words(const uint8_t *p, uint32_t (&out)[N]) {
+    const uint32_t a = tm_smem_u32(p);
+    const uint32_t *w = (const uint32_t *)(p - (a & 3u));
+    const uint32_t sh = (a & 3u) * 8u;
+    uint32_t prev = w[0];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        const uint32_t next = w[i + 1];
+        out[i] = __funnelshift_r(prev, next, sh);
+        prev = next;
+    }
+}
+
+__device__ __forceinline__ __half2 as_half2(uint32_t v) { return *(const __half2 *)&v; }
+__device__ __forceinline__ uint32_t as_u32(__half2 v) { return *(const uint32_t *)&v; }
+
+// Four unsigned bytes (each < 256) -> two half2 holding byte - offset, in byte order.
+__device__ __forceinline__ void bytes_to_half2(uint32_t w, __half2 offset, __half2 &v01, __half2 &v23) {
+    // 0x64xx is the fp16 bit pattern of 1024 + xx
+    v01 = __hsub2(as_half2(__byte_perm(w, 0x64646464u, 0x4140)), offset);
+    v23 = __hsub2(as_half2(__byte_perm(w, 0x64646464u, 0x4342)), offset);
+}
+
+// ---- converters: 32 values of row `rowp` (packed bytes in shared memory) for K step `kq` of the slab ----
+template <int KQ>
+__device__ __forceinline__ void conv_q4k(const uint8_t *rowp, int h, uint4 (&outv)[4]) {
+    const uint4 hdr = *(const uint4 *)rowp;
+    const uint4 q0 = *(const uint4 *)(rowp + 16 + 32 * KQ), q1 = *(const uint4 *)(rowp + 32 + 32 * KQ);
+    // 6-bit scale / min of sub-block 2*KQ + h (bit selection of get_scale_min_k4)
+    uint32_t sc, mn;
+    if (KQ < 2) {
+        const int sh = 8 * (2 * KQ + h);
+        sc = (hdr.y >> sh) & 63u;
+        mn = (hdr.z >> sh) & 63u;
+    } else {
+        const int sh = 8 * (2 * KQ + h - 4);
+        sc = ((hdr.w >> sh) & 0xFu) | (((hdr.y >> (sh + 6)) & 3u) << 4);
+        mn = ((hdr.w >> (sh + 4)) & 0xFu) | (((hdr.z >> (sh + 6)) & 3u) << 4);
+    }
+    const float d = half_bits_to_float((uint16_t)(hdr.x & 0xFFFFu));
+    const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
+    const __half2 d1 = __float2half2_rn(__fmul_rn(d, (float)sc));
+    const __half2 m1n = __float2half2_rn(-__fmul_rn(dmin, (float)mn));
+    const __half2 off = __float2half2_rn(1024.0f);
+    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const int nsh = 4 * h;
+    uint32_t o[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t nib = (w[j] >> nsh) & 0x0F0F0F0Fu;
+        __half2 a, b;
+        bytes_to_half2(nib, off, a, b);
+        o[2 * j] = as_u32(__hfma2(a, d1, m1n));
+        o[2 * j + 1] = as_u32(__hfma2(b, d1, m1n));
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) outv[c] = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+}
+
+__device__ __forceinline__ void conv_q6k(const uint8_t *blk, int kq, int h, uint4 (&outv)[4]) {
+    const int n = kq >> 1, c = 2 * (kq & 1) + h;  // values 128n + 32c + l
+    uint32_t ql[8], qh[8];
+    tm_lds_words<8>(blk + n * 64 + (c & 1) * 32, ql);
+    tm_lds_words<8>(blk + 128 + n * 32, qh);
+    const uint32_t sc2 = *(const uint16_t *)(blk + 192 + n * 8 + 2 * c);
+    const float d = half_bits_to_float(*(const uint16_t *)(blk + 208));
+    const __half2 ds0 = __float2half2_rn(__fmul_rn(d, (float)(int8_t)(sc2 & 0xFFu)));
+    const __half2 ds1 = __float2half2_rn(__fmul_rn(d, (float)(int8_t)(sc2 >> 8)));
+    const __half2 off = __float2half2_rn(1056.0f);  // 1024 + 32
+    uint32_t o[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t lo4 = (c & 2) ? ((ql[j] >> 4) & 0x0F0F0F0Fu) : (ql[j] & 0x0F0F0F0Fu);
+        const uint32_t u = lo4 | (((qh[j] >> (2 * c)) & 0x03030303u) << 4);
+        __half2 a, b;
+        bytes_to_half2(u, off, a, b);
+        const __half2 ds = j < 4 ? ds0 : ds1;
+        o[2 * j] = as_u32(__hmul2(a, ds));
+        o[2 * j + 1] = as_u32(__hmul2(b, ds));
+    }
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) outv[cc] = make_uint4(o[4 * cc], o[4 * cc + 1], o[4 * cc + 2], o[4 * cc + 3]);
+}
+
+__device__ __forceinline__ void conv_q8_0(const uint8_t *blk, uint4 (&outv)[4]) {
+    const __half2 dh = __half2half2(__ushort_as_half(*(const uint16_t *)blk));
+    uint32_t q[8];
+    tm_lds_words<8>(blk + 2, q);
+    const __half2 off = __float2half2_rn(1152.0f);  // 1024 + 128
+    uint32_t o[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        __half2 a, b;
+        bytes_to_half2(q[j] ^ 0x80808080u, off, a, b);
+        o[2 * j] = as_u32(__hmul2(a, dh));
+        o[2 * j + 1] = as_u32(__hmul2(b, dh));
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) outv[c] = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+}
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(TM_THREADS, 1)
+gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                const GemmTmaParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    using RC = RawCfg<KIND>;
+    constexpr int B_BYTES = BN * TM_BK * 2;
+    constexpr int STAGE_BYTES = TM_A_BYTES + B_BYTES;
+    constexpr int RAW_STAGE_BYTES = TM_BM * RC::BOX_W + 128;  // + slack for the one-word over-read
+
+    const uint32_t raw_addr = tm_smem_u32(smem_raw);
+    const uint32_t bar_base = (raw_addr + 7u) & ~7u;
+    const uint32_t tile_base = (bar_base + 512u + 1023u) & ~1023u;
+    uint8_t *tiles = smem_raw + (tile_base - raw_addr);
+    const int S = p.stages, R = p.raw_stages;
+    uint8_t *raw_ring = tiles + (size_t)S * STAGE_BYTES;
+    const uint32_t raw_ring_addr = tile_base + (uint32_t)S * STAGE_BYTES;
+    // barrier slots (8 bytes each): full[8] (unused[8]) stage_empty[8] raw_full[8] raw_empty[8] accum
+    const uint32_t a_full = bar_base, st_empty = bar_base + 128u, raw_full = bar_base + 192u,
+                   raw_empty = bar_base + 256u, accum_bar = bar_base + 320u;
+    uint32_t *tmem_slot = (uint32_t *)(smem_raw + (bar_base - raw_addr) + 336);
+    volatile int *abort_flag = (volatile int *)(smem_raw + (bar_base - raw_addr) + 344);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f0 = blockIdx.x * p.rows_per_cta, t0 = blockIdx.y * BN;
+    const int rows_here = min(p.rows_per_cta, p.F - f0);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S; ++i) {
+            tm_mbar_init(a_full + 8u * i, TM_CONV_WARPS + 1);  // eight converter warps + the activation tile's expect_tx
+            tm_mbar_init(st_empty + 8u * i, 1);
+        }
+        for (int i = 0; i < R; ++i) {
+            tm_mbar_init(raw_full + 8u * i, 1);
+            tm_mbar_init(raw_empty + 8u * i, TM_ALL_CONV);
+        }
+        tm_mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == TM_ALL_CONV) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tm_smem_u32(tmem_slot)),
+                     "r"((uint32_t)BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == TM_ALL_CONV + 1) {
+        // ------------------------------ TMA producer: activation tiles ------------------------------
+        if (lane == 0) {
+            bool ok = true;
+            int st = 0;
+            uint32_t phase = 1;  // parity of the previous use of the stage
+            for (int ks = 0; ks < p.ksteps && ok; ++ks) {
+                MCU_TRACE_POINT(2, ks, 0);
+                if (ks >= S) ok = tm_mbar_wait_relaxed(st_empty + 8u * st, phase);
+                if (!ok) break;
+                tm_mbar_expect_tx(a_full + 8u * st, (uint32_t)B_BYTES);
+                tm_tma_load_2d(tile_base + (uint32_t)st * STAGE_BYTES + TM_A_BYTES, &map_x, ks * TM_BK, t0, a_full + 8u * st);
+                MCU_TRACE_POINT(2, ks, 1);
+                if (++st == S) {
+                    st = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (!ok) {
+                atomicExch(p.err, 6);
+                *abort_flag = 1;
+            }
+        }
+        __syncwarp();
+    } else if (warp == TM_ALL_CONV + 2) {
+        // ------------------------------ TMA producer: packed weight slabs ------------------------------
+        // Runs ahead by the depth of the slab ring, independently of the MMA stages: this is the HBM stream.
+        if (lane == 0) {
+            bool ok = true;
+            const uint32_t raw_bytes = (uint32_t)p.rows_per_cta * RC::BOX_W;
+            const int n_slabs = (p.ksteps + RC::KR - 1) / RC::KR;
+            int rs = 0;
+            uint32_t phase = 1;  // parity of the previous use of the slab slot
+            for (int j = 0; j < n_slabs && ok; ++j) {
+                if (j >= R) ok = tm_mbar_wait_relaxed(raw_empty + 8u * rs, phase);
+                if (!ok) break;
+                tm_mbar_expect_tx(raw_full + 8u * rs, raw_bytes);
+                tm_tma_load_2d(raw_ring_addr + (uint32_t)rs * RAW_STAGE_BYTES, &map_w, (j * RC::UNIT) & ~15, f0,
+                               raw_full + 8u * rs);
+                if (++rs == R) {
+                    rs = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (!ok) {
+                atomicExch(p.err, 10);
+                *abort_flag = 1;
+            }
+        }
+        __syncwarp();
+    } else if (warp == TM_ALL_CONV) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = tm_idesc(BN);
+            bool ok = true;
+            // This single thread paces the tensor core: keep its per-step instruction count minimal (running
+            // stage counter and descriptors instead of divisions and re-encoding).
+            const uint64_t a_desc0 = tm_smem_desc(tile_base), b_desc0 = tm_smem_desc(tile_base + TM_A_BYTES);
+            constexpr uint64_t desc_step = (uint64_t)(STAGE_BYTES >> 4);
+            uint64_t a_desc = a_desc0, b_desc = b_desc0;
+            uint32_t full_bar = a_full, empty_bar = st_empty, phase = 0, acc = 0;
+            int st = 0;
+            for (int ks = 0; ks < p.ksteps; ++ks) {
+                MCU_TRACE_POINT(0, ks, 0);
+                ok = tm_mbar_wait(full_bar, phase);  // weight tile converted and activation tile landed
+                MCU_TRACE_POINT(0, ks, 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                tm_mma(tmem_base, a_desc, b_desc, idesc, acc);
+                tm_mma(tmem_base, a_desc + 2, b_desc + 2, idesc, 1u);  // +32 bytes along K inside the swizzle row
+                tm_mma(tmem_base, a_desc + 4, b_desc + 4, idesc, 1u);
+                tm_mma(tmem_base, a_desc + 6, b_desc + 6, idesc, 1u);
+                acc = 1u;
+                tm_commit(empty_bar);
+                MCU_TRACE_POINT(0, ks, 3);
+                if (++st == S) {
+                    st = 0;
+                    phase ^= 1u;
+                    a_desc = a_desc0, b_desc = b_desc0, full_bar = a_full, empty_bar = st_empty;
+                } else {
+                    a_desc += desc_step, b_desc += desc_step, full_bar += 8u, empty_bar += 8u;
+                }
+            }
+            if (!ok) {
+                atomicExch(p.err, 7);
+                *abort_flag = 1;
+            }
+            tm_commit(accum_bar);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ converters ------------------------------
+        // Two groups of eight warps; group g converts the K steps with (step index inside the slab) % 2 == g.
+        const int group = warp / TM_CONV_WARPS;
+        const int tid = threadIdx.x - group * (TM_CONV_WARPS * 32);
+        const int r = tid >> 1, h = tid & 1;
+        const bool row_live = r < rows_here;
+        bool ok = true;
+        const int n_slabs = (p.ksteps + RC::KR - 1) / RC::KR;
+        int rs = 0, st = 0;              // running ring positions of the slab and of the K step
+        uint32_t raw_phase = 0, st_phase = 1;  // st_phase: parity of the previous use of stage st
+        for (int j = 0; j < n_slabs && ok; ++j) {
+            ok = tm_mbar_wait_relaxed(raw_full + 8u * rs, raw_phase);
+            if (!ok || *abort_flag) {
+                if (!ok && lane == 0) atomicExch(p.err, 8);
+                ok = false;
+                break;
+            }
+            const uint8_t *rowp = raw_ring + (size_t)rs * RAW_STAGE_BYTES + (size_t)r * RC::BOX_W + ((j * RC::UNIT) & 15);
+            auto do_step = [&](auto kq_tag) {
+                constexpr int KQ = decltype(kq_tag)::value;
+                const int ks = j * RC::KR + KQ;
+                const int my_st = st;
+                const uint32_t my_phase = st_phase;
+                if (++st == S) {  // every warp tracks every step, also the ones of the other group
+                    st = 0;
+                    st_phase ^= 1u;
+                }
+                if ((KQ & 1) != group || ks >= p.ksteps || !ok) return;
+                if (threadIdx.x == 0 || threadIdx.x == 256) MCU_TRACE_POINT(1, ks, 0);
+                if (ks >= S) ok = tm_mbar_wait_relaxed(st_empty + 8u * my_st, my_phase);
+                if (!ok) {
+                    if (lane == 0) atomicExch(p.err, 8);
+                    return;
+                }
+                if (threadIdx.x == 0 || threadIdx.x == 256) MCU_TRACE_POINT(1, ks, 1);
+                uint4 wv[4];
+                if (row_live) {
+                    if constexpr (KIND == KIND_Q4_K) conv_q4k<KQ>(rowp, h, wv);
+                    else if constexpr (KIND == KIND_Q6_K) conv_q6k(rowp, KQ, h, wv);
+                    else {
+                        const int blk = 4 * j + 2 * KQ + h;
+                        if (blk < p.nb) conv_q8_0(rowp + (2 * KQ + h) * Q8_0_BYTES, wv);
+                        else wv[0] = wv[1] = wv[2] = wv[3] = make_uint4(0, 0, 0, 0);
+                    }
+                } else {
+                    wv[0] = wv[1] = wv[2] = wv[3] = make_uint4(0, 0, 0, 0);
+                }
+                uint8_t *a_tile = tiles + (size_t)my_st * STAGE_BYTES;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) *(uint4 *)(a_tile + r * 128 + (((4 * h + c) ^ (r & 7)) << 4)) = wv[c];
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) tm_mbar_arrive(a_full + 8u * my_st);
+                if (threadIdx.x == 0 || threadIdx.x == 256) MCU_TRACE_POINT(1, ks, 2);
+            };
+            do_step(std::integral_constant<int, 0>{});
+            do_step(std::integral_constant<int, 1>{});
+            if constexpr (RC::KR == 4) {
+                do_step(std::integral_constant<int, 2>{});
+                do_step(std::integral_constant<int, 3>{});
+            }
+            __syncwarp();
+            if (lane == 0) tm_mbar_arrive(raw_empty + 8u * rs);  // this warp no longer reads the slab
+            if (++rs == R) {
+                rs = 0;
+                raw_phase ^= 1u;
+            }
+        }
+
+        // ------------------------------ epilogue ------------------------------
+        if (ok && group == 0) ok = tm_mbar_wait_relaxed(accum_bar, 0);
+        if (!ok && lane == 0) atomicExch(p.err, 9);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok && group == 0 && !*abort_flag) {
+            const int q = warp & 3;
+            const int col0 = (warp >> 2) * (BN / 2);
+            const int fr = 32 * q + lane;
+            const int f = f0 + fr;
+            const bool f_ok = fr < rows_here;
+            const float bias = (p.bias != nullptr && f_ok) ? p.bias[f] : 0.0f;
+            for (int cb = 0; cb < BN / 2; cb += 32) {
+                if (t0 + col0 + cb >= p.T) break;  // warp-uniform: no tokens left in this column block
+                uint32_t v[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(col0 + cb);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]),
+                      "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]),
+                      "=r"(v[30]), "=r"(v[31])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (f_ok) {
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) {
+                        const int t = t0 + col0 + cb + jj;
+                        if (t < p.T) p.out[(size_t)t * p.ldo + f] = __uint_as_float(v[jj]) * p.rowscale[t] + bias;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == TM_ALL_CONV) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult st;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &st) == cudaSuccess &&
+            st == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+static bool force_v1() {
+    static const bool v = getenv("MARMOT_CUDA_GEMM_NO_TMA") != nullptr;
+    return v;
+}
+
+bool gemm_tma_supported(int kind, const void *W, const void *W2, int T, int K, int F) {
+    if (force_v1() || !kind_supported(kind) || T < 1 || F < 1 || K < 1) return false;
+    if (((uintptr_t)W & 15) || ((uintptr_t)W2 & 15)) return false;
+    const int bv = block_values(kind), nb = (K + bv - 1) / bv;
+    const long row_bytes = (long)nb * block_bytes(kind);
+    if (row_bytes % 16) return false;  // tensor-map row stride
+    return encode_tiled_fn() != nullptr;
+}
+
+template <int KIND, int BN>
+static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, GemmTmaParams p, long row_bytes,
+                                 cudaStream_t s) {
+    using RC = RawCfg<KIND>;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (enc == nullptr) return cudaErrorNotSupported;
+    alignas(64) CUtensorMap map_w, map_x;
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)p.F};
+        const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+        const cuuint32_t box[2] = {(cuuint32_t)RC::BOX_W, (cuuint32_t)p.rows_per_cta};
+        const cuuint32_t es[2] = {1, 1};
+        if (enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(W), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)ldxh, (cuuint64_t)p.T};
+        const cuuint64_t strides[1] = {(cuuint64_t)ldxh * 2};
+        const cuuint32_t box[2] = {(cuuint32_t)TM_BK, (cuuint32_t)BN};
+        const cuuint32_t es[2] = {1, 1};
+        if (enc(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(xh), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    constexpr int stage_bytes = TM_A_BYTES + BN * TM_BK * 2;
+    constexpr int raw_stage_bytes = TM_BM * RC::BOX_W + 128;
+    const int budget = 210 * 1024 - 2048;
+    const int raw_slabs = (p.ksteps + RC::KR - 1) / RC::KR;
+    // The slab ring carries the HBM stream: deep enough for ~64 KB in flight per SM; the MMA stages get the rest.
+    int R = BN <= 64 ? 5 : (BN <= 128 ? 4 : 3);
+    if (R > raw_slabs) R = raw_slabs;
+    if (R > TM_MAX_RING) R = TM_MAX_RING;
+    int S = (budget - R * raw_stage_bytes) / stage_bytes;
+    while (S < 2 && R > 1) {
+        --R;
+        S = (budget - R * raw_stage_bytes) / stage_bytes;
+    }
+    if (S > TM_MAX_RING) S = TM_MAX_RING;
+    if (S > p.ksteps) S = p.ksteps;
+    if (S < 1) return cudaErrorInvalidConfiguration;
+    p.stages = S;
+    p.raw_stages = R;
+    const int smem = 2048 + S * stage_bytes + R * raw_stage_bytes;
+    static int configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tma_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured = smem;
+    }
+    dim3 grid((unsigned)((p.F + p.rows_per_cta - 1) / p.rows_per_cta), (unsigned)((p.T + BN - 1) / BN), 1);
+    gemm_tma_kernel<KIND, BN><<<grid, TM_THREADS, smem, s>>>(map_w, map_x, p);
+    return cudaGetLastError();
+}
+
+template <int KIND>
+static cudaError_t launch_tma_kind(const void *W, const __half *xh, int ldxh, const GemmTmaParams &p, long row_bytes,
+                                   cudaStream_t s) {
+    if (p.T <= 64) return launch_tma_bn<KIND, 64>(W, xh, ldxh, p, row_bytes, s);
+    if (p.T <= 128) return launch_tma_bn<KIND, 128>(W, xh, ldxh, p, row_bytes, s);
+    return launch_tma_bn<KIND, 256>(W, xh, ldxh, p, row_bytes, s);
+}
+
+#ifdef MCU_TRACE
+long long *g_trace_buf = nullptr;
+extern "C" long long *mcu_debug_trace_buffer() { return g_trace_buf; }
+#endif
+
+cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __half *xh, const float *rowscale, int ldxh,
+                            int T, int K, int F, const float *bias, float *out, float *out2, int ldo, int *err_flag,
+                            cudaStream_t s, int *launches) {
+    GemmTmaParams p;
+    p.bias = bias;
+    p.rowscale = rowscale;
+    p.err = err_flag;
+    p.ldo = ldo;
+    p.T = T;
+    p.F = F;
+    const int bv = block_values(kind);
+    p.nb = (K + bv - 1) / bv;
+    p.ksteps = (p.nb * bv + TM_BK - 1) / TM_BK;
+    const long row_bytes = (long)p.nb * block_bytes(kind);
+    // weight-stream bound for few tokens: spread the rows evenly over the SMs
+    int rows = TM_BM;
+    if (T <= 64) {
+        const int sms = device_sm_count();
+        const int waves = (F + TM_BM * sms - 1) / (TM_BM * sms);  // passes over the SMs with full tiles
+        rows = (F + sms * waves - 1) / (sms * waves);
+        rows = (rows + 7) / 8 * 8;
+        if (rows > TM_BM) rows = TM_BM;
+        if (rows < 8) rows = 8;
+    }
+    p.rows_per_cta = rows;
+    p.stages = p.raw_stages = 0;
+#ifdef MCU_TRACE
+    {
+        static long long *trace_buf = nullptr;
+        if (trace_buf == nullptr) cudaMalloc(&trace_buf, 3 * 64 * 4 * sizeof(long long));
+        cudaMemsetAsync(trace_buf, 0, 3 * 64 * 4 * sizeof(long long), s);
+        p.trace = trace_buf;
+        g_trace_buf = trace_buf;
+    }
+#endif
+    int n = 0;
+    for (int pass = 0; pass < (W2 != nullptr ? 2 : 1); ++pass) {
+        const void *w = pass == 0 ? W : W2;
+        p.out = pass == 0 ? out : out2;
+        cudaError_t e = kind == KIND_Q4_K ? launch_tma_kind<KIND_Q4_K>(w, xh, ldxh, p, row_bytes, s)
+            : kind == KIND_Q6_K           ? launch_tma_kind<KIND_Q6_K>(w, xh, ldxh, p, row_bytes, s)
+                                          : launch_tma_kind<KIND_Q8_0>(w, xh, ldxh, p, row_bytes, s);
+        if (e != cudaSuccess) return e;
+        ++n;
+    }
+    if (launches != nullptr) *launches = n;
+    return cudaSuccess;
+}
+
+}  // namespace mcu

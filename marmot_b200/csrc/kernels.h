@@ -20,6 +20,10 @@ struct ActBuffers {
 cudaError_t launch_quantize_act(int kind, const float *x, int ldx, int T, int K, const ActBuffers &a, __half *xh,
                                 cudaStream_t s);
 
+// fp16 operands of the tensor-core matmul from the quantized activations: xh[t][k] = d*q*2^-e_t (row stride kp),
+// rowscale[t] = 2^e_t.
+cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, __half *xh, float *rowscale, cudaStream_t s);
+
 // blocks -> f32 (bit-exact with the reference dequantizers)
 cudaError_t launch_dequantize(int kind, const void *blocks, size_t n_values, float *out, cudaStream_t s);
 
@@ -40,9 +44,16 @@ cudaError_t launch_gemv_stream(int kind, const void *W, const void *W2, const fl
 // memory, activations given as fp16 (d*q of the quantized activations, row stride ldxh), f32
 // accumulation in tensor memory.
 bool gemm_tc_supported(int kind, int T, int K, int F);
-cudaError_t launch_gemm_tc(int kind, const void *W, const void *W2, const __half *xh, int ldxh, int T, int K, int F,
-                           const float *bias, float *out, float *out2, int ldo, int *err_flag, cudaStream_t s,
-                           int *launches);
+cudaError_t launch_gemm_tc(int kind, const void *W, const void *W2, const __half *xh, const float *rowscale, int ldxh,
+                           int T, int K, int F, const float *bias, float *out, float *out2, int ldo, int *err_flag,
+                           cudaStream_t s, int *launches);
+
+// TMA-fed variant of the tensor-core matmul (packed weight slabs and activation tiles arrive by
+// cp.async.bulk.tensor); needs 16-byte aligned weights whose rows are 16-byte multiples.
+bool gemm_tma_supported(int kind, const void *W, const void *W2, int T, int K, int F);
+cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __half *xh, const float *rowscale, int ldxh,
+                            int T, int K, int F, const float *bias, float *out, float *out2, int ldo, int *err_flag,
+                            cudaStream_t s, int *launches);
 
 int device_sm_count();
 

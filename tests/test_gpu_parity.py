@@ -294,8 +294,9 @@ def test_topk_matches_oracle_with_ties(ctx, oracle):
 
 def _moe_case(rng, T, H, FF, E, k, kinds):
     hid = rng.normal(0, 1, (T, H)).astype(np.float32)
-    gate = np.concatenate([random_blocks(kinds[0], FF, H, rng) for _ in range(E)])
-    up = np.concatenate([random_blocks(kinds[1], FF, H, rng) for _ in range(E)])
+    # small block scales keep the synthetic expert weights at a realistic magnitude (|w| < 1)
+    gate = np.concatenate([random_blocks(kinds[0], FF, H, rng, d_sigma=0.0005) for _ in range(E)])
+    up = np.concatenate([random_blocks(kinds[1], FF, H, rng, d_sigma=0.0005) for _ in range(E)])
     down = np.concatenate([random_blocks(kinds[2], H, FF, rng, d_sigma=0.0005) for _ in range(E)])
     logits = rng.normal(0, 1, (T, E)).astype(np.float32)
     p = np.exp(logits - logits.max(1, keepdims=True))

@@ -13,9 +13,11 @@ BLOCK_BYTES = {KIND_Q8_0: 34, KIND_Q4_K: 144, KIND_Q6_K: 210}
 TOL_FP32 = 2e-3
 # tensor-core kernels (fp16 operands, f32 accumulation): max relative error 1e-2
 TOL_MMA = 1e-2
-# MoE expert FFN: two chained matmuls with a GLU in between; the reference's own quantized MoE tests accept
-# 3e-2 and more (tests/backend/test_backend_moe.c:496-620)
-TOL_MOE = 3e-2
+# MoE expert FFN: two chained matmuls with a GLU in between, and the intermediate is re-quantized to Q8_K, so a
+# 1e-3 perturbation of the first stage flips quantizer roundings of the second stage's input (each flip is
+# 1/127 of a block's amax).  The reference's own Q4_K + Q6_K MoE tests accept 8e-2 (decode) and 9e-2 (prefill)
+# between its backends for this reason (tests/backend/test_backend_moe.c:901,1052,1147,1173).
+TOL_MOE = 8e-2
 
 
 def row_bytes(kind: int, K: int) -> int:
