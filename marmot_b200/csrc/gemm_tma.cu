@@ -31,7 +31,10 @@ constexpr int TM_BK = 64;
 constexpr int TM_CONV_WARPS = 8;   // warps per converter group: one K step needs 256 threads (row, 32-value half)
 constexpr int TM_CONV_GROUPS = 2;  // the groups alternate K steps
 constexpr int TM_ALL_CONV = TM_CONV_WARPS * TM_CONV_GROUPS;
-constexpr int TM_THREADS = (TM_ALL_CONV + 3) * 32;  // + MMA issuer, activation-tile producer, weight-slab producer
+constexpr int TM_MAX_ISSUERS = 4;  // MMA-issuing warps, each with its own TMEM accumulator (see NACC in the kernel)
+constexpr int TM_B_PRODUCER = TM_ALL_CONV + TM_MAX_ISSUERS;
+constexpr int TM_W_PRODUCER = TM_B_PRODUCER + 1;
+constexpr int TM_THREADS = (TM_W_PRODUCER + 1) * 32;
 constexpr int TM_A_BYTES = TM_BM * TM_BK * 2;
 constexpr int TM_MAX_RING = 8;
 constexpr uint32_t TM_SPIN_LIMIT = 1u << 22;
@@ -67,6 +70,7 @@ struct GemmTmaParams {
     int rows_per_cta;  // weight rows per CTA (= tensor-map box rows), <= 128
     int stages;        // MMA stage ring depth
     int raw_stages;    // raw slab ring depth
+    int issuers;       // MMA-issuing threads in use: 1, 2 or 4, a divisor of `stages`
 #ifdef MCU_TRACE
     long long *trace;  // development aid: clock64 samples of CTA 0, [agent][step][point]
 #endif
@@ -266,6 +270,11 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     constexpr int B_BYTES = BN * TM_BK * 2;
     constexpr int STAGE_BYTES = TM_A_BYTES + B_BYTES;
     constexpr int RAW_STAGE_BYTES = TM_BM * RC::BOX_W + 128;  // + slack for the one-word over-read
+    // One thread can issue tcgen05.mma only so fast (a few hundred cycles per K step including its barrier
+    // wait and commit), which is far slower than the tensor core for narrow tiles.  NACC threads therefore issue
+    // interleaved K steps (step ks -> issuer ks % NACC), each into its own accumulator; the epilogue adds them.
+    constexpr int NACC = BN == 64 ? 4 : (BN == 128 ? 2 : 1);
+    constexpr uint32_t TMEM_COLS = NACC * BN;  // 256 for every BN: a power of two >= 32
 
     const uint32_t raw_addr = tm_smem_u32(smem_raw);
     const uint32_t bar_base = (raw_addr + 7u) & ~7u;
@@ -293,13 +302,13 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             tm_mbar_init(raw_full + 8u * i, 1);
             tm_mbar_init(raw_empty + 8u * i, TM_ALL_CONV);
         }
-        tm_mbar_init(accum_bar, 1);
+        tm_mbar_init(accum_bar, (uint32_t)p.issuers);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == TM_ALL_CONV) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tm_smem_u32(tmem_slot)),
-                     "r"((uint32_t)BN)
+                     "r"(TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -308,7 +317,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == TM_ALL_CONV + 1) {
+    if (warp == TM_B_PRODUCER) {
         // ------------------------------ TMA producer: activation tiles ------------------------------
         if (lane == 0) {
             bool ok = true;
@@ -332,7 +341,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             }
         }
         __syncwarp();
-    } else if (warp == TM_ALL_CONV + 2) {
+    } else if (warp == TM_W_PRODUCER) {
         // ------------------------------ TMA producer: packed weight slabs ------------------------------
         // Runs ahead by the depth of the slab ring, independently of the MMA stages: this is the HBM stream.
         if (lane == 0) {
@@ -358,44 +367,45 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             }
         }
         __syncwarp();
-    } else if (warp == TM_ALL_CONV) {
-        // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
+    } else if (warp >= TM_ALL_CONV) {
+        // ------------------------------ MMA issuers ------------------------------
+        const int issuer = warp - TM_ALL_CONV;
+        if (lane == 0 && issuer < p.issuers) {
             constexpr uint32_t idesc = tm_idesc(BN);
             bool ok = true;
-            // This single thread paces the tensor core: keep its per-step instruction count minimal (running
-            // stage counter and descriptors instead of divisions and re-encoding).
+            // These threads pace the tensor core: keep the per-step instruction count minimal (running ring
+            // position and descriptors instead of divisions and re-encoding).
             const uint64_t a_desc0 = tm_smem_desc(tile_base), b_desc0 = tm_smem_desc(tile_base + TM_A_BYTES);
             constexpr uint64_t desc_step = (uint64_t)(STAGE_BYTES >> 4);
-            uint64_t a_desc = a_desc0, b_desc = b_desc0;
-            uint32_t full_bar = a_full, empty_bar = st_empty, phase = 0, acc = 0;
-            int st = 0;
-            for (int ks = 0; ks < p.ksteps; ++ks) {
+            const uint32_t tmem_acc = tmem_base + (uint32_t)(issuer * BN);
+            int st = issuer % S;
+            uint32_t phase = (uint32_t)((issuer / S) & 1), acc = 0;
+            const int nacc = p.issuers;
+            for (int ks = issuer; ks < p.ksteps; ks += nacc) {
                 MCU_TRACE_POINT(0, ks, 0);
-                ok = tm_mbar_wait(full_bar, phase);  // weight tile converted and activation tile landed
+                ok = tm_mbar_wait(a_full + 8u * st, phase);  // weight tile converted and activation tile landed
                 MCU_TRACE_POINT(0, ks, 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                tm_mma(tmem_base, a_desc, b_desc, idesc, acc);
-                tm_mma(tmem_base, a_desc + 2, b_desc + 2, idesc, 1u);  // +32 bytes along K inside the swizzle row
-                tm_mma(tmem_base, a_desc + 4, b_desc + 4, idesc, 1u);
-                tm_mma(tmem_base, a_desc + 6, b_desc + 6, idesc, 1u);
+                const uint64_t a_desc = a_desc0 + desc_step * (uint64_t)st, b_desc = b_desc0 + desc_step * (uint64_t)st;
+                tm_mma(tmem_acc, a_desc, b_desc, idesc, acc);
+                tm_mma(tmem_acc, a_desc + 2, b_desc + 2, idesc, 1u);  // +32 bytes along K inside the swizzle row
+                tm_mma(tmem_acc, a_desc + 4, b_desc + 4, idesc, 1u);
+                tm_mma(tmem_acc, a_desc + 6, b_desc + 6, idesc, 1u);
                 acc = 1u;
-                tm_commit(empty_bar);
+                tm_commit(st_empty + 8u * st);
                 MCU_TRACE_POINT(0, ks, 3);
-                if (++st == S) {
-                    st = 0;
+                st += nacc;
+                while (st >= S) {
+                    st -= S;
                     phase ^= 1u;
-                    a_desc = a_desc0, b_desc = b_desc0, full_bar = a_full, empty_bar = st_empty;
-                } else {
-                    a_desc += desc_step, b_desc += desc_step, full_bar += 8u, empty_bar += 8u;
                 }
             }
             if (!ok) {
                 atomicExch(p.err, 7);
                 *abort_flag = 1;
             }
-            tm_commit(accum_bar);
+            tm_commit(accum_bar);  // arrives when every MMA this thread issued has completed
         }
         __syncwarp();
     } else {
@@ -481,25 +491,35 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             const float bias = (p.bias != nullptr && f_ok) ? p.bias[f] : 0.0f;
             for (int cb = 0; cb < BN / 2; cb += 32) {
                 if (t0 + col0 + cb >= p.T) break;  // warp-uniform: no tokens left in this column block
-                uint32_t v[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(col0 + cb);
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]),
-                      "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]),
-                      "=r"(v[30]), "=r"(v[31])
-                    : "r"(taddr)
-                    : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float sum[32];
+#pragma unroll
+                for (int jj = 0; jj < 32; ++jj) sum[jj] = 0.0f;
+                const int n_used = p.ksteps < p.issuers ? p.ksteps : p.issuers;  // accumulators that received a K step
+#pragma unroll
+                for (int a = 0; a < NACC; ++a) {
+                    if (a >= n_used) break;  // warp-uniform
+                    uint32_t v[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(a * BN + col0 + cb);
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+                          "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
+                          "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
+                          "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                        : "r"(taddr)
+                        : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) sum[jj] += __uint_as_float(v[jj]);
+                }
                 if (f_ok) {
 #pragma unroll
                     for (int jj = 0; jj < 32; ++jj) {
                         const int t = t0 + col0 + cb + jj;
-                        if (t < p.T) p.out[(size_t)t * p.ldo + f] = __uint_as_float(v[jj]) * p.rowscale[t] + bias;
+                        if (t < p.T) p.out[(size_t)t * p.ldo + f] = sum[jj] * p.rowscale[t] + bias;
                     }
                 }
             }
@@ -507,9 +527,15 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (*abort_flag) {
+        // A wait ran out and the agents stopped early: bulk tensor copies may still be landing in this CTA's
+        // shared memory.  Give them time to finish before the CTA (and its shared memory) goes away.
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
     if (warp == TM_ALL_CONV) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -587,9 +613,24 @@ static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, Gemm
         --R;
         S = (budget - R * raw_stage_bytes) / stage_bytes;
     }
+    constexpr int NACC = BN == 64 ? 4 : (BN == 128 ? 2 : 1);
+    while (S < NACC && R > 2) {  // every issuer needs a stage of its own
+        --R;
+        S = (budget - R * raw_stage_bytes) / stage_bytes;
+    }
     if (S > TM_MAX_RING) S = TM_MAX_RING;
     if (S > p.ksteps) S = p.ksteps;
     if (S < 1) return cudaErrorInvalidConfiguration;
+    // Issuer i takes the K steps ks = i (mod issuers) and, with the ring depth a multiple of the issuer count,
+    // always the same stages: successive uses of one full-barrier are then waited on by one thread in order.
+    // (A parity wait cannot tell "this phase" from "two phases ago"; an issuer that got ahead of the thread
+    // owning the previous use of the stage would fall through its wait.)
+    static const int issuer_cap = getenv("MARMOT_CUDA_GEMM_ISSUERS") ? atoi(getenv("MARMOT_CUDA_GEMM_ISSUERS")) : NACC;
+    int issuers = NACC;
+    if (issuer_cap >= 1 && issuers > issuer_cap) issuers = issuer_cap >= 4 ? 4 : (issuer_cap >= 2 ? 2 : 1);
+    while (issuers > 1 && S < issuers) issuers /= 2;
+    S = S / issuers * issuers;
+    p.issuers = issuers;
     p.stages = S;
     p.raw_stages = R;
     const int smem = 2048 + S * stage_bytes + R * raw_stage_bytes;
@@ -642,7 +683,7 @@ cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __hal
         if (rows < 8) rows = 8;
     }
     p.rows_per_cta = rows;
-    p.stages = p.raw_stages = 0;
+    p.stages = p.raw_stages = p.issuers = 0;
 #ifdef MCU_TRACE
     {
         static long long *trace_buf = nullptr;
