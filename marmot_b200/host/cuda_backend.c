@@ -1,0 +1,577 @@
+// marmot CUDA backend, host side (C23): the device-ops vtable and the implementation functions the
+// generated CUDA dispatch entries call, written against marmot's own headers.  Every function here is
+// a thin adapter from marmot tensors to the plain-pointer C ABI of libmarmot_cuda (marmot_cuda.h); no
+// arithmetic happens on the host.
+//
+// Reference counterparts (paths in the marmot tree):
+//   marmot_get_cuda_ops            <- marmot_get_cpu_ops, src/backends/cpu/dispatch/device_ops.c:12-30
+//   cuda_matmul_quantized_*        <- cpu_matmul_quantized_{q4_k,q6_k,q8_0}, matmul_quant_dispatch.c:905-960
+//   cuda_matmul_quantized_dual_output <- cpu_matmul_quantized_dual_output, matmul_quant_dispatch.c:593-856
+//   cuda_moe_experts_impl          <- cpu_moe_experts_impl, src/backends/cpu/ops/moe/moe_ops.c:1069-1178
+//   cuda_topk_impl                 <- cpu_topk_impl, moe_ops.c:789-889
+//   cuda_dequantize_*              <- cpu_dequantize_*, src/backends/cpu/quantization/formats/*.c
+//
+// Residency: marmot tensors own host memory and are identified by their host pointer.  The backend keeps a
+// map host range -> device mirror.  `memcpy_to_device(p, p, n)` means "make [p, p+n) resident / refresh it"
+// and `memcpy_from_device(p, p, n)` "make the host copy current" (src/core/tensor/transfer.c:22,49-51).
+// Interior pointers (views into a larger allocation, e.g. one expert of a stacked MoE weight) resolve to
+// an offset inside the mirror of the enclosing range.
+#include "marmot/device.h"
+#include "marmot/error.h"
+#include "marmot/ops_types.h"
+#include "marmot/tensor.h"
+#include "marmot/types.h"
+
+#include "core/helpers/matmul.h"
+
+#include "marmot_cuda.h"
+
+#include <pthread.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+typedef struct {
+    uintptr_t host;  // start of the host range
+    size_t bytes;
+    void *dev;
+} cuda_mirror_t;
+
+typedef struct cuda_ctx {
+    mcu_context_t *mcu;
+    pthread_mutex_t mu;
+    cuda_mirror_t *mirrors;  // sorted by host address, ranges never overlap
+    size_t n_mirrors, cap_mirrors;
+    size_t bytes_resident;
+} cuda_ctx_t;
+
+static marmot_error_t cuda_fail(int rc) {
+    marmot_set_error((marmot_error_t)rc, mcu_last_error_message());
+    return (marmot_error_t)rc;
+}
+
+// ---- residency map ------------------------------------------------------------------------------------
+
+// index of the first mirror whose end lies beyond `addr`
+static size_t mirror_lower_bound(const cuda_ctx_t *c, uintptr_t addr) {
+    size_t lo = 0, hi = c->n_mirrors;
+    while (lo < hi) {
+        const size_t mid = (lo + hi) / 2;
+        if (c->mirrors[mid].host + c->mirrors[mid].bytes <= addr) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+
+// mirror that fully contains [addr, addr + bytes), or nullptr
+static cuda_mirror_t *mirror_find(cuda_ctx_t *c, uintptr_t addr, size_t bytes) {
+    const size_t i = mirror_lower_bound(c, addr);
+    if (i == c->n_mirrors) return nullptr;
+    cuda_mirror_t *m = &c->mirrors[i];
+    if (m->host <= addr && addr + bytes <= m->host + m->bytes) return m;
+    return nullptr;
+}
+
+static void mirror_drop_overlapping(cuda_ctx_t *c, uintptr_t addr, size_t bytes) {
+    size_t i = mirror_lower_bound(c, addr);
+    while (i < c->n_mirrors && c->mirrors[i].host < addr + bytes) {
+        mcu_free(c->mcu, c->mirrors[i].dev);
+        c->bytes_resident -= c->mirrors[i].bytes;
+        memmove(&c->mirrors[i], &c->mirrors[i + 1], (c->n_mirrors - i - 1) * sizeof(cuda_mirror_t));
+        c->n_mirrors--;
+    }
+}
+
+// Device address of host range [addr, addr+bytes); allocates a mirror when none covers it (ranges that only
+// partly overlap an older mirror replace it).
+static marmot_error_t mirror_get(cuda_ctx_t *c, const void *host, size_t bytes, bool *created, void **dev_out) {
+    const uintptr_t addr = (uintptr_t)host;
+    *created = false;
+    cuda_mirror_t *m = mirror_find(c, addr, bytes);
+    if (m != nullptr) {
+        *dev_out = (uint8_t *)m->dev + (addr - m->host);
+        return MARMOT_SUCCESS;
+    }
+    mirror_drop_overlapping(c, addr, bytes);
+    if (c->n_mirrors == c->cap_mirrors) {
+        const size_t cap = c->cap_mirrors == 0 ? 64 : c->cap_mirrors * 2;
+        cuda_mirror_t *grown = realloc(c->mirrors, cap * sizeof(cuda_mirror_t));
+        if (grown == nullptr) {
+            marmot_set_error(MARMOT_ERROR_OUT_OF_MEMORY, "CUDA residency map allocation failed");
+            return MARMOT_ERROR_OUT_OF_MEMORY;
+        }
+        c->mirrors = grown;
+        c->cap_mirrors = cap;
+    }
+    void *dev = nullptr;
+    const int rc = mcu_malloc(c->mcu, bytes, &dev);
+    if (rc != 0) return cuda_fail(rc);
+    const size_t at = mirror_lower_bound(c, addr);
+    memmove(&c->mirrors[at + 1], &c->mirrors[at], (c->n_mirrors - at) * sizeof(cuda_mirror_t));
+    c->mirrors[at] = (cuda_mirror_t){.host = addr, .bytes = bytes, .dev = dev};
+    c->n_mirrors++;
+    c->bytes_resident += bytes;
+    *created = true;
+    *dev_out = dev;
+    return MARMOT_SUCCESS;
+}
+
+// ---- tensors <-> mirrors ----------------------------------------------------------------------------------
+
+static size_t tensor_bytes(const marmot_tensor_t *t) {
+    const size_t logical = marmot_tensor_size_bytes(t);
+    return logical != 0 ? logical : t->capacity_bytes;
+}
+
+// Read-only operand: resident and up to date on the device.
+static marmot_error_t resident_ro(cuda_ctx_t *c, const marmot_tensor_t *t, size_t bytes, const void **dev) {
+    bool created = false;
+    void *d = nullptr;
+    marmot_error_t st = mirror_get(c, t->data, bytes, &created, &d);
+    if (st != MARMOT_SUCCESS) return st;
+    if (created || t->memory_location != MARMOT_MEMORY_DEVICE) {
+        const int rc = mcu_memcpy_to_device(c->mcu, d, t->data, bytes);
+        if (rc != 0) return cuda_fail(rc);
+        // the two copies are now equal; like the CPU backend's pack caches this bookkeeping is not part of the
+        // tensor's logical value
+        marmot_tensor_t *mt = (marmot_tensor_t *)t;
+        mt->memory_location = MARMOT_MEMORY_DEVICE;
+        mt->needs_sync = false;
+    }
+    *dev = d;
+    return MARMOT_SUCCESS;
+}
+
+// Output operand: a mirror to write into; the device copy becomes the current one.
+static marmot_error_t resident_rw(cuda_ctx_t *c, marmot_tensor_t *t, size_t bytes, void **dev) {
+    bool created = false;
+    marmot_error_t st = mirror_get(c, t->data, bytes, &created, dev);
+    if (st != MARMOT_SUCCESS) return st;
+    t->memory_location = MARMOT_MEMORY_DEVICE;
+    t->needs_sync = true;  // marmot_tensor_to_host() will fetch it (src/core/tensor/transfer.c:36-62)
+    return MARMOT_SUCCESS;
+}
+
+// ---- device-ops vtable (include/marmot/device.h:43-66) ------------------------------------------------------
+
+static marmot_error_t cuda_init(void **device_ctx) {
+    if (device_ctx == nullptr) return MARMOT_ERROR_INVALID_ARGUMENT;
+    cuda_ctx_t *c = calloc(1, sizeof(*c));
+    if (c == nullptr) {
+        marmot_set_error(MARMOT_ERROR_OUT_OF_MEMORY, "CUDA context allocation failed");
+        return MARMOT_ERROR_OUT_OF_MEMORY;
+    }
+    int device = 0;
+    const char *env = getenv("MARMOT_CUDA_DEVICE");
+    if (env != nullptr) device = atoi(env);
+    const int rc = mcu_context_create(device, &c->mcu);
+    if (rc != 0) {
+        free(c);
+        return cuda_fail(rc);
+    }
+    pthread_mutex_init(&c->mu, nullptr);
+    *device_ctx = c;
+    return MARMOT_SUCCESS;
+}
+
+static void cuda_destroy(const void *device_ctx) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) return;
+    mcu_synchronize(c->mcu);
+    for (size_t i = 0; i < c->n_mirrors; ++i) mcu_free(c->mcu, c->mirrors[i].dev);
+    free(c->mirrors);
+    mcu_context_destroy(c->mcu);
+    pthread_mutex_destroy(&c->mu);
+    free(c);
+}
+
+static marmot_error_t cuda_configure(const void *device_ctx, const marmot_context_t *ctx) {
+    (void)ctx;
+    return device_ctx != nullptr ? MARMOT_SUCCESS : MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+}
+
+static marmot_error_t cuda_alloc(const void *device_ctx, size_t size, void **ptr) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    const int rc = mcu_malloc(c->mcu, size, ptr);
+    return rc == 0 ? MARMOT_SUCCESS : cuda_fail(rc);
+}
+
+static void cuda_free(const void *device_ctx, void *ptr) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c != nullptr) mcu_free(c->mcu, ptr);
+}
+
+// dst is the identity (host address) of the tensor storage; src holds the bytes (often the same pointer)
+static marmot_error_t cuda_memcpy_to_device(const void *device_ctx, void *dst, const void *src, size_t size) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    if (size == 0) return MARMOT_SUCCESS;
+    pthread_mutex_lock(&c->mu);
+    bool created = false;
+    void *d = nullptr;
+    marmot_error_t st = mirror_get(c, dst, size, &created, &d);
+    if (st == MARMOT_SUCCESS) {
+        const int rc = mcu_memcpy_to_device(c->mcu, d, src, size);
+        if (rc != 0) st = cuda_fail(rc);
+    }
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
+
+static marmot_error_t cuda_memcpy_from_device(const void *device_ctx, void *dst, const void *src, size_t size) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    if (size == 0) return MARMOT_SUCCESS;
+    pthread_mutex_lock(&c->mu);
+    marmot_error_t st = MARMOT_SUCCESS;
+    cuda_mirror_t *m = mirror_find(c, (uintptr_t)src, size);
+    if (m != nullptr) {
+        const int rc = mcu_memcpy_to_host(c->mcu, dst, (const uint8_t *)m->dev + ((uintptr_t)src - m->host), size);
+        if (rc != 0) st = cuda_fail(rc);
+    } else {
+        const int rc = mcu_synchronize(c->mcu);  // nothing resident for this range: the host copy is the only one
+        if (rc != 0) st = cuda_fail(rc);
+    }
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
+
+static marmot_error_t cuda_synchronize(const void *device_ctx) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    const int rc = mcu_synchronize(c->mcu);
+    return rc == 0 ? MARMOT_SUCCESS : cuda_fail(rc);
+}
+
+static marmot_error_t cuda_allocator_usage(const void *device_ctx, marmot_allocator_usage_t *usage) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr || usage == nullptr) return MARMOT_ERROR_INVALID_ARGUMENT;
+    memset(usage, 0, sizeof(*usage));
+    usage->current_bytes = c->bytes_resident;
+    usage->active_allocations = c->n_mirrors;
+    return MARMOT_SUCCESS;
+}
+
+static void cuda_on_host_range_freed(void *device_ctx, const void *start, size_t length) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr || start == nullptr) return;
+    pthread_mutex_lock(&c->mu);
+    mirror_drop_overlapping(c, (uintptr_t)start, length > 0 ? length : 1);
+    pthread_mutex_unlock(&c->mu);
+}
+
+static void cuda_on_host_ptr_freed(void *device_ctx, const void *ptr) { cuda_on_host_range_freed(device_ctx, ptr, 1); }
+
+static const marmot_device_ops_t g_cuda_ops = {
+    .init = cuda_init,
+    .destroy = cuda_destroy,
+    .configure = cuda_configure,
+    .alloc = cuda_alloc,
+    .free = cuda_free,
+    .memcpy_to_device = cuda_memcpy_to_device,
+    .memcpy_from_device = cuda_memcpy_from_device,
+    .synchronize = cuda_synchronize,
+    .allocator_usage = cuda_allocator_usage,
+    .graph_batch_begin = nullptr,
+    .graph_batch_end = nullptr,
+    .on_host_ptr_freed = cuda_on_host_ptr_freed,
+    .on_host_range_freed = cuda_on_host_range_freed,
+};
+
+const marmot_device_ops_t *marmot_get_cuda_ops(void) { return &g_cuda_ops; }
+
+// ---- operator implementations ---------------------------------------------------------------------------------
+
+static int mcu_kind_of(marmot_quant_kind_t kind) {
+    switch (kind) {
+    case MARMOT_QUANT_KIND_Q4_K: return MCU_KIND_Q4_K;
+    case MARMOT_QUANT_KIND_Q6_K: return MCU_KIND_Q6_K;
+    case MARMOT_QUANT_KIND_Q8_0: return MCU_KIND_Q8_0;
+    default: return -1;
+    }
+}
+
+static marmot_error_t cuda_matmul_quantized(
+    const void *device_ctx, const marmot_tensor_t *input, const marmot_tensor_t *weight_a,
+    const marmot_tensor_t *weight_b, const marmot_matmul_epilogue_t *epilogue, marmot_tensor_t *out_a,
+    marmot_tensor_t *out_b, marmot_quant_kind_t expect_kind
+) {
+    if (input == nullptr || weight_a == nullptr || out_a == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "Tensor argument must not be null");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) {
+        marmot_set_error(MARMOT_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+        return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    }
+    marmot_matmul_dims_t dims = {0};
+    marmot_matmul_activation_profile_t profile = {0};
+    const marmot_quant_kind_traits_t *traits = nullptr;
+    marmot_error_t st = marmot_matmul_validate_quantized(input, weight_a, out_a, &dims, &profile, &traits);
+    if (st != MARMOT_SUCCESS) return st;
+    if (weight_a->quant_kind != expect_kind || mcu_kind_of(weight_a->quant_kind) < 0) {
+        marmot_set_error(MARMOT_ERROR_NOT_IMPLEMENTED, "CUDA quantized matmul: unsupported quant kind");
+        return MARMOT_ERROR_NOT_IMPLEMENTED;
+    }
+    if (!profile.input_is_fp32 || !profile.output_is_fp32) {
+        marmot_set_error(MARMOT_ERROR_UNSUPPORTED_DTYPE, "CUDA quantized matmul takes FLOAT32 activations and output");
+        return MARMOT_ERROR_UNSUPPORTED_DTYPE;
+    }
+    if (input->shape.strides[1] != 1 || out_a->shape.strides[1] != 1) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "CUDA quantized matmul needs unit inner strides");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    const int kind = mcu_kind_of(weight_a->quant_kind);
+    const size_t T = dims.N, K = dims.K, F = dims.M;
+    const size_t ldx = input->shape.strides[0], ldo = out_a->shape.strides[0];
+    if (weight_b != nullptr) {
+        if (out_b == nullptr || weight_b->quant_kind != weight_a->quant_kind || weight_b->shape.shape[0] != F ||
+            weight_b->shape.shape[1] != K || out_b->shape.strides[0] != ldo) {
+            marmot_set_error(MARMOT_ERROR_DIMENSION_MISMATCH, "dual-output matmul operands do not match");
+            return MARMOT_ERROR_DIMENSION_MISMATCH;
+        }
+    }
+    const size_t w_bytes = F * mcu_row_bytes(kind, K);
+    pthread_mutex_lock(&c->mu);
+    const void *x = nullptr, *wa = nullptr, *wb = nullptr, *bias = nullptr;
+    void *ya = nullptr, *yb = nullptr;
+    st = resident_ro(c, input, ((T - 1) * ldx + K) * sizeof(float), &x);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, weight_a, w_bytes, &wa);
+    if (st == MARMOT_SUCCESS && weight_b != nullptr) st = resident_ro(c, weight_b, w_bytes, &wb);
+    if (st == MARMOT_SUCCESS && epilogue != nullptr && epilogue->bias != nullptr) {
+        if (epilogue->bias->dtype != MARMOT_DTYPE_FLOAT32 || marmot_tensor_num_elements(epilogue->bias) != F) {
+            marmot_set_error(MARMOT_ERROR_UNSUPPORTED_DTYPE, "CUDA matmul bias must be FLOAT32 [features]");
+            st = MARMOT_ERROR_UNSUPPORTED_DTYPE;
+        } else {
+            st = resident_ro(c, epilogue->bias, F * sizeof(float), &bias);
+        }
+    }
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, out_a, ((T - 1) * ldo + F) * sizeof(float), &ya);
+    if (st == MARMOT_SUCCESS && out_b != nullptr) st = resident_rw(c, out_b, ((T - 1) * ldo + F) * sizeof(float), &yb);
+    if (st == MARMOT_SUCCESS) {
+        const int rc = weight_b == nullptr
+            ? mcu_linear(c->mcu, kind, x, ldx, wa, T, K, F, bias, ya, ldo)
+            : mcu_linear_dual(c->mcu, kind, x, ldx, wa, wb, T, K, F, ya, yb, ldo);
+        if (rc != 0) st = cuda_fail(rc);
+    }
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
+
+marmot_error_t cuda_matmul_quantized_q4_k(
+    const void *device_ctx, const marmot_tensor_t *input, const marmot_tensor_t *weight,
+    const marmot_matmul_epilogue_t *epilogue, marmot_tensor_t *out
+) {
+    return cuda_matmul_quantized(device_ctx, input, weight, nullptr, epilogue, out, nullptr, MARMOT_QUANT_KIND_Q4_K);
+}
+
+marmot_error_t cuda_matmul_quantized_q6_k(
+    const void *device_ctx, const marmot_tensor_t *input, const marmot_tensor_t *weight,
+    const marmot_matmul_epilogue_t *epilogue, marmot_tensor_t *out
+) {
+    return cuda_matmul_quantized(device_ctx, input, weight, nullptr, epilogue, out, nullptr, MARMOT_QUANT_KIND_Q6_K);
+}
+
+marmot_error_t cuda_matmul_quantized_q8_0(
+    const void *device_ctx, const marmot_tensor_t *input, const marmot_tensor_t *weight,
+    const marmot_matmul_epilogue_t *epilogue, marmot_tensor_t *out
+) {
+    return cuda_matmul_quantized(device_ctx, input, weight, nullptr, epilogue, out, nullptr, MARMOT_QUANT_KIND_Q8_0);
+}
+
+marmot_error_t cuda_matmul_quantized_dual_output(
+    const void *device_ctx, const marmot_tensor_t *input, const marmot_tensor_t *weight_a,
+    const marmot_tensor_t *weight_b, marmot_tensor_t *out_a, marmot_tensor_t *out_b
+) {
+    if (weight_a == nullptr || weight_b == nullptr || out_b == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "Tensor argument must not be null");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    return cuda_matmul_quantized(device_ctx, input, weight_a, weight_b, nullptr, out_a, out_b, weight_a->quant_kind);
+}
+
+// Replaces cpu_topk_impl (src/backends/cpu/ops/moe/moe_ops.c:789-889): the same checks in the same order,
+// FLOAT32 values only.
+marmot_error_t cuda_topk_impl(const void *device_ctx, const marmot_topk_desc_t *desc) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (desc == nullptr || desc->x == nullptr || desc->values_out == nullptr || desc->indices_out == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "TopK descriptor is incomplete");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    if (desc->x->dtype != MARMOT_DTYPE_FLOAT32 || desc->values_out->dtype != MARMOT_DTYPE_FLOAT32 ||
+        desc->indices_out->dtype != MARMOT_DTYPE_INT32) {
+        marmot_set_error(MARMOT_ERROR_UNSUPPORTED_DTYPE, "CUDA TopK supports FLOAT32 values and INT32 indices only");
+        return MARMOT_ERROR_UNSUPPORTED_DTYPE;
+    }
+    if (desc->x->shape.ndim != 2 || desc->values_out->shape.ndim != 2 || desc->indices_out->shape.ndim != 2) {
+        marmot_set_error(MARMOT_ERROR_DIMENSION_MISMATCH, "TopK expects 2D tensors");
+        return MARMOT_ERROR_DIMENSION_MISMATCH;
+    }
+    if (desc->axis != 1 && desc->axis != -1) {
+        marmot_set_error(MARMOT_ERROR_NOT_IMPLEMENTED, "TopK currently supports only the last axis");
+        return MARMOT_ERROR_NOT_IMPLEMENTED;
+    }
+    const size_t rows = desc->x->shape.shape[0], cols = desc->x->shape.shape[1], k = desc->k;
+    if (k == 0 || k > cols || desc->values_out->shape.shape[0] != rows || desc->indices_out->shape.shape[0] != rows ||
+        desc->values_out->shape.shape[1] != k || desc->indices_out->shape.shape[1] != k) {
+        marmot_set_error(MARMOT_ERROR_DIMENSION_MISMATCH, "TopK shapes do not match");
+        return MARMOT_ERROR_DIMENSION_MISMATCH;
+    }
+    if (desc->values_out->shape.strides[0] != k || desc->indices_out->shape.strides[0] != k) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "CUDA TopK needs contiguous outputs");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    if (c == nullptr) {
+        marmot_set_error(MARMOT_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+        return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    }
+    const size_t ldx = desc->x->shape.strides[0];
+    pthread_mutex_lock(&c->mu);
+    const void *x = nullptr;
+    void *vals = nullptr, *idx = nullptr;
+    marmot_error_t st = resident_ro(c, desc->x, ((rows - 1) * ldx + cols) * sizeof(float), &x);
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, desc->values_out, rows * k * sizeof(float), &vals);
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, desc->indices_out, rows * k * sizeof(int32_t), &idx);
+    if (st == MARMOT_SUCCESS) {
+        const int rc = mcu_topk(c->mcu, x, rows, cols, ldx, k, vals, idx);
+        if (rc != 0) st = cuda_fail(rc);
+    }
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
+
+// Replaces cpu_moe_experts_impl (src/backends/cpu/ops/moe/moe_ops.c:1069-1178) for quantized experts with FLOAT32
+// activations. Expert tensors are [in, out, experts] in GGUF order (shape[0] innermost), as the reference reads
+// them (moe_ops.c:897-898).
+marmot_error_t cuda_moe_experts_impl(const void *device_ctx, const marmot_moe_experts_desc_t *desc) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (desc == nullptr || desc->hidden_states == nullptr || desc->gate_exps == nullptr || desc->up_exps == nullptr ||
+        desc->down_exps == nullptr || desc->topk_ids == nullptr || desc->topk_weights == nullptr ||
+        desc->out == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "MoE descriptor is incomplete");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    const int gk = mcu_kind_of(desc->gate_exps->quant_kind), uk = mcu_kind_of(desc->up_exps->quant_kind),
+              dk = mcu_kind_of(desc->down_exps->quant_kind);
+    if (gk < 0 || uk < 0 || dk < 0) {
+        marmot_set_error(MARMOT_ERROR_NOT_IMPLEMENTED, "CUDA MoE experts needs Q4_K, Q6_K or Q8_0 expert weights");
+        return MARMOT_ERROR_NOT_IMPLEMENTED;
+    }
+    if (desc->hidden_states->dtype != MARMOT_DTYPE_FLOAT32 || desc->topk_weights->dtype != MARMOT_DTYPE_FLOAT32 ||
+        desc->out->dtype != MARMOT_DTYPE_FLOAT32 || desc->topk_ids->dtype != MARMOT_DTYPE_INT32) {
+        marmot_set_error(
+            MARMOT_ERROR_UNSUPPORTED_DTYPE,
+            "CUDA MoE experts supports FLOAT32 activations with FLOAT32 router weights and INT32 expert ids"
+        );
+        return MARMOT_ERROR_UNSUPPORTED_DTYPE;
+    }
+    const marmot_tensor_t *h = desc->hidden_states;
+    if (h->shape.ndim != 2 || desc->out->shape.ndim != 2 || desc->topk_ids->shape.ndim != 2 ||
+        desc->topk_weights->shape.ndim != 2 || desc->gate_exps->shape.ndim != 3 || desc->up_exps->shape.ndim != 3 ||
+        desc->down_exps->shape.ndim != 3) {
+        marmot_set_error(MARMOT_ERROR_DIMENSION_MISMATCH, "MoE tensors have the wrong rank");
+        return MARMOT_ERROR_DIMENSION_MISMATCH;
+    }
+    const size_t T = h->shape.shape[0], H = h->shape.shape[1];
+    const size_t FF = desc->gate_exps->shape.shape[1], E = desc->gate_exps->shape.shape[2];
+    const size_t k = desc->topk_ids->shape.shape[1];
+    const size_t *us = desc->up_exps->shape.shape, *ds = desc->down_exps->shape.shape;
+    if (desc->gate_exps->shape.shape[0] != H || us[0] != H || us[1] != FF || us[2] != E || ds[0] != FF || ds[1] != H ||
+        ds[2] != E || desc->out->shape.shape[0] != T || desc->out->shape.shape[1] != H ||
+        desc->topk_ids->shape.shape[0] != T || desc->topk_weights->shape.shape[0] != T ||
+        desc->topk_weights->shape.shape[1] != k) {
+        marmot_set_error(MARMOT_ERROR_DIMENSION_MISMATCH, "MoE tensor shapes do not match");
+        return MARMOT_ERROR_DIMENSION_MISMATCH;
+    }
+    if (h->shape.strides[0] != H || desc->out->shape.strides[0] != H || desc->topk_ids->shape.strides[0] != k ||
+        desc->topk_weights->shape.strides[0] != k) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "CUDA MoE experts needs contiguous activations");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    if (c == nullptr) {
+        marmot_set_error(MARMOT_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+        return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    }
+    pthread_mutex_lock(&c->mu);
+    const void *hid = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr, *ids = nullptr, *wts = nullptr;
+    void *out = nullptr;
+    marmot_error_t st = resident_ro(c, h, T * H * sizeof(float), &hid);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, desc->gate_exps, E * FF * mcu_row_bytes(gk, H), &gate);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, desc->up_exps, E * FF * mcu_row_bytes(uk, H), &up);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, desc->down_exps, E * H * mcu_row_bytes(dk, FF), &down);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, desc->topk_ids, T * k * sizeof(int32_t), &ids);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, desc->topk_weights, T * k * sizeof(float), &wts);
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, desc->out, T * H * sizeof(float), &out);
+    if (st == MARMOT_SUCCESS) {
+        const int rc = mcu_moe_experts(
+            c->mcu, gk, uk, dk, hid, T, H, FF, E, gate, up, down, ids, wts, k, (int)desc->ffn_type,
+            desc->weights_scale, (int)desc->router_weight_policy, out
+        );
+        if (rc != 0) st = cuda_fail(rc);
+    }
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
+
+// Replaces cpu_dequantize_{q4_k,q6_k,q8_0} -> cpu_dequantize_blockwise
+// (src/backends/cpu/quantization/ops/quantize_core.c:268-330): rows are padded to whole blocks in the input.
+static marmot_error_t
+cuda_dequantize_blockwise(const void *device_ctx, int kind, const marmot_tensor_t *input, marmot_tensor_t *output) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (input == nullptr || output == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "Null tensor pointer");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    if (input->dtype != MARMOT_DTYPE_UINT8 && input->dtype != MARMOT_DTYPE_INT8) {
+        marmot_set_error(MARMOT_ERROR_UNSUPPORTED_DTYPE, "Block dequantization expects UINT8 or INT8 input buffer");
+        return MARMOT_ERROR_UNSUPPORTED_DTYPE;
+    }
+    if (output->dtype != MARMOT_DTYPE_FLOAT32) {
+        marmot_set_error(MARMOT_ERROR_UNSUPPORTED_DTYPE, "Block dequantization requires FLOAT32 output");
+        return MARMOT_ERROR_UNSUPPORTED_DTYPE;
+    }
+    const size_t total = marmot_tensor_num_elements(output);
+    const size_t rows = output->shape.ndim == 2 ? output->shape.shape[0] : 1;
+    const size_t row = output->shape.ndim == 2 ? output->shape.shape[1] : total;
+    const size_t row_bytes = mcu_row_bytes(kind, row);
+    if (rows * row_bytes > tensor_bytes(input)) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "Quantized input buffer too small");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    if (c == nullptr) {
+        marmot_set_error(MARMOT_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+        return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    }
+    const size_t block = kind == MCU_KIND_Q8_0 ? 32 : 256;
+    pthread_mutex_lock(&c->mu);
+    const void *src = nullptr;
+    void *dst = nullptr;
+    marmot_error_t st = resident_ro(c, input, rows * row_bytes, &src);
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, output, total * sizeof(float), &dst);
+    if (st == MARMOT_SUCCESS) {
+        int rc = 0;
+        if (row % block == 0) {
+            rc = mcu_dequantize(c->mcu, kind, src, total, dst);
+        } else {
+            for (size_t r = 0; r < rows && rc == 0; ++r)
+                rc = mcu_dequantize(c->mcu, kind, (const uint8_t *)src + r * row_bytes, row, (float *)dst + r * row);
+        }
+        if (rc != 0) st = cuda_fail(rc);
+    }
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
+
+marmot_error_t cuda_dequantize_q4_k(const void *device_ctx, const marmot_tensor_t *input, marmot_tensor_t *output) {
+    return cuda_dequantize_blockwise(device_ctx, MCU_KIND_Q4_K, input, output);
+}
+
+marmot_error_t cuda_dequantize_q6_k(const void *device_ctx, const marmot_tensor_t *input, marmot_tensor_t *output) {
+    return cuda_dequantize_blockwise(device_ctx, MCU_KIND_Q6_K, input, output);
+}
+
+marmot_error_t cuda_dequantize_q8_0(const void *device_ctx, const marmot_tensor_t *input, marmot_tensor_t *output) {
+    return cuda_dequantize_blockwise(device_ctx, MCU_KIND_Q8_0, input, output);
+}
