@@ -39,6 +39,7 @@ W_BYTES = F_DIM * (K_DIM // 256) * 144
 ALG_BYTES = W_BYTES + T_TOK * K_DIM * 4 + T_TOK * F_DIM * 4  # 9 469 952
 METRIC = "q4k_gemv_hbm_gbps"
 UNIT = "GB/s"
+NCU_TRAFFIC_BYTES = 9_476_864  # DRAM bytes of one launch, from the committed ncu capture of this shape
 WORKLOAD = "Q4_K GEMV T=1 K=4096 F=4096 (BASELINE config 1), rotation of distinct weight matrices"
 
 
@@ -134,6 +135,62 @@ def cpu_gemv_time(copies: int, iters: int, threads: int):
     return dt, kind
 
 
+def time_other_regimes(ctx, dev):
+    """Short CUDA-graph timings of the other regimes of the path (not the headline): large-F GEMVs of the three
+    formats, the batched-decode shape and the Q8_0 prefill GEMM of BASELINE config 2.  Each entry is one
+    `mcu_linear` call (activation quantisation included), rotating over weight copies larger than L2."""
+    import torch
+
+    from marmot_b200.profile_case import synthetic_blocks
+    from marmot_b200.runtime import KIND_BY_NAME, row_bytes
+
+    peak_bw, _ = measured_peaks()
+    peaks = json.loads((REPO / "MEASURED_PEAKS.json").read_text()) if (REPO / "MEASURED_PEAKS.json").exists() else {}
+    peak_tf = float(peaks.get("bf16_tflops", 1590.0))
+    out = []
+    stream = torch.cuda.Stream(dev)
+    ctx.set_stream(stream.cuda_stream)
+    rng = np.random.default_rng(11)
+    for name, T, K, F, copies in [("q4_k", 1, 4096, 28672, 4), ("q6_k", 1, 4096, 28672, 4), ("q8_0", 1, 4096, 28672, 4),
+                                  ("q4_k", 8, 4096, 14336, 8), ("q4_k", 64, 4096, 14336, 4),
+                                  ("q8_0", 512, 4096, 14336, 2), ("q4_k", 512, 4096, 14336, 2)]:
+        kind = KIND_BY_NAME[name]
+        ws = [ctx.upload(synthetic_blocks(kind, F, K, rng)) for _ in range(copies)]
+        x = torch.from_numpy(rng.normal(0, 1, (T, K)).astype(np.float32)).to(dev)
+        y = torch.empty((T, F), dtype=torch.float32, device=dev)
+        with torch.cuda.stream(stream):
+            for w in ws:
+                ctx.linear(kind, x, w, F, out=y)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for w in ws:
+                ctx.linear(kind, x, w, F, out=y)
+        reps = 10
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                g.replay()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
+        nbytes = F * row_bytes(kind, K) + 4 * T * (K + F)
+        gbs, tf = nbytes / us / 1e3, 2.0 * T * K * F / us / 1e6
+        entry = {"quant": name, "T": T, "K": K, "F": F, "us_per_call": round(us, 2), "GBps": round(gbs, 1),
+                 "TFLOPs": round(tf, 2)}
+        if T <= 64:
+            entry["frac_hbm"] = round(gbs / peak_bw, 3)
+        else:
+            entry["frac_tensor"] = round(tf / peak_tf, 3)
+        out.append(entry)
+        del g, ws
+    ctx.set_stream(0)
+    return out
+
+
 def run_reference_arm(args, rank: int):
     if rank != 0:
         return
@@ -171,6 +228,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-extra", action="store_true", help="skip the short timings of the other regimes")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -301,10 +359,15 @@ def main():
                 "d2h_bytes_per_step": R * T_TOK * F_DIM * 4, "steps": e2e_steps,
                 "note": "weights device resident; activations from pinned host memory, result read back to host"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": peak_kind, "frac_of_nominal_8TBs": achieved / 8000.0,
-                     "kernel": "gemv_q4_k_kernel<1>", "us_per_launch": per_launch_s * 1e6},
+                     "traffic": NCU_TRAFFIC_BYTES, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of "
+                     "one launch of this kernel and shape (profiles/gemv_stream_q4k_T1_K4096_F4096.md)",
+                     "peak_source": peak_kind, "frac_of_nominal_8TBs": achieved / 8000.0,
+                     "algorithmic_bytes": ALG_BYTES, "kernel": "gemv_stream_kernel<Q4_K, T=1, NW=14, MINB=2>",
+                     "us_per_launch": per_launch_s * 1e6},
         "clocks": clocks,
     }
+    if not args.no_extra and world == 1:
+        line["other_regimes"] = time_other_regimes(ctx, dev)
     if not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         iters = 200

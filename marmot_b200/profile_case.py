@@ -1,0 +1,94 @@
+"""Run one quantized-linear shape a few times through the C ABI: the small, self-ending command that a
+profiler (ncu) or a quick timing wraps.
+
+    python -m marmot_b200.profile_case --kind q4_k -T 1 -K 4096 -F 4096 --copies 16 --iters 3
+
+The weights rotate over ``--copies`` distinct matrices so that a memory-bound kernel reads from HBM rather
+than from L2.  With ``--time`` the calls are also captured in a CUDA graph and replayed, and the average
+device time per call is printed (a number taken under a profiler means nothing).
+"""
+from __future__ import annotations
+
+import argparse
+
+import numpy as np
+
+from .runtime import BLOCK_BYTES, BLOCK_VALUES, KIND_BY_NAME, KIND_Q4_K, KIND_Q6_K, Context, row_bytes
+
+REGIMES = {"auto": 0, "gemv": 1, "gemm": 2, "gemv_plain": 3}
+
+
+def synthetic_blocks(kind: int, rows: int, K: int, rng: np.random.Generator) -> np.ndarray:
+    """Random block payloads with finite fp16 scales (0x1C00..0x1FFF is roughly 0.004..0.008)."""
+    nb = (K + BLOCK_VALUES[kind] - 1) // BLOCK_VALUES[kind]
+    blocks = rng.integers(0, 256, (rows * nb, BLOCK_BYTES[kind]), dtype=np.uint8)
+    scale_hi = rng.integers(0x1C, 0x20, rows * nb, dtype=np.uint8)
+    if kind == KIND_Q4_K:
+        blocks[:, 1] = scale_hi
+        blocks[:, 3] = scale_hi
+    elif kind == KIND_Q6_K:
+        blocks[:, 209] = scale_hi
+    else:
+        blocks[:, 1] = scale_hi
+    return blocks.reshape(-1)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--kind", default="q4_k", choices=sorted(KIND_BY_NAME))
+    ap.add_argument("-T", type=int, default=1, help="tokens")
+    ap.add_argument("-K", type=int, default=4096, help="reduction length")
+    ap.add_argument("-F", type=int, default=4096, help="output features")
+    ap.add_argument("--copies", type=int, default=16)
+    ap.add_argument("--iters", type=int, default=3, help="passes over the rotation")
+    ap.add_argument("--regime", default="auto", choices=sorted(REGIMES))
+    ap.add_argument("--time", action="store_true", help="also replay a CUDA graph of one pass and print us per call")
+    args = ap.parse_args()
+
+    import torch
+
+    kind = KIND_BY_NAME[args.kind]
+    dev = torch.device("cuda", 0)
+    ctx = Context(0)
+    ctx.set_regime(REGIMES[args.regime])
+    rng = np.random.default_rng(0)
+    weights = [ctx.upload(synthetic_blocks(kind, args.F, args.K, rng)) for _ in range(args.copies)]
+    x = torch.from_numpy(rng.normal(0, 1, (args.T, args.K)).astype(np.float32)).to(dev)
+    out = torch.empty((args.T, args.F), dtype=torch.float32, device=dev)
+
+    def one_pass():
+        for w in weights:
+            ctx.linear(kind, x, w, args.F, out=out)
+
+    stream = torch.cuda.Stream(dev)
+    ctx.set_stream(stream.cuda_stream)
+    with torch.cuda.stream(stream):
+        for _ in range(args.iters):
+            one_pass()
+    torch.cuda.synchronize()
+    nbytes = args.F * row_bytes(kind, args.K) + 4 * args.T * (args.K + args.F)
+    print(f"{args.kind} T={args.T} K={args.K} F={args.F}: {args.copies} weight copies, {args.iters} passes, "
+          f"{ctx.launch_count()} kernel launches, {nbytes} algorithmic bytes per call")
+    if args.time:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 20
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * args.copies)
+        flops = 2.0 * args.T * args.K * args.F
+        print(f"{us:.2f} us per call, {nbytes / us / 1e3:.0f} GB/s algorithmic, {flops / us / 1e6:.1f} TFLOP/s")
+    ctx.set_stream(0)
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main()
