@@ -162,6 +162,45 @@ int mcu_moe_experts(
     float *out_dev
 );
 
+/* ---- tensor / expert parallelism over the GPUs of one box.  No reference counterpart: the reference runs on
+ *      one device (include/marmot/device.h:72-80) and only reserves placeholders for sharding
+ *      (include/marmot/graph/kernel_selection.h:18-23). ---- */
+
+/* MoE expert FFN of the experts [expert_begin, expert_begin + expert_count) only: gate/up/down hold those
+ * experts' matrices, topk_ids still name experts of the whole model (0..E-1), router weights are normalised
+ * over all selected experts, and routes to other experts add nothing to out.  Summing the outputs of ranks
+ * that partition the experts gives mcu_moe_experts' result. */
+int mcu_moe_experts_local(
+    mcu_context_t *ctx, int gate_kind, int up_kind, int down_kind, const float *hidden_dev, size_t T, size_t H,
+    size_t FF, size_t E, size_t expert_begin, size_t expert_count, const void *gate_dev, const void *up_dev,
+    const void *down_dev, const int32_t *topk_ids_dev, const float *topk_weights_dev, size_t k, int ffn_type,
+    float weights_scale, int router_weight_policy, float *out_dev
+);
+
+/* Peer communicator: a staging buffer per rank, mapped into the other ranks (one process per GPU, CUDA IPC),
+ * and a one-shot all-reduce(sum) kernel over peer loads with a fixed summation order (rank 0 first), so all
+ * ranks obtain bit-identical results.  Set-up: every rank creates a communicator, exports its 64-byte handle,
+ * the host exchanges the handles (any transport), every rank connects with the array of all handles in rank
+ * order.  All ranks must issue the same sequence of all-reduces.  A peer that does not arrive within two
+ * seconds makes the kernel give up: the next mcu_synchronize reports the error, nothing hangs.
+ * Destroy only after all ranks have synchronised (a barrier on the host). */
+typedef struct mcu_peer_comm mcu_peer_comm_t;
+#define MCU_PEER_HANDLE_BYTES 64
+int mcu_peer_comm_create(mcu_context_t *ctx, int rank, int world, size_t max_bytes, mcu_peer_comm_t **out);
+int mcu_peer_comm_export(mcu_peer_comm_t *comm, void *handle_out /* MCU_PEER_HANDLE_BYTES */);
+int mcu_peer_comm_connect(mcu_peer_comm_t *comm, const void *all_handles /* world x MCU_PEER_HANDLE_BYTES */);
+/* Device buffer (max_bytes) that the NEXT mcu_peer_allreduce sums across ranks: write the partial result here. */
+void *mcu_peer_comm_staging(mcu_peer_comm_t *comm);
+int mcu_peer_allreduce(mcu_peer_comm_t *comm, size_t n_floats, float *out_dev);
+void mcu_peer_comm_destroy(mcu_peer_comm_t *comm);
+
+/* Row-parallel quantized linear: this rank's K-slice of the weights times its K-slice of the activations, written
+ * straight into the staging buffer, then the all-reduce; out [T][F] contiguous. */
+int mcu_linear_allreduce(
+    mcu_context_t *ctx, mcu_peer_comm_t *comm, int kind, const float *x_dev, size_t ldx, const void *w_dev, size_t T,
+    size_t K, size_t F, float *out_dev
+);
+
 #ifdef __cplusplus
 }
 #endif

@@ -95,6 +95,11 @@ static int check_device_error(mcu_context *ctx) {
     return MCU_SUCCESS;
 }
 
+namespace mcu {
+int context_device(const mcu_context *ctx) { return ctx->device; }
+int *context_err_flag(mcu_context *ctx) { return ctx->dev_err; }
+}  // namespace mcu
+
 static int check_ctx(mcu_context *ctx) {
     if (ctx == nullptr) return fail(MCU_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
     MCU_CUDA(cudaSetDevice(ctx->device));
@@ -391,11 +396,15 @@ int mcu_topk(mcu_context_t *ctx, const float *x_dev, size_t rows, size_t cols, s
     return MCU_SUCCESS;
 }
 
-int mcu_moe_experts(mcu_context_t *ctx, int gate_kind, int up_kind, int down_kind, const float *hidden_dev, size_t T,
-                    size_t H, size_t FF, size_t E, const void *gate_dev, const void *up_dev, const void *down_dev,
-                    const int32_t *topk_ids_dev, const float *topk_weights_dev, size_t k, int ffn_type,
-                    float weights_scale, int router_weight_policy, float *out_dev) {
+// Experts [e_begin, e_begin + e_count) are local: gate/up/down hold only those, and routes to other experts
+// contribute nothing to out (their share is another rank's).
+static int moe_experts_impl(mcu_context_t *ctx, int gate_kind, int up_kind, int down_kind, const float *hidden_dev,
+                            size_t T, size_t H, size_t FF, size_t E, size_t e_begin, size_t e_count,
+                            const void *gate_dev, const void *up_dev, const void *down_dev,
+                            const int32_t *topk_ids_dev, const float *topk_weights_dev, size_t k, int ffn_type,
+                            float weights_scale, int router_weight_policy, float *out_dev) {
     if (int rc = check_ctx(ctx)) return rc;
+    if (e_begin + e_count > E) return fail(MCU_ERROR_INVALID_ARGUMENT, "local expert range exceeds the expert count");
     if (hidden_dev == nullptr || gate_dev == nullptr || up_dev == nullptr || down_dev == nullptr ||
         topk_ids_dev == nullptr || topk_weights_dev == nullptr || out_dev == nullptr)
         return fail(MCU_ERROR_INVALID_ARGUMENT, "MoE experts descriptor is incomplete");
@@ -427,8 +436,6 @@ int mcu_moe_experts(mcu_context_t *ctx, int gate_kind, int up_kind, int down_kin
     count_launches(3);
     float *route_hidden = (float *)ctx->moe_hidden.ptr, *gate_out = (float *)ctx->moe_gate.ptr;
     float *up_out = (float *)ctx->moe_up.ptr, *route_down = (float *)ctx->moe_down.ptr;
-    MCU_CUDA(launch_moe_gather(hidden_dev, H, rb.sorted_tok, (int)routes, (int)H, route_hidden, s));
-    count_launches(1);
     // The per-expert launches need the group sizes on the host.
     ctx->host_counts.resize(2 * (E + 1));
     MCU_CUDA(cudaMemcpyAsync(ctx->host_counts.data(), rb.counts, 2 * (E + 1) * sizeof(int), cudaMemcpyDeviceToHost, s));
@@ -436,13 +443,16 @@ int mcu_moe_experts(mcu_context_t *ctx, int gate_kind, int up_kind, int down_kin
     if (ctx->host_counts[E] != 0) return fail(MCU_ERROR_INVALID_ARGUMENT, "MoE expert id is out of range");
     const int *counts = ctx->host_counts.data();
     const int *offsets = counts + (E + 1);
+    const int pos_lo = offsets[e_begin], pos_hi = offsets[e_begin + e_count];  // sorted positions of the local routes
+    MCU_CUDA(launch_moe_gather(hidden_dev, H, rb.sorted_tok, pos_lo, pos_hi, (int)H, route_hidden, s));
+    count_launches(1);
     const size_t gate_slice = FF * mcu_row_bytes(gate_kind, H), up_slice = FF * mcu_row_bytes(up_kind, H);
     const size_t down_slice = H * mcu_row_bytes(down_kind, FF);
-    for (size_t e = 0; e < E; ++e) {
-        const size_t cnt = (size_t)counts[e], off = (size_t)offsets[e];
+    for (size_t e = e_begin; e < e_begin + e_count; ++e) {
+        const size_t cnt = (size_t)counts[e], off = (size_t)offsets[e], le = e - e_begin;
         if (cnt == 0) continue;
         const float *hx = route_hidden + off * H;
-        const uint8_t *ge = (const uint8_t *)gate_dev + e * gate_slice, *ue = (const uint8_t *)up_dev + e * up_slice;
+        const uint8_t *ge = (const uint8_t *)gate_dev + le * gate_slice, *ue = (const uint8_t *)up_dev + le * up_slice;
         int rc;
         if (gate_kind == up_kind) {
             rc = linear_locked(ctx, gate_kind, hx, H, ge, ue, cnt, H, FF, nullptr, gate_out + off * FF, up_out + off * FF, FF);
@@ -454,13 +464,32 @@ int mcu_moe_experts(mcu_context_t *ctx, int gate_kind, int up_kind, int down_kin
         if (rc != 0) return rc;
         MCU_CUDA(launch_moe_glu(gate_out + off * FF, up_out + off * FF, cnt * FF, ffn_type == MCU_FFN_GEGLU, s));
         count_launches(1);
-        rc = linear_locked(ctx, down_kind, gate_out + off * FF, FF, (const uint8_t *)down_dev + e * down_slice, nullptr,
+        rc = linear_locked(ctx, down_kind, gate_out + off * FF, FF, (const uint8_t *)down_dev + le * down_slice, nullptr,
                            cnt, FF, H, nullptr, route_down + off * H, nullptr, H);
         if (rc != 0) return rc;
     }
-    MCU_CUDA(launch_moe_combine(route_down, rb.sorted_w, rb.route_pos, (int)T, (int)k, (int)H, out_dev, H, s));
+    MCU_CUDA(launch_moe_combine(route_down, rb.sorted_w, rb.route_pos, (int)T, (int)k, (int)H, pos_lo, pos_hi, out_dev, H,
+                                s));
     count_launches(1);
     return MCU_SUCCESS;
+}
+
+int mcu_moe_experts(mcu_context_t *ctx, int gate_kind, int up_kind, int down_kind, const float *hidden_dev, size_t T,
+                    size_t H, size_t FF, size_t E, const void *gate_dev, const void *up_dev, const void *down_dev,
+                    const int32_t *topk_ids_dev, const float *topk_weights_dev, size_t k, int ffn_type,
+                    float weights_scale, int router_weight_policy, float *out_dev) {
+    return moe_experts_impl(ctx, gate_kind, up_kind, down_kind, hidden_dev, T, H, FF, E, 0, E, gate_dev, up_dev, down_dev,
+                            topk_ids_dev, topk_weights_dev, k, ffn_type, weights_scale, router_weight_policy, out_dev);
+}
+
+int mcu_moe_experts_local(mcu_context_t *ctx, int gate_kind, int up_kind, int down_kind, const float *hidden_dev,
+                          size_t T, size_t H, size_t FF, size_t E, size_t expert_begin, size_t expert_count,
+                          const void *gate_dev, const void *up_dev, const void *down_dev,
+                          const int32_t *topk_ids_dev, const float *topk_weights_dev, size_t k, int ffn_type,
+                          float weights_scale, int router_weight_policy, float *out_dev) {
+    return moe_experts_impl(ctx, gate_kind, up_kind, down_kind, hidden_dev, T, H, FF, E, expert_begin, expert_count,
+                            gate_dev, up_dev, down_dev, topk_ids_dev, topk_weights_dev, k, ffn_type, weights_scale,
+                            router_weight_policy, out_dev);
 }
 
 }  // extern "C"

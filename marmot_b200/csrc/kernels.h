@@ -62,3 +62,10 @@ int set_error(int code, const char *message);
 void count_launches(int n);
 
 }  // namespace mcu
+
+// Accessors of the opaque context for the other translation units.
+struct mcu_context;
+namespace mcu {
+int context_device(const mcu_context *ctx);
+int *context_err_flag(mcu_context *ctx);
+}  // namespace mcu

@@ -100,8 +100,8 @@ __global__ void moe_scatter_kernel(const int32_t *__restrict__ ids, const float 
 
 // route_hidden[r][:] = hidden[sorted_tok[r]][:]
 __global__ void moe_gather_kernel(const float *__restrict__ hidden, size_t ldh, const int32_t *__restrict__ sorted_tok,
-                                  int H, float *__restrict__ route_hidden) {
-    const int r = blockIdx.x;
+                                  int r0, int H, float *__restrict__ route_hidden) {
+    const int r = r0 + blockIdx.x;
     const float *src = hidden + (size_t)sorted_tok[r] * ldh;
     float *dst = route_hidden + (size_t)r * H;
     for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = src[c];
@@ -123,8 +123,8 @@ __global__ void moe_glu_kernel(float *__restrict__ gate, const float *__restrict
 // order, moe_ops.c:1034-1042), of w * down[pos][c]; products and sums rounded separately.
 template <int MAXK>
 __global__ void moe_combine_kernel(const float *__restrict__ route_down, const float *__restrict__ sorted_w,
-                                   const int32_t *__restrict__ route_pos, int k, int H, float *__restrict__ out,
-                                   size_t ldo) {
+                                   const int32_t *__restrict__ route_pos, int k, int H, int pos_lo, int pos_hi,
+                                   float *__restrict__ out, size_t ldo) {
     const int t = blockIdx.x;
     int pos[MAXK];
     float w[MAXK];
@@ -141,7 +141,10 @@ __global__ void moe_combine_kernel(const float *__restrict__ route_down, const f
     for (int j = 0; j < k; ++j) w[j] = sorted_w[pos[j]];
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float acc = 0.0f;
-        for (int j = 0; j < k; ++j) acc = __fadd_rn(acc, __fmul_rn(w[j], route_down[(size_t)pos[j] * H + c]));
+        for (int j = 0; j < k; ++j) {
+            if (pos[j] < pos_lo || pos[j] >= pos_hi) continue;  // another rank's expert
+            acc = __fadd_rn(acc, __fmul_rn(w[j], route_down[(size_t)pos[j] * H + c]));
+        }
         out[(size_t)t * ldo + c] = acc;
     }
 }
@@ -165,10 +168,10 @@ cudaError_t launch_moe_route(const int32_t *ids, const float *weights, int T, in
     return cudaGetLastError();
 }
 
-cudaError_t launch_moe_gather(const float *hidden, size_t ldh, const int32_t *sorted_tok, int routes, int H,
+cudaError_t launch_moe_gather(const float *hidden, size_t ldh, const int32_t *sorted_tok, int pos_lo, int pos_hi, int H,
                               float *route_hidden, cudaStream_t s) {
-    if (routes <= 0) return cudaSuccess;
-    moe_gather_kernel<<<routes, 256, 0, s>>>(hidden, ldh, sorted_tok, H, route_hidden);
+    if (pos_hi <= pos_lo) return cudaSuccess;
+    moe_gather_kernel<<<pos_hi - pos_lo, 256, 0, s>>>(hidden, ldh, sorted_tok, pos_lo, H, route_hidden);
     return cudaGetLastError();
 }
 
@@ -179,10 +182,10 @@ cudaError_t launch_moe_glu(float *gate, const float *up, size_t n, int geglu, cu
 }
 
 cudaError_t launch_moe_combine(const float *route_down, const float *sorted_w, const int32_t *route_pos, int T, int k,
-                               int H, float *out, size_t ldo, cudaStream_t s) {
+                               int H, int pos_lo, int pos_hi, float *out, size_t ldo, cudaStream_t s) {
     if (T <= 0) return cudaSuccess;
     if (k > MOE_MAX_TOPK) return cudaErrorInvalidValue;
-    moe_combine_kernel<MOE_MAX_TOPK><<<T, 256, 0, s>>>(route_down, sorted_w, route_pos, k, H, out, ldo);
+    moe_combine_kernel<MOE_MAX_TOPK><<<T, 256, 0, s>>>(route_down, sorted_w, route_pos, k, H, pos_lo, pos_hi, out, ldo);
     return cudaGetLastError();
 }
 

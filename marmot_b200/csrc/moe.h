@@ -21,10 +21,12 @@ cudaError_t launch_topk(const float *x, int rows, int cols, size_t ldx, int k, f
                         cudaStream_t s);
 cudaError_t launch_moe_route(const int32_t *ids, const float *weights, int T, int k, int E, float weights_scale,
                              int renormalize, const MoeRouteBuffers &b, cudaStream_t s);
-cudaError_t launch_moe_gather(const float *hidden, size_t ldh, const int32_t *sorted_tok, int routes, int H,
+// rows [pos_lo, pos_hi) of the sorted route list only
+cudaError_t launch_moe_gather(const float *hidden, size_t ldh, const int32_t *sorted_tok, int pos_lo, int pos_hi, int H,
                               float *route_hidden, cudaStream_t s);
 cudaError_t launch_moe_glu(float *gate, const float *up, size_t n, int geglu, cudaStream_t s);
+// routes whose sorted position lies outside [pos_lo, pos_hi) are skipped
 cudaError_t launch_moe_combine(const float *route_down, const float *sorted_w, const int32_t *route_pos, int T, int k,
-                               int H, float *out, size_t ldo, cudaStream_t s);
+                               int H, int pos_lo, int pos_hi, float *out, size_t ldo, cudaStream_t s);
 
 }  // namespace mcu

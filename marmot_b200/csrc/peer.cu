@@ -1,0 +1,245 @@
+// Peer communicator for tensor-parallel row-parallel outputs: one staging buffer per rank, mapped into every
+// other rank of the box (CUDA IPC over NVLink), and a one-shot all-reduce kernel that sums the ranks' partial
+// results with plain peer loads in a fixed rank order, so every rank gets bit-identical sums.
+//
+// Protocol (per rank, everything on the context's stream):
+//   1. the producer (a matmul) writes its partial result into this rank's staging slot of parity p = epoch & 1;
+//   2. allreduce kernel: one thread per peer stores `epoch` into flag[p][rank] of that peer (release, system
+//      scope); every CTA then waits (acquire, bounded) until all world flags of its own rank have reached
+//      `epoch`, and sums the world staging slots element-wise, rank 0 first.
+// Two parities are enough: a rank can only pass the wait of call n+1 after every peer has started call n+1,
+// i.e. finished reading call n, and it overwrites parity n & 1 again in call n+2 at the earliest.
+// A wait that runs out (a peer that never arrives) sets the context's error flag and skips the sum; the
+// kernel always terminates.
+#include "../../include/marmot_cuda.h"
+
+#include "common.cuh"
+#include "kernels.h"
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+namespace mcu {
+
+constexpr int PEER_MAX_WORLD = 8;
+constexpr size_t PEER_FLAG_BYTES = 2 * PEER_MAX_WORLD * 128;  // [parity][rank], one 128-byte line per flag
+constexpr unsigned long long PEER_WAIT_NS = 2000000000ull;    // 2 s
+
+struct PeerParams {
+    const uint8_t *base[PEER_MAX_WORLD];  // every rank's buffer as mapped in this process
+    uint8_t *flag_base[PEER_MAX_WORLD];
+    int rank, world;
+    uint32_t epoch;
+    size_t slot_offset;  // byte offset of the parity's staging slot inside a buffer
+    size_t n;            // floats
+    float *out;
+    int *err;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const PeerParams p) {
+    __shared__ int ok_s;
+    const int parity = p.epoch & 1u;
+    if (threadIdx.x == 0) ok_s = 1;
+    if (blockIdx.x == 0 && threadIdx.x < p.world) {
+        // this rank's partial result was written by earlier work on this stream
+        __threadfence_system();
+        uint32_t *f = (uint32_t *)(p.flag_base[threadIdx.x] + ((size_t)parity * PEER_MAX_WORLD + p.rank) * 128);
+        st_release_sys(f, p.epoch);
+    }
+    __syncthreads();
+    if (threadIdx.x < p.world) {
+        const uint32_t *f =
+            (const uint32_t *)(p.flag_base[p.rank] + ((size_t)parity * PEER_MAX_WORLD + threadIdx.x) * 128);
+        const unsigned long long t0 = global_ns();
+        // epochs only grow; the signed difference tolerates wrap-around
+        while ((int32_t)(ld_acquire_sys(f) - p.epoch) < 0) {
+            if (global_ns() - t0 > PEER_WAIT_NS) {
+                atomicExch(p.err, 21);
+                ok_s = 0;
+                break;
+            }
+            __nanosleep(200);
+        }
+    }
+    __syncthreads();
+    if (!ok_s) return;
+    const size_t n4 = p.n / 4;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 acc = __ldcg((const float4 *)(p.base[0] + p.slot_offset) + i);
+        for (int r = 1; r < p.world; ++r) {
+            const float4 v = __ldcg((const float4 *)(p.base[r] + p.slot_offset) + i);
+            acc.x = __fadd_rn(acc.x, v.x);
+            acc.y = __fadd_rn(acc.y, v.y);
+            acc.z = __fadd_rn(acc.z, v.z);
+            acc.w = __fadd_rn(acc.w, v.w);
+        }
+        ((float4 *)p.out)[i] = acc;
+    }
+    for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n; i += stride) {
+        float acc = __ldcg((const float *)(p.base[0] + p.slot_offset) + i);
+        for (int r = 1; r < p.world; ++r) acc = __fadd_rn(acc, __ldcg((const float *)(p.base[r] + p.slot_offset) + i));
+        p.out[i] = acc;
+    }
+}
+
+}  // namespace mcu
+
+using namespace mcu;
+
+struct mcu_peer_comm {
+    mcu_context_t *ctx = nullptr;
+    int rank = 0, world = 1;
+    size_t capacity = 0;  // bytes of one staging slot
+    uint8_t *local = nullptr;
+    uint8_t *mapped[PEER_MAX_WORLD] = {};
+    bool connected = false;
+    uint32_t epoch = 0;
+};
+
+#define PEER_CUDA(expr)                                                                   \
+    do {                                                                                  \
+        cudaError_t e__ = (expr);                                                         \
+        if (e__ != cudaSuccess) {                                                         \
+            char msg__[256];                                                              \
+            snprintf(msg__, sizeof(msg__), "%s: %s", #expr, cudaGetErrorString(e__));     \
+            return set_error(MCU_ERROR_INVALID_OPERATION, msg__);                         \
+        }                                                                                 \
+    } while (0)
+
+extern "C" {
+
+int mcu_peer_comm_create(mcu_context_t *ctx, int rank, int world, size_t max_bytes, mcu_peer_comm_t **out) {
+    if (out == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    if (ctx == nullptr) return set_error(MCU_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+    if (world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world)
+        return set_error(MCU_ERROR_INVALID_ARGUMENT, "peer communicator: bad rank / world (at most 8 ranks)");
+    if (max_bytes == 0) return set_error(MCU_ERROR_INVALID_ARGUMENT, "peer communicator: empty staging buffer");
+    PEER_CUDA(cudaSetDevice(context_device(ctx)));
+    mcu_peer_comm *c = new (std::nothrow) mcu_peer_comm;
+    if (c == nullptr) return set_error(MCU_ERROR_OUT_OF_MEMORY, "peer communicator allocation failed");
+    c->ctx = ctx;
+    c->rank = rank;
+    c->world = world;
+    c->capacity = (max_bytes + 255) & ~(size_t)255;
+    const size_t total = PEER_FLAG_BYTES + 2 * c->capacity;
+    cudaError_t e = cudaMalloc((void **)&c->local, total);
+    if (e != cudaSuccess) {
+        delete c;
+        return set_error(MCU_ERROR_OUT_OF_MEMORY, "peer communicator: cudaMalloc failed");
+    }
+    e = cudaMemset(c->local, 0, total);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(c->local);
+        delete c;
+        return set_error(MCU_ERROR_INVALID_OPERATION, cudaGetErrorString(e));
+    }
+    c->mapped[rank] = c->local;
+    c->connected = world == 1;
+    *out = c;
+    return MCU_SUCCESS;
+}
+
+int mcu_peer_comm_export(mcu_peer_comm_t *c, void *handle_out) {
+    if (c == nullptr || handle_out == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == MCU_PEER_HANDLE_BYTES, "handle size");
+    cudaIpcMemHandle_t h;
+    PEER_CUDA(cudaSetDevice(context_device(c->ctx)));
+    PEER_CUDA(cudaIpcGetMemHandle(&h, c->local));
+    memcpy(handle_out, &h, sizeof(h));
+    return MCU_SUCCESS;
+}
+
+int mcu_peer_comm_connect(mcu_peer_comm_t *c, const void *all_handles) {
+    if (c == nullptr || all_handles == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "null argument");
+    if (c->connected) return MCU_SUCCESS;
+    PEER_CUDA(cudaSetDevice(context_device(c->ctx)));
+    for (int r = 0; r < c->world; ++r) {
+        if (r == c->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t *)all_handles + (size_t)r * MCU_PEER_HANDLE_BYTES, sizeof(h));
+        void *p = nullptr;
+        PEER_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        c->mapped[r] = (uint8_t *)p;
+    }
+    c->connected = true;
+    return MCU_SUCCESS;
+}
+
+void *mcu_peer_comm_staging(mcu_peer_comm_t *c) {
+    if (c == nullptr) return nullptr;
+    // slot of the NEXT all-reduce
+    return c->local + PEER_FLAG_BYTES + (size_t)((c->epoch + 1) & 1u) * c->capacity;
+}
+
+int mcu_peer_allreduce(mcu_peer_comm_t *c, size_t n_floats, float *out_dev) {
+    if (c == nullptr || out_dev == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "null argument");
+    if (!c->connected) return set_error(MCU_ERROR_INVALID_OPERATION, "peer communicator is not connected");
+    if (n_floats * sizeof(float) > c->capacity)
+        return set_error(MCU_ERROR_INVALID_ARGUMENT, "all-reduce larger than the communicator's staging buffer");
+    if (n_floats == 0) return MCU_SUCCESS;
+    if ((uintptr_t)out_dev & 15) return set_error(MCU_ERROR_INVALID_ARGUMENT, "all-reduce output must be 16-byte aligned");
+    PEER_CUDA(cudaSetDevice(context_device(c->ctx)));
+    c->epoch += 1;
+    PeerParams p;
+    memset(&p, 0, sizeof(p));
+    for (int r = 0; r < c->world; ++r) {
+        p.base[r] = c->mapped[r];
+        p.flag_base[r] = c->mapped[r];
+    }
+    p.rank = c->rank;
+    p.world = c->world;
+    p.epoch = c->epoch;
+    p.slot_offset = PEER_FLAG_BYTES + (size_t)(c->epoch & 1u) * c->capacity;
+    p.n = n_floats;
+    p.out = out_dev;
+    p.err = context_err_flag(c->ctx);
+    const size_t n4 = (n_floats + 3) / 4;
+    int blocks = (int)((n4 + 511) / 512);
+    const int max_blocks = 2 * device_sm_count();
+    if (blocks > max_blocks) blocks = max_blocks;
+    if (blocks < 1) blocks = 1;
+    allreduce_oneshot_kernel<<<blocks, 512, 0, (cudaStream_t)mcu_context_get_stream(c->ctx)>>>(p);
+    PEER_CUDA(cudaGetLastError());
+    count_launches(1);
+    return MCU_SUCCESS;
+}
+
+int mcu_linear_allreduce(mcu_context_t *ctx, mcu_peer_comm_t *c, int kind, const float *x_dev, size_t ldx,
+                         const void *w_dev, size_t T, size_t K, size_t F, float *out_dev) {
+    if (c == nullptr || c->ctx != ctx) return set_error(MCU_ERROR_INVALID_ARGUMENT, "communicator of another context");
+    if (T * F * sizeof(float) > c->capacity)
+        return set_error(MCU_ERROR_INVALID_ARGUMENT, "result larger than the communicator's staging buffer");
+    float *staging = (float *)mcu_peer_comm_staging(c);
+    if (int rc = mcu_linear(ctx, kind, x_dev, ldx, w_dev, T, K, F, nullptr, staging, F)) return rc;
+    return mcu_peer_allreduce(c, T * F, out_dev);
+}
+
+void mcu_peer_comm_destroy(mcu_peer_comm_t *c) {
+    if (c == nullptr) return;
+    cudaSetDevice(context_device(c->ctx));
+    cudaStreamSynchronize((cudaStream_t)mcu_context_get_stream(c->ctx));
+    for (int r = 0; r < c->world; ++r)
+        if (r != c->rank && c->mapped[r] != nullptr) cudaIpcCloseMemHandle(c->mapped[r]);
+    if (c->local != nullptr) cudaFree(c->local);
+    delete c;
+}
+
+}  // extern "C"

@@ -24,7 +24,9 @@ EXPORTS = (
     "mcu_context_set_regime", "mcu_synchronize", "mcu_last_error_message", "mcu_kernel_launch_count",
     "mcu_malloc", "mcu_free", "mcu_memcpy_to_device", "mcu_memcpy_to_host", "mcu_row_bytes", "mcu_dequantize",
     "mcu_quantize_activations", "mcu_linear", "mcu_linear_dual", "mcu_linear_host", "mcu_topk", "mcu_moe_experts",
-    "mcu_linear_static_scratch",
+    "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_peer_comm_create", "mcu_peer_comm_export",
+    "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
+    "mcu_linear_allreduce",
 )
 
 
@@ -79,6 +81,17 @@ def load_library() -> C.CDLL:
     L.mcu_linear_static_scratch.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_topk.argtypes = [vp, vp, sz, sz, sz, sz, vp, vp]
     L.mcu_moe_experts.argtypes = [vp, i32, i32, i32, vp, sz, sz, sz, sz, vp, vp, vp, vp, vp, sz, i32, f32, i32, vp]
+    L.mcu_moe_experts_local.argtypes = [vp, i32, i32, i32, vp, sz, sz, sz, sz, sz, sz, vp, vp, vp, vp, vp, sz, i32, f32,
+                                        i32, vp]
+    L.mcu_peer_comm_create.argtypes = [vp, i32, i32, sz, C.POINTER(vp)]
+    L.mcu_peer_comm_export.argtypes = [vp, vp]
+    L.mcu_peer_comm_connect.argtypes = [vp, vp]
+    L.mcu_peer_comm_staging.argtypes = [vp]
+    L.mcu_peer_comm_staging.restype = vp
+    L.mcu_peer_allreduce.argtypes = [vp, sz, vp]
+    L.mcu_peer_comm_destroy.argtypes = [vp]
+    L.mcu_peer_comm_destroy.restype = None
+    L.mcu_linear_allreduce.argtypes = [vp, vp, i32, vp, sz, vp, sz, sz, sz, vp]
     _lib = L
     return L
 
@@ -204,3 +217,70 @@ class Context:
                                              _ptr(gate), _ptr(up), _ptr(down), _ptr(topk_ids), _ptr(topk_weights), k,
                                              ffn_type, weights_scale, policy, _ptr(out)))
         return out
+
+    def moe_experts_local(self, kinds, hidden, gate, up, down, topk_ids, topk_weights, FF: int, E: int,
+                          expert_begin: int, expert_count: int, ffn_type: int = FFN_SWIGLU,
+                          weights_scale: float = 1.0, policy: int = ROUTER_RENORMALIZE_SELECTED, out=None):
+        """This rank's share of the MoE output: gate/up/down hold experts [expert_begin, +expert_count) only."""
+        T, H = hidden.shape
+        k = topk_ids.shape[1]
+        if out is None:
+            out = self.torch.empty((T, H), dtype=self.torch.float32, device=hidden.device)
+        self._check(self.lib.mcu_moe_experts_local(
+            self.handle, kinds[0], kinds[1], kinds[2], _ptr(hidden), T, H, FF, E, expert_begin, expert_count,
+            _ptr(gate), _ptr(up), _ptr(down), _ptr(topk_ids), _ptr(topk_weights), k, ffn_type, weights_scale, policy,
+            _ptr(out)))
+        return out
+
+
+class PeerComm:
+    """mcu_peer_comm: staging buffers mapped across the ranks of one box and the one-shot all-reduce kernel.
+    `exchange(handle_bytes) -> list of every rank's handle bytes in rank order` is the host transport
+    (torch.distributed.all_gather_object in tensor_parallel.py)."""
+
+    def __init__(self, ctx: "Context", rank: int, world: int, max_bytes: int, exchange):
+        self.ctx, self.rank, self.world, self.max_bytes = ctx, rank, world, max_bytes
+        h = C.c_void_p()
+        ctx._check(ctx.lib.mcu_peer_comm_create(ctx.handle, rank, world, max_bytes, C.byref(h)))
+        self.handle = h
+        mine = C.create_string_buffer(64)
+        ctx._check(ctx.lib.mcu_peer_comm_export(h, mine))
+        handles = exchange(bytes(mine.raw))
+        assert len(handles) == world and all(len(x) == 64 for x in handles)
+        ctx._check(ctx.lib.mcu_peer_comm_connect(h, C.create_string_buffer(b"".join(handles), 64 * world)))
+
+    def staging(self, shape):
+        """The buffer the next all-reduce sums, as a float32 torch tensor of `shape` (a view, no copy)."""
+        n = int(np.prod(shape))
+        assert n * 4 <= self.max_bytes
+        ptr = self.ctx.lib.mcu_peer_comm_staging(self.handle)
+        return _tensor_from_ptr(self.ctx.torch, ptr, shape, self.ctx.device)
+
+    def allreduce(self, n_floats: int, out):
+        self.ctx._check(self.ctx.lib.mcu_peer_allreduce(self.handle, n_floats, _ptr(out)))
+        return out
+
+    def linear_allreduce(self, kind: int, x, w, F: int, out=None):
+        T, K = x.shape
+        if out is None:
+            out = self.ctx.torch.empty((T, F), dtype=self.ctx.torch.float32, device=x.device)
+        self.ctx._check(self.ctx.lib.mcu_linear_allreduce(self.ctx.handle, self.handle, kind, _ptr(x), x.stride(0),
+                                                          _ptr(w), T, K, F, _ptr(out)))
+        return out
+
+    def close(self):
+        if self.handle:
+            self.ctx.lib.mcu_peer_comm_destroy(self.handle)
+            self.handle = None
+
+
+def _tensor_from_ptr(torch, ptr: int, shape, device_index: int):
+    """float32 torch view of device memory owned by the library (CUDA array interface)."""
+
+    class _Ext:
+        pass
+
+    e = _Ext()
+    e.__cuda_array_interface__ = {"shape": tuple(int(v) for v in shape), "typestr": "<f4", "data": (int(ptr), False),
+                                  "version": 2}
+    return torch.as_tensor(e, device=torch.device("cuda", device_index))

@@ -1,0 +1,115 @@
+"""One rank of the multi-GPU tensor-parallel check (launched by torch.distributed.run from
+test_tensor_parallel_gpu.py or by hand).  Every rank builds the same weights, shards them, runs the
+column-/row-/expert-parallel layers on its GPU and compares with the unsharded operator on the same GPU.
+Prints one JSON line per rank; exit code 0 means every check passed."""
+from __future__ import annotations
+
+import json
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+from marmot_b200 import Context  # noqa: E402
+from marmot_b200 import tensor_parallel as tp  # noqa: E402
+from marmot_b200.runtime import KIND_Q4_K, KIND_Q6_K, KIND_Q8_0, MarmotCudaError  # noqa: E402
+from tests.util import TOL_FP32, TOL_MMA, TOL_MOE, max_rel_err, random_blocks  # noqa: E402
+
+
+def main() -> int:
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    ctx = Context(local)
+    group = tp.Group(rank, world, dist)
+    comm = tp.make_peer_comm(ctx, group, 8 << 20)
+    res, ok = {}, True
+
+    def check(name, cond, value=None):
+        nonlocal ok
+        res[name] = value if value is not None else bool(cond)
+        if not cond:
+            ok = False
+
+    # the all-reduce kernel alone: fixed summation order, identical on all ranks
+    n = 100003
+    parts = [np.random.default_rng(100 + r).normal(0, 1, n).astype(np.float32) for r in range(world)]
+    want = parts[0].copy()
+    for r in range(1, world):
+        want = want + parts[r]
+    for rep in range(3):  # both parities and a reuse
+        comm.staging((n,)).copy_(torch.from_numpy(parts[rank]).to(dev))
+        out = torch.empty(n, dtype=torch.float32, device=dev)
+        comm.allreduce(n, out)
+        ctx.synchronize()
+        check(f"allreduce_exact_{rep}", np.array_equal(out.cpu().numpy(), want))
+
+    rng = np.random.default_rng(42)
+    for kind in (KIND_Q4_K, KIND_Q6_K, KIND_Q8_0):
+        for T in (1, 5, 48):
+            K, F = 2048, 384
+            W = random_blocks(kind, F, K, rng)
+            x = torch.from_numpy(rng.normal(0, 1, (T, K)).astype(np.float32)).to(dev)
+            want = ctx.linear(kind, x, ctx.upload(W), F).cpu().numpy()
+            tol = TOL_FP32 if T <= 8 else TOL_MMA
+            col = tp.ColumnParallelLinear(ctx, group, kind, W, F, K, granule=16)
+            y = col(x, gather=True).cpu().numpy()
+            check(f"col_{kind}_{T}", max_rel_err(y, want) <= tol, float(max_rel_err(y, want)))
+            for name, c in (("nccl", None), ("peer", comm)):
+                row = tp.RowParallelLinear(ctx, group, kind, W, F, K, comm=c)
+                y = row(x)
+                ctx.synchronize()
+                e = float(max_rel_err(y.cpu().numpy(), want))
+                check(f"row_{name}_{kind}_{T}", e <= tol, e)
+                gathered = [torch.empty_like(y) for _ in range(world)]
+                dist.all_gather(gathered, y)
+                if name == "peer":  # every rank holds the same bits
+                    check(f"row_peer_same_{kind}_{T}", all(torch.equal(g, gathered[0]) for g in gathered))
+
+    T, H, FF, E, k = 40, 512, 1024, 8, 2
+    gate = np.concatenate([random_blocks(KIND_Q4_K, FF, H, rng, d_sigma=0.0005) for _ in range(E)])
+    up = np.concatenate([random_blocks(KIND_Q4_K, FF, H, rng, d_sigma=0.0005) for _ in range(E)])
+    down = np.concatenate([random_blocks(KIND_Q6_K, H, FF, rng) for _ in range(E)])
+    hidden = torch.from_numpy(rng.normal(0, 1, (T, H)).astype(np.float32)).to(dev)
+    ids = torch.from_numpy(np.stack([rng.permutation(E)[:k] for _ in range(T)]).astype(np.int32)).to(dev)
+    wts = torch.from_numpy(rng.uniform(0.1, 1.0, (T, k)).astype(np.float32)).to(dev)
+    kinds = (KIND_Q4_K, KIND_Q4_K, KIND_Q6_K)
+    want = ctx.moe_experts(kinds, hidden, ctx.upload(gate), ctx.upload(up), ctx.upload(down), ids, wts, FF, E).cpu().numpy()
+    for name, c in (("nccl", None), ("peer", comm)):
+        moe = tp.ExpertParallelMoE(ctx, group, kinds, gate, up, down, H, FF, E, comm=c)
+        y = moe(hidden, ids, wts)
+        ctx.synchronize()
+        e = float(max_rel_err(y.cpu().numpy(), want))
+        check(f"moe_{name}", e <= TOL_MOE, e)
+
+    # a peer that never arrives: the bounded wait gives up and the error reaches the host; nothing hangs
+    dist.barrier()
+    torch.cuda.synchronize()
+    if rank == 0 and world > 1:
+        out = torch.empty(16, dtype=torch.float32, device=dev)
+        comm.staging((16,)).zero_()
+        comm.allreduce(16, out)
+        try:
+            ctx.synchronize()
+            check("timeout_reported", False)
+        except MarmotCudaError as exc:
+            check("timeout_reported", "timed out" in str(exc))
+    dist.barrier()
+    torch.cuda.synchronize()
+    print(json.dumps({"rank": rank, "ok": ok, **res}), flush=True)
+    # the communicator's epochs now differ between ranks: it is not used again
+    comm.close()
+    ctx.close()
+    dist.destroy_process_group()
+    return 0 if ok else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
