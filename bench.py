@@ -191,6 +191,119 @@ def time_other_regimes(ctx, dev):
     return out
 
 
+LLAMA8B = {"layers": 32, "d": 4096, "ffn": 14336, "kv": 1024, "vocab": 128256}
+
+
+def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
+    """The weight-streaming part of a Llama-3-8B-shape Q4_K_M decode step for T concurrent sequences, tensor
+    parallel over `world` GPUs: per layer q/k/v (column-parallel), attention output (row-parallel + all-reduce),
+    gate/up (column-parallel, one dual launch), down (row-parallel + all-reduce), and the vocabulary projection once
+    per step.  Attention, norms and RoPE are not part of it.  Every rank draws its own shard-shaped random weights
+    (distinct per layer, so nothing is re-read from L2); the step is captured in a CUDA graph and replayed."""
+    import torch
+
+    from marmot_b200 import tensor_parallel as tp
+    from marmot_b200.profile_case import synthetic_blocks_device
+    from marmot_b200.runtime import KIND_Q6_K, row_bytes
+
+    m = LLAMA8B
+    d, ffn, kv, vocab, L = m["d"], m["ffn"], m["kv"], m["vocab"], m["layers"]
+    if d % (256 * world) or ffn % (256 * world) or kv % world:
+        return {"skipped": f"shapes do not divide over {world} ranks"}
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    Q4, Q6 = KIND_Q4_K, KIND_Q6_K
+    group = tp.Group(rank, world, dist if world > 1 else None)
+    comm = tp.make_peer_comm(ctx, group, T * d * 4) if world > 1 else None
+    mk = lambda kind, F, K: synthetic_blocks_device(torch, kind, F, K, dev, gen)
+    layers, wbytes = [], 0
+    for _ in range(L):
+        w = {"q": (Q4, mk(Q4, d // world, d), d // world, d), "k": (Q4, mk(Q4, kv // world, d), kv // world, d),
+             "v": (Q6, mk(Q6, kv // world, d), kv // world, d), "o": (Q4, mk(Q4, d, d // world), d, d // world),
+             "gate": (Q4, mk(Q4, ffn // world, d), ffn // world, d), "up": (Q4, mk(Q4, ffn // world, d), ffn // world, d),
+             "down": (Q6, mk(Q6, d, ffn // world), d, ffn // world)}
+        wbytes += sum(F * row_bytes(kind, K) for kind, _, F, K in w.values())
+        layers.append(w)
+    v_lo, v_hi = tp.shard_range(vocab, world, rank, 32)
+    head = (Q6, mk(Q6, v_hi - v_lo, d), v_hi - v_lo, d)
+    wbytes += head[2] * row_bytes(Q6, d)
+    x = torch.randn((T, d), device=dev, generator=gen)
+    x_attn = torch.randn((T, d // world), device=dev, generator=gen)
+    x_ffn = torch.randn((T, ffn // world), device=dev, generator=gen)
+    bufs = {n: torch.empty((T, F), dtype=torch.float32, device=dev)
+            for n, F in (("q", d // world), ("k", kv // world), ("v", kv // world), ("o", d), ("gate", ffn // world),
+                         ("up", ffn // world), ("down", d), ("head", v_hi - v_lo))}
+
+    def row_parallel(entry, xin, out, how):
+        kind, wt, F, K = entry
+        if world == 1:
+            ctx.linear(kind, xin, wt, F, out=out)
+        elif how == "peer":
+            comm.linear_allreduce(kind, xin, wt, F, out=out)
+        else:
+            ctx.linear(kind, xin, wt, F, out=out)
+            dist.all_reduce(out)
+
+    def step(how):
+        for w in layers:
+            for n in ("q", "k", "v"):
+                kind, wt, F, K = w[n]
+                ctx.linear(kind, x, wt, F, out=bufs[n])
+            row_parallel(w["o"], x_attn, bufs["o"], how)
+            ctx.linear_dual(Q4, x, w["gate"][1], w["up"][1], w["gate"][2], out_a=bufs["gate"], out_b=bufs["up"])
+            row_parallel(w["down"], x_ffn, bufs["down"], how)
+        kind, wt, F, K = head
+        ctx.linear(kind, x, wt, F, out=bufs["head"])
+
+    result = {"T": T, "layers": L, "weight_bytes_per_gpu": wbytes, "tensor_parallel": world}
+    stream = torch.cuda.Stream(dev)
+    ctx.set_stream(stream.cuda_stream)
+    for how in (["single"] if world == 1 else ["peer", "nccl"]):
+        try:
+            with torch.cuda.stream(stream):
+                for _ in range(2):
+                    step(how)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            l0 = ctx.launch_count()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                step(how)
+            launches = ctx.launch_count() - l0
+            reps = 5
+            with torch.cuda.stream(stream):
+                for _ in range(2):
+                    g.replay()
+                torch.cuda.synchronize()
+                if world > 1:
+                    dist.barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(reps):
+                    g.replay()
+                e1.record(stream)
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            if world > 1:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            ctx.synchronize()
+            result[how] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(T / ms * 1e3, 1),
+                           "weight_GBps_per_gpu": round(wbytes / ms / 1e6, 1), "kernel_launches_per_step": int(launches)}
+            del g
+        except Exception as exc:  # e.g. a collective that cannot be captured
+            result[how] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+    ctx.set_stream(0)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    if comm is not None:
+        comm.close()
+    return result
+
+
 def run_reference_arm(args, rank: int):
     if rank != 0:
         return
@@ -334,6 +447,10 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
 
+    tp_section = None
+    if not args.no_extra:
+        tp_section = time_tp_decode_matmuls(ctx, dev, rank, world, dist)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -366,6 +483,8 @@ def main():
                      "us_per_launch": per_launch_s * 1e6},
         "clocks": clocks,
     }
+    if tp_section is not None:
+        line["llama8b_decode_matmuls"] = tp_section
     if not args.no_extra and world == 1:
         line["other_regimes"] = time_other_regimes(ctx, dev)
     if not args.no_cpu_baseline:

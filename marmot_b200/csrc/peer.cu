@@ -9,6 +9,9 @@
 //      `epoch`, and sums the world staging slots element-wise, rank 0 first.
 // Two parities are enough: a rank can only pass the wait of call n+1 after every peer has started call n+1,
 // i.e. finished reading call n, and it overwrites parity n & 1 again in call n+2 at the earliest.
+// The epoch lives in device memory (read by every CTA at its start, advanced by the last CTA to finish), so a
+// captured CUDA graph can be replayed; the staging pointer a producer writes to is fixed at capture, which is
+// why a graph must hold an even number of all-reduces per communicator.
 // A wait that runs out (a peer that never arrives) sets the context's error flag and skips the sum; the
 // kernel always terminates.
 #include "../../include/marmot_cuda.h"
@@ -23,16 +26,17 @@
 namespace mcu {
 
 constexpr int PEER_MAX_WORLD = 8;
-constexpr size_t PEER_FLAG_BYTES = 2 * PEER_MAX_WORLD * 128;  // [parity][rank], one 128-byte line per flag
+constexpr size_t PEER_CTR_OFFSET = 2 * PEER_MAX_WORLD * 128;  // epoch counter and CTA ticket of the owning rank
+constexpr size_t PEER_FLAG_BYTES = PEER_CTR_OFFSET + 128;     // flags [parity][rank], one 128-byte line each, + counters
 constexpr unsigned long long PEER_WAIT_NS = 2000000000ull;    // 2 s
 
 struct PeerParams {
     const uint8_t *base[PEER_MAX_WORLD];  // every rank's buffer as mapped in this process
     uint8_t *flag_base[PEER_MAX_WORLD];
     int rank, world;
-    uint32_t epoch;
-    size_t slot_offset;  // byte offset of the parity's staging slot inside a buffer
-    size_t n;            // floats
+    uint32_t *ctr;    // this rank's {epoch of the last finished all-reduce, ticket}
+    size_t capacity;  // bytes of one staging slot
+    size_t n;         // floats
     float *out;
     int *err;
 };
@@ -53,13 +57,20 @@ __device__ __forceinline__ unsigned long long global_ns() {
 
 __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const PeerParams p) {
     __shared__ int ok_s;
-    const int parity = p.epoch & 1u;
-    if (threadIdx.x == 0) ok_s = 1;
+    __shared__ uint32_t epoch_s;
+    if (threadIdx.x == 0) {
+        ok_s = 1;
+        epoch_s = *(volatile uint32_t *)p.ctr + 1u;
+    }
+    __syncthreads();
+    const uint32_t epoch = epoch_s;
+    const int parity = epoch & 1u;
+    const size_t slot_offset = PEER_FLAG_BYTES + (size_t)parity * p.capacity;
     if (blockIdx.x == 0 && threadIdx.x < p.world) {
         // this rank's partial result was written by earlier work on this stream
         __threadfence_system();
         uint32_t *f = (uint32_t *)(p.flag_base[threadIdx.x] + ((size_t)parity * PEER_MAX_WORLD + p.rank) * 128);
-        st_release_sys(f, p.epoch);
+        st_release_sys(f, epoch);
     }
     __syncthreads();
     if (threadIdx.x < p.world) {
@@ -67,7 +78,7 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const PeerParams
             (const uint32_t *)(p.flag_base[p.rank] + ((size_t)parity * PEER_MAX_WORLD + threadIdx.x) * 128);
         const unsigned long long t0 = global_ns();
         // epochs only grow; the signed difference tolerates wrap-around
-        while ((int32_t)(ld_acquire_sys(f) - p.epoch) < 0) {
+        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
             if (global_ns() - t0 > PEER_WAIT_NS) {
                 atomicExch(p.err, 21);
                 ok_s = 0;
@@ -77,13 +88,13 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const PeerParams
         }
     }
     __syncthreads();
-    if (!ok_s) return;
-    const size_t n4 = p.n / 4;
+    const size_t n4 = ok_s ? p.n / 4 : 0;
+    const size_t n_all = ok_s ? p.n : 0;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
-        float4 acc = __ldcg((const float4 *)(p.base[0] + p.slot_offset) + i);
+        float4 acc = __ldcg((const float4 *)(p.base[0] + slot_offset) + i);
         for (int r = 1; r < p.world; ++r) {
-            const float4 v = __ldcg((const float4 *)(p.base[r] + p.slot_offset) + i);
+            const float4 v = __ldcg((const float4 *)(p.base[r] + slot_offset) + i);
             acc.x = __fadd_rn(acc.x, v.x);
             acc.y = __fadd_rn(acc.y, v.y);
             acc.z = __fadd_rn(acc.z, v.z);
@@ -91,10 +102,20 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const PeerParams
         }
         ((float4 *)p.out)[i] = acc;
     }
-    for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n; i += stride) {
-        float acc = __ldcg((const float *)(p.base[0] + p.slot_offset) + i);
-        for (int r = 1; r < p.world; ++r) acc = __fadd_rn(acc, __ldcg((const float *)(p.base[r] + p.slot_offset) + i));
+    for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_all; i += stride) {
+        float acc = __ldcg((const float *)(p.base[0] + slot_offset) + i);
+        for (int r = 1; r < p.world; ++r) acc = __fadd_rn(acc, __ldcg((const float *)(p.base[r] + slot_offset) + i));
         p.out[i] = acc;
+    }
+    // the last CTA to get here publishes the epoch for the next launch (every CTA has read it by now)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(p.ctr + 1, 1u) == gridDim.x - 1) {
+            p.ctr[1] = 0;
+            __threadfence();
+            *(volatile uint32_t *)p.ctr = epoch;
+        }
     }
 }
 
@@ -197,7 +218,7 @@ int mcu_peer_allreduce(mcu_peer_comm_t *c, size_t n_floats, float *out_dev) {
     if (n_floats == 0) return MCU_SUCCESS;
     if ((uintptr_t)out_dev & 15) return set_error(MCU_ERROR_INVALID_ARGUMENT, "all-reduce output must be 16-byte aligned");
     PEER_CUDA(cudaSetDevice(context_device(c->ctx)));
-    c->epoch += 1;
+    c->epoch += 1;  // host mirror: only its parity is used (mcu_peer_comm_staging)
     PeerParams p;
     memset(&p, 0, sizeof(p));
     for (int r = 0; r < c->world; ++r) {
@@ -206,8 +227,8 @@ int mcu_peer_allreduce(mcu_peer_comm_t *c, size_t n_floats, float *out_dev) {
     }
     p.rank = c->rank;
     p.world = c->world;
-    p.epoch = c->epoch;
-    p.slot_offset = PEER_FLAG_BYTES + (size_t)(c->epoch & 1u) * c->capacity;
+    p.ctr = (uint32_t *)(c->local + PEER_CTR_OFFSET);
+    p.capacity = c->capacity;
     p.n = n_floats;
     p.out = out_dev;
     p.err = context_err_flag(c->ctx);

@@ -33,6 +33,16 @@ def synthetic_blocks(kind: int, rows: int, K: int, rng: np.random.Generator) -> 
     return blocks.reshape(-1)
 
 
+def synthetic_blocks_device(torch, kind: int, rows: int, K: int, device, generator=None):
+    """The same on the GPU (a uint8 tensor), for weights too large to draw on the host in reasonable time."""
+    nb = (K + BLOCK_VALUES[kind] - 1) // BLOCK_VALUES[kind]
+    blocks = torch.randint(0, 256, (rows * nb, BLOCK_BYTES[kind]), dtype=torch.uint8, device=device, generator=generator)
+    scale_hi = torch.randint(0x1C, 0x20, (rows * nb,), dtype=torch.uint8, device=device, generator=generator)
+    for col in ((1, 3) if kind == KIND_Q4_K else (209,) if kind == KIND_Q6_K else (1,)):
+        blocks[:, col] = scale_hi
+    return blocks.reshape(-1)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--kind", default="q4_k", choices=sorted(KIND_BY_NAME))

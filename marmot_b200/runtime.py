@@ -180,11 +180,11 @@ class Context:
                                         out.stride(0)))
         return out
 
-    def linear_dual(self, kind: int, x, w_a, w_b, F: int):
+    def linear_dual(self, kind: int, x, w_a, w_b, F: int, out_a=None, out_b=None):
         T, K = x.shape
         tc = self.torch
-        oa = tc.empty((T, F), dtype=tc.float32, device=x.device)
-        ob = tc.empty((T, F), dtype=tc.float32, device=x.device)
+        oa = out_a if out_a is not None else tc.empty((T, F), dtype=tc.float32, device=x.device)
+        ob = out_b if out_b is not None else tc.empty((T, F), dtype=tc.float32, device=x.device)
         self._check(self.lib.mcu_linear_dual(self.handle, kind, _ptr(x), x.stride(0), _ptr(w_a), _ptr(w_b), T, K, F,
                                              _ptr(oa), _ptr(ob), F))
         return oa, ob
