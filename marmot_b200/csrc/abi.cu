@@ -255,7 +255,7 @@ static int validate_linear(int kind, const void *x, const void *w, const void *o
 
 // Quantize the activations into the context workspace.
 static int pack_activations(mcu_context *ctx, int kind, const float *x, size_t ldx, size_t T, size_t K, bool want_half,
-                            ActBuffers &ab) {
+                            bool k_perm, ActBuffers &ab) {
     const size_t bv = (size_t)block_values(kind);
     const size_t nb = (K + bv - 1) / bv, kp = nb * bv;
     if (int rc = ensure(ctx, ctx->act_qs, T * kp)) return rc;
@@ -272,8 +272,8 @@ static int pack_activations(mcu_context *ctx, int kind, const float *x, size_t l
     MCU_CUDA(launch_quantize_act(kind, x, (int)ldx, (int)T, (int)K, ab, nullptr, ctx->stream));
     count_launches(1);
     if (want_half) {
-        MCU_CUDA(launch_half_acts(kind, ab, (int)T, (int)K, (__half *)ctx->act_half.ptr, (float *)ctx->act_rowscale.ptr,
-                                  ctx->stream));
+        MCU_CUDA(launch_half_acts(kind, ab, (int)T, (int)K, k_perm, (__half *)ctx->act_half.ptr,
+                                  (float *)ctx->act_rowscale.ptr, ctx->stream));
         count_launches(1);
     }
     return MCU_SUCCESS;
@@ -287,11 +287,12 @@ static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx,
     ActBuffers ab;
     if (gemm) {
         if (gemm_tc_supported(kind, (int)T, (int)K, (int)F)) {
-            if (int rc = pack_activations(ctx, kind, x, ldx, T, K, true, ab)) return rc;
+            const bool tma = gemm_tma_supported(kind, w, w2, (int)T, (int)K, (int)F);
+            if (int rc = pack_activations(ctx, kind, x, ldx, T, K, true, tma, ab)) return rc;
             const size_t bv = (size_t)block_values(kind);
             const size_t kp = (K + bv - 1) / bv * bv;
             int launches = 0;
-            if (gemm_tma_supported(kind, w, w2, (int)T, (int)K, (int)F))
+            if (tma)
                 MCU_CUDA(launch_gemm_tma(kind, w, w2, (const __half *)ctx->act_half.ptr,
                                          (const float *)ctx->act_rowscale.ptr, (int)kp, (int)T, (int)K, (int)F,
                                          bias, out, out2, (int)ldo, ctx->dev_err, ctx->stream, &launches));
@@ -312,7 +313,7 @@ static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx,
         count_launches(1);
         return MCU_SUCCESS;
     }
-    if (int rc = pack_activations(ctx, kind, x, ldx, T, K, false, ab)) return rc;
+    if (int rc = pack_activations(ctx, kind, x, ldx, T, K, false, false, ab)) return rc;
     const size_t bv = (size_t)block_values(kind);
     const size_t nb = (K + bv - 1) / bv, kp = nb * bv;
     for (size_t t0 = 0; t0 < T; t0 += GEMV_MAX_T) {

@@ -116,7 +116,7 @@ quantize_q8_0_kernel(const float *__restrict__ x, int ldx, int T, int K, int nb,
 // activations inside the fp16 range (and tiny ones out of the subnormals); the matmul epilogue multiplies
 // the row back by rowscale[t] = 2^e_t.  One CTA per token.
 __global__ void __launch_bounds__(256)
-half_acts_kernel(int kq, const int8_t *__restrict__ qs, const float *__restrict__ dq, int nb, int kp,
+half_acts_kernel(int kq, int perm, const int8_t *__restrict__ qs, const float *__restrict__ dq, int nb, int kp,
                  __half *__restrict__ xh, float *__restrict__ rowscale) {
     __shared__ float red[8];
     __shared__ float inv_s;
@@ -147,16 +147,19 @@ half_acts_kernel(int kq, const int8_t *__restrict__ qs, const float *__restrict_
     __half *hrow = xh + (size_t)t * kp;
     const int bv = kq ? QK_K : Q8_0_VALUES;
     for (int k = threadIdx.x; k < kp; k += blockDim.x) {
-        const int blk = k / bv;
-        const int pos = kq ? blk * QK_K + q8k_split_pos(k - blk * QK_K) : k;
+        // perm: position 4g + (0,1,2,3) holds value 4g + (0,2,1,3)
+        const int src = perm ? ((k & ~3) | ((k & 1) << 1) | ((k >> 1) & 1)) : k;
+        const int blk = src / bv;
+        const int pos = kq ? blk * QK_K + q8k_split_pos(src - blk * QK_K) : src;
         hrow[k] = __float2half_rn(__fmul_rn(__fmul_rn(drow[blk], inv), (float)qrow[pos]));
     }
 }
 
-cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, __half *xh, float *rowscale, cudaStream_t s) {
+cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, bool k_perm, __half *xh, float *rowscale,
+                             cudaStream_t s) {
     if (T <= 0) return cudaSuccess;
     const int bv = block_values(kind), nb = (K + bv - 1) / bv;
-    half_acts_kernel<<<T, 256, 0, s>>>(kind != KIND_Q8_0, a.qs, a.d, nb, nb * bv, xh, rowscale);
+    half_acts_kernel<<<T, 256, 0, s>>>(kind != KIND_Q8_0, k_perm ? 1 : 0, a.qs, a.d, nb, nb * bv, xh, rowscale);
     return cudaGetLastError();
 }
 

@@ -1,15 +1,17 @@
 // TMA-fed variant of the tensor-core quantized matmul (tcgen05 + TMEM), used when the weight rows are
 // 16-byte multiples (K % 2048 == 0 for Q6_K, K % 256 == 0 for Q8_0, always for Q4_K).
 //
-//   warp 18     one thread streams slabs of RAW packed weight blocks (rows_box rows x one super-block
+//   warp 21     one thread streams slabs of RAW packed weight blocks (rows_box rows x one super-block
 //               column, no swizzle) from HBM into a ring with cp.async.bulk.tensor.
-//   warp 17     one thread loads the BN x 64 fp16 activation tile of every K step (SWIZZLE_128B) straight
+//   warp 20     one thread loads the BN x 64 fp16 activation tile of every K step (SWIZZLE_128B) straight
 //               into the MMA stage, also with cp.async.bulk.tensor.
-//   warps 0..15 converters, two groups that alternate K steps: read the packed blocks from shared memory,
-//               dequantise 32 values per thread with packed-half arithmetic (byte -> 1024+q by PRMT,
-//               -1024, one HFMA2 per two values) and store the fp16 A tile in the canonical K-major
-//               SWIZZLE_128B layout; group 0 later runs the epilogue (tcgen05.ld, + bias, coalesced stores).
-//   warp 16     one thread issues tcgen05.mma (M = 128, N = BN, K = 16) and tcgen05.commit; owns TMEM.
+//   warps 0..15 converters, four groups of four warps, group g taking the K steps with ks % 4 == g: every
+//               thread dequantises the 64 values of one weight row from the packed blocks in shared memory
+//               with packed-half arithmetic (nibble -> 1024+q by mask-and-or, -1024, one HFMA2 per two
+//               values) and stores them into the fp16 A tile in the canonical K-major SWIZZLE_128B layout;
+//               warps 0..7 later run the epilogue (tcgen05.ld, + bias, coalesced stores).
+//   warps 16..19 one thread each issues tcgen05.mma (M = 128, N = BN, K = 16) and tcgen05.commit for the K
+//               steps ks % issuers == i into its own TMEM accumulator (narrow tiles are issue bound).
 //
 // For few tokens (T <= 64) the matmul is bound by the weight stream, so the CTAs take fewer than 128
 // weight rows each (F split evenly over the SMs, rounded up to 8) instead of full 128-row tiles that
@@ -28,16 +30,18 @@ namespace mcu {
 
 constexpr int TM_BM = 128;
 constexpr int TM_BK = 64;
-constexpr int TM_CONV_WARPS = 8;   // warps per converter group: one K step needs 256 threads (row, 32-value half)
-constexpr int TM_CONV_GROUPS = 2;  // the groups alternate K steps
-constexpr int TM_ALL_CONV = TM_CONV_WARPS * TM_CONV_GROUPS;
+constexpr int TM_ALL_CONV = 16;  // converter warps, split into G groups (template parameter of the kernel):
+                                 // G = 4: one weight row (64 values) per thread, group g takes the K steps ks % 4 == g;
+                                 // G = 2: half a row (32 values) per thread, the groups alternate K steps.
+                                 // A group must never be two uses of a stage ahead of the MMA (a parity wait cannot
+                                 // tell them apart), which holds when the stage ring is at least G deep.
 constexpr int TM_MAX_ISSUERS = 4;  // MMA-issuing warps, each with its own TMEM accumulator (see NACC in the kernel)
 constexpr int TM_B_PRODUCER = TM_ALL_CONV + TM_MAX_ISSUERS;
 constexpr int TM_W_PRODUCER = TM_B_PRODUCER + 1;
 constexpr int TM_THREADS = (TM_W_PRODUCER + 1) * 32;
 constexpr int TM_A_BYTES = TM_BM * TM_BK * 2;
 constexpr int TM_MAX_RING = 8;
-constexpr uint32_t TM_SPIN_LIMIT = 1u << 22;
+constexpr uint32_t TM_SPIN_LIMIT = 1u << 20;
 
 template <int KIND>
 struct RawCfg;
@@ -70,7 +74,8 @@ struct GemmTmaParams {
     int rows_per_cta;  // weight rows per CTA (= tensor-map box rows), <= 128
     int stages;        // MMA stage ring depth
     int raw_stages;    // raw slab ring depth
-    int issuers;       // MMA-issuing threads in use: 1, 2 or 4, a divisor of `stages`
+    int raw_stage_bytes;  // bytes of one slab slot (a multiple of 128)
+    int issuers;       // MMA-issuing warps in use (1..4), a divisor of `stages`
 #ifdef MCU_TRACE
     long long *trace;  // development aid: clock64 samples of CTA 0, [agent][step][point]
 #endif
@@ -96,37 +101,25 @@ __device__ __forceinline__ void tm_mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void tm_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// Bounded wait: every try_wait may suspend the thread in hardware for up to TM_WAIT_HINT_NS and returns early
+// when the phase completes, so waiting warps execute next to no instructions; TM_SPIN_LIMIT tries bound the
+// whole wait to about two seconds, after which the caller records an error and winds down.
+constexpr uint32_t TM_WAIT_HINT_NS = 2000;
 __device__ __forceinline__ bool tm_mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < TM_SPIN_LIMIT; ++i) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
-            : "r"(bar), "r"(parity)
+            : "r"(bar), "r"(parity), "r"(TM_WAIT_HINT_NS)
             : "memory");
         if (ok) return true;
     }
     return false;
 }
-// Same, for the agents that have slack (converters, producers): sleep between polls so that waiting warps
-// do not take issue slots from the single thread that feeds the tensor core.
-__device__ __forceinline__ bool tm_mbar_wait_relaxed(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < TM_SPIN_LIMIT; ++i) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        __nanosleep(40);
-    }
-    return false;
-}
+__device__ __forceinline__ bool tm_mbar_wait_relaxed(uint32_t bar, uint32_t parity) { return tm_mbar_wait(bar, parity); }
 // 2-D tiled tensor load, completion counted in bytes on an mbarrier of this CTA (no multicast).
 __device__ __forceinline__ void tm_tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
     asm volatile(
@@ -176,50 +169,100 @@ __device__ __forceinline__ void tm_lds_words(const uint8_t *p, uint32_t (&out)[N
 __device__ __forceinline__ __half2 as_half2(uint32_t v) { return *(const __half2 *)&v; }
 __device__ __forceinline__ uint32_t as_u32(__half2 v) { return *(const uint32_t *)&v; }
 
-// Four unsigned bytes (each < 256) -> two half2 holding byte - offset, in byte order.
-__device__ __forceinline__ void bytes_to_half2(uint32_t w, __half2 offset, __half2 &v01, __half2 &v23) {
+// The fp16 tiles hold every group of four consecutive K values in the order (0, 2, 1, 3): the two 16-bit lanes of
+// a 32-bit word then come from bytes (0, 2) and (1, 3) of a packed word, which is what mask-and-or extraction
+// yields without shuffling bytes.  The activation rows are written in the same order (half_acts_kernel).
+
+// Four unsigned bytes (each < 256) -> two half2 holding byte - offset: bytes (0, 2) and bytes (1, 3).
+__device__ __forceinline__ void bytes_to_half2(uint32_t w, __half2 offset, __half2 &v02, __half2 &v13) {
     // 0x64xx is the fp16 bit pattern of 1024 + xx
-    v01 = __hsub2(as_half2(__byte_perm(w, 0x64646464u, 0x4140)), offset);
-    v23 = __hsub2(as_half2(__byte_perm(w, 0x64646464u, 0x4342)), offset);
+    v02 = __hsub2(as_half2(__byte_perm(w, 0x64646464u, 0x4240)), offset);
+    v13 = __hsub2(as_half2(__byte_perm(w, 0x64646464u, 0x4341)), offset);
+}
+__device__ __forceinline__ __half2 bcast_lo(__half2 v) { return as_half2(__byte_perm(as_u32(v), 0u, 0x1010)); }
+__device__ __forceinline__ __half2 bcast_hi(__half2 v) { return as_half2(__byte_perm(as_u32(v), 0u, 0x3232)); }
+
+// ---- converters: the 64 values of one weight row for K step KQ of the slab, as eight 16-byte chunks ----
+
+// Q4_K: bytes 32*kq .. 32*kq+31 of qs hold sub-block 2*kq in their low nibbles and 2*kq+1 in their high nibbles.
+// Everything stays in packed-half and integer lanes: 6-bit scales become fp16 through the 0x6400 pattern, the
+// products d*sc and dmin*m are single fp16 roundings of exact values (11-bit x 6-bit), exactly what rounding the
+// f32 products would give.
+// 6-bit scales and mins of the sub-blocks 2*kq (byte 0) and 2*kq+1 (byte 1): the bit selection of
+// get_scale_min_k4 on two bytes at once.  kq is uniform over the warp.
+__device__ __forceinline__ void q4k_scale_bytes(const uint4 &hdr, int kq, uint32_t &sc2, uint32_t &mn2) {
+    const int sh = 16 * (kq & 1);
+    if (kq < 2) {
+        sc2 = (hdr.y >> sh) & 0x3F3Fu;
+        mn2 = (hdr.z >> sh) & 0x3F3Fu;
+    } else {
+        sc2 = ((hdr.w >> sh) & 0x0F0Fu) | (((hdr.y >> (sh + 6)) & 0x0303u) << 4);
+        mn2 = ((hdr.w >> (sh + 4)) & 0x0F0Fu) | (((hdr.z >> (sh + 6)) & 0x0303u) << 4);
+    }
 }
 
-// ---- converters: 32 values of row `rowp` (packed bytes in shared memory) for K step `kq` of the slab ----
-template <int KQ>
-__device__ __forceinline__ void conv_q4k(const uint8_t *rowp, int h, uint4 (&outv)[4]) {
-    const uint4 hdr = *(const uint4 *)rowp;
-    const uint4 q0 = *(const uint4 *)(rowp + 16 + 32 * KQ), q1 = *(const uint4 *)(rowp + 32 + 32 * KQ);
-    // 6-bit scale / min of sub-block 2*KQ + h (bit selection of get_scale_min_k4)
-    uint32_t sc, mn;
-    if (KQ < 2) {
-        const int sh = 8 * (2 * KQ + h);
-        sc = (hdr.y >> sh) & 63u;
-        mn = (hdr.z >> sh) & 63u;
-    } else {
-        const int sh = 8 * (2 * KQ + h - 4);
-        sc = ((hdr.w >> sh) & 0xFu) | (((hdr.y >> (sh + 6)) & 3u) << 4);
-        mn = ((hdr.w >> (sh + 4)) & 0xFu) | (((hdr.z >> (sh + 6)) & 3u) << 4);
-    }
-    const float d = half_bits_to_float((uint16_t)(hdr.x & 0xFFFFu));
-    const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
-    const __half2 d1 = __float2half2_rn(__fmul_rn(d, (float)sc));
-    const __half2 m1n = __float2half2_rn(-__fmul_rn(dmin, (float)mn));
-    const __half2 off = __float2half2_rn(1024.0f);
+__device__ __forceinline__ void conv_q4k(const uint8_t *rowp, int kq, uint4 (&outv)[8]) {
+    const uint4 hdr = *(const uint4 *)rowp;  // d, dmin | scales[0..3] | scales[4..7] | scales[8..11]
+    const uint4 q0 = *(const uint4 *)(rowp + 16 + 32 * kq), q1 = *(const uint4 *)(rowp + 32 + 32 * kq);
+    uint32_t sc2, mn2;
+    q4k_scale_bytes(hdr, kq, sc2, mn2);
+    const __half2 k1024 = as_half2(0x64006400u), k64 = as_half2(0x54005400u);
+    const __half2 sc_h = __hsub2(as_half2(__byte_perm(sc2, 0x64646464u, 0x4140)), k1024);  // (sc_a, sc_b)
+    const __half2 mn_h = __hsub2(as_half2(__byte_perm(mn2, 0x64646464u, 0x4140)), k1024);
+    const __half2 dd = as_half2(__byte_perm(hdr.x, 0u, 0x1010));                     // (d, d)
+    const __half2 nd = as_half2(__byte_perm(hdr.x, 0u, 0x3232) ^ 0x80008000u);       // (-dmin, -dmin)
+    const __half2 s2 = __hmul2(sc_h, dd), m2 = __hmul2(mn_h, nd);
+    const __half2 sa = bcast_lo(s2), sb = bcast_hi(s2), ma = bcast_lo(m2), mb = bcast_hi(m2);
     const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-    const int nsh = 4 * h;
+    uint32_t oa[16], ob[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t ws = w[i] >> 8;
+        // 0x6400 | n = 1024 + n;  0x5400 | (n << 4) = 64 + n
+        const __half2 a0 = as_half2((w[i] & 0x000F000Fu) | 0x64006400u), a1 = as_half2((ws & 0x000F000Fu) | 0x64006400u);
+        const __half2 b0 = as_half2((w[i] & 0x00F000F0u) | 0x54005400u), b1 = as_half2((ws & 0x00F000F0u) | 0x54005400u);
+        oa[2 * i] = as_u32(__hfma2(__hsub2(a0, k1024), sa, ma));
+        oa[2 * i + 1] = as_u32(__hfma2(__hsub2(a1, k1024), sa, ma));
+        ob[2 * i] = as_u32(__hfma2(__hsub2(b0, k64), sb, mb));
+        ob[2 * i + 1] = as_u32(__hfma2(__hsub2(b1, k64), sb, mb));
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        outv[c] = make_uint4(oa[4 * c], oa[4 * c + 1], oa[4 * c + 2], oa[4 * c + 3]);
+        outv[4 + c] = make_uint4(ob[4 * c], ob[4 * c + 1], ob[4 * c + 2], ob[4 * c + 3]);
+    }
+}
+
+// The same for half a row: h = 0 takes the low nibbles (sub-block 2*kq), h = 1 the high nibbles (2*kq+1) of the
+// step's 32 bytes; out[0..3] are the 16-byte chunks 4h .. 4h+3 of the tile row.
+__device__ __forceinline__ void conv_q4k_half(const uint8_t *rowp, int kq, int h, uint4 (&outv)[4]) {
+    const uint4 hdr = *(const uint4 *)rowp;
+    const uint4 q0 = *(const uint4 *)(rowp + 16 + 32 * kq), q1 = *(const uint4 *)(rowp + 32 + 32 * kq);
+    uint32_t sc2, mn2;
+    q4k_scale_bytes(hdr, kq, sc2, mn2);
+    const __half2 k1024 = as_half2(0x64006400u);
+    const __half2 sc_h = __hsub2(as_half2(__byte_perm(sc2, 0x64646464u, 0x4140)), k1024);
+    const __half2 mn_h = __hsub2(as_half2(__byte_perm(mn2, 0x64646464u, 0x4140)), k1024);
+    const __half2 dd = as_half2(__byte_perm(hdr.x, 0u, 0x1010));
+    const __half2 nd = as_half2(__byte_perm(hdr.x, 0u, 0x3232) ^ 0x80008000u);
+    const __half2 s2 = __hmul2(sc_h, dd), m2 = __hmul2(mn_h, nd);
+    const __half2 sv = h ? bcast_hi(s2) : bcast_lo(s2), mv = h ? bcast_hi(m2) : bcast_lo(m2);
+    const uint32_t mask = h ? 0x00F000F0u : 0x000F000Fu, magic = h ? 0x54005400u : 0x64006400u;
+    const __half2 off = as_half2(magic);
+    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
     uint32_t o[16];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const uint32_t nib = (w[j] >> nsh) & 0x0F0F0F0Fu;
-        __half2 a, b;
-        bytes_to_half2(nib, off, a, b);
-        o[2 * j] = as_u32(__hfma2(a, d1, m1n));
-        o[2 * j + 1] = as_u32(__hfma2(b, d1, m1n));
+    for (int i = 0; i < 8; ++i) {
+        const __half2 v0 = as_half2((w[i] & mask) | magic), v1 = as_half2(((w[i] >> 8) & mask) | magic);
+        o[2 * i] = as_u32(__hfma2(__hsub2(v0, off), sv, mv));
+        o[2 * i + 1] = as_u32(__hfma2(__hsub2(v1, off), sv, mv));
     }
 #pragma unroll
     for (int c = 0; c < 4; ++c) outv[c] = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
 }
 
-__device__ __forceinline__ void conv_q6k(const uint8_t *blk, int kq, int h, uint4 (&outv)[4]) {
+// Q6_K: 32 values (half h of K step kq) of one block.
+__device__ __forceinline__ void conv_q6k(const uint8_t *blk, int kq, int h, uint4 *outv) {
     const int n = kq >> 1, c = 2 * (kq & 1) + h;  // values 128n + 32c + l
     uint32_t ql[8], qh[8];
     tm_lds_words<8>(blk + n * 64 + (c & 1) * 32, ql);
@@ -244,7 +287,8 @@ __device__ __forceinline__ void conv_q6k(const uint8_t *blk, int kq, int h, uint
     for (int cc = 0; cc < 4; ++cc) outv[cc] = make_uint4(o[4 * cc], o[4 * cc + 1], o[4 * cc + 2], o[4 * cc + 3]);
 }
 
-__device__ __forceinline__ void conv_q8_0(const uint8_t *blk, uint4 (&outv)[4]) {
+// Q8_0: one 32-value block.
+__device__ __forceinline__ void conv_q8_0(const uint8_t *blk, uint4 *outv) {
     const __half2 dh = __half2half2(__ushort_as_half(*(const uint16_t *)blk));
     uint32_t q[8];
     tm_lds_words<8>(blk + 2, q);
@@ -258,10 +302,20 @@ __device__ __forceinline__ void conv_q8_0(const uint8_t *blk, uint4 (&outv)[4]) 
         o[2 * j + 1] = as_u32(__hmul2(b, dh));
     }
 #pragma unroll
-    for (int c = 0; c < 4; ++c) outv[c] = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+    for (int cc = 0; cc < 4; ++cc) outv[cc] = make_uint4(o[4 * cc], o[4 * cc + 1], o[4 * cc + 2], o[4 * cc + 3]);
 }
 
-template <int KIND, int BN>
+__device__ __forceinline__ bool tm_elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+template <int KIND, int BN, int G>
 __global__ void __launch_bounds__(TM_THREADS, 1)
 gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                 const GemmTmaParams p) {
@@ -269,12 +323,13 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     using RC = RawCfg<KIND>;
     constexpr int B_BYTES = BN * TM_BK * 2;
     constexpr int STAGE_BYTES = TM_A_BYTES + B_BYTES;
-    constexpr int RAW_STAGE_BYTES = TM_BM * RC::BOX_W + 128;  // + slack for the one-word over-read
+    const int RAW_STAGE_BYTES = p.raw_stage_bytes;  // rows_per_cta * BOX_W rounded to 128, + slack for the one-word over-read
     // One thread can issue tcgen05.mma only so fast (a few hundred cycles per K step including its barrier
     // wait and commit), which is far slower than the tensor core for narrow tiles.  NACC threads therefore issue
     // interleaved K steps (step ks -> issuer ks % NACC), each into its own accumulator; the epilogue adds them.
     constexpr int NACC = BN == 64 ? 4 : (BN == 128 ? 2 : 1);
     constexpr uint32_t TMEM_COLS = NACC * BN;  // 256 for every BN: a power of two >= 32
+    constexpr int GW = TM_ALL_CONV / G;        // warps per converter group
 
     const uint32_t raw_addr = tm_smem_u32(smem_raw);
     const uint32_t bar_base = (raw_addr + 7u) & ~7u;
@@ -283,8 +338,13 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const int S = p.stages, R = p.raw_stages;
     uint8_t *raw_ring = tiles + (size_t)S * STAGE_BYTES;
     const uint32_t raw_ring_addr = tile_base + (uint32_t)S * STAGE_BYTES;
-    // barrier slots (8 bytes each): full[8] (unused[8]) stage_empty[8] raw_full[8] raw_empty[8] accum
-    const uint32_t a_full = bar_base, st_empty = bar_base + 128u, raw_full = bar_base + 192u,
+    // barrier slots (8 bytes each): full[8] stage_empty_odd[8] stage_empty[8] raw_full[8] raw_empty[8] accum
+    // Stage-release barriers come in two sets used by alternate uses of a stage (use = ks / S): the converter
+    // groups wait for a stage only at every G-th step, and with one barrier per stage a group could be two
+    // phases ahead of it, which a parity wait cannot tell from "done".  With two sets the phases of one barrier
+    // are 2*S steps apart, and everything up to step ks - 3*S is complete before any group reaches step ks
+    // (the activation producer walks the steps in order), as long as S >= G.
+    const uint32_t a_full = bar_base, st_empty = bar_base + 128u, st_empty_odd = bar_base + 64u, raw_full = bar_base + 192u,
                    raw_empty = bar_base + 256u, accum_bar = bar_base + 320u;
     uint32_t *tmem_slot = (uint32_t *)(smem_raw + (bar_base - raw_addr) + 336);
     volatile int *abort_flag = (volatile int *)(smem_raw + (bar_base - raw_addr) + 344);
@@ -295,8 +355,9 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < S; ++i) {
-            tm_mbar_init(a_full + 8u * i, TM_CONV_WARPS + 1);  // eight converter warps + the activation tile's expect_tx
+            tm_mbar_init(a_full + 8u * i, GW + 1);  // a group's converter warps + the activation tile's expect_tx
             tm_mbar_init(st_empty + 8u * i, 1);
+            tm_mbar_init(st_empty_odd + 8u * i, 1);
         }
         for (int i = 0; i < R; ++i) {
             tm_mbar_init(raw_full + 8u * i, 1);
@@ -322,17 +383,18 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         if (lane == 0) {
             bool ok = true;
             int st = 0;
-            uint32_t phase = 1;  // parity of the previous use of the stage
+            uint32_t use = 0;  // ks / S
             for (int ks = 0; ks < p.ksteps && ok; ++ks) {
                 MCU_TRACE_POINT(2, ks, 0);
-                if (ks >= S) ok = tm_mbar_wait_relaxed(st_empty + 8u * st, phase);
+                if (use >= 1)  // release of the previous use of this stage
+                    ok = tm_mbar_wait_relaxed((((use - 1) & 1u) ? st_empty_odd : st_empty) + 8u * st, ((use - 1) >> 1) & 1u);
                 if (!ok) break;
                 tm_mbar_expect_tx(a_full + 8u * st, (uint32_t)B_BYTES);
                 tm_tma_load_2d(tile_base + (uint32_t)st * STAGE_BYTES + TM_A_BYTES, &map_x, ks * TM_BK, t0, a_full + 8u * st);
                 MCU_TRACE_POINT(2, ks, 1);
                 if (++st == S) {
                     st = 0;
-                    phase ^= 1u;
+                    ++use;
                 }
             }
             if (!ok) {
@@ -351,11 +413,13 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             int rs = 0;
             uint32_t phase = 1;  // parity of the previous use of the slab slot
             for (int j = 0; j < n_slabs && ok; ++j) {
+                MCU_TRACE_POINT(3, j, 0);
                 if (j >= R) ok = tm_mbar_wait_relaxed(raw_empty + 8u * rs, phase);
                 if (!ok) break;
                 tm_mbar_expect_tx(raw_full + 8u * rs, raw_bytes);
                 tm_tma_load_2d(raw_ring_addr + (uint32_t)rs * RAW_STAGE_BYTES, &map_w, (j * RC::UNIT) & ~15, f0,
                                raw_full + 8u * rs);
+                MCU_TRACE_POINT(3, j, 1);
                 if (++rs == R) {
                     rs = 0;
                     phase ^= 1u;
@@ -369,107 +433,137 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         __syncwarp();
     } else if (warp >= TM_ALL_CONV) {
         // ------------------------------ MMA issuers ------------------------------
+        // The whole warp runs the loop; one elected lane issues the MMAs and commits (always the same lane, so
+        // tcgen05.commit covers every MMA of this issuer).
         const int issuer = warp - TM_ALL_CONV;
-        if (lane == 0 && issuer < p.issuers) {
+        if (issuer < p.issuers) {
             constexpr uint32_t idesc = tm_idesc(BN);
             bool ok = true;
-            // These threads pace the tensor core: keep the per-step instruction count minimal (running ring
-            // position and descriptors instead of divisions and re-encoding).
             const uint64_t a_desc0 = tm_smem_desc(tile_base), b_desc0 = tm_smem_desc(tile_base + TM_A_BYTES);
             constexpr uint64_t desc_step = (uint64_t)(STAGE_BYTES >> 4);
             const uint32_t tmem_acc = tmem_base + (uint32_t)(issuer * BN);
             int st = issuer % S;
-            uint32_t phase = (uint32_t)((issuer / S) & 1), acc = 0;
+            uint32_t use = (uint32_t)(issuer / S), acc = 0;
             const int nacc = p.issuers;
             for (int ks = issuer; ks < p.ksteps; ks += nacc) {
-                MCU_TRACE_POINT(0, ks, 0);
-                ok = tm_mbar_wait(a_full + 8u * st, phase);  // weight tile converted and activation tile landed
-                MCU_TRACE_POINT(0, ks, 1);
+                if (lane == 0) MCU_TRACE_POINT(0, ks, 0);
+                ok = tm_mbar_wait(a_full + 8u * st, use & 1u);  // weight tile converted and activation tile landed
+                ok = __all_sync(0xffffffffu, ok);
+                if (lane == 0) MCU_TRACE_POINT(0, ks, 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t a_desc = a_desc0 + desc_step * (uint64_t)st, b_desc = b_desc0 + desc_step * (uint64_t)st;
-                tm_mma(tmem_acc, a_desc, b_desc, idesc, acc);
-                tm_mma(tmem_acc, a_desc + 2, b_desc + 2, idesc, 1u);  // +32 bytes along K inside the swizzle row
-                tm_mma(tmem_acc, a_desc + 4, b_desc + 4, idesc, 1u);
-                tm_mma(tmem_acc, a_desc + 6, b_desc + 6, idesc, 1u);
+                if (tm_elect_one()) {
+                    const uint64_t a_desc = a_desc0 + desc_step * (uint64_t)st, b_desc = b_desc0 + desc_step * (uint64_t)st;
+                    tm_mma(tmem_acc, a_desc, b_desc, idesc, acc);
+                    tm_mma(tmem_acc, a_desc + 2, b_desc + 2, idesc, 1u);  // +32 bytes along K inside the swizzle row
+                    tm_mma(tmem_acc, a_desc + 4, b_desc + 4, idesc, 1u);
+                    tm_mma(tmem_acc, a_desc + 6, b_desc + 6, idesc, 1u);
+                    MCU_TRACE_POINT(0, ks, 2);
+                    tm_commit(((use & 1u) ? st_empty_odd : st_empty) + 8u * st);
+                    MCU_TRACE_POINT(0, ks, 3);
+                }
+                __syncwarp();
                 acc = 1u;
-                tm_commit(st_empty + 8u * st);
-                MCU_TRACE_POINT(0, ks, 3);
                 st += nacc;
                 while (st >= S) {
                     st -= S;
-                    phase ^= 1u;
+                    ++use;
                 }
             }
-            if (!ok) {
+            if (!ok && lane == 0) {
                 atomicExch(p.err, 7);
                 *abort_flag = 1;
             }
-            tm_commit(accum_bar);  // arrives when every MMA this thread issued has completed
+            __syncwarp();
+            if (tm_elect_one()) tm_commit(accum_bar);  // arrives when every MMA this issuer issued has completed
         }
         __syncwarp();
     } else {
         // ------------------------------ converters ------------------------------
-        // Two groups of eight warps; group g converts the K steps with (step index inside the slab) % 2 == g.
-        const int group = warp / TM_CONV_WARPS;
-        const int tid = threadIdx.x - group * (TM_CONV_WARPS * 32);
-        const int r = tid >> 1, h = tid & 1;
+        // G groups of GW warps; group g converts the K steps with ks % G == g.
+        const int group = warp / GW;
+        const int gtid = threadIdx.x - group * (GW * 32);
+        const int r = G == 4 ? gtid : gtid >> 1;  // weight row of this thread
+        const int hc = gtid & 1;                  // G == 2: which half of the row's step
         const bool row_live = r < rows_here;
         bool ok = true;
         const int n_slabs = (p.ksteps + RC::KR - 1) / RC::KR;
-        int rs = 0, st = 0;              // running ring positions of the slab and of the K step
-        uint32_t raw_phase = 0, st_phase = 1;  // st_phase: parity of the previous use of stage st
+        // Every warp visits every slab in order (wait for it, release it), and converts the K steps of its group
+        // that fall into it: one code path, no per-step template copies (the instruction cache matters here).
+        int rs = 0, st = group, ks = group;  // ring positions of the slab and of this group's next K step
+        uint32_t raw_phase = 0, use = 0;     // use = ks / S
         for (int j = 0; j < n_slabs && ok; ++j) {
+            if (threadIdx.x == 0) MCU_TRACE_POINT(3, j, 2);
             ok = tm_mbar_wait_relaxed(raw_full + 8u * rs, raw_phase);
+            if (threadIdx.x == 0) MCU_TRACE_POINT(3, j, 3);
             if (!ok || *abort_flag) {
                 if (!ok && lane == 0) atomicExch(p.err, 8);
                 ok = false;
                 break;
             }
             const uint8_t *rowp = raw_ring + (size_t)rs * RAW_STAGE_BYTES + (size_t)r * RC::BOX_W + ((j * RC::UNIT) & 15);
-            auto do_step = [&](auto kq_tag) {
-                constexpr int KQ = decltype(kq_tag)::value;
-                const int ks = j * RC::KR + KQ;
-                const int my_st = st;
-                const uint32_t my_phase = st_phase;
-                if (++st == S) {  // every warp tracks every step, also the ones of the other group
-                    st = 0;
-                    st_phase ^= 1u;
-                }
-                if ((KQ & 1) != group || ks >= p.ksteps || !ok) return;
-                if (threadIdx.x == 0 || threadIdx.x == 256) MCU_TRACE_POINT(1, ks, 0);
-                if (ks >= S) ok = tm_mbar_wait_relaxed(st_empty + 8u * my_st, my_phase);
+            for (; ks < (j + 1) * RC::KR && ks < p.ksteps; ks += G) {
+                const int kq = ks - j * RC::KR;
+                if (gtid == 0) MCU_TRACE_POINT(1, ks, 0);
+                if (use >= 1)  // the MMA that read the previous contents of this stage has completed
+                    ok = tm_mbar_wait_relaxed((((use - 1) & 1u) ? st_empty_odd : st_empty) + 8u * st, ((use - 1) >> 1) & 1u);
                 if (!ok) {
                     if (lane == 0) atomicExch(p.err, 8);
-                    return;
+                    break;
                 }
-                if (threadIdx.x == 0 || threadIdx.x == 256) MCU_TRACE_POINT(1, ks, 1);
-                uint4 wv[4];
-                if (row_live) {
-                    if constexpr (KIND == KIND_Q4_K) conv_q4k<KQ>(rowp, h, wv);
-                    else if constexpr (KIND == KIND_Q6_K) conv_q6k(rowp, KQ, h, wv);
-                    else {
-                        const int blk = 4 * j + 2 * KQ + h;
-                        if (blk < p.nb) conv_q8_0(rowp + (2 * KQ + h) * Q8_0_BYTES, wv);
-                        else wv[0] = wv[1] = wv[2] = wv[3] = make_uint4(0, 0, 0, 0);
-                    }
-                } else {
-                    wv[0] = wv[1] = wv[2] = wv[3] = make_uint4(0, 0, 0, 0);
-                }
-                uint8_t *a_tile = tiles + (size_t)my_st * STAGE_BYTES;
+                if (gtid == 0) MCU_TRACE_POINT(1, ks, 1);
+                uint8_t *a_row = tiles + (size_t)st * STAGE_BYTES + r * 128;
+                if constexpr (G == 4) {
+                    uint4 wv[8];
+                    if (row_live) {
+                        if constexpr (KIND == KIND_Q4_K) {
+                            conv_q4k(rowp, kq, wv);
+                        } else if constexpr (KIND == KIND_Q6_K) {
+                            conv_q6k(rowp, kq, 0, wv);
+                            conv_q6k(rowp, kq, 1, wv + 4);
+                        } else {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) *(uint4 *)(a_tile + r * 128 + (((4 * h + c) ^ (r & 7)) << 4)) = wv[c];
+                            for (int h = 0; h < 2; ++h) {
+                                const int blk = 4 * j + 2 * kq + h;
+                                if (blk < p.nb) conv_q8_0(rowp + (2 * kq + h) * Q8_0_BYTES, wv + 4 * h);
+                                else wv[4 * h] = wv[4 * h + 1] = wv[4 * h + 2] = wv[4 * h + 3] = make_uint4(0, 0, 0, 0);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) wv[c] = make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) *(uint4 *)(a_row + ((c ^ (r & 7)) << 4)) = wv[c];
+                } else {
+                    uint4 wv[4];
+                    if (row_live) {
+                        if constexpr (KIND == KIND_Q4_K) {
+                            conv_q4k_half(rowp, kq, hc, wv);
+                        } else if constexpr (KIND == KIND_Q6_K) {
+                            conv_q6k(rowp, kq, hc, wv);
+                        } else {
+                            const int blk = 4 * j + 2 * kq + hc;
+                            if (blk < p.nb) conv_q8_0(rowp + (2 * kq + hc) * Q8_0_BYTES, wv);
+                            else wv[0] = wv[1] = wv[2] = wv[3] = make_uint4(0, 0, 0, 0);
+                        }
+                    } else {
+                        wv[0] = wv[1] = wv[2] = wv[3] = make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) *(uint4 *)(a_row + (((4 * hc + c) ^ (r & 7)) << 4)) = wv[c];
+                }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) tm_mbar_arrive(a_full + 8u * my_st);
-                if (threadIdx.x == 0 || threadIdx.x == 256) MCU_TRACE_POINT(1, ks, 2);
-            };
-            do_step(std::integral_constant<int, 0>{});
-            do_step(std::integral_constant<int, 1>{});
-            if constexpr (RC::KR == 4) {
-                do_step(std::integral_constant<int, 2>{});
-                do_step(std::integral_constant<int, 3>{});
+                if (lane == 0) tm_mbar_arrive(a_full + 8u * st);
+                if (gtid == 0) MCU_TRACE_POINT(1, ks, 2);
+                st += G;
+                while (st >= S) {
+                    st -= S;
+                    ++use;
+                }
             }
+            if (!ok) break;
             __syncwarp();
             if (lane == 0) tm_mbar_arrive(raw_empty + 8u * rs);  // this warp no longer reads the slab
             if (++rs == R) {
@@ -479,10 +573,10 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
 
         // ------------------------------ epilogue ------------------------------
-        if (ok && group == 0) ok = tm_mbar_wait_relaxed(accum_bar, 0);
+        if (ok && warp < 8) ok = tm_mbar_wait_relaxed(accum_bar, 0);
         if (!ok && lane == 0) atomicExch(p.err, 9);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok && group == 0 && !*abort_flag) {
+        if (ok && warp < 8 && !*abort_flag) {
             const int q = warp & 3;
             const int col0 = (warp >> 2) * (BN / 2);
             const int fr = 32 * q + lane;
@@ -573,7 +667,7 @@ bool gemm_tma_supported(int kind, const void *W, const void *W2, int T, int K, i
     return encode_tiled_fn() != nullptr;
 }
 
-template <int KIND, int BN>
+template <int KIND, int BN, int G>
 static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, GemmTmaParams p, long row_bytes,
                                  cudaStream_t s) {
     using RC = RawCfg<KIND>;
@@ -601,56 +695,58 @@ static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, Gemm
             return cudaErrorInvalidValue;
     }
     constexpr int stage_bytes = TM_A_BYTES + BN * TM_BK * 2;
-    constexpr int raw_stage_bytes = TM_BM * RC::BOX_W + 128;
+    const int raw_stage_bytes = (p.rows_per_cta * RC::BOX_W + 127) / 128 * 128 + 128;
     const int budget = 210 * 1024 - 2048;
     const int raw_slabs = (p.ksteps + RC::KR - 1) / RC::KR;
-    // The slab ring carries the HBM stream: deep enough for ~64 KB in flight per SM; the MMA stages get the rest.
-    int R = BN <= 64 ? 5 : (BN <= 128 ? 4 : 3);
+    // The slab ring carries the HBM stream (about 50 KB in flight per SM); the MMA stages get the rest.  The
+    // stage ring is at least G deep (see TM_ALL_CONV) and is cut to a multiple of the issuer count: issuer i takes
+    // the K steps ks = i (mod issuers) and with that always the same stages, so successive uses of one
+    // full-barrier are waited on by one thread in order.  (A parity wait cannot tell "this phase" from "two
+    // phases ago"; an issuer that got ahead of the thread owning the previous use of the stage would fall
+    // through its wait.)
+    int R = BN <= 128 ? 4 : 3;
     if (R > raw_slabs) R = raw_slabs;
-    if (R > TM_MAX_RING) R = TM_MAX_RING;
     int S = (budget - R * raw_stage_bytes) / stage_bytes;
-    while (S < 2 && R > 1) {
+    if (S < G + 2 && R > 3) {  // a ring deeper than G lets a group convert while its previous step is still in the MMA
         --R;
         S = (budget - R * raw_stage_bytes) / stage_bytes;
     }
-    constexpr int NACC = BN == 64 ? 4 : (BN == 128 ? 2 : 1);
-    while (S < NACC && R > 2) {  // every issuer needs a stage of its own
+    while (S < G && R > 1) {
         --R;
         S = (budget - R * raw_stage_bytes) / stage_bytes;
     }
+    if (S < G) return cudaErrorInvalidConfiguration;
     if (S > TM_MAX_RING) S = TM_MAX_RING;
-    if (S > p.ksteps) S = p.ksteps;
-    if (S < 1) return cudaErrorInvalidConfiguration;
-    // Issuer i takes the K steps ks = i (mod issuers) and, with the ring depth a multiple of the issuer count,
-    // always the same stages: successive uses of one full-barrier are then waited on by one thread in order.
-    // (A parity wait cannot tell "this phase" from "two phases ago"; an issuer that got ahead of the thread
-    // owning the previous use of the stage would fall through its wait.)
+    constexpr int NACC = BN == 64 ? 4 : (BN == 128 ? 2 : 1);
     static const int issuer_cap = getenv("MARMOT_CUDA_GEMM_ISSUERS") ? atoi(getenv("MARMOT_CUDA_GEMM_ISSUERS")) : NACC;
-    int issuers = NACC;
-    if (issuer_cap >= 1 && issuers > issuer_cap) issuers = issuer_cap >= 4 ? 4 : (issuer_cap >= 2 ? 2 : 1);
-    while (issuers > 1 && S < issuers) issuers /= 2;
+    int max_issuers = NACC;
+    if (issuer_cap >= 1 && max_issuers > issuer_cap) max_issuers = issuer_cap;
+    int issuers = 1;  // the count that keeps most stages after rounding down (at least G); ties go to more issuers
+    for (int i = 2; i <= max_issuers; ++i)
+        if (S / i * i >= G && S / i * i >= S / issuers * issuers) issuers = i;
     S = S / issuers * issuers;
+    p.raw_stage_bytes = raw_stage_bytes;
     p.issuers = issuers;
     p.stages = S;
     p.raw_stages = R;
     const int smem = 2048 + S * stage_bytes + R * raw_stage_bytes;
     static int configured = 0;
     if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tma_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tma_kernel<KIND, BN, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         configured = smem;
     }
     dim3 grid((unsigned)((p.F + p.rows_per_cta - 1) / p.rows_per_cta), (unsigned)((p.T + BN - 1) / BN), 1);
-    gemm_tma_kernel<KIND, BN><<<grid, TM_THREADS, smem, s>>>(map_w, map_x, p);
+    gemm_tma_kernel<KIND, BN, G><<<grid, TM_THREADS, smem, s>>>(map_w, map_x, p);
     return cudaGetLastError();
 }
 
 template <int KIND>
 static cudaError_t launch_tma_kind(const void *W, const __half *xh, int ldxh, const GemmTmaParams &p, long row_bytes,
                                    cudaStream_t s) {
-    if (p.T <= 64) return launch_tma_bn<KIND, 64>(W, xh, ldxh, p, row_bytes, s);
-    if (p.T <= 128) return launch_tma_bn<KIND, 128>(W, xh, ldxh, p, row_bytes, s);
-    return launch_tma_bn<KIND, 256>(W, xh, ldxh, p, row_bytes, s);
+    if (p.T <= 64) return launch_tma_bn<KIND, 64, 4>(W, xh, ldxh, p, row_bytes, s);
+    if (p.T <= 128) return launch_tma_bn<KIND, 128, 4>(W, xh, ldxh, p, row_bytes, s);
+    return launch_tma_bn<KIND, 256, 2>(W, xh, ldxh, p, row_bytes, s);
 }
 
 #ifdef MCU_TRACE
@@ -683,12 +779,12 @@ cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __hal
         if (rows < 8) rows = 8;
     }
     p.rows_per_cta = rows;
-    p.stages = p.raw_stages = p.issuers = 0;
+    p.stages = p.raw_stages = p.issuers = p.raw_stage_bytes = 0;
 #ifdef MCU_TRACE
     {
         static long long *trace_buf = nullptr;
-        if (trace_buf == nullptr) cudaMalloc(&trace_buf, 3 * 64 * 4 * sizeof(long long));
-        cudaMemsetAsync(trace_buf, 0, 3 * 64 * 4 * sizeof(long long), s);
+        if (trace_buf == nullptr) cudaMalloc(&trace_buf, 4 * 64 * 4 * sizeof(long long));
+        cudaMemsetAsync(trace_buf, 0, 4 * 64 * 4 * sizeof(long long), s);
         p.trace = trace_buf;
         g_trace_buf = trace_buf;
     }

@@ -21,8 +21,10 @@ cudaError_t launch_quantize_act(int kind, const float *x, int ldx, int T, int K,
                                 cudaStream_t s);
 
 // fp16 operands of the tensor-core matmul from the quantized activations: xh[t][k] = d*q*2^-e_t (row stride kp),
-// rowscale[t] = 2^e_t.
-cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, __half *xh, float *rowscale, cudaStream_t s);
+// rowscale[t] = 2^e_t.  k_perm stores every four consecutive K values in the order (0, 2, 1, 3), the order in
+// which the TMA-fed matmul lays out its dequantised weights.
+cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, bool k_perm, __half *xh, float *rowscale,
+                             cudaStream_t s);
 
 // blocks -> f32 (bit-exact with the reference dequantizers)
 cudaError_t launch_dequantize(int kind, const void *blocks, size_t n_values, float *out, cudaStream_t s);
