@@ -18,6 +18,11 @@
  *   - Functions taking `*_dev` pointers expect device memory and only enqueue work on the
  *     context's stream; functions with `_host` in the name take host memory, copy in and out on
  *     that stream and return after the result is in host memory.
+ *   - Quantized weights are model constants: a matmul starts streaming them before the kernel
+ *     enqueued ahead of it on the stream has finished (programmatic dependent launch; only the
+ *     activations, bias and output wait for it).  Weights produced by a kernel on the same stream
+ *     must therefore be complete (stream or event synchronised) before the first matmul that reads
+ *     them is enqueued; weights brought in by mcu_memcpy_to_device or cudaMemcpy* need nothing.
  *   - There is no CPU fallback: every entry point fails with MCU_ERROR_DEVICE_NOT_AVAILABLE when
  *     no CUDA device can be used.
  */

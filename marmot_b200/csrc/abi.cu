@@ -288,9 +288,17 @@ static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx,
     if (gemm) {
         if (gemm_tc_supported(kind, (int)T, (int)K, (int)F)) {
             const bool tma = gemm_tma_supported(kind, w, w2, (int)T, (int)K, (int)F);
-            if (int rc = pack_activations(ctx, kind, x, ldx, T, K, true, tma, ab)) return rc;
             const size_t bv = (size_t)block_values(kind);
             const size_t kp = (K + bv - 1) / bv * bv;
+            if (act_half_fused_smem(kind, (int)K) <= 48 * 1024) {
+                if (int rc = ensure(ctx, ctx->act_half, T * kp * sizeof(__half))) return rc;
+                if (int rc = ensure(ctx, ctx->act_rowscale, T * sizeof(float))) return rc;
+                MCU_CUDA(launch_act_half_fused(kind, x, (int)ldx, (int)T, (int)K, tma, (__half *)ctx->act_half.ptr,
+                                               (float *)ctx->act_rowscale.ptr, ctx->stream));
+                count_launches(1);
+            } else if (int rc = pack_activations(ctx, kind, x, ldx, T, K, true, tma, ab)) {
+                return rc;
+            }
             int launches = 0;
             if (tma)
                 MCU_CUDA(launch_gemm_tma(kind, w, w2, (const __half *)ctx->act_half.ptr,

@@ -155,6 +155,140 @@ half_acts_kernel(int kq, int perm, const int8_t *__restrict__ qs, const float *_
     }
 }
 
+// Quantise-and-stage in one kernel for the tensor-core matmul, which needs neither the int8 values nor the block
+// sums in global memory: one CTA per token quantises the row block by block exactly as the kernels above (values
+// and scales kept in shared memory), then writes xh and rowscale exactly as half_acts_kernel.  Launched with
+// programmatic stream serialization: everything before griddepcontrol.wait is independent of earlier kernels.
+template <bool KQ>
+__global__ void __launch_bounds__(256)
+act_half_fused_kernel(const float *__restrict__ x, int ldx, int K, int nb, int perm, __half *__restrict__ xh,
+                      float *__restrict__ rowscale) {
+    extern __shared__ __align__(16) uint8_t act_sm[];
+    constexpr int BV = KQ ? QK_K : Q8_0_VALUES;
+    const int kp = nb * BV;
+    int8_t *q_s = (int8_t *)act_sm;
+    float *d_s = (float *)(act_sm + ((kp + 15) & ~15));
+    __shared__ float red[8];
+    __shared__ float inv_s;
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const float *xrow = x + (size_t)t * ldx;
+    if (KQ) {
+        for (int blk = warp; blk < nb; blk += 8) {
+            const float *row = xrow + (size_t)blk * QK_K;
+            const int len = min(QK_K, K - blk * QK_K);
+            float v[8];
+            float best_abs = 0.0f, best_val = 0.0f;
+            int best_idx = 0x7fffffff;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int idx = lane + 32 * i;
+                v[i] = idx < len ? row[idx] : 0.0f;
+                const float a = fabsf(v[i]);
+                if (a > best_abs) {
+                    best_abs = a;
+                    best_val = v[i];
+                    best_idx = idx;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float oa = __shfl_xor_sync(0xffffffffu, best_abs, o);
+                const float ov = __shfl_xor_sync(0xffffffffu, best_val, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, best_idx, o);
+                if (oa > best_abs || (oa == best_abs && oi < best_idx)) {
+                    best_abs = oa;
+                    best_val = ov;
+                    best_idx = oi;
+                }
+            }
+            float d = 0.0f, iscale = 0.0f;
+            if (best_abs > 0.0f) {
+                iscale = __fdiv_rn(-127.0f, best_val);
+                d = __fdiv_rn(1.0f, iscale);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                int q = best_abs > 0.0f ? min(nearest_int(__fmul_rn(iscale, v[i])), 127) : 0;
+                q_s[blk * QK_K + lane + 32 * i] = (int8_t)q;
+            }
+            if (lane == 0) d_s[blk] = d;
+        }
+    } else {
+        for (int blk = warp; blk < nb; blk += 8) {
+            const int k = blk * Q8_0_VALUES + lane;
+            const float v = k < K ? xrow[k] : 0.0f;
+            float amax = fabsf(v);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            float scale = __fdiv_rn(amax, 127.0f);
+            if (scale < FLT_MIN) scale = 1.0f;
+            const float inv = __fdiv_rn(1.0f, scale);
+            int q = (int)roundf(__fmul_rn(v, inv));
+            q = max(-127, min(127, q));
+            q_s[k] = (int8_t)q;
+            if (lane == 0) d_s[blk] = __half2float(__float2half_rn(scale));
+        }
+    }
+    __syncthreads();
+    float m = 0.0f;
+    for (int b = threadIdx.x; b < nb; b += blockDim.x) m = fmaxf(m, fabsf(d_s[b]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float mm = 0.0f;
+        for (int i = 0; i < 8; ++i) mm = fmaxf(mm, red[i]);
+        mm *= 127.0f;
+        int e = 0;
+        if (mm > 0.0f && mm < 3.0e38f) {
+            (void)frexpf(mm, &e);
+            e -= 14;
+            e = max(-100, min(100, e));
+        }
+        inv_s = ldexpf(1.0f, -e);
+        rowscale[t] = ldexpf(1.0f, e);
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    __half2 *hrow = (__half2 *)(xh + (size_t)t * kp);
+    for (int k2 = threadIdx.x; k2 < kp / 2; k2 += blockDim.x) {
+        const int k = 2 * k2;
+        // perm: position 4g + (0,1,2,3) holds value 4g + (0,2,1,3)
+        const int s0 = perm ? ((k & ~3) | ((k & 2) >> 1)) : k;           // k even: 0 -> 0, 2 -> 1
+        const int s1 = perm ? ((k & ~3) | 2 | ((k & 2) >> 1)) : k + 1;   // k+1 odd: 1 -> 2, 3 -> 3
+        const float a = __fmul_rn(__fmul_rn(d_s[s0 / BV], inv), (float)q_s[s0]);
+        const float b = __fmul_rn(__fmul_rn(d_s[s1 / BV], inv), (float)q_s[s1]);
+        hrow[k2] = __floats2half2_rn(a, b);
+    }
+}
+
+size_t act_half_fused_smem(int kind, int K) {
+    const int bv = block_values(kind), nb = (K + bv - 1) / bv;
+    return (size_t)((nb * bv + 15) & ~15) + (size_t)nb * sizeof(float);
+}
+
+cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int K, bool k_perm, __half *xh,
+                                  float *rowscale, cudaStream_t s) {
+    if (T <= 0) return cudaSuccess;
+    const int bv = block_values(kind), nb = (K + bv - 1) / bv;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)T, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.dynamicSmemBytes = act_half_fused_smem(kind, K);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (kind == KIND_Q8_0)
+        return cudaLaunchKernelEx(&cfg, act_half_fused_kernel<false>, x, ldx, K, nb, k_perm ? 1 : 0, xh, rowscale);
+    return cudaLaunchKernelEx(&cfg, act_half_fused_kernel<true>, x, ldx, K, nb, k_perm ? 1 : 0, xh, rowscale);
+}
+
 cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, bool k_perm, __half *xh, float *rowscale,
                              cudaStream_t s) {
     if (T <= 0) return cudaSuccess;

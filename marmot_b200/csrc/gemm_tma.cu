@@ -377,10 +377,15 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    // Programmatic dependent launch: the next kernel of the stream may start its own prologue now.  Here the packed
+    // weights are taken to be final when the call is enqueued, so their stream starts at once; the activations,
+    // the per-token scales and the output belong to earlier kernels until griddepcontrol.wait returns.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == TM_B_PRODUCER) {
         // ------------------------------ TMA producer: activation tiles ------------------------------
         if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             int st = 0;
             uint32_t use = 0;  // ks / S
@@ -573,6 +578,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
 
         // ------------------------------ epilogue ------------------------------
+        if (warp < 8) asm volatile("griddepcontrol.wait;" ::: "memory");
         if (ok && warp < 8) ok = tm_mbar_wait_relaxed(accum_bar, 0);
         if (!ok && lane == 0) atomicExch(p.err, 9);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -737,8 +743,18 @@ static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, Gemm
         configured = smem;
     }
     dim3 grid((unsigned)((p.F + p.rows_per_cta - 1) / p.rows_per_cta), (unsigned)((p.T + BN - 1) / BN), 1);
-    gemm_tma_kernel<KIND, BN, G><<<grid, TM_THREADS, smem, s>>>(map_w, map_x, p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(TM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    static const bool no_pdl = getenv("MARMOT_CUDA_NO_PDL") != nullptr;  // diagnostic switch
+    cfg.numAttrs = no_pdl ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, gemm_tma_kernel<KIND, BN, G>, map_w, map_x, p);
 }
 
 template <int KIND>

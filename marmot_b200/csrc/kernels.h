@@ -26,6 +26,12 @@ cudaError_t launch_quantize_act(int kind, const float *x, int ldx, int T, int K,
 cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, bool k_perm, __half *xh, float *rowscale,
                              cudaStream_t s);
 
+// The two steps above in one kernel (one CTA per token, the quantized row kept in shared memory) when the int8
+// values are not needed in global memory; usable while act_half_fused_smem() fits the default 48 KB.
+size_t act_half_fused_smem(int kind, int K);
+cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int K, bool k_perm, __half *xh,
+                                  float *rowscale, cudaStream_t s);
+
 // blocks -> f32 (bit-exact with the reference dequantizers)
 cudaError_t launch_dequantize(int kind, const void *blocks, size_t n_values, float *out, cudaStream_t s);
 
