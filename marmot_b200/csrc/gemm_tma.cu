@@ -120,6 +120,18 @@ __device__ __forceinline__ bool tm_mbar_wait(uint32_t bar, uint32_t parity) {
     return false;
 }
 __device__ __forceinline__ bool tm_mbar_wait_relaxed(uint32_t bar, uint32_t parity) { return tm_mbar_wait(bar, parity); }
+// Non-blocking test, issued ahead of the work that hides its latency; a negative answer is followed by a real wait.
+__device__ __forceinline__ bool tm_mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // 2-D tiled tensor load, completion counted in bytes on an mbarrier of this CTA (no multicast).
 __device__ __forceinline__ void tm_tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
     asm volatile(
@@ -497,9 +509,10 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // that fall into it: one code path, no per-step template copies (the instruction cache matters here).
         int rs = 0, st = group, ks = group;  // ring positions of the slab and of this group's next K step
         uint32_t raw_phase = 0, use = 0;     // use = ks / S
+        bool raw_ready = false;              // answer of the early test for the slab about to be visited
         for (int j = 0; j < n_slabs && ok; ++j) {
             if (threadIdx.x == 0) MCU_TRACE_POINT(3, j, 2);
-            ok = tm_mbar_wait_relaxed(raw_full + 8u * rs, raw_phase);
+            if (!raw_ready) ok = tm_mbar_wait_relaxed(raw_full + 8u * rs, raw_phase);
             if (threadIdx.x == 0) MCU_TRACE_POINT(3, j, 3);
             if (!ok || *abort_flag) {
                 if (!ok && lane == 0) atomicExch(p.err, 8);
@@ -510,13 +523,11 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             for (; ks < (j + 1) * RC::KR && ks < p.ksteps; ks += G) {
                 const int kq = ks - j * RC::KR;
                 if (gtid == 0) MCU_TRACE_POINT(1, ks, 0);
-                if (use >= 1)  // the MMA that read the previous contents of this stage has completed
-                    ok = tm_mbar_wait_relaxed((((use - 1) & 1u) ? st_empty_odd : st_empty) + 8u * st, ((use - 1) >> 1) & 1u);
-                if (!ok) {
-                    if (lane == 0) atomicExch(p.err, 8);
-                    break;
-                }
-                if (gtid == 0) MCU_TRACE_POINT(1, ks, 1);
+                // Has the MMA that read the previous contents of this stage completed?  Asked now, needed only
+                // before the stores: the conversion in between hides the answer's latency.
+                const uint32_t rel_bar = (((use - 1) & 1u) ? st_empty_odd : st_empty) + 8u * st;
+                const uint32_t rel_parity = ((use - 1) >> 1) & 1u;
+                const bool stage_free = use >= 1 ? tm_mbar_test(rel_bar, rel_parity) : true;
                 uint8_t *a_row = tiles + (size_t)st * STAGE_BYTES + r * 128;
                 if constexpr (G == 4) {
                     uint4 wv[8];
@@ -538,8 +549,12 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                         for (int c = 0; c < 8; ++c) wv[c] = make_uint4(0, 0, 0, 0);
                     }
+                    if (!stage_free) ok = tm_mbar_wait_relaxed(rel_bar, rel_parity);
+                    if (gtid == 0) MCU_TRACE_POINT(1, ks, 1);
+                    if (ok) {
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) *(uint4 *)(a_row + ((c ^ (r & 7)) << 4)) = wv[c];
+                        for (int c = 0; c < 8; ++c) *(uint4 *)(a_row + ((c ^ (r & 7)) << 4)) = wv[c];
+                    }
                 } else {
                     uint4 wv[4];
                     if (row_live) {
@@ -555,8 +570,17 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     } else {
                         wv[0] = wv[1] = wv[2] = wv[3] = make_uint4(0, 0, 0, 0);
                     }
+                    if (!stage_free) ok = tm_mbar_wait_relaxed(rel_bar, rel_parity);
+                    if (gtid == 0) MCU_TRACE_POINT(1, ks, 1);
+                    if (ok) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) *(uint4 *)(a_row + (((4 * hc + c) ^ (r & 7)) << 4)) = wv[c];
+                        for (int c = 0; c < 4; ++c) *(uint4 *)(a_row + (((4 * hc + c) ^ (r & 7)) << 4)) = wv[c];
+                    }
+                }
+                if (!__all_sync(0xffffffffu, ok)) {  // a wait ran out: the stage was not written, nothing is signalled
+                    ok = false;
+                    if (lane == 0) atomicExch(p.err, 8);
+                    break;
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
@@ -569,12 +593,14 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 }
             }
             if (!ok) break;
-            __syncwarp();
-            if (lane == 0) tm_mbar_arrive(raw_empty + 8u * rs);  // this warp no longer reads the slab
+            const int released = rs;
             if (++rs == R) {
                 rs = 0;
                 raw_phase ^= 1u;
             }
+            raw_ready = j + 1 < n_slabs ? tm_mbar_test(raw_full + 8u * rs, raw_phase) : false;  // asked early
+            __syncwarp();
+            if (lane == 0) tm_mbar_arrive(raw_empty + 8u * released);  // this warp no longer reads the slab
         }
 
         // ------------------------------ epilogue ------------------------------

@@ -1,7 +1,7 @@
 """One rank of the multi-GPU tensor-parallel check (launched by torch.distributed.run from
 test_tensor_parallel_gpu.py or by hand).  Every rank builds the same weights, shards them, runs the
 column-/row-/expert-parallel layers on its GPU and compares with the unsharded operator on the same GPU.
-Prints one JSON line per rank; exit code 0 means every check passed."""
+Rank 0 prints one JSON line per rank; exit code 0 means every check of that rank passed."""
 from __future__ import annotations
 
 import json
@@ -103,7 +103,12 @@ def main() -> int:
             check("timeout_reported", "timed out" in str(exc))
     dist.barrier()
     torch.cuda.synchronize()
-    print(json.dumps({"rank": rank, "ok": ok, **res}), flush=True)
+    # one writer: lines of several ranks printed at once can interleave in the launcher's pipe
+    gathered = [None] * world
+    dist.all_gather_object(gathered, {"rank": rank, "ok": ok, **res})
+    if rank == 0:
+        for item in gathered:
+            print(json.dumps(item), flush=True)
     # the communicator's epochs now differ between ranks: it is not used again
     comm.close()
     ctx.close()
