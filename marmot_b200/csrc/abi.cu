@@ -67,6 +67,8 @@ struct mcu_context {
     // workspace (grows on demand, never shrinks)
     Buffer act_qs, act_d, act_bsums, act_half, act_rowscale, x_stage, out_stage, bias_stage;
     Buffer moe_meta, moe_hidden, moe_gate, moe_up, moe_down;
+    Buffer gemm_partial;         // split-K partial tiles
+    int *gemm_counters = nullptr;  // split-K tile tickets (zero between launches)
     std::vector<int> host_counts;
     int *dev_err = nullptr;  // set by kernels whose bounded device-side waits ran out
 };
@@ -138,6 +140,8 @@ int mcu_context_create(int device, mcu_context_t **out) {
     ctx->stream = ctx->own_stream;
     e = cudaMalloc(&ctx->dev_err, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->dev_err, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->gemm_counters, GEMM_TMA_MAX_TILE_COUNTERS * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->gemm_counters, 0, GEMM_TMA_MAX_TILE_COUNTERS * sizeof(int));
     if (e != cudaSuccess) {
         cudaStreamDestroy(ctx->own_stream);
         delete ctx;
@@ -156,10 +160,11 @@ void mcu_context_destroy(mcu_context_t *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     Buffer *bufs[] = {&ctx->act_qs,   &ctx->act_d,      &ctx->act_bsums, &ctx->act_half, &ctx->act_rowscale, &ctx->x_stage, &ctx->out_stage,
-                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down};
+                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down, &ctx->gemm_partial};
     for (Buffer *b : bufs)
         if (b->ptr != nullptr) cudaFree(b->ptr);
     if (ctx->dev_err != nullptr) cudaFree(ctx->dev_err);
+    if (ctx->gemm_counters != nullptr) cudaFree(ctx->gemm_counters);
     if (ctx->own_stream != nullptr) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
 }
@@ -300,10 +305,13 @@ static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx,
                 return rc;
             }
             int launches = 0;
-            if (tma)
+            if (tma) {
+                if (int rc = ensure(ctx, ctx->gemm_partial, gemm_tma_workspace_bytes(kind, (int)T, (int)K, (int)F))) return rc;
                 MCU_CUDA(launch_gemm_tma(kind, w, w2, (const __half *)ctx->act_half.ptr,
                                          (const float *)ctx->act_rowscale.ptr, (int)kp, (int)T, (int)K, (int)F,
-                                         bias, out, out2, (int)ldo, ctx->dev_err, ctx->stream, &launches));
+                                         bias, out, out2, (int)ldo, (float *)ctx->gemm_partial.ptr, ctx->gemm_counters,
+                                         ctx->dev_err, ctx->stream, &launches));
+            }
             else
                 MCU_CUDA(launch_gemm_tc(kind, w, w2, (const __half *)ctx->act_half.ptr,
                                         (const float *)ctx->act_rowscale.ptr, (int)kp, (int)T, (int)K, (int)F,

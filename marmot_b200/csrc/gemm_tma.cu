@@ -41,7 +41,7 @@ constexpr int TM_W_PRODUCER = TM_B_PRODUCER + 1;
 constexpr int TM_THREADS = (TM_W_PRODUCER + 1) * 32;
 constexpr int TM_A_BYTES = TM_BM * TM_BK * 2;
 constexpr int TM_MAX_RING = 8;
-constexpr uint32_t TM_SPIN_LIMIT = 1u << 20;
+constexpr uint32_t TM_SPIN_LIMIT = 1u << 24;
 
 template <int KIND>
 struct RawCfg;
@@ -76,6 +76,12 @@ struct GemmTmaParams {
     int raw_stages;    // raw slab ring depth
     int raw_stage_bytes;  // bytes of one slab slot (a multiple of 128)
     int issuers;       // MMA-issuing warps in use (1..4), a divisor of `stages`
+    // Split K (few tokens, few row tiles): blockIdx.z takes `slabs_per_split` slabs of K; every CTA writes its
+    // partial tile to `partial` [split][T][F] and the last CTA of a tile to arrive (ticket in `counters`) adds the
+    // partials in split order, so the result does not depend on the arrival order.
+    int splits, slabs_per_split;
+    float *partial;
+    int *counters;
 #ifdef MCU_TRACE
     long long *trace;  // development aid: clock64 samples of CTA 0, [agent][step][point]
 #endif
@@ -84,7 +90,7 @@ struct GemmTmaParams {
 #ifdef MCU_TRACE
 #define MCU_TRACE_POINT(agent, step, point)                                                          \
     do {                                                                                             \
-        if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (step) < 64)                 \
+        if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (step) < 64)                 \
             p.trace[((agent) * 64 + (step)) * 4 + (point)] = clock64();                               \
     } while (0)
 #else
@@ -101,19 +107,18 @@ __device__ __forceinline__ void tm_mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void tm_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Bounded wait: every try_wait may suspend the thread in hardware for up to TM_WAIT_HINT_NS and returns early
-// when the phase completes, so waiting warps execute next to no instructions; TM_SPIN_LIMIT tries bound the
-// whole wait to about two seconds, after which the caller records an error and winds down.
-constexpr uint32_t TM_WAIT_HINT_NS = 2000;
+// Bounded wait on an mbarrier phase.  try_wait suspends the thread in hardware for a short, system-chosen time and
+// returns early when the phase completes, so a waiting warp executes few instructions; TM_SPIN_LIMIT tries
+// bound the whole wait, after which the caller records an error and winds down.
 __device__ __forceinline__ bool tm_mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < TM_SPIN_LIMIT; ++i) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
-            : "r"(bar), "r"(parity), "r"(TM_WAIT_HINT_NS)
+            : "r"(bar), "r"(parity)
             : "memory");
         if (ok) return true;
     }
@@ -362,8 +367,14 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     volatile int *abort_flag = (volatile int *)(smem_raw + (bar_base - raw_addr) + 344);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) MCU_TRACE_POINT(3, 32, 0);
     const int f0 = blockIdx.x * p.rows_per_cta, t0 = blockIdx.y * BN;
     const int rows_here = min(p.rows_per_cta, p.F - f0);
+    // this CTA's share of K: slabs [j0, j1), K steps [ks0, ks0 + nsteps)
+    const int j0 = (int)blockIdx.z * p.slabs_per_split;
+    const int j1 = min((p.ksteps + RC::KR - 1) / RC::KR, j0 + p.slabs_per_split);
+    const int ks0 = j0 * RC::KR;
+    const int nsteps = min(p.ksteps, j1 * RC::KR) - ks0;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < S; ++i) {
@@ -389,6 +400,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) MCU_TRACE_POINT(3, 33, 0);
     // Programmatic dependent launch: the next kernel of the stream may start its own prologue now.  Here the packed
     // weights are taken to be final when the call is enqueued, so their stream starts at once; the activations,
     // the per-token scales and the output belong to earlier kernels until griddepcontrol.wait returns.
@@ -401,13 +413,13 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             bool ok = true;
             int st = 0;
             uint32_t use = 0;  // ks / S
-            for (int ks = 0; ks < p.ksteps && ok; ++ks) {
+            for (int ks = 0; ks < nsteps && ok; ++ks) {  // ks: step index inside this CTA's share
                 MCU_TRACE_POINT(2, ks, 0);
                 if (use >= 1)  // release of the previous use of this stage
                     ok = tm_mbar_wait_relaxed((((use - 1) & 1u) ? st_empty_odd : st_empty) + 8u * st, ((use - 1) >> 1) & 1u);
                 if (!ok) break;
                 tm_mbar_expect_tx(a_full + 8u * st, (uint32_t)B_BYTES);
-                tm_tma_load_2d(tile_base + (uint32_t)st * STAGE_BYTES + TM_A_BYTES, &map_x, ks * TM_BK, t0, a_full + 8u * st);
+                tm_tma_load_2d(tile_base + (uint32_t)st * STAGE_BYTES + TM_A_BYTES, &map_x, (ks0 + ks) * TM_BK, t0, a_full + 8u * st);
                 MCU_TRACE_POINT(2, ks, 1);
                 if (++st == S) {
                     st = 0;
@@ -426,17 +438,16 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         if (lane == 0) {
             bool ok = true;
             const uint32_t raw_bytes = (uint32_t)p.rows_per_cta * RC::BOX_W;
-            const int n_slabs = (p.ksteps + RC::KR - 1) / RC::KR;
             int rs = 0;
             uint32_t phase = 1;  // parity of the previous use of the slab slot
-            for (int j = 0; j < n_slabs && ok; ++j) {
-                MCU_TRACE_POINT(3, j, 0);
-                if (j >= R) ok = tm_mbar_wait_relaxed(raw_empty + 8u * rs, phase);
+            for (int j = j0; j < j1 && ok; ++j) {
+                MCU_TRACE_POINT(3, j - j0, 0);
+                if (j - j0 >= R) ok = tm_mbar_wait_relaxed(raw_empty + 8u * rs, phase);
                 if (!ok) break;
                 tm_mbar_expect_tx(raw_full + 8u * rs, raw_bytes);
                 tm_tma_load_2d(raw_ring_addr + (uint32_t)rs * RAW_STAGE_BYTES, &map_w, (j * RC::UNIT) & ~15, f0,
                                raw_full + 8u * rs);
-                MCU_TRACE_POINT(3, j, 1);
+                MCU_TRACE_POINT(3, j - j0, 1);
                 if (++rs == R) {
                     rs = 0;
                     phase ^= 1u;
@@ -462,7 +473,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             int st = issuer % S;
             uint32_t use = (uint32_t)(issuer / S), acc = 0;
             const int nacc = p.issuers;
-            for (int ks = issuer; ks < p.ksteps; ks += nacc) {
+            for (int ks = issuer; ks < nsteps; ks += nacc) {
                 if (lane == 0) MCU_TRACE_POINT(0, ks, 0);
                 ok = tm_mbar_wait(a_full + 8u * st, use & 1u);  // weight tile converted and activation tile landed
                 ok = __all_sync(0xffffffffu, ok);
@@ -504,25 +515,24 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const int hc = gtid & 1;                  // G == 2: which half of the row's step
         const bool row_live = r < rows_here;
         bool ok = true;
-        const int n_slabs = (p.ksteps + RC::KR - 1) / RC::KR;
         // Every warp visits every slab in order (wait for it, release it), and converts the K steps of its group
         // that fall into it: one code path, no per-step template copies (the instruction cache matters here).
-        int rs = 0, st = group, ks = group;  // ring positions of the slab and of this group's next K step
-        uint32_t raw_phase = 0, use = 0;     // use = ks / S
-        bool raw_ready = false;              // answer of the early test for the slab about to be visited
-        for (int j = 0; j < n_slabs && ok; ++j) {
-            if (threadIdx.x == 0) MCU_TRACE_POINT(3, j, 2);
+        int rs = 0, st = group, ks = ks0 + group;  // ring positions of the slab and of this group's next K step
+        uint32_t raw_phase = 0, use = 0;           // use = (ks - ks0) / S
+        bool raw_ready = false;                    // answer of the early test for the slab about to be visited
+        for (int j = j0; j < j1 && ok; ++j) {
+            if (threadIdx.x == 0) MCU_TRACE_POINT(3, j - j0, 2);
             if (!raw_ready) ok = tm_mbar_wait_relaxed(raw_full + 8u * rs, raw_phase);
-            if (threadIdx.x == 0) MCU_TRACE_POINT(3, j, 3);
+            if (threadIdx.x == 0) MCU_TRACE_POINT(3, j - j0, 3);
             if (!ok || *abort_flag) {
                 if (!ok && lane == 0) atomicExch(p.err, 8);
                 ok = false;
                 break;
             }
             const uint8_t *rowp = raw_ring + (size_t)rs * RAW_STAGE_BYTES + (size_t)r * RC::BOX_W + ((j * RC::UNIT) & 15);
-            for (; ks < (j + 1) * RC::KR && ks < p.ksteps; ks += G) {
+            for (; ks < (j + 1) * RC::KR && ks < ks0 + nsteps; ks += G) {
                 const int kq = ks - j * RC::KR;
-                if (gtid == 0) MCU_TRACE_POINT(1, ks, 0);
+                if (gtid == 0) MCU_TRACE_POINT(1, ks - ks0, 0);
                 // Has the MMA that read the previous contents of this stage completed?  Asked now, needed only
                 // before the stores: the conversion in between hides the answer's latency.
                 const uint32_t rel_bar = (((use - 1) & 1u) ? st_empty_odd : st_empty) + 8u * st;
@@ -550,7 +560,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         for (int c = 0; c < 8; ++c) wv[c] = make_uint4(0, 0, 0, 0);
                     }
                     if (!stage_free) ok = tm_mbar_wait_relaxed(rel_bar, rel_parity);
-                    if (gtid == 0) MCU_TRACE_POINT(1, ks, 1);
+                    if (gtid == 0) MCU_TRACE_POINT(1, ks - ks0, 1);
                     if (ok) {
 #pragma unroll
                         for (int c = 0; c < 8; ++c) *(uint4 *)(a_row + ((c ^ (r & 7)) << 4)) = wv[c];
@@ -571,7 +581,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         wv[0] = wv[1] = wv[2] = wv[3] = make_uint4(0, 0, 0, 0);
                     }
                     if (!stage_free) ok = tm_mbar_wait_relaxed(rel_bar, rel_parity);
-                    if (gtid == 0) MCU_TRACE_POINT(1, ks, 1);
+                    if (gtid == 0) MCU_TRACE_POINT(1, ks - ks0, 1);
                     if (ok) {
 #pragma unroll
                         for (int c = 0; c < 4; ++c) *(uint4 *)(a_row + (((4 * hc + c) ^ (r & 7)) << 4)) = wv[c];
@@ -585,7 +595,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) tm_mbar_arrive(a_full + 8u * st);
-                if (gtid == 0) MCU_TRACE_POINT(1, ks, 2);
+                if (gtid == 0) MCU_TRACE_POINT(1, ks - ks0, 2);
                 st += G;
                 while (st >= S) {
                     st -= S;
@@ -598,14 +608,16 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 rs = 0;
                 raw_phase ^= 1u;
             }
-            raw_ready = j + 1 < n_slabs ? tm_mbar_test(raw_full + 8u * rs, raw_phase) : false;  // asked early
+            raw_ready = j + 1 < j1 ? tm_mbar_test(raw_full + 8u * rs, raw_phase) : false;  // asked early
             __syncwarp();
             if (lane == 0) tm_mbar_arrive(raw_empty + 8u * released);  // this warp no longer reads the slab
         }
 
         // ------------------------------ epilogue ------------------------------
         if (warp < 8) asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (threadIdx.x == 0) MCU_TRACE_POINT(3, 34, 0);
         if (ok && warp < 8) ok = tm_mbar_wait_relaxed(accum_bar, 0);
+        if (threadIdx.x == 0) MCU_TRACE_POINT(3, 35, 0);
         if (!ok && lane == 0) atomicExch(p.err, 9);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok && warp < 8 && !*abort_flag) {
@@ -620,7 +632,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 float sum[32];
 #pragma unroll
                 for (int jj = 0; jj < 32; ++jj) sum[jj] = 0.0f;
-                const int n_used = p.ksteps < p.issuers ? p.ksteps : p.issuers;  // accumulators that received a K step
+                const int n_used = nsteps < p.issuers ? nsteps : p.issuers;  // accumulators that received a K step
 #pragma unroll
                 for (int a = 0; a < NACC; ++a) {
                     if (a >= n_used) break;  // warp-uniform
@@ -642,17 +654,87 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     for (int jj = 0; jj < 32; ++jj) sum[jj] += __uint_as_float(v[jj]);
                 }
                 if (f_ok) {
+                    if (p.splits == 1) {
 #pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) {
-                        const int t = t0 + col0 + cb + jj;
-                        if (t < p.T) p.out[(size_t)t * p.ldo + f] = sum[jj] * p.rowscale[t] + bias;
+                        for (int jj = 0; jj < 32; ++jj) {
+                            const int t = t0 + col0 + cb + jj;
+                            if (t < p.T) p.out[(size_t)t * p.ldo + f] = sum[jj] * p.rowscale[t] + bias;
+                        }
+                    } else {
+                        float *part = p.partial + (size_t)blockIdx.z * p.T * p.F;
+#pragma unroll
+                        for (int jj = 0; jj < 32; ++jj) {
+                            const int t = t0 + col0 + cb + jj;
+                            if (t < p.T) __stcg(part + (size_t)t * p.F + f, sum[jj]);
+                        }
                     }
                 }
             }
         }
     }
+    if (threadIdx.x == 0) MCU_TRACE_POINT(3, 36, 0);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if (p.splits > 1) {
+        // Last CTA of this tile to finish adds the partial tiles, in split order.
+        __shared__ int last_s;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int *ctr = p.counters + blockIdx.y * gridDim.x + blockIdx.x;
+            const int ticket = atomicAdd(ctr, 1);
+            last_s = ticket == p.splits - 1;
+            if (last_s) *ctr = 0;  // ready for the next launch
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) MCU_TRACE_POINT(3, 37, 0);
+        if (last_s && !*abort_flag) {
+            __threadfence();
+            const int t_here = min(BN, p.T - t0);
+            constexpr int MAXS = 16;  // plan_tma never asks for more splits
+            if ((p.F & 3) == 0 && (rows_here & 3) == 0 && (p.ldo & 3) == 0 && p.splits <= MAXS) {
+                // four features per thread and all splits' loads in flight at once: the tile is small, the reads are
+                // L2 latency bound
+                const int r4 = rows_here >> 2;
+                for (int i = threadIdx.x; i < t_here * r4; i += blockDim.x) {
+                    const int tt = i / r4, fr = (i - tt * r4) << 2;
+                    const int t = t0 + tt, f = f0 + fr;
+                    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                    for (int z0 = 0; z0 < MAXS; z0 += 8) {
+                        if (z0 >= p.splits) break;
+                        float4 v[8];
+#pragma unroll
+                        for (int z = 0; z < 8; ++z)
+                            if (z0 + z < p.splits)
+                                v[z] = __ldcg((const float4 *)(p.partial + ((size_t)(z0 + z) * p.T + t) * p.F + f));
+#pragma unroll
+                        for (int z = 0; z < 8; ++z)
+                            if (z0 + z < p.splits) {
+                                acc.x += v[z].x;
+                                acc.y += v[z].y;
+                                acc.z += v[z].z;
+                                acc.w += v[z].w;
+                            }
+                    }
+                    const float rsc = p.rowscale[t];
+                    float4 b = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (p.bias != nullptr) b = *(const float4 *)(p.bias + f);
+                    *(float4 *)(p.out + (size_t)t * p.ldo + f) =
+                        make_float4(acc.x * rsc + b.x, acc.y * rsc + b.y, acc.z * rsc + b.z, acc.w * rsc + b.w);
+                }
+            } else {
+                for (int i = threadIdx.x; i < t_here * rows_here; i += blockDim.x) {
+                    const int tt = i / rows_here, fr = i - tt * rows_here;
+                    const int t = t0 + tt, f = f0 + fr;
+                    float acc = 0.0f;
+                    for (int z = 0; z < p.splits; ++z) acc += __ldcg(p.partial + ((size_t)z * p.T + t) * p.F + f);
+                    p.out[(size_t)t * p.ldo + f] = acc * p.rowscale[t] + (p.bias != nullptr ? p.bias[f] : 0.0f);
+                }
+            }
+        }
+    }
     __syncthreads();
+    if (threadIdx.x == 0) MCU_TRACE_POINT(3, 38, 0);
     if (*abort_flag) {
         // A wait ran out and the agents stopped early: bulk tensor copies may still be landing in this CTA's
         // shared memory.  Give them time to finish before the CTA (and its shared memory) goes away.
@@ -688,6 +770,46 @@ static EncodeTiledFn encode_tiled_fn() {
 static bool force_v1() {
     static const bool v = getenv("MARMOT_CUDA_GEMM_NO_TMA") != nullptr;
     return v;
+}
+
+// Tiling for few tokens (T <= 64), where the matmul is bound by the weight stream and by the latency of the K loop:
+// full 128-row tiles when K can be split so that tiles x splits still fills the SMs (the serial K loop gets
+// shorter), otherwise the rows spread evenly over the SMs.
+struct TmaPlan {
+    int rows_per_cta, splits, slabs_per_split;
+};
+static TmaPlan plan_tma(int kind, int T, int K, int F) {
+    const int bv = block_values(kind), nb = (K + bv - 1) / bv;
+    const int ksteps = (nb * bv + TM_BK - 1) / TM_BK;
+    const int kr = kind == KIND_Q8_0 ? 2 : 4;
+    const int n_slabs = (ksteps + kr - 1) / kr;
+    TmaPlan pl{TM_BM, 1, n_slabs};
+    if (T > 64) return pl;
+    static const bool no_split = getenv("MARMOT_CUDA_GEMM_NO_SPLITK") != nullptr;  // diagnostic switch
+    const int sms = device_sm_count();
+    const int tiles = (F + TM_BM - 1) / TM_BM;
+    int splits = no_split ? 1 : sms / tiles;
+    if (splits > 16) splits = 16;
+    if (splits >= 2 && n_slabs >= 2) {
+        if (splits > n_slabs) splits = n_slabs;
+        pl.slabs_per_split = (n_slabs + splits - 1) / splits;
+        pl.splits = (n_slabs + pl.slabs_per_split - 1) / pl.slabs_per_split;
+        if (pl.splits >= 2) return pl;
+        pl.splits = 1;
+        pl.slabs_per_split = n_slabs;
+    }
+    const int waves = (F + TM_BM * sms - 1) / (TM_BM * sms);  // passes over the SMs with full tiles
+    int rows = (F + sms * waves - 1) / (sms * waves);
+    rows = (rows + 7) / 8 * 8;
+    if (rows > TM_BM) rows = TM_BM;
+    if (rows < 8) rows = 8;
+    pl.rows_per_cta = rows;
+    return pl;
+}
+
+size_t gemm_tma_workspace_bytes(int kind, int T, int K, int F) {
+    const TmaPlan pl = plan_tma(kind, T, K, F);
+    return pl.splits > 1 ? (size_t)pl.splits * T * F * sizeof(float) : 0;
 }
 
 bool gemm_tma_supported(int kind, const void *W, const void *W2, int T, int K, int F) {
@@ -729,7 +851,7 @@ static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, Gemm
     constexpr int stage_bytes = TM_A_BYTES + BN * TM_BK * 2;
     const int raw_stage_bytes = (p.rows_per_cta * RC::BOX_W + 127) / 128 * 128 + 128;
     const int budget = 210 * 1024 - 2048;
-    const int raw_slabs = (p.ksteps + RC::KR - 1) / RC::KR;
+    const int raw_slabs = p.slabs_per_split;
     // The slab ring carries the HBM stream (about 50 KB in flight per SM); the MMA stages get the rest.  The
     // stage ring is at least G deep (see TM_ALL_CONV) and is cut to a multiple of the issuer count: issuer i takes
     // the K steps ks = i (mod issuers) and with that always the same stages, so successive uses of one
@@ -768,7 +890,7 @@ static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, Gemm
         if (e != cudaSuccess) return e;
         configured = smem;
     }
-    dim3 grid((unsigned)((p.F + p.rows_per_cta - 1) / p.rows_per_cta), (unsigned)((p.T + BN - 1) / BN), 1);
+    dim3 grid((unsigned)((p.F + p.rows_per_cta - 1) / p.rows_per_cta), (unsigned)((p.T + BN - 1) / BN), (unsigned)p.splits);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(TM_THREADS, 1, 1);
@@ -797,8 +919,8 @@ extern "C" long long *mcu_debug_trace_buffer() { return g_trace_buf; }
 #endif
 
 cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __half *xh, const float *rowscale, int ldxh,
-                            int T, int K, int F, const float *bias, float *out, float *out2, int ldo, int *err_flag,
-                            cudaStream_t s, int *launches) {
+                            int T, int K, int F, const float *bias, float *out, float *out2, int ldo, float *partial,
+                            int *counters, int *err_flag, cudaStream_t s, int *launches) {
     GemmTmaParams p;
     p.bias = bias;
     p.rowscale = rowscale;
@@ -810,17 +932,14 @@ cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __hal
     p.nb = (K + bv - 1) / bv;
     p.ksteps = (p.nb * bv + TM_BK - 1) / TM_BK;
     const long row_bytes = (long)p.nb * block_bytes(kind);
-    // weight-stream bound for few tokens: spread the rows evenly over the SMs
-    int rows = TM_BM;
-    if (T <= 64) {
-        const int sms = device_sm_count();
-        const int waves = (F + TM_BM * sms - 1) / (TM_BM * sms);  // passes over the SMs with full tiles
-        rows = (F + sms * waves - 1) / (sms * waves);
-        rows = (rows + 7) / 8 * 8;
-        if (rows > TM_BM) rows = TM_BM;
-        if (rows < 8) rows = 8;
-    }
-    p.rows_per_cta = rows;
+    const TmaPlan pl = plan_tma(kind, T, K, F);
+    p.rows_per_cta = pl.rows_per_cta;
+    p.splits = pl.splits;
+    p.slabs_per_split = pl.slabs_per_split;
+    p.partial = partial;
+    p.counters = counters;
+    if (p.splits > 1 && (partial == nullptr || counters == nullptr || (F + TM_BM - 1) / TM_BM > GEMM_TMA_MAX_TILE_COUNTERS))
+        return cudaErrorInvalidValue;
     p.stages = p.raw_stages = p.issuers = p.raw_stage_bytes = 0;
 #ifdef MCU_TRACE
     {

@@ -59,9 +59,13 @@ cudaError_t launch_gemm_tc(int kind, const void *W, const void *W2, const __half
 // TMA-fed variant of the tensor-core matmul (packed weight slabs and activation tiles arrive by
 // cp.async.bulk.tensor); needs 16-byte aligned weights whose rows are 16-byte multiples.
 bool gemm_tma_supported(int kind, const void *W, const void *W2, int T, int K, int F);
+// Split-K workspace: `partial` needs gemm_tma_workspace_bytes() bytes (0: no split for this shape), `counters`
+// GEMM_TMA_MAX_TILE_COUNTERS zero-initialised ints that the kernel leaves zero again.
+constexpr int GEMM_TMA_MAX_TILE_COUNTERS = 4096;
+size_t gemm_tma_workspace_bytes(int kind, int T, int K, int F);
 cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __half *xh, const float *rowscale, int ldxh,
-                            int T, int K, int F, const float *bias, float *out, float *out2, int ldo, int *err_flag,
-                            cudaStream_t s, int *launches);
+                            int T, int K, int F, const float *bias, float *out, float *out2, int ldo, float *partial,
+                            int *counters, int *err_flag, cudaStream_t s, int *launches);
 
 int device_sm_count();
 
