@@ -208,8 +208,12 @@ def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
 
     m = LLAMA8B
     d, ffn, kv, vocab, L = m["d"], m["ffn"], m["kv"], m["vocab"], m["layers"]
-    if d % (256 * world) or ffn % (256 * world) or kv % world:
+    if d % (256 * world) or kv % world:
         return {"skipped": f"shapes do not divide over {world} ranks"}
+    # the FFN width is dealt out in 2048-value granules (the same ranges for gate/up rows and down's K), so that the
+    # Q6_K rows of every down shard stay 16-byte multiples; ranks may differ by one granule
+    f_lo, f_hi = tp.shard_range(ffn, world, rank, 2048)
+    ffn_r = f_hi - f_lo
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
     Q4, Q6 = KIND_Q4_K, KIND_Q6_K
@@ -220,8 +224,8 @@ def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
     for _ in range(L):
         w = {"q": (Q4, mk(Q4, d // world, d), d // world, d), "k": (Q4, mk(Q4, kv // world, d), kv // world, d),
              "v": (Q6, mk(Q6, kv // world, d), kv // world, d), "o": (Q4, mk(Q4, d, d // world), d, d // world),
-             "gate": (Q4, mk(Q4, ffn // world, d), ffn // world, d), "up": (Q4, mk(Q4, ffn // world, d), ffn // world, d),
-             "down": (Q6, mk(Q6, d, ffn // world), d, ffn // world)}
+             "gate": (Q4, mk(Q4, ffn_r, d), ffn_r, d), "up": (Q4, mk(Q4, ffn_r, d), ffn_r, d),
+             "down": (Q6, mk(Q6, d, ffn_r), d, ffn_r)}
         wbytes += sum(F * row_bytes(kind, K) for kind, _, F, K in w.values())
         layers.append(w)
     v_lo, v_hi = tp.shard_range(vocab, world, rank, 32)
@@ -229,14 +233,21 @@ def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
     wbytes += head[2] * row_bytes(Q6, d)
     x = torch.randn((T, d), device=dev, generator=gen)
     x_attn = torch.randn((T, d // world), device=dev, generator=gen)
-    x_ffn = torch.randn((T, ffn // world), device=dev, generator=gen)
+    x_ffn = torch.randn((T, max(ffn_r, 1)), device=dev, generator=gen)
     bufs = {n: torch.empty((T, F), dtype=torch.float32, device=dev)
-            for n, F in (("q", d // world), ("k", kv // world), ("v", kv // world), ("o", d), ("gate", ffn // world),
-                         ("up", ffn // world), ("down", d), ("head", v_hi - v_lo))}
+            for n, F in (("q", d // world), ("k", kv // world), ("v", kv // world), ("o", d), ("gate", max(ffn_r, 1)),
+                         ("up", max(ffn_r, 1)), ("down", d), ("head", v_hi - v_lo))}
 
     def row_parallel(entry, xin, out, how):
         kind, wt, F, K = entry
-        if world == 1:
+        if K == 0:  # more ranks than granules: this rank adds zeros
+            if how == "peer":
+                comm.staging((T, F)).zero_()
+                comm.allreduce(T * F, out)
+            else:
+                out.zero_()
+                dist.all_reduce(out)
+        elif world == 1:
             ctx.linear(kind, xin, wt, F, out=out)
         elif how == "peer":
             comm.linear_allreduce(kind, xin, wt, F, out=out)
@@ -250,7 +261,8 @@ def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
                 kind, wt, F, K = w[n]
                 ctx.linear(kind, x, wt, F, out=bufs[n])
             row_parallel(w["o"], x_attn, bufs["o"], how)
-            ctx.linear_dual(Q4, x, w["gate"][1], w["up"][1], w["gate"][2], out_a=bufs["gate"], out_b=bufs["up"])
+            if ffn_r > 0:
+                ctx.linear_dual(Q4, x, w["gate"][1], w["up"][1], w["gate"][2], out_a=bufs["gate"], out_b=bufs["up"])
             row_parallel(w["down"], x_ffn, bufs["down"], how)
         kind, wt, F, K = head
         ctx.linear(kind, x, wt, F, out=bufs["head"])

@@ -48,16 +48,29 @@ def shard_rows(blocks: np.ndarray, kind: int, F: int, K: int, world: int, rank: 
     return np.ascontiguousarray(blocks[lo:hi]).reshape(-1), lo, hi
 
 
-def shard_k(blocks: np.ndarray, kind: int, F: int, K: int, world: int, rank: int):
+def k_granule(kind: int, K: int) -> int:
+    """Granule (in values) for splitting K: the smallest run of blocks whose bytes are a multiple of 16, so that
+    every shard's rows stay 16-byte multiples and the TMA-fed matmul applies (Q4_K: 256, Q6_K: 2048, Q8_0: 256);
+    the block size when K is not a multiple of that."""
+    bv, bb = BLOCK_VALUES[kind], BLOCK_BYTES[kind]
+    blocks = 16 // np.gcd(bb, 16)
+    return int(bv * blocks) if K % (bv * blocks) == 0 else bv
+
+
+def shard_k(blocks: np.ndarray, kind: int, F: int, K: int, world: int, rank: int, granule: int | None = None):
     """Row-parallel shard: for every row the blocks covering K-range [k_lo, k_hi), packed as a contiguous
-    [F, k_hi - k_lo] matrix.  Returns (bytes, k_lo, k_hi).  K must be a whole number of blocks."""
+    [F, k_hi - k_lo] matrix.  Returns (bytes, k_lo, k_hi).  K must be a whole number of blocks; shards are whole
+    granules (default k_granule), so they may differ in size by one granule and the last ranks may get none."""
     bv, bb = BLOCK_VALUES[kind], BLOCK_BYTES[kind]
     if K % bv:
         raise ValueError(f"K={K} is not a whole number of {bv}-value blocks")
     nb = K // bv
+    g = granule or k_granule(kind, K)
+    if g % bv:
+        raise ValueError(f"granule {g} is not a whole number of {bv}-value blocks")
     blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(F, nb, bb)
-    b_lo, b_hi = shard_range(nb, world, rank)
-    return np.ascontiguousarray(blocks[:, b_lo:b_hi]).reshape(-1), b_lo * bv, b_hi * bv
+    k_lo, k_hi = shard_range(K, world, rank, g)
+    return np.ascontiguousarray(blocks[:, k_lo // bv:k_hi // bv]).reshape(-1), k_lo, k_hi
 
 
 def shard_experts(stacked: np.ndarray, E: int, world: int, rank: int):
@@ -117,16 +130,26 @@ class RowParallelLinear:
     """y = sum over ranks of x[:, k_lo:k_hi] @ W[:, k_lo:k_hi].T; x may be the full activation (sliced here)
     or already this rank's slice (the output of a column-parallel layer)."""
 
-    def __init__(self, backend, group: Group, kind: int, blocks: np.ndarray, F: int, K: int, comm=None):
+    def __init__(self, backend, group: Group, kind: int, blocks: np.ndarray, F: int, K: int, comm=None,
+                 granule: int | None = None):
         self.backend, self.group, self.kind, self.F, self.K = backend, group, kind, F, K
-        shard, self.k_lo, self.k_hi = shard_k(blocks, kind, F, K, group.world, group.rank)
-        self.weight = backend.upload(shard)
+        shard, self.k_lo, self.k_hi = shard_k(blocks, kind, F, K, group.world, group.rank, granule)
+        self.weight = backend.upload(shard) if self.k_hi > self.k_lo else None
         self.comm = comm  # runtime.PeerComm: the library's own all-reduce instead of torch.distributed
 
     def __call__(self, x):
         kw = self.k_hi - self.k_lo
+        peer = self.comm is not None and self.group.world > 1
+        if kw == 0:  # more ranks than granules: this rank contributes zeros
+            import torch
+
+            T = x.shape[0]
+            if peer:
+                self.comm.staging((T, self.F)).zero_()
+                return self.comm.allreduce(T * self.F, torch.empty((T, self.F), dtype=torch.float32, device=x.device))
+            return self.group.all_reduce_(torch.zeros((T, self.F), dtype=torch.float32, device=x.device))
         xs = x if x.shape[1] == kw else x[:, self.k_lo:self.k_hi]
-        if self.comm is not None and self.group.world > 1:
+        if peer:
             return self.comm.linear_allreduce(self.kind, xs, self.weight, self.F)
         y = self.backend.linear(self.kind, xs, self.weight, self.F)
         return self.group.all_reduce_(y)

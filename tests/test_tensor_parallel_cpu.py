@@ -36,15 +36,30 @@ def test_shards_are_the_right_bytes(kind):
     rows = W.reshape(F, rb)
     got = np.concatenate([tp.shard_rows(W, kind, F, K, world, r)[0] for r in range(world)])
     assert np.array_equal(got, W)  # row shards concatenate back to the matrix
+    bv = K // (rb // bb)
     for r in range(world):
-        shard, k_lo, k_hi = tp.shard_k(W, kind, F, K, world, r)
+        shard, k_lo, k_hi = tp.shard_k(W, kind, F, K, world, r, granule=bv)
         assert (k_lo, k_hi) == (r * K // world, (r + 1) * K // world)
         per_row = shard.reshape(F, -1)
         assert per_row.shape[1] == row_bytes(kind, k_hi - k_lo)
-        b_lo = k_lo // (K // (rb // bb))
+        b_lo = k_lo // bv
         assert np.array_equal(per_row, rows[:, b_lo * bb:b_lo * bb + per_row.shape[1]])
+    # default granule: every shard's rows are 16-byte multiples, shards cover K, sizes differ by at most one granule
+    g = tp.k_granule(kind, K)
+    spans = [tp.shard_k(W, kind, F, K, world, r)[1:] for r in range(world)]
+    assert spans[0][0] == 0 and spans[-1][1] == K and all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    assert all((hi - lo) % g == 0 for lo, hi in spans)
+    if kind != KIND_Q6_K:  # Q6_K needs K % 2048 == 0 for 16-byte shard rows (checked below on a wider matrix)
+        assert all(row_bytes(kind, hi - lo) % 16 == 0 for lo, hi in spans)
+    else:
+        W6 = random_blocks(kind, 2, 14336, rng)
+        spans6 = [tp.shard_k(W6, kind, 2, 14336, 8, r)[1:] for r in range(8)]
+        assert [hi - lo for lo, hi in spans6] == [2048] * 7 + [0]
+        assert all(row_bytes(kind, hi - lo) % 16 == 0 for lo, hi in spans6)
     with pytest.raises(ValueError):
         tp.shard_k(W, kind, F, 1000, world, 0)
+    assert tp.k_granule(KIND_Q6_K, 14336) == 2048 and tp.k_granule(KIND_Q6_K, 1024) == 256
+    assert tp.k_granule(KIND_Q4_K, 4096) == 256 and tp.k_granule(KIND_Q8_0, 4096) == 256
 
 
 class OracleBackend:
