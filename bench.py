@@ -238,10 +238,16 @@ def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
             for n, F in (("q", d // world), ("k", kv // world), ("v", kv // world), ("o", d), ("gate", max(ffn_r, 1)),
                          ("up", max(ffn_r, 1)), ("down", d), ("head", v_hi - v_lo))}
 
+    ffn_empty_somewhere = any(b == a for a, b in (tp.shard_range(ffn, world, r, 2048) for r in range(world)))
+
     def row_parallel(entry, xin, out, how):
         kind, wt, F, K = entry
-        if K == 0:  # more ranks than granules: this rank adds zeros
-            if how == "peer":
+        unfused = ffn_empty_somewhere and K != d // world  # the down projection when some rank has no share of it
+        if how in ("peer", "peer_fused") and unfused and K > 0:
+            ctx.linear(kind, xin, wt, F, out=comm.staging((T, F)))
+            comm.allreduce(T * F, out)
+        elif K == 0:  # more ranks than granules: this rank adds zeros
+            if how in ("peer", "peer_fused"):
                 comm.staging((T, F)).zero_()
                 comm.allreduce(T * F, out)
             else:
@@ -249,7 +255,7 @@ def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
                 dist.all_reduce(out)
         elif world == 1:
             ctx.linear(kind, xin, wt, F, out=out)
-        elif how == "peer":
+        elif how in ("peer", "peer_fused"):
             comm.linear_allreduce(kind, xin, wt, F, out=out)
         else:
             ctx.linear(kind, xin, wt, F, out=out)
@@ -270,8 +276,10 @@ def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
     result = {"T": T, "layers": L, "weight_bytes_per_gpu": wbytes, "tensor_parallel": world}
     stream = torch.cuda.Stream(dev)
     ctx.set_stream(stream.cuda_stream)
-    for how in (["single"] if world == 1 else ["peer", "nccl"]):
+    for how in (["single"] if world == 1 else ["peer", "peer_fused", "nccl"]):
         try:
+            if comm is not None:
+                comm.set_fused(how == "peer_fused")  # one kernel for matmul + all-reduce instead of two
             with torch.cuda.stream(stream):
                 for _ in range(2):
                     step(how)

@@ -200,7 +200,15 @@ int mcu_peer_allreduce(mcu_peer_comm_t *comm, size_t n_floats, float *out_dev);
 void mcu_peer_comm_destroy(mcu_peer_comm_t *comm);
 
 /* Row-parallel quantized linear: this rank's K-slice of the weights times its K-slice of the activations, written
- * straight into the staging buffer, then the all-reduce; out [T][F] contiguous. */
+ * straight into the staging buffer, then the all-reduce; out [T][F] contiguous.
+ * Two forms, chosen per communicator with mcu_peer_comm_set_fused (every rank must choose the same):
+ *   0 (default)  the matmul kernel followed by the all-reduce kernel on the same stream;
+ *   1            for 8 < T <= 64 and TMA-capable weights ONE kernel: the matmul's epilogue publishes each finished
+ *                tile (one flag per rank and tile), waits (bounded) for the same tile of the other ranks, pulls their
+ *                tiles with peer loads and adds in rank order; other shapes fall back to form 0.
+ * Measured on 2 GPUs at T = 64 the two-kernel form is the faster one (25 vs 32 us for a 4096x2048 shard), which
+ * is why it is the default. */
+int mcu_peer_comm_set_fused(mcu_peer_comm_t *comm, int enabled);
 int mcu_linear_allreduce(
     mcu_context_t *ctx, mcu_peer_comm_t *comm, int kind, const float *x_dev, size_t ldx, const void *w_dev, size_t T,
     size_t K, size_t F, float *out_dev

@@ -345,6 +345,33 @@ static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx,
     return MCU_SUCCESS;
 }
 
+extern "C++" {
+namespace mcu {
+int linear_fused_allreduce(mcu_context *ctx, int kind, const float *x, size_t ldx, const void *w, size_t T, size_t K,
+                           size_t F, float *out, const PeerFuse &fuse) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (int rc = validate_linear(kind, x, w, out, T, K, F, ldx, F)) return rc;
+    if (ctx->regime == MCU_REGIME_GEMV || ctx->regime == MCU_REGIME_GEMV_PLAIN || !gemm_tma_can_fuse(kind, (int)T, (int)F) ||
+        !gemm_tma_supported(kind, w, nullptr, (int)T, (int)K, (int)F) || act_half_fused_smem(kind, (int)K) > 48 * 1024)
+        return fail(MCU_ERROR_NOT_IMPLEMENTED, "shape or weights do not suit the fused matmul + all-reduce");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    const size_t bv = (size_t)block_values(kind);
+    const size_t kp = (K + bv - 1) / bv * bv;
+    if (int rc = ensure(ctx, ctx->act_half, T * kp * sizeof(__half))) return rc;
+    if (int rc = ensure(ctx, ctx->act_rowscale, T * sizeof(float))) return rc;
+    if (int rc = ensure(ctx, ctx->gemm_partial, gemm_tma_workspace_bytes(kind, (int)T, (int)K, (int)F))) return rc;
+    MCU_CUDA(launch_act_half_fused(kind, x, (int)ldx, (int)T, (int)K, true, (__half *)ctx->act_half.ptr,
+                                   (float *)ctx->act_rowscale.ptr, ctx->stream));
+    int launches = 0;
+    MCU_CUDA(launch_gemm_tma(kind, w, nullptr, (const __half *)ctx->act_half.ptr, (const float *)ctx->act_rowscale.ptr,
+                             (int)kp, (int)T, (int)K, (int)F, nullptr, out, nullptr, (int)F, (float *)ctx->gemm_partial.ptr,
+                             ctx->gemm_counters, ctx->dev_err, ctx->stream, &launches, &fuse));
+    count_launches(1 + launches);
+    return MCU_SUCCESS;
+}
+}  // namespace mcu
+}  // extern "C++"
+
 int mcu_quantize_activations(mcu_context_t *ctx, int weight_kind, const float *x_dev, size_t ldx, size_t T, size_t K,
                              int8_t *qs_dev, float *d_dev, int16_t *bsums_dev) {
     if (int rc = check_ctx(ctx)) return rc;

@@ -23,6 +23,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <type_traits>
 
@@ -82,6 +83,7 @@ struct GemmTmaParams {
     int splits, slabs_per_split;
     float *partial;
     int *counters;
+    PeerFuse fuse;  // world > 0: finished tiles go to all ranks' slots and are summed there (see kernels.h)
 #ifdef MCU_TRACE
     long long *trace;  // development aid: clock64 samples of CTA 0, [agent][step][point]
 #endif
@@ -376,7 +378,11 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const int ks0 = j0 * RC::KR;
     const int nsteps = min(p.ksteps, j1 * RC::KR) - ks0;
 
+    __shared__ uint32_t epoch_s;
+    __shared__ int last_s, peer_ok_s;
     if (threadIdx.x == 0) {
+        last_s = 1;
+        peer_ok_s = 1;
         for (int i = 0; i < S; ++i) {
             tm_mbar_init(a_full + 8u * i, GW + 1);  // a group's converter warps + the activation tile's expect_tx
             tm_mbar_init(st_empty + 8u * i, 1);
@@ -615,6 +621,9 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
         // ------------------------------ epilogue ------------------------------
         if (warp < 8) asm volatile("griddepcontrol.wait;" ::: "memory");
+        // the epoch of this collective: only now is the previous kernel of the stream (which may have been the
+        // previous collective) certain to have published its own
+        if (threadIdx.x == 0 && p.fuse.world > 0) epoch_s = *(volatile uint32_t *)p.fuse.ctr + 1u;
         if (threadIdx.x == 0) MCU_TRACE_POINT(3, 34, 0);
         if (ok && warp < 8) ok = tm_mbar_wait_relaxed(accum_bar, 0);
         if (threadIdx.x == 0) MCU_TRACE_POINT(3, 35, 0);
@@ -654,7 +663,15 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     for (int jj = 0; jj < 32; ++jj) sum[jj] += __uint_as_float(v[jj]);
                 }
                 if (f_ok) {
-                    if (p.splits == 1) {
+                    if (p.splits == 1 && p.fuse.world > 0) {
+                        // partial result of this rank: into its own peer-visible staging buffer; bias comes later
+                        float *mine = p.fuse.slots[p.fuse.rank];
+#pragma unroll
+                        for (int jj = 0; jj < 32; ++jj) {
+                            const int t = t0 + col0 + cb + jj;
+                            if (t < p.T) __stcg(mine + (size_t)t * p.F + f, sum[jj] * p.rowscale[t]);
+                        }
+                    } else if (p.splits == 1) {
 #pragma unroll
                         for (int jj = 0; jj < 32; ++jj) {
                             const int t = t0 + col0 + cb + jj;
@@ -676,7 +693,6 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     if (p.splits > 1) {
         // Last CTA of this tile to finish adds the partial tiles, in split order.
-        __shared__ int last_s;
         __threadfence();
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -717,6 +733,11 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                             }
                     }
                     const float rsc = p.rowscale[t];
+                    if (p.fuse.world > 0) {
+                        __stcg((float4 *)(p.fuse.slots[p.fuse.rank] + (size_t)t * p.F + f),
+                               make_float4(acc.x * rsc, acc.y * rsc, acc.z * rsc, acc.w * rsc));
+                        continue;
+                    }
                     float4 b = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                     if (p.bias != nullptr) b = *(const float4 *)(p.bias + f);
                     *(float4 *)(p.out + (size_t)t * p.ldo + f) =
@@ -730,6 +751,75 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     for (int z = 0; z < p.splits; ++z) acc += __ldcg(p.partial + ((size_t)z * p.T + t) * p.F + f);
                     p.out[(size_t)t * p.ldo + f] = acc * p.rowscale[t] + (p.bias != nullptr ? p.bias[f] : 0.0f);
                 }
+            }
+        }
+    }
+    if (p.fuse.world > 0 && last_s) {
+        // This CTA has written a finished tile of this rank's partial result to the rank's staging buffer.  Publish it
+        // (one flag per rank and tile), wait for the same tile of the other ranks, pull their tiles over NVLink with
+        // plain loads and add in rank order.  (last_s is CTA-uniform; with split K only the CTA that summed the
+        // splits gets here.)
+        const uint32_t epoch = epoch_s;
+        const int tile = blockIdx.x;
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x < p.fuse.world) {
+            if ((epoch & 1u) != p.fuse.parity_of_next) {
+                atomicExch(p.err, 22);  // host and device disagree about the epoch: skip the exchange
+                peer_ok_s = 0;
+            } else {
+                uint32_t *f = p.fuse.flags[threadIdx.x] + p.fuse.rank * PEER_FUSE_MAX_TILES + tile;
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+                const uint32_t *mine = p.fuse.flags[p.fuse.rank] + threadIdx.x * PEER_FUSE_MAX_TILES + tile;
+                unsigned long long t_start, t_now;
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_start));
+                for (;;) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+                    if ((int32_t)(v - epoch) >= 0) break;
+                    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_now));
+                    if (t_now - t_start > 2000000000ull) {  // a peer that never arrives: report, do not hang
+                        atomicExch(p.err, 21);
+                        peer_ok_s = 0;
+                        break;
+                    }
+                    __nanosleep(100);
+                }
+            }
+        }
+        __syncthreads();
+        if (peer_ok_s) {
+            const int t_here = min(BN, p.T - t0);
+            const int r4 = rows_here >> 2;  // fused launches use F % 4 == 0 and full-width tiles
+            for (int i = threadIdx.x; i < t_here * r4; i += blockDim.x) {
+                const int tt = i / r4, fr = (i - tt * r4) << 2;
+                const int t = t0 + tt, f = f0 + fr;
+                const size_t at = (size_t)t * p.F + f;
+                float4 v[PEER_FUSE_MAX_WORLD];
+#pragma unroll
+                for (int r = 0; r < PEER_FUSE_MAX_WORLD; ++r)
+                    if (r < p.fuse.world) v[r] = __ldcg((const float4 *)(p.fuse.slots[r] + at));  // all loads in flight
+                float4 acc = v[0];
+#pragma unroll
+                for (int r = 1; r < PEER_FUSE_MAX_WORLD; ++r)
+                    if (r < p.fuse.world) {
+                        acc.x += v[r].x;
+                        acc.y += v[r].y;
+                        acc.z += v[r].z;
+                        acc.w += v[r].w;
+                    }
+                float4 b = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (p.bias != nullptr) b = *(const float4 *)(p.bias + f);
+                *(float4 *)(p.out + (size_t)t * p.ldo + f) = make_float4(acc.x + b.x, acc.y + b.y, acc.z + b.z, acc.w + b.w);
+            }
+        }
+        // the last tile owner of the grid publishes the epoch for the next collective of this communicator
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(p.fuse.ctr + 1, 1u) == gridDim.x * gridDim.y - 1) {
+                p.fuse.ctr[1] = 0;
+                __threadfence();
+                *(volatile uint32_t *)p.fuse.ctr = epoch;
             }
         }
     }
@@ -805,6 +895,10 @@ static TmaPlan plan_tma(int kind, int T, int K, int F) {
     if (rows < 8) rows = 8;
     pl.rows_per_cta = rows;
     return pl;
+}
+
+bool gemm_tma_can_fuse(int kind, int T, int F) {
+    return kind_supported(kind) && T > GEMV_MAX_T && T <= 64 && F % 4 == 0 && (F + TM_BM - 1) / TM_BM <= PEER_FUSE_MAX_TILES;
 }
 
 size_t gemm_tma_workspace_bytes(int kind, int T, int K, int F) {
@@ -920,7 +1014,7 @@ extern "C" long long *mcu_debug_trace_buffer() { return g_trace_buf; }
 
 cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __half *xh, const float *rowscale, int ldxh,
                             int T, int K, int F, const float *bias, float *out, float *out2, int ldo, float *partial,
-                            int *counters, int *err_flag, cudaStream_t s, int *launches) {
+                            int *counters, int *err_flag, cudaStream_t s, int *launches, const PeerFuse *fuse) {
     GemmTmaParams p;
     p.bias = bias;
     p.rowscale = rowscale;
@@ -932,7 +1026,14 @@ cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __hal
     p.nb = (K + bv - 1) / bv;
     p.ksteps = (p.nb * bv + TM_BK - 1) / TM_BK;
     const long row_bytes = (long)p.nb * block_bytes(kind);
-    const TmaPlan pl = plan_tma(kind, T, K, F);
+    TmaPlan pl = plan_tma(kind, T, K, F);
+    memset(&p.fuse, 0, sizeof(p.fuse));
+    if (fuse != nullptr && fuse->world > 0) {
+        if (!gemm_tma_can_fuse(kind, T, F) || W2 != nullptr || ldo != F || (size_t)T * F > fuse->slot_floats)
+            return cudaErrorInvalidValue;
+        pl.rows_per_cta = TM_BM;  // tiles must be the same on every rank, whatever its share of K
+        p.fuse = *fuse;
+    }
     p.rows_per_cta = pl.rows_per_cta;
     p.splits = pl.splits;
     p.slabs_per_split = pl.slabs_per_split;

@@ -56,6 +56,21 @@ cudaError_t launch_gemm_tc(int kind, const void *W, const void *W2, const __half
                            int T, int K, int F, const float *bias, float *out, float *out2, int ldo, int *err_flag,
                            cudaStream_t s, int *launches);
 
+// Row-parallel matmul fused with its all-reduce over peer memory (gemm_tma, T <= 64, full 128-row tiles): every CTA
+// that holds a finished output tile stores it into this rank's peer-visible staging buffer, releases one flag per
+// rank and tile, waits (bounded) for the same tile of all ranks, pulls their tiles with plain peer loads and adds
+// them in rank order.  world == 0 means "not fused".
+constexpr int PEER_FUSE_MAX_WORLD = 8;
+constexpr int PEER_FUSE_MAX_TILES = 128;
+struct PeerFuse {
+    float *slots[PEER_FUSE_MAX_WORLD];     // rank d's staging buffer for this parity, as mapped in this process
+    uint32_t *flags[PEER_FUSE_MAX_WORLD];  // rank d's flags for this parity: [world][PEER_FUSE_MAX_TILES]
+    uint32_t *ctr;                         // this rank's {epoch of the last finished collective, ticket}
+    size_t slot_floats;                    // capacity of a staging buffer
+    int rank, world;
+    uint32_t parity_of_next;               // parity the host expects for the next epoch (consistency check)
+};
+
 // TMA-fed variant of the tensor-core matmul (packed weight slabs and activation tiles arrive by
 // cp.async.bulk.tensor); needs 16-byte aligned weights whose rows are 16-byte multiples.
 bool gemm_tma_supported(int kind, const void *W, const void *W2, int T, int K, int F);
@@ -65,7 +80,10 @@ constexpr int GEMM_TMA_MAX_TILE_COUNTERS = 4096;
 size_t gemm_tma_workspace_bytes(int kind, int T, int K, int F);
 cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __half *xh, const float *rowscale, int ldxh,
                             int T, int K, int F, const float *bias, float *out, float *out2, int ldo, float *partial,
-                            int *counters, int *err_flag, cudaStream_t s, int *launches);
+                            int *counters, int *err_flag, cudaStream_t s, int *launches,
+                            const PeerFuse *fuse = nullptr);
+// Can launch_gemm_tma fuse the all-reduce for this shape (same answer on every rank: it depends on T and F only)?
+bool gemm_tma_can_fuse(int kind, int T, int F);
 
 int device_sm_count();
 
@@ -80,4 +98,8 @@ struct mcu_context;
 namespace mcu {
 int context_device(const mcu_context *ctx);
 int *context_err_flag(mcu_context *ctx);
+// mcu_linear with the all-reduce fused into the matmul's epilogue; MCU_ERROR_NOT_IMPLEMENTED when the shape or the
+// weights do not allow it (the caller then runs the matmul and the all-reduce kernel separately).
+int linear_fused_allreduce(mcu_context *ctx, int kind, const float *x, size_t ldx, const void *w, size_t T, size_t K,
+                           size_t F, float *out, const PeerFuse &fuse);
 }  // namespace mcu

@@ -20,6 +20,7 @@
 #include "kernels.h"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -27,7 +28,12 @@ namespace mcu {
 
 constexpr int PEER_MAX_WORLD = 8;
 constexpr size_t PEER_CTR_OFFSET = 2 * PEER_MAX_WORLD * 128;  // epoch counter and CTA ticket of the owning rank
-constexpr size_t PEER_FLAG_BYTES = PEER_CTR_OFFSET + 128;     // flags [parity][rank], one 128-byte line each, + counters
+// flags of the fused matmul + all-reduce: [parity][source rank][tile] u32
+constexpr size_t PEER_FUSE_FLAG_OFFSET = 4096;
+constexpr size_t PEER_FUSE_FLAG_BYTES = 2 * (size_t)PEER_FUSE_MAX_WORLD * PEER_FUSE_MAX_TILES * sizeof(uint32_t);
+// all flags and counters; the staging buffers follow: [parity][capacity]
+constexpr size_t PEER_FLAG_BYTES = PEER_FUSE_FLAG_OFFSET + PEER_FUSE_FLAG_BYTES;
+static_assert(PEER_CTR_OFFSET + 128 <= PEER_FUSE_FLAG_OFFSET && PEER_FLAG_BYTES % 256 == 0, "layout");
 constexpr unsigned long long PEER_WAIT_NS = 2000000000ull;    // 2 s
 
 struct PeerParams {
@@ -130,6 +136,7 @@ struct mcu_peer_comm {
     uint8_t *local = nullptr;
     uint8_t *mapped[PEER_MAX_WORLD] = {};
     bool connected = false;
+    bool fused = false;  // mcu_linear_allreduce as one kernel (see mcu_peer_comm_set_fused)
     uint32_t epoch = 0;
 };
 
@@ -204,6 +211,12 @@ int mcu_peer_comm_connect(mcu_peer_comm_t *c, const void *all_handles) {
     return MCU_SUCCESS;
 }
 
+int mcu_peer_comm_set_fused(mcu_peer_comm_t *c, int enabled) {
+    if (c == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "null argument");
+    c->fused = enabled != 0;
+    return MCU_SUCCESS;
+}
+
 void *mcu_peer_comm_staging(mcu_peer_comm_t *c) {
     if (c == nullptr) return nullptr;
     // slot of the NEXT all-reduce
@@ -248,6 +261,32 @@ int mcu_linear_allreduce(mcu_context_t *ctx, mcu_peer_comm_t *c, int kind, const
     if (c == nullptr || c->ctx != ctx) return set_error(MCU_ERROR_INVALID_ARGUMENT, "communicator of another context");
     if (T * F * sizeof(float) > c->capacity)
         return set_error(MCU_ERROR_INVALID_ARGUMENT, "result larger than the communicator's staging buffer");
+    if (!c->connected) return set_error(MCU_ERROR_INVALID_OPERATION, "peer communicator is not connected");
+    if (c->fused && c->world > 1 && gemm_tma_can_fuse(kind, (int)T, (int)F) && ((uintptr_t)out_dev & 15) == 0) {
+        // one kernel: the matmul's epilogue publishes its tiles and pulls the peers' tiles
+        const uint32_t parity = (c->epoch + 1) & 1u;
+        PeerFuse f;
+        memset(&f, 0, sizeof(f));
+        const size_t slots_off = PEER_FLAG_BYTES + (size_t)parity * c->capacity;
+        const size_t flags_off = PEER_FUSE_FLAG_OFFSET + (size_t)parity * PEER_FUSE_MAX_WORLD * PEER_FUSE_MAX_TILES * sizeof(uint32_t);
+        for (int r = 0; r < c->world; ++r) {
+            f.slots[r] = (float *)(c->mapped[r] + slots_off);
+            f.flags[r] = (uint32_t *)(c->mapped[r] + flags_off);
+        }
+        f.ctr = (uint32_t *)(c->local + PEER_CTR_OFFSET);
+        f.slot_floats = c->capacity / sizeof(float);
+        f.rank = c->rank;
+        f.world = c->world;
+        f.parity_of_next = parity;
+        const int rc = linear_fused_allreduce(ctx, kind, x_dev, ldx, w_dev, T, K, F, out_dev, f);
+        if (rc == MCU_SUCCESS) {
+            c->epoch += 1;
+            return rc;
+        }
+        if (rc != MCU_ERROR_NOT_IMPLEMENTED) return rc;
+        // the weights do not suit the TMA matmul: two kernels below (all ranks take the same decision when their
+        // shards are cut in k_granule units)
+    }
     float *staging = (float *)mcu_peer_comm_staging(c);
     if (int rc = mcu_linear(ctx, kind, x_dev, ldx, w_dev, T, K, F, nullptr, staging, F)) return rc;
     return mcu_peer_allreduce(c, T * F, out_dev);

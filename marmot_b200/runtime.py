@@ -26,7 +26,7 @@ EXPORTS = (
     "mcu_quantize_activations", "mcu_linear", "mcu_linear_dual", "mcu_linear_host", "mcu_topk", "mcu_moe_experts",
     "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_peer_comm_create", "mcu_peer_comm_export",
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
-    "mcu_linear_allreduce",
+    "mcu_linear_allreduce", "mcu_peer_comm_set_fused",
 )
 
 
@@ -92,6 +92,7 @@ def load_library() -> C.CDLL:
     L.mcu_peer_comm_destroy.argtypes = [vp]
     L.mcu_peer_comm_destroy.restype = None
     L.mcu_linear_allreduce.argtypes = [vp, vp, i32, vp, sz, vp, sz, sz, sz, vp]
+    L.mcu_peer_comm_set_fused.argtypes = [vp, i32]
     _lib = L
     return L
 
@@ -248,6 +249,10 @@ class PeerComm:
         handles = exchange(bytes(mine.raw))
         assert len(handles) == world and all(len(x) == 64 for x in handles)
         ctx._check(ctx.lib.mcu_peer_comm_connect(h, C.create_string_buffer(b"".join(handles), 64 * world)))
+
+    def set_fused(self, enabled: bool):
+        """One-kernel form of linear_allreduce (matmul epilogue + all-reduce); every rank must choose the same."""
+        self.ctx._check(self.ctx.lib.mcu_peer_comm_set_fused(self.handle, 1 if enabled else 0))
 
     def staging(self, shape):
         """The buffer the next all-reduce sums, as a float32 torch tensor of `shape` (a view, no copy)."""

@@ -135,6 +135,11 @@ class RowParallelLinear:
         self.backend, self.group, self.kind, self.F, self.K = backend, group, kind, F, K
         shard, self.k_lo, self.k_hi = shard_k(blocks, kind, F, K, group.world, group.rank, granule)
         self.weight = backend.upload(shard) if self.k_hi > self.k_lo else None
+        g = granule or k_granule(kind, K)
+        spans = [shard_range(K, group.world, r, g) for r in range(group.world)]
+        # a rank without a share cannot take part in the fused matmul + all-reduce kernel: then every rank runs the
+        # matmul and the all-reduce kernel separately (all ranks must issue the same sequence of collectives)
+        self.any_empty = any(hi == lo for lo, hi in spans)
         self.comm = comm  # runtime.PeerComm: the library's own all-reduce instead of torch.distributed
 
     def __call__(self, x):
@@ -149,6 +154,12 @@ class RowParallelLinear:
                 return self.comm.allreduce(T * self.F, torch.empty((T, self.F), dtype=torch.float32, device=x.device))
             return self.group.all_reduce_(torch.zeros((T, self.F), dtype=torch.float32, device=x.device))
         xs = x if x.shape[1] == kw else x[:, self.k_lo:self.k_hi]
+        if peer and self.any_empty:
+            import torch
+
+            T = x.shape[0]
+            self.backend.linear(self.kind, xs, self.weight, self.F, out=self.comm.staging((T, self.F)))
+            return self.comm.allreduce(T * self.F, torch.empty((T, self.F), dtype=torch.float32, device=x.device))
         if peer:
             return self.comm.linear_allreduce(self.kind, xs, self.weight, self.F)
         y = self.backend.linear(self.kind, xs, self.weight, self.F)

@@ -62,7 +62,9 @@ def main() -> int:
             col = tp.ColumnParallelLinear(ctx, group, kind, W, F, K, granule=16)
             y = col(x, gather=True).cpu().numpy()
             check(f"col_{kind}_{T}", max_rel_err(y, want) <= tol, float(max_rel_err(y, want)))
-            for name, c in (("nccl", None), ("peer", comm)):
+            for name, c in (("nccl", None), ("peer", comm), ("fused", comm)):
+                if c is not None:
+                    c.set_fused(name == "fused")  # the one-kernel form applies to T = 48 here, else it falls back
                 row = tp.RowParallelLinear(ctx, group, kind, W, F, K, comm=c)
                 y = row(x)
                 ctx.synchronize()
@@ -70,8 +72,9 @@ def main() -> int:
                 check(f"row_{name}_{kind}_{T}", e <= tol, e)
                 gathered = [torch.empty_like(y) for _ in range(world)]
                 dist.all_gather(gathered, y)
-                if name == "peer":  # every rank holds the same bits
-                    check(f"row_peer_same_{kind}_{T}", all(torch.equal(g, gathered[0]) for g in gathered))
+                if name != "nccl":  # every rank holds the same bits
+                    check(f"row_{name}_same_{kind}_{T}", all(torch.equal(g, gathered[0]) for g in gathered))
+            comm.set_fused(False)
 
     T, H, FF, E, k = 40, 512, 1024, 8, 2
     gate = np.concatenate([random_blocks(KIND_Q4_K, FF, H, rng, d_sigma=0.0005) for _ in range(E)])
