@@ -42,7 +42,7 @@ constexpr int TM_W_PRODUCER = TM_B_PRODUCER + 1;
 constexpr int TM_THREADS = (TM_W_PRODUCER + 1) * 32;
 constexpr int TM_A_BYTES = TM_BM * TM_BK * 2;
 constexpr int TM_MAX_RING = 8;
-constexpr uint32_t TM_SPIN_LIMIT = 1u << 24;
+constexpr uint32_t TM_SPIN_LIMIT = 1u << 22;
 
 template <int KIND>
 struct RawCfg;
@@ -123,6 +123,7 @@ __device__ __forceinline__ bool tm_mbar_wait(uint32_t bar, uint32_t parity) {
             : "r"(bar), "r"(parity)
             : "memory");
         if (ok) return true;
+        __nanosleep(32);  // a failed try costs issue slots the dequantising warps need
     }
     return false;
 }
