@@ -324,6 +324,70 @@ def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
     return result
 
 
+def time_moe_c5(ctx, dev, rank: int, world: int, dist):
+    """BASELINE config 5: Mixtral-8x7B-shape expert FFN (8 experts, top-2, d=4096, FFN 14336, Q4_K), 2048 tokens,
+    softmax top-2 routing of N(0,1) logits; expert parallel over the ranks (contiguous expert ranges, router
+    replicated, outputs summed by the peer all-reduce).  Host-timed: the operator reads the group sizes back once per
+    call, so it cannot be captured in a CUDA graph."""
+    import torch
+
+    from marmot_b200 import tensor_parallel as tp
+    from marmot_b200.profile_case import synthetic_blocks_device
+
+    T, H, FF, E, k = 2048, 4096, 14336, 8, 2
+    if E % world:
+        return {"skipped": f"{E} experts do not divide over {world} ranks"}
+    e_lo, e_hi = tp.shard_range(E, world, rank)
+    n_local = e_hi - e_lo
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(77)  # the same router inputs on every rank
+    hidden = torch.randn((T, H), device=dev, generator=gen)
+    probs = torch.softmax(torch.randn((T, E), device=dev, generator=gen), dim=1)
+    vals, ids = ctx.topk(probs, k)
+    gen.manual_seed(1000 + rank)
+    gate = synthetic_blocks_device(torch, KIND_Q4_K, n_local * FF, H, dev, gen)
+    up = synthetic_blocks_device(torch, KIND_Q4_K, n_local * FF, H, dev, gen)
+    down = synthetic_blocks_device(torch, KIND_Q4_K, n_local * H, FF, dev, gen)
+    kinds = (KIND_Q4_K,) * 3
+    group = tp.Group(rank, world, dist if world > 1 else None)
+    comm = tp.make_peer_comm(ctx, group, T * H * 4) if world > 1 else None
+    out = torch.empty((T, H), dtype=torch.float32, device=dev)
+
+    def call():
+        if world == 1:
+            ctx.moe_experts_local(kinds, hidden, gate, up, down, ids, vals, FF, E, 0, E, out=out)
+        else:
+            ctx.moe_experts_local(kinds, hidden, gate, up, down, ids, vals, FF, E, e_lo, n_local,
+                                  out=comm.staging((T, H)))
+            comm.allreduce(T * H, out)
+
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    reps = 10
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        call()
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / reps
+    if world > 1:
+        t = torch.tensor([dt], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+        dist.barrier()
+        torch.cuda.synchronize()
+    if comm is not None:
+        comm.close()
+    flops = T * k * 3 * 2 * H * FF
+    peaks = json.loads((REPO / "MEASURED_PEAKS.json").read_text()) if (REPO / "MEASURED_PEAKS.json").exists() else {}
+    tf = flops / dt / 1e12
+    return {"tokens": T, "experts": E, "top_k": k, "expert_parallel": world, "ms_per_call": round(dt * 1e3, 3),
+            "TFLOPs_total": round(tf, 1), "frac_tensor_per_gpu": round(tf / world / float(peaks.get("bf16_tflops", 1590.0)), 3),
+            "timing": "host wall clock around 10 calls, max over ranks"}
+
+
 def run_reference_arm(args, rank: int):
     if rank != 0:
         return
@@ -467,9 +531,10 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
 
-    tp_section = None
+    tp_section = moe_section = None
     if not args.no_extra:
         tp_section = time_tp_decode_matmuls(ctx, dev, rank, world, dist)
+        moe_section = time_moe_c5(ctx, dev, rank, world, dist)
 
     if rank != 0:
         if world > 1:
@@ -505,6 +570,8 @@ def main():
     }
     if tp_section is not None:
         line["llama8b_decode_matmuls"] = tp_section
+    if moe_section is not None:
+        line["moe_mixtral_expert_ffn"] = moe_section
     if not args.no_extra and world == 1:
         line["other_regimes"] = time_other_regimes(ctx, dev)
     if not args.no_cpu_baseline:
