@@ -55,6 +55,13 @@ class Oracle:
         L.mo_moe_experts.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
                                      C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_size_t, C.c_int, C.c_float, C.c_int, C.c_void_p, C.c_int]
+        vp, sz, f32 = C.c_void_p, C.c_size_t, C.c_float
+        L.mo_rmsnorm_f32.argtypes = [vp, vp, vp, sz, sz, f32, f32, vp]
+        L.mo_rope_f32.argtypes = [vp, vp, sz, sz, f32, f32, C.c_int, vp]
+        L.mo_swiglu_f32.argtypes = [vp, vp, sz, vp]
+        L.mo_paged_attention_f32.argtypes = [vp, sz, vp, vp, vp, vp, vp, C.c_int, C.c_int, vp, sz, sz, sz, sz, sz, sz, sz, f32, vp]
+        L.mo_embedding_gather.argtypes = [C.c_int, vp, sz, vp, sz, vp]
+        L.mo_argmax_f32.argtypes = [vp, sz, sz, vp]
 
     def dequantize(self, kind: int, blocks: np.ndarray, n_values: int) -> np.ndarray:
         blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
@@ -119,6 +126,66 @@ class Oracle:
         return out
 
 
+    # ---- decoder operators (marmot_oracle_decoder.c) ----
+    def rmsnorm(self, x, weight, eps: float, residual=None, weight_offset: float = 0.0) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        rows, n = x.shape
+        out = np.empty_like(x)
+        res = None if residual is None else np.ascontiguousarray(residual, dtype=np.float32)
+        w = None if weight is None else np.ascontiguousarray(weight, dtype=np.float32)
+        self.lib.mo_rmsnorm_f32(_p(x), _p(res) if res is not None else None, _p(w) if w is not None else None, rows, n,
+                                C.c_float(eps), C.c_float(weight_offset), _p(out))
+        return out
+
+    def rope(self, x, positions, theta: float = 10000.0, freq_scale: float = 1.0, neox: bool = False) -> np.ndarray:
+        """x [rows, dim], one position per row."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        pos = np.ascontiguousarray(positions, dtype=np.int32)
+        out = np.empty_like(x)
+        self.lib.mo_rope_f32(_p(x), _p(pos), x.shape[0], x.shape[1], C.c_float(theta), C.c_float(freq_scale),
+                             1 if neox else 0, _p(out))
+        return out
+
+    def swiglu(self, a, b) -> np.ndarray:
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        b = np.ascontiguousarray(b, dtype=np.float32)
+        out = np.empty_like(a)
+        self.lib.mo_swiglu_f32(_p(a), _p(b), a.size, _p(out))
+        return out
+
+    def paged_attention(self, token_meta, q, k_new, v_new, kv_k, kv_v, block_table, layer: int, block_size: int,
+                        scale: float, kv_truncate: bool = False) -> np.ndarray:
+        """q [T, Hq, hd], k_new/v_new [T, Hkv, hd], pool [blocks, layers, Hkv, block_size, hd] f32 or f16 (updated in
+        place), token_meta [T, 4] u32, block_table [seqs, max_blocks] u32.  kv_truncate: write an f16 pool with the
+        truncating conversion of the reference's scalar build instead of round-to-nearest-even."""
+        meta = np.ascontiguousarray(token_meta, dtype=np.uint32)
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        k_new = np.ascontiguousarray(k_new, dtype=np.float32)
+        v_new = np.ascontiguousarray(v_new, dtype=np.float32)
+        table = np.ascontiguousarray(block_table, dtype=np.uint32)
+        assert kv_k.flags.c_contiguous and kv_v.flags.c_contiguous and kv_k.dtype in (np.float32, np.float16)
+        T, hq, hd = q.shape
+        out = np.empty_like(q)
+        rc = self.lib.mo_paged_attention_f32(
+            _p(meta), T, _p(q), _p(k_new), _p(v_new), _p(kv_k), _p(kv_v), 1 if kv_k.dtype == np.float16 else 0,
+            1 if kv_truncate else 0, _p(table), table.shape[1], kv_k.shape[1], layer, hq, k_new.shape[1], hd, block_size, C.c_float(scale), _p(out))
+        assert rc == 0, rc
+        return out
+
+    def embedding_gather(self, kind: int, table: np.ndarray, dim: int, ids) -> np.ndarray:
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        table = np.ascontiguousarray(table, dtype=np.uint8)
+        out = np.empty((len(ids), dim), dtype=np.float32)
+        assert self.lib.mo_embedding_gather(kind, _p(table), dim, _p(ids), len(ids), _p(out)) == 0
+        return out
+
+    def argmax(self, x) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty(x.shape[0], dtype=np.int32)
+        self.lib.mo_argmax_f32(_p(x), x.shape[0], x.shape[1], _p(out))
+        return out
+
+
 # ---------------------------------------------------------------------------
 # The reference library itself
 # ---------------------------------------------------------------------------
@@ -157,6 +224,34 @@ class _TopkDesc(C.Structure):
                 ("axis", C.c_int32), ("k", C.c_uint32)]
 
 
+class _RmsnormDesc(C.Structure):
+    """struct marmot_rmsnorm_desc, include/marmot/ops_types.h:181-187."""
+    _fields_ = [("x", C.POINTER(_Tensor)), ("residual", C.POINTER(_Tensor)), ("weight", C.POINTER(_Tensor)),
+                ("out", C.POINTER(_Tensor)), ("eps", C.c_float)]
+
+
+class _RopeParams(C.Structure):
+    """struct marmot_rope_params, include/marmot/ops_types.h:98-112."""
+    _fields_ = [("positions", C.POINTER(_Tensor)), ("scaling_type", C.c_int), ("rope_type", C.c_int),
+                ("theta", C.c_float), ("freq_scale", C.c_float), ("ext_factor", C.c_float), ("attn_factor", C.c_float),
+                ("beta_fast", C.c_float), ("beta_slow", C.c_float), ("orig_ctx_len", C.c_uint32),
+                ("head_dim", C.c_uint32), ("apply_to_q", C.c_bool), ("apply_to_k", C.c_bool)]
+
+
+class _PagedAttentionDesc(C.Structure):
+    """marmot_paged_attention_desc_t, include/marmot/ops/paged_attention.h:32-56."""
+    _fields_ = [("struct_size", C.c_uint32), ("struct_version", C.c_uint32), ("flags", C.c_uint64),
+                ("token_count", C.c_uint32), ("layer_idx", C.c_uint32), ("num_q_heads", C.c_uint32),
+                ("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("block_size", C.c_uint32),
+                ("scale", C.c_float), ("token_meta", C.POINTER(_Tensor)), ("q", C.POINTER(_Tensor)),
+                ("k_new", C.POINTER(_Tensor)), ("v_new", C.POINTER(_Tensor)), ("kv_k", C.POINTER(_Tensor)),
+                ("kv_v", C.POINTER(_Tensor)), ("block_table", C.POINTER(_Tensor)), ("out", C.POINTER(_Tensor)),
+                ("pnext", C.c_void_p), ("reserved", C.c_uint64 * 4)]
+
+
+DT_U32 = 8
+
+
 class Reference:
     """The reference CPU backend, driven through its public C API."""
 
@@ -185,6 +280,10 @@ class Reference:
         for n in ("q4_k", "q6_k", "q8_0"):
             getattr(L, f"marmot_quantize_{n}").argtypes = [C.c_void_p, TP, TP]
             getattr(L, f"marmot_dequantize_{n}").argtypes = [C.c_void_p, TP, TP]
+        L.marmot_rmsnorm.argtypes = [C.c_void_p, C.POINTER(_RmsnormDesc)]
+        L.marmot_rope.argtypes = [C.c_void_p, TP, C.POINTER(_RopeParams), TP]
+        L.marmot_swiglu.argtypes = [C.c_void_p, TP, TP, TP]
+        L.marmot_paged_attention.argtypes = [C.c_void_p, C.POINTER(_PagedAttentionDesc)]
         self.ctx = L.marmot_init(0)
         if not self.ctx:
             raise RuntimeError("marmot_init(MARMOT_BACKEND_CPU) failed")
@@ -268,6 +367,68 @@ class Reference:
         finally:
             self.lib.marmot_tensor_destroy(to)
             self.lib.marmot_tensor_destroy(tq)
+
+    # ---- decoder operators ----
+    def rmsnorm(self, x, weight, eps: float, residual=None) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        tx, to = self._tensor(x.shape, DT_F32, x), self._tensor(x.shape, DT_F32)
+        tw = self._tensor((x.shape[1],), DT_F32, np.ascontiguousarray(weight, dtype=np.float32)) if weight is not None else None
+        tr = self._tensor(x.shape, DT_F32, np.ascontiguousarray(residual, dtype=np.float32)) if residual is not None else None
+        try:
+            desc = _RmsnormDesc(tx, tr, tw, to, eps)
+            self._check(self.lib.marmot_rmsnorm(self.ctx, C.byref(desc)), "marmot_rmsnorm")
+            return self._read(to, x.shape, np.float32)
+        finally:
+            for t in (to, tx, tw, tr):
+                if t is not None:
+                    self.lib.marmot_tensor_destroy(t)
+
+    def rope(self, x, positions, theta: float = 10000.0, freq_scale: float = 1.0, neox: bool = False) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        pos = np.ascontiguousarray(positions, dtype=np.int32)
+        tx, to = self._tensor(x.shape, DT_F32, x), self._tensor(x.shape, DT_F32)
+        tp = self._tensor(pos.shape, DT_I32, pos)
+        try:
+            params = _RopeParams(tp, 1 if freq_scale != 1.0 else 0, 1 if neox else 0, theta, freq_scale, 0.0, 1.0, 32.0,
+                                 1.0, 0, x.shape[1], True, True)
+            self._check(self.lib.marmot_rope(self.ctx, tx, C.byref(params), to), "marmot_rope")
+            return self._read(to, x.shape, np.float32)
+        finally:
+            for t in (tp, to, tx):
+                self.lib.marmot_tensor_destroy(t)
+
+    def swiglu(self, a, b) -> np.ndarray:
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        b = np.ascontiguousarray(b, dtype=np.float32)
+        ta, tb, to = self._tensor(a.shape, DT_F32, a), self._tensor(a.shape, DT_F32, b), self._tensor(a.shape, DT_F32)
+        try:
+            self._check(self.lib.marmot_swiglu(self.ctx, ta, tb, to), "marmot_swiglu")
+            return self._read(to, a.shape, np.float32)
+        finally:
+            for t in (to, tb, ta):
+                self.lib.marmot_tensor_destroy(t)
+
+    def paged_attention(self, token_meta, q, k_new, v_new, kv_k, kv_v, block_table, layer: int, block_size: int,
+                        scale: float):
+        """Returns (out, kv_k, kv_v) with the pools after the call."""
+        meta = np.ascontiguousarray(token_meta, dtype=np.uint32)
+        table = np.ascontiguousarray(block_table, dtype=np.uint32)
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        kv_dt = DT_F16 if kv_k.dtype == np.float16 else DT_F32
+        T, hq, hd = q.shape
+        tm, tt = self._tensor(meta.shape, DT_U32, meta), self._tensor(table.shape, DT_U32, table)
+        tq, tk, tv = self._tensor(q.shape, DT_F32, q), self._tensor(k_new.shape, DT_F32, k_new), self._tensor(v_new.shape, DT_F32, v_new)
+        pk, pv = self._tensor(kv_k.shape, kv_dt, kv_k), self._tensor(kv_v.shape, kv_dt, kv_v)
+        to = self._tensor(q.shape, DT_F32)
+        try:
+            desc = _PagedAttentionDesc(C.sizeof(_PagedAttentionDesc), 1, 0, T, layer, hq, k_new.shape[1], hd, block_size,
+                                       scale, tm, tq, tk, tv, pk, pv, tt, to, None, (C.c_uint64 * 4)())
+            self._check(self.lib.marmot_paged_attention(self.ctx, C.byref(desc)), "marmot_paged_attention")
+            return (self._read(to, q.shape, np.float32), self._read(pk, kv_k.shape, kv_k.dtype),
+                    self._read(pv, kv_v.shape, kv_v.dtype))
+        finally:
+            for t in (to, pv, pk, tv, tk, tq, tt, tm):
+                self.lib.marmot_tensor_destroy(t)
 
     def _expert_tensor(self, kind: int, blocks: np.ndarray, rows: int, cols: int, experts: int):
         """3-D expert weight in GGUF ne order {cols, rows, experts}, as tests/backend/test_backend_moe.c:77-124."""

@@ -12,17 +12,18 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 SRC = HERE / "marmot_oracle.c"
+SRC_DECODER = HERE / "marmot_oracle_decoder.c"
 OUT = HERE / "libmarmot_oracle.so"
 
 
 def build(force: bool = False) -> Path:
     if not force and OUT.exists() and OUT.stat().st_mtime >= max(
-        SRC.stat().st_mtime, (HERE / "marmot_oracle.h").stat().st_mtime
+        SRC.stat().st_mtime, SRC_DECODER.stat().st_mtime, (HERE / "marmot_oracle.h").stat().st_mtime
     ):
         return OUT
     cmd = [
         "gcc", "-std=c11", "-O2", "-march=x86-64-v3", "-ffp-contract=off", "-fopenmp", "-fPIC", "-shared",
-        "-Wall", "-Wextra", "-o", str(OUT), str(SRC), "-lm",
+        "-Wall", "-Wextra", "-o", str(OUT), str(SRC), str(SRC_DECODER), "-lm",
     ]
     subprocess.run(cmd, check=True)
     return OUT

@@ -81,6 +81,19 @@ int mo_moe_experts(
     int ffn_type, float weights_scale, int policy, float *out, int n_threads
 );
 
+/* ---- decoder operators around the matmuls (marmot_oracle_decoder.c) ---- */
+void mo_rmsnorm_f32(const float *x, const float *residual, const float *weight, size_t rows, size_t n, float eps,
+                    float weight_offset, float *out);
+void mo_rope_f32(const float *x, const int32_t *positions, size_t rows, size_t dim, float theta, float freq_scale,
+                 int neox, float *out);
+void mo_swiglu_f32(const float *a, const float *b, size_t n, float *out);
+int mo_paged_attention_f32(const uint32_t *token_meta, size_t T, const float *q, const float *k_new, const float *v_new,
+                           void *kv_k, void *kv_v, int kv_is_half, int kv_truncate, const uint32_t *block_table,
+                           size_t max_blocks_per_seq, size_t n_layers, size_t layer, size_t n_q_heads,
+                           size_t n_kv_heads, size_t head_dim, size_t block_size, float scale, float *out);
+int mo_embedding_gather(int kind, const void *table, size_t dim, const int32_t *ids, size_t T, float *out);
+void mo_argmax_f32(const float *x, size_t rows, size_t n, int32_t *out);
+
 #ifdef __cplusplus
 }
 #endif

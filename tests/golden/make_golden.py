@@ -9,6 +9,7 @@ Two fixture files are produced next to this script:
   tests/backend/golden_vec_dot_llama.h and the quantizer blocks + dequantised
   values of tests/backend/golden_quant_llama.h.  They are read by compiling a
   small dumper against those headers (the arrays are C initialisers).
+* ``decoder_cases.npz`` - RMSNorm / RoPE / SwiGLU / paged attention of the reference CPU backend on seeded inputs
 * ``ref_cases.npz`` - seeded inputs pushed through the reference CPU backend
   itself (oracle/_ref/libmarmot_ref.so): quantized weights, dequantised values,
   matmul and MoE outputs at small ragged shapes.
@@ -136,11 +137,43 @@ def make_ref_cases() -> dict[str, np.ndarray]:
     return out
 
 
+def make_decoder_cases() -> dict[str, np.ndarray]:
+    """RMSNorm / RoPE / SwiGLU / paged-attention outputs of the reference CPU backend (one thread: see
+    tests/test_oracle_decoder.py) on seeded inputs; the attention cases are the ones the tests rebuild."""
+    from oracle.bindings import Reference
+    from tests.test_oracle_decoder import ATTENTION_CASES, attention_case
+
+    ref = Reference(threads=1)
+    rng = np.random.default_rng(99)
+    out: dict[str, np.ndarray] = {}
+    x = rng.normal(0, 2, (5, 256)).astype(np.float32)
+    w = rng.normal(1, 0.1, 256).astype(np.float32)
+    res = rng.normal(0, 1, (5, 256)).astype(np.float32)
+    out.update(rms_x=x, rms_w=w, rms_res=res, rms_out=ref.rmsnorm(x, w, 1e-5, residual=res))
+    xr = rng.normal(0, 1, (6, 128)).astype(np.float32)
+    pos = np.array([0, 1, 31, 255, 1000, 4095], dtype=np.int32)
+    out.update(rope_x=xr, rope_pos=pos, rope_out=ref.rope(xr, pos, 500000.0))
+    a, b = rng.normal(0, 3, 512).astype(np.float32), rng.normal(0, 1, 512).astype(np.float32)
+    out.update(glu_a=a, glu_b=b, glu_out=ref.swiglu(a, b))
+    for name in sorted(ATTENTION_CASES):
+        case = attention_case(np.random.default_rng(sum(map(ord, name))), **ATTENTION_CASES[name])
+        o, kk, vv = ref.paged_attention(case["meta"], case["q"], case["k_new"], case["v_new"], case["kv_k"].copy(),
+                                        case["kv_v"].copy(), case["table"], case["layer"], case["block_size"],
+                                        case["scale"])
+        for k, v in case.items():
+            out[f"{name}.{k}"] = np.asarray(v)
+        out[f"{name}.out"] = o
+        out[f"{name}.kv_k_after"] = kk
+    ref.close()
+    return out
+
+
 def main() -> None:
     ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(os.environ.get("MARMOT_REFERENCE_ROOT", "/root/reference"))
     np.savez_compressed(HERE / "llama_goldens.npz", **dump_reference_goldens(ref_root))
     np.savez_compressed(HERE / "ref_cases.npz", **make_ref_cases())
-    for f in ("llama_goldens.npz", "ref_cases.npz"):
+    np.savez_compressed(HERE / "decoder_cases.npz", **make_decoder_cases())
+    for f in ("llama_goldens.npz", "ref_cases.npz", "decoder_cases.npz"):
         print(f, (HERE / f).stat().st_size, "bytes")
 
 
