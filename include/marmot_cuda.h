@@ -167,6 +167,48 @@ int mcu_moe_experts(
     float *out_dev
 );
 
+/* ---- decoder operators around the matmuls (f32 activations), the callers of the hot path in a decode step:
+ *      marmot_rmsnorm (src/backends/cpu/ops/normalization/scalar/normalization_scalar.c:780-833),
+ *      marmot_rope (src/backends/cpu/ops/rope/rope_dispatch.c:144-382; no YaRN / long-rope scaling),
+ *      marmot_swiglu / marmot_add (src/backends/cpu/ops/elementwise/scalar/elementwise_f32_scalar.c),
+ *      marmot_paged_attention (include/marmot/ops/paged_attention.h:32-56,
+ *      src/backends/cpu/ops/paged_attention/paged_attention_ref.c:599-1082),
+ *      marmot_embedding_gather on a block-quantized table, marmot_reduce_argmax over the last axis. ---- */
+enum { MCU_ROPE_NORM = 0, MCU_ROPE_NEOX = 1 }; /* marmot_rope_type_t, include/marmot/types.h:263-267 */
+enum { MCU_KV_F32 = 0, MCU_KV_F16 = 1 };       /* dtype of the paged KV pool */
+
+/* out = (x [+ residual]) * rsqrt(mean((x [+ residual])^2) + eps) * (weight + weight_offset); residual and weight may
+ * be NULL; rows x n contiguous. */
+int mcu_rmsnorm(
+    mcu_context_t *ctx, const float *x_dev, const float *residual_dev, const float *weight_dev, size_t rows, size_t n,
+    float eps, float weight_offset, float *out_dev
+);
+/* x [T][n_heads][head_dim] with row stride ldx (floats), one int32 position per token; pairs (2i, 2i+1) for
+ * MCU_ROPE_NORM, (i, i + head_dim/2) for MCU_ROPE_NEOX; angle = pos * theta^(-2i/head_dim) * freq_scale. */
+int mcu_rope(
+    mcu_context_t *ctx, const float *x_dev, size_t ldx, const int32_t *positions_dev, size_t T, size_t n_heads,
+    size_t head_dim, float theta, float freq_scale, int rope_type, float *out_dev, size_t ldo
+);
+int mcu_swiglu(mcu_context_t *ctx, const float *gate_dev, const float *up_dev, size_t n, float *out_dev);
+int mcu_add(mcu_context_t *ctx, const float *a_dev, const float *b_dev, size_t n, float *out_dev);
+int mcu_argmax(mcu_context_t *ctx, const float *x_dev, size_t rows, size_t n, int32_t *out_dev);
+/* out [T][dim] = dequantised rows ids[t] of a quantized [rows][dim] table (bit-exact with mcu_dequantize). */
+int mcu_embedding_gather(
+    mcu_context_t *ctx, int kind, const void *table_dev, size_t dim, const int32_t *ids_dev, size_t T, float *out_dev
+);
+/* Paged attention for T tokens (decode steps and prefill chunks alike).  token_meta [T][4] u32 = {seq_slot, pos, kv_slot,
+ * flags}; q/out [T][n_q_heads][head_dim], k_new/v_new [T][n_kv_heads][head_dim], contiguous; the KV pool
+ * [blocks][n_layers][n_kv_heads][block_size][head_dim] (f32 or f16) first receives the new rows at kv_slot
+ * (block = kv_slot / block_size; f16 pools round to nearest even like the reference's NEON / F16C conversions), then
+ * every token attends to positions 0..pos of its sequence through block_table [seqs][max_blocks_per_seq]
+ * (0xFFFFFFFF = no block).  head_dim 64 or 128. */
+int mcu_paged_attention(
+    mcu_context_t *ctx, const uint32_t *token_meta_dev, size_t T, const float *q_dev, const float *k_new_dev,
+    const float *v_new_dev, void *kv_k_dev, void *kv_v_dev, int kv_dtype, const uint32_t *block_table_dev,
+    size_t max_blocks_per_seq, size_t n_layers, size_t layer, size_t n_q_heads, size_t n_kv_heads, size_t head_dim,
+    size_t block_size, float scale, float *out_dev
+);
+
 /* ---- tensor / expert parallelism over the GPUs of one box.  No reference counterpart: the reference runs on
  *      one device (include/marmot/device.h:72-80) and only reserves placeholders for sharding
  *      (include/marmot/graph/kernel_selection.h:18-23). ---- */

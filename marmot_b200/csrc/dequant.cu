@@ -10,12 +10,19 @@ namespace mcu {
 
 // Each thread produces four consecutive values (one float4 when the tail allows).
 __global__ void __launch_bounds__(256)
-dequantize_q4_k_kernel(const uint8_t *__restrict__ blocks, size_t n_values, float *__restrict__ out) {
+dequantize_q4_k_kernel(const uint8_t *__restrict__ blocks, size_t n_values, float *__restrict__ out,
+                       const int32_t *__restrict__ row_ids, size_t row_values, size_t row_bytes) {
     const size_t q4 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // index of the group of 4 values
     const size_t e0 = q4 * 4;
     if (e0 >= n_values) return;
-    const size_t blk = e0 / QK_K;
-    const int e = (int)(e0 - blk * QK_K);
+    size_t er = e0;  // value index inside the source row (gather) or inside the whole buffer
+    if (row_ids != nullptr) {
+        const size_t t = e0 / row_values;
+        er = e0 - t * row_values;
+        blocks += (size_t)row_ids[t] * row_bytes;
+    }
+    const size_t blk = er / QK_K;
+    const int e = (int)(er - blk * QK_K);
     const uint8_t *b = blocks + blk * Q4_K_BYTES;
     const float d = half_bits_to_float(*(const uint16_t *)b);
     const float dmin = half_bits_to_float(*(const uint16_t *)(b + 2));
@@ -37,12 +44,19 @@ dequantize_q4_k_kernel(const uint8_t *__restrict__ blocks, size_t n_values, floa
 }
 
 __global__ void __launch_bounds__(256)
-dequantize_q6_k_kernel(const uint8_t *__restrict__ blocks, size_t n_values, float *__restrict__ out) {
+dequantize_q6_k_kernel(const uint8_t *__restrict__ blocks, size_t n_values, float *__restrict__ out,
+                       const int32_t *__restrict__ row_ids, size_t row_values, size_t row_bytes) {
     const size_t q4 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t e0 = q4 * 4;
     if (e0 >= n_values) return;
-    const size_t blk = e0 / QK_K;
-    const int e = (int)(e0 - blk * QK_K);
+    size_t er = e0;
+    if (row_ids != nullptr) {
+        const size_t t = e0 / row_values;
+        er = e0 - t * row_values;
+        blocks += (size_t)row_ids[t] * row_bytes;
+    }
+    const size_t blk = er / QK_K;
+    const int e = (int)(er - blk * QK_K);
     const uint8_t *b = blocks + blk * Q6_K_BYTES;
     const float d = half_bits_to_float((uint16_t)(b[208] | (b[209] << 8)));
     const int n = e >> 7, c = (e >> 5) & 3, l = e & 31;  // value = 128n + 32c + l
@@ -60,12 +74,19 @@ dequantize_q6_k_kernel(const uint8_t *__restrict__ blocks, size_t n_values, floa
 }
 
 __global__ void __launch_bounds__(256)
-dequantize_q8_0_kernel(const uint8_t *__restrict__ blocks, size_t n_values, float *__restrict__ out) {
+dequantize_q8_0_kernel(const uint8_t *__restrict__ blocks, size_t n_values, float *__restrict__ out,
+                       const int32_t *__restrict__ row_ids, size_t row_values, size_t row_bytes) {
     const size_t q4 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t e0 = q4 * 4;
     if (e0 >= n_values) return;
-    const size_t blk = e0 / Q8_0_VALUES;
-    const int e = (int)(e0 - blk * Q8_0_VALUES);
+    size_t er = e0;
+    if (row_ids != nullptr) {
+        const size_t t = e0 / row_values;
+        er = e0 - t * row_values;
+        blocks += (size_t)row_ids[t] * row_bytes;
+    }
+    const size_t blk = er / Q8_0_VALUES;
+    const int e = (int)(er - blk * Q8_0_VALUES);
     const uint8_t *b = blocks + blk * Q8_0_BYTES;
     const float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
 #pragma unroll
@@ -73,16 +94,28 @@ dequantize_q8_0_kernel(const uint8_t *__restrict__ blocks, size_t n_values, floa
         if (e0 + i < n_values) out[e0 + i] = __fmul_rn((float)(int8_t)b[2 + e + i], d);
 }
 
-cudaError_t launch_dequantize(int kind, const void *blocks, size_t n_values, float *out, cudaStream_t s) {
+static cudaError_t launch_dequant_any(int kind, const void *blocks, size_t n_values, float *out, const int32_t *row_ids,
+                                      size_t row_values, size_t row_bytes, cudaStream_t s) {
     if (n_values == 0) return cudaSuccess;
     const size_t groups = (n_values + 3) / 4;
     const unsigned grid = (unsigned)((groups + 255) / 256);
     const uint8_t *b = (const uint8_t *)blocks;
-    if (kind == KIND_Q4_K) dequantize_q4_k_kernel<<<grid, 256, 0, s>>>(b, n_values, out);
-    else if (kind == KIND_Q6_K) dequantize_q6_k_kernel<<<grid, 256, 0, s>>>(b, n_values, out);
-    else if (kind == KIND_Q8_0) dequantize_q8_0_kernel<<<grid, 256, 0, s>>>(b, n_values, out);
+    if (kind == KIND_Q4_K) dequantize_q4_k_kernel<<<grid, 256, 0, s>>>(b, n_values, out, row_ids, row_values, row_bytes);
+    else if (kind == KIND_Q6_K) dequantize_q6_k_kernel<<<grid, 256, 0, s>>>(b, n_values, out, row_ids, row_values, row_bytes);
+    else if (kind == KIND_Q8_0) dequantize_q8_0_kernel<<<grid, 256, 0, s>>>(b, n_values, out, row_ids, row_values, row_bytes);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
+}
+
+cudaError_t launch_dequantize(int kind, const void *blocks, size_t n_values, float *out, cudaStream_t s) {
+    return launch_dequant_any(kind, blocks, n_values, out, nullptr, 0, 0, s);
+}
+
+// out[t][:] = dequantised row row_ids[t] of a [rows][dim] table; dim a multiple of 4.
+cudaError_t launch_dequantize_rows(int kind, const void *table, size_t dim, size_t row_bytes, const int32_t *row_ids,
+                                   size_t n_rows, float *out, cudaStream_t s) {
+    if (dim % 4) return cudaErrorInvalidValue;
+    return launch_dequant_any(kind, table, n_rows * dim, out, row_ids, dim, row_bytes, s);
 }
 
 }  // namespace mcu

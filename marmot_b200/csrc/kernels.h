@@ -34,6 +34,9 @@ cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int 
 
 // blocks -> f32 (bit-exact with the reference dequantizers)
 cudaError_t launch_dequantize(int kind, const void *blocks, size_t n_values, float *out, cudaStream_t s);
+// rows row_ids[0..n_rows) of a quantized [rows][dim] table -> f32 [n_rows][dim] (embedding gather)
+cudaError_t launch_dequantize_rows(int kind, const void *table, size_t dim, size_t row_bytes, const int32_t *row_ids,
+                                   size_t n_rows, float *out, cudaStream_t s);
 
 // Decode-regime matmul, T <= GEMV_MAX_T tokens: out[t*ldo + f] = dot(W[f], act[t]) (+ bias[f]).
 // W2/out2 non-null computes a second weight matrix of the same shape from the same activations.

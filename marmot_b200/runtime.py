@@ -26,7 +26,8 @@ EXPORTS = (
     "mcu_quantize_activations", "mcu_linear", "mcu_linear_dual", "mcu_linear_host", "mcu_topk", "mcu_moe_experts",
     "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_peer_comm_create", "mcu_peer_comm_export",
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
-    "mcu_linear_allreduce", "mcu_peer_comm_set_fused",
+    "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
+    "mcu_embedding_gather", "mcu_paged_attention",
 )
 
 
@@ -93,6 +94,13 @@ def load_library() -> C.CDLL:
     L.mcu_peer_comm_destroy.restype = None
     L.mcu_linear_allreduce.argtypes = [vp, vp, i32, vp, sz, vp, sz, sz, sz, vp]
     L.mcu_peer_comm_set_fused.argtypes = [vp, i32]
+    L.mcu_rmsnorm.argtypes = [vp, vp, vp, vp, sz, sz, f32, f32, vp]
+    L.mcu_rope.argtypes = [vp, vp, sz, vp, sz, sz, sz, f32, f32, i32, vp, sz]
+    L.mcu_swiglu.argtypes = [vp, vp, vp, sz, vp]
+    L.mcu_add.argtypes = [vp, vp, vp, sz, vp]
+    L.mcu_argmax.argtypes = [vp, vp, sz, sz, vp]
+    L.mcu_embedding_gather.argtypes = [vp, i32, vp, sz, vp, sz, vp]
+    L.mcu_paged_attention.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, i32, vp, sz, sz, sz, sz, sz, sz, sz, f32, vp]
     _lib = L
     return L
 
@@ -217,6 +225,65 @@ class Context:
         self._check(self.lib.mcu_moe_experts(self.handle, kinds[0], kinds[1], kinds[2], _ptr(hidden), T, H, FF, E,
                                              _ptr(gate), _ptr(up), _ptr(down), _ptr(topk_ids), _ptr(topk_weights), k,
                                              ffn_type, weights_scale, policy, _ptr(out)))
+        return out
+
+    # ---- decoder operators ----
+    def rmsnorm(self, x, weight, eps: float, residual=None, weight_offset: float = 0.0, out=None):
+        rows, n = x.shape
+        if out is None:
+            out = self.torch.empty_like(x)
+        self._check(self.lib.mcu_rmsnorm(self.handle, _ptr(x), _ptr(residual), _ptr(weight), rows, n, eps, weight_offset,
+                                         _ptr(out)))
+        return out
+
+    def rope(self, x, positions, n_heads: int, head_dim: int, theta: float = 10000.0, freq_scale: float = 1.0,
+             neox: bool = False, out=None):
+        """x [T, n_heads*head_dim] (row stride allowed), positions int32 [T]; out may alias x."""
+        T = x.shape[0]
+        if out is None:
+            out = self.torch.empty((T, n_heads * head_dim), dtype=self.torch.float32, device=x.device)
+        self._check(self.lib.mcu_rope(self.handle, _ptr(x), x.stride(0), _ptr(positions), T, n_heads, head_dim, theta,
+                                      freq_scale, 1 if neox else 0, _ptr(out), out.stride(0)))
+        return out
+
+    def swiglu(self, gate, up, out=None):
+        if out is None:
+            out = self.torch.empty_like(gate)
+        self._check(self.lib.mcu_swiglu(self.handle, _ptr(gate), _ptr(up), gate.numel(), _ptr(out)))
+        return out
+
+    def add(self, a, b, out=None):
+        if out is None:
+            out = self.torch.empty_like(a)
+        self._check(self.lib.mcu_add(self.handle, _ptr(a), _ptr(b), a.numel(), _ptr(out)))
+        return out
+
+    def argmax(self, x, out=None):
+        rows, n = x.shape
+        if out is None:
+            out = self.torch.empty((rows,), dtype=self.torch.int32, device=x.device)
+        self._check(self.lib.mcu_argmax(self.handle, _ptr(x), rows, n, _ptr(out)))
+        return out
+
+    def embedding_gather(self, kind: int, table, dim: int, ids, out=None):
+        T = ids.shape[0]
+        if out is None:
+            out = self.torch.empty((T, dim), dtype=self.torch.float32, device=ids.device)
+        self._check(self.lib.mcu_embedding_gather(self.handle, kind, _ptr(table), dim, _ptr(ids), T, _ptr(out)))
+        return out
+
+    def paged_attention(self, token_meta, q, k_new, v_new, kv_k, kv_v, block_table, layer: int, n_q_heads: int,
+                        n_kv_heads: int, head_dim: int, block_size: int, scale: float, out=None):
+        """q [T, n_q_heads*head_dim], k_new/v_new [T, n_kv_heads*head_dim] (contiguous); the pool tensors
+        [blocks, layers, kv_heads, block_size, head_dim] (float32 or float16) are updated in place."""
+        T = q.shape[0]
+        if out is None:
+            out = self.torch.empty_like(q)
+        kv_dtype = 1 if kv_k.dtype == self.torch.float16 else 0
+        self._check(self.lib.mcu_paged_attention(
+            self.handle, _ptr(token_meta), T, _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(kv_k), _ptr(kv_v), kv_dtype,
+            _ptr(block_table), block_table.shape[1], kv_k.shape[1], layer, n_q_heads, n_kv_heads, head_dim, block_size,
+            scale, _ptr(out)))
         return out
 
     def moe_experts_local(self, kinds, hidden, gate, up, down, topk_ids, topk_weights, FF: int, E: int,
