@@ -1,0 +1,147 @@
+"""A Llama-shape decoder step driven through the C ABI: the op sequence the reference's GGUF graph builder emits per
+layer (src/graph/gguf/graph_builder.cpp:1454-2400) -- rms_norm, linear q/k/v, rope, paged_attention (KV append inside),
+linear o, add, rms_norm, linear gate/up, swiglu, linear down, add; tail rms_norm, linear output -- on random-init
+weights of a named shape, quantized in the Q4_K_M mix (Q4_K everywhere, Q6_K for attn_v, ffn_down and output).
+
+Plumbing only: every operator is one call into libmarmot_cuda; torch holds the buffers and replays the CUDA graph.
+Used by bench.py (decode tokens/s of BASELINE configs 3 and 4) and by the decode parity test.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from .runtime import KIND_Q4_K, KIND_Q6_K, Context, row_bytes
+
+
+@dataclass
+class DecoderShape:
+    layers: int
+    d: int
+    ffn: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    vocab: int
+    rope_theta: float = 10000.0
+    rms_eps: float = 1e-5
+
+
+TINYLLAMA_1B = DecoderShape(22, 2048, 5632, 32, 4, 64, 32000, 10000.0)
+LLAMA3_8B = DecoderShape(32, 4096, 14336, 32, 8, 128, 128256, 500000.0)
+
+# (name, quant kind, rows, cols as functions of the shape): the Q4_K_M mix
+LAYER_WEIGHTS = (
+    ("wq", KIND_Q4_K, lambda s: s.n_heads * s.head_dim, lambda s: s.d),
+    ("wk", KIND_Q4_K, lambda s: s.n_kv_heads * s.head_dim, lambda s: s.d),
+    ("wv", KIND_Q6_K, lambda s: s.n_kv_heads * s.head_dim, lambda s: s.d),
+    ("wo", KIND_Q4_K, lambda s: s.d, lambda s: s.n_heads * s.head_dim),
+    ("gate", KIND_Q4_K, lambda s: s.ffn, lambda s: s.d),
+    ("up", KIND_Q4_K, lambda s: s.ffn, lambda s: s.d),
+    ("down", KIND_Q6_K, lambda s: s.d, lambda s: s.ffn),
+)
+
+
+def weight_bytes(shape: DecoderShape) -> int:
+    """Packed weight bytes one decode step streams (all layers + output projection; the embedding gather reads rows)."""
+    per_layer = sum(rows(shape) * row_bytes(kind, cols(shape)) for _, kind, rows, cols in LAYER_WEIGHTS)
+    return shape.layers * per_layer + shape.vocab * row_bytes(KIND_Q6_K, shape.d)
+
+
+class Decoder:
+    """Weights are given as host byte arrays (`weights[name]`, per layer `weights[f"l{i}.{name}"]`) or drawn on the
+    device when `weights` is None (timing only)."""
+
+    def __init__(self, ctx: Context, shape: DecoderShape, max_seqs: int, max_ctx: int, block_size: int = 16,
+                 kv_dtype=None, weights: dict | None = None, seed: int = 0):
+        import torch
+
+        from .profile_case import synthetic_blocks_device
+
+        self.ctx, self.shape, self.torch = ctx, shape, torch
+        self.block_size, self.max_seqs = block_size, max_seqs
+        dev = torch.device("cuda", ctx.device)
+        self.dev = dev
+        s = shape
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(seed)
+
+        def mat(name, kind, rows, cols):
+            if weights is not None:
+                return ctx.upload(weights[name])
+            return synthetic_blocks_device(torch, kind, rows, cols, dev, gen)
+
+        def vec(name, n):
+            if weights is not None:
+                return torch.from_numpy(np.ascontiguousarray(weights[name], dtype=np.float32)).to(dev)
+            return torch.ones(n, dtype=torch.float32, device=dev)
+
+        self.layers = []
+        for i in range(s.layers):
+            lw = {name: mat(f"l{i}.{name}", kind, rows(s), cols(s)) for name, kind, rows, cols in LAYER_WEIGHTS}
+            lw["attn_norm"] = vec(f"l{i}.attn_norm", s.d)
+            lw["ffn_norm"] = vec(f"l{i}.ffn_norm", s.d)
+            self.layers.append(lw)
+        self.tok_embd = mat("tok_embd", KIND_Q4_K, s.vocab, s.d)
+        self.output = mat("output", KIND_Q6_K, s.vocab, s.d)
+        self.out_norm = vec("out_norm", s.d)
+
+        self.max_blocks = (max_ctx + block_size - 1) // block_size
+        n_blocks = max_seqs * self.max_blocks
+        kv_dtype = kv_dtype or torch.float16
+        pool = (n_blocks, s.layers, s.n_kv_heads, block_size, s.head_dim)
+        self.kv_k = torch.zeros(pool, dtype=kv_dtype, device=dev)
+        self.kv_v = torch.zeros(pool, dtype=kv_dtype, device=dev)
+        # sequence i owns the blocks [i*max_blocks, (i+1)*max_blocks): a static block table (the allocator is the
+        # serving engine's business, not this path's)
+        table = np.arange(n_blocks, dtype=np.uint32).reshape(max_seqs, self.max_blocks)
+        self.block_table = torch.from_numpy(table).to(dev)
+        self._bufs = {}
+
+    def _buf(self, name, shape, dtype=None):
+        key = (name, tuple(shape))
+        if key not in self._bufs:
+            self._bufs[key] = self.torch.empty(shape, dtype=dtype or self.torch.float32, device=self.dev)
+        return self._bufs[key]
+
+    def token_meta(self, seq_slots, positions):
+        """[T, 4] u32 rows {seq_slot, pos, kv_slot, flags} for tokens at `positions` of sequences `seq_slots`."""
+        seq = np.asarray(seq_slots, dtype=np.int64)
+        pos = np.asarray(positions, dtype=np.int64)
+        block = seq * self.max_blocks + pos // self.block_size
+        kv_slot = block * self.block_size + pos % self.block_size
+        return np.stack([seq, pos, kv_slot, np.zeros_like(seq)], axis=1).astype(np.uint32)
+
+    def step(self, ids, meta, positions, logits_out=None):
+        """One forward pass for T tokens: ids int32 [T], meta u32 [T, 4], positions int32 [T] (device tensors).
+        Returns logits [T, vocab]."""
+        ctx, s = self.ctx, self.shape
+        T = ids.shape[0]
+        hq, hkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
+        x = ctx.embedding_gather(KIND_Q4_K, self.tok_embd, s.d, ids, out=self._buf("x", (T, s.d)))
+        h = self._buf("h", (T, s.d))
+        q, k, v = self._buf("q", (T, hq * hd)), self._buf("k", (T, hkv * hd)), self._buf("v", (T, hkv * hd))
+        att, proj = self._buf("att", (T, hq * hd)), self._buf("proj", (T, s.d))
+        gate, up = self._buf("gate", (T, s.ffn)), self._buf("up", (T, s.ffn))
+        scale = float(hd) ** -0.5
+        for i, lw in enumerate(self.layers):
+            ctx.rmsnorm(x, lw["attn_norm"], s.rms_eps, out=h)
+            ctx.linear(KIND_Q4_K, h, lw["wq"], hq * hd, out=q)
+            ctx.linear(KIND_Q4_K, h, lw["wk"], hkv * hd, out=k)
+            ctx.linear(KIND_Q6_K, h, lw["wv"], hkv * hd, out=v)
+            ctx.rope(q, positions, hq, hd, s.rope_theta, out=q)
+            ctx.rope(k, positions, hkv, hd, s.rope_theta, out=k)
+            ctx.paged_attention(meta, q, k, v, self.kv_k, self.kv_v, self.block_table, i, hq, hkv, hd, self.block_size,
+                                scale, out=att)
+            ctx.linear(KIND_Q4_K, att, lw["wo"], s.d, out=proj)
+            ctx.add(x, proj, out=x)
+            ctx.rmsnorm(x, lw["ffn_norm"], s.rms_eps, out=h)
+            ctx.linear_dual(KIND_Q4_K, h, lw["gate"], lw["up"], s.ffn, out_a=gate, out_b=up)
+            ctx.swiglu(gate, up, out=gate)
+            ctx.linear(KIND_Q6_K, gate, lw["down"], s.d, out=proj)
+            ctx.add(x, proj, out=x)
+        ctx.rmsnorm(x, self.out_norm, s.rms_eps, out=h)
+        logits = logits_out if logits_out is not None else self._buf("logits", (T, s.vocab))
+        ctx.linear(KIND_Q6_K, h, self.output, s.vocab, out=logits)
+        return logits
