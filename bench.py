@@ -324,6 +324,77 @@ def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
     return result
 
 
+def time_decode(ctx, dev):
+    """Decode tokens/s of the Llama-shape decoders of BASELINE configs 3 and 4 on one GPU, random-init Q4_K_M weights,
+    fp16 paged KV cache with 16-token blocks, the whole step (embedding gather, 7 matmuls + attention + glue per layer,
+    output projection, argmax, position update) captured in one CUDA graph and replayed; greedy sampling stays on the
+    device.  Config 3: TinyLlama-1.1B shape, batch 1, 128-token prompt, 256 decoded tokens.  Config 4: Llama-3-8B shape,
+    64 sequences with contexts uniform in [256, 4096], one decode step repeated at fixed contexts."""
+    import torch
+
+    from marmot_b200.decoder import LLAMA3_8B, TINYLLAMA_1B, Decoder, weight_bytes
+
+    peak_bw, _ = measured_peaks()
+    out = {}
+
+    def run(shape, n_seq, ctx_lens, n_prompt, n_decode, advance):
+        max_ctx = int(max(ctx_lens)) + n_decode + 16
+        dec = Decoder(ctx, shape, max_seqs=n_seq, max_ctx=max_ctx, block_size=16, kv_dtype=torch.float16, seed=5)
+        stream = torch.cuda.Stream(dev)
+        ctx.set_stream(stream.cuda_stream)
+        rng = np.random.default_rng(3)
+        with torch.cuda.stream(stream):
+            if n_prompt > 0:  # prefill the prompt in one call (tensor-core regime)
+                ids = torch.from_numpy(rng.integers(0, shape.vocab, n_prompt).astype(np.int32)).to(dev)
+                pos = np.arange(n_prompt, dtype=np.int32)
+                dec.step(ids, torch.from_numpy(dec.token_meta([0] * n_prompt, pos)).to(dev), torch.from_numpy(pos).to(dev))
+            ids = torch.from_numpy(rng.integers(0, shape.vocab, n_seq).astype(np.int32)).to(dev)
+            pos_np = np.asarray(ctx_lens, dtype=np.int32)
+            pos = torch.from_numpy(pos_np).to(dev)
+            meta = torch.from_numpy(dec.token_meta(np.arange(n_seq), pos_np)).to(dev)
+            meta_i32 = meta.view(torch.int32)  # torch has no uint32 arithmetic on CUDA; the values stay below 2^31
+            logits = torch.empty((n_seq, shape.vocab), dtype=torch.float32, device=dev)
+
+            def one_token():
+                dec.step(ids, meta, pos, logits_out=logits)
+                ctx.argmax(logits, out=ids)
+                if advance:  # a sequence's blocks are contiguous here, so kv_slot advances with the position
+                    pos.add_(1)
+                    meta_i32[:, 1:3] += 1
+
+            one_token()
+            torch.cuda.synchronize()
+            l0 = ctx.launch_count()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                one_token()
+            launches = ctx.launch_count() - l0
+            for _ in range(3):
+                g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(n_decode):
+                g.replay()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n_decode
+        ctx.set_stream(0)
+        wb = weight_bytes(shape)
+        mean_ctx = float(np.mean(ctx_lens)) + (n_decode / 2 if advance else 0)
+        kvb = n_seq * mean_ctx * shape.layers * shape.n_kv_heads * shape.head_dim * 2 * 2
+        return {"ms_per_step": round(ms, 4), "tokens_per_s": round(n_seq / ms * 1e3, 1), "sequences": n_seq,
+                "weight_bytes_per_step": wb, "kv_bytes_per_step": int(kvb),
+                "GBps": round((wb + kvb) / ms / 1e6, 1), "frac_hbm": round((wb + kvb) / ms / 1e6 / peak_bw, 3),
+                "kernel_launches_per_step": int(launches)}
+
+    out["tinyllama_1b_batch1"] = run(TINYLLAMA_1B, 1, [128], 128, 256, True)
+    torch.cuda.empty_cache()
+    lens = np.random.default_rng(4).integers(256, 4097, 64)
+    out["llama3_8b_64seq"] = run(LLAMA3_8B, 64, lens, 0, 20, False)
+    torch.cuda.empty_cache()
+    return out
+
+
 def time_moe_c5(ctx, dev, rank: int, world: int, dist):
     """BASELINE config 5: Mixtral-8x7B-shape expert FFN (8 experts, top-2, d=4096, FFN 14336, Q4_K), 2048 tokens,
     softmax top-2 routing of N(0,1) logits; expert parallel over the ranks (contiguous expert ranges, router
@@ -531,10 +602,12 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
 
-    tp_section = moe_section = None
+    tp_section = moe_section = decode_section = None
     if not args.no_extra:
         tp_section = time_tp_decode_matmuls(ctx, dev, rank, world, dist)
         moe_section = time_moe_c5(ctx, dev, rank, world, dist)
+        if world == 1:
+            decode_section = time_decode(ctx, dev)
 
     if rank != 0:
         if world > 1:
@@ -572,6 +645,8 @@ def main():
         line["llama8b_decode_matmuls"] = tp_section
     if moe_section is not None:
         line["moe_mixtral_expert_ffn"] = moe_section
+    if decode_section is not None:
+        line["decode"] = decode_section
     if not args.no_extra and world == 1:
         line["other_regimes"] = time_other_regimes(ctx, dev)
     if not args.no_cpu_baseline:

@@ -68,6 +68,7 @@ struct mcu_context {
     Buffer act_qs, act_d, act_bsums, act_half, act_rowscale, x_stage, out_stage, bias_stage;
     Buffer moe_meta, moe_hidden, moe_gate, moe_up, moe_down;
     Buffer gemm_partial;         // split-K partial tiles
+    Buffer attn_partial;         // split-KV partial attention states
     int *gemm_counters = nullptr;  // split-K tile tickets (zero between launches)
     std::vector<int> host_counts;
     int *dev_err = nullptr;  // set by kernels whose bounded device-side waits ran out
@@ -100,6 +101,12 @@ static int check_device_error(mcu_context *ctx) {
 namespace mcu {
 int context_device(const mcu_context *ctx) { return ctx->device; }
 int *context_err_flag(mcu_context *ctx) { return ctx->dev_err; }
+int context_attention_scratch(mcu_context *ctx, size_t bytes, void **out) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (int rc = ensure(ctx, ctx->attn_partial, bytes)) return rc;
+    *out = ctx->attn_partial.ptr;
+    return MCU_SUCCESS;
+}
 }  // namespace mcu
 
 static int check_ctx(mcu_context *ctx) {
@@ -160,7 +167,7 @@ void mcu_context_destroy(mcu_context_t *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     Buffer *bufs[] = {&ctx->act_qs,   &ctx->act_d,      &ctx->act_bsums, &ctx->act_half, &ctx->act_rowscale, &ctx->x_stage, &ctx->out_stage,
-                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down, &ctx->gemm_partial};
+                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down, &ctx->gemm_partial, &ctx->attn_partial};
     for (Buffer *b : bufs)
         if (b->ptr != nullptr) cudaFree(b->ptr);
     if (ctx->dev_err != nullptr) cudaFree(ctx->dev_err);

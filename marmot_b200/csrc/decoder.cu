@@ -156,22 +156,68 @@ __global__ void kv_append_kernel(PagedParams p, int head_dim) {
     }
 }
 
-// One CTA per (query head, token): 4 warps, every group of 8 lanes walks its own positions (16 positions per CTA
-// iteration) holding HD/8 dimensions per lane; online softmax per group, the 16 group states merged at the end.
+// DPL consecutive pool elements -> f32 with 16-byte loads.
+template <int DPL>
+__device__ __forceinline__ void kv_load_vec(const float *p, float (&v)[DPL]) {
+#pragma unroll
+    for (int i = 0; i < DPL; i += 4) {
+        const float4 t = *(const float4 *)(p + i);
+        v[i] = t.x;
+        v[i + 1] = t.y;
+        v[i + 2] = t.z;
+        v[i + 3] = t.w;
+    }
+}
+template <int DPL>
+__device__ __forceinline__ void kv_load_vec(const __half *p, float (&v)[DPL]) {
+#pragma unroll
+    for (int i = 0; i < DPL; i += 8) {
+        const uint4 t = *(const uint4 *)(p + i);
+        const __half2 *h2 = (const __half2 *)&t;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h2[j]);
+            v[i + 2 * j] = f.x;
+            v[i + 2 * j + 1] = f.y;
+        }
+    }
+}
+
+// Split-KV attention.  One CTA per (KV head, token, chunk of `chunk` positions), one warp per query head of the head's
+// group.  The CTA stages tiles of 32 K rows and 32 V rows in shared memory with 16-byte loads spread over all its
+// threads (every pool byte is fetched once per CTA, and a thread has several loads in flight), then every warp scores
+// the tile for its query head: groups of 8 lanes take one row each, HD/8 dimensions per lane, online softmax per
+// lane group.  The 4 group states of a warp are merged and written as one partial state {m, l, acc[HD]} per
+// (token, query head, chunk); paged_attention_merge_kernel combines the chunks, so long contexts never serialise on
+// one warp.
+constexpr int PA_MAX_GROUP = 8;
+constexpr int PA_TILE = 32;
 template <typename KV, int HD>
-__global__ void __launch_bounds__(128) paged_attention_kernel(PagedParams p) {
-    constexpr int DPL = HD / 8;  // dimensions per lane
-    __shared__ float s_acc[16][HD];
-    __shared__ float s_m[16], s_l[16];
-    const int qh = blockIdx.x, t = blockIdx.y;
+__global__ void __launch_bounds__(32 * PA_MAX_GROUP) paged_attention_kernel(PagedParams p, int chunk, float *partial) {
+    constexpr int DPL = HD / 8;                          // dimensions per lane
+    constexpr int ROW_BYTES = HD * (int)sizeof(KV);
+    constexpr int PIECES = ROW_BYTES / 16;               // 16-byte pieces per row
+    constexpr int TILE_BYTES = PA_TILE * ROW_BYTES;
+    constexpr int ACC_BYTES = PA_MAX_GROUP * 4 * HD * (int)sizeof(float);
+    constexpr int SMEM_BYTES = 2 * TILE_BYTES > ACC_BYTES ? 2 * TILE_BYTES : ACC_BYTES;
+    __shared__ __align__(16) uint8_t s_buf[SMEM_BYTES];  // K tile | V tile; reused for the group states at the end
+    __shared__ float s_m[PA_MAX_GROUP][4], s_l[PA_MAX_GROUP][4];
+    __shared__ int s_live[PA_TILE];
+    const int h = blockIdx.x, t = blockIdx.y, c = blockIdx.z, n_chunks = gridDim.z;
+    const uint32_t kv_len = p.meta[t * 4 + 1] + 1u;
+    const uint32_t p0 = (uint32_t)c * (uint32_t)chunk;
+    if (p0 >= kv_len) return;  // the merge kernel derives the number of live chunks from kv_len as well
+    const uint32_t p1 = min(kv_len, p0 + (uint32_t)chunk);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane >> 3, l8 = lane & 7;
-    const int group = warp * 4 + sub;
-    const uint32_t seq = p.meta[t * 4 + 0], kv_len = p.meta[t * 4 + 1] + 1u;
-    const int h = qh / (p.n_q_heads / p.n_kv_heads);
+    const int gsize = p.n_q_heads / p.n_kv_heads;
+    const int qh = h * gsize + warp;
+    const uint32_t seq = p.meta[t * 4 + 0];
     const size_t bs = (size_t)1 << p.block_shift;
     const size_t s3 = HD, s2 = bs * s3, s1 = (size_t)p.n_kv_heads * s2, s0 = (size_t)p.n_layers * s1;
     const size_t head_off = (size_t)p.layer * s1 + (size_t)h * s2;
+    const uint32_t *table = p.table + (size_t)seq * p.max_blocks;
+    uint8_t *s_k = s_buf, *s_v = s_buf + TILE_BYTES;
 
     float qv[DPL], acc[DPL];
     const float *qrow = p.q + ((size_t)t * p.n_q_heads + qh) * HD + l8 * DPL;
@@ -181,54 +227,100 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(PagedParams p) {
         acc[d] = 0.0f;
     }
     float m = -INFINITY, l = 0.0f;
-    const uint32_t gmask = 0xFFu << (8 * sub);
-    for (uint32_t pos = (uint32_t)group; pos < kv_len; pos += 16u) {
-        const uint32_t lb = pos >> p.block_shift;
-        if (lb >= (uint32_t)p.max_blocks) break;
-        const uint32_t tb = p.table[(size_t)seq * p.max_blocks + lb];
-        if (tb == 0xFFFFFFFFu) continue;
-        const size_t base = (size_t)tb * s0 + head_off + (size_t)(pos & (uint32_t)(bs - 1)) * s3 + l8 * DPL;
-        const KV *kr = (const KV *)p.kv_k + base, *vr = (const KV *)p.kv_v + base;
-        float dot = 0.0f;
-#pragma unroll
-        for (int d = 0; d < DPL; ++d) dot += qv[d] * kv_load(kr + d);
-        dot += __shfl_xor_sync(gmask, dot, 1);  // the eight lanes of a group share their trip count, groups do not
-        dot += __shfl_xor_sync(gmask, dot, 2);
-        dot += __shfl_xor_sync(gmask, dot, 4);
-        const float m_new = fmaxf(m, dot);
-        const float keep = m == -INFINITY ? 0.0f : expf(m - m_new);
-        const float w = expf(dot - m_new);
-        l = l * keep + w;
-#pragma unroll
-        for (int d = 0; d < DPL; ++d) acc[d] = acc[d] * keep + w * kv_load(vr + d);
-        m = m_new;
-    }
-    // the loop is not warp-uniform (groups run out of positions at different times): reconverge before shuffles end
-    __syncwarp();
-    if (l8 == 0) {
-        s_m[group] = m;
-        s_l[group] = l;
-    }
-#pragma unroll
-    for (int d = 0; d < DPL; ++d) s_acc[group][l8 * DPL + d] = acc[d];
-    __syncthreads();
-    float *orow = p.out + ((size_t)t * p.n_q_heads + qh) * HD;
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float M = -INFINITY;
-#pragma unroll
-        for (int g = 0; g < 16; ++g) M = fmaxf(M, s_m[g]);
-        float L = 0.0f, o = 0.0f;
-        if (M != -INFINITY) {
-#pragma unroll
-            for (int g = 0; g < 16; ++g) {
-                if (s_m[g] == -INFINITY) continue;
-                const float e = expf(s_m[g] - M);
-                L += s_l[g] * e;
-                o += s_acc[g][d] * e;
+    for (uint32_t t0 = p0; t0 < p1; t0 += PA_TILE) {
+        // stage the tile
+        for (int idx = threadIdx.x; idx < PA_TILE * PIECES; idx += blockDim.x) {
+            const int r = idx / PIECES, pc = idx - r * PIECES;
+            const uint32_t pos = t0 + (uint32_t)r;
+            const uint32_t lb = pos >> p.block_shift;
+            uint32_t tb = 0xFFFFFFFFu;
+            if (pos < p1 && lb < (uint32_t)p.max_blocks) tb = table[lb];
+            if (pc == 0) s_live[r] = tb != 0xFFFFFFFFu;
+            if (tb != 0xFFFFFFFFu) {
+                const size_t base = (size_t)tb * s0 + head_off + (size_t)(pos & (uint32_t)(bs - 1)) * s3;
+                const uint4 kq = *((const uint4 *)((const KV *)p.kv_k + base) + pc);
+                const uint4 vq = *((const uint4 *)((const KV *)p.kv_v + base) + pc);
+                *((uint4 *)(s_k + r * ROW_BYTES) + pc) = kq;
+                *((uint4 *)(s_v + r * ROW_BYTES) + pc) = vq;
             }
         }
-        orow[d] = L > 0.0f ? o / L : 0.0f;
+        __syncthreads();
+        // score the tile: lane group `sub` takes rows sub, sub+4, ...
+#pragma unroll 2
+        for (int r = sub; r < PA_TILE; r += 4) {
+            if (!s_live[r]) continue;  // uniform over the lane group (and over the warps)
+            float kf[DPL], vf[DPL];
+            kv_load_vec<DPL>((const KV *)(s_k + r * ROW_BYTES) + l8 * DPL, kf);
+            kv_load_vec<DPL>((const KV *)(s_v + r * ROW_BYTES) + l8 * DPL, vf);
+            float dot = 0.0f;
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) dot += qv[d] * kf[d];
+            const uint32_t gmask = 0xFFu << (8 * sub);
+            dot += __shfl_xor_sync(gmask, dot, 1);  // the eight lanes of a group decide alike
+            dot += __shfl_xor_sync(gmask, dot, 2);
+            dot += __shfl_xor_sync(gmask, dot, 4);
+            const float m_new = fmaxf(m, dot);
+            const float keep = m == -INFINITY ? 0.0f : expf(m - m_new);
+            const float w = expf(dot - m_new);
+            l = l * keep + w;
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) acc[d] = acc[d] * keep + w * vf[d];
+            m = m_new;
+        }
+        __syncthreads();
     }
+    // merge the four lane-group states of this warp; the tile buffers are free now
+    float (*s_acc)[4][HD] = (float (*)[4][HD])s_buf;
+    if (l8 == 0) {
+        s_m[warp][sub] = m;
+        s_l[warp][sub] = l;
+    }
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) s_acc[warp][sub][l8 * DPL + d] = acc[d];
+    __syncwarp();
+    // partial state of this chunk: [token][query head][chunk][2 + HD]
+    float *pr = partial + (((size_t)t * p.n_q_heads + qh) * n_chunks + c) * (HD + 2);
+    float M = -INFINITY;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) M = fmaxf(M, s_m[warp][g]);
+    float e[4], L = 0.0f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        e[g] = (M == -INFINITY || s_m[warp][g] == -INFINITY) ? 0.0f : expf(s_m[warp][g] - M);
+        L += s_l[warp][g] * e[g];
+    }
+    if (lane == 0) {
+        pr[0] = M;
+        pr[1] = L;
+    }
+    for (int d = lane; d < HD; d += 32) {
+        float o = 0.0f;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) o += s_acc[warp][g][d] * e[g];
+        pr[2 + d] = o;
+    }
+}
+
+// out[t][qh][:] from the chunk states; grid (query heads, tokens), HD threads.
+template <int HD>
+__global__ void paged_attention_merge_kernel(PagedParams p, int chunk, int n_chunks, const float *partial) {
+    const int qh = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
+    const uint32_t kv_len = p.meta[t * 4 + 1] + 1u;
+    const int live = min(n_chunks, (int)((kv_len + (uint32_t)chunk - 1u) / (uint32_t)chunk));
+    const float *pr = partial + ((size_t)t * p.n_q_heads + qh) * n_chunks * (HD + 2);
+    float M = -INFINITY;
+    for (int c = 0; c < live; ++c) M = fmaxf(M, pr[(size_t)c * (HD + 2)]);
+    float L = 0.0f, o = 0.0f;
+    if (M != -INFINITY) {
+        for (int c = 0; c < live; ++c) {
+            const float mc = pr[(size_t)c * (HD + 2)];
+            if (mc == -INFINITY) continue;
+            const float e = expf(mc - M);
+            L += pr[(size_t)c * (HD + 2) + 1] * e;
+            o += pr[(size_t)c * (HD + 2) + 2 + d] * e;
+        }
+    }
+    p.out[((size_t)t * p.n_q_heads + qh) * HD + d] = L > 0.0f ? o / L : 0.0f;
 }
 
 }  // namespace mcu
@@ -352,6 +444,8 @@ int mcu_paged_attention(mcu_context_t *ctx, const uint32_t *token_meta_dev, size
         return set_error(MCU_ERROR_INVALID_ARGUMENT, "paged_attention descriptor is incomplete");
     if (kv_dtype != MCU_KV_F32 && kv_dtype != MCU_KV_F16)
         return set_error(MCU_ERROR_UNSUPPORTED_DTYPE, "paged_attention KV pool must be FLOAT32 or FLOAT16");
+    if (((uintptr_t)kv_k_dev | (uintptr_t)kv_v_dev) & 15)
+        return set_error(MCU_ERROR_INVALID_ARGUMENT, "paged_attention KV pools must be 16-byte aligned");
     if (head_dim != 64 && head_dim != 128)
         return set_error(MCU_ERROR_NOT_IMPLEMENTED, "paged_attention supports head_dim 64 and 128");
     if (block_size == 0 || (block_size & (block_size - 1)) != 0)
@@ -375,18 +469,36 @@ int mcu_paged_attention(mcu_context_t *ctx, const uint32_t *token_meta_dev, size
     p.block_shift = 0;
     while (((size_t)1 << p.block_shift) < block_size) ++p.block_shift;
     p.scale = scale;
-    const dim3 ag((unsigned)T, (unsigned)n_kv_heads), qg((unsigned)n_q_heads, (unsigned)T);
+    if (n_q_heads / n_kv_heads > (size_t)PA_MAX_GROUP)
+        return set_error(MCU_ERROR_NOT_IMPLEMENTED, "paged_attention supports up to 8 query heads per KV head");
+    // chunk of positions per CTA: long enough to amortise the set-up, short enough that every SM gets several CTAs
+    // even for one short sequence.  The context length lives in device memory, so the grid covers the longest
+    // context the block table allows; CTAs beyond a token's length return at once.
+    const size_t max_positions = max_blocks_per_seq * block_size;
+    size_t chunk = 256;
+    while (chunk > 32 && n_kv_heads * T * ((max_positions + chunk - 1) / chunk) < 2 * (size_t)device_sm_count()) chunk /= 2;
+    const size_t n_chunks = (max_positions + chunk - 1) / chunk;
+    if (n_chunks > 65535) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "paged_attention context bound too long");
+    void *scratch = nullptr;
+    if (int rc = context_attention_scratch(ctx, T * n_q_heads * n_chunks * (head_dim + 2) * sizeof(float), &scratch))
+        return rc;
+    float *partial = (float *)scratch;
+    const dim3 ag((unsigned)T, (unsigned)n_kv_heads), qg((unsigned)n_kv_heads, (unsigned)T, (unsigned)n_chunks);
+    const dim3 mg((unsigned)n_q_heads, (unsigned)T);
+    const unsigned threads = 32u * (unsigned)(n_q_heads / n_kv_heads);
     if (kv_dtype == MCU_KV_F16) {
         kv_append_kernel<__half><<<ag, 128, 0, s>>>(p, (int)head_dim);
-        if (head_dim == 64) paged_attention_kernel<__half, 64><<<qg, 128, 0, s>>>(p);
-        else paged_attention_kernel<__half, 128><<<qg, 128, 0, s>>>(p);
+        if (head_dim == 64) paged_attention_kernel<__half, 64><<<qg, threads, 0, s>>>(p, (int)chunk, partial);
+        else paged_attention_kernel<__half, 128><<<qg, threads, 0, s>>>(p, (int)chunk, partial);
     } else {
         kv_append_kernel<float><<<ag, 128, 0, s>>>(p, (int)head_dim);
-        if (head_dim == 64) paged_attention_kernel<float, 64><<<qg, 128, 0, s>>>(p);
-        else paged_attention_kernel<float, 128><<<qg, 128, 0, s>>>(p);
+        if (head_dim == 64) paged_attention_kernel<float, 64><<<qg, threads, 0, s>>>(p, (int)chunk, partial);
+        else paged_attention_kernel<float, 128><<<qg, threads, 0, s>>>(p, (int)chunk, partial);
     }
+    if (head_dim == 64) paged_attention_merge_kernel<64><<<mg, 64, 0, s>>>(p, (int)chunk, (int)n_chunks, partial);
+    else paged_attention_merge_kernel<128><<<mg, 128, 0, s>>>(p, (int)chunk, (int)n_chunks, partial);
     DEC_CUDA(cudaGetLastError());
-    count_launches(2);
+    count_launches(3);
     return MCU_SUCCESS;
 }
 
