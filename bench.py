@@ -324,7 +324,7 @@ def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
     return result
 
 
-def time_decode(ctx, dev):
+def time_decode(ctx, dev, rank: int = 0, world: int = 1, dist=None):
     """Decode tokens/s of the Llama-shape decoders of BASELINE configs 3 and 4 on one GPU, random-init Q4_K_M weights,
     fp16 paged KV cache with 16-token blocks, the whole step (embedding gather, 7 matmuls + attention + glue per layer,
     output projection, argmax, position update) captured in one CUDA graph and replayed; greedy sampling stays on the
@@ -332,14 +332,18 @@ def time_decode(ctx, dev):
     64 sequences with contexts uniform in [256, 4096], one decode step repeated at fixed contexts."""
     import torch
 
+    from marmot_b200 import tensor_parallel as tp
     from marmot_b200.decoder import LLAMA3_8B, TINYLLAMA_1B, Decoder, weight_bytes
 
     peak_bw, _ = measured_peaks()
     out = {}
+    group = tp.Group(rank, world, dist if world > 1 else None)
 
     def run(shape, n_seq, ctx_lens, n_prompt, n_decode, advance):
         max_ctx = int(max(ctx_lens)) + n_decode + 16
-        dec = Decoder(ctx, shape, max_seqs=n_seq, max_ctx=max_ctx, block_size=16, kv_dtype=torch.float16, seed=5)
+        comm = tp.make_peer_comm(ctx, group, n_seq * max(shape.d, world) * 4) if world > 1 else None
+        dec = Decoder(ctx, shape, max_seqs=n_seq, max_ctx=max_ctx, block_size=16, kv_dtype=torch.float16, seed=5,
+                      group=group, comm=comm)
         stream = torch.cuda.Stream(dev)
         ctx.set_stream(stream.cuda_stream)
         rng = np.random.default_rng(3)
@@ -353,17 +357,20 @@ def time_decode(ctx, dev):
             pos = torch.from_numpy(pos_np).to(dev)
             meta = torch.from_numpy(dec.token_meta(np.arange(n_seq), pos_np)).to(dev)
             meta_i32 = meta.view(torch.int32)  # torch has no uint32 arithmetic on CUDA; the values stay below 2^31
-            logits = torch.empty((n_seq, shape.vocab), dtype=torch.float32, device=dev)
+            logits = torch.empty((n_seq, dec.local_vocab), dtype=torch.float32, device=dev)
 
             def one_token():
                 dec.step(ids, meta, pos, logits_out=logits)
-                ctx.argmax(logits, out=ids)
+                dec.greedy(logits, ids)
                 if advance:  # a sequence's blocks are contiguous here, so kv_slot advances with the position
                     pos.add_(1)
                     meta_i32[:, 1:3] += 1
 
             one_token()
+            one_token()  # an even number of eager steps: the communicator's staging parity is what the graph captures
             torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
             l0 = ctx.launch_count()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
@@ -371,6 +378,9 @@ def time_decode(ctx, dev):
             launches = ctx.launch_count() - l0
             for _ in range(3):
                 g.replay()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
             for _ in range(n_decode):
@@ -378,17 +388,30 @@ def time_decode(ctx, dev):
             e1.record(stream)
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / n_decode
+        ctx.synchronize()  # reports a peer wait that ran out
         ctx.set_stream(0)
-        wb = weight_bytes(shape)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+            dist.barrier()
+            torch.cuda.synchronize()
+            comm.close()
+        wb = weight_bytes(dec.local) - dec.local.vocab * row_bytes_q6(dec.local.d) + dec.local_vocab * row_bytes_q6(dec.local.d)
+        kv_heads_here = dec.local.n_kv_heads
         mean_ctx = float(np.mean(ctx_lens)) + (n_decode / 2 if advance else 0)
-        kvb = n_seq * mean_ctx * shape.layers * shape.n_kv_heads * shape.head_dim * 2 * 2
+        kvb = n_seq * mean_ctx * shape.layers * kv_heads_here * shape.head_dim * 2 * 2
         return {"ms_per_step": round(ms, 4), "tokens_per_s": round(n_seq / ms * 1e3, 1), "sequences": n_seq,
-                "weight_bytes_per_step": wb, "kv_bytes_per_step": int(kvb),
+                "tensor_parallel": world, "weight_bytes_per_step_per_gpu": wb, "kv_bytes_per_step_per_gpu": int(kvb),
                 "GBps": round((wb + kvb) / ms / 1e6, 1), "frac_hbm": round((wb + kvb) / ms / 1e6 / peak_bw, 3),
                 "kernel_launches_per_step": int(launches)}
 
-    out["tinyllama_1b_batch1"] = run(TINYLLAMA_1B, 1, [128], 128, 256, True)
-    torch.cuda.empty_cache()
+    def row_bytes_q6(K):
+        return (K // 256) * 210
+
+    if world == 1:
+        out["tinyllama_1b_batch1"] = run(TINYLLAMA_1B, 1, [128], 128, 256, True)
+        torch.cuda.empty_cache()
     lens = np.random.default_rng(4).integers(256, 4097, 64)
     out["llama3_8b_64seq"] = run(LLAMA3_8B, 64, lens, 0, 20, False)
     torch.cuda.empty_cache()
@@ -606,8 +629,8 @@ def main():
     if not args.no_extra:
         tp_section = time_tp_decode_matmuls(ctx, dev, rank, world, dist)
         moe_section = time_moe_c5(ctx, dev, rank, world, dist)
-        if world == 1:
-            decode_section = time_decode(ctx, dev)
+        if LLAMA8B["kv"] // 128 % world == 0:
+            decode_section = time_decode(ctx, dev, rank, world, dist)
 
     if rank != 0:
         if world > 1:

@@ -50,26 +50,52 @@ def weight_bytes(shape: DecoderShape) -> int:
 
 
 class Decoder:
-    """Weights are given as host byte arrays (`weights[name]`, per layer `weights[f"l{i}.{name}"]`) or drawn on the
-    device when `weights` is None (timing only)."""
+    """Weights are given as host byte arrays (`weights[name]`, per layer `weights[f"l{i}.{name}"]`; single rank only)
+    or drawn on the device when `weights` is None (timing only).
+
+    Tensor parallel over the ranks of `group` (tensor_parallel.Group) with `comm` (runtime.PeerComm): query and KV
+    heads, the FFN width (in 2048-value granules, so that the Q6_K down shards keep 16-byte rows) and the vocabulary
+    are dealt out; attention output and ffn_down are row-parallel with one all-reduce each; every rank keeps the
+    residual stream, its own slice of the KV pool and finds the global argmax from the ranks' local maxima."""
 
     def __init__(self, ctx: Context, shape: DecoderShape, max_seqs: int, max_ctx: int, block_size: int = 16,
-                 kv_dtype=None, weights: dict | None = None, seed: int = 0):
+                 kv_dtype=None, weights: dict | None = None, seed: int = 0, group=None, comm=None):
         import torch
 
+        from . import tensor_parallel as tp
         from .profile_case import synthetic_blocks_device
 
         self.ctx, self.shape, self.torch = ctx, shape, torch
         self.block_size, self.max_seqs = block_size, max_seqs
         dev = torch.device("cuda", ctx.device)
         self.dev = dev
+        self.group = group or tp.Group()
+        self.comm = comm
+        world, rank = self.group.world, self.group.rank
+        if world > 1:
+            if weights is not None:
+                raise NotImplementedError("tensor-parallel Decoder draws its own shard-shaped weights")
+            if shape.n_kv_heads % world or shape.n_heads % world or comm is None:
+                raise ValueError("heads must divide over the ranks and a PeerComm is needed")
+            f_lo, f_hi = tp.shard_range(shape.ffn, world, rank, 2048)
+            v_lo, v_hi = tp.shard_range(shape.vocab, world, rank, 32)
+            self.v_lo = v_lo
+            self.ffn_empty_somewhere = any(b == a for a, b in (tp.shard_range(shape.ffn, world, r, 2048) for r in range(world)))
+            shape = DecoderShape(shape.layers, shape.d, f_hi - f_lo, shape.n_heads // world, shape.n_kv_heads // world,
+                                 shape.head_dim, shape.vocab, shape.rope_theta, shape.rms_eps)
+            self.local_vocab = v_hi - v_lo
+        else:
+            self.v_lo, self.local_vocab, self.ffn_empty_somewhere = 0, shape.vocab, False
+        self.local = shape  # this rank's share of heads / FFN width (d, layers, vocab as in the full shape)
         s = shape
         gen = torch.Generator(device=dev)
-        gen.manual_seed(seed)
+        gen.manual_seed(seed + 1000 * rank)
 
         def mat(name, kind, rows, cols):
             if weights is not None:
                 return ctx.upload(weights[name])
+            if rows == 0 or cols == 0:
+                return None
             return synthetic_blocks_device(torch, kind, rows, cols, dev, gen)
 
         def vec(name, n):
@@ -83,8 +109,10 @@ class Decoder:
             lw["attn_norm"] = vec(f"l{i}.attn_norm", s.d)
             lw["ffn_norm"] = vec(f"l{i}.ffn_norm", s.d)
             self.layers.append(lw)
+        gen.manual_seed(seed)  # the embedding table is replicated: the same on every rank
         self.tok_embd = mat("tok_embd", KIND_Q4_K, s.vocab, s.d)
-        self.output = mat("output", KIND_Q6_K, s.vocab, s.d)
+        gen.manual_seed(seed + 77 + 1000 * rank)
+        self.output = mat("output", KIND_Q6_K, self.local_vocab, s.d)
         self.out_norm = vec("out_norm", s.d)
 
         self.max_blocks = (max_ctx + block_size - 1) // block_size
@@ -113,17 +141,50 @@ class Decoder:
         kv_slot = block * self.block_size + pos % self.block_size
         return np.stack([seq, pos, kv_slot, np.zeros_like(seq)], axis=1).astype(np.uint32)
 
+    def _row_parallel(self, kind, x, w, F, out, K):
+        """out = all-reduce over the ranks of x @ w.T (this rank's K-slice)."""
+        if self.group.world == 1:
+            return self.ctx.linear(kind, x, w, F, out=out)
+        T = x.shape[0]
+        if K == 0:  # this rank has no share of the FFN width: it adds zeros
+            self.comm.staging((T, F)).zero_()
+            return self.comm.allreduce(T * F, out)
+        if self.ffn_empty_somewhere and K == self.local.ffn:  # all ranks must then use the two-kernel form
+            self.ctx.linear(kind, x, w, F, out=self.comm.staging((T, F)))
+            return self.comm.allreduce(T * F, out)
+        return self.comm.linear_allreduce(kind, x, w, F, out=out)
+
+    def greedy(self, logits, ids_out):
+        """Global argmax of the ranks' logits slices into ids_out (int32 [T]); two small all-reduces gather the local
+        maxima (an even number keeps the communicator's staging parity stable across CUDA-graph replays)."""
+        ctx, torch = self.ctx, self.torch
+        T = logits.shape[0]
+        if self.group.world == 1:
+            return ctx.argmax(logits, out=ids_out)
+        world, rank = self.group.world, self.group.rank
+        local_idx = ctx.argmax(logits, out=self._buf("lidx", (T,), torch.int32))
+        local_val = logits.gather(1, local_idx.long().unsqueeze(1)).squeeze(1)
+        vals, idxs = self._buf("gvals", (T, world)), self._buf("gidx", (T, world))
+        for src, dst in ((local_val, vals), ((local_idx + self.v_lo).float(), idxs)):
+            st = self.comm.staging((T, world))
+            st.zero_()
+            st[:, rank] = src
+            self.comm.allreduce(T * world, dst)
+        best = vals.argmax(dim=1, keepdim=True)  # ties: the lowest rank, i.e. the lowest vocabulary index
+        ids_out.copy_(idxs.gather(1, best).squeeze(1).to(torch.int32))
+        return ids_out
+
     def step(self, ids, meta, positions, logits_out=None):
         """One forward pass for T tokens: ids int32 [T], meta u32 [T, 4], positions int32 [T] (device tensors).
-        Returns logits [T, vocab]."""
-        ctx, s = self.ctx, self.shape
+        Returns logits [T, vocab] (tensor parallel: this rank's vocabulary slice [T, local_vocab])."""
+        ctx, s = self.ctx, self.local
         T = ids.shape[0]
         hq, hkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
         x = ctx.embedding_gather(KIND_Q4_K, self.tok_embd, s.d, ids, out=self._buf("x", (T, s.d)))
         h = self._buf("h", (T, s.d))
         q, k, v = self._buf("q", (T, hq * hd)), self._buf("k", (T, hkv * hd)), self._buf("v", (T, hkv * hd))
         att, proj = self._buf("att", (T, hq * hd)), self._buf("proj", (T, s.d))
-        gate, up = self._buf("gate", (T, s.ffn)), self._buf("up", (T, s.ffn))
+        gate, up = self._buf("gate", (T, max(s.ffn, 1))), self._buf("up", (T, max(s.ffn, 1)))
         scale = float(hd) ** -0.5
         for i, lw in enumerate(self.layers):
             ctx.rmsnorm(x, lw["attn_norm"], s.rms_eps, out=h)
@@ -134,14 +195,15 @@ class Decoder:
             ctx.rope(k, positions, hkv, hd, s.rope_theta, out=k)
             ctx.paged_attention(meta, q, k, v, self.kv_k, self.kv_v, self.block_table, i, hq, hkv, hd, self.block_size,
                                 scale, out=att)
-            ctx.linear(KIND_Q4_K, att, lw["wo"], s.d, out=proj)
+            self._row_parallel(KIND_Q4_K, att, lw["wo"], s.d, proj, hq * hd)
             ctx.add(x, proj, out=x)
             ctx.rmsnorm(x, lw["ffn_norm"], s.rms_eps, out=h)
-            ctx.linear_dual(KIND_Q4_K, h, lw["gate"], lw["up"], s.ffn, out_a=gate, out_b=up)
-            ctx.swiglu(gate, up, out=gate)
-            ctx.linear(KIND_Q6_K, gate, lw["down"], s.d, out=proj)
+            if s.ffn > 0:
+                ctx.linear_dual(KIND_Q4_K, h, lw["gate"], lw["up"], s.ffn, out_a=gate, out_b=up)
+                ctx.swiglu(gate, up, out=gate)
+            self._row_parallel(KIND_Q6_K, gate, lw["down"], s.d, proj, s.ffn)
             ctx.add(x, proj, out=x)
         ctx.rmsnorm(x, self.out_norm, s.rms_eps, out=h)
-        logits = logits_out if logits_out is not None else self._buf("logits", (T, s.vocab))
-        ctx.linear(KIND_Q6_K, h, self.output, s.vocab, out=logits)
+        logits = logits_out if logits_out is not None else self._buf("logits", (T, self.local_vocab))
+        ctx.linear(KIND_Q6_K, h, self.output, self.local_vocab, out=logits)
         return logits
