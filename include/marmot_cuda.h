@@ -189,6 +189,17 @@ int mcu_rope(
     mcu_context_t *ctx, const float *x_dev, size_t ldx, const int32_t *positions_dev, size_t T, size_t n_heads,
     size_t head_dim, float theta, float freq_scale, int rope_type, float *out_dev, size_t ldo
 );
+/* Two reference operators in one launch each (same arithmetic as the separate calls):
+ *   mcu_add_rmsnorm  x_out = x + delta, h_out = rmsnorm(x_out) * (weight + offset)   (marmot_add, then marmot_rmsnorm);
+ *   mcu_rope_qk      mcu_rope in place on the query and the key projection of the same tokens. */
+int mcu_add_rmsnorm(
+    mcu_context_t *ctx, const float *x_dev, const float *delta_dev, const float *weight_dev, size_t rows, size_t n,
+    float eps, float weight_offset, float *x_out_dev, float *h_out_dev
+);
+int mcu_rope_qk(
+    mcu_context_t *ctx, float *q_dev, size_t ldq, size_t n_q_heads, float *k_dev, size_t ldk, size_t n_k_heads,
+    const int32_t *positions_dev, size_t T, size_t head_dim, float theta, float freq_scale, int rope_type
+);
 int mcu_swiglu(mcu_context_t *ctx, const float *gate_dev, const float *up_dev, size_t n, float *out_dev);
 int mcu_add(mcu_context_t *ctx, const float *a_dev, const float *b_dev, size_t n, float *out_dev);
 int mcu_argmax(mcu_context_t *ctx, const float *x_dev, size_t rows, size_t n, int32_t *out_dev);

@@ -13,14 +13,44 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cuda_fp16.h>
 
 namespace mcu {
+
+// Every kernel of this file is launched with programmatic stream serialization and starts by waiting for the
+// kernel ahead of it (so nothing is read or written early), then lets the kernel behind it start its own launch:
+// the launch latencies of a chain of small kernels overlap instead of adding up.
+#define MCU_PDL_PROLOGUE()                                        \
+    asm volatile("griddepcontrol.wait;" ::: "memory");            \
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl_smem(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                   Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    static const bool no_pdl = getenv("MARMOT_CUDA_NO_PDL") != nullptr;  // diagnostic switch
+    cfg.numAttrs = no_pdl ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
+    return launch_pdl_smem(kernel, grid, block, 0, s, args...);
+}
 
 // ---------------------------------------------------------------- RMSNorm
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual, const float *__restrict__ weight, int n,
                float eps, float weight_offset, float *__restrict__ out) {
+    MCU_PDL_PROLOGUE();
     __shared__ float red[8];
     __shared__ float inv_s;
     const size_t row = blockIdx.x;
@@ -50,6 +80,39 @@ rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ residual, 
     }
 }
 
+// x_out = x + delta (the residual update), h_out = RMSNorm(x_out) * weight: the add and the rms_norm that follow every
+// row-parallel projection, in one pass over the row.  x_out may alias x.
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(const float *x, const float *__restrict__ delta, const float *__restrict__ weight, int n, float eps,
+                   float weight_offset, float *x_out, float *__restrict__ h_out) {
+    MCU_PDL_PROLOGUE();
+    __shared__ float red[8];
+    __shared__ float inv_s;
+    const size_t row = blockIdx.x;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = __fadd_rn(x[row * n + i], delta[row * n + i]);
+        x_out[row * n + i] = v;
+        sum += v * v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.0f;
+        for (int i = 0; i < 8; ++i) s += red[i];
+        inv_s = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(s, (float)n), eps)));
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float y = __fmul_rn(x_out[row * n + i], inv);  // this thread wrote that element above
+        if (weight != nullptr) y = __fmul_rn(y, __fadd_rn(weight[i], weight_offset));
+        h_out[row * n + i] = y;
+    }
+}
+
 // ---------------------------------------------------------------- RoPE
 constexpr int ROPE_MAX_PAIRS = 128;
 struct RopeFreqs {
@@ -59,6 +122,7 @@ struct RopeFreqs {
 // x [T][n_heads][head_dim] with row stride ldx; one position per token.
 __global__ void rope_kernel(const float *__restrict__ x, size_t ldx, const int32_t *__restrict__ positions, int n_heads,
                             int head_dim, int neox, RopeFreqs freqs, float *__restrict__ out, size_t ldo) {
+    MCU_PDL_PROLOGUE();
     const int t = blockIdx.x;
     const int half = head_dim >> 1;
     const float pos = (float)positions[t];
@@ -75,18 +139,42 @@ __global__ void rope_kernel(const float *__restrict__ x, size_t ldx, const int32
     }
 }
 
+// The same for the query and key projections of a token in one launch, in place.
+__global__ void rope_qk_kernel(float *__restrict__ q, size_t ldq, int n_q_heads, float *__restrict__ k, size_t ldk,
+                               int n_k_heads, const int32_t *__restrict__ positions, int head_dim, int neox,
+                               RopeFreqs freqs) {
+    MCU_PDL_PROLOGUE();
+    const int t = blockIdx.x;
+    const int half = head_dim >> 1;
+    const float pos = (float)positions[t];
+    for (int idx = threadIdx.x; idx < (n_q_heads + n_k_heads) * half; idx += blockDim.x) {
+        const int hh = idx / half, i = idx - hh * half;
+        float s, c;
+        sincosf(__fmul_rn(pos, freqs.f[i]), &s, &c);
+        const int e = neox ? i : 2 * i, o = neox ? i + half : 2 * i + 1;
+        float *row = hh < n_q_heads ? q + (size_t)t * ldq + (size_t)hh * head_dim
+                                    : k + (size_t)t * ldk + (size_t)(hh - n_q_heads) * head_dim;
+        const float xe = row[e], xo = row[o];
+        row[e] = __fsub_rn(__fmul_rn(xe, c), __fmul_rn(xo, s));
+        row[o] = __fadd_rn(__fmul_rn(xe, s), __fmul_rn(xo, c));
+    }
+}
+
 // ---------------------------------------------------------------- elementwise
 __global__ void swiglu_kernel(const float *__restrict__ a, const float *__restrict__ b, size_t n, float *__restrict__ out) {
+    MCU_PDL_PROLOGUE();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __fmul_rn(__fdiv_rn(a[i], __fadd_rn(1.0f, expf(-a[i]))), b[i]);
 }
 __global__ void add_kernel(const float *__restrict__ a, const float *__restrict__ b, size_t n, float *__restrict__ out) {
+    MCU_PDL_PROLOGUE();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __fadd_rn(a[i], b[i]);
 }
 
 // argmax over the last axis, first maximum wins; one CTA per row
 __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ x, int n, int32_t *__restrict__ out) {
+    MCU_PDL_PROLOGUE();
     __shared__ float bv[8];
     __shared__ int bi[8];
     const float *xr = x + (size_t)blockIdx.x * n;
@@ -143,6 +231,7 @@ __device__ __forceinline__ void kv_store(__half *p, float v) { *p = __float2half
 // conversions).  grid (T, kv_heads), threads over head_dim.
 template <typename KV>
 __global__ void kv_append_kernel(PagedParams p, int head_dim) {
+    MCU_PDL_PROLOGUE();
     const int t = blockIdx.x, h = blockIdx.y;
     const uint32_t kv_slot = p.meta[t * 4 + 2];
     const size_t bs = (size_t)1 << p.block_shift;
@@ -203,6 +292,7 @@ __global__ void __launch_bounds__(32 * PA_MAX_GROUP) paged_attention_kernel(Page
     __shared__ __align__(16) uint8_t s_buf[SMEM_BYTES];  // K tile | V tile; reused for the group states at the end
     __shared__ float s_m[PA_MAX_GROUP][4], s_l[PA_MAX_GROUP][4];
     __shared__ int s_live[PA_TILE];
+    MCU_PDL_PROLOGUE();
     const int h = blockIdx.x, t = blockIdx.y, c = blockIdx.z, n_chunks = gridDim.z;
     const uint32_t kv_len = p.meta[t * 4 + 1] + 1u;
     const uint32_t p0 = (uint32_t)c * (uint32_t)chunk;
@@ -301,9 +391,222 @@ __global__ void __launch_bounds__(32 * PA_MAX_GROUP) paged_attention_kernel(Page
     }
 }
 
+// ---------------------------------------------------------------- f16-pool attention on the tensor cores
+// The same split-KV scheme for f16 pools with the two products on mma.sync m16n8k16 (f16 in, f32 accumulate).
+// One CTA per (KV head, token, chunk of 128 positions); each of its four warps owns one tile of 32 positions: it
+// copies the tile's K and V rows into its own shared-memory slice with cp.async (16-byte pieces, XOR-swizzled by row
+// so that ldmatrix reads are conflict-free), and meanwhile builds the A fragments of Q.  The M rows of the MMA are
+// the query heads of the KV head's group (at most 8; rows 8..15 are zero), so a K/V byte is read from HBM once for
+// the whole group and scored by one instruction stream.
+//   S = Q K^T : A = Q (heads x dims), B = K rows as they lie in the pool (ldmatrix, no transpose)
+//   O = P V   : A = P straight from the S accumulators, B = V through ldmatrix.trans
+// Q and P are split into an f16 head and an f16 tail (x = hi + lo, two MMAs each), K and V are f16 already, so the
+// products carry about 22 significant bits and the result stays within 1e-6 of f32 arithmetic.
+// A warp sees exactly one tile, so its softmax needs no running rescale; the four warps' states are merged through
+// shared memory in warp order and written as one partial state per (token, query head, chunk).
+constexpr int PM_WARPS = 4;
+constexpr int PM_TILE = 32;
+constexpr int PM_CHUNK = PM_WARPS * PM_TILE;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+// D += A B with the lower eight rows of A zero (a1 = a3 = 0).
+__device__ __forceinline__ void mma_top_rows(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+// (x, y) as an f16 pair plus the f16 pair of what that rounding lost.
+__device__ __forceinline__ void split_half2(float x, float y, uint32_t &hi, uint32_t &lo) {
+    const __half2 h = __floats2half2_rn(x, y);
+    const float2 f = __half22float2(h);
+    const __half2 t = __floats2half2_rn(x - f.x, y - f.y);
+    hi = *(const uint32_t *)&h;
+    lo = *(const uint32_t *)&t;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(PagedParams p, float *partial) {
+    constexpr int ROWB = HD * 2;            // bytes of a K or V row
+    constexpr int PIECES = ROWB / 16;       // 16-byte pieces per row
+    constexpr int TILEB = PM_TILE * ROWB;
+    constexpr int KS = HD / 16;             // k steps of Q K^T
+    constexpr int NT = HD / 8;              // n tiles of P V
+    extern __shared__ __align__(128) uint8_t pm_smem[];  // [warp][K tile | V tile]; reused for the warps' states
+    MCU_PDL_PROLOGUE();
+    const int h = blockIdx.x, t = blockIdx.y, c = blockIdx.z, n_chunks = gridDim.z;
+    const uint32_t kv_len = p.meta[t * 4 + 1] + 1u;
+    const uint32_t p0 = (uint32_t)c * PM_CHUNK;
+    if (p0 >= kv_len) return;
+    const uint32_t p1 = min(kv_len, p0 + (uint32_t)PM_CHUNK);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, tq = lane & 3;
+    const int gsize = p.n_q_heads / p.n_kv_heads;
+    const uint32_t seq = p.meta[t * 4 + 0];
+    const size_t bs = (size_t)1 << p.block_shift;
+    const size_t s3 = HD, s2 = bs * s3, s1 = (size_t)p.n_kv_heads * s2, s0 = (size_t)p.n_layers * s1;
+    const size_t head_off = (size_t)p.layer * s1 + (size_t)h * s2;
+    const uint32_t *table = p.table + (size_t)seq * p.max_blocks;
+    const uint32_t sK = (uint32_t)__cvta_generic_to_shared(pm_smem) + (uint32_t)(warp * 2 * TILEB);
+    const uint32_t sV = sK + TILEB;
+    const uint32_t k0 = p0 + (uint32_t)(warp * PM_TILE);  // this warp's positions [k0, k0 + 32)
+    const bool has_tile = k0 < p1;                        // uniform over the warp
+
+    // stage the tile: lane r looks up the pool block of position k0 + r, the warp copies two rows per step
+    uint32_t live = 0;
+    if (has_tile) {
+        const uint32_t pos = k0 + (uint32_t)lane, lb = pos >> p.block_shift;
+        uint32_t tb = 0xFFFFFFFFu;
+        if (pos < p1 && lb < (uint32_t)p.max_blocks) tb = table[lb];
+        live = __ballot_sync(0xffffffffu, tb != 0xFFFFFFFFu);
+        const size_t row_base = tb != 0xFFFFFFFFu ? (size_t)tb * s0 + head_off + (size_t)(pos & (uint32_t)(bs - 1)) * s3 : 0;
+#pragma unroll 4
+        for (int idx = lane; idx < PM_TILE * PIECES; idx += 32) {
+            const int r = idx / PIECES, pc = idx - r * PIECES;
+            const unsigned long long base = __shfl_sync(0xffffffffu, (unsigned long long)row_base, r);
+            const uint32_t off = (uint32_t)(r * ROWB + ((pc ^ (r & 7)) << 4));
+            if ((live >> r) & 1u) {
+                cp_async16(sK + off, (const __half *)p.kv_k + base + pc * 8);
+                cp_async16(sV + off, (const __half *)p.kv_v + base + pc * 8);
+            } else {  // never scored, but 0 * garbage must not become NaN
+                asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(sK + off), "r"(0u) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(sV + off), "r"(0u) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+
+    // A fragments of Q (row g = query head g of the group): a0 = dims 16s + 2tq, +1; a2 = dims 16s + 8 + 2tq, +1
+    uint32_t qhi[KS][2], qlo[KS][2];
+    {
+        const bool head_ok = g < gsize;
+        const float *qrow = p.q + ((size_t)t * p.n_q_heads + (size_t)h * gsize + (head_ok ? g : 0)) * HD;
+#pragma unroll
+        for (int s = 0; s < KS; ++s)
+#pragma unroll
+            for (int hk = 0; hk < 2; ++hk) {
+                float x = head_ok ? qrow[16 * s + 8 * hk + 2 * tq] : 0.0f;
+                float y = head_ok ? qrow[16 * s + 8 * hk + 2 * tq + 1] : 0.0f;
+                if (p.scale != 1.0f) {
+                    x = __fmul_rn(x, p.scale);
+                    y = __fmul_rn(y, p.scale);
+                }
+                split_half2(x, y, qhi[s][hk], qlo[s][hk]);
+            }
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+    float m = -INFINITY, l = 0.0f;
+    if (has_tile) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+        // S[head g][key 8j + 2tq, +1] in sc[j][0..1]
+        float sc[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
+#pragma unroll
+            for (int s = 0; s < KS; s += 2) {
+                // matrices: (keys 8j.., piece 2s), (piece 2s+1), (piece 2s+2), (piece 2s+3)
+                const int r = 8 * j + (lane & 7), pc = 2 * s + (lane >> 3);
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(sK + (uint32_t)(r * ROWB + ((pc ^ (r & 7)) << 4)), b0, b1, b2, b3);
+                mma_top_rows(sc[j], qhi[s][0], qhi[s][1], b0, b1);
+                mma_top_rows(sc[j], qlo[s][0], qlo[s][1], b0, b1);
+                mma_top_rows(sc[j], qhi[s + 1][0], qhi[s + 1][1], b2, b3);
+                mma_top_rows(sc[j], qlo[s + 1][0], qlo[s + 1][1], b2, b3);
+            }
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                if (!((live >> (8 * j + 2 * tq + e)) & 1u)) sc[j][e] = -INFINITY;
+                mx = fmaxf(mx, sc[j][e]);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        uint32_t phi[4], plo[4];
+        float psum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float w0 = mx == -INFINITY ? 0.0f : expf(sc[j][0] - mx);
+            const float w1 = mx == -INFINITY ? 0.0f : expf(sc[j][1] - mx);
+            psum += w0 + w1;
+            split_half2(w0, w1, phi[j], plo[j]);
+        }
+        psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+        m = mx;
+        l = psum;
+        // O[head g][dim 8n + 2tq, +1] += P V
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int n = 0; n < NT; n += 2) {
+                // matrices: (keys 16u.., piece n), (keys 16u+8.., piece n), (keys 16u.., piece n+1), (keys 16u+8.., piece n+1)
+                const int mi = lane >> 3;
+                const int r = 16 * u + 8 * (mi & 1) + (lane & 7), pc = n + (mi >> 1);
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_trans(sV + (uint32_t)(r * ROWB + ((pc ^ (r & 7)) << 4)), b0, b1, b2, b3);
+                mma_top_rows(o[n], phi[2 * u], phi[2 * u + 1], b0, b1);
+                mma_top_rows(o[n], plo[2 * u], plo[2 * u + 1], b0, b1);
+                mma_top_rows(o[n + 1], phi[2 * u], phi[2 * u + 1], b2, b3);
+                mma_top_rows(o[n + 1], plo[2 * u], plo[2 * u + 1], b2, b3);
+            }
+    }
+    // merge the warps' states: the tile slices are free once every warp is past its MMAs
+    __syncthreads();
+    float *s_o = (float *)pm_smem;                                        // [warp][8 heads][HD]
+    float *s_m = s_o + PM_WARPS * 8 * HD, *s_l = s_m + PM_WARPS * 8;      // [warp][8 heads]
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+        *(float2 *)(s_o + ((size_t)warp * 8 + g) * HD + 8 * n + 2 * tq) = make_float2(o[n][0], o[n][1]);
+    if (tq == 0) {
+        s_m[warp * 8 + g] = m;
+        s_l[warp * 8 + g] = l;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < gsize * HD; idx += blockDim.x) {
+        const int hh = idx / HD, d = idx - hh * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < PM_WARPS; ++w) M = fmaxf(M, s_m[w * 8 + hh]);
+        float L = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int w = 0; w < PM_WARPS; ++w) {
+            const float mw = s_m[w * 8 + hh];
+            const float e = (M == -INFINITY || mw == -INFINITY) ? 0.0f : expf(mw - M);
+            L += s_l[w * 8 + hh] * e;
+            O += s_o[((size_t)w * 8 + hh) * HD + d] * e;
+        }
+        float *pr = partial + (((size_t)t * p.n_q_heads + (size_t)h * gsize + hh) * n_chunks + c) * (HD + 2);
+        if (d == 0) {
+            pr[0] = M;
+            pr[1] = L;
+        }
+        pr[2 + d] = O;
+    }
+}
+
 // out[t][qh][:] from the chunk states; grid (query heads, tokens), HD threads.
 template <int HD>
 __global__ void paged_attention_merge_kernel(PagedParams p, int chunk, int n_chunks, const float *partial) {
+    MCU_PDL_PROLOGUE();
     const int qh = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
     const uint32_t kv_len = p.meta[t * 4 + 1] + 1u;
     const int live = min(n_chunks, (int)((kv_len + (uint32_t)chunk - 1u) / (uint32_t)chunk));
@@ -353,8 +656,8 @@ int mcu_rmsnorm(mcu_context_t *ctx, const float *x_dev, const float *residual_de
     if (rows == 0 || n == 0) return MCU_SUCCESS;
     if (x_dev == nullptr || out_dev == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "null tensor data");
     if (n > (size_t)1 << 30 || rows > (size_t)1 << 30) return set_error(MCU_ERROR_INVALID_ARGUMENT, "dimension too large");
-    rmsnorm_kernel<<<(unsigned)rows, 256, 0, s>>>(x_dev, residual_dev, weight_dev, (int)n, eps, weight_offset, out_dev);
-    DEC_CUDA(cudaGetLastError());
+    DEC_CUDA(launch_pdl(rmsnorm_kernel, dim3((unsigned)rows), dim3(256), s, x_dev, residual_dev, weight_dev, (int)n, eps,
+                        weight_offset, out_dev));
     count_launches(1);
     return MCU_SUCCESS;
 }
@@ -375,9 +678,43 @@ int mcu_rope(mcu_context_t *ctx, const float *x_dev, size_t ldx, const int32_t *
     RopeFreqs fr;
     for (size_t i = 0; i < head_dim / 2; ++i)
         fr.f[i] = powf(theta, -((float)(2 * i) / (float)head_dim)) * freq_scale;  // src/core/helpers/rope.c:111
-    rope_kernel<<<(unsigned)T, 128, 0, s>>>(x_dev, ldx, positions_dev, (int)n_heads, (int)head_dim,
-                                            rope_type == MCU_ROPE_NEOX ? 1 : 0, fr, out_dev, ldo);
-    DEC_CUDA(cudaGetLastError());
+    DEC_CUDA(launch_pdl(rope_kernel, dim3((unsigned)T), dim3(128), s, x_dev, ldx, positions_dev, (int)n_heads, (int)head_dim,
+                        rope_type == MCU_ROPE_NEOX ? 1 : 0, fr, out_dev, ldo));
+    count_launches(1);
+    return MCU_SUCCESS;
+}
+
+int mcu_add_rmsnorm(mcu_context_t *ctx, const float *x_dev, const float *delta_dev, const float *weight_dev, size_t rows,
+                    size_t n, float eps, float weight_offset, float *x_out_dev, float *h_out_dev) {
+    cudaStream_t s;
+    if (int rc = dec_begin(ctx, &s)) return rc;
+    if (rows == 0 || n == 0) return MCU_SUCCESS;
+    if (x_dev == nullptr || delta_dev == nullptr || x_out_dev == nullptr || h_out_dev == nullptr)
+        return set_error(MCU_ERROR_INVALID_ARGUMENT, "null tensor data");
+    if (n > (size_t)1 << 30 || rows > (size_t)1 << 30) return set_error(MCU_ERROR_INVALID_ARGUMENT, "dimension too large");
+    DEC_CUDA(launch_pdl(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(256), s, x_dev, delta_dev, weight_dev, (int)n, eps,
+                        weight_offset, x_out_dev, h_out_dev));
+    count_launches(1);
+    return MCU_SUCCESS;
+}
+
+int mcu_rope_qk(mcu_context_t *ctx, float *q_dev, size_t ldq, size_t n_q_heads, float *k_dev, size_t ldk, size_t n_k_heads,
+                const int32_t *positions_dev, size_t T, size_t head_dim, float theta, float freq_scale, int rope_type) {
+    cudaStream_t s;
+    if (int rc = dec_begin(ctx, &s)) return rc;
+    if (T == 0 || n_q_heads + n_k_heads == 0) return MCU_SUCCESS;
+    if (q_dev == nullptr || k_dev == nullptr || positions_dev == nullptr)
+        return set_error(MCU_ERROR_INVALID_ARGUMENT, "null tensor data");
+    if (head_dim % 2 != 0) return set_error(MCU_ERROR_DIMENSION_MISMATCH, "RoPE requires even dimension");
+    if (head_dim / 2 > (size_t)ROPE_MAX_PAIRS) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "RoPE head_dim above 256");
+    if (rope_type != MCU_ROPE_NORM && rope_type != MCU_ROPE_NEOX)
+        return set_error(MCU_ERROR_NOT_IMPLEMENTED, "unknown RoPE type");
+    if (ldq < n_q_heads * head_dim || ldk < n_k_heads * head_dim)
+        return set_error(MCU_ERROR_DIMENSION_MISMATCH, "RoPE requires row strides >= feature dimension");
+    RopeFreqs fr;
+    for (size_t i = 0; i < head_dim / 2; ++i) fr.f[i] = powf(theta, -((float)(2 * i) / (float)head_dim)) * freq_scale;
+    DEC_CUDA(launch_pdl(rope_qk_kernel, dim3((unsigned)T), dim3(128), s, q_dev, ldq, (int)n_q_heads, k_dev, ldk,
+                        (int)n_k_heads, positions_dev, (int)head_dim, rope_type == MCU_ROPE_NEOX ? 1 : 0, fr));
     count_launches(1);
     return MCU_SUCCESS;
 }
@@ -388,8 +725,7 @@ int mcu_swiglu(mcu_context_t *ctx, const float *gate_dev, const float *up_dev, s
     if (n == 0) return MCU_SUCCESS;
     if (gate_dev == nullptr || up_dev == nullptr || out_dev == nullptr)
         return set_error(MCU_ERROR_INVALID_ARGUMENT, "null tensor data");
-    swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(gate_dev, up_dev, n, out_dev);
-    DEC_CUDA(cudaGetLastError());
+    DEC_CUDA(launch_pdl(swiglu_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), s, gate_dev, up_dev, n, out_dev));
     count_launches(1);
     return MCU_SUCCESS;
 }
@@ -400,8 +736,7 @@ int mcu_add(mcu_context_t *ctx, const float *a_dev, const float *b_dev, size_t n
     if (n == 0) return MCU_SUCCESS;
     if (a_dev == nullptr || b_dev == nullptr || out_dev == nullptr)
         return set_error(MCU_ERROR_INVALID_ARGUMENT, "null tensor data");
-    add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a_dev, b_dev, n, out_dev);
-    DEC_CUDA(cudaGetLastError());
+    DEC_CUDA(launch_pdl(add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), s, a_dev, b_dev, n, out_dev));
     count_launches(1);
     return MCU_SUCCESS;
 }
@@ -411,8 +746,7 @@ int mcu_argmax(mcu_context_t *ctx, const float *x_dev, size_t rows, size_t n, in
     if (int rc = dec_begin(ctx, &s)) return rc;
     if (rows == 0) return MCU_SUCCESS;
     if (x_dev == nullptr || out_dev == nullptr || n == 0) return set_error(MCU_ERROR_INVALID_ARGUMENT, "null tensor data");
-    argmax_kernel<<<(unsigned)rows, 256, 0, s>>>(x_dev, (int)n, out_dev);
-    DEC_CUDA(cudaGetLastError());
+    DEC_CUDA(launch_pdl(argmax_kernel, dim3((unsigned)rows), dim3(256), s, x_dev, (int)n, out_dev));
     count_launches(1);
     return MCU_SUCCESS;
 }
@@ -475,8 +809,11 @@ int mcu_paged_attention(mcu_context_t *ctx, const uint32_t *token_meta_dev, size
     // even for one short sequence.  The context length lives in device memory, so the grid covers the longest
     // context the block table allows; CTAs beyond a token's length return at once.
     const size_t max_positions = max_blocks_per_seq * block_size;
-    size_t chunk = 256;
-    while (chunk > 32 && n_kv_heads * T * ((max_positions + chunk - 1) / chunk) < 2 * (size_t)device_sm_count()) chunk /= 2;
+    const bool mma_path = kv_dtype == MCU_KV_F16;  // f16 pools: tensor-core kernel, fixed 128-position chunks
+    size_t chunk = mma_path ? (size_t)PM_CHUNK : 256;
+    while (!mma_path && chunk > 32 &&
+           n_kv_heads * T * ((max_positions + chunk - 1) / chunk) < 2 * (size_t)device_sm_count())
+        chunk /= 2;
     const size_t n_chunks = (max_positions + chunk - 1) / chunk;
     if (n_chunks > 65535) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "paged_attention context bound too long");
     void *scratch = nullptr;
@@ -486,18 +823,27 @@ int mcu_paged_attention(mcu_context_t *ctx, const uint32_t *token_meta_dev, size
     const dim3 ag((unsigned)T, (unsigned)n_kv_heads), qg((unsigned)n_kv_heads, (unsigned)T, (unsigned)n_chunks);
     const dim3 mg((unsigned)n_q_heads, (unsigned)T);
     const unsigned threads = 32u * (unsigned)(n_q_heads / n_kv_heads);
-    if (kv_dtype == MCU_KV_F16) {
-        kv_append_kernel<__half><<<ag, 128, 0, s>>>(p, (int)head_dim);
-        if (head_dim == 64) paged_attention_kernel<__half, 64><<<qg, threads, 0, s>>>(p, (int)chunk, partial);
-        else paged_attention_kernel<__half, 128><<<qg, threads, 0, s>>>(p, (int)chunk, partial);
+    const dim3 tb(threads);
+    if (mma_path) {
+        const size_t smem = (size_t)PM_WARPS * 2 * PM_TILE * head_dim * 2;  // >= the warps' merge states (8 heads each)
+        if (head_dim == 64)
+            DEC_CUDA(cudaFuncSetAttribute(paged_attention_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        else
+            DEC_CUDA(cudaFuncSetAttribute(paged_attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DEC_CUDA(launch_pdl(kv_append_kernel<__half>, ag, dim3(128), s, p, (int)head_dim));
+        if (head_dim == 64)
+            DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<64>, qg, dim3(32 * PM_WARPS), smem, s, p, partial));
+        else
+            DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<128>, qg, dim3(32 * PM_WARPS), smem, s, p, partial));
     } else {
-        kv_append_kernel<float><<<ag, 128, 0, s>>>(p, (int)head_dim);
-        if (head_dim == 64) paged_attention_kernel<float, 64><<<qg, threads, 0, s>>>(p, (int)chunk, partial);
-        else paged_attention_kernel<float, 128><<<qg, threads, 0, s>>>(p, (int)chunk, partial);
+        DEC_CUDA(launch_pdl(kv_append_kernel<float>, ag, dim3(128), s, p, (int)head_dim));
+        if (head_dim == 64) DEC_CUDA(launch_pdl(paged_attention_kernel<float, 64>, qg, tb, s, p, (int)chunk, partial));
+        else DEC_CUDA(launch_pdl(paged_attention_kernel<float, 128>, qg, tb, s, p, (int)chunk, partial));
     }
-    if (head_dim == 64) paged_attention_merge_kernel<64><<<mg, 64, 0, s>>>(p, (int)chunk, (int)n_chunks, partial);
-    else paged_attention_merge_kernel<128><<<mg, 128, 0, s>>>(p, (int)chunk, (int)n_chunks, partial);
-    DEC_CUDA(cudaGetLastError());
+    if (head_dim == 64)
+        DEC_CUDA(launch_pdl(paged_attention_merge_kernel<64>, mg, dim3(64), s, p, (int)chunk, (int)n_chunks, (const float *)partial));
+    else
+        DEC_CUDA(launch_pdl(paged_attention_merge_kernel<128>, mg, dim3(128), s, p, (int)chunk, (int)n_chunks, (const float *)partial));
     count_launches(3);
     return MCU_SUCCESS;
 }

@@ -50,8 +50,8 @@ def weight_bytes(shape: DecoderShape) -> int:
 
 
 class Decoder:
-    """Weights are given as host byte arrays (`weights[name]`, per layer `weights[f"l{i}.{name}"]`; single rank only)
-    or drawn on the device when `weights` is None (timing only).
+    """Weights are given as host byte arrays of the full model (`weights[name]`, per layer `weights[f"l{i}.{name}"]`;
+    each rank cuts its own share out of them) or drawn on the device when `weights` is None (timing only).
 
     Tensor parallel over the ranks of `group` (tensor_parallel.Group) with `comm` (runtime.PeerComm): query and KV
     heads, the FFN width (in 2048-value granules, so that the Q6_K down shards keep 16-byte rows) and the vocabulary
@@ -72,9 +72,9 @@ class Decoder:
         self.group = group or tp.Group()
         self.comm = comm
         world, rank = self.group.world, self.group.rank
+        full = shape
+        f_lo, f_hi, v_lo, v_hi = 0, shape.ffn, 0, shape.vocab
         if world > 1:
-            if weights is not None:
-                raise NotImplementedError("tensor-parallel Decoder draws its own shard-shaped weights")
             if shape.n_kv_heads % world or shape.n_heads % world or comm is None:
                 raise ValueError("heads must divide over the ranks and a PeerComm is needed")
             f_lo, f_hi = tp.shard_range(shape.ffn, world, rank, 2048)
@@ -91,11 +91,31 @@ class Decoder:
         gen = torch.Generator(device=dev)
         gen.manual_seed(seed + 1000 * rank)
 
+        def cut(name, kind, w):
+            """This rank's share of a full-model matrix: heads, FFN rows and vocabulary rows are contiguous row ranges;
+            the two row-parallel matrices are cut along K (block columns repacked per row)."""
+            base = name.split(".")[-1]
+            if world == 1 or base == "tok_embd":
+                return w
+            if base in ("wq", "wk", "wv"):
+                F = (full.n_heads if base == "wq" else full.n_kv_heads) * full.head_dim
+                return tp.shard_rows(w, kind, F, full.d, world, rank, F // world)[0]
+            if base == "wo":
+                K = full.n_heads * full.head_dim
+                return tp.shard_k(w, kind, full.d, K, world, rank, K // world)[0]
+            if base in ("gate", "up"):
+                return tp.shard_rows(w, kind, full.ffn, full.d, world, rank, 2048)[0]
+            if base == "down":
+                return tp.shard_k(w, kind, full.d, full.ffn, world, rank, 2048)[0]
+            if base == "output":
+                return tp.shard_rows(w, kind, full.vocab, full.d, world, rank, 32)[0]
+            raise KeyError(name)
+
         def mat(name, kind, rows, cols):
-            if weights is not None:
-                return ctx.upload(weights[name])
             if rows == 0 or cols == 0:
                 return None
+            if weights is not None:
+                return ctx.upload(cut(name, kind, weights[name]))
             return synthetic_blocks_device(torch, kind, rows, cols, dev, gen)
 
         def vec(name, n):
@@ -186,24 +206,23 @@ class Decoder:
         att, proj = self._buf("att", (T, hq * hd)), self._buf("proj", (T, s.d))
         gate, up = self._buf("gate", (T, max(s.ffn, 1))), self._buf("up", (T, max(s.ffn, 1)))
         scale = float(hd) ** -0.5
+        # the residual add that ends a block and the rms_norm that opens the next one run as one kernel
+        ctx.rmsnorm(x, self.layers[0]["attn_norm"], s.rms_eps, out=h)
         for i, lw in enumerate(self.layers):
-            ctx.rmsnorm(x, lw["attn_norm"], s.rms_eps, out=h)
             ctx.linear(KIND_Q4_K, h, lw["wq"], hq * hd, out=q)
             ctx.linear(KIND_Q4_K, h, lw["wk"], hkv * hd, out=k)
             ctx.linear(KIND_Q6_K, h, lw["wv"], hkv * hd, out=v)
-            ctx.rope(q, positions, hq, hd, s.rope_theta, out=q)
-            ctx.rope(k, positions, hkv, hd, s.rope_theta, out=k)
+            ctx.rope_qk(q, k, positions, hq, hkv, hd, s.rope_theta)
             ctx.paged_attention(meta, q, k, v, self.kv_k, self.kv_v, self.block_table, i, hq, hkv, hd, self.block_size,
                                 scale, out=att)
             self._row_parallel(KIND_Q4_K, att, lw["wo"], s.d, proj, hq * hd)
-            ctx.add(x, proj, out=x)
-            ctx.rmsnorm(x, lw["ffn_norm"], s.rms_eps, out=h)
+            ctx.add_rmsnorm(x, proj, lw["ffn_norm"], s.rms_eps, x, h)
             if s.ffn > 0:
                 ctx.linear_dual(KIND_Q4_K, h, lw["gate"], lw["up"], s.ffn, out_a=gate, out_b=up)
                 ctx.swiglu(gate, up, out=gate)
             self._row_parallel(KIND_Q6_K, gate, lw["down"], s.d, proj, s.ffn)
-            ctx.add(x, proj, out=x)
-        ctx.rmsnorm(x, self.out_norm, s.rms_eps, out=h)
+            nxt = self.layers[i + 1]["attn_norm"] if i + 1 < len(self.layers) else self.out_norm
+            ctx.add_rmsnorm(x, proj, nxt, s.rms_eps, x, h)
         logits = logits_out if logits_out is not None else self._buf("logits", (T, self.local_vocab))
         ctx.linear(KIND_Q6_K, h, self.output, self.local_vocab, out=logits)
         return logits

@@ -1,7 +1,8 @@
-"""Run one quantized-linear shape a few times through the C ABI: the small, self-ending command that a
-profiler (ncu) or a quick timing wraps.
+"""Run one quantized-linear shape (or one paged-attention decode step) a few times through the C ABI: the small,
+self-ending command that a profiler (ncu) or a quick timing wraps.
 
     python -m marmot_b200.profile_case --kind q4_k -T 1 -K 4096 -F 4096 --copies 16 --iters 3
+    python -m marmot_b200.profile_case --op attention --seqs 64 --ctx 2048 --layers 4 --iters 2 --time
 
 The weights rotate over ``--copies`` distinct matrices so that a memory-bound kernel reads from HBM rather
 than from L2.  With ``--time`` the calls are also captured in a CUDA graph and replayed, and the average
@@ -43,8 +44,75 @@ def synthetic_blocks_device(torch, kind: int, rows: int, K: int, device, generat
     return blocks.reshape(-1)
 
 
+def attention_case(args) -> None:
+    """Decode-step attention: `seqs` sequences of `ctx` cached positions each, one new token per sequence, the layers of
+    the pool visited in turn (so that consecutive calls read different memory).  Pool bytes read per call:
+    2 (K and V) * seqs * (ctx + 1) * kv_heads * head_dim * element size."""
+    import torch
+
+    dev = torch.device("cuda", 0)
+    ctx = Context(0)
+    hq, hkv, hd, bs, L = args.q_heads, args.kv_heads, args.head_dim, 16, args.layers
+    kv_dtype = torch.float16 if args.kv == "f16" else torch.float32
+    per_seq = (args.ctx + 1 + bs - 1) // bs
+    n_blocks = args.seqs * per_seq
+    gen = torch.Generator(device=dev).manual_seed(0)
+    kv_k = torch.randn((n_blocks, L, hkv, bs, hd), device=dev, generator=gen).to(kv_dtype)
+    kv_v = torch.randn((n_blocks, L, hkv, bs, hd), device=dev, generator=gen).to(kv_dtype)
+    table = torch.arange(n_blocks, dtype=torch.int32, device=dev).view(args.seqs, per_seq).contiguous()
+    meta = np.zeros((args.seqs, 4), dtype=np.uint32)
+    meta[:, 0] = np.arange(args.seqs)
+    meta[:, 1] = args.ctx
+    meta[:, 2] = np.arange(args.seqs) * per_seq * bs + args.ctx
+    meta = torch.from_numpy(meta.view(np.int32)).to(dev)
+    q = torch.randn((args.seqs, hq * hd), device=dev, generator=gen)
+    k = torch.randn((args.seqs, hkv * hd), device=dev, generator=gen)
+    v = torch.randn((args.seqs, hkv * hd), device=dev, generator=gen)
+    out = torch.empty_like(q)
+
+    def one_pass():
+        for layer in range(L):
+            ctx.paged_attention(meta, q, k, v, kv_k, kv_v, table, layer, hq, hkv, hd, bs, hd ** -0.5, out=out)
+
+    stream = torch.cuda.Stream(dev)
+    ctx.set_stream(stream.cuda_stream)
+    with torch.cuda.stream(stream):
+        for _ in range(args.iters):
+            one_pass()
+    torch.cuda.synchronize()
+    nbytes = 2 * args.seqs * (args.ctx + 1) * hkv * hd * kv_k.element_size()
+    print(f"attention seqs={args.seqs} ctx={args.ctx} heads={hq}/{hkv}x{hd} kv={args.kv}: {L} layers, {args.iters} passes, "
+          f"{ctx.launch_count()} kernel launches, {nbytes} pool bytes per call, pool {2 * kv_k.numel() * kv_k.element_size() >> 20} MiB")
+    if args.time:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * L)
+        print(f"{us:.2f} us per call (append + attention + merge), {nbytes / us / 1e3:.0f} GB/s of pool bytes")
+    ctx.set_stream(0)
+    ctx.close()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--op", default="linear", choices=["linear", "attention"])
+    ap.add_argument("--seqs", type=int, default=64, help="attention: sequences (one new token each)")
+    ap.add_argument("--ctx", type=int, default=2048, help="attention: cached positions per sequence")
+    ap.add_argument("--layers", type=int, default=4, help="attention: layers in the pool, visited in turn")
+    ap.add_argument("--q-heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--kv", default="f16", choices=["f16", "f32"])
     ap.add_argument("--kind", default="q4_k", choices=sorted(KIND_BY_NAME))
     ap.add_argument("-T", type=int, default=1, help="tokens")
     ap.add_argument("-K", type=int, default=4096, help="reduction length")
@@ -54,6 +122,8 @@ def main() -> None:
     ap.add_argument("--regime", default="auto", choices=sorted(REGIMES))
     ap.add_argument("--time", action="store_true", help="also replay a CUDA graph of one pass and print us per call")
     args = ap.parse_args()
+    if args.op == "attention":
+        return attention_case(args)
 
     import torch
 

@@ -27,7 +27,7 @@ EXPORTS = (
     "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_peer_comm_create", "mcu_peer_comm_export",
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
     "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
-    "mcu_embedding_gather", "mcu_paged_attention",
+    "mcu_embedding_gather", "mcu_paged_attention", "mcu_add_rmsnorm", "mcu_rope_qk",
 )
 
 
@@ -97,6 +97,8 @@ def load_library() -> C.CDLL:
     L.mcu_rmsnorm.argtypes = [vp, vp, vp, vp, sz, sz, f32, f32, vp]
     L.mcu_rope.argtypes = [vp, vp, sz, vp, sz, sz, sz, f32, f32, i32, vp, sz]
     L.mcu_swiglu.argtypes = [vp, vp, vp, sz, vp]
+    L.mcu_add_rmsnorm.argtypes = [vp, vp, vp, vp, sz, sz, f32, f32, vp, vp]
+    L.mcu_rope_qk.argtypes = [vp, vp, sz, sz, vp, sz, sz, vp, sz, sz, f32, f32, i32]
     L.mcu_add.argtypes = [vp, vp, vp, sz, vp]
     L.mcu_argmax.argtypes = [vp, vp, sz, sz, vp]
     L.mcu_embedding_gather.argtypes = [vp, i32, vp, sz, vp, sz, vp]
@@ -245,6 +247,20 @@ class Context:
         self._check(self.lib.mcu_rope(self.handle, _ptr(x), x.stride(0), _ptr(positions), T, n_heads, head_dim, theta,
                                       freq_scale, 1 if neox else 0, _ptr(out), out.stride(0)))
         return out
+
+    def add_rmsnorm(self, x, delta, weight, eps: float, x_out, h_out, weight_offset: float = 0.0):
+        """x_out = x + delta; h_out = rmsnorm(x_out) * weight (x_out may be x)."""
+        rows, n = x.shape
+        self._check(self.lib.mcu_add_rmsnorm(self.handle, _ptr(x), _ptr(delta), _ptr(weight), rows, n, eps, weight_offset,
+                                             _ptr(x_out), _ptr(h_out)))
+        return x_out, h_out
+
+    def rope_qk(self, q, k, positions, n_q_heads: int, n_k_heads: int, head_dim: int, theta: float = 10000.0,
+                freq_scale: float = 1.0, neox: bool = False):
+        """RoPE in place on q [T, n_q_heads*head_dim] and k [T, n_k_heads*head_dim]."""
+        self._check(self.lib.mcu_rope_qk(self.handle, _ptr(q), q.stride(0), n_q_heads, _ptr(k), k.stride(0), n_k_heads,
+                                         _ptr(positions), q.shape[0], head_dim, theta, freq_scale, 1 if neox else 0))
+        return q, k
 
     def swiglu(self, gate, up, out=None):
         if out is None:

@@ -57,6 +57,33 @@ def test_rope(ctx, oracle, heads, hd, theta, neox):
     assert np.array_equal(xd.cpu().numpy(), got)
 
 
+@pytest.mark.parametrize("rows,n", [(1, 2048), (64, 4096), (5, 37)])
+def test_add_rmsnorm_is_add_then_rmsnorm(ctx, oracle, rows, n):
+    rng = np.random.default_rng(rows + n)
+    x = rng.normal(0, 2, (rows, n)).astype(np.float32)
+    delta = rng.normal(0, 1, (rows, n)).astype(np.float32)
+    w = rng.normal(1, 0.1, n).astype(np.float32)
+    xd, h = dev(x), torch.empty((rows, n), dtype=torch.float32, device="cuda")
+    ctx.add_rmsnorm(xd, dev(delta), dev(w), 1e-5, xd, h)  # residual stream updated in place
+    assert np.array_equal(xd.cpu().numpy(), x + delta)
+    assert rel(h.cpu().numpy(), oracle.rmsnorm(x + delta, w, 1e-5)) <= 1e-5
+    # the very bits of the two separate operators
+    two = ctx.rmsnorm(ctx.add(dev(x), dev(delta)), dev(w), 1e-5)
+    assert torch.equal(h, two)
+
+
+@pytest.mark.parametrize("hq,hkv,hd,neox", [(32, 4, 64, False), (32, 8, 128, False), (4, 4, 64, True)])
+def test_rope_qk_is_two_ropes(ctx, hq, hkv, hd, neox):
+    rng = np.random.default_rng(hq + hd)
+    pos = dev(np.array([0, 3, 100, 2047], dtype=np.int32))
+    q = dev(rng.normal(0, 1, (4, hq * hd)).astype(np.float32))
+    k = dev(rng.normal(0, 1, (4, hkv * hd)).astype(np.float32))
+    want_q = ctx.rope(q, pos, hq, hd, 500000.0, 1.0, neox)
+    want_k = ctx.rope(k, pos, hkv, hd, 500000.0, 1.0, neox)
+    ctx.rope_qk(q, k, pos, hq, hkv, hd, 500000.0, 1.0, neox)
+    assert torch.equal(q, want_q) and torch.equal(k, want_k)
+
+
 def test_swiglu_add_argmax_embedding(ctx, oracle):
     rng = np.random.default_rng(3)
     a, b = rng.normal(0, 3, 5000).astype(np.float32), rng.normal(0, 1, 5000).astype(np.float32)

@@ -92,6 +92,41 @@ def main() -> int:
         e = float(max_rel_err(y.cpu().numpy(), want))
         check(f"moe_{name}", e <= TOL_MOE, e)
 
+    # a whole decoder step: every rank cuts its share out of the same full-model weights; logits slices and the greedy
+    # pick must match the single-GPU decoder on the full weights (only the f32 order of the row-parallel sums differs)
+    from marmot_b200.decoder import LAYER_WEIGHTS, Decoder, DecoderShape
+
+    shape = DecoderShape(layers=2, d=512, ffn=4096, n_heads=16, n_kv_heads=8, head_dim=128, vocab=1024)
+    wrng = np.random.default_rng(7)
+    weights = {}
+    for i in range(shape.layers):
+        for name, kind, rows, cols in LAYER_WEIGHTS:
+            weights[f"l{i}.{name}"] = random_blocks(kind, rows(shape), cols(shape), wrng, d_sigma=0.0003)
+        weights[f"l{i}.attn_norm"] = wrng.normal(1, 0.1, shape.d).astype(np.float32)
+        weights[f"l{i}.ffn_norm"] = wrng.normal(1, 0.1, shape.d).astype(np.float32)
+    weights["tok_embd"] = random_blocks(KIND_Q4_K, shape.vocab, shape.d, wrng, d_sigma=0.003)
+    weights["output"] = random_blocks(KIND_Q6_K, shape.vocab, shape.d, wrng, d_sigma=0.0003)
+    weights["out_norm"] = wrng.normal(1, 0.1, shape.d).astype(np.float32)
+    if shape.n_kv_heads % world == 0:
+        one = Decoder(ctx, shape, max_seqs=2, max_ctx=64, weights=weights)
+        many = Decoder(ctx, shape, max_seqs=2, max_ctx=64, weights=weights, group=group, comm=comm)
+        ids = torch.from_numpy(wrng.integers(0, shape.vocab, 5).astype(np.int32)).to(dev)
+        pos_np = np.arange(5, dtype=np.int32)
+        for step in range(3):
+            pos = torch.from_numpy(pos_np).to(dev)
+            meta = torch.from_numpy(one.token_meta([1] * len(pos_np), pos_np)).to(dev)
+            want = one.step(ids, meta, pos).clone()
+            got = many.step(ids, meta, pos)
+            ctx.synchronize()
+            e = float(max_rel_err(got.cpu().numpy(), want[:, many.v_lo:many.v_lo + many.local_vocab].cpu().numpy()))
+            check(f"decoder_logits_{step}", e <= 5 * TOL_FP32, e)
+            pick = torch.empty(len(pos_np), dtype=torch.int32, device=dev)
+            many.greedy(got, pick)
+            ctx.synchronize()
+            check(f"decoder_greedy_{step}", torch.equal(pick.long(), want.argmax(dim=1)))
+            ids = pick[-1:].clone()
+            pos_np = pos_np[-1:] + 1
+
     # a peer that never arrives: the bounded wait gives up and the error reaches the host; nothing hangs
     dist.barrier()
     torch.cuda.synchronize()
