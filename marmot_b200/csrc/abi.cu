@@ -267,7 +267,7 @@ static int validate_linear(int kind, const void *x, const void *w, const void *o
 
 // Quantize the activations into the context workspace.
 static int pack_activations(mcu_context *ctx, int kind, const float *x, size_t ldx, size_t T, size_t K, bool want_half,
-                            bool k_perm, ActBuffers &ab) {
+                            int k_order, ActBuffers &ab) {
     const size_t bv = (size_t)block_values(kind);
     const size_t nb = (K + bv - 1) / bv, kp = nb * bv;
     if (int rc = ensure(ctx, ctx->act_qs, T * kp)) return rc;
@@ -284,7 +284,7 @@ static int pack_activations(mcu_context *ctx, int kind, const float *x, size_t l
     MCU_CUDA(launch_quantize_act(kind, x, (int)ldx, (int)T, (int)K, ab, nullptr, ctx->stream));
     count_launches(1);
     if (want_half) {
-        MCU_CUDA(launch_half_acts(kind, ab, (int)T, (int)K, k_perm, (__half *)ctx->act_half.ptr,
+        MCU_CUDA(launch_half_acts(kind, ab, (int)T, (int)K, k_order, (__half *)ctx->act_half.ptr,
                                   (float *)ctx->act_rowscale.ptr, ctx->stream));
         count_launches(1);
     }
@@ -300,19 +300,29 @@ static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx,
     if (gemm) {
         if (gemm_tc_supported(kind, (int)T, (int)K, (int)F)) {
             const bool tma = gemm_tma_supported(kind, w, w2, (int)T, (int)K, (int)F);
+            const bool warp_mma = gemm_warp_supported(kind, w, w2, (int)T, (int)K, (int)F);
+            const int k_order = warp_mma ? ACT_ORDER_FRAG16 : tma ? ACT_ORDER_QUAD : ACT_ORDER_NATURAL;
             const size_t bv = (size_t)block_values(kind);
             const size_t kp = (K + bv - 1) / bv * bv;
             if (act_half_fused_smem(kind, (int)K) <= 48 * 1024) {
                 if (int rc = ensure(ctx, ctx->act_half, T * kp * sizeof(__half))) return rc;
                 if (int rc = ensure(ctx, ctx->act_rowscale, T * sizeof(float))) return rc;
-                MCU_CUDA(launch_act_half_fused(kind, x, (int)ldx, (int)T, (int)K, tma, (__half *)ctx->act_half.ptr,
+                MCU_CUDA(launch_act_half_fused(kind, x, (int)ldx, (int)T, (int)K, k_order, (__half *)ctx->act_half.ptr,
                                                (float *)ctx->act_rowscale.ptr, ctx->stream));
                 count_launches(1);
-            } else if (int rc = pack_activations(ctx, kind, x, ldx, T, K, true, tma, ab)) {
+            } else if (int rc = pack_activations(ctx, kind, x, ldx, T, K, true, k_order, ab)) {
                 return rc;
             }
             int launches = 0;
-            if (tma) {
+            if (warp_mma) {
+                if (int rc = ensure(ctx, ctx->gemm_partial, gemm_warp_workspace_bytes(kind, (int)T, (int)K, (int)F, w2 != nullptr)))
+                    return rc;
+                MCU_CUDA(launch_gemm_warp(kind, w, w2, (const __half *)ctx->act_half.ptr,
+                                          (const float *)ctx->act_rowscale.ptr, (int)kp, (int)T, (int)K, (int)F, bias, out,
+                                          out2, (int)ldo, (float *)ctx->gemm_partial.ptr, ctx->gemm_counters, ctx->dev_err,
+                                          ctx->stream));
+                launches = 1;
+            } else if (tma) {
                 if (int rc = ensure(ctx, ctx->gemm_partial, gemm_tma_workspace_bytes(kind, (int)T, (int)K, (int)F))) return rc;
                 MCU_CUDA(launch_gemm_tma(kind, w, w2, (const __half *)ctx->act_half.ptr,
                                          (const float *)ctx->act_rowscale.ptr, (int)kp, (int)T, (int)K, (int)F,
@@ -336,7 +346,7 @@ static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx,
         count_launches(1);
         return MCU_SUCCESS;
     }
-    if (int rc = pack_activations(ctx, kind, x, ldx, T, K, false, false, ab)) return rc;
+    if (int rc = pack_activations(ctx, kind, x, ldx, T, K, false, ACT_ORDER_NATURAL, ab)) return rc;
     const size_t bv = (size_t)block_values(kind);
     const size_t nb = (K + bv - 1) / bv, kp = nb * bv;
     for (size_t t0 = 0; t0 < T; t0 += GEMV_MAX_T) {
@@ -367,7 +377,7 @@ int linear_fused_allreduce(mcu_context *ctx, int kind, const float *x, size_t ld
     if (int rc = ensure(ctx, ctx->act_half, T * kp * sizeof(__half))) return rc;
     if (int rc = ensure(ctx, ctx->act_rowscale, T * sizeof(float))) return rc;
     if (int rc = ensure(ctx, ctx->gemm_partial, gemm_tma_workspace_bytes(kind, (int)T, (int)K, (int)F))) return rc;
-    MCU_CUDA(launch_act_half_fused(kind, x, (int)ldx, (int)T, (int)K, true, (__half *)ctx->act_half.ptr,
+    MCU_CUDA(launch_act_half_fused(kind, x, (int)ldx, (int)T, (int)K, ACT_ORDER_QUAD, (__half *)ctx->act_half.ptr,
                                    (float *)ctx->act_rowscale.ptr, ctx->stream));
     int launches = 0;
     MCU_CUDA(launch_gemm_tma(kind, w, nullptr, (const __half *)ctx->act_half.ptr, (const float *)ctx->act_rowscale.ptr,

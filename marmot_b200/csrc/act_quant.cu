@@ -111,6 +111,16 @@ quantize_q8_0_kernel(const float *__restrict__ x, int ldx, int T, int K, int nb,
     }
 }
 
+// Which value of a row goes to position k (see ACT_ORDER_* in kernels.h).
+__device__ __forceinline__ int act_order_source(int k, int order) {
+    if (order == ACT_ORDER_QUAD) return (k & ~3) | ((k & 1) << 1) | ((k >> 1) & 1);
+    if (order == ACT_ORDER_FRAG16) {
+        const int p = k & 15;
+        return (k & ~15) | (((p & 7) >> 1) << 2) | (p >> 3) | ((p & 1) << 1);
+    }
+    return k;
+}
+
 // fp16 operands for the tensor-core path: xh[t][k] = (d*q) * 2^-e_t, with one exponent per token chosen so
 // that the largest magnitude of the row is about 2^14.  The power-of-two scale is exact, keeps large
 // activations inside the fp16 range (and tiny ones out of the subnormals); the matmul epilogue multiplies
@@ -147,8 +157,7 @@ half_acts_kernel(int kq, int perm, const int8_t *__restrict__ qs, const float *_
     __half *hrow = xh + (size_t)t * kp;
     const int bv = kq ? QK_K : Q8_0_VALUES;
     for (int k = threadIdx.x; k < kp; k += blockDim.x) {
-        // perm: position 4g + (0,1,2,3) holds value 4g + (0,2,1,3)
-        const int src = perm ? ((k & ~3) | ((k & 1) << 1) | ((k >> 1) & 1)) : k;
+        const int src = act_order_source(k, perm);
         const int blk = src / bv;
         const int pos = kq ? blk * QK_K + q8k_split_pos(src - blk * QK_K) : src;
         hrow[k] = __float2half_rn(__fmul_rn(__fmul_rn(drow[blk], inv), (float)qrow[pos]));
@@ -256,9 +265,7 @@ act_half_fused_kernel(const float *__restrict__ x, int ldx, int K, int nb, int p
     __half2 *hrow = (__half2 *)(xh + (size_t)t * kp);
     for (int k2 = threadIdx.x; k2 < kp / 2; k2 += blockDim.x) {
         const int k = 2 * k2;
-        // perm: position 4g + (0,1,2,3) holds value 4g + (0,2,1,3)
-        const int s0 = perm ? ((k & ~3) | ((k & 2) >> 1)) : k;           // k even: 0 -> 0, 2 -> 1
-        const int s1 = perm ? ((k & ~3) | 2 | ((k & 2) >> 1)) : k + 1;   // k+1 odd: 1 -> 2, 3 -> 3
+        const int s0 = act_order_source(k, perm), s1 = act_order_source(k + 1, perm);
         const float a = __fmul_rn(__fmul_rn(d_s[s0 / BV], inv), (float)q_s[s0]);
         const float b = __fmul_rn(__fmul_rn(d_s[s1 / BV], inv), (float)q_s[s1]);
         hrow[k2] = __floats2half2_rn(a, b);
@@ -270,7 +277,7 @@ size_t act_half_fused_smem(int kind, int K) {
     return (size_t)((nb * bv + 15) & ~15) + (size_t)nb * sizeof(float);
 }
 
-cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int K, bool k_perm, __half *xh,
+cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int K, int k_order, __half *xh,
                                   float *rowscale, cudaStream_t s) {
     if (T <= 0) return cudaSuccess;
     const int bv = block_values(kind), nb = (K + bv - 1) / bv;
@@ -285,15 +292,15 @@ cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (kind == KIND_Q8_0)
-        return cudaLaunchKernelEx(&cfg, act_half_fused_kernel<false>, x, ldx, K, nb, k_perm ? 1 : 0, xh, rowscale);
-    return cudaLaunchKernelEx(&cfg, act_half_fused_kernel<true>, x, ldx, K, nb, k_perm ? 1 : 0, xh, rowscale);
+        return cudaLaunchKernelEx(&cfg, act_half_fused_kernel<false>, x, ldx, K, nb, k_order, xh, rowscale);
+    return cudaLaunchKernelEx(&cfg, act_half_fused_kernel<true>, x, ldx, K, nb, k_order, xh, rowscale);
 }
 
-cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, bool k_perm, __half *xh, float *rowscale,
+cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, int k_order, __half *xh, float *rowscale,
                              cudaStream_t s) {
     if (T <= 0) return cudaSuccess;
     const int bv = block_values(kind), nb = (K + bv - 1) / bv;
-    half_acts_kernel<<<T, 256, 0, s>>>(kind != KIND_Q8_0, k_perm ? 1 : 0, a.qs, a.d, nb, nb * bv, xh, rowscale);
+    half_acts_kernel<<<T, 256, 0, s>>>(kind != KIND_Q8_0, k_order, a.qs, a.d, nb, nb * bv, xh, rowscale);
     return cudaGetLastError();
 }
 

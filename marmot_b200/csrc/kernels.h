@@ -21,15 +21,18 @@ cudaError_t launch_quantize_act(int kind, const float *x, int ldx, int T, int K,
                                 cudaStream_t s);
 
 // fp16 operands of the tensor-core matmul from the quantized activations: xh[t][k] = d*q*2^-e_t (row stride kp),
-// rowscale[t] = 2^e_t.  k_perm stores every four consecutive K values in the order (0, 2, 1, 3), the order in
-// which the TMA-fed matmul lays out its dequantised weights.
-cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, bool k_perm, __half *xh, float *rowscale,
+// rowscale[t] = 2^e_t.  k_order: the order of the K values inside a row, matching how the matmul that reads it
+// extracts packed weights: ACT_ORDER_NATURAL; ACT_ORDER_QUAD stores every four consecutive values as (0, 2, 1, 3)
+// (gemm_tma); ACT_ORDER_FRAG16 stores every sixteen values v = 4t + j at position 8(j & 1) + 2t + (j >> 1), the k
+// labelling of the mma.sync fragments of gemm_warp.
+constexpr int ACT_ORDER_NATURAL = 0, ACT_ORDER_QUAD = 1, ACT_ORDER_FRAG16 = 2;
+cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, int k_order, __half *xh, float *rowscale,
                              cudaStream_t s);
 
 // The two steps above in one kernel (one CTA per token, the quantized row kept in shared memory) when the int8
 // values are not needed in global memory; usable while act_half_fused_smem() fits the default 48 KB.
 size_t act_half_fused_smem(int kind, int K);
-cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int K, bool k_perm, __half *xh,
+cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int K, int k_order, __half *xh,
                                   float *rowscale, cudaStream_t s);
 
 // blocks -> f32 (bit-exact with the reference dequantizers)
@@ -85,6 +88,13 @@ cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __hal
                             int T, int K, int F, const float *bias, float *out, float *out2, int ldo, float *partial,
                             int *counters, int *err_flag, cudaStream_t s, int *launches,
                             const PeerFuse *fuse = nullptr);
+// Register-operand variant for 8 < T <= 64 tokens on Q4_K / Q6_K (mma.sync fragments built straight from the packed
+// words, nothing dequantised to shared memory); activations in ACT_ORDER_FRAG16; same workspace contract.
+bool gemm_warp_supported(int kind, const void *W, const void *W2, int T, int K, int F);
+size_t gemm_warp_workspace_bytes(int kind, int T, int K, int F, bool dual);
+cudaError_t launch_gemm_warp(int kind, const void *W, const void *W2, const __half *xh, const float *rowscale, int ldxh,
+                             int T, int K, int F, const float *bias, float *out, float *out2, int ldo, float *partial,
+                             int *counters, int *err_flag, cudaStream_t s);
 // Can launch_gemm_tma fuse the all-reduce for this shape (same answer on every rank: it depends on T and F only)?
 bool gemm_tma_can_fuse(int kind, int T, int F);
 
