@@ -513,22 +513,35 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
     if (has_tile) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncwarp();
-        // S[head g][key 8j + 2tq, +1] in sc[j][0..1]
-        float sc[4][4];
+        // S[head g][key 8j + 2tq, +1] in sc[j][0..1].  The head and the tail of Q accumulate separately and the four
+        // key tiles alternate, so that consecutive MMAs never wait for one another's accumulator.
+        float sc[4][4], st[4][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
-            for (int s = 0; s < KS; s += 2) {
+            for (int e = 0; e < 4; ++e) sc[j][e] = st[j][e] = 0.0f;
+#pragma unroll
+        for (int s = 0; s < KS; s += 2) {
+            uint32_t b[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
                 // matrices: (keys 8j.., piece 2s), (piece 2s+1), (piece 2s+2), (piece 2s+3)
                 const int r = 8 * j + (lane & 7), pc = 2 * s + (lane >> 3);
-                uint32_t b0, b1, b2, b3;
-                ldsm_x4(sK + (uint32_t)(r * ROWB + ((pc ^ (r & 7)) << 4)), b0, b1, b2, b3);
-                mma_top_rows(sc[j], qhi[s][0], qhi[s][1], b0, b1);
-                mma_top_rows(sc[j], qlo[s][0], qlo[s][1], b0, b1);
-                mma_top_rows(sc[j], qhi[s + 1][0], qhi[s + 1][1], b2, b3);
-                mma_top_rows(sc[j], qlo[s + 1][0], qlo[s + 1][1], b2, b3);
+                ldsm_x4(sK + (uint32_t)(r * ROWB + ((pc ^ (r & 7)) << 4)), b[j][0], b[j][1], b[j][2], b[j][3]);
             }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) mma_top_rows(sc[j], qhi[s][0], qhi[s][1], b[j][0], b[j][1]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) mma_top_rows(st[j], qlo[s][0], qlo[s][1], b[j][0], b[j][1]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) mma_top_rows(sc[j], qhi[s + 1][0], qhi[s + 1][1], b[j][2], b[j][3]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) mma_top_rows(st[j], qlo[s + 1][0], qlo[s + 1][1], b[j][2], b[j][3]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            sc[j][0] += st[j][0];
+            sc[j][1] += st[j][1];
         }
         float mx = -INFINITY;
 #pragma unroll
@@ -553,26 +566,37 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
         psum += __shfl_xor_sync(0xffffffffu, psum, 2);
         m = mx;
         l = psum;
-        // O[head g][dim 8n + 2tq, +1] += P V
+        // O[head g][dim 8n + 2tq, +1] += P V, four dimension tiles at a time (independent accumulators back to back)
 #pragma unroll
         for (int u = 0; u < 2; ++u)
 #pragma unroll
-            for (int n = 0; n < NT; n += 2) {
+            for (int n = 0; n < NT; n += 4) {
                 // matrices: (keys 16u.., piece n), (keys 16u+8.., piece n), (keys 16u.., piece n+1), (keys 16u+8.., piece n+1)
                 const int mi = lane >> 3;
-                const int r = 16 * u + 8 * (mi & 1) + (lane & 7), pc = n + (mi >> 1);
-                uint32_t b0, b1, b2, b3;
-                ldsm_x4_trans(sV + (uint32_t)(r * ROWB + ((pc ^ (r & 7)) << 4)), b0, b1, b2, b3);
-                mma_top_rows(o[n], phi[2 * u], phi[2 * u + 1], b0, b1);
-                mma_top_rows(o[n], plo[2 * u], plo[2 * u + 1], b0, b1);
-                mma_top_rows(o[n + 1], phi[2 * u], phi[2 * u + 1], b2, b3);
-                mma_top_rows(o[n + 1], plo[2 * u], plo[2 * u + 1], b2, b3);
+                const int r = 16 * u + 8 * (mi & 1) + (lane & 7);
+                uint32_t b[2][4];
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    const int pc = n + 2 * h2 + (mi >> 1);
+                    ldsm_x4_trans(sV + (uint32_t)(r * ROWB + ((pc ^ (r & 7)) << 4)), b[h2][0], b[h2][1], b[h2][2], b[h2][3]);
+                }
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    mma_top_rows(o[n + 2 * h2], phi[2 * u], phi[2 * u + 1], b[h2][0], b[h2][1]);
+                    mma_top_rows(o[n + 2 * h2 + 1], phi[2 * u], phi[2 * u + 1], b[h2][2], b[h2][3]);
+                }
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    mma_top_rows(o[n + 2 * h2], plo[2 * u], plo[2 * u + 1], b[h2][0], b[h2][1]);
+                    mma_top_rows(o[n + 2 * h2 + 1], plo[2 * u], plo[2 * u + 1], b[h2][2], b[h2][3]);
+                }
             }
     }
     // merge the warps' states: the tile slices are free once every warp is past its MMAs
     __syncthreads();
     float *s_o = (float *)pm_smem;                                        // [warp][8 heads][HD]
     float *s_m = s_o + PM_WARPS * 8 * HD, *s_l = s_m + PM_WARPS * 8;      // [warp][8 heads]
+    float *s_e = s_l + PM_WARPS * 8;                                      // weight of a warp's state in the chunk state
 #pragma unroll
     for (int n = 0; n < NT; ++n)
         *(float2 *)(s_o + ((size_t)warp * 8 + g) * HD + 8 * n + 2 * tq) = make_float2(o[n][0], o[n][1]);
@@ -581,21 +605,29 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
         s_l[warp * 8 + g] = l;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < gsize * HD; idx += blockDim.x) {
-        const int hh = idx / HD, d = idx - hh * HD;
+    if (threadIdx.x < PM_WARPS * 8) {
+        const int hh = threadIdx.x & 7;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < PM_WARPS; ++w) M = fmaxf(M, s_m[w * 8 + hh]);
+        const float mw = s_m[threadIdx.x];
+        s_e[threadIdx.x] = (M == -INFINITY || mw == -INFINITY) ? 0.0f : expf(mw - M);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < gsize * HD; idx += blockDim.x) {
+        const int hh = idx / HD, d = idx - hh * HD;
         float L = 0.0f, O = 0.0f;
 #pragma unroll
-        for (int w = 0; w < PM_WARPS; ++w) {
-            const float mw = s_m[w * 8 + hh];
-            const float e = (M == -INFINITY || mw == -INFINITY) ? 0.0f : expf(mw - M);
+        for (int w = 0; w < PM_WARPS; ++w) {  // warp order: deterministic
+            const float e = s_e[w * 8 + hh];
             L += s_l[w * 8 + hh] * e;
             O += s_o[((size_t)w * 8 + hh) * HD + d] * e;
         }
         float *pr = partial + (((size_t)t * p.n_q_heads + (size_t)h * gsize + hh) * n_chunks + c) * (HD + 2);
         if (d == 0) {
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < PM_WARPS; ++w) M = fmaxf(M, s_m[w * 8 + hh]);
             pr[0] = M;
             pr[1] = L;
         }

@@ -157,6 +157,23 @@ def test_gemm_tensor_core_vs_oracle(ctx, oracle, name, T, K, F):
     assert cosine(got, ref) >= 0.999
 
 
+def test_register_operand_kernel_on_q4_k():
+    """Q6_K takes the register-operand (mma.sync) kernel for 8 < T <= 64 by default; Q4_K only behind a switch that is
+    read once per process, so its parity cases run in a child process with the switch set."""
+    import os
+    import subprocess
+    import sys
+
+    from pathlib import Path
+
+    REPO_ROOT = Path(__file__).resolve().parents[1]
+    env = {**os.environ, "MARMOT_CUDA_GEMM_WARP_Q4K": "1"}
+    r = subprocess.run([sys.executable, "-m", "pytest", "tests/test_gpu_parity.py", "-x", "-q", "-k",
+                        "(test_gemm_tensor_core_vs_oracle or test_dual_output_equals_two_singles) and q4_k"],
+                       cwd=REPO_ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+
+
 def test_config_q8_0_prefill_gemm_full_size(ctx, oracle):
     """Q8_0 prefill GEMM, 512 tokens x K = 4096 x F = 14336, with the benchmark's value distributions."""
     kind, T, K, F = KIND_Q8_0, 512, 4096, 14336
