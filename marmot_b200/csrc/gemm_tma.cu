@@ -71,7 +71,7 @@ struct GemmTmaParams {
     int *err;
     int ldo, T, F, nb;
     int ksteps;
-    int rows_per_cta;  // weight rows per CTA (= tensor-map box rows), <= 128
+    int rows_per_cta;  // weight rows per CTA (= tensor-map box rows): <= 128, or 256 for two row tiles
     int stages;        // MMA stage ring depth
     int raw_stages;    // raw slab ring depth
     int raw_stage_bytes;  // bytes of one slab slot (a multiple of 128)
@@ -208,20 +208,26 @@ __device__ __forceinline__ void conv_q8_0(const uint8_t *blk, uint4 *outv) {
     for (int cc = 0; cc < 4; ++cc) outv[cc] = make_uint4(o[4 * cc], o[4 * cc + 1], o[4 * cc + 2], o[4 * cc + 3]);
 }
 
-template <int KIND, int BN, int G>
+// RT = 2 (with BN = 256, G = 1): the CTA owns two 128-row weight tiles and multiplies both with the same activation
+// tile of a K step into two accumulators (all 512 TMEM columns).  With one row tile the 256-token activation tile
+// (32 KB from L2 per K step) bounds the step at about half the tensor rate; two row tiles halve the activation bytes
+// per MMA.  All sixteen converter warps then work on the same K step (half a row per thread, 256 rows).
+template <int KIND, int BN, int G, int RT = 1>
 __global__ void __launch_bounds__(TM_THREADS, 1)
 gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                 const GemmTmaParams p) {
     extern __shared__ uint8_t smem_raw[];
     using RC = RawCfg<KIND>;
     constexpr int B_BYTES = BN * TM_BK * 2;
-    constexpr int STAGE_BYTES = TM_A_BYTES + B_BYTES;
+    static_assert(RT == 1 || (RT == 2 && BN == 256 && G == 1), "two row tiles need the 256-token tile");
+    constexpr int A_BYTES = RT * TM_A_BYTES;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     const int RAW_STAGE_BYTES = p.raw_stage_bytes;  // rows_per_cta * BOX_W rounded to 128, + slack for the one-word over-read
     // One thread can issue tcgen05.mma only so fast (a few hundred cycles per K step including its barrier
     // wait and commit), which is far slower than the tensor core for narrow tiles.  NACC threads therefore issue
     // interleaved K steps (step ks -> issuer ks % NACC), each into its own accumulator; the epilogue adds them.
     constexpr int NACC = BN == 64 ? 4 : (BN == 128 ? 2 : 1);
-    constexpr uint32_t TMEM_COLS = NACC * BN;  // 256 for every BN: a power of two >= 32
+    constexpr uint32_t TMEM_COLS = RT * NACC * BN;  // 256 for every BN with one row tile, 512 with two
     constexpr int GW = TM_ALL_CONV / G;        // warps per converter group
 
     const uint32_t raw_addr = tm_smem_u32(smem_raw);
@@ -299,7 +305,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     ok = tm_mbar_wait_relaxed((((use - 1) & 1u) ? st_empty_odd : st_empty) + 8u * st, ((use - 1) >> 1) & 1u);
                 if (!ok) break;
                 tm_mbar_expect_tx(a_full + 8u * st, (uint32_t)B_BYTES);
-                tm_tma_load_2d(tile_base + (uint32_t)st * STAGE_BYTES + TM_A_BYTES, &map_x, (ks0 + ks) * TM_BK, t0, a_full + 8u * st);
+                tm_tma_load_2d(tile_base + (uint32_t)st * STAGE_BYTES + A_BYTES, &map_x, (ks0 + ks) * TM_BK, t0, a_full + 8u * st);
                 MCU_TRACE_POINT(2, ks, 1);
                 if (++st == S) {
                     st = 0;
@@ -347,7 +353,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         if (issuer < p.issuers) {
             constexpr uint32_t idesc = tm_idesc(BN);
             bool ok = true;
-            const uint64_t a_desc0 = tm_smem_desc(tile_base), b_desc0 = tm_smem_desc(tile_base + TM_A_BYTES);
+            const uint64_t a_desc0 = tm_smem_desc(tile_base), b_desc0 = tm_smem_desc(tile_base + A_BYTES);
             constexpr uint64_t desc_step = (uint64_t)(STAGE_BYTES >> 4);
             const uint32_t tmem_acc = tmem_base + (uint32_t)(issuer * BN);
             int st = issuer % S;
@@ -366,6 +372,13 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     tm_mma(tmem_acc, a_desc + 2, b_desc + 2, idesc, 1u);  // +32 bytes along K inside the swizzle row
                     tm_mma(tmem_acc, a_desc + 4, b_desc + 4, idesc, 1u);
                     tm_mma(tmem_acc, a_desc + 6, b_desc + 6, idesc, 1u);
+                    if constexpr (RT == 2) {  // the second row tile: next 16 KB of the stage, next BN columns of TMEM
+                        constexpr uint64_t a2 = (uint64_t)(TM_A_BYTES >> 4);
+                        tm_mma(tmem_acc + BN, a_desc + a2, b_desc, idesc, acc);
+                        tm_mma(tmem_acc + BN, a_desc + a2 + 2, b_desc + 2, idesc, 1u);
+                        tm_mma(tmem_acc + BN, a_desc + a2 + 4, b_desc + 4, idesc, 1u);
+                        tm_mma(tmem_acc + BN, a_desc + a2 + 6, b_desc + 6, idesc, 1u);
+                    }
                     MCU_TRACE_POINT(0, ks, 2);
                     tm_commit(((use & 1u) ? st_empty_odd : st_empty) + 8u * st);
                     MCU_TRACE_POINT(0, ks, 3);
@@ -506,7 +519,9 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         if (ok && warp < 8 && !*abort_flag) {
             const int q = warp & 3;
             const int col0 = (warp >> 2) * (BN / 2);
-            const int fr = 32 * q + lane;
+#pragma unroll 1
+            for (int rt = 0; rt < RT; ++rt) {
+            const int fr = TM_BM * rt + 32 * q + lane;
             const int f = f0 + fr;
             const bool f_ok = fr < rows_here;
             const float bias = (p.bias != nullptr && f_ok) ? p.bias[f] : 0.0f;
@@ -520,7 +535,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 for (int a = 0; a < NACC; ++a) {
                     if (a >= n_used) break;  // warp-uniform
                     uint32_t v[32];
-                    const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(a * BN + col0 + cb);
+                    const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)((rt * NACC + a) * BN + col0 + cb);
                     asm volatile(
                         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -561,6 +576,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     }
                 }
             }
+            }  // row tiles
         }
     }
     if (threadIdx.x == 0) MCU_TRACE_POINT(3, 36, 0);
@@ -731,9 +747,22 @@ static TmaPlan plan_tma(int kind, int T, int K, int F) {
     const int kr = kind == KIND_Q8_0 ? 2 : 4;
     const int n_slabs = (ksteps + kr - 1) / kr;
     TmaPlan pl{TM_BM, 1, n_slabs};
-    if (T > 64) return pl;
-    static const bool no_split = getenv("MARMOT_CUDA_GEMM_NO_SPLITK") != nullptr;  // diagnostic switch
     const int sms = device_sm_count();
+    // T > 64: full tiles (shorter tiles that would fill the last wave better finish no sooner: the MMA computes
+    // M = 128 rows whatever the tile holds, and a converter warp takes as long for a half-empty tile).  With 256-token
+    // tiles and enough work to fill most SMs a CTA takes two row tiles (see the kernel's RT parameter); Q6_K slabs are
+    // too large for that.
+    if (T > 64) {
+        static const bool one_tile = getenv("MARMOT_CUDA_GEMM_ONE_ROW_TILE") != nullptr;  // diagnostic switch
+        // Measured K-step times: about 1290 cycles with one row tile, 2250 with two (F = 14336, T = 512: 99 -> 90 us for
+        // Q8_0, 83 -> 76 us for Q4_K); two tiles win when they save a wave (224 units on 148 SMs -> 112).
+        const long t_tiles = (T + 255) / 256;
+        const long waves2 = ((long)((F + 2 * TM_BM - 1) / (2 * TM_BM)) * t_tiles + sms - 1) / sms;
+        const long waves1 = ((long)((F + TM_BM - 1) / TM_BM) * t_tiles + sms - 1) / sms;
+        if (T > 128 && kind != KIND_Q6_K && !one_tile && waves2 * 175 < waves1 * 97) pl.rows_per_cta = 2 * TM_BM;
+        return pl;
+    }
+    static const bool no_split = getenv("MARMOT_CUDA_GEMM_NO_SPLITK") != nullptr;  // diagnostic switch
     const int tiles = (F + TM_BM - 1) / TM_BM;
     int splits = no_split ? 1 : sms / tiles;
     if (splits > 16) splits = 16;
@@ -772,7 +801,7 @@ bool gemm_tma_supported(int kind, const void *W, const void *W2, int T, int K, i
     return encode_tiled_fn() != nullptr;
 }
 
-template <int KIND, int BN, int G>
+template <int KIND, int BN, int G, int RT = 1>
 static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, GemmTmaParams p, long row_bytes,
                                  cudaStream_t s) {
     using RC = RawCfg<KIND>;
@@ -799,7 +828,7 @@ static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, Gemm
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    constexpr int stage_bytes = TM_A_BYTES + BN * TM_BK * 2;
+    constexpr int stage_bytes = RT * TM_A_BYTES + BN * TM_BK * 2;
     const int raw_stage_bytes = (p.rows_per_cta * RC::BOX_W + 127) / 128 * 128 + 128;
     const int budget = 210 * 1024 - 2048;
     const int raw_slabs = p.slabs_per_split;
@@ -809,7 +838,7 @@ static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, Gemm
     // full-barrier are waited on by one thread in order.  (A parity wait cannot tell "this phase" from "two
     // phases ago"; an issuer that got ahead of the thread owning the previous use of the stage would fall
     // through its wait.)
-    int R = BN <= 128 ? 4 : 3;
+    int R = RT == 2 ? 2 : (BN <= 128 ? 4 : 3);  // two row tiles: two 64 KB stages and two 256-row slabs fill the SM
     if (R > raw_slabs) R = raw_slabs;
     int S = (budget - R * raw_stage_bytes) / stage_bytes;
     if (S < G + 2 && R > 3) {  // a ring deeper than G lets a group convert while its previous step is still in the MMA
@@ -837,7 +866,7 @@ static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, Gemm
     const int smem = 2048 + S * stage_bytes + R * raw_stage_bytes;
     static int configured = 0;
     if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tma_kernel<KIND, BN, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tma_kernel<KIND, BN, G, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         configured = smem;
     }
@@ -853,7 +882,7 @@ static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, Gemm
     cfg.attrs = attr;
     static const bool no_pdl = getenv("MARMOT_CUDA_NO_PDL") != nullptr;  // diagnostic switch
     cfg.numAttrs = no_pdl ? 0 : 1;
-    return cudaLaunchKernelEx(&cfg, gemm_tma_kernel<KIND, BN, G>, map_w, map_x, p);
+    return cudaLaunchKernelEx(&cfg, gemm_tma_kernel<KIND, BN, G, RT>, map_w, map_x, p);
 }
 
 template <int KIND>
@@ -861,6 +890,8 @@ static cudaError_t launch_tma_kind(const void *W, const __half *xh, int ldxh, co
                                    cudaStream_t s) {
     if (p.T <= 64) return launch_tma_bn<KIND, 64, 4>(W, xh, ldxh, p, row_bytes, s);
     if (p.T <= 128) return launch_tma_bn<KIND, 128, 4>(W, xh, ldxh, p, row_bytes, s);
+    if constexpr (KIND != KIND_Q6_K)
+        if (p.rows_per_cta == 2 * TM_BM) return launch_tma_bn<KIND, 256, 1, 2>(W, xh, ldxh, p, row_bytes, s);
     return launch_tma_bn<KIND, 256, 2>(W, xh, ldxh, p, row_bytes, s);
 }
 
