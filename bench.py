@@ -339,11 +339,17 @@ def time_decode(ctx, dev, rank: int = 0, world: int = 1, dist=None):
     out = {}
     group = tp.Group(rank, world, dist if world > 1 else None)
 
-    def run(shape, n_seq, ctx_lens, n_prompt, n_decode, advance):
+    def run(shape, n_seq, ctx_lens, n_prompt, n_decode, advance, replicas=False):
+        """replicas: every rank holds all weights and decodes its own share of the sequences (no collective)."""
         max_ctx = int(max(ctx_lens)) + n_decode + 16
-        comm = tp.make_peer_comm(ctx, group, n_seq * max(shape.d, world) * 4) if world > 1 else None
+        total_seq = n_seq
+        if replicas:
+            ctx_lens = np.asarray(ctx_lens)[rank::world]
+            n_seq = len(ctx_lens)
+        tpar = world > 1 and not replicas
+        comm = tp.make_peer_comm(ctx, group, n_seq * max(shape.d, world) * 4) if tpar else None
         dec = Decoder(ctx, shape, max_seqs=n_seq, max_ctx=max_ctx, block_size=16, kv_dtype=torch.float16, seed=5,
-                      group=group, comm=comm)
+                      group=group if tpar else None, comm=comm)
         stream = torch.cuda.Stream(dev)
         ctx.set_stream(stream.cuda_stream)
         rng = np.random.default_rng(3)
@@ -396,13 +402,15 @@ def time_decode(ctx, dev, rank: int = 0, world: int = 1, dist=None):
             ms = float(t.item())
             dist.barrier()
             torch.cuda.synchronize()
-            comm.close()
+            if comm is not None:
+                comm.close()
         wb = weight_bytes(dec.local) - dec.local.vocab * row_bytes_q6(dec.local.d) + dec.local_vocab * row_bytes_q6(dec.local.d)
         kv_heads_here = dec.local.n_kv_heads
         mean_ctx = float(np.mean(ctx_lens)) + (n_decode / 2 if advance else 0)
         kvb = n_seq * mean_ctx * shape.layers * kv_heads_here * shape.head_dim * 2 * 2
-        return {"ms_per_step": round(ms, 4), "tokens_per_s": round(n_seq / ms * 1e3, 1), "sequences": n_seq,
-                "tensor_parallel": world, "weight_bytes_per_step_per_gpu": wb, "kv_bytes_per_step_per_gpu": int(kvb),
+        return {"ms_per_step": round(ms, 4), "tokens_per_s": round(total_seq / ms * 1e3, 1), "sequences": total_seq,
+                "tensor_parallel": world if tpar else 1, "replicas": world if replicas else 1,
+                "weight_bytes_per_step_per_gpu": wb, "kv_bytes_per_step_per_gpu": int(kvb),
                 "GBps": round((wb + kvb) / ms / 1e6, 1), "frac_hbm": round((wb + kvb) / ms / 1e6 / peak_bw, 3),
                 "kernel_launches_per_step": int(launches)}
 
@@ -415,6 +423,9 @@ def time_decode(ctx, dev, rank: int = 0, world: int = 1, dist=None):
     lens = np.random.default_rng(4).integers(256, 4097, 64)
     out["llama3_8b_64seq"] = run(LLAMA3_8B, 64, lens, 0, 20, False)
     torch.cuda.empty_cache()
+    if world > 1:  # the same 64 sequences dealt out over replicas of the whole model (it fits one GPU many times over)
+        out["llama3_8b_64seq_replicas"] = run(LLAMA3_8B, 64, lens, 0, 20, False, replicas=True)
+        torch.cuda.empty_cache()
     return out
 
 
