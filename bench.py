@@ -11,7 +11,8 @@ Printed on rank 0 as one JSON line:
   value     GB/s of algorithmic bytes (packed weights + x + y = 9 469 952 B per GEMV) over the timed
             region, inputs resident in HBM, summed over ranks
   e2e       the same through ``mcu_linear_host``: activations start in pinned host memory and the
-            result is copied back to the host inside the timed region (weights stay resident)
+            result lands in pinned host memory inside the timed region (weights stay resident; the
+            activations are copied to the device, the kernel writes the result over PCIe in place)
   roofline  the GEMV kernel against the measured HBM copy bandwidth
   cpu_baseline  the reference CPU backend (or the oracle port) on the host cores, bounded sample
 
@@ -666,7 +667,8 @@ def main():
         "gpu_launches": int(launches),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": R * T_TOK * K_DIM * 4,
                 "d2h_bytes_per_step": R * T_TOK * F_DIM * 4, "steps": e2e_steps,
-                "note": "weights device resident; activations from pinned host memory, result read back to host"},
+                "note": "weights device resident; activations copied from pinned host memory, result written to pinned host "
+                        "memory by the kernel (in place over PCIe), host synchronised per GEMV"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of "
                      "one launch of this kernel and shape (profiles/gemv_stream_q4k_T1_K4096_F4096.md)",

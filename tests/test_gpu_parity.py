@@ -250,6 +250,25 @@ def test_linear_host_buffers(ctx, oracle):
     assert max_rel_err(got, oracle.linear(kind, x, W, F, bias=bias)) <= TOL_FP32
 
 
+@pytest.mark.parametrize("T,strided", [(1, False), (3, True), (12, False)])
+def test_linear_host_pinned_buffers_equal_staged_copies(ctx, T, strided):
+    """A page-locked result buffer is written in place by the decode kernels (T <= 8); the result must be the very bits
+    of the staged-copy path, which pageable buffers take."""
+    import torch
+
+    kind, K, F = KIND_Q4_K, 2048, 264
+    rng = np.random.default_rng(T)
+    w = ctx.upload(random_blocks(kind, F, K, rng))
+    ld = K + 64 if strided else K
+    x_pin = torch.zeros((T, ld), dtype=torch.float32).pin_memory()
+    x_pin[:, :K] = torch.from_numpy(rng.normal(0, 1, (T, K)).astype(np.float32))
+    out_pin = torch.full((T, F), np.nan, dtype=torch.float32).pin_memory()
+    x_np = x_pin.numpy()[:, :K]  # a view: same page-locked memory, row stride ld
+    got = ctx.linear_host(kind, x_np, w, F, out_host=out_pin.numpy())
+    want = ctx.linear_host(kind, np.ascontiguousarray(x_np), w, F)  # pageable copies
+    assert np.array_equal(bits(got), bits(want))
+
+
 def test_config_q4k_gemv_full_size(ctx, oracle):
     """The single-token Q4_K GEMV at 4096 x 4096 with the benchmark's value distributions."""
     kind, T, K, F = KIND_Q4_K, 1, 4096, 4096
