@@ -68,6 +68,21 @@ typedef struct mcu_context mcu_context_t;
 /* ---- context: the device half of marmot_device_ops (include/marmot/device.h:43-66);
  *      stands in for cpu_init / cpu_destroy / cpu_synchronize
  *      (src/backends/cpu/runtime/runtime.c:1409-1443, src/backends/cpu/dispatch/device_ops.c:12-30). ---- */
+/* What marmot_cuda_detect_default_caps fills marmot_device_caps_t from (include/marmot/device_caps.h:14-71; the reference
+ * reserves backend.cuda.{sm_count, shared_mem_kb, compute_capability} there).  MCU_ERROR_DEVICE_NOT_AVAILABLE when the
+ * process sees no such device. */
+typedef struct mcu_device_caps {
+    int sm_count;
+    int compute_capability;  /* 100 for sm_100 */
+    int shared_mem_kb;       /* per SM */
+    int l2_cache_kb;
+    int sm_clock_mhz;
+    float mem_bw_gbps;       /* nominal: 2 x memory clock x bus width */
+    size_t total_mem_bytes;
+    int copy_engines;
+} mcu_device_caps_t;
+int mcu_device_caps(int device, mcu_device_caps_t *out);
+
 int mcu_context_create(int device, mcu_context_t **out);
 void mcu_context_destroy(mcu_context_t *ctx);
 /* Use a stream owned by the caller (cudaStream_t passed as void*); NULL restores the context's own

@@ -121,6 +121,29 @@ const char *mcu_last_error_message(void) { return g_err; }
 
 uint64_t mcu_kernel_launch_count(const mcu_context_t *) { return g_kernel_launches.load(); }
 
+int mcu_device_caps(int device, mcu_device_caps_t *out) {
+    if (out == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "out is null");
+    memset(out, 0, sizeof(*out));
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        return fail(MCU_ERROR_DEVICE_NOT_AVAILABLE, "no CUDA device: %s", cudaGetErrorString(e));
+    }
+    if (device < 0 || device >= n) return fail(MCU_ERROR_DEVICE_NOT_AVAILABLE, "device %d out of range (%d)", device, n);
+    cudaDeviceProp prop;
+    MCU_CUDA(cudaGetDeviceProperties(&prop, device));
+    out->sm_count = prop.multiProcessorCount;
+    out->compute_capability = prop.major * 10 + prop.minor;
+    out->shared_mem_kb = (int)(prop.sharedMemPerMultiprocessor / 1024);
+    out->l2_cache_kb = prop.l2CacheSize / 1024;
+    out->sm_clock_mhz = prop.clockRate / 1000;
+    out->mem_bw_gbps = 2.0f * (float)prop.memoryClockRate * 1e3f * (float)(prop.memoryBusWidth / 8) / 1e9f;
+    out->total_mem_bytes = prop.totalGlobalMem;
+    out->copy_engines = prop.asyncEngineCount;
+    return MCU_SUCCESS;
+}
+
 int mcu_context_create(int device, mcu_context_t **out) {
     if (out == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "out is null");
     *out = nullptr;
@@ -450,8 +473,11 @@ int mcu_linear_host(mcu_context_t *ctx, int kind, const float *x_host, size_t ld
     float *xd = nullptr, *od = nullptr, *bd = nullptr;
     if (int rc = ensure(ctx, ctx->x_stage, T * K * sizeof(float))) return rc;
     xd = (float *)ctx->x_stage.ptr;
-    MCU_CUDA(cudaMemcpy2DAsync(xd, K * sizeof(float), x_host, ldx * sizeof(float), K * sizeof(float), T,
-                               cudaMemcpyHostToDevice, ctx->stream));
+    if (ldx == K)
+        MCU_CUDA(cudaMemcpyAsync(xd, x_host, T * K * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    else
+        MCU_CUDA(cudaMemcpy2DAsync(xd, K * sizeof(float), x_host, ldx * sizeof(float), K * sizeof(float), T,
+                                   cudaMemcpyHostToDevice, ctx->stream));
     if (out_map != nullptr) {
         od = out_map;
     } else {

@@ -10,6 +10,8 @@
 //   cuda_moe_experts_impl          <- cpu_moe_experts_impl, src/backends/cpu/ops/moe/moe_ops.c:1069-1178
 //   cuda_topk_impl                 <- cpu_topk_impl, moe_ops.c:789-889
 //   cuda_dequantize_*              <- cpu_dequantize_*, src/backends/cpu/quantization/formats/*.c
+//   marmot_cuda_query_kernel, marmot_cuda_detect_default_caps, marmot_cuda_default_preferences
+//                                  <- the externs of src/core/dispatch/kernel_query.c:10-17
 //
 // Residency: marmot tensors own host memory and are identified by their host pointer.  The backend keeps a
 // map host range -> device mirror.  `memcpy_to_device(p, p, n)` means "make [p, p+n) resident / refresh it"
@@ -22,6 +24,11 @@
 #include "marmot/tensor.h"
 #include "marmot/types.h"
 
+#include "marmot/device_caps.h"
+#include "marmot/graph/kernel_selection.h"
+#include "marmot/graph/op_signature.h"
+
+#include "core/dispatch/kernel_query.h"
 #include "core/helpers/matmul.h"
 
 #include "marmot_cuda.h"
@@ -574,4 +581,202 @@ marmot_error_t cuda_dequantize_q6_k(const void *device_ctx, const marmot_tensor_
 
 marmot_error_t cuda_dequantize_q8_0(const void *device_ctx, const marmot_tensor_t *input, marmot_tensor_t *output) {
     return cuda_dequantize_blockwise(device_ctx, MCU_KIND_Q8_0, input, output);
+}
+
+// ---- kernel query, capabilities, preferences ----------------------------------------------------------
+// Reference counterparts: marmot_cpu_query_kernel / marmot_metal_query_kernel (generated, called from
+// src/core/dispatch/kernel_query.c:35-52), marmot_metal_detect_default_caps and marmot_*_default_preferences
+// (kernel_query.c:88-132, src/backends/cpu/runtime/runtime.c:1388-1407).  A signature without a CUDA kernel is
+// answered with supported = false here, at query time: nothing is ever computed on the host instead
+// (src/core/dispatch/dispatch_execute.c:214-233 would otherwise look for an unfused fallback).
+//
+// The kernel ids below continue marmot's generated enumeration (include/marmot/traits_ids.gen.h); the codegen
+// assigns the real values when it emits the CUDA tables from the .def files, in this order.
+enum {
+    CUDA_KERNEL_MATMUL_Q4_K_F32_NT = MARMOT_KERNEL_COUNT,
+    CUDA_KERNEL_MATMUL_Q6_K_F32_NT,
+    CUDA_KERNEL_MATMUL_Q8_0_F32_NT,
+    CUDA_KERNEL_MOE_EXPERTS_Q4_K,
+    CUDA_KERNEL_MOE_EXPERTS_Q6_K,
+    CUDA_KERNEL_MOE_EXPERTS_Q8_0,
+    CUDA_KERNEL_TOPK_F32,
+    CUDA_KERNEL_DEQUANTIZE_Q4_K,
+    CUDA_KERNEL_DEQUANTIZE_Q6_K,
+    CUDA_KERNEL_DEQUANTIZE_Q8_0,
+    CUDA_KERNEL_EMBEDDING_Q4_K,
+    CUDA_KERNEL_EMBEDDING_Q6_K,
+    CUDA_KERNEL_EMBEDDING_Q8_0,
+    CUDA_KERNEL_RMS_NORM_F32,
+    CUDA_KERNEL_RMS_NORM_GEMMA_F32,
+    CUDA_KERNEL_ROPE_F32,
+    CUDA_KERNEL_ADD_F32,
+    CUDA_KERNEL_SWIGLU_F32,
+    CUDA_KERNEL_PAGED_ATTENTION_F32_KV_F32,
+    CUDA_KERNEL_PAGED_ATTENTION_F32_KV_F16,
+    CUDA_KERNEL_ARGMAX_F32,
+    CUDA_KERNEL_END,
+};
+
+static marmot_kernel_selection_t cuda_unsupported(const char *reason) {
+    return (marmot_kernel_selection_t){
+        .supported = false,
+        .kernel_id = MARMOT_KERNEL_INVALID,
+        .op_index = MARMOT_KERNEL_OP_INDEX_INVALID,
+        .fallback_reason = reason,
+    };
+}
+
+// bytes moved / bandwidth + flops / tensor rate + a launch: the same shape of estimate the other backends give the
+// graph scheduler; est_comm_us / shardable_axes / device_affinity stay 0 as everywhere in the reference
+// (include/marmot/graph/kernel_selection.h:18-23).
+static marmot_kernel_selection_t
+cuda_supported(int kernel, const marmot_device_caps_t *caps, double bytes, double flops, double workspace_bytes) {
+    const double bw = caps->mem_bw_gbps > 0.0f ? caps->mem_bw_gbps : 6500.0;            // GB/s
+    const double tf = caps->peak_flops_tflops_fp16 > 0.0f ? caps->peak_flops_tflops_fp16 : 1600.0;
+    const double launch = caps->launch_overhead_us > 0.0f ? caps->launch_overhead_us : 4.0;
+    const double t_mem = bytes / (bw * 1e3), t_math = flops / (tf * 1e6);  // microseconds
+    return (marmot_kernel_selection_t){
+        .supported = true,
+        .kernel_id = (marmot_kernel_id_t)kernel,
+        .op_index = (uint16_t)(kernel - (int)MARMOT_KERNEL_COUNT),
+        .estimated_us = launch + (t_mem > t_math ? t_mem : t_math),
+        .est_workspace_mb = workspace_bytes / (1024.0 * 1024.0),
+        .confidence = 0.8f,
+        .fallback_reason = nullptr,
+    };
+}
+
+static int cuda_kind_slot(marmot_qscheme_id_t q) {  // 0 / 1 / 2 for the three block formats with kernels, else -1
+    switch (q) {
+    case MARMOT_QSCHEME_Q4_K:
+        return 0;
+    case MARMOT_QSCHEME_Q6_K:
+        return 1;
+    case MARMOT_QSCHEME_Q8_0:
+        return 2;
+    default:
+        return -1;
+    }
+}
+
+static double cuda_bits_per_weight(int slot) { return slot == 0 ? 4.5 : slot == 1 ? 6.5625 : 8.5; }
+
+marmot_kernel_selection_t marmot_cuda_query_kernel(const marmot_op_signature_t *sig, const marmot_device_caps_t *caps) {
+    if (sig == nullptr || caps == nullptr) return cuda_unsupported("Invalid kernel query arguments");
+    if (caps->backend.cuda.compute_capability / 10 != 10)
+        return cuda_unsupported("CUDA kernels are built for sm_100a only");
+    if (sig->variant_flags != 0) return cuda_unsupported("no fused variants on CUDA");
+    const bool f32_io = sig->input_dtype == MARMOT_DTYPE_FLOAT32 && sig->output_dtype == MARMOT_DTYPE_FLOAT32;
+    const int slot = cuda_kind_slot(sig->qscheme_id);
+    switch (sig->op_id) {
+    case MARMOT_OP_MATMUL:
+    case MARMOT_OP_LINEAR: {
+        if (slot < 0) return cuda_unsupported("CUDA matmul covers Q4_K, Q6_K and Q8_0 weights");
+        if (!f32_io) return cuda_unsupported("CUDA quantized matmul takes FLOAT32 activations and writes FLOAT32");
+        if (sig->matmul_layout != MARMOT_MATMUL_LAYOUT_NT) return cuda_unsupported("CUDA quantized matmul is NT only");
+        if (sig->weight_layout != MARMOT_WEIGHT_LAYOUT_SEPARATE) return cuda_unsupported("packed weight layouts are CPU caches");
+        if ((sig->epilogue_flags & ~(uint32_t)MARMOT_EPILOGUE_BIAS) != 0 || sig->activation != MARMOT_DEVICE_UNARY_IDENTITY)
+            return cuda_unsupported("CUDA matmul epilogue is bias only");
+        if (sig->stride_mode == MARMOT_STRIDE_MODE_STRIDED) return cuda_unsupported("inner stride must be 1");
+        const double T = (double)sig->dims.matmul.N, K = (double)sig->dims.matmul.K, F = (double)sig->dims.matmul.M;
+        const double bytes = F * K * cuda_bits_per_weight(slot) / 8.0 + 4.0 * T * (K + F);
+        // split-K partial tiles of the few-token tensor-core path (at most sixteen splits)
+        const double ws = (T > 8 && T <= 64) ? 16.0 * T * F * 4.0 : 0.0;
+        return cuda_supported(CUDA_KERNEL_MATMUL_Q4_K_F32_NT + slot, caps, bytes, 2.0 * T * K * F, ws + 2.0 * T * K);
+    }
+    case MARMOT_OP_MOE_EXPERTS:
+        if (slot < 0) return cuda_unsupported("CUDA MoE experts cover Q4_K, Q6_K and Q8_0 weights");
+        if (!f32_io) return cuda_unsupported("CUDA MoE experts take FLOAT32 activations");
+        return cuda_supported(CUDA_KERNEL_MOE_EXPERTS_Q4_K + slot, caps, 0.0, 0.0, 0.0);
+    case MARMOT_OP_TOPK:
+        if (sig->input_dtype != MARMOT_DTYPE_FLOAT32) return cuda_unsupported("CUDA top-k is FLOAT32");
+        return cuda_supported(CUDA_KERNEL_TOPK_F32, caps, 0.0, 0.0, 0.0);
+    case MARMOT_OP_DEQUANTIZE:
+        if (slot < 0 || sig->output_dtype != MARMOT_DTYPE_FLOAT32)
+            return cuda_unsupported("CUDA dequantize covers Q4_K, Q6_K and Q8_0 to FLOAT32");
+        return cuda_supported(CUDA_KERNEL_DEQUANTIZE_Q4_K + slot, caps, 4.0 * sig->dims.elementwise.n_elems, 0.0, 0.0);
+    case MARMOT_OP_EMBEDDING:
+        if (slot < 0 || sig->output_dtype != MARMOT_DTYPE_FLOAT32)
+            return cuda_unsupported("CUDA embedding gather covers Q4_K, Q6_K and Q8_0 tables to FLOAT32");
+        return cuda_supported(CUDA_KERNEL_EMBEDDING_Q4_K + slot, caps, 0.0, 0.0, 0.0);
+    case MARMOT_OP_RMS_NORM:
+    case MARMOT_OP_RMS_NORM_GEMMA:
+        if (!f32_io) return cuda_unsupported("CUDA RMSNorm is FLOAT32");
+        return cuda_supported(sig->op_id == MARMOT_OP_RMS_NORM ? CUDA_KERNEL_RMS_NORM_F32 : CUDA_KERNEL_RMS_NORM_GEMMA_F32,
+                              caps, 8.0 * sig->dims.layernorm.n * sig->dims.layernorm.d, 0.0, 0.0);
+    case MARMOT_OP_ROPE:
+        if (!f32_io) return cuda_unsupported("CUDA RoPE is FLOAT32");
+        return cuda_supported(CUDA_KERNEL_ROPE_F32, caps, 0.0, 0.0, 0.0);
+    case MARMOT_OP_ADD:
+    case MARMOT_OP_SWIGLU:
+        if (!f32_io) return cuda_unsupported("CUDA elementwise kernels are FLOAT32");
+        if (sig->stride_mode != MARMOT_STRIDE_MODE_ANY && sig->stride_mode != MARMOT_STRIDE_MODE_CONTIGUOUS)
+            return cuda_unsupported("CUDA elementwise kernels take contiguous tensors");
+        return cuda_supported(sig->op_id == MARMOT_OP_ADD ? CUDA_KERNEL_ADD_F32 : CUDA_KERNEL_SWIGLU_F32, caps,
+                              12.0 * sig->dims.elementwise.n_elems, 0.0, 0.0);
+    case MARMOT_OP_PAGED_ATTENTION:
+        if (!f32_io) return cuda_unsupported("CUDA paged attention takes FLOAT32 q/k/v");
+        if (sig->weight_dtype == MARMOT_DTYPE_FLOAT16)
+            return cuda_supported(CUDA_KERNEL_PAGED_ATTENTION_F32_KV_F16, caps, 0.0, 0.0, 0.0);
+        if (sig->weight_dtype == MARMOT_DTYPE_FLOAT32)
+            return cuda_supported(CUDA_KERNEL_PAGED_ATTENTION_F32_KV_F32, caps, 0.0, 0.0, 0.0);
+        return cuda_unsupported("CUDA paged attention KV pool must be FLOAT32 or FLOAT16");
+    case MARMOT_OP_REDUCTION_ARGMAX:
+        if (sig->input_dtype != MARMOT_DTYPE_FLOAT32) return cuda_unsupported("CUDA argmax is FLOAT32");
+        return cuda_supported(CUDA_KERNEL_ARGMAX_F32, caps, 0.0, 0.0, 0.0);
+    default:
+        return cuda_unsupported("no CUDA kernel for this operator");
+    }
+}
+
+marmot_device_caps_t marmot_cuda_detect_default_caps(void) {
+    marmot_device_caps_t caps;
+    memset(&caps, 0, sizeof(caps));
+    mcu_device_caps_t dc;
+    if (mcu_device_caps(0, &dc) != MCU_SUCCESS) return caps;  // no device: every query answers "unsupported"
+    const double ghz = dc.sm_clock_mhz / 1000.0;
+    caps.peak_flops_tflops_fp32 = (float)(dc.sm_count * 128 * 2 * ghz / 1000.0);
+    // fifth-generation tensor cores: 8192 dense fp16/bf16 FMAs per SM and clock
+    caps.peak_flops_tflops_fp16 = (float)(dc.sm_count * 8192.0 * 2 * ghz / 1000.0);
+    caps.mem_bw_gbps = dc.mem_bw_gbps;
+    caps.launch_overhead_us = 4.0f;
+    caps.edge_penalty_alpha = 0.0f;
+    caps.l1_cache_kb = (uint32_t)dc.shared_mem_kb;
+    caps.l2_cache_kb = (uint32_t)dc.l2_cache_kb;
+    caps.num_compute_units = (uint32_t)dc.sm_count;
+    caps.simd_width = 32;
+    caps.has_fma = true;
+    caps.has_fp16_compute = true;
+    caps.has_bf16_compute = true;
+    caps.has_tensor_cores = true;
+    caps.has_simdgroup_mm = false;
+    caps.h2d_bw_gbps = 55.0f;  // PCIe 5 x16
+    caps.d2h_bw_gbps = 55.0f;
+    caps.d2d_bw_gbps = 900.0f;  // NVLink 5, per direction
+    caps.d2d_lat_us = 2.0f;
+    caps.copy_engines = (uint32_t)dc.copy_engines;
+    caps.max_streams = 1;  // one stream per context
+    caps.backend.cuda.sm_count = (uint32_t)dc.sm_count;
+    caps.backend.cuda.shared_mem_kb = (uint32_t)dc.shared_mem_kb;
+    caps.backend.cuda.compute_capability = (uint32_t)dc.compute_capability;
+    return caps;
+}
+
+bool marmot_cuda_default_preferences(const marmot_device_caps_t *caps, marmot_backend_preferences_t *out) {
+    if (out == nullptr) return false;
+    (void)caps;
+    *out = (marmot_backend_preferences_t){
+        .policy =
+            {
+                .embedding_quant_output_dtype = MARMOT_DTYPE_FLOAT32,
+                .quant_activation_mode = MARMOT_QUANT_ACTIVATION_AUTO,
+                .variant_flags_mask = 0,  // no fused variants: the graph builder emits the plain operators
+                .embedding_prefer_gpu_private = true,
+                .embedding_allow_quant_decode_on_the_fly = true,
+                .matmul_requires_temp_tensors = false,
+                .matmul_prefer_packed_weights = false,  // raw GGUF blocks are what the kernels stream
+            },
+        .routing_policy = MARMOT_ROUTING_ALWAYS_GPU,
+    };
+    return true;
 }

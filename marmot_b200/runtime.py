@@ -27,7 +27,7 @@ EXPORTS = (
     "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_peer_comm_create", "mcu_peer_comm_export",
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
     "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
-    "mcu_embedding_gather", "mcu_paged_attention", "mcu_add_rmsnorm", "mcu_rope_qk",
+    "mcu_embedding_gather", "mcu_paged_attention", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps",
 )
 
 

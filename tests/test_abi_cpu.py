@@ -51,6 +51,35 @@ def test_no_cpu_fallback_without_device(lib):
     assert lib.mcu_synchronize(None) == -3
 
 
+class DeviceCaps(C.Structure):
+    """struct mcu_device_caps, include/marmot_cuda.h."""
+    _fields_ = [("sm_count", C.c_int), ("compute_capability", C.c_int), ("shared_mem_kb", C.c_int),
+                ("l2_cache_kb", C.c_int), ("sm_clock_mhz", C.c_int), ("mem_bw_gbps", C.c_float),
+                ("total_mem_bytes", C.c_size_t), ("copy_engines", C.c_int)]
+
+
+def test_device_caps_without_device(lib):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    caps = DeviceCaps(sm_count=7)
+    lib.mcu_device_caps.argtypes = [C.c_int, C.POINTER(DeviceCaps)]
+    assert lib.mcu_device_caps(0, C.byref(caps)) == -3  # MCU_ERROR_DEVICE_NOT_AVAILABLE
+    assert caps.sm_count == 0  # cleared, not left as it was
+    assert lib.mcu_device_caps(0, None) != 0
+
+
+@pytest.mark.gpu
+def test_device_caps_of_a_b200(lib):
+    caps = DeviceCaps()
+    lib.mcu_device_caps.argtypes = [C.c_int, C.POINTER(DeviceCaps)]
+    assert lib.mcu_device_caps(0, C.byref(caps)) == 0
+    assert caps.compute_capability == 100 and caps.sm_count >= 100
+    assert caps.mem_bw_gbps > 4000 and caps.total_mem_bytes > 100 << 30 and caps.shared_mem_kb >= 200
+    assert lib.mcu_device_caps(99, C.byref(caps)) == -3
+
+
 def test_missing_library_is_loud(monkeypatch, tmp_path):
     from marmot_b200 import runtime
 
