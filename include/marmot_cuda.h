@@ -118,6 +118,17 @@ int mcu_quantize_activations(
     float *d_dev, int16_t *bsums_dev
 );
 
+/* ---- quantized row dot: cpu_vec_dot (src/backends/cpu/ops/vec_dot/vec_dot.c:6-65, the public marmot_vec_dot),
+ *      the building block the reference's own golden vectors pin (tests/backend/golden_vec_dot_llama.h).
+ *      One weight row of num_blocks GGUF blocks times one PRE-QUANTIZED activation row given as the reference's
+ *      block structs (Q8_K blocks of 292 bytes {f32 d, int8 qs[256], int16 bsums[16]} for the K-quants,
+ *      Q8_0 blocks of 34 bytes for Q8_0), both in host memory as in the reference API; the integer dots and the
+ *      per-block f32 terms are those of the decode kernels. ---- */
+int mcu_vec_dot_host(
+    mcu_context_t *ctx, int weight_kind, const void *weights_host, const void *activations_host, size_t num_blocks,
+    float *result_host
+);
+
 /* ---- quantized linear: cpu_matmul_quantized_{q4_k,q6_k,q8_0} -> cpu_matmul_quantized_impl
  *      (src/backends/cpu/ops/matmul/quantized/matmul_quant_dispatch.c:373-591,905-960) with the bias epilogue of
  *      cpu_matmul_apply_epilogue (src/backends/cpu/ops/matmul/matmul_epilogue.c).

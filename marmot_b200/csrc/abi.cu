@@ -437,6 +437,83 @@ int mcu_quantize_activations(mcu_context_t *ctx, int weight_kind, const float *x
     return MCU_SUCCESS;
 }
 
+static float half_bits_to_float_host(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1Fu, man = h & 0x3FFu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else {  // subnormal: normalise
+            int e = -1;
+            uint32_t m = man;
+            do {
+                ++e;
+                m <<= 1;
+            } while ((m & 0x400u) == 0);
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((m & 0x3FFu) << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7F800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 112u) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, sizeof(f));
+    return f;
+}
+
+int mcu_vec_dot_host(mcu_context_t *ctx, int weight_kind, const void *weights_host, const void *activations_host,
+                     size_t num_blocks, float *result_host) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (result_host == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "vec_dot: null result");
+    if (!kind_supported(weight_kind)) return fail(MCU_ERROR_NOT_IMPLEMENTED, "quant kind %d has no CUDA kernel", weight_kind);
+    if (weights_host == nullptr || activations_host == nullptr || num_blocks == 0) {
+        *result_host = 0.0f;  // as cpu_vec_dot
+        return MCU_SUCCESS;
+    }
+    const bool kq = weight_kind != MCU_KIND_Q8_0;
+    const size_t bv = (size_t)block_values(weight_kind), kp = num_blocks * bv;
+    if (kp > ((size_t)1 << 24)) return fail(MCU_ERROR_INVALID_ARGUMENT, "vec_dot: row too long");
+    // The activation blocks as the structure of arrays the decode kernels read (no arithmetic: bytes are moved).
+    std::vector<int8_t> qs(kp);
+    std::vector<float> d(num_blocks);
+    std::vector<int16_t> bsums(kq ? num_blocks * 16 : 0);
+    const uint8_t *a = (const uint8_t *)activations_host;
+    for (size_t b = 0; b < num_blocks; ++b) {
+        if (kq) {  // {f32 d, int8 qs[256], int16 bsums[16]}
+            const uint8_t *blk = a + b * 292;
+            memcpy(&d[b], blk, 4);
+            for (int v = 0; v < 256; ++v) qs[b * 256 + ((v >> 5) & 1) * 128 + (v >> 6) * 32 + (v & 31)] = (int8_t)blk[4 + v];
+            memcpy(&bsums[b * 16], blk + 260, 32);
+        } else {  // {f16 d, int8 qs[32]}
+            const uint8_t *blk = a + b * 34;
+            uint16_t hb;
+            memcpy(&hb, blk, 2);
+            d[b] = half_bits_to_float_host(hb);
+            memcpy(&qs[b * 32], blk + 2, 32);
+        }
+    }
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    const size_t wbytes = num_blocks * (size_t)block_bytes(weight_kind);
+    if (int rc = ensure(ctx, ctx->act_qs, kp)) return rc;
+    if (int rc = ensure(ctx, ctx->act_d, num_blocks * sizeof(float))) return rc;
+    if (int rc = ensure(ctx, ctx->act_bsums, (kq ? num_blocks * 16 : 1) * sizeof(int16_t))) return rc;
+    if (int rc = ensure(ctx, ctx->x_stage, wbytes)) return rc;
+    if (int rc = ensure(ctx, ctx->out_stage, sizeof(float))) return rc;
+    cudaStream_t s = ctx->stream;
+    MCU_CUDA(cudaMemcpyAsync(ctx->act_qs.ptr, qs.data(), kp, cudaMemcpyHostToDevice, s));
+    MCU_CUDA(cudaMemcpyAsync(ctx->act_d.ptr, d.data(), num_blocks * sizeof(float), cudaMemcpyHostToDevice, s));
+    if (kq) MCU_CUDA(cudaMemcpyAsync(ctx->act_bsums.ptr, bsums.data(), num_blocks * 32, cudaMemcpyHostToDevice, s));
+    MCU_CUDA(cudaMemcpyAsync(ctx->x_stage.ptr, weights_host, wbytes, cudaMemcpyHostToDevice, s));
+    ActBuffers ab{(int8_t *)ctx->act_qs.ptr, (float *)ctx->act_d.ptr, (int16_t *)ctx->act_bsums.ptr};
+    MCU_CUDA(launch_gemv(weight_kind, ctx->x_stage.ptr, nullptr, ab, 1, (int)kp, 1, nullptr, (float *)ctx->out_stage.ptr,
+                         nullptr, 1, s));
+    count_launches(1);
+    MCU_CUDA(cudaMemcpyAsync(result_host, ctx->out_stage.ptr, sizeof(float), cudaMemcpyDeviceToHost, s));
+    MCU_CUDA(cudaStreamSynchronize(s));  // the host vectors above must outlive the copies
+    return check_device_error(ctx);
+}
+
 int mcu_linear(mcu_context_t *ctx, int kind, const float *x_dev, size_t ldx, const void *w_dev, size_t T, size_t K,
                size_t F, const float *bias_dev, float *out_dev, size_t ldo) {
     if (int rc = check_ctx(ctx)) return rc;

@@ -10,6 +10,7 @@
 //   cuda_moe_experts_impl          <- cpu_moe_experts_impl, src/backends/cpu/ops/moe/moe_ops.c:1069-1178
 //   cuda_topk_impl                 <- cpu_topk_impl, moe_ops.c:789-889
 //   cuda_dequantize_*              <- cpu_dequantize_*, src/backends/cpu/quantization/formats/*.c
+//   cuda_vec_dot                   <- cpu_vec_dot, src/backends/cpu/ops/vec_dot/vec_dot.c:6-65
 //   marmot_cuda_query_kernel, marmot_cuda_detect_default_caps, marmot_cuda_default_preferences
 //                                  <- the externs of src/core/dispatch/kernel_query.c:10-17
 //
@@ -581,6 +582,41 @@ marmot_error_t cuda_dequantize_q6_k(const void *device_ctx, const marmot_tensor_
 
 marmot_error_t cuda_dequantize_q8_0(const void *device_ctx, const marmot_tensor_t *input, marmot_tensor_t *output) {
     return cuda_dequantize_blockwise(device_ctx, MCU_KIND_Q8_0, input, output);
+}
+
+// ---- quantized row dot (the public marmot_vec_dot; host pointers, as in the reference) ----------------
+// num_blocks counts 32-value blocks in the descriptor's convention for Q8_0 activations and 256-value super-blocks for
+// Q8_K ones, exactly what cpu_vec_dot hands to its dot kernels (src/backends/cpu/ops/vec_dot/vec_dot.c:52-62).
+marmot_error_t cuda_vec_dot(const void *device_ctx, const marmot_vec_dot_descriptor_t *desc, float *result) {
+    if (desc == nullptr || result == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "cuda_vec_dot: null descriptor or result");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    if (desc->weights == nullptr || desc->activations == nullptr || desc->num_blocks == 0) {
+        *result = 0.0f;
+        return MARMOT_SUCCESS;
+    }
+    if (device_ctx == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "cuda_vec_dot: null device context");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    const int kind = mcu_kind_of(desc->weight_kind);
+    if (kind < 0) {
+        marmot_set_error(MARMOT_ERROR_NOT_IMPLEMENTED, "cuda_vec_dot: unsupported quantization kind");
+        return MARMOT_ERROR_NOT_IMPLEMENTED;
+    }
+    if (desc->layout != MARMOT_QUANT_LAYOUT_GGUF) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "cuda_vec_dot: quantization layout mismatch");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    const marmot_quant_kind_t expected = kind == MCU_KIND_Q8_0 ? MARMOT_QUANT_KIND_Q8_0 : MARMOT_QUANT_KIND_Q8_K;
+    if (desc->activation_kind != expected) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "cuda_vec_dot: activation kind mismatch");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    const int rc = mcu_vec_dot_host(c->mcu, kind, desc->weights, desc->activations, desc->num_blocks, result);
+    return rc == 0 ? MARMOT_SUCCESS : cuda_fail(rc);
 }
 
 // ---- kernel query, capabilities, preferences ----------------------------------------------------------

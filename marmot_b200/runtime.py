@@ -27,7 +27,7 @@ EXPORTS = (
     "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_peer_comm_create", "mcu_peer_comm_export",
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
     "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
-    "mcu_embedding_gather", "mcu_paged_attention", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps",
+    "mcu_embedding_gather", "mcu_paged_attention", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps", "mcu_vec_dot_host",
 )
 
 
@@ -81,6 +81,7 @@ def load_library() -> C.CDLL:
     L.mcu_linear_host.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_linear_static_scratch.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_topk.argtypes = [vp, vp, sz, sz, sz, sz, vp, vp]
+    L.mcu_vec_dot_host.argtypes = [vp, i32, vp, vp, sz, vp]
     L.mcu_moe_experts.argtypes = [vp, i32, i32, i32, vp, sz, sz, sz, sz, vp, vp, vp, vp, vp, sz, i32, f32, i32, vp]
     L.mcu_moe_experts_local.argtypes = [vp, i32, i32, i32, vp, sz, sz, sz, sz, sz, sz, vp, vp, vp, vp, vp, sz, i32, f32,
                                         i32, vp]
@@ -210,6 +211,14 @@ class Context:
         self._check(self.lib.mcu_linear_host(self.handle, kind, x_host.ctypes.data, x_host.strides[0] // 4, _ptr(w), T, K,
                                              F, bp, out_host.ctypes.data, out_host.strides[0] // 4))
         return out_host
+
+    def vec_dot_host(self, kind: int, weights: np.ndarray, activations: np.ndarray, num_blocks: int) -> float:
+        """One weight row times one pre-quantized activation row (reference block structs as uint8 arrays)."""
+        w = np.ascontiguousarray(weights, dtype=np.uint8)
+        a = np.ascontiguousarray(activations, dtype=np.uint8)
+        out = C.c_float(0.0)
+        self._check(self.lib.mcu_vec_dot_host(self.handle, kind, w.ctypes.data, a.ctypes.data, num_blocks, C.byref(out)))
+        return float(out.value)
 
     def topk(self, x, k: int):
         rows, cols = x.shape

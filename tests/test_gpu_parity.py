@@ -212,6 +212,33 @@ def test_linear_llama_golden(ctx, llama_goldens, name):
     assert np.all(np.abs(got - exp) <= np.abs(exp) * 5e-5 + 2e-5)
 
 
+@pytest.mark.parametrize("name,act,nb", [("q4_k", "q8_k", 1), ("q6_k", "q8_k", 1), ("q8_0", "q8_0", 8)])
+def test_vec_dot_llama_golden(ctx, oracle, llama_goldens, name, act, nb):
+    """The row dot on pre-quantized activation blocks against the reference's llama.cpp golden vectors, at the
+    reference's own tolerance (tests/backend/test_vec_dot.c:135-156), and against the oracle."""
+    w, a = llama_goldens[f"vec_dot_{name}_weights"], llama_goldens[f"vec_dot_{act}_activations"]
+    got = ctx.vec_dot_host(KINDS[name], w, a, nb)
+    exp = float(llama_goldens[f"vec_dot_{name}_{act}_expected"][0])
+    assert abs(got - exp) <= abs(exp) * 2e-5 + 1e-5
+    ref = oracle.vec_dot(KINDS[name], w, a, nb)
+    assert abs(got - ref) <= abs(ref) * 2e-6 + 1e-6
+    assert ctx.vec_dot_host(KINDS[name], w, a, 0) == 0.0  # as cpu_vec_dot: nothing to do
+
+
+def test_vec_dot_long_row(ctx, oracle):
+    """A 4096-value row: activations packed by the oracle into the reference's Q8_K / Q8_0 block structs."""
+    rng = np.random.default_rng(11)
+    K = 4096
+    x = rng.normal(0, 1, K).astype(np.float32)
+    for kind in (KIND_Q4_K, KIND_Q6_K, KIND_Q8_0):
+        W = random_blocks(kind, 1, K, rng)
+        acts = oracle.pack_q8_0(x) if kind == KIND_Q8_0 else oracle.pack_q8_k(x)
+        nb = K // (32 if kind == KIND_Q8_0 else 256)
+        got = ctx.vec_dot_host(kind, W, acts, nb)
+        want = oracle.vec_dot(kind, W, acts, nb)
+        assert abs(got - want) <= abs(want) * 2e-5 + 1e-5
+
+
 @pytest.mark.parametrize("name", NAMES)
 @pytest.mark.parametrize("case", [0, 1, 2])
 def test_linear_reference_fixture(ctx, ref_cases, name, case):

@@ -219,3 +219,35 @@ def test_moe_experts(backend):
             ref.lib.marmot_tensor_destroy(t)
     assert max_rel_err(got, want) <= TOL_MOE
     assert cosine(got, want) >= 0.999
+
+
+class _VecDotDesc(C.Structure):
+    """struct marmot_vec_dot_descriptor, include/marmot/ops_types.h:136-143."""
+    _fields_ = [("weights", C.c_void_p), ("activations", C.c_void_p), ("num_blocks", C.c_size_t),
+                ("weight_kind", C.c_int), ("activation_kind", C.c_int), ("layout", C.c_int)]
+
+
+@pytest.mark.parametrize("name,kind,act,act_kind,nb", [("q4_k", KIND_Q4_K, "q8_k", 12, 1), ("q6_k", KIND_Q6_K, "q8_k", 12, 1),
+                                                      ("q8_0", KIND_Q8_0, "q8_0", KIND_Q8_0, 8)])
+def test_vec_dot_llama_golden(backend, llama_goldens, name, kind, act, act_kind, nb):
+    """cuda_vec_dot on the reference's llama.cpp golden vectors, at the tolerance of tests/backend/test_vec_dot.c:135-156,
+    and against the reference's own cpu_vec_dot through the public marmot_vec_dot."""
+    L = backend.lib
+    L.cuda_vec_dot.argtypes = [C.c_void_p, C.POINTER(_VecDotDesc), C.POINTER(C.c_float)]
+    w = np.ascontiguousarray(llama_goldens[f"vec_dot_{name}_weights"], dtype=np.uint8)
+    a = np.ascontiguousarray(llama_goldens[f"vec_dot_{act}_activations"], dtype=np.uint8)
+    desc = _VecDotDesc(w.ctypes.data, a.ctypes.data, nb, kind, act_kind, 1)  # MARMOT_QUANT_LAYOUT_GGUF
+    out = C.c_float(-1.0)
+    assert L.cuda_vec_dot(backend.ctx, C.byref(desc), C.byref(out)) == 0
+    exp = float(llama_goldens[f"vec_dot_{name}_{act}_expected"][0])
+    assert abs(out.value - exp) <= abs(exp) * 2e-5 + 1e-5
+    ref = backend.ref.lib
+    ref.marmot_vec_dot.argtypes = [C.c_void_p, C.POINTER(_VecDotDesc), C.POINTER(C.c_float)]
+    want = C.c_float(-1.0)
+    assert ref.marmot_vec_dot(backend.ref.ctx, C.byref(desc), C.byref(want)) == 0
+    assert abs(out.value - want.value) <= abs(want.value) * 2e-6 + 1e-6
+    # the reference's argument checks
+    bad = _VecDotDesc(w.ctypes.data, a.ctypes.data, nb, kind, KIND_Q4_K, 1)
+    assert L.cuda_vec_dot(backend.ctx, C.byref(bad), C.byref(out)) != 0  # activation kind mismatch
+    empty = _VecDotDesc(w.ctypes.data, a.ctypes.data, 0, kind, act_kind, 1)
+    assert L.cuda_vec_dot(backend.ctx, C.byref(empty), C.byref(out)) == 0 and out.value == 0.0
