@@ -246,6 +246,65 @@ int mcu_paged_attention(
     size_t block_size, float scale, float *out_dev
 );
 
+/* ---- paged KV-cache pool: marmot_kv_pool_* (include/marmot/inference/kv_pool.h:65-101, implementation
+ *      src/inference/kv_pool/kv_pool.cpp).  Same bookkeeping, decision for decision (slot and block order, reference
+ *      counts and copy on write for shared prefixes, retained blocks, swap with the exchange path, error codes); the K
+ *      and V pools [blocks][layers][kv_heads][block_size][head_dim] and the block table [max_seqs][max_blocks_per_seq]
+ *      u32 live in device memory (what mcu_paged_attention reads), swap blocks in page-locked host memory, and every
+ *      table edit, clone and swap is an asynchronous copy on the context's stream: kernels enqueued after a call see
+ *      its effect, and nothing waits for the device.  kv_slot = (block_id << log2(block_size)) | offset, as in the
+ *      reference.  A pool created with ctx == NULL keeps books only (no storage), for admission planning.
+ *      FP8 pools (per-block scales) are not covered: MCU_ERROR_UNSUPPORTED_DTYPE. ---- */
+#define MCU_BLOCK_ID_INVALID 0xFFFFFFFFu
+enum { MCU_KV_POOL_FLAG_NONE = 0, MCU_KV_POOL_FLAG_DETERMINISTIC_ALLOC = 1 };
+typedef struct mcu_kv_pool mcu_kv_pool_t;
+typedef struct mcu_kv_pool_options {
+    uint64_t flags;
+    size_t max_seqs, max_seq_len, block_size;
+    size_t num_blocks, num_swap_blocks, num_layers, num_kv_heads, head_dim;
+    int kv_dtype; /* MCU_KV_F32 / MCU_KV_F16 */
+} mcu_kv_pool_options_t;
+typedef struct mcu_kv_append_plan {
+    uint32_t seq;
+    size_t token_count;
+    uint64_t cookie;
+} mcu_kv_append_plan_t;
+typedef struct mcu_kv_prefix_plan {
+    uint32_t seq;
+    size_t num_blocks, prefix_len;
+    uint64_t cookie;
+} mcu_kv_prefix_plan_t;
+int mcu_kv_pool_options_init(mcu_kv_pool_options_t *opts);
+int mcu_kv_pool_create(mcu_context_t *ctx, const mcu_kv_pool_options_t *opts, mcu_kv_pool_t **out_pool);
+void mcu_kv_pool_destroy(mcu_kv_pool_t *pool);
+int mcu_kv_pool_acquire_seq(mcu_kv_pool_t *pool, uint32_t *out_seq);
+int mcu_kv_pool_release_seq(mcu_kv_pool_t *pool, uint32_t seq);
+int mcu_kv_pool_prepare_append(
+    mcu_kv_pool_t *pool, uint32_t seq, size_t token_count, mcu_kv_append_plan_t *out_plan, uint32_t *out_slots,
+    size_t *out_start_pos
+);
+int mcu_kv_pool_commit_append(mcu_kv_pool_t *pool, const mcu_kv_append_plan_t *plan);
+void mcu_kv_pool_abort_append(mcu_kv_pool_t *pool, const mcu_kv_append_plan_t *plan);
+int mcu_kv_pool_prepare_prefix_attach(
+    mcu_kv_pool_t *pool, uint32_t seq, const uint32_t *block_ids, size_t num_blocks, size_t prefix_len,
+    mcu_kv_prefix_plan_t *out_plan
+);
+int mcu_kv_pool_commit_prefix_attach(mcu_kv_pool_t *pool, const mcu_kv_prefix_plan_t *plan);
+void mcu_kv_pool_abort_prefix_attach(mcu_kv_pool_t *pool, const mcu_kv_prefix_plan_t *plan);
+/* device pointers of the K pool, the V pool and the block table (marmot_kv_pool_get_tensors); NULL for a books-only pool */
+int mcu_kv_pool_get_pointers(
+    mcu_kv_pool_t *pool, void **out_k_dev, void **out_v_dev, uint32_t **out_block_table_dev, size_t *out_max_blocks_per_seq
+);
+size_t mcu_kv_pool_free_block_count(mcu_kv_pool_t *pool);
+size_t mcu_kv_pool_total_block_count(mcu_kv_pool_t *pool);
+size_t mcu_kv_pool_seq_len(mcu_kv_pool_t *pool, uint32_t seq);
+uint32_t mcu_kv_pool_block_id(mcu_kv_pool_t *pool, uint32_t seq, size_t logical_block);
+uint32_t mcu_kv_pool_block_generation(mcu_kv_pool_t *pool, uint32_t block_id);
+void mcu_kv_pool_set_block_retained(mcu_kv_pool_t *pool, uint32_t block_id, int retained);
+int mcu_kv_pool_swap_out_seq(mcu_kv_pool_t *pool, uint32_t seq);
+int mcu_kv_pool_swap_in_seq(mcu_kv_pool_t *pool, uint32_t seq);
+int mcu_kv_pool_is_seq_swapped(mcu_kv_pool_t *pool, uint32_t seq, int *out_swapped);
+
 /* ---- tensor / expert parallelism over the GPUs of one box.  No reference counterpart: the reference runs on
  *      one device (include/marmot/device.h:72-80) and only reserves placeholders for sharding
  *      (include/marmot/graph/kernel_selection.h:18-23). ---- */

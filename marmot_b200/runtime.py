@@ -28,6 +28,12 @@ EXPORTS = (
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
     "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
     "mcu_embedding_gather", "mcu_paged_attention", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps", "mcu_vec_dot_host",
+    "mcu_kv_pool_options_init", "mcu_kv_pool_create", "mcu_kv_pool_destroy", "mcu_kv_pool_acquire_seq",
+    "mcu_kv_pool_release_seq", "mcu_kv_pool_prepare_append", "mcu_kv_pool_commit_append", "mcu_kv_pool_abort_append",
+    "mcu_kv_pool_prepare_prefix_attach", "mcu_kv_pool_commit_prefix_attach", "mcu_kv_pool_abort_prefix_attach",
+    "mcu_kv_pool_get_pointers", "mcu_kv_pool_free_block_count", "mcu_kv_pool_total_block_count", "mcu_kv_pool_seq_len",
+    "mcu_kv_pool_block_id", "mcu_kv_pool_block_generation", "mcu_kv_pool_set_block_retained", "mcu_kv_pool_swap_out_seq",
+    "mcu_kv_pool_swap_in_seq", "mcu_kv_pool_is_seq_swapped",
 )
 
 
@@ -381,3 +387,156 @@ def _tensor_from_ptr(torch, ptr: int, shape, device_index: int):
     e.__cuda_array_interface__ = {"shape": tuple(int(v) for v in shape), "typestr": "<f4", "data": (int(ptr), False),
                                   "version": 2}
     return torch.as_tensor(e, device=torch.device("cuda", device_index))
+
+
+class _KvPoolOptions(C.Structure):
+    """struct mcu_kv_pool_options."""
+    _fields_ = [("flags", C.c_uint64), ("max_seqs", C.c_size_t), ("max_seq_len", C.c_size_t), ("block_size", C.c_size_t),
+                ("num_blocks", C.c_size_t), ("num_swap_blocks", C.c_size_t), ("num_layers", C.c_size_t),
+                ("num_kv_heads", C.c_size_t), ("head_dim", C.c_size_t), ("kv_dtype", C.c_int)]
+
+
+class _KvAppendPlan(C.Structure):
+    _fields_ = [("seq", C.c_uint32), ("token_count", C.c_size_t), ("cookie", C.c_uint64)]
+
+
+class _KvPrefixPlan(C.Structure):
+    _fields_ = [("seq", C.c_uint32), ("num_blocks", C.c_size_t), ("prefix_len", C.c_size_t), ("cookie", C.c_uint64)]
+
+
+class KvPool:
+    """The paged KV-cache pool (marmot_cuda.h: mcu_kv_pool_*).  `ctx=None` keeps books only (no GPU needed).
+    Methods return the library's status code (0 = success) next to their outputs, as the reference API does."""
+
+    def __init__(self, ctx: "Context | None", *, max_seqs: int, max_seq_len: int, block_size: int, num_blocks: int,
+                 num_swap_blocks: int = 0, num_layers: int = 1, num_kv_heads: int = 1, head_dim: int = 64,
+                 kv_f16: bool = True, deterministic: bool = False, lib=None):
+        self.lib = L = lib or (ctx.lib if ctx is not None else load_library())
+        self.ctx = ctx
+        vp, sz, u32 = C.c_void_p, C.c_size_t, C.c_uint32
+        L.mcu_kv_pool_create.argtypes = [vp, C.POINTER(_KvPoolOptions), C.POINTER(vp)]
+        L.mcu_kv_pool_destroy.argtypes = [vp]
+        L.mcu_kv_pool_destroy.restype = None
+        L.mcu_kv_pool_acquire_seq.argtypes = [vp, C.POINTER(u32)]
+        L.mcu_kv_pool_release_seq.argtypes = [vp, u32]
+        L.mcu_kv_pool_prepare_append.argtypes = [vp, u32, sz, C.POINTER(_KvAppendPlan), C.POINTER(u32), C.POINTER(sz)]
+        L.mcu_kv_pool_commit_append.argtypes = [vp, C.POINTER(_KvAppendPlan)]
+        L.mcu_kv_pool_abort_append.argtypes = [vp, C.POINTER(_KvAppendPlan)]
+        L.mcu_kv_pool_abort_append.restype = None
+        L.mcu_kv_pool_prepare_prefix_attach.argtypes = [vp, u32, C.POINTER(u32), sz, sz, C.POINTER(_KvPrefixPlan)]
+        L.mcu_kv_pool_commit_prefix_attach.argtypes = [vp, C.POINTER(_KvPrefixPlan)]
+        L.mcu_kv_pool_abort_prefix_attach.argtypes = [vp, C.POINTER(_KvPrefixPlan)]
+        L.mcu_kv_pool_abort_prefix_attach.restype = None
+        L.mcu_kv_pool_get_pointers.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(sz)]
+        for name in ("free_block_count", "total_block_count"):
+            getattr(L, f"mcu_kv_pool_{name}").argtypes = [vp]
+            getattr(L, f"mcu_kv_pool_{name}").restype = sz
+        L.mcu_kv_pool_seq_len.argtypes = [vp, u32]
+        L.mcu_kv_pool_seq_len.restype = sz
+        L.mcu_kv_pool_block_id.argtypes = [vp, u32, sz]
+        L.mcu_kv_pool_block_id.restype = u32
+        L.mcu_kv_pool_block_generation.argtypes = [vp, u32]
+        L.mcu_kv_pool_block_generation.restype = u32
+        L.mcu_kv_pool_set_block_retained.argtypes = [vp, u32, C.c_int]
+        L.mcu_kv_pool_set_block_retained.restype = None
+        L.mcu_kv_pool_swap_out_seq.argtypes = [vp, u32]
+        L.mcu_kv_pool_swap_in_seq.argtypes = [vp, u32]
+        L.mcu_kv_pool_is_seq_swapped.argtypes = [vp, u32, C.POINTER(C.c_int)]
+        opts = _KvPoolOptions(1 if deterministic else 0, max_seqs, max_seq_len, block_size, num_blocks, num_swap_blocks,
+                              num_layers, num_kv_heads, head_dim, 1 if kv_f16 else 0)
+        self.shape = (num_blocks, num_layers, num_kv_heads, block_size, head_dim)
+        self.kv_f16 = kv_f16
+        self.max_seqs = max_seqs
+        h = vp()
+        rc = L.mcu_kv_pool_create(ctx.handle if ctx is not None else None, C.byref(opts), C.byref(h))
+        if rc != 0:
+            raise MarmotCudaError(rc, L.mcu_last_error_message().decode())
+        self.handle = h
+
+    def close(self):
+        if self.handle:
+            self.lib.mcu_kv_pool_destroy(self.handle)
+            self.handle = None
+
+    def acquire_seq(self):
+        seq = C.c_uint32(0xFFFFFFFF)
+        rc = self.lib.mcu_kv_pool_acquire_seq(self.handle, C.byref(seq))
+        return rc, seq.value
+
+    def release_seq(self, seq: int) -> int:
+        return self.lib.mcu_kv_pool_release_seq(self.handle, seq)
+
+    def prepare_append(self, seq: int, n: int):
+        plan = _KvAppendPlan()
+        slots = (C.c_uint32 * max(n, 1))()
+        start = C.c_size_t(0)
+        rc = self.lib.mcu_kv_pool_prepare_append(self.handle, seq, n, C.byref(plan), slots, C.byref(start))
+        return rc, plan, list(slots[:n]) if rc == 0 else [], start.value
+
+    def commit_append(self, plan) -> int:
+        return self.lib.mcu_kv_pool_commit_append(self.handle, C.byref(plan))
+
+    def abort_append(self, plan) -> None:
+        self.lib.mcu_kv_pool_abort_append(self.handle, C.byref(plan))
+
+    def prepare_prefix_attach(self, seq: int, block_ids, prefix_len: int):
+        plan = _KvPrefixPlan()
+        ids = (C.c_uint32 * max(len(block_ids), 1))(*block_ids)
+        rc = self.lib.mcu_kv_pool_prepare_prefix_attach(self.handle, seq, ids, len(block_ids), prefix_len, C.byref(plan))
+        return rc, plan
+
+    def commit_prefix_attach(self, plan) -> int:
+        return self.lib.mcu_kv_pool_commit_prefix_attach(self.handle, C.byref(plan))
+
+    def abort_prefix_attach(self, plan) -> None:
+        self.lib.mcu_kv_pool_abort_prefix_attach(self.handle, C.byref(plan))
+
+    def free_block_count(self) -> int:
+        return self.lib.mcu_kv_pool_free_block_count(self.handle)
+
+    def total_block_count(self) -> int:
+        return self.lib.mcu_kv_pool_total_block_count(self.handle)
+
+    def seq_len(self, seq: int) -> int:
+        return self.lib.mcu_kv_pool_seq_len(self.handle, seq)
+
+    def block_id(self, seq: int, logical: int) -> int:
+        return self.lib.mcu_kv_pool_block_id(self.handle, seq, logical)
+
+    def block_generation(self, block: int) -> int:
+        return self.lib.mcu_kv_pool_block_generation(self.handle, block)
+
+    def set_block_retained(self, block: int, keep: bool) -> None:
+        self.lib.mcu_kv_pool_set_block_retained(self.handle, block, 1 if keep else 0)
+
+    def swap_out(self, seq: int) -> int:
+        return self.lib.mcu_kv_pool_swap_out_seq(self.handle, seq)
+
+    def swap_in(self, seq: int) -> int:
+        return self.lib.mcu_kv_pool_swap_in_seq(self.handle, seq)
+
+    def is_swapped(self, seq: int) -> bool:
+        out = C.c_int(0)
+        self.lib.mcu_kv_pool_is_seq_swapped(self.handle, seq, C.byref(out))
+        return bool(out.value)
+
+    def tensors(self):
+        """(kv_k, kv_v, block_table) as torch tensors over the pool's device memory (no copy)."""
+        import torch
+
+        k, v, t, mb = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_size_t()
+        self.lib.mcu_kv_pool_get_pointers(self.handle, C.byref(k), C.byref(v), C.byref(t), C.byref(mb))
+        if not k.value:
+            raise MarmotCudaError(-1, "the pool keeps books only: it has no storage")
+        dev = torch.device("cuda", self.ctx.device)
+        dt = torch.float16 if self.kv_f16 else torch.float32
+
+        def view(ptr, shape, dtype):
+            n = int(np.prod(shape))
+            holder = type("_Cai", (), {"__cuda_array_interface__": {
+                "shape": (n,), "typestr": {torch.float16: "<f2", torch.float32: "<f4", torch.int32: "<i4"}[dtype],
+                "data": (ptr, False), "version": 2}})()
+            return torch.as_tensor(holder, device=dev).view(shape)
+
+        return (view(k.value, self.shape, dt), view(v.value, self.shape, dt),
+                view(t.value, (self.max_seqs, mb.value), torch.int32))

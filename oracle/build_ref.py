@@ -185,6 +185,38 @@ def build(ref_root: Path, jobs: int | None = None, verbose: bool = True) -> Path
     return OUT_LIB
 
 
+KV_POOL_LIB = OUT_DIR / "libmarmot_ref_kvpool.so"
+KV_POOL_SOURCES = ("src/inference/kv_pool/kv_pool.cpp", "src/inference/common/storage.cpp", "src/api/kv_pool_api.cpp")
+
+
+def build_kv_pool(ref_root: Path) -> Path:
+    """The reference's paged KV-cache pool (C++23, three translation units compiled where they lie) as a second
+    library beside libmarmot_ref.so, which supplies the tensor API it uses.  The checker of the CUDA pool's books."""
+    ref_root = ref_root.resolve()
+    if not OUT_LIB.exists():
+        raise FileNotFoundError("build libmarmot_ref.so first")
+    newest = max((ref_root / s).stat().st_mtime for s in KV_POOL_SOURCES)
+    if KV_POOL_LIB.exists() and KV_POOL_LIB.stat().st_mtime >= max(newest, OUT_LIB.stat().st_mtime):
+        return KV_POOL_LIB
+    stage = Path(tempfile.mkdtemp(prefix="marmot_ref_kvpool_"))
+    try:
+        objs = []
+        for i, src in enumerate(KV_POOL_SOURCES):
+            obj = stage / f"{i}.o"
+            subprocess.run(["g++", "-std=c++23", "-O1", "-fPIC", "-w", "-include", "utility", "-include", "cmath", *DEFINES,
+                            f"-I{ref_root / 'include'}", f"-I{ref_root / 'src'}", f"-I{ref_root}", "-c", str(ref_root / src),
+                            "-o", str(obj)], check=True)
+            objs.append(str(obj))
+        tmp = stage / KV_POOL_LIB.name
+        subprocess.run(["g++", "-shared", "-o", str(tmp), *objs, f"-L{OUT_DIR}", f"-l:{OUT_LIB.name}", "-Wl,-rpath,$ORIGIN"],
+                       check=True)
+        shutil.copyfile(tmp, KV_POOL_LIB)
+    finally:
+        shutil.rmtree(stage, ignore_errors=True)
+    return KV_POOL_LIB
+
+
 if __name__ == "__main__":
     root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(os.environ.get("MARMOT_REFERENCE_ROOT", "/root/reference"))
     print(build(root))
+    print(build_kv_pool(root))

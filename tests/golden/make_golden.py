@@ -168,12 +168,35 @@ def make_decoder_cases() -> dict[str, np.ndarray]:
     return out
 
 
+def make_kv_pool_traces() -> dict:
+    """Everything observable of the reference's KV-cache pool (status codes, sequence and kv slots, free counts, block
+    tables) on the seeded random schedules of tests/kv_pool_ref.py:drive."""
+    import json
+
+    from oracle.bindings import Reference
+    from tests.kv_pool_ref import RefKvPool
+    from tests.test_kv_pool_cpu import CONFIGS, run
+
+    ref = Reference()
+    out = {}
+    for name in sorted(CONFIGS):
+        for seed in (1, 2):
+            pool = RefKvPool(ref, **CONFIGS[name])
+            out[f"{name}/{seed}"] = json.loads(json.dumps(run(pool, name, seed)))
+            pool.close()
+    ref.close()
+    return out
+
+
 def main() -> None:
     ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(os.environ.get("MARMOT_REFERENCE_ROOT", "/root/reference"))
     np.savez_compressed(HERE / "llama_goldens.npz", **dump_reference_goldens(ref_root))
     np.savez_compressed(HERE / "ref_cases.npz", **make_ref_cases())
     np.savez_compressed(HERE / "decoder_cases.npz", **make_decoder_cases())
-    for f in ("llama_goldens.npz", "ref_cases.npz", "decoder_cases.npz"):
+    import json
+
+    (HERE / "kv_pool_traces.json").write_text(json.dumps(make_kv_pool_traces(), separators=(",", ":")))
+    for f in ("llama_goldens.npz", "ref_cases.npz", "decoder_cases.npz", "kv_pool_traces.json"):
         print(f, (HERE / f).stat().st_size, "bytes")
 
 
