@@ -90,6 +90,19 @@ void mcu_context_destroy(mcu_context_t *ctx);
 int mcu_context_set_stream(mcu_context_t *ctx, void *cuda_stream);
 void *mcu_context_get_stream(mcu_context_t *ctx);
 int mcu_context_set_regime(mcu_context_t *ctx, int regime);
+
+/* ---- CUDA-graph capture: what graph_batch_begin / graph_batch_end of the device-ops vtable bracket
+ *      (include/marmot/device.h:59-60, called around a bytecode program by src/core/context/context.c:260-286).
+ *      Every call between begin and end is recorded on the context's stream instead of run; mcu_graph_launch replays
+ *      the whole sequence with one launch (a decode step of a few hundred small kernels is bound by launch latency
+ *      otherwise).  Run the sequence once before capturing: workspace cannot grow during a capture, and the entry
+ *      points that wait for the device (mcu_linear_host, mcu_vec_dot_host, mcu_moe_experts, mcu_synchronize) refuse
+ *      to be captured.  The recorded pointers are the ones passed during capture: update inputs in place. ---- */
+typedef struct mcu_graph mcu_graph_t;
+int mcu_graph_capture_begin(mcu_context_t *ctx);
+int mcu_graph_capture_end(mcu_context_t *ctx, mcu_graph_t **out_graph); /* out_graph NULL: discard the capture */
+int mcu_graph_launch(mcu_graph_t *graph);
+void mcu_graph_destroy(mcu_graph_t *graph);
 int mcu_synchronize(mcu_context_t *ctx);
 const char *mcu_last_error_message(void);
 /* Number of kernels this context has launched so far. */

@@ -74,8 +74,22 @@ struct mcu_context {
     int *dev_err = nullptr;  // set by kernels whose bounded device-side waits ran out
 };
 
+static bool stream_is_capturing(cudaStream_t s) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &st) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return st != cudaStreamCaptureStatusNone;
+}
+
 static int ensure(mcu_context *ctx, Buffer &b, size_t bytes) {
     if (bytes <= b.cap) return MCU_SUCCESS;
+    // Growing means a synchronize, a free and an allocation: none of that can be recorded into a CUDA graph, and the
+    // graph would keep the old address anyway.
+    if (stream_is_capturing(ctx->stream))
+        return fail(MCU_ERROR_INVALID_OPERATION,
+                    "workspace would have to grow during stream capture: run the same call once before capturing");
     // Kernels already enqueued may still read the old allocation.
     MCU_CUDA(cudaStreamSynchronize(ctx->stream));
     if (b.ptr != nullptr) MCU_CUDA(cudaFree(b.ptr));
@@ -209,6 +223,66 @@ int mcu_context_set_stream(mcu_context_t *ctx, void *cuda_stream) {
 
 void *mcu_context_get_stream(mcu_context_t *ctx) { return ctx != nullptr ? (void *)ctx->stream : nullptr; }
 
+// ---- CUDA-graph capture of a sequence of calls on the context's stream ----
+struct mcu_graph {
+    cudaGraphExec_t exec = nullptr;
+    mcu_context *ctx = nullptr;
+};
+
+int mcu_graph_capture_begin(mcu_context_t *ctx) {
+    if (int rc = check_ctx(ctx)) return rc;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (stream_is_capturing(ctx->stream)) return fail(MCU_ERROR_INVALID_OPERATION, "a capture is already in progress");
+    if (ctx->stream == nullptr || ctx->stream == cudaStreamLegacy || ctx->stream == cudaStreamPerThread)
+        return fail(MCU_ERROR_INVALID_OPERATION,
+                    "the default stream cannot be captured: give the context a stream of its own (mcu_context_set_stream)");
+    MCU_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    return MCU_SUCCESS;
+}
+
+int mcu_graph_capture_end(mcu_context_t *ctx, mcu_graph_t **out) {
+    if (int rc = check_ctx(ctx)) return rc;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (out != nullptr) *out = nullptr;
+    if (!stream_is_capturing(ctx->stream)) return fail(MCU_ERROR_INVALID_OPERATION, "no capture in progress");
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    if (e != cudaSuccess || graph == nullptr) {
+        (void)cudaGetLastError();
+        return fail(MCU_ERROR_INVALID_OPERATION, "stream capture failed: %s", cudaGetErrorString(e));
+    }
+    if (out == nullptr) {  // the caller only wanted to end (discard) the capture
+        cudaGraphDestroy(graph);
+        return MCU_SUCCESS;
+    }
+    mcu_graph *g = new (std::nothrow) mcu_graph();
+    if (g == nullptr) {
+        cudaGraphDestroy(graph);
+        return fail(MCU_ERROR_OUT_OF_MEMORY, "graph handle allocation failed");
+    }
+    e = cudaGraphInstantiate(&g->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) {
+        delete g;
+        return cuda_fail(e, "cudaGraphInstantiate");
+    }
+    g->ctx = ctx;
+    *out = g;
+    return MCU_SUCCESS;
+}
+
+int mcu_graph_launch(mcu_graph_t *graph) {
+    if (graph == nullptr || graph->exec == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "null graph");
+    MCU_CUDA(cudaGraphLaunch(graph->exec, graph->ctx->stream));
+    return MCU_SUCCESS;
+}
+
+void mcu_graph_destroy(mcu_graph_t *graph) {
+    if (graph == nullptr) return;
+    if (graph->exec != nullptr) cudaGraphExecDestroy(graph->exec);
+    delete graph;
+}
+
 int mcu_context_set_regime(mcu_context_t *ctx, int regime) {
     if (ctx == nullptr) return fail(MCU_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
     if (regime < MCU_REGIME_AUTO || regime > MCU_REGIME_GEMV_PLAIN) return fail(MCU_ERROR_INVALID_ARGUMENT, "bad regime");
@@ -218,6 +292,7 @@ int mcu_context_set_regime(mcu_context_t *ctx, int regime) {
 
 int mcu_synchronize(mcu_context_t *ctx) {
     if (int rc = check_ctx(ctx)) return rc;
+    if (stream_is_capturing(ctx->stream)) return fail(MCU_ERROR_INVALID_OPERATION, "cannot synchronize during stream capture");
     MCU_CUDA(cudaStreamSynchronize(ctx->stream));
     return check_device_error(ctx);
 }
@@ -471,6 +546,8 @@ int mcu_vec_dot_host(mcu_context_t *ctx, int weight_kind, const void *weights_ho
         *result_host = 0.0f;  // as cpu_vec_dot
         return MCU_SUCCESS;
     }
+    if (stream_is_capturing(ctx->stream))
+        return fail(MCU_ERROR_INVALID_OPERATION, "mcu_vec_dot_host waits for its result: it cannot be captured");
     const bool kq = weight_kind != MCU_KIND_Q8_0;
     const size_t bv = (size_t)block_values(weight_kind), kp = num_blocks * bv;
     if (kp > ((size_t)1 << 24)) return fail(MCU_ERROR_INVALID_ARGUMENT, "vec_dot: row too long");
@@ -539,6 +616,8 @@ int mcu_linear_host(mcu_context_t *ctx, int kind, const float *x_host, size_t ld
     if (int rc = check_ctx(ctx)) return rc;
     if (int rc = validate_linear(kind, x_host, w_dev, out_host, T, K, F, ldx, ldo)) return rc;
     if (T == 0 || F == 0) return MCU_SUCCESS;
+    if (stream_is_capturing(ctx->stream))
+        return fail(MCU_ERROR_INVALID_OPERATION, "mcu_linear_host waits for its result: it cannot be captured");
     std::lock_guard<std::mutex> lock(ctx->mu);
     // A page-locked result buffer that is mapped into the device's address space is written in place by the decode
     // kernels (a few KB of posted writes over PCIe), which saves the copy-back launch: 226 against 198 GB/s end to end
@@ -604,6 +683,9 @@ static int moe_experts_impl(mcu_context_t *ctx, int gate_kind, int up_kind, int 
     if (k == 0 || k > (size_t)MOE_MAX_TOPK || E == 0 || H == 0 || FF == 0)
         return fail(MCU_ERROR_DIMENSION_MISMATCH, "MoE experts shapes do not match");
     if (T == 0) return MCU_SUCCESS;
+    if (stream_is_capturing(ctx->stream))
+        return fail(MCU_ERROR_INVALID_OPERATION,
+                    "MoE experts read the group sizes back to size the per-expert launches: the call cannot be captured");
     std::lock_guard<std::mutex> lock(ctx->mu);
     const size_t routes = T * k;
     // routing metadata: counts[E+1] | offsets[E+1] | sorted_tok | sorted_w | route_pos

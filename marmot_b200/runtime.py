@@ -34,6 +34,7 @@ EXPORTS = (
     "mcu_kv_pool_get_pointers", "mcu_kv_pool_free_block_count", "mcu_kv_pool_total_block_count", "mcu_kv_pool_seq_len",
     "mcu_kv_pool_block_id", "mcu_kv_pool_block_generation", "mcu_kv_pool_set_block_retained", "mcu_kv_pool_swap_out_seq",
     "mcu_kv_pool_swap_in_seq", "mcu_kv_pool_is_seq_swapped",
+    "mcu_graph_capture_begin", "mcu_graph_capture_end", "mcu_graph_launch", "mcu_graph_destroy",
 )
 
 
@@ -218,6 +219,17 @@ class Context:
                                              F, bp, out_host.ctypes.data, out_host.strides[0] // 4))
         return out_host
 
+    def graph_capture_begin(self) -> None:
+        """Start recording the calls made on this context (they are not run); see graph_capture_end."""
+        self.lib.mcu_graph_capture_begin.argtypes = [C.c_void_p]
+        self._check(self.lib.mcu_graph_capture_begin(self.handle))
+
+    def graph_capture_end(self) -> "Graph":
+        self.lib.mcu_graph_capture_end.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+        h = C.c_void_p()
+        self._check(self.lib.mcu_graph_capture_end(self.handle, C.byref(h)))
+        return Graph(self, h)
+
     def vec_dot_host(self, kind: int, weights: np.ndarray, activations: np.ndarray, num_blocks: int) -> float:
         """One weight row times one pre-quantized activation row (reference block structs as uint8 arrays)."""
         w = np.ascontiguousarray(weights, dtype=np.uint8)
@@ -387,6 +399,24 @@ def _tensor_from_ptr(torch, ptr: int, shape, device_index: int):
     e.__cuda_array_interface__ = {"shape": tuple(int(v) for v in shape), "typestr": "<f4", "data": (int(ptr), False),
                                   "version": 2}
     return torch.as_tensor(e, device=torch.device("cuda", device_index))
+
+
+class Graph:
+    """A recorded sequence of calls (marmot_cuda.h: mcu_graph_*); launch() replays it on the context's stream."""
+
+    def __init__(self, ctx: "Context", handle):
+        self.ctx, self.handle = ctx, handle
+        ctx.lib.mcu_graph_launch.argtypes = [C.c_void_p]
+        ctx.lib.mcu_graph_destroy.argtypes = [C.c_void_p]
+        ctx.lib.mcu_graph_destroy.restype = None
+
+    def launch(self) -> None:
+        self.ctx._check(self.ctx.lib.mcu_graph_launch(self.handle))
+
+    def close(self) -> None:
+        if self.handle:
+            self.ctx.lib.mcu_graph_destroy(self.handle)
+            self.handle = None
 
 
 class _KvPoolOptions(C.Structure):

@@ -162,3 +162,74 @@ def test_paged_attention_full_size_properties(ctx):
     out = ctx.paged_attention(dev(meta), q, k_dom, v_mark, kv_k, kv_v, dev(table), 0, hq, hkv, hd, bs, hd ** -0.5)
     got = out.view(n_seq, hkv, hq // hkv, hd)[:, :, 0, :].reshape(n_seq, hkv * hd)
     assert float((got - v_mark.half().float()).abs().max()) <= 1e-3
+
+
+def test_graph_capture_replays_a_call_sequence(ctx, oracle):
+    """A short chain (RMSNorm -> Q4_K linear -> add -> argmax) recorded once through the C ABI's own capture and replayed
+    on new input contents; the calls that wait for the device refuse to be captured and leave the capture intact."""
+    from marmot_b200.runtime import MarmotCudaError
+
+    rng = np.random.default_rng(21)
+    T, K, F = 3, 1024, 256
+    w = ctx.upload(random_blocks(KIND_Q4_K, F, K, rng))
+    norm_w = dev(rng.normal(1, 0.1, K).astype(np.float32))
+    x = dev(rng.normal(0, 1, (T, K)).astype(np.float32))
+    res = dev(rng.normal(0, 1, (T, F)).astype(np.float32))
+    h, y = torch.empty_like(x), torch.empty((T, F), dtype=torch.float32, device="cuda")
+    pick = torch.empty(T, dtype=torch.int32, device="cuda")
+
+    def chain():
+        ctx.rmsnorm(x, norm_w, 1e-5, out=h)
+        ctx.linear(KIND_Q4_K, h, w, F, out=y)
+        ctx.add(y, res, out=y)
+        ctx.argmax(y, out=pick)
+
+    chain()  # sizes the workspace
+    ctx.synchronize()
+    want_first = y.clone()
+    with pytest.raises(MarmotCudaError, match="default stream"):
+        ctx.graph_capture_begin()  # the fixture's context rides torch's default stream, which cannot be captured
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    ctx.set_stream(stream.cuda_stream)
+    try:
+        with torch.cuda.stream(stream):
+            _capture_and_replay(ctx, chain, rng, x, y, pick, w, want_first, K, F)
+    finally:
+        ctx.set_stream(0)
+
+
+def _capture_and_replay(ctx, chain, rng, x, y, pick, w, want_first, K, F):
+    from marmot_b200.runtime import MarmotCudaError
+
+    ctx.graph_capture_begin()
+    chain()
+    with pytest.raises(MarmotCudaError):
+        ctx.synchronize()  # refused, and the capture goes on
+    with pytest.raises(MarmotCudaError):
+        ctx.linear_host(KIND_Q4_K, np.zeros((1, K), dtype=np.float32), w, F)
+    graph = ctx.graph_capture_end()
+    y.zero_()
+    graph.launch()
+    ctx.synchronize()
+    assert torch.equal(y, want_first)
+    x.copy_(dev(rng.normal(0, 1, tuple(x.shape)).astype(np.float32)))  # new contents, same buffers
+    graph.launch()
+    ctx.synchronize()
+    got, got_pick = y.clone(), pick.clone()
+    chain()
+    ctx.synchronize()
+    assert torch.equal(got, y) and torch.equal(got_pick, pick)
+    graph.close()
+    with pytest.raises(MarmotCudaError):
+        ctx.graph_capture_end()  # nothing in progress
+    # a call that needs more workspace than any before it cannot be captured: it says so instead of breaking the capture
+    big = dev(rng.normal(0, 1, (48, 4096)).astype(np.float32))
+    wb = ctx.upload(random_blocks(KIND_Q4_K, 64, 4096, rng))
+    ctx.graph_capture_begin()
+    with pytest.raises(MarmotCudaError, match="before capturing"):
+        ctx.linear(KIND_Q4_K, big, wb, 64)
+    ctx.lib.mcu_graph_capture_end.argtypes = [__import__("ctypes").c_void_p, __import__("ctypes").c_void_p]
+    assert ctx.lib.mcu_graph_capture_end(ctx.handle, None) == 0  # discard
+    ctx.linear(KIND_Q4_K, big, wb, 64)  # fine outside a capture
+    ctx.synchronize()
