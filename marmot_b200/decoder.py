@@ -59,7 +59,7 @@ class Decoder:
     residual stream, its own slice of the KV pool and finds the global argmax from the ranks' local maxima."""
 
     def __init__(self, ctx: Context, shape: DecoderShape, max_seqs: int, max_ctx: int, block_size: int = 16,
-                 kv_dtype=None, weights: dict | None = None, seed: int = 0, group=None, comm=None):
+                 kv_dtype=None, weights: dict | None = None, seed: int = 0, group=None, comm=None, kv_pool=None):
         import torch
 
         from . import tensor_parallel as tp
@@ -136,15 +136,24 @@ class Decoder:
         self.out_norm = vec("out_norm", s.d)
 
         self.max_blocks = (max_ctx + block_size - 1) // block_size
-        n_blocks = max_seqs * self.max_blocks
-        kv_dtype = kv_dtype or torch.float16
-        pool = (n_blocks, s.layers, s.n_kv_heads, block_size, s.head_dim)
-        self.kv_k = torch.zeros(pool, dtype=kv_dtype, device=dev)
-        self.kv_v = torch.zeros(pool, dtype=kv_dtype, device=dev)
-        # sequence i owns the blocks [i*max_blocks, (i+1)*max_blocks): a static block table (the allocator is the
-        # serving engine's business, not this path's)
-        table = np.arange(n_blocks, dtype=np.uint32).reshape(max_seqs, self.max_blocks)
-        self.block_table = torch.from_numpy(table).to(dev)
+        self.kv_pool = kv_pool
+        if kv_pool is not None:
+            # blocks, block table and kv slots come from a runtime.KvPool (the caller plans appends with it and builds
+            # token_meta from the slots it hands out): what a serving engine with sequences coming and going does
+            self.kv_k, self.kv_v, self.block_table = kv_pool.tensors()
+            want = (s.layers, s.n_kv_heads, block_size, s.head_dim)
+            if tuple(self.kv_k.shape[1:]) != want:
+                raise ValueError(f"KV pool blocks are {tuple(self.kv_k.shape[1:])}, the model needs {want}")
+            self.max_blocks = self.block_table.shape[1]
+        else:
+            n_blocks = max_seqs * self.max_blocks
+            kv_dtype = kv_dtype or torch.float16
+            pool = (n_blocks, s.layers, s.n_kv_heads, block_size, s.head_dim)
+            self.kv_k = torch.zeros(pool, dtype=kv_dtype, device=dev)
+            self.kv_v = torch.zeros(pool, dtype=kv_dtype, device=dev)
+            # sequence i owns the blocks [i*max_blocks, (i+1)*max_blocks): a static block table
+            table = np.arange(n_blocks, dtype=np.uint32).reshape(max_seqs, self.max_blocks)
+            self.block_table = torch.from_numpy(table).to(dev)
         self._bufs = {}
 
     def _buf(self, name, shape, dtype=None):
@@ -153,10 +162,15 @@ class Decoder:
             self._bufs[key] = self.torch.empty(shape, dtype=dtype or self.torch.float32, device=self.dev)
         return self._bufs[key]
 
-    def token_meta(self, seq_slots, positions):
-        """[T, 4] u32 rows {seq_slot, pos, kv_slot, flags} for tokens at `positions` of sequences `seq_slots`."""
+    def token_meta(self, seq_slots, positions, kv_slots=None):
+        """[T, 4] u32 rows {seq_slot, pos, kv_slot, flags} for tokens at `positions` of sequences `seq_slots`; with a
+        KV pool the kv slots are the ones its prepare_append returned."""
         seq = np.asarray(seq_slots, dtype=np.int64)
         pos = np.asarray(positions, dtype=np.int64)
+        if kv_slots is not None:
+            return np.stack([seq, pos, np.asarray(kv_slots, dtype=np.int64), np.zeros_like(seq)], axis=1).astype(np.uint32)
+        if self.kv_pool is not None:
+            raise ValueError("with a KV pool, pass the kv slots that prepare_append returned")
         block = seq * self.max_blocks + pos // self.block_size
         kv_slot = block * self.block_size + pos % self.block_size
         return np.stack([seq, pos, kv_slot, np.zeros_like(seq)], axis=1).astype(np.uint32)

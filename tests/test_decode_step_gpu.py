@@ -67,3 +67,36 @@ def test_prefill_then_greedy_decode(oracle, prompt_len, kv_dtype):
     err_k = float(np.max(np.abs(dec.kv_k.cpu().numpy().astype(np.float32) - ref_k)) / np.max(np.abs(ref_k)))
     assert err_k <= (5e-3 if prompt_len <= 8 else 0.1), err_k
     ctx.close()
+
+
+def test_decode_with_pool_managed_cache_equals_static_cache():
+    """Two sequences prefill and decode in turns; one decoder keeps the static one-range-per-sequence cache, the other
+    takes blocks, table and kv slots from a KvPool in which the two sequences' blocks interleave.  Same logits, bit
+    for bit: only where the K/V rows live differs."""
+    from marmot_b200.runtime import KvPool
+
+    rng = np.random.default_rng(77)
+    weights = make_weights(rng)
+    ctx = Context(0)
+    pool = KvPool(ctx, max_seqs=2, max_seq_len=64, block_size=16, num_blocks=8, num_layers=SHAPE.layers,
+                  num_kv_heads=SHAPE.n_kv_heads, head_dim=SHAPE.head_dim)
+    try:
+        static = Decoder(ctx, SHAPE, max_seqs=2, max_ctx=64, weights=weights)
+        pooled = Decoder(ctx, SHAPE, max_seqs=2, max_ctx=64, weights=weights, kv_pool=pool)
+        seqs = [pool.acquire_seq()[1], pool.acquire_seq()[1]]
+        lengths = [0, 0]
+        for which, n in [(0, 9), (1, 20), (0, 1), (1, 1), (0, 12), (1, 1), (0, 1)]:
+            ids = torch.from_numpy(rng.integers(0, SHAPE.vocab, n).astype(np.int32)).cuda()
+            pos_np = np.arange(lengths[which], lengths[which] + n, dtype=np.int32)
+            pos = torch.from_numpy(pos_np).cuda()
+            rc, plan, slots, start = pool.prepare_append(seqs[which], n)
+            assert rc == 0 and start == lengths[which]
+            want = static.step(ids, torch.from_numpy(static.token_meta([which] * n, pos_np)).cuda(), pos).clone()
+            got = pooled.step(ids, torch.from_numpy(pooled.token_meta([seqs[which]] * n, pos_np, kv_slots=slots)).cuda(), pos)
+            assert torch.equal(got, want), (which, n)
+            assert pool.commit_append(plan) == 0
+            lengths[which] += n
+        assert pool.block_id(seqs[0], 1) != pool.block_id(seqs[0], 0) + 1  # the blocks did interleave
+    finally:
+        pool.close()
+        ctx.close()
