@@ -259,6 +259,37 @@ int mcu_paged_attention(
     size_t block_size, float scale, float *out_dev
 );
 
+/* ---- GGUF model files: the reading half of the reference's loader (src/graph/gguf/loader.cpp) and the uploads of
+ *      a tensor-parallel rank.  The file is memory-mapped and indexed once; payloads go to the device straight out of
+ *      the mapping: whole tensors and row ranges (column-parallel shards) as one copy, a K range of every row
+ *      (row-parallel shards: a run of blocks per row) as one strided 2-D copy into a packed [rows][K shard] matrix.
+ *      GGUF versions 2 and 3; dims[0] is the innermost (K) extent as in the file. ---- */
+typedef struct mcu_gguf mcu_gguf_t;
+typedef struct mcu_gguf_tensor_info {
+    const char *name;      /* owned by the handle */
+    uint32_t ggml_type;    /* 0 F32, 1 F16, 8 Q8_0, 12 Q4_K, 14 Q6_K, ... */
+    int kind;              /* MCU_KIND_* for the three block formats with kernels, else -1 */
+    uint32_t n_dims;
+    uint64_t dims[4];
+    size_t nbytes;         /* 0 when the type's layout is unknown to this library */
+    const void *data;      /* host pointer into the mapping */
+} mcu_gguf_tensor_info_t;
+int mcu_gguf_open(const char *path, mcu_gguf_t **out);
+void mcu_gguf_close(mcu_gguf_t *g);
+size_t mcu_gguf_tensor_count(const mcu_gguf_t *g);
+int mcu_gguf_find_tensor(const mcu_gguf_t *g, const char *name); /* index, or -1 */
+int mcu_gguf_tensor_info(const mcu_gguf_t *g, size_t index, mcu_gguf_tensor_info_t *out);
+/* metadata by key: integers (any width, bool; arrays answer with their length), floats, strings */
+int mcu_gguf_meta_u64(const mcu_gguf_t *g, const char *key, uint64_t *out);
+int mcu_gguf_meta_f64(const mcu_gguf_t *g, const char *key, double *out);
+int mcu_gguf_meta_str(const mcu_gguf_t *g, const char *key, const char **out, size_t *out_len);
+/* rows [row_lo, row_hi) x values [k_lo, k_hi) of tensor `index` -> dst_dev, packed; asynchronous on the context's stream
+ * (the mapping must stay open until the stream has passed the copy) */
+int mcu_gguf_upload(
+    mcu_context_t *ctx, const mcu_gguf_t *g, size_t index, size_t row_lo, size_t row_hi, size_t k_lo, size_t k_hi,
+    void *dst_dev
+);
+
 /* ---- paged KV-cache pool: marmot_kv_pool_* (include/marmot/inference/kv_pool.h:65-101, implementation
  *      src/inference/kv_pool/kv_pool.cpp).  Same bookkeeping, decision for decision (slot and block order, reference
  *      counts and copy on write for shared prefixes, retained blocks, swap with the exchange path, error codes); the K

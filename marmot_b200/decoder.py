@@ -50,7 +50,9 @@ def weight_bytes(shape: DecoderShape) -> int:
 
 
 class Decoder:
-    """Weights are given as host byte arrays of the full model (`weights[name]`, per layer `weights[f"l{i}.{name}"]`;
+    """`device_weights` are this rank's shards already on the device (what gguf.load_llama_decoder uploads), with
+    `kinds[name]` naming each matrix's block format (a Q4_K_M file mixes Q4_K and Q6_K from layer to layer); otherwise
+    weights are given as host byte arrays of the full model (`weights[name]`, per layer `weights[f"l{i}.{name}"]`;
     each rank cuts its own share out of them) or drawn on the device when `weights` is None (timing only).
 
     Tensor parallel over the ranks of `group` (tensor_parallel.Group) with `comm` (runtime.PeerComm): query and KV
@@ -59,7 +61,8 @@ class Decoder:
     residual stream, its own slice of the KV pool and finds the global argmax from the ranks' local maxima."""
 
     def __init__(self, ctx: Context, shape: DecoderShape, max_seqs: int, max_ctx: int, block_size: int = 16,
-                 kv_dtype=None, weights: dict | None = None, seed: int = 0, group=None, comm=None, kv_pool=None):
+                 kv_dtype=None, weights: dict | None = None, seed: int = 0, group=None, comm=None, kv_pool=None,
+                 device_weights: dict | None = None, kinds: dict | None = None):
         import torch
 
         from . import tensor_parallel as tp
@@ -91,6 +94,13 @@ class Decoder:
         gen = torch.Generator(device=dev)
         gen.manual_seed(seed + 1000 * rank)
 
+        default_kinds = {n: k for n, k, _, _ in LAYER_WEIGHTS}
+        default_kinds.update(tok_embd=KIND_Q4_K, output=KIND_Q6_K)
+        self.kinds = {}
+
+        def kind_of(name):
+            return (kinds or {}).get(name, default_kinds[name.split(".")[-1]])
+
         def cut(name, kind, w):
             """This rank's share of a full-model matrix: heads, FFN rows and vocabulary rows are contiguous row ranges;
             the two row-parallel matrices are cut along K (block columns repacked per row)."""
@@ -112,6 +122,9 @@ class Decoder:
             raise KeyError(name)
 
         def mat(name, kind, rows, cols):
+            kind = self.kinds[name] = kind_of(name)
+            if device_weights is not None:
+                return device_weights[name]
             if rows == 0 or cols == 0:
                 return None
             if weights is not None:
@@ -119,6 +132,8 @@ class Decoder:
             return synthetic_blocks_device(torch, kind, rows, cols, dev, gen)
 
         def vec(name, n):
+            if device_weights is not None:
+                return device_weights[name]
             if weights is not None:
                 return torch.from_numpy(np.ascontiguousarray(weights[name], dtype=np.float32)).to(dev)
             return torch.ones(n, dtype=torch.float32, device=dev)
@@ -214,7 +229,8 @@ class Decoder:
         ctx, s = self.ctx, self.local
         T = ids.shape[0]
         hq, hkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
-        x = ctx.embedding_gather(KIND_Q4_K, self.tok_embd, s.d, ids, out=self._buf("x", (T, s.d)))
+        kd = self.kinds
+        x = ctx.embedding_gather(kd["tok_embd"], self.tok_embd, s.d, ids, out=self._buf("x", (T, s.d)))
         h = self._buf("h", (T, s.d))
         q, k, v = self._buf("q", (T, hq * hd)), self._buf("k", (T, hkv * hd)), self._buf("v", (T, hkv * hd))
         att, proj = self._buf("att", (T, hq * hd)), self._buf("proj", (T, s.d))
@@ -223,20 +239,24 @@ class Decoder:
         # the residual add that ends a block and the rms_norm that opens the next one run as one kernel
         ctx.rmsnorm(x, self.layers[0]["attn_norm"], s.rms_eps, out=h)
         for i, lw in enumerate(self.layers):
-            ctx.linear(KIND_Q4_K, h, lw["wq"], hq * hd, out=q)
-            ctx.linear(KIND_Q4_K, h, lw["wk"], hkv * hd, out=k)
-            ctx.linear(KIND_Q6_K, h, lw["wv"], hkv * hd, out=v)
+            ctx.linear(kd[f"l{i}.wq"], h, lw["wq"], hq * hd, out=q)
+            ctx.linear(kd[f"l{i}.wk"], h, lw["wk"], hkv * hd, out=k)
+            ctx.linear(kd[f"l{i}.wv"], h, lw["wv"], hkv * hd, out=v)
             ctx.rope_qk(q, k, positions, hq, hkv, hd, s.rope_theta)
             ctx.paged_attention(meta, q, k, v, self.kv_k, self.kv_v, self.block_table, i, hq, hkv, hd, self.block_size,
                                 scale, out=att)
-            self._row_parallel(KIND_Q4_K, att, lw["wo"], s.d, proj, hq * hd)
+            self._row_parallel(kd[f"l{i}.wo"], att, lw["wo"], s.d, proj, hq * hd)
             ctx.add_rmsnorm(x, proj, lw["ffn_norm"], s.rms_eps, x, h)
             if s.ffn > 0:
-                ctx.linear_dual(KIND_Q4_K, h, lw["gate"], lw["up"], s.ffn, out_a=gate, out_b=up)
+                if kd[f"l{i}.gate"] == kd[f"l{i}.up"]:
+                    ctx.linear_dual(kd[f"l{i}.gate"], h, lw["gate"], lw["up"], s.ffn, out_a=gate, out_b=up)
+                else:
+                    ctx.linear(kd[f"l{i}.gate"], h, lw["gate"], s.ffn, out=gate)
+                    ctx.linear(kd[f"l{i}.up"], h, lw["up"], s.ffn, out=up)
                 ctx.swiglu(gate, up, out=gate)
-            self._row_parallel(KIND_Q6_K, gate, lw["down"], s.d, proj, s.ffn)
+            self._row_parallel(kd[f"l{i}.down"], gate, lw["down"], s.d, proj, s.ffn)
             nxt = self.layers[i + 1]["attn_norm"] if i + 1 < len(self.layers) else self.out_norm
             ctx.add_rmsnorm(x, proj, nxt, s.rms_eps, x, h)
         logits = logits_out if logits_out is not None else self._buf("logits", (T, self.local_vocab))
-        ctx.linear(KIND_Q6_K, h, self.output, self.local_vocab, out=logits)
+        ctx.linear(kd["output"], h, self.output, self.local_vocab, out=logits)
         return logits

@@ -35,6 +35,8 @@ EXPORTS = (
     "mcu_kv_pool_block_id", "mcu_kv_pool_block_generation", "mcu_kv_pool_set_block_retained", "mcu_kv_pool_swap_out_seq",
     "mcu_kv_pool_swap_in_seq", "mcu_kv_pool_is_seq_swapped",
     "mcu_graph_capture_begin", "mcu_graph_capture_end", "mcu_graph_launch", "mcu_graph_destroy",
+    "mcu_gguf_open", "mcu_gguf_close", "mcu_gguf_tensor_count", "mcu_gguf_find_tensor", "mcu_gguf_tensor_info",
+    "mcu_gguf_meta_u64", "mcu_gguf_meta_f64", "mcu_gguf_meta_str", "mcu_gguf_upload",
 )
 
 

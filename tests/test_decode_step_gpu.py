@@ -100,3 +100,45 @@ def test_decode_with_pool_managed_cache_equals_static_cache():
     finally:
         pool.close()
         ctx.close()
+
+
+@pytest.mark.parametrize("tie_output", [False, True])
+def test_decoder_loaded_from_gguf_equals_direct_weights(tmp_path, tie_output):
+    """A synthetic Llama-family GGUF file (Q4_K_M-like mix: attn_v and ffn_down alternate between Q6_K and Q4_K by
+    layer) loaded through the library's reader gives the very logits of the same weights handed over as arrays."""
+    from marmot_b200.gguf import load_llama_decoder
+    from tests.gguf_writer import write_llama
+
+    rng = np.random.default_rng(5)
+    kinds = {"l1.wv": KIND_Q4_K, "l1.down": KIND_Q4_K, "l0.wq": KIND_Q6_K}
+    if tie_output:
+        kinds["output"] = KIND_Q4_K  # the embedding table doubles as the output projection
+    weights = make_weights(rng)
+    for name, kind in kinds.items():
+        if name == "output":
+            continue
+        _, _, rows, cols = next(w for w in LAYER_WEIGHTS if w[0] == name.split(".")[1])
+        weights[name] = random_blocks(kind, rows(SHAPE), cols(SHAPE), rng, d_sigma=0.0003)
+    if tie_output:
+        weights["output"] = weights["tok_embd"]
+    path = tmp_path / "llama.gguf"
+    write_llama(path, SHAPE, weights, kinds, tie_output=tie_output)
+    ctx = Context(0)
+    try:
+        direct = Decoder(ctx, SHAPE, max_seqs=2, max_ctx=64, weights=weights, kinds=kinds)
+        loaded = load_llama_decoder(str(path), ctx, max_seqs=2, max_ctx=64)
+        import dataclasses
+
+        got_shape, want_shape = dataclasses.asdict(loaded.shape), dataclasses.asdict(SHAPE)
+        for key in ("rope_theta", "rms_eps"):  # stored as f32 in the file
+            assert np.float32(got_shape.pop(key)) == np.float32(want_shape.pop(key))
+        assert got_shape == want_shape
+        assert loaded.kinds["l1.wv"] == KIND_Q4_K and loaded.kinds["l0.wv"] == KIND_Q6_K
+        for n, start in ((7, 0), (1, 7), (12, 8)):
+            ids = torch.from_numpy(rng.integers(0, SHAPE.vocab, n).astype(np.int32)).cuda()
+            pos_np = np.arange(start, start + n, dtype=np.int32)
+            meta = torch.from_numpy(direct.token_meta([1] * n, pos_np)).cuda()
+            pos = torch.from_numpy(pos_np).cuda()
+            assert torch.equal(loaded.step(ids, meta, pos), direct.step(ids, meta, pos))
+    finally:
+        ctx.close()

@@ -127,6 +127,26 @@ def main() -> int:
             ids = pick[-1:].clone()
             pos_np = pos_np[-1:] + 1
 
+    # the same model from a GGUF file: every rank uploads only its share (row ranges, and K ranges as strided copies)
+    if shape.n_kv_heads % world == 0:
+        import tempfile
+
+        from marmot_b200.gguf import load_llama_decoder
+        from tests.gguf_writer import write_llama
+
+        with tempfile.TemporaryDirectory() as d:
+            path = os.path.join(d, f"rank{rank}.gguf")
+            write_llama(path, shape, weights)
+            from_file = load_llama_decoder(path, ctx, max_seqs=2, max_ctx=64, group=group, comm=comm)
+        ids = torch.from_numpy(wrng.integers(0, shape.vocab, 6).astype(np.int32)).to(dev)
+        pos_np = np.arange(6, dtype=np.int32)
+        pos = torch.from_numpy(pos_np).to(dev)
+        meta = torch.from_numpy(one.token_meta([0] * 6, pos_np)).to(dev)
+        want = many.step(ids, meta, pos).clone()  # shards cut on the host from the same weights
+        got = from_file.step(ids, meta, pos)
+        ctx.synchronize()
+        check("decoder_from_gguf", torch.equal(got, want))
+
     # a peer that never arrives: the bounded wait gives up and the error reaches the host; nothing hangs
     dist.barrier()
     torch.cuda.synchronize()
