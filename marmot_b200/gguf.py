@@ -136,10 +136,12 @@ def load_llama_decoder(path: str, ctx, max_seqs: int, max_ctx: int, block_size: 
         n_heads = f.meta_int(f"{arch}.attention.head_count")
         d = f.meta_int(f"{arch}.embedding_length")
         emb = f.info(f.find("token_embd.weight"))
+        q0 = f.find("blk.0.attn_q.weight")  # without an explicit key length the query projection tells the head size
+        hd_default = int(f.info(q0)["dims"][1]) // n_heads if q0 >= 0 else d // n_heads
         shape = DecoderShape(
             layers=f.meta_int(f"{arch}.block_count"), d=d, ffn=f.meta_int(f"{arch}.feed_forward_length"),
             n_heads=n_heads, n_kv_heads=f.meta_int(f"{arch}.attention.head_count_kv", n_heads),
-            head_dim=f.meta_int(f"{arch}.attention.key_length", d // n_heads), vocab=int(emb["dims"][1]),
+            head_dim=f.meta_int(f"{arch}.attention.key_length", hd_default), vocab=int(emb["dims"][1]),
             rope_theta=f.meta_float(f"{arch}.rope.freq_base", 10000.0),
             rms_eps=f.meta_float(f"{arch}.attention.layer_norm_rms_epsilon", 1e-5))
         hd = shape.head_dim
