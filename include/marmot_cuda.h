@@ -198,7 +198,11 @@ int mcu_topk(
 /* ---- MoE expert FFN: cpu_moe_experts_impl -> cpu_moe_execute_grouped / cpu_moe_execute_decode
  *      (src/backends/cpu/ops/moe/moe_ops.c:1069-1178, 891-1049, 622-787).
  *      hidden [T][H] f32; gate/up: E contiguous [FF][H] quantized matrices; down: E contiguous [H][FF];
- *      topk_ids [T][k] int32, topk_weights [T][k] f32; out [T][H] f32. ---- */
+ *      topk_ids [T][k] int32, topk_weights [T][k] f32; out [T][H] f32.
+ *      With T * k >= 256 (gate and up of one kind, weight rows a multiple of 16 bytes) the call reads nothing back: it is
+ *      asynchronous, may be recorded by mcu_graph_capture_begin/end, and an expert id outside [0, E) is reported by the
+ *      next mcu_synchronize as MCU_ERROR_INVALID_ARGUMENT.  Smaller batches read the group sizes back (one stream
+ *      synchronisation), report a bad id from the call itself and refuse to be captured. ---- */
 int mcu_moe_experts(
     mcu_context_t *ctx, int gate_kind, int up_kind, int down_kind, const float *hidden_dev, size_t T, size_t H,
     size_t FF, size_t E, const void *gate_dev, const void *up_dev, const void *down_dev, const int32_t *topk_ids_dev,

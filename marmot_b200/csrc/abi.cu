@@ -107,6 +107,7 @@ static int check_device_error(mcu_context *ctx) {
     MCU_CUDA(cudaMemcpy(&flag, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
     if (flag != 0) {
         cudaMemset(ctx->dev_err, 0, sizeof(int));
+        if (flag == 40) return fail(MCU_ERROR_INVALID_ARGUMENT, "MoE expert id is out of range (found by an earlier call)");
         return fail(MCU_ERROR_INVALID_OPERATION, "a device-side wait timed out (code %d)", flag);
     }
     return MCU_SUCCESS;
@@ -683,9 +684,6 @@ static int moe_experts_impl(mcu_context_t *ctx, int gate_kind, int up_kind, int 
     if (k == 0 || k > (size_t)MOE_MAX_TOPK || E == 0 || H == 0 || FF == 0)
         return fail(MCU_ERROR_DIMENSION_MISMATCH, "MoE experts shapes do not match");
     if (T == 0) return MCU_SUCCESS;
-    if (stream_is_capturing(ctx->stream))
-        return fail(MCU_ERROR_INVALID_OPERATION,
-                    "MoE experts read the group sizes back to size the per-expert launches: the call cannot be captured");
     std::lock_guard<std::mutex> lock(ctx->mu);
     const size_t routes = T * k;
     // routing metadata: counts[E+1] | offsets[E+1] | sorted_tok | sorted_w | route_pos
@@ -707,6 +705,43 @@ static int moe_experts_impl(mcu_context_t *ctx, int gate_kind, int up_kind, int 
     count_launches(3);
     float *route_hidden = (float *)ctx->moe_hidden.ptr, *gate_out = (float *)ctx->moe_gate.ptr;
     float *up_out = (float *)ctx->moe_up.ptr, *route_down = (float *)ctx->moe_down.ptr;
+    // Large batches: one grouped launch per projection over all local experts, sized from the device-resident counts.
+    // Nothing is read back, so the call neither waits for the device nor breaks a stream capture.
+    static const bool no_grouped = getenv("MARMOT_CUDA_MOE_NO_GROUPED") != nullptr;  // diagnostic switch
+    const bool grouped = !no_grouped && routes >= 256 && gate_kind == up_kind &&
+        gemm_tma_grouped_supported(gate_kind, gate_dev, (int)H, (int)FF) &&
+        gemm_tma_grouped_supported(up_kind, up_dev, (int)H, (int)FF) &&
+        gemm_tma_grouped_supported(down_kind, down_dev, (int)FF, (int)H) &&
+        act_half_fused_smem(gate_kind, (int)H) <= 48 * 1024 && act_half_fused_smem(down_kind, (int)FF) <= 48 * 1024 &&
+        routes < ((size_t)1 << 24);
+    if (grouped) {
+        const size_t kp_h = (H + block_values(gate_kind) - 1) / block_values(gate_kind) * block_values(gate_kind);
+        const size_t kp_f = (FF + block_values(down_kind) - 1) / block_values(down_kind) * block_values(down_kind);
+        const size_t kp_max = kp_h > kp_f ? kp_h : kp_f;
+        if (int rc = ensure(ctx, ctx->act_half, routes * kp_max * sizeof(__half))) return rc;
+        if (int rc = ensure(ctx, ctx->act_rowscale, routes * sizeof(float))) return rc;
+        __half *xh = (__half *)ctx->act_half.ptr;
+        float *rowscale = (float *)ctx->act_rowscale.ptr;
+        const int *cnt = rb.counts + e_begin, *off = rb.offsets + e_begin;
+        // every route is gathered and staged (rows of other ranks' experts are never multiplied nor combined)
+        MCU_CUDA(launch_moe_gather(hidden_dev, H, rb.sorted_tok, 0, (int)routes, (int)H, route_hidden, s));
+        MCU_CUDA(launch_act_half_fused(gate_kind, route_hidden, (int)H, (int)routes, (int)H, ACT_ORDER_QUAD, xh, rowscale, s));
+        MCU_CUDA(launch_gemm_tma_grouped(gate_kind, gate_dev, (int)e_count, xh, rowscale, (int)kp_h, (int)routes, (int)H,
+                                         (int)FF, cnt, off, gate_out, (int)FF, ctx->dev_err, s));
+        MCU_CUDA(launch_gemm_tma_grouped(up_kind, up_dev, (int)e_count, xh, rowscale, (int)kp_h, (int)routes, (int)H, (int)FF,
+                                         cnt, off, up_out, (int)FF, ctx->dev_err, s));
+        MCU_CUDA(launch_moe_glu(gate_out, up_out, routes * FF, ffn_type == MCU_FFN_GEGLU, s));
+        MCU_CUDA(launch_act_half_fused(down_kind, gate_out, (int)FF, (int)routes, (int)FF, ACT_ORDER_QUAD, xh, rowscale, s));
+        MCU_CUDA(launch_gemm_tma_grouped(down_kind, down_dev, (int)e_count, xh, rowscale, (int)kp_f, (int)routes, (int)FF,
+                                         (int)H, cnt, off, route_down, (int)H, ctx->dev_err, s));
+        MCU_CUDA(launch_moe_combine_dev(route_down, rb.sorted_w, rb.route_pos, (int)T, (int)k, (int)H, rb.offsets,
+                                        (int)e_begin, (int)(e_begin + e_count), rb.counts + E, ctx->dev_err, out_dev, H, s));
+        count_launches(8);
+        return MCU_SUCCESS;
+    }
+    if (stream_is_capturing(s))
+        return fail(MCU_ERROR_INVALID_OPERATION,
+                    "this MoE shape reads the group sizes back to size the per-expert launches: the call cannot be captured");
     // The per-expert launches need the group sizes on the host.
     ctx->host_counts.resize(2 * (E + 1));
     MCU_CUDA(cudaMemcpyAsync(ctx->host_counts.data(), rb.counts, 2 * (E + 1) * sizeof(int), cudaMemcpyDeviceToHost, s));

@@ -83,6 +83,10 @@ struct GemmTmaParams {
     float *partial;
     int *counters;
     PeerFuse fuse;  // world > 0: finished tiles go to all ranks' slots and are summed there (see kernels.h)
+    // Grouped launch (MoE experts): blockIdx.z is the group; it owns group_counts[z] activation rows starting at row
+    // group_offsets[z] of xh / rowscale / out, and the weight rows [z * F, (z + 1) * F) of the stacked matrix.  The
+    // counts live in device memory (no host read-back); token tiles beyond a group's count exit at once.
+    const int *group_counts, *group_offsets;
 #ifdef MCU_TRACE
     long long *trace;  // development aid: clock64 samples of CTA 0, [agent][step][point]
 #endif
@@ -252,8 +256,15 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     if (threadIdx.x == 0) MCU_TRACE_POINT(3, 32, 0);
     const int f0 = blockIdx.x * p.rows_per_cta, t0 = blockIdx.y * BN;
     const int rows_here = min(p.rows_per_cta, p.F - f0);
+    const bool grouped = p.group_counts != nullptr;
+    // The group tables were written by kernels that finished before the kernel ahead of this one started (they do
+    // not trigger their dependents early), so they may be read before griddepcontrol.wait.
+    const int T_here = grouped ? p.group_counts[blockIdx.z] : p.T;
+    const int row_off = grouped ? p.group_offsets[blockIdx.z] : 0;  // first activation / output row of the group
+    const int w_row0 = (grouped ? (int)blockIdx.z * p.F : 0) + f0;  // first weight row in the (stacked) matrix
+    if (t0 >= T_here) return;  // uniform over the CTA, before any barrier or tensor memory exists
     // this CTA's share of K: slabs [j0, j1), K steps [ks0, ks0 + nsteps)
-    const int j0 = (int)blockIdx.z * p.slabs_per_split;
+    const int j0 = grouped ? 0 : (int)blockIdx.z * p.slabs_per_split;
     const int j1 = min((p.ksteps + RC::KR - 1) / RC::KR, j0 + p.slabs_per_split);
     const int ks0 = j0 * RC::KR;
     const int nsteps = min(p.ksteps, j1 * RC::KR) - ks0;
@@ -305,7 +316,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     ok = tm_mbar_wait_relaxed((((use - 1) & 1u) ? st_empty_odd : st_empty) + 8u * st, ((use - 1) >> 1) & 1u);
                 if (!ok) break;
                 tm_mbar_expect_tx(a_full + 8u * st, (uint32_t)B_BYTES);
-                tm_tma_load_2d(tile_base + (uint32_t)st * STAGE_BYTES + A_BYTES, &map_x, (ks0 + ks) * TM_BK, t0, a_full + 8u * st);
+                tm_tma_load_2d(tile_base + (uint32_t)st * STAGE_BYTES + A_BYTES, &map_x, (ks0 + ks) * TM_BK, row_off + t0, a_full + 8u * st);
                 MCU_TRACE_POINT(2, ks, 1);
                 if (++st == S) {
                     st = 0;
@@ -331,7 +342,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 if (j - j0 >= R) ok = tm_mbar_wait_relaxed(raw_empty + 8u * rs, phase);
                 if (!ok) break;
                 tm_mbar_expect_tx(raw_full + 8u * rs, raw_bytes);
-                tm_tma_load_2d(raw_ring_addr + (uint32_t)rs * RAW_STAGE_BYTES, &map_w, (j * RC::UNIT) & ~15, f0,
+                tm_tma_load_2d(raw_ring_addr + (uint32_t)rs * RAW_STAGE_BYTES, &map_w, (j * RC::UNIT) & ~15, w_row0,
                                raw_full + 8u * rs);
                 MCU_TRACE_POINT(3, j - j0, 1);
                 if (++rs == R) {
@@ -526,7 +537,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             const bool f_ok = fr < rows_here;
             const float bias = (p.bias != nullptr && f_ok) ? p.bias[f] : 0.0f;
             for (int cb = 0; cb < BN / 2; cb += 32) {
-                if (t0 + col0 + cb >= p.T) break;  // warp-uniform: no tokens left in this column block
+                if (t0 + col0 + cb >= T_here) break;  // warp-uniform: no tokens left in this column block
                 float sum[32];
 #pragma unroll
                 for (int jj = 0; jj < 32; ++jj) sum[jj] = 0.0f;
@@ -564,7 +575,8 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                         for (int jj = 0; jj < 32; ++jj) {
                             const int t = t0 + col0 + cb + jj;
-                            if (t < p.T) p.out[(size_t)t * p.ldo + f] = sum[jj] * p.rowscale[t] + bias;
+                            if (t < T_here)
+                                p.out[(size_t)(row_off + t) * p.ldo + f] = sum[jj] * p.rowscale[row_off + t] + bias;
                         }
                     } else {
                         float *part = p.partial + (size_t)blockIdx.z * p.T * p.F;
@@ -803,13 +815,13 @@ bool gemm_tma_supported(int kind, const void *W, const void *W2, int T, int K, i
 
 template <int KIND, int BN, int G, int RT = 1>
 static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, GemmTmaParams p, long row_bytes,
-                                 cudaStream_t s) {
+                                 cudaStream_t s, int groups = 0, int total_rows = 0) {
     using RC = RawCfg<KIND>;
     EncodeTiledFn enc = encode_tiled_fn();
     if (enc == nullptr) return cudaErrorNotSupported;
     alignas(64) CUtensorMap map_w, map_x;
     {
-        const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)p.F};
+        const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)p.F * (cuuint64_t)(groups > 0 ? groups : 1)};
         const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
         const cuuint32_t box[2] = {(cuuint32_t)RC::BOX_W, (cuuint32_t)p.rows_per_cta};
         const cuuint32_t es[2] = {1, 1};
@@ -819,7 +831,7 @@ static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, Gemm
             return cudaErrorInvalidValue;
     }
     {
-        const cuuint64_t dims[2] = {(cuuint64_t)ldxh, (cuuint64_t)p.T};
+        const cuuint64_t dims[2] = {(cuuint64_t)ldxh, (cuuint64_t)(groups > 0 ? total_rows : p.T)};
         const cuuint64_t strides[1] = {(cuuint64_t)ldxh * 2};
         const cuuint32_t box[2] = {(cuuint32_t)TM_BK, (cuuint32_t)BN};
         const cuuint32_t es[2] = {1, 1};
@@ -871,6 +883,7 @@ static cudaError_t launch_tma_bn(const void *W, const __half *xh, int ldxh, Gemm
         configured = smem;
     }
     dim3 grid((unsigned)((p.F + p.rows_per_cta - 1) / p.rows_per_cta), (unsigned)((p.T + BN - 1) / BN), (unsigned)p.splits);
+    if (groups > 0) grid = dim3(grid.x, (unsigned)((total_rows + BN - 1) / BN), (unsigned)groups);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(TM_THREADS, 1, 1);
@@ -916,6 +929,7 @@ cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __hal
     const long row_bytes = (long)p.nb * block_bytes(kind);
     TmaPlan pl = plan_tma(kind, T, K, F);
     memset(&p.fuse, 0, sizeof(p.fuse));
+    p.group_counts = p.group_offsets = nullptr;
     if (fuse != nullptr && fuse->world > 0) {
         if (!gemm_tma_can_fuse(kind, T, F) || W2 != nullptr || ldo != F || (size_t)T * F > fuse->slot_floats)
             return cudaErrorInvalidValue;
@@ -951,6 +965,46 @@ cudaError_t launch_gemm_tma(int kind, const void *W, const void *W2, const __hal
     }
     if (launches != nullptr) *launches = n;
     return cudaSuccess;
+}
+
+bool gemm_tma_grouped_supported(int kind, const void *W, int K, int F) {
+    return gemm_tma_supported(kind, W, nullptr, 256, K, F);
+}
+
+// n_groups matmuls in one launch: group g multiplies its group_counts[g] rows of xh (from row group_offsets[g]) with the
+// weight rows [g * F, (g + 1) * F) of the stacked matrix W.  The 256-token tile configuration is used whatever the
+// counts turn out to be (they are device data): meant for batches with many rows per group.
+cudaError_t launch_gemm_tma_grouped(int kind, const void *W, int n_groups, const __half *xh, const float *rowscale,
+                                    int ldxh, int total_rows, int K, int F, const int *group_counts,
+                                    const int *group_offsets, float *out, int ldo, int *err_flag, cudaStream_t s) {
+    if (n_groups <= 0 || total_rows <= 0) return cudaSuccess;
+    if (n_groups > 65535 || (total_rows + 255) / 256 > 65535) return cudaErrorInvalidValue;
+    GemmTmaParams p;
+    memset(&p, 0, sizeof(p));
+    p.rowscale = rowscale;
+    p.out = out;
+    p.err = err_flag;
+    p.ldo = ldo;
+    p.T = total_rows;
+    p.F = F;
+    const int bv = block_values(kind);
+    p.nb = (K + bv - 1) / bv;
+    p.ksteps = (p.nb * bv + TM_BK - 1) / TM_BK;
+    const long row_bytes = (long)p.nb * block_bytes(kind);
+    p.splits = 1;
+    p.slabs_per_split = (p.ksteps + (kind == KIND_Q8_0 ? 2 : 4) - 1) / (kind == KIND_Q8_0 ? 2 : 4);
+    p.group_counts = group_counts;
+    p.group_offsets = group_offsets;
+    static const bool one_tile = getenv("MARMOT_CUDA_GEMM_ONE_ROW_TILE") != nullptr;  // diagnostic switch
+    const bool two = kind != KIND_Q6_K && !one_tile && F % (2 * TM_BM) == 0;
+    p.rows_per_cta = two ? 2 * TM_BM : TM_BM;
+    if (kind == KIND_Q4_K)
+        return two ? launch_tma_bn<KIND_Q4_K, 256, 1, 2>(W, xh, ldxh, p, row_bytes, s, n_groups, total_rows)
+                   : launch_tma_bn<KIND_Q4_K, 256, 2>(W, xh, ldxh, p, row_bytes, s, n_groups, total_rows);
+    if (kind == KIND_Q8_0)
+        return two ? launch_tma_bn<KIND_Q8_0, 256, 1, 2>(W, xh, ldxh, p, row_bytes, s, n_groups, total_rows)
+                   : launch_tma_bn<KIND_Q8_0, 256, 2>(W, xh, ldxh, p, row_bytes, s, n_groups, total_rows);
+    return launch_tma_bn<KIND_Q6_K, 256, 2>(W, xh, ldxh, p, row_bytes, s, n_groups, total_rows);
 }
 
 }  // namespace mcu

@@ -95,6 +95,12 @@ size_t gemm_warp_workspace_bytes(int kind, int T, int K, int F, bool dual);
 cudaError_t launch_gemm_warp(int kind, const void *W, const void *W2, const __half *xh, const float *rowscale, int ldxh,
                              int T, int K, int F, const float *bias, float *out, float *out2, int ldo, float *partial,
                              int *counters, int *err_flag, cudaStream_t s);
+// Grouped form (MoE experts): one launch for n_groups matmuls over a stacked weight matrix [n_groups * F, K]; group g
+// owns group_counts[g] rows of xh / rowscale / out starting at row group_offsets[g] (device arrays: no host read-back).
+bool gemm_tma_grouped_supported(int kind, const void *W, int K, int F);
+cudaError_t launch_gemm_tma_grouped(int kind, const void *W, int n_groups, const __half *xh, const float *rowscale,
+                                    int ldxh, int total_rows, int K, int F, const int *group_counts,
+                                    const int *group_offsets, float *out, int ldo, int *err_flag, cudaStream_t s);
 // Can launch_gemm_tma fuse the all-reduce for this shape (same answer on every rank: it depends on T and F only)?
 bool gemm_tma_can_fuse(int kind, int T, int F);
 

@@ -149,6 +149,49 @@ __global__ void moe_combine_kernel(const float *__restrict__ route_down, const f
     }
 }
 
+// The same with the local range of sorted positions taken from the device-resident offsets (experts
+// [e_begin, e_end)): no host read-back.  Block 0 also reports an out-of-range expert id through the error flag.
+template <int MAXK>
+__global__ void moe_combine_dev_kernel(const float *__restrict__ route_down, const float *__restrict__ sorted_w,
+                                       const int32_t *__restrict__ route_pos, int k, int H,
+                                       const int *__restrict__ offsets, int e_begin, int e_end,
+                                       const int *__restrict__ bad_id_count, int *err, float *__restrict__ out, size_t ldo) {
+    const int t = blockIdx.x;
+    const int pos_lo = offsets[e_begin], pos_hi = offsets[e_end];
+    if (t == 0 && threadIdx.x == 0 && *bad_id_count != 0) atomicExch(err, 40);
+    int pos[MAXK];
+    float w[MAXK];
+    for (int j = 0; j < k; ++j) pos[j] = route_pos[(size_t)t * k + j];
+    for (int i = 1; i < k; ++i) {
+        const int p = pos[i];
+        int j = i;
+        while (j > 0 && pos[j - 1] > p) {
+            pos[j] = pos[j - 1];
+            --j;
+        }
+        pos[j] = p;
+    }
+    for (int j = 0; j < k; ++j) w[j] = sorted_w[pos[j]];
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < k; ++j) {
+            if (pos[j] < pos_lo || pos[j] >= pos_hi) continue;
+            acc = __fadd_rn(acc, __fmul_rn(w[j], route_down[(size_t)pos[j] * H + c]));
+        }
+        out[(size_t)t * ldo + c] = acc;
+    }
+}
+
+cudaError_t launch_moe_combine_dev(const float *route_down, const float *sorted_w, const int32_t *route_pos, int T, int k,
+                                   int H, const int *offsets, int e_begin, int e_end, const int *bad_id_count, int *err,
+                                   float *out, size_t ldo, cudaStream_t s) {
+    if (T <= 0) return cudaSuccess;
+    if (k > MOE_MAX_TOPK) return cudaErrorInvalidValue;
+    moe_combine_dev_kernel<MOE_MAX_TOPK><<<T, 256, 0, s>>>(route_down, sorted_w, route_pos, k, H, offsets, e_begin, e_end,
+                                                            bad_id_count, err, out, ldo);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_topk(const float *x, int rows, int cols, size_t ldx, int k, float *values, int32_t *indices,
                         cudaStream_t s) {
     if (rows <= 0) return cudaSuccess;

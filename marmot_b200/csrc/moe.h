@@ -29,4 +29,10 @@ cudaError_t launch_moe_glu(float *gate, const float *up, size_t n, int geglu, cu
 cudaError_t launch_moe_combine(const float *route_down, const float *sorted_w, const int32_t *route_pos, int T, int k,
                                int H, int pos_lo, int pos_hi, float *out, size_t ldo, cudaStream_t s);
 
+// combine with the local range given as experts [e_begin, e_end) and looked up in the device-resident offsets;
+// *bad_id_count != 0 (an expert id out of range was seen while counting) sets *err to 40
+cudaError_t launch_moe_combine_dev(const float *route_down, const float *sorted_w, const int32_t *route_pos, int T, int k,
+                                   int H, const int *offsets, int e_begin, int e_end, const int *bad_id_count, int *err,
+                                   float *out, size_t ldo, cudaStream_t s);
+
 }  // namespace mcu

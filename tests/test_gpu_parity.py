@@ -381,6 +381,93 @@ def test_moe_experts_vs_oracle(ctx, oracle, T, k, policy, scale):
     assert max_rel_err(got, ref) <= TOL_MOE and cosine(got, ref) >= 0.999
 
 
+@pytest.mark.parametrize("kinds", [(KIND_Q4_K, KIND_Q4_K, KIND_Q6_K), (KIND_Q8_0, KIND_Q8_0, KIND_Q4_K)])
+def test_moe_grouped_path_vs_oracle(ctx, oracle, kinds):
+    """256 routes or more take the grouped launches (one per projection over all experts, sized from the device-resident
+    counts, nothing read back): against the oracle, against the per-expert path's tolerance, for an expert nobody
+    selects, for a local expert range, and recorded into a CUDA graph."""
+    H, FF, E, T, k = 256, 2048, 5, 150, 2  # Q6_K rows of 2048 values are a multiple of 16 bytes, as the tensor map needs
+    rng = np.random.default_rng(12)
+    hid, gate, up, down, p = _moe_case(rng, T, H, FF, E, k, kinds)
+    p[:, 3] = 0.0  # expert 3 receives no route
+    vals, ids = oracle.topk(p, k)
+    ref = oracle.moe_experts(kinds, hid, gate, up, down, ids, vals, FF, E)
+    gd, ud, dd = ctx.upload(gate), ctx.upload(up), ctx.upload(down)
+    hd_, idd, vd = dev(ctx, hid), dev(ctx, ids), dev(ctx, vals)
+    launches = ctx.launch_count()
+    got = ctx.moe_experts(kinds, hd_, gd, ud, dd, idd, vd, FF, E)
+    assert ctx.launch_count() - launches == 3 + 8  # route (3 kernels) + the grouped sequence, whatever the expert count
+    ctx.synchronize()
+    got = got.cpu().numpy()
+    assert max_rel_err(got, ref) <= TOL_MOE and cosine(got, ref) >= 0.999
+    # experts [1, 4) only: the other experts' routes contribute nothing
+    sl = lambda w, rows, K, kind: w.reshape(E, -1)[1:4].reshape(-1)
+    part = ctx.moe_experts_local(kinds, hd_, ctx.upload(sl(gate, FF, H, kinds[0])), ctx.upload(sl(up, FF, H, kinds[1])),
+                                 ctx.upload(sl(down, H, FF, kinds[2])), idd, vd, FF, E, 1, 3)
+    rest = ctx.moe_experts_local(kinds, hd_, ctx.upload(gate.reshape(E, -1)[0:1].reshape(-1)),
+                                 ctx.upload(up.reshape(E, -1)[0:1].reshape(-1)),
+                                 ctx.upload(down.reshape(E, -1)[0:1].reshape(-1)), idd, vd, FF, E, 0, 1)
+    last = ctx.moe_experts_local(kinds, hd_, ctx.upload(gate.reshape(E, -1)[4:5].reshape(-1)),
+                                 ctx.upload(up.reshape(E, -1)[4:5].reshape(-1)),
+                                 ctx.upload(down.reshape(E, -1)[4:5].reshape(-1)), idd, vd, FF, E, 4, 1)
+    ctx.synchronize()
+    total = (part + rest + last).cpu().numpy()
+    assert max_rel_err(total, got) <= 1e-5  # the same products, summed per rank first
+    # an out-of-range expert id is found on the device and reported at the next synchronize
+    from marmot_b200 import MarmotCudaError
+
+    bad = ids.copy()
+    bad[7, 1] = E + 2
+    ctx.moe_experts(kinds, hd_, gd, ud, dd, dev(ctx, bad), vd, FF, E)
+    with pytest.raises(MarmotCudaError) as e:
+        ctx.synchronize()
+    assert e.value.code == -1
+    ctx.synchronize()  # reported once
+
+
+def test_moe_grouped_path_records_into_a_graph(ctx):
+    """With 256 routes or more nothing is read back, so the whole expert block can be captured once and replayed on new
+    token contents and new routing; a small batch says that it cannot be captured and leaves the capture usable."""
+    import torch
+
+    from marmot_b200 import MarmotCudaError
+
+    H, FF, E, T, k = 256, 512, 4, 160, 2
+    kinds = (KIND_Q4_K, KIND_Q4_K, KIND_Q8_0)
+    rng = np.random.default_rng(31)
+    hid, gate, up, down, p = _moe_case(rng, T, H, FF, E, k, kinds)
+    gd, ud, dd = ctx.upload(gate), ctx.upload(up), ctx.upload(down)
+    hd_ = dev(ctx, hid)
+    order = np.argsort(-p, axis=1)[:, :k].astype(np.int32)
+    idd, vd = dev(ctx, order), dev(ctx, np.take_along_axis(p, order, 1))
+    out = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    run = lambda: ctx.moe_experts_local(kinds, hd_, gd, ud, dd, idd, vd, FF, E, 0, E, out=out)
+    run()  # sizes the workspace
+    ctx.synchronize()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    ctx.set_stream(stream.cuda_stream)
+    try:
+        with torch.cuda.stream(stream):
+            ctx.graph_capture_begin()
+            run()
+            with pytest.raises(MarmotCudaError, match="cannot be captured"):
+                ctx.moe_experts_local(kinds, hd_[:8], gd, ud, dd, idd[:8], vd[:8], FF, E, 0, E, out=out[:8])
+            graph = ctx.graph_capture_end()
+            hd_.copy_(dev(ctx, rng.normal(0, 1, (T, H)).astype(np.float32)))
+            idd.copy_(dev(ctx, ((order + 1) % E).astype(np.int32)))
+            out.zero_()
+            graph.launch()
+            ctx.synchronize()
+            replayed = out.clone()
+            run()
+            ctx.synchronize()
+            assert torch.equal(replayed, out)
+            graph.close()
+    finally:
+        ctx.set_stream(0)
+
+
 def test_moe_reference_fixture(ctx, ref_cases):
     T, H, FF, E, k = (int(v) for v in ref_cases["moe_dims"])
     kinds = (KIND_Q4_K, KIND_Q4_K, KIND_Q6_K)
