@@ -723,20 +723,28 @@ static int moe_experts_impl(mcu_context_t *ctx, int gate_kind, int up_kind, int 
         __half *xh = (__half *)ctx->act_half.ptr;
         float *rowscale = (float *)ctx->act_rowscale.ptr;
         const int *cnt = rb.counts + e_begin, *off = rb.offsets + e_begin;
-        // every route is gathered and staged (rows of other ranks' experts are never multiplied nor combined)
-        MCU_CUDA(launch_moe_gather(hidden_dev, H, rb.sorted_tok, 0, (int)routes, (int)H, route_hidden, s));
-        MCU_CUDA(launch_act_half_fused(gate_kind, route_hidden, (int)H, (int)routes, (int)H, ACT_ORDER_QUAD, xh, rowscale, s));
+        // The staging kernels fetch their rows themselves: the routed token's hidden row for gate/up, act(gate) * up
+        // for down.  Routes of other ranks' experts (outside [offsets[e_begin], offsets[e_end])) are skipped there,
+        // never multiplied and never combined.
+        ActSource from_hidden, from_glu;
+        from_hidden.row_index = rb.sorted_tok;
+        from_hidden.row_lo = from_glu.row_lo = rb.offsets + e_begin;
+        from_hidden.row_hi = from_glu.row_hi = rb.offsets + e_begin + e_count;
+        from_glu.x2 = up_out;
+        from_glu.glu = ffn_type == MCU_FFN_GEGLU ? 2 : 1;
+        MCU_CUDA(launch_act_half_fused_from(gate_kind, hidden_dev, (int)H, from_hidden, (int)routes, (int)H, ACT_ORDER_QUAD,
+                                            xh, rowscale, s));
         MCU_CUDA(launch_gemm_tma_grouped(gate_kind, gate_dev, (int)e_count, xh, rowscale, (int)kp_h, (int)routes, (int)H,
                                          (int)FF, cnt, off, gate_out, (int)FF, ctx->dev_err, s));
         MCU_CUDA(launch_gemm_tma_grouped(up_kind, up_dev, (int)e_count, xh, rowscale, (int)kp_h, (int)routes, (int)H, (int)FF,
                                          cnt, off, up_out, (int)FF, ctx->dev_err, s));
-        MCU_CUDA(launch_moe_glu(gate_out, up_out, routes * FF, ffn_type == MCU_FFN_GEGLU, s));
-        MCU_CUDA(launch_act_half_fused(down_kind, gate_out, (int)FF, (int)routes, (int)FF, ACT_ORDER_QUAD, xh, rowscale, s));
+        MCU_CUDA(launch_act_half_fused_from(down_kind, gate_out, (int)FF, from_glu, (int)routes, (int)FF, ACT_ORDER_QUAD, xh,
+                                            rowscale, s));
         MCU_CUDA(launch_gemm_tma_grouped(down_kind, down_dev, (int)e_count, xh, rowscale, (int)kp_f, (int)routes, (int)FF,
                                          (int)H, cnt, off, route_down, (int)H, ctx->dev_err, s));
         MCU_CUDA(launch_moe_combine_dev(route_down, rb.sorted_w, rb.route_pos, (int)T, (int)k, (int)H, rb.offsets,
                                         (int)e_begin, (int)(e_begin + e_count), rb.counts + E, ctx->dev_err, out_dev, H, s));
-        count_launches(8);
+        count_launches(6);
         return MCU_SUCCESS;
     }
     if (stream_is_capturing(s))

@@ -170,8 +170,8 @@ half_acts_kernel(int kq, int perm, const int8_t *__restrict__ qs, const float *_
 // programmatic stream serialization: everything before griddepcontrol.wait is independent of earlier kernels.
 template <bool KQ>
 __global__ void __launch_bounds__(256)
-act_half_fused_kernel(const float *__restrict__ x, int ldx, int K, int nb, int perm, __half *__restrict__ xh,
-                      float *__restrict__ rowscale) {
+act_half_fused_kernel(const float *__restrict__ x, int ldx, ActSource src, int K, int nb, int perm,
+                      __half *__restrict__ xh, float *__restrict__ rowscale) {
     extern __shared__ __align__(16) uint8_t act_sm[];
     constexpr int BV = KQ ? QK_K : Q8_0_VALUES;
     const int kp = nb * BV;
@@ -182,10 +182,22 @@ act_half_fused_kernel(const float *__restrict__ x, int ldx, int K, int nb, int p
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const float *xrow = x + (size_t)t * ldx;
+    if (src.row_lo != nullptr && (t < *src.row_lo || t >= *src.row_hi)) return;  // not this rank's row
+    const size_t row_off = (size_t)(src.row_index != nullptr ? src.row_index[t] : t) * ldx;
+    const float *xrow = x + row_off;
+    const float *urow = src.x2 != nullptr ? src.x2 + row_off : nullptr;
+    const int glu = src.glu;
+    // one value of the row: plain, or act(gate) * up with every operation rounded separately
+    auto value = [&](int k) -> float {
+        const float g = xrow[k];
+        if (urow == nullptr) return g;
+        float a;
+        if (glu == 2) a = __fmul_rn(__fmul_rn(0.5f, g), __fadd_rn(1.0f, erff(__fmul_rn(g, 0.7071067811865475f))));
+        else a = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+        return __fmul_rn(a, urow[k]);
+    };
     if (KQ) {
         for (int blk = warp; blk < nb; blk += 8) {
-            const float *row = xrow + (size_t)blk * QK_K;
             const int len = min(QK_K, K - blk * QK_K);
             float v[8];
             float best_abs = 0.0f, best_val = 0.0f;
@@ -193,7 +205,7 @@ act_half_fused_kernel(const float *__restrict__ x, int ldx, int K, int nb, int p
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int idx = lane + 32 * i;
-                v[i] = idx < len ? row[idx] : 0.0f;
+                v[i] = idx < len ? value(blk * QK_K + idx) : 0.0f;
                 const float a = fabsf(v[i]);
                 if (a > best_abs) {
                     best_abs = a;
@@ -227,7 +239,7 @@ act_half_fused_kernel(const float *__restrict__ x, int ldx, int K, int nb, int p
     } else {
         for (int blk = warp; blk < nb; blk += 8) {
             const int k = blk * Q8_0_VALUES + lane;
-            const float v = k < K ? xrow[k] : 0.0f;
+            const float v = k < K ? value(k) : 0.0f;
             float amax = fabsf(v);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -277,8 +289,8 @@ size_t act_half_fused_smem(int kind, int K) {
     return (size_t)((nb * bv + 15) & ~15) + (size_t)nb * sizeof(float);
 }
 
-cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int K, int k_order, __half *xh,
-                                  float *rowscale, cudaStream_t s) {
+cudaError_t launch_act_half_fused_from(int kind, const float *x, int ldx, const ActSource &src, int T, int K, int k_order,
+                                       __half *xh, float *rowscale, cudaStream_t s) {
     if (T <= 0) return cudaSuccess;
     const int bv = block_values(kind), nb = (K + bv - 1) / bv;
     cudaLaunchConfig_t cfg = {};
@@ -292,8 +304,13 @@ cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (kind == KIND_Q8_0)
-        return cudaLaunchKernelEx(&cfg, act_half_fused_kernel<false>, x, ldx, K, nb, k_order, xh, rowscale);
-    return cudaLaunchKernelEx(&cfg, act_half_fused_kernel<true>, x, ldx, K, nb, k_order, xh, rowscale);
+        return cudaLaunchKernelEx(&cfg, act_half_fused_kernel<false>, x, ldx, src, K, nb, k_order, xh, rowscale);
+    return cudaLaunchKernelEx(&cfg, act_half_fused_kernel<true>, x, ldx, src, K, nb, k_order, xh, rowscale);
+}
+
+cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int K, int k_order, __half *xh,
+                                  float *rowscale, cudaStream_t s) {
+    return launch_act_half_fused_from(kind, x, ldx, ActSource{}, T, K, k_order, xh, rowscale, s);
 }
 
 cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, int k_order, __half *xh, float *rowscale,

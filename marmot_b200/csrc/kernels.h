@@ -34,6 +34,17 @@ cudaError_t launch_half_acts(int kind, const ActBuffers &a, int T, int K, int k_
 size_t act_half_fused_smem(int kind, int K);
 cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int K, int k_order, __half *xh,
                                   float *rowscale, cudaStream_t s);
+// Where the staging kernel takes its rows from, for callers that would otherwise run a gather or a GLU pass first:
+// row t comes from x + row_index[t] * ldx when row_index is set; with x2 set the value is act(x) * x2 (glu 1 = SiLU,
+// 2 = GELU, rounded like the MoE GLU kernel); rows outside [*row_lo, *row_hi) (device-resident) are skipped.
+struct ActSource {
+    const float *x2 = nullptr;
+    int glu = 0;
+    const int32_t *row_index = nullptr;
+    const int *row_lo = nullptr, *row_hi = nullptr;
+};
+cudaError_t launch_act_half_fused_from(int kind, const float *x, int ldx, const ActSource &src, int T, int K, int k_order,
+                                       __half *xh, float *rowscale, cudaStream_t s);
 
 // blocks -> f32 (bit-exact with the reference dequantizers)
 cudaError_t launch_dequantize(int kind, const void *blocks, size_t n_values, float *out, cudaStream_t s);
