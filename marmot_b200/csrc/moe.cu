@@ -65,21 +65,43 @@ __global__ void moe_prefix_kernel(const int *__restrict__ counts, int E, int *__
     }
 }
 
-// One warp per expert walks the routes in order (token-major, slot-minor) and assigns stable
-// positions with ballots; writes the sorted token ids, the normalised weights
-// (renormalise policy: weight * (scale / sum of the token's weights), 0 when the sum <= FLT_MIN,
-// moe_ops.c:960-967) and the inverse map route -> position.
-__global__ void moe_scatter_kernel(const int32_t *__restrict__ ids, const float *__restrict__ weights, int T, int k,
-                                   const int *__restrict__ offsets, float weights_scale, int renormalize,
-                                   int32_t *__restrict__ sorted_tok, float *__restrict__ sorted_w,
-                                   int32_t *__restrict__ route_pos) {
+// One CTA per expert assigns stable positions to its routes in route order (token-major, slot-minor): each of the 32
+// warps takes a contiguous chunk of the routes, counts its matches with ballots, an exclusive prefix over the warps'
+// counts gives every chunk its first position, and a second pass over the chunk places the routes.  Writes the sorted
+// token ids, the normalised weights (renormalise policy: weight * (scale / sum of the token's weights), 0 when the
+// sum <= FLT_MIN, moe_ops.c:960-967) and the inverse map route -> position.
+__global__ void __launch_bounds__(1024)
+moe_scatter_kernel(const int32_t *__restrict__ ids, const float *__restrict__ weights, int T, int k,
+                   const int *__restrict__ offsets, float weights_scale, int renormalize,
+                   int32_t *__restrict__ sorted_tok, float *__restrict__ sorted_w, int32_t *__restrict__ route_pos) {
+    __shared__ int warp_first[32];
     const int e = blockIdx.x;
-    const int lane = threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int routes = T * k;
-    int cursor = offsets[e];
-    for (int base = 0; base < routes; base += 32) {
+    const int chunk = ((routes + 31) / 32 + 31) & ~31;  // routes per warp, a multiple of the warp size
+    const int lo = warp * chunk, hi = min(routes, lo + chunk);
+    int n = 0;
+    for (int base = lo; base < hi; base += 32) {
         const int i = base + lane;
-        const bool mine = i < routes && ids[i] == e;
+        n += __popc(__ballot_sync(0xffffffffu, i < hi && ids[i] == e));
+    }
+    if (lane == 0) warp_first[warp] = n;
+    __syncthreads();
+    if (warp == 0) {
+        const int mine = warp_first[lane];
+        int incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        warp_first[lane] = offsets[e] + incl - mine;
+    }
+    __syncthreads();
+    int cursor = warp_first[warp];
+    for (int base = lo; base < hi; base += 32) {
+        const int i = base + lane;
+        const bool mine = i < hi && ids[i] == e;
         const unsigned m = __ballot_sync(0xffffffffu, mine);
         if (mine) {
             const int pos = cursor + __popc(m & ((1u << lane) - 1u));
@@ -206,7 +228,7 @@ cudaError_t launch_moe_route(const int32_t *ids, const float *weights, int T, in
     if (err != cudaSuccess) return err;
     moe_count_kernel<<<(routes + 255) / 256, 256, 0, s>>>(ids, routes, E, b.counts, b.counts + E);
     moe_prefix_kernel<<<1, 32, 0, s>>>(b.counts, E, b.offsets);
-    moe_scatter_kernel<<<E, 32, 0, s>>>(ids, weights, T, k, b.offsets, weights_scale, renormalize, b.sorted_tok,
+    moe_scatter_kernel<<<E, 1024, 0, s>>>(ids, weights, T, k, b.offsets, weights_scale, renormalize, b.sorted_tok,
                                         b.sorted_w, b.route_pos);
     return cudaGetLastError();
 }

@@ -103,9 +103,59 @@ def attention_case(args) -> None:
     ctx.close()
 
 
+def moe_case(args) -> None:
+    """Expert FFN block: -T tokens, --top-k routes each over --experts experts of shape K (hidden) x F (expert FFN),
+    gate/up/down all of --kind; routing is uniform random without repeats.  FLOPs per call: 6 * T * top_k * K * F."""
+    import torch
+
+    dev = torch.device("cuda", 0)
+    ctx = Context(0)
+    kind = KIND_BY_NAME[args.kind]
+    E, k, T, H, FF = args.experts, args.top_k, args.T, args.K, args.F
+    gen = torch.Generator(device=dev).manual_seed(0)
+    gate = synthetic_blocks_device(torch, kind, E * FF, H, dev, gen)
+    up = synthetic_blocks_device(torch, kind, E * FF, H, dev, gen)
+    down = synthetic_blocks_device(torch, kind, E * H, FF, dev, gen)
+    hidden = torch.randn((T, H), device=dev, generator=gen)
+    scores = torch.rand((T, E), device=dev, generator=gen)
+    vals, ids = torch.topk(scores, k, dim=1)
+    ids = ids.to(torch.int32).contiguous()
+    vals = (vals / vals.sum(1, keepdim=True)).contiguous()
+    out = torch.empty((T, H), dtype=torch.float32, device=dev)
+    kinds = (kind, kind, kind)
+
+    def one_pass():
+        ctx.moe_experts_local(kinds, hidden, gate, up, down, ids, vals, FF, E, 0, E, out=out)
+
+    stream = torch.cuda.Stream(dev)
+    ctx.set_stream(stream.cuda_stream)
+    with torch.cuda.stream(stream):
+        for _ in range(args.iters):
+            one_pass()
+    torch.cuda.synchronize()
+    flops = 6.0 * T * k * H * FF
+    print(f"moe {args.kind} T={T} top_k={k} experts={E} H={H} FF={FF}: {args.iters} calls, {ctx.launch_count()} kernel "
+          f"launches, {flops / 1e9:.1f} GFLOP per call")
+    if args.time:
+        with torch.cuda.stream(stream):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            e0.record(stream)
+            for _ in range(reps):
+                one_pass()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        print(f"{us:.1f} us per call, {flops / us / 1e6:.1f} TFLOP/s")
+    ctx.set_stream(0)
+    ctx.close()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--op", default="linear", choices=["linear", "attention"])
+    ap.add_argument("--op", default="linear", choices=["linear", "attention", "moe"])
+    ap.add_argument("--experts", type=int, default=8, help="moe: experts")
+    ap.add_argument("--top-k", type=int, default=2, help="moe: routes per token")
     ap.add_argument("--seqs", type=int, default=64, help="attention: sequences (one new token each)")
     ap.add_argument("--ctx", type=int, default=2048, help="attention: cached positions per sequence")
     ap.add_argument("--layers", type=int, default=4, help="attention: layers in the pool, visited in turn")
@@ -124,6 +174,8 @@ def main() -> None:
     args = ap.parse_args()
     if args.op == "attention":
         return attention_case(args)
+    if args.op == "moe":
+        return moe_case(args)
 
     import torch
 
