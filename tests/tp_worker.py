@@ -91,6 +91,20 @@ def main() -> int:
         ctx.synchronize()
         e = float(max_rel_err(y.cpu().numpy(), want))
         check(f"moe_{name}", e <= TOL_MOE, e)
+    # 256 routes or more: the grouped launches, which skip the routes of other ranks' experts on the device
+    T = 160
+    down4 = np.concatenate([random_blocks(KIND_Q4_K, H, FF, rng, d_sigma=0.0005) for _ in range(E)])
+    hidden = torch.from_numpy(rng.normal(0, 1, (T, H)).astype(np.float32)).to(dev)
+    ids = torch.from_numpy(np.stack([rng.permutation(E)[:k] for _ in range(T)]).astype(np.int32)).to(dev)
+    wts = torch.from_numpy(rng.uniform(0.1, 1.0, (T, k)).astype(np.float32)).to(dev)
+    kinds = (KIND_Q4_K, KIND_Q4_K, KIND_Q4_K)
+    want = ctx.moe_experts(kinds, hidden, ctx.upload(gate), ctx.upload(up), ctx.upload(down4), ids, wts, FF, E).cpu().numpy()
+    for name, c in (("nccl", None), ("peer", comm)):
+        moe = tp.ExpertParallelMoE(ctx, group, kinds, gate, up, down4, H, FF, E, comm=c)
+        y = moe(hidden, ids, wts)
+        ctx.synchronize()
+        e = float(max_rel_err(y.cpu().numpy(), want))
+        check(f"moe_grouped_{name}", e <= 1e-5, e)  # the same products as on one GPU, summed per rank first
 
     # a whole decoder step: every rank cuts its share out of the same full-model weights; logits slices and the greedy
     # pick must match the single-GPU decoder on the full weights (only the f32 order of the row-parallel sums differs)
