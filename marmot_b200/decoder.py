@@ -170,6 +170,32 @@ class Decoder:
             table = np.arange(n_blocks, dtype=np.uint32).reshape(max_seqs, self.max_blocks)
             self.block_table = torch.from_numpy(table).to(dev)
         self._bufs = {}
+        self._side = None
+
+    def _side_contexts(self):
+        """Two more contexts on streams of their own (each with its own workspace), for the key and value projections,
+        which read the same normalised activations as the query projection and are small enough at decode batch sizes
+        that their duration is mostly fixed latency: the three run side by side and rejoin before RoPE.  The fork and
+        the join are stream-to-stream waits, so a CUDA-graph capture of the step records them as graph edges."""
+        if self._side is None:
+            import os
+
+            torch = self.torch
+            if os.environ.get("MARMOT_DECODER_SERIAL_QKV"):  # diagnostic switch: one stream, three calls in turn
+                self._side = ()
+            else:
+                streams = [torch.cuda.Stream(self.dev) for _ in range(2)]
+                ctxs = [Context(self.ctx.device, use_torch_stream=False) for _ in streams]
+                for c, st in zip(ctxs, streams):
+                    c.set_stream(st.cuda_stream)
+                self._side = (ctxs, streams)
+        return self._side
+
+    def _main_stream(self):
+        handle = self.ctx.lib.mcu_context_get_stream(self.ctx.handle) or 0
+        if handle in (0, 1):  # the legacy default stream
+            return self.torch.cuda.default_stream(self.dev)
+        return self.torch.cuda.ExternalStream(handle, device=self.dev)
 
     def _buf(self, name, shape, dtype=None):
         key = (name, tuple(shape))
@@ -238,10 +264,22 @@ class Decoder:
         scale = float(hd) ** -0.5
         # the residual add that ends a block and the rms_norm that opens the next one run as one kernel
         ctx.rmsnorm(x, self.layers[0]["attn_norm"], s.rms_eps, out=h)
+        side = self._side_contexts()
+        main = self._main_stream() if side else None
         for i, lw in enumerate(self.layers):
-            ctx.linear(kd[f"l{i}.wq"], h, lw["wq"], hq * hd, out=q)
-            ctx.linear(kd[f"l{i}.wk"], h, lw["wk"], hkv * hd, out=k)
-            ctx.linear(kd[f"l{i}.wv"], h, lw["wv"], hkv * hd, out=v)
+            if side:
+                (ctx_k, ctx_v), (st_k, st_v) = side
+                st_k.wait_stream(main)
+                st_v.wait_stream(main)
+                ctx_k.linear(kd[f"l{i}.wk"], h, lw["wk"], hkv * hd, out=k)
+                ctx_v.linear(kd[f"l{i}.wv"], h, lw["wv"], hkv * hd, out=v)
+                ctx.linear(kd[f"l{i}.wq"], h, lw["wq"], hq * hd, out=q)
+                main.wait_stream(st_k)
+                main.wait_stream(st_v)
+            else:
+                ctx.linear(kd[f"l{i}.wq"], h, lw["wq"], hq * hd, out=q)
+                ctx.linear(kd[f"l{i}.wk"], h, lw["wk"], hkv * hd, out=k)
+                ctx.linear(kd[f"l{i}.wv"], h, lw["wv"], hkv * hd, out=v)
             ctx.rope_qk(q, k, positions, hq, hkv, hd, s.rope_theta)
             ctx.paged_attention(meta, q, k, v, self.kv_k, self.kv_v, self.block_table, i, hq, hkv, hd, self.block_size,
                                 scale, out=att)
