@@ -53,7 +53,7 @@ def measured_peaks():
 
 
 def make_weights(seed: int) -> np.ndarray:
-    from tests.util import random_blocks
+    from marmot_b200.synthetic import random_blocks
 
     return random_blocks(KIND_Q4_K, F_DIM, K_DIM, np.random.default_rng(seed))
 
@@ -105,35 +105,48 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_gemv_time(copies: int, iters: int, threads: int):
-    """Seconds per GEMV of the CPU checker on this host (reference library when present)."""
-    from oracle.bindings import REF_LIB, Oracle, Reference
+class CpuGemv:
+    """The CPU checker's GEMV on this host (the reference library when present, else the oracle port): one context and
+    one set of weight tensors for the whole run, as a model holds them."""
 
-    ws = [make_weights(1000 + i) for i in range(copies)]
-    x = np.random.default_rng(5).normal(0, 1, (T_TOK, K_DIM)).astype(np.float32)
-    if REF_LIB.exists():
-        ref = Reference(threads=threads)
-        # keep the weight tensors alive across calls, as a model would
-        import ctypes as C
-        tw = [ref._qtensor((F_DIM, K_DIM), KIND_Q4_K, w) for w in ws]
-        tx = ref._tensor((T_TOK, K_DIM), 0, x)
-        to = ref._tensor((T_TOK, F_DIM), 0)
-        run = lambda i: ref._check(ref.lib.marmot_linear(ref.ctx, tx, tw[i % copies], None, to), "marmot_linear")
-        kind = "reference"
-    else:
-        from oracle import build_oracle
+    def __init__(self, copies: int, threads: int):
+        from oracle.bindings import REF_LIB, Oracle, Reference
 
-        build_oracle.build()
-        orc = Oracle()
-        run = lambda i: orc.linear(KIND_Q4_K, x, ws[i % copies], F_DIM, threads=threads)
-        kind = "port"
-    for i in range(3):
-        run(i)
-    t0 = time.perf_counter()
-    for i in range(iters):
-        run(i)
-    dt = (time.perf_counter() - t0) / iters
-    return dt, kind
+        self.copies, self.threads = copies, threads
+        ws = [make_weights(1000 + i) for i in range(copies)]
+        x = np.random.default_rng(5).normal(0, 1, (T_TOK, K_DIM)).astype(np.float32)
+        if REF_LIB.exists():
+            ref = Reference(threads=threads)
+            tw = [ref._qtensor((F_DIM, K_DIM), KIND_Q4_K, w) for w in ws]
+            tx = ref._tensor((T_TOK, K_DIM), 0, x)
+            to = ref._tensor((T_TOK, F_DIM), 0)
+            self._keep = (ref, tw, tx, to, ws)
+            self.run = lambda i: ref._check(ref.lib.marmot_linear(ref.ctx, tx, tw[i % copies], None, to), "marmot_linear")
+            self.kind = "reference"
+        else:
+            from oracle import build_oracle
+
+            build_oracle.build()
+            orc = Oracle()
+            self._keep = (orc, ws)
+            self.run = lambda i: orc.linear(KIND_Q4_K, x, ws[i % copies], F_DIM, threads=threads)
+            self.kind = "port"
+        for i in range(max(copies, 8)):  # every weight copy touched, thread pool and caches warm
+            self.run(i)
+
+    def seconds(self, n: int, start: int = 0) -> float:
+        """Wall time of n GEMVs, rotating over the weight copies."""
+        t0 = time.perf_counter()
+        for i in range(start, start + n):
+            self.run(i)
+        return time.perf_counter() - t0
+
+
+def workload_config(copies: int) -> dict:
+    """The workload description both arms print (the driver compares the two dictionaries)."""
+    return {"workload": WORKLOAD, "T": T_TOK, "K": K_DIM, "F": F_DIM, "quant": "Q4_K", "weight_copies": copies,
+            "l2_policy": f"inputs larger than L2: rotation over {copies * W_BYTES / 1e6:.0f} MB of weights",
+            "multi_gpu": "replicas only (independent GEMVs per rank, no collective)"}
 
 
 def time_other_regimes(ctx, dev):
@@ -142,7 +155,7 @@ def time_other_regimes(ctx, dev):
     `mcu_linear` call (activation quantisation included), rotating over weight copies larger than L2."""
     import torch
 
-    from marmot_b200.profile_case import synthetic_blocks
+    from marmot_b200.synthetic import synthetic_blocks
     from marmot_b200.runtime import KIND_BY_NAME, row_bytes
 
     peak_bw, _ = measured_peaks()
@@ -204,7 +217,7 @@ def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
     import torch
 
     from marmot_b200 import tensor_parallel as tp
-    from marmot_b200.profile_case import synthetic_blocks_device
+    from marmot_b200.synthetic import synthetic_blocks_device
     from marmot_b200.runtime import KIND_Q6_K, row_bytes
 
     m = LLAMA8B
@@ -438,7 +451,7 @@ def time_moe_c5(ctx, dev, rank: int, world: int, dist):
     import torch
 
     from marmot_b200 import tensor_parallel as tp
-    from marmot_b200.profile_case import synthetic_blocks_device
+    from marmot_b200.synthetic import synthetic_blocks_device
 
     T, H, FF, E, k = 2048, 4096, 14336, 8, 2
     if E % world:
@@ -495,28 +508,25 @@ def time_moe_c5(ctx, dev, rank: int, world: int, dist):
 
 
 def run_reference_arm(args, rank: int):
+    """The reference's own CPU implementation of the path on all host cores: a step is one rotation over the same
+    number of distinct weight matrices as the GPU arm's step."""
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    per_step = 8  # GEMVs per step: a bounded sample of the rotation
-    copies = 4
-    from oracle.bindings import REF_LIB
-
-    times = []
-    # warm-up + timed steps share one loop helper; each step = per_step GEMVs
-    dt, kind = cpu_gemv_time(copies, per_step * max(1, args.warmup), threads)
-    for _ in range(args.steps):
-        dt, kind = cpu_gemv_time(copies, per_step, threads)
-        times.append(dt * per_step)
+    copies = args.copies
+    cpu = CpuGemv(copies, threads)
+    for w in range(args.warmup):
+        cpu.seconds(copies, w * copies)
+    times = [cpu.seconds(copies, s * copies) for s in range(args.steps)]
     total = sum(times)
-    value = args.steps * per_step * ALG_BYTES / total / 1e9
-    sample = f"{per_step} GEMVs per step over {copies} weight copies, {threads} host threads"
+    value = args.steps * copies * ALG_BYTES / total / 1e9
+    sample = f"{copies} GEMVs per step (one rotation over {copies} weight copies), {threads} host threads, one context"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8 dot, f32 scale", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "T": T_TOK, "K": K_DIM, "F": F_DIM, "quant": "Q4_K"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "config": workload_config(copies),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": cpu.kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -661,9 +671,8 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 dot, f32 scale", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "T": T_TOK, "K": K_DIM, "F": F_DIM, "quant": "Q4_K", "weight_copies": R, "launch": "eager" if args.no_graph else "cuda graph of one step, replayed",
-                   "l2_policy": f"inputs larger than L2: rotation over {R * W_BYTES / 1e6:.0f} MB of weights",
-                   "multi_gpu": "replicas only (independent GEMVs per rank, no collective)"},
+        "config": workload_config(R),
+        "launch": "eager" if args.no_graph else "cuda graph of one step, replayed",
         "gpu_launches": int(launches),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": R * T_TOK * K_DIM * 4,
                 "d2h_bytes_per_step": R * T_TOK * F_DIM * 4, "steps": e2e_steps,
@@ -687,10 +696,11 @@ def main():
         line["other_regimes"] = time_other_regimes(ctx, dev)
     if not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        iters = 200
-        dt, kind = cpu_gemv_time(4, iters, threads)
-        line["cpu_baseline"] = {"value": ALG_BYTES / dt / 1e9, "unit": UNIT, "cores": threads, "kind": kind,
-                                "sample": f"{iters} GEMVs over 4 weight copies ({dt * 1e3:.3f} ms each)"}
+        cpu = CpuGemv(R, threads)
+        iters = 8 * R
+        dt = cpu.seconds(iters) / iters
+        line["cpu_baseline"] = {"value": ALG_BYTES / dt / 1e9, "unit": UNIT, "cores": threads, "kind": cpu.kind,
+                                "sample": f"{iters} GEMVs rotating over {R} weight copies ({dt * 1e3:.3f} ms each), one context"}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

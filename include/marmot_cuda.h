@@ -177,7 +177,10 @@ int mcu_linear_host(
  *      loads the library holds it until the process exits).  The call takes no context and performs no
  *      cudaMalloc, cudaFree or other allocating call; it enqueues two kernels on `cuda_stream` (a cudaStream_t,
  *      NULL = default stream) of the current device.  The first call on each device looks up the array's
- *      device address (cudaGetSymbolAddress); make that first call outside of any stream capture.
+ *      device address (cudaGetSymbolAddress); make that first call outside of any stream capture.  With lazy
+ *      module loading that first call is also when the driver loads the two kernels and the array onto the
+ *      device, which may itself take device memory: make it early, before the rest of the device memory is
+ *      reserved, so that later calls are certain to need nothing.
  *      All calls share the one array and it keeps the last call's contents.  Nothing in it needs clearing
  *      (each call rewrites every byte it later reads), but two calls that overlap on the GPU, e.g. on
  *      different streams, race on it: serialise them. ---- */

@@ -12,6 +12,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <climits>
 #include <mutex>
 #include <vector>
 
@@ -46,8 +47,17 @@ static int cuda_fail(cudaError_t e, const char *what) {
         if (e__ != cudaSuccess) return cuda_fail(e__, #expr);       \
     } while (0)
 
-static int g_sm_count = 0;
-int device_sm_count() { return g_sm_count > 0 ? g_sm_count : 148; }
+// SM count of the calling thread's current device (every launcher runs with its context's device current).
+int device_sm_count() {
+    static std::atomic<int> cache[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int v = cache[dev].load(std::memory_order_relaxed);
+    if (v > 0) return v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+    cache[dev].store(v, std::memory_order_relaxed);
+    return v;
+}
 
 struct Buffer {
     void *ptr = nullptr;
@@ -173,7 +183,6 @@ int mcu_context_create(int device, mcu_context_t **out) {
     if (prop.major != 10)
         return fail(MCU_ERROR_BACKEND_INIT_FAILED, "device %d is sm_%d%d; this library is built for sm_100a only", device,
                     prop.major, prop.minor);
-    g_sm_count = prop.multiProcessorCount;
     mcu_context *ctx = new (std::nothrow) mcu_context();
     if (ctx == nullptr) return fail(MCU_ERROR_OUT_OF_MEMORY, "context allocation failed");
     ctx->device = device;
@@ -287,6 +296,7 @@ void mcu_graph_destroy(mcu_graph_t *graph) {
 int mcu_context_set_regime(mcu_context_t *ctx, int regime) {
     if (ctx == nullptr) return fail(MCU_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
     if (regime < MCU_REGIME_AUTO || regime > MCU_REGIME_GEMV_PLAIN) return fail(MCU_ERROR_INVALID_ARGUMENT, "bad regime");
+    std::lock_guard<std::mutex> lock(ctx->mu);
     ctx->regime = regime;
     return MCU_SUCCESS;
 }
@@ -358,6 +368,8 @@ static int validate_linear(int kind, const void *x, const void *w, const void *o
     if (ldx < K || ldo < F) return fail(MCU_ERROR_DIMENSION_MISMATCH, "row stride smaller than the row");
     if (T > (size_t)1 << 30 || F > (size_t)1 << 30 || K > (size_t)1 << 30)
         return fail(MCU_ERROR_INVALID_ARGUMENT, "dimension too large");
+    // the launchers carry row strides as int
+    if (ldx > (size_t)INT_MAX || ldo > (size_t)INT_MAX) return fail(MCU_ERROR_INVALID_ARGUMENT, "row stride too large");
     const uintptr_t align = kind == MCU_KIND_Q4_K ? 15 : 1;
     if ((uintptr_t)w & align)
         return fail(MCU_ERROR_INVALID_ARGUMENT, "weight blocks must be %d-byte aligned", (int)align + 1);
@@ -507,6 +519,8 @@ int mcu_quantize_activations(mcu_context_t *ctx, int weight_kind, const float *x
     if (x_dev == nullptr || qs_dev == nullptr || d_dev == nullptr || (weight_kind != MCU_KIND_Q8_0 && bsums_dev == nullptr))
         return fail(MCU_ERROR_INVALID_ARGUMENT, "null tensor data");
     if (K == 0 || ldx < K) return fail(MCU_ERROR_DIMENSION_MISMATCH, "bad K / ldx");
+    if (ldx > (size_t)INT_MAX || T > (size_t)1 << 30 || K > (size_t)1 << 30)
+        return fail(MCU_ERROR_INVALID_ARGUMENT, "dimension or row stride too large");
     ActBuffers ab{qs_dev, d_dev, bsums_dev};
     MCU_CUDA(launch_quantize_act(weight_kind, x_dev, (int)ldx, (int)T, (int)K, ab, nullptr, ctx->stream));
     count_launches(1);

@@ -69,6 +69,13 @@ size_t type_bytes(uint32_t type, uint64_t n) {
     }
 }
 
+// values per block of a ggml tensor type (1 for the plain float / integer types)
+uint64_t type_block_values(uint32_t type) {
+    if (type == 0 || type == 1 || type == 30) return 1;
+    if (type == 8 || (type >= 2 && type <= 7)) return 32;
+    return 256;
+}
+
 struct Reader {
     const uint8_t *p, *end;
     bool ok = true;
@@ -133,8 +140,9 @@ bool read_value(Reader &r, uint32_t type, MetaValue &out) {
             r.ok = false;  // nested arrays do not occur in model files
         } else {
             const size_t es = scalar_size(out.elem_type);
-            if (es == 0) r.ok = false;
-            else r.skip(out.count * es);
+            uint64_t span = 0;
+            if (es == 0 || __builtin_mul_overflow(out.count, (uint64_t)es, &span)) r.ok = false;
+            else r.skip(span);
         }
         break;
     }
@@ -196,22 +204,37 @@ int mcu_gguf_open(const char *path, mcu_gguf_t **out) {
         t.name = r.str();
         t.n_dims = r.get<uint32_t>();
         if (!r.ok || t.n_dims == 0 || t.n_dims > 4) return bail(MCU_ERROR_INVALID_ARGUMENT, "gguf: malformed tensor directory");
+        // The element count comes from the file: a product that wraps would pass the end-of-file check below with a
+        // tiny byte size while row ranges computed from the dimensions point far outside the mapping.
         uint64_t n = 1;
+        bool wrapped = false;
         for (uint32_t d = 0; d < t.n_dims; ++d) {
             t.dims[d] = r.get<uint64_t>();
-            n *= t.dims[d];
+            wrapped = wrapped || __builtin_mul_overflow(n, t.dims[d], &n);
         }
         t.type = r.get<uint32_t>();
         t.offset = r.get<uint64_t>();
         if (!r.ok) return bail(MCU_ERROR_INVALID_ARGUMENT, "gguf: malformed tensor directory");
+        if (wrapped || n > ((uint64_t)1 << 48))
+            return bail(MCU_ERROR_INVALID_ARGUMENT, "gguf: tensor dimensions overflow");
         t.nbytes = type_bytes(t.type, n);
+        if (t.nbytes != 0) {
+            // rows must be whole blocks, or the per-row byte size used by the uploads would not tile the payload
+            uint64_t rows = n / (t.dims[0] ? t.dims[0] : 1);
+            if (t.dims[0] == 0 || type_bytes(t.type, t.dims[0]) * rows != t.nbytes ||
+                t.dims[0] % type_block_values(t.type) != 0)
+                return bail(MCU_ERROR_INVALID_ARGUMENT, "gguf: tensor rows are not whole blocks");
+        }
         g->by_name[t.name] = (size_t)i;
     }
     uint64_t align = 32;
     auto it = g->meta.find("general.alignment");
     if (it != g->meta.end() && it->second.u > 0) align = it->second.u;
+    if ((align & (align - 1)) != 0 || align > ((uint64_t)1 << 20))
+        return bail(MCU_ERROR_INVALID_ARGUMENT, "gguf: general.alignment must be a power of two up to 1 MiB");
     const size_t at = (size_t)(r.p - g->map);
     g->data_start = (at + align - 1) / align * align;
+    if (g->data_start > g->map_bytes) return bail(MCU_ERROR_INVALID_ARGUMENT, "gguf: header runs past the end of the file");
     for (const TensorEntry &t : g->tensors)
         if (t.nbytes != 0 && (g->data_start + t.offset > g->map_bytes || t.nbytes > g->map_bytes - g->data_start - t.offset))
             return bail(MCU_ERROR_INVALID_ARGUMENT, "gguf: tensor data runs past the end of the file");
@@ -292,7 +315,7 @@ int mcu_gguf_upload(mcu_context_t *ctx, const mcu_gguf_t *g, size_t index, size_
     if (row_hi > rows || row_lo > row_hi || k_hi > K || k_lo > k_hi) return gguf_fail(MCU_ERROR_DIMENSION_MISMATCH, "gguf: shard outside the tensor");
     const size_t row_bytes = type_bytes(t.type, K), lo_bytes = type_bytes(t.type, k_lo), hi_bytes = type_bytes(t.type, k_hi);
     // a K shard must fall on block boundaries: the byte offsets of k_lo and k_hi must describe them exactly
-    const uint64_t bv = (t.type == 0 || t.type == 1 || t.type == 30) ? 1 : (t.type == 8 || (t.type >= 2 && t.type <= 7)) ? 32 : 256;
+    const uint64_t bv = type_block_values(t.type);
     if (k_lo % bv != 0 || k_hi % bv != 0) return gguf_fail(MCU_ERROR_DIMENSION_MISMATCH, "gguf: K shard must be whole blocks");
     if (row_hi == row_lo || k_hi == k_lo) return MCU_SUCCESS;
     cudaError_t e = cudaSetDevice(context_device(ctx));

@@ -40,14 +40,17 @@ __global__ void topk_kernel(const float *__restrict__ x, int rows, int cols, siz
     }
 }
 
-// counts[e] = number of routes to expert e; bad_flag set when an id is out of range.
+// counts[e] = number of routes to expert e; bad_flag set when an id is out of range.  A route with such an id gets
+// position -1, which the scatter kernel never overwrites and the combine kernels skip, so that no later kernel
+// indexes with a stale or uninitialised position.
 __global__ void moe_count_kernel(const int32_t *__restrict__ ids, int routes, int E, int *__restrict__ counts,
-                                 int *__restrict__ bad_flag) {
+                                 int *__restrict__ bad_flag, int32_t *__restrict__ route_pos) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= routes) return;
     const int e = ids[i];
     if (e < 0 || e >= E) {
         atomicExch(bad_flag, 1);
+        route_pos[i] = -1;
         return;
     }
     atomicAdd(&counts[e], 1);
@@ -160,11 +163,11 @@ __global__ void moe_combine_kernel(const float *__restrict__ route_down, const f
         }
         pos[j] = p;
     }
-    for (int j = 0; j < k; ++j) w[j] = sorted_w[pos[j]];
+    for (int j = 0; j < k; ++j) w[j] = (pos[j] >= pos_lo && pos[j] < pos_hi) ? sorted_w[pos[j]] : 0.0f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float acc = 0.0f;
         for (int j = 0; j < k; ++j) {
-            if (pos[j] < pos_lo || pos[j] >= pos_hi) continue;  // another rank's expert
+            if (pos[j] < pos_lo || pos[j] >= pos_hi) continue;  // another rank's expert, or a rejected id
             acc = __fadd_rn(acc, __fmul_rn(w[j], route_down[(size_t)pos[j] * H + c]));
         }
         out[(size_t)t * ldo + c] = acc;
@@ -193,11 +196,12 @@ __global__ void moe_combine_dev_kernel(const float *__restrict__ route_down, con
         }
         pos[j] = p;
     }
-    for (int j = 0; j < k; ++j) w[j] = sorted_w[pos[j]];
+    const bool bad = *bad_id_count != 0;  // the call is rejected as a whole: zeros out, error at synchronize
+    for (int j = 0; j < k; ++j) w[j] = (!bad && pos[j] >= pos_lo && pos[j] < pos_hi) ? sorted_w[pos[j]] : 0.0f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float acc = 0.0f;
         for (int j = 0; j < k; ++j) {
-            if (pos[j] < pos_lo || pos[j] >= pos_hi) continue;
+            if (bad || pos[j] < pos_lo || pos[j] >= pos_hi) continue;
             acc = __fadd_rn(acc, __fmul_rn(w[j], route_down[(size_t)pos[j] * H + c]));
         }
         out[(size_t)t * ldo + c] = acc;
@@ -226,7 +230,7 @@ cudaError_t launch_moe_route(const int32_t *ids, const float *weights, int T, in
     const int routes = T * k;
     cudaError_t err = cudaMemsetAsync(b.counts, 0, (size_t)(E + 1) * sizeof(int), s);
     if (err != cudaSuccess) return err;
-    moe_count_kernel<<<(routes + 255) / 256, 256, 0, s>>>(ids, routes, E, b.counts, b.counts + E);
+    moe_count_kernel<<<(routes + 255) / 256, 256, 0, s>>>(ids, routes, E, b.counts, b.counts + E, b.route_pos);
     moe_prefix_kernel<<<1, 32, 0, s>>>(b.counts, E, b.offsets);
     moe_scatter_kernel<<<E, 1024, 0, s>>>(ids, weights, T, k, b.offsets, weights_scale, renormalize, b.sorted_tok,
                                         b.sorted_w, b.route_pos);

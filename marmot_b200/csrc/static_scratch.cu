@@ -70,7 +70,8 @@ extern "C" int mcu_linear_static_scratch(void *cuda_stream, int kind, const floa
         return set_error(MCU_ERROR_INVALID_ARGUMENT, msg);
     }
     if (K == 0 || ldx < K || ldo < F) return set_error(MCU_ERROR_DIMENSION_MISMATCH, "bad K or row stride");
-    if (F > ((size_t)1 << 30)) return set_error(MCU_ERROR_INVALID_ARGUMENT, "dimension too large");
+    if (F > ((size_t)1 << 30) || ldx > ((size_t)1 << 30) || ldo > ((size_t)1 << 30))
+        return set_error(MCU_ERROR_INVALID_ARGUMENT, "dimension or row stride too large");
     if ((uintptr_t)w_dev & (kind == MCU_KIND_Q4_K ? 15 : 1))
         return set_error(MCU_ERROR_INVALID_ARGUMENT, "weight blocks are not aligned");
     unsigned char *scratch = nullptr;

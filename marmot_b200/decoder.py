@@ -66,7 +66,7 @@ class Decoder:
         import torch
 
         from . import tensor_parallel as tp
-        from .profile_case import synthetic_blocks_device
+        from .synthetic import synthetic_blocks_device
 
         self.ctx, self.shape, self.torch = ctx, shape, torch
         self.block_size, self.max_seqs = block_size, max_seqs

@@ -122,28 +122,46 @@ class GgufFile:
         return out.view(torch.float32) if i["ggml_type"] == 0 else out
 
 
+# Architectures whose layer is exactly what `decoder.Decoder` computes: interleaved-pair ("NORM") RoPE, no attention
+# bias, no q/k norm.  The reference picks these traits per architecture (src/graph/gguf/architecture.cpp:12-143):
+# qwen2 / qwen3 / phi3 / gemma rotate half-split pairs ("NEOX"), qwen2 adds attention biases, qwen3 normalises q and k.
+SUPPORTED_ARCHITECTURES = ("llama", "mistral")
+
+
+def decoder_shape_from_gguf(f: "GgufFile"):
+    """The hyper-parameters the reference's graph builder reads (src/graph/gguf/graph_builder.cpp) as a DecoderShape.
+    Files of an architecture whose layer differs from the Llama layer are refused rather than decoded wrongly."""
+    from .decoder import DecoderShape
+
+    arch = f.meta_str("general.architecture", "llama")
+    if arch not in SUPPORTED_ARCHITECTURES:
+        raise MarmotCudaError(-1, f"architecture '{arch}' is not supported by the CUDA decoder "
+                                  f"(supported: {', '.join(SUPPORTED_ARCHITECTURES)}): its RoPE pairing, attention "
+                                  "biases or q/k normalisation differ from the Llama layer")
+    n_heads = f.meta_int(f"{arch}.attention.head_count")
+    d = f.meta_int(f"{arch}.embedding_length")
+    emb = f.info(f.find("token_embd.weight"))
+    q0 = f.find("blk.0.attn_q.weight")  # without an explicit key length the query projection tells the head size
+    hd_default = int(f.info(q0)["dims"][1]) // n_heads if q0 >= 0 else d // n_heads
+    return DecoderShape(
+        layers=f.meta_int(f"{arch}.block_count"), d=d, ffn=f.meta_int(f"{arch}.feed_forward_length"),
+        n_heads=n_heads, n_kv_heads=f.meta_int(f"{arch}.attention.head_count_kv", n_heads),
+        head_dim=f.meta_int(f"{arch}.attention.key_length", hd_default), vocab=int(emb["dims"][1]),
+        rope_theta=f.meta_float(f"{arch}.rope.freq_base", 10000.0),
+        rms_eps=f.meta_float(f"{arch}.attention.layer_norm_rms_epsilon", 1e-5))
+
+
 def load_llama_decoder(path: str, ctx, max_seqs: int, max_ctx: int, block_size: int = 16, kv_dtype=None, group=None,
                        comm=None, kv_pool=None):
     """A `decoder.Decoder` over the weights of a Llama-family GGUF file; with `group` / `comm` this rank's
     tensor-parallel share (see decoder.Decoder)."""
     from . import tensor_parallel as tp
-    from .decoder import Decoder, DecoderShape
+    from .decoder import Decoder
 
     group = group or tp.Group()
     world, rank = group.world, group.rank
     with GgufFile(path, lib=ctx.lib) as f:
-        arch = f.meta_str("general.architecture", "llama")
-        n_heads = f.meta_int(f"{arch}.attention.head_count")
-        d = f.meta_int(f"{arch}.embedding_length")
-        emb = f.info(f.find("token_embd.weight"))
-        q0 = f.find("blk.0.attn_q.weight")  # without an explicit key length the query projection tells the head size
-        hd_default = int(f.info(q0)["dims"][1]) // n_heads if q0 >= 0 else d // n_heads
-        shape = DecoderShape(
-            layers=f.meta_int(f"{arch}.block_count"), d=d, ffn=f.meta_int(f"{arch}.feed_forward_length"),
-            n_heads=n_heads, n_kv_heads=f.meta_int(f"{arch}.attention.head_count_kv", n_heads),
-            head_dim=f.meta_int(f"{arch}.attention.key_length", hd_default), vocab=int(emb["dims"][1]),
-            rope_theta=f.meta_float(f"{arch}.rope.freq_base", 10000.0),
-            rms_eps=f.meta_float(f"{arch}.attention.layer_norm_rms_epsilon", 1e-5))
+        shape = decoder_shape_from_gguf(f)
         hd = shape.head_dim
         if world > 1 and (shape.n_heads % world or shape.n_kv_heads % world):
             raise ValueError("heads must divide over the ranks")

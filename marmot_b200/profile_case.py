@@ -14,34 +14,10 @@ import argparse
 
 import numpy as np
 
-from .runtime import BLOCK_BYTES, BLOCK_VALUES, KIND_BY_NAME, KIND_Q4_K, KIND_Q6_K, Context, row_bytes
+from .runtime import KIND_BY_NAME, KIND_Q4_K, KIND_Q6_K, Context, row_bytes
+from .synthetic import synthetic_blocks, synthetic_blocks_device
 
 REGIMES = {"auto": 0, "gemv": 1, "gemm": 2, "gemv_plain": 3}
-
-
-def synthetic_blocks(kind: int, rows: int, K: int, rng: np.random.Generator) -> np.ndarray:
-    """Random block payloads with finite fp16 scales (0x1C00..0x1FFF is roughly 0.004..0.008)."""
-    nb = (K + BLOCK_VALUES[kind] - 1) // BLOCK_VALUES[kind]
-    blocks = rng.integers(0, 256, (rows * nb, BLOCK_BYTES[kind]), dtype=np.uint8)
-    scale_hi = rng.integers(0x1C, 0x20, rows * nb, dtype=np.uint8)
-    if kind == KIND_Q4_K:
-        blocks[:, 1] = scale_hi
-        blocks[:, 3] = scale_hi
-    elif kind == KIND_Q6_K:
-        blocks[:, 209] = scale_hi
-    else:
-        blocks[:, 1] = scale_hi
-    return blocks.reshape(-1)
-
-
-def synthetic_blocks_device(torch, kind: int, rows: int, K: int, device, generator=None):
-    """The same on the GPU (a uint8 tensor), for weights too large to draw on the host in reasonable time."""
-    nb = (K + BLOCK_VALUES[kind] - 1) // BLOCK_VALUES[kind]
-    blocks = torch.randint(0, 256, (rows * nb, BLOCK_BYTES[kind]), dtype=torch.uint8, device=device, generator=generator)
-    scale_hi = torch.randint(0x1C, 0x20, (rows * nb,), dtype=torch.uint8, device=device, generator=generator)
-    for col in ((1, 3) if kind == KIND_Q4_K else (209,) if kind == KIND_Q6_K else (1,)):
-        blocks[:, col] = scale_hi
-    return blocks.reshape(-1)
 
 
 def attention_case(args) -> None:

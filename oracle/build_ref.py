@@ -216,7 +216,22 @@ def build_kv_pool(ref_root: Path) -> Path:
     return KV_POOL_LIB
 
 
+def find_reference_root() -> Path | None:
+    """The marmot checkout to build from: $MARMOT_REFERENCE_ROOT, else a directory `reference` beside this
+    repository; None when neither holds a marmot source tree."""
+    cands = []
+    if os.environ.get("MARMOT_REFERENCE_ROOT"):
+        cands.append(Path(os.environ["MARMOT_REFERENCE_ROOT"]))
+    cands.append(Path(__file__).resolve().parent.parent.parent / "reference")
+    for c in cands:
+        if (c / "meson.build").exists() and (c / "include" / "marmot").is_dir():
+            return c
+    return None
+
+
 if __name__ == "__main__":
-    root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(os.environ.get("MARMOT_REFERENCE_ROOT", "/root/reference"))
+    root = Path(sys.argv[1]) if len(sys.argv) > 1 else find_reference_root()
+    if root is None:
+        sys.exit("no marmot checkout: pass its path or set MARMOT_REFERENCE_ROOT")
     print(build(root))
     print(build_kv_pool(root))

@@ -189,7 +189,11 @@ def make_kv_pool_traces() -> dict:
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(os.environ.get("MARMOT_REFERENCE_ROOT", "/root/reference"))
+    from oracle.build_ref import find_reference_root
+
+    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else find_reference_root()
+    if ref_root is None:
+        sys.exit("no marmot checkout: pass its path or set MARMOT_REFERENCE_ROOT")
     np.savez_compressed(HERE / "llama_goldens.npz", **dump_reference_goldens(ref_root))
     np.savez_compressed(HERE / "ref_cases.npz", **make_ref_cases())
     np.savez_compressed(HERE / "decoder_cases.npz", **make_decoder_cases())

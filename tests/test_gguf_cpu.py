@@ -60,3 +60,56 @@ def test_malformed_files_are_refused(tmp_path):
             GgufFile(p)
     with pytest.raises(MarmotCudaError):
         GgufFile(tmp_path / "absent.gguf")
+
+
+def test_crafted_directories_are_refused(tmp_path):
+    """Sizes in the tensor directory come from the file: products that wrap, rows that are not whole blocks and
+    odd alignments must be refused at open, before any row range is computed from them."""
+    blocks = random_blocks(KIND_Q4_K, 1, 256, np.random.default_rng(0))
+    cases = {
+        "wrapping_dims": dict(tensors=[("a.weight", GGML_Q4_K, (256, (1 << 56) + 1), blocks)]),
+        "huge_dims": dict(tensors=[("a.weight", GGML_Q4_K, (256, 1 << 50), blocks)]),
+        "partial_block_rows": dict(tensors=[("a.weight", GGML_Q4_K, (128, 2), blocks)]),
+        "odd_alignment": dict(tensors=[("a.weight", GGML_Q4_K, (256, 1), blocks)], alignment=48),
+        "huge_alignment": dict(tensors=[("a.weight", GGML_Q4_K, (256, 1), blocks)], alignment=1 << 30),
+    }
+    for name, kw in cases.items():
+        p = tmp_path / f"{name}.gguf"
+        meta = {"general.architecture": "llama"}
+        if name == "huge_alignment":  # written with a sane layout, the metadata value alone is absurd
+            meta["general.alignment"] = kw.pop("alignment")
+        write_gguf(p, meta, **kw)
+        with pytest.raises(MarmotCudaError):
+            GgufFile(p)
+    # an array whose byte length wraps
+    good = tmp_path / "arr.gguf"
+    write_gguf(good, {"general.architecture": "llama", "arr": np.arange(4, dtype=np.int32)},
+               [("a.weight", GGML_Q4_K, (256, 1), blocks)])
+    raw = bytearray(good.read_bytes())
+    at = raw.find(b"arr") + 3 + 4 + 4  # key, value type (array), element type
+    raw[at:at + 8] = struct.pack("<Q", (1 << 62) + 1)
+    bad = tmp_path / "arr_bad.gguf"
+    bad.write_bytes(bytes(raw))
+    with pytest.raises(MarmotCudaError):
+        GgufFile(bad)
+
+
+def test_unsupported_architectures_are_refused(tmp_path):
+    """A qwen2 / phi3 file has the same tensor names but another layer (half-split RoPE pairs, attention biases, q/k
+    norm); decoding it with the Llama layer would give wrong logits without any error, so the loader refuses it."""
+    from marmot_b200.gguf import decoder_shape_from_gguf
+
+    emb = random_blocks(KIND_Q4_K, 8, 256, np.random.default_rng(1))
+    for arch, ok in (("llama", True), ("mistral", True), ("qwen2", False), ("phi3", False), ("gemma", False), ("qwen3", False)):
+        p = tmp_path / f"{arch}.gguf"
+        write_gguf(p, {"general.architecture": arch, f"{arch}.block_count": 2, f"{arch}.embedding_length": 256,
+                       f"{arch}.feed_forward_length": 512, f"{arch}.attention.head_count": 4,
+                       f"{arch}.attention.head_count_kv": 2}, [("token_embd.weight", GGML_Q4_K, (256, 8), emb)])
+        with GgufFile(p) as f:
+            if ok:
+                shape = decoder_shape_from_gguf(f)
+                assert (shape.layers, shape.d, shape.ffn, shape.n_heads, shape.n_kv_heads, shape.head_dim, shape.vocab) == \
+                    (2, 256, 512, 4, 2, 64, 8)
+            else:
+                with pytest.raises(MarmotCudaError, match=arch):
+                    decoder_shape_from_gguf(f)

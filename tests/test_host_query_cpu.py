@@ -11,7 +11,18 @@ from pathlib import Path
 import pytest
 
 REPO = Path(__file__).resolve().parents[1]
-MARMOT = Path(os.environ.get("MARMOT_SOURCE_DIR", "/root/reference"))
+
+
+def _marmot_checkout() -> Path:
+    """$MARMOT_SOURCE_DIR, else the checkout the oracle recipes find; a path that does not exist when there is none."""
+    if os.environ.get("MARMOT_SOURCE_DIR"):
+        return Path(os.environ["MARMOT_SOURCE_DIR"])
+    from oracle.build_ref import find_reference_root
+
+    return find_reference_root() or REPO / "no-marmot-checkout"
+
+
+MARMOT = _marmot_checkout()
 PKG = REPO / "marmot_b200"
 
 

@@ -18,7 +18,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("kind", [KIND_Q4_K, KIND_Q6_K, KIND_Q8_0])
-def test_static_scratch_matches_mcu_linear_on_two_calls(kind):
+def test_static_scratch_matches_mcu_linear_on_two_calls(kind, oracle):
     import torch
 
     if not torch.cuda.is_available():
@@ -32,9 +32,12 @@ def test_static_scratch_matches_mcu_linear_on_two_calls(kind):
     rng = np.random.default_rng(kind)
     # second call: fewer tokens and a shorter, ragged K, so stale bytes of the first call stay in the array
     for T, K, F in [(5, 4096, 200), (2, 1000, 64)]:
-        W = ctx.upload(random_blocks(kind, F, K, rng))
-        x = torch.from_numpy(rng.normal(0, 1, (T, K)).astype(np.float32)).cuda()
-        bias = torch.from_numpy(rng.normal(0, 1, F).astype(np.float32)).cuda()
+        W_host = random_blocks(kind, F, K, rng)
+        W = ctx.upload(W_host)
+        x_host = rng.normal(0, 1, (T, K)).astype(np.float32)
+        bias_host = rng.normal(0, 1, F).astype(np.float32)
+        x = torch.from_numpy(x_host).cuda()
+        bias = torch.from_numpy(bias_host).cuda()
         out = torch.full((T, F), float("nan"), dtype=torch.float32, device="cuda")
         rc = lib.mcu_linear_static_scratch(stream, kind, x.data_ptr(), K, W.data_ptr(), T, K, F, bias.data_ptr(),
                                            out.data_ptr(), F)
@@ -42,6 +45,8 @@ def test_static_scratch_matches_mcu_linear_on_two_calls(kind):
         got = out.cpu().numpy()
         ref = ctx.linear(kind, x, W, F, bias=bias).cpu().numpy()
         assert max_rel_err(got, ref) <= TOL_FP32
+        # and directly against the CPU oracle of the reference's arithmetic
+        assert max_rel_err(got, oracle.linear(kind, x_host, W_host, F, bias=bias_host)) <= TOL_FP32
         # same kernels as the context's plain decode path: identical bits
         ctx.set_regime(REGIME_GEMV_PLAIN)
         plain = ctx.linear(kind, x, W, F, bias=bias).cpu().numpy()

@@ -4,6 +4,8 @@ from __future__ import annotations
 
 import numpy as np
 
+from marmot_b200.synthetic import random_blocks  # noqa: F401  (the tests draw their weights with the product generator)
+
 KIND_Q8_0, KIND_Q4_K, KIND_Q6_K = 5, 9, 11
 KINDS = {"q4_k": KIND_Q4_K, "q6_k": KIND_Q6_K, "q8_0": KIND_Q8_0}
 BLOCK_VALUES = {KIND_Q8_0: 32, KIND_Q4_K: 256, KIND_Q6_K: 256}
@@ -39,30 +41,6 @@ def cosine(a: np.ndarray, b: np.ndarray) -> float:
     a = np.asarray(a, dtype=np.float64).ravel()
     b = np.asarray(b, dtype=np.float64).ravel()
     return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-300))
-
-
-def random_blocks(kind: int, rows: int, K: int, rng: np.random.Generator, d_sigma: float | None = None) -> np.ndarray:
-    """Synthetic weights drawn directly in block space (every bit pattern of the payload is legal):
-    fp16 d / dmin = |N(0, sigma)|, 6-bit scales/mins uniform, quants uniform."""
-    bv, bb = BLOCK_VALUES[kind], BLOCK_BYTES[kind]
-    nb = (K + bv - 1) // bv
-    n = rows * nb
-    out = np.empty((n, bb), dtype=np.uint8)
-    if kind == KIND_Q4_K:
-        sigma = 0.02 if d_sigma is None else d_sigma
-        out[:, 0:2] = np.abs(rng.normal(0, sigma, n)).astype(np.float16).view(np.uint8).reshape(n, 2)
-        out[:, 2:4] = np.abs(rng.normal(0, sigma, n)).astype(np.float16).view(np.uint8).reshape(n, 2)
-        out[:, 4:] = rng.integers(0, 256, (n, 140), dtype=np.uint8)  # scales (6-bit fields) + nibbles
-    elif kind == KIND_Q6_K:
-        sigma = 0.002 if d_sigma is None else d_sigma
-        out[:, :192] = rng.integers(0, 256, (n, 192), dtype=np.uint8)
-        out[:, 192:208] = rng.integers(-64, 64, (n, 16)).astype(np.int8).view(np.uint8)
-        out[:, 208:210] = np.abs(rng.normal(0, sigma, n)).astype(np.float16).view(np.uint8).reshape(n, 2)
-    else:
-        sigma = 0.01 if d_sigma is None else d_sigma
-        out[:, 0:2] = np.abs(rng.normal(0, sigma, n)).astype(np.float16).view(np.uint8).reshape(n, 2)
-        out[:, 2:] = rng.integers(-127, 128, (n, 32)).astype(np.int8).view(np.uint8)
-    return out.reshape(-1)
 
 
 def unpack_q8_k(blocks: np.ndarray, T: int, nb: int):
