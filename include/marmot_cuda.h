@@ -371,6 +371,24 @@ int mcu_moe_experts_local(
     float weights_scale, int router_weight_policy, float *out_dev
 );
 
+/* The intermediate results of the context's last mcu_moe_experts / mcu_moe_experts_local call, for checking the
+ * operator stage by stage: device pointers into the context's workspace, valid until the next MoE call on the
+ * context (synchronize first).  Rows are in sorted-route order (expert-major, then route order): sorted_tok[r] is the
+ * token of sorted route r, offsets[e] .. offsets[e+1] are expert e's rows.  gate_out holds the gate projection where
+ * the GLU is applied by the consumer of the down projection (T * k >= 256), act(gate) * up otherwise. */
+typedef struct mcu_moe_buffers {
+    const int32_t *offsets;     /* [E + 1] */
+    const int32_t *sorted_tok;  /* [routes] */
+    const float *sorted_w;      /* [routes] normalised router weights */
+    const int32_t *route_pos;   /* [T * k] sorted position of every route, -1 for a rejected expert id */
+    const float *gate_out;      /* [routes][FF] */
+    const float *up_out;        /* [routes][FF] */
+    const float *route_down;    /* [routes][H] */
+    size_t routes, experts;
+    int grouped;                /* 1 when the grouped launches ran (gate_out is then the plain gate projection) */
+} mcu_moe_buffers_t;
+int mcu_moe_last_buffers(mcu_context_t *ctx, mcu_moe_buffers_t *out);
+
 /* Peer communicator: a staging buffer per rank, mapped into the other ranks (one process per GPU, CUDA IPC),
  * and a one-shot all-reduce(sum) kernel over peer loads with a fixed summation order (rank 0 first), so all
  * ranks obtain bit-identical results.  Set-up: every rank creates a communicator, exports its 64-byte handle,

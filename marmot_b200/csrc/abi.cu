@@ -81,6 +81,8 @@ struct mcu_context {
     Buffer attn_partial;         // split-KV partial attention states
     int *gemm_counters = nullptr;  // split-K tile tickets (zero between launches)
     std::vector<int> host_counts;
+    size_t moe_last_routes = 0, moe_last_experts = 0;  // shape of the last MoE call (mcu_moe_last_buffers)
+    int moe_last_grouped = 0;
     int *dev_err = nullptr;  // set by kernels whose bounded device-side waits ran out
 };
 
@@ -714,6 +716,9 @@ static int moe_experts_impl(mcu_context_t *ctx, int gate_kind, int up_kind, int 
     rb.sorted_w = (float *)(rb.sorted_tok + routes);
     rb.route_pos = (int32_t *)(rb.sorted_w + routes);
     cudaStream_t s = ctx->stream;
+    ctx->moe_last_routes = routes;
+    ctx->moe_last_experts = E;
+    ctx->moe_last_grouped = 0;
     const int renorm = router_weight_policy == MCU_ROUTER_RENORMALIZE_SELECTED;
     MCU_CUDA(launch_moe_route(topk_ids_dev, topk_weights_dev, (int)T, (int)k, (int)E, weights_scale, renorm, rb, s));
     count_launches(3);
@@ -759,6 +764,7 @@ static int moe_experts_impl(mcu_context_t *ctx, int gate_kind, int up_kind, int 
         MCU_CUDA(launch_moe_combine_dev(route_down, rb.sorted_w, rb.route_pos, (int)T, (int)k, (int)H, rb.offsets,
                                         (int)e_begin, (int)(e_begin + e_count), rb.counts + E, ctx->dev_err, out_dev, H, s));
         count_launches(6);
+        ctx->moe_last_grouped = 1;
         return MCU_SUCCESS;
     }
     if (stream_is_capturing(s))
@@ -799,6 +805,27 @@ static int moe_experts_impl(mcu_context_t *ctx, int gate_kind, int up_kind, int 
     MCU_CUDA(launch_moe_combine(route_down, rb.sorted_w, rb.route_pos, (int)T, (int)k, (int)H, pos_lo, pos_hi, out_dev, H,
                                 s));
     count_launches(1);
+    return MCU_SUCCESS;
+}
+
+int mcu_moe_last_buffers(mcu_context_t *ctx, mcu_moe_buffers_t *out) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (out == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "null output");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (ctx->moe_last_routes == 0 || ctx->moe_meta.ptr == nullptr)
+        return fail(MCU_ERROR_INVALID_OPERATION, "no MoE call has run on this context");
+    const size_t E = ctx->moe_last_experts, routes = ctx->moe_last_routes;
+    const int *counts = (const int *)ctx->moe_meta.ptr;
+    out->offsets = counts + (E + 1);
+    out->sorted_tok = (const int32_t *)(out->offsets + (E + 1));
+    out->sorted_w = (const float *)(out->sorted_tok + routes);
+    out->route_pos = (const int32_t *)(out->sorted_w + routes);
+    out->gate_out = (const float *)ctx->moe_gate.ptr;
+    out->up_out = (const float *)ctx->moe_up.ptr;
+    out->route_down = (const float *)ctx->moe_down.ptr;
+    out->routes = routes;
+    out->experts = E;
+    out->grouped = ctx->moe_last_grouped;
     return MCU_SUCCESS;
 }
 

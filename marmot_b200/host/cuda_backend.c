@@ -21,6 +21,7 @@
 // an offset inside the mirror of the enclosing range.
 #include "marmot/device.h"
 #include "marmot/error.h"
+#include "marmot/ops/paged_attention.h"
 #include "marmot/ops_types.h"
 #include "marmot/tensor.h"
 #include "marmot/types.h"
@@ -43,6 +44,7 @@ typedef struct {
     uintptr_t host;  // start of the host range
     size_t bytes;
     void *dev;
+    bool dirty;  // an operator wrote the device copy and the host copy has not been refreshed since
 } cuda_mirror_t;
 
 typedef struct cuda_ctx {
@@ -51,6 +53,10 @@ typedef struct cuda_ctx {
     cuda_mirror_t *mirrors;  // sorted by host address, ranges never overlap
     size_t n_mirrors, cap_mirrors;
     size_t bytes_resident;
+    // graph_batch_begin / graph_batch_end (include/marmot/device.h:57-60)
+    int batch_depth;
+    bool batch_capture;    // MARMOT_CUDA_GRAPH_BATCH=capture: a batch is recorded into a CUDA graph and launched at its end
+    bool capture_open;
 } cuda_ctx_t;
 
 static marmot_error_t cuda_fail(int rc) {
@@ -80,9 +86,14 @@ static cuda_mirror_t *mirror_find(cuda_ctx_t *c, uintptr_t addr, size_t bytes) {
     return nullptr;
 }
 
-static void mirror_drop_overlapping(cuda_ctx_t *c, uintptr_t addr, size_t bytes) {
+// Drops the mirrors that overlap [addr, addr + bytes).  With `write_back` a mirror whose device copy is the current
+// one is first copied to its host range (a larger operand is about to replace it and will be uploaded from there);
+// without, the host memory itself is going away.
+static void mirror_drop_overlapping(cuda_ctx_t *c, uintptr_t addr, size_t bytes, bool write_back) {
     size_t i = mirror_lower_bound(c, addr);
     while (i < c->n_mirrors && c->mirrors[i].host < addr + bytes) {
+        if (write_back && c->mirrors[i].dirty)
+            (void)mcu_memcpy_to_host(c->mcu, (void *)c->mirrors[i].host, c->mirrors[i].dev, c->mirrors[i].bytes);
         mcu_free(c->mcu, c->mirrors[i].dev);
         c->bytes_resident -= c->mirrors[i].bytes;
         memmove(&c->mirrors[i], &c->mirrors[i + 1], (c->n_mirrors - i - 1) * sizeof(cuda_mirror_t));
@@ -100,7 +111,13 @@ static marmot_error_t mirror_get(cuda_ctx_t *c, const void *host, size_t bytes, 
         *dev_out = (uint8_t *)m->dev + (addr - m->host);
         return MARMOT_SUCCESS;
     }
-    mirror_drop_overlapping(c, addr, bytes);
+    if (c->capture_open) {
+        marmot_set_error(MARMOT_ERROR_INVALID_OPERATION,
+                         "CUDA graph batch: an operand is not resident; make tensors resident (marmot_tensor_to_device) "
+                         "and run the program once before a captured batch");
+        return MARMOT_ERROR_INVALID_OPERATION;
+    }
+    mirror_drop_overlapping(c, addr, bytes, true);
     if (c->n_mirrors == c->cap_mirrors) {
         const size_t cap = c->cap_mirrors == 0 ? 64 : c->cap_mirrors * 2;
         cuda_mirror_t *grown = realloc(c->mirrors, cap * sizeof(cuda_mirror_t));
@@ -116,7 +133,7 @@ static marmot_error_t mirror_get(cuda_ctx_t *c, const void *host, size_t bytes, 
     if (rc != 0) return cuda_fail(rc);
     const size_t at = mirror_lower_bound(c, addr);
     memmove(&c->mirrors[at + 1], &c->mirrors[at], (c->n_mirrors - at) * sizeof(cuda_mirror_t));
-    c->mirrors[at] = (cuda_mirror_t){.host = addr, .bytes = bytes, .dev = dev};
+    c->mirrors[at] = (cuda_mirror_t){.host = addr, .bytes = bytes, .dev = dev, .dirty = false};
     c->n_mirrors++;
     c->bytes_resident += bytes;
     *created = true;
@@ -138,6 +155,11 @@ static marmot_error_t resident_ro(cuda_ctx_t *c, const marmot_tensor_t *t, size_
     marmot_error_t st = mirror_get(c, t->data, bytes, &created, &d);
     if (st != MARMOT_SUCCESS) return st;
     if (created || t->memory_location != MARMOT_MEMORY_DEVICE) {
+        if (c->capture_open) {
+            marmot_set_error(MARMOT_ERROR_INVALID_OPERATION, "CUDA graph batch: an operand's host copy is newer than its "
+                                                             "device copy; upload it before the batch");
+            return MARMOT_ERROR_INVALID_OPERATION;
+        }
         const int rc = mcu_memcpy_to_device(c->mcu, d, t->data, bytes);
         if (rc != 0) return cuda_fail(rc);
         // the two copies are now equal; like the CPU backend's pack caches this bookkeeping is not part of the
@@ -155,6 +177,8 @@ static marmot_error_t resident_rw(cuda_ctx_t *c, marmot_tensor_t *t, size_t byte
     bool created = false;
     marmot_error_t st = mirror_get(c, t->data, bytes, &created, dev);
     if (st != MARMOT_SUCCESS) return st;
+    cuda_mirror_t *m = mirror_find(c, (uintptr_t)t->data, bytes);
+    if (m != nullptr) m->dirty = true;
     t->memory_location = MARMOT_MEMORY_DEVICE;
     t->needs_sync = true;  // marmot_tensor_to_host() will fetch it (src/core/tensor/transfer.c:36-62)
     return MARMOT_SUCCESS;
@@ -178,6 +202,8 @@ static marmot_error_t cuda_init(void **device_ctx) {
         return cuda_fail(rc);
     }
     pthread_mutex_init(&c->mu, nullptr);
+    const char *batch = getenv("MARMOT_CUDA_GRAPH_BATCH");
+    c->batch_capture = batch != nullptr && strcmp(batch, "capture") == 0;
     *device_ctx = c;
     return MARMOT_SUCCESS;
 }
@@ -185,6 +211,10 @@ static marmot_error_t cuda_init(void **device_ctx) {
 static void cuda_destroy(const void *device_ctx) {
     cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
     if (c == nullptr) return;
+    if (c->capture_open) {  // a batch that was never ended: drop the recording before anything else touches the stream
+        (void)mcu_graph_capture_end(c->mcu, nullptr);
+        c->capture_open = false;
+    }
     mcu_synchronize(c->mcu);
     for (size_t i = 0; i < c->n_mirrors; ++i) mcu_free(c->mcu, c->mirrors[i].dev);
     free(c->mirrors);
@@ -222,6 +252,8 @@ static marmot_error_t cuda_memcpy_to_device(const void *device_ctx, void *dst, c
     if (st == MARMOT_SUCCESS) {
         const int rc = mcu_memcpy_to_device(c->mcu, d, src, size);
         if (rc != 0) st = cuda_fail(rc);
+        cuda_mirror_t *m = mirror_find(c, (uintptr_t)dst, size);
+        if (rc == 0 && m != nullptr && (uintptr_t)dst == m->host && size == m->bytes) m->dirty = false;
     }
     pthread_mutex_unlock(&c->mu);
     return st;
@@ -237,6 +269,7 @@ static marmot_error_t cuda_memcpy_from_device(const void *device_ctx, void *dst,
     if (m != nullptr) {
         const int rc = mcu_memcpy_to_host(c->mcu, dst, (const uint8_t *)m->dev + ((uintptr_t)src - m->host), size);
         if (rc != 0) st = cuda_fail(rc);
+        else if (dst == src && (uintptr_t)src == m->host && size == m->bytes) m->dirty = false;
     } else {
         const int rc = mcu_synchronize(c->mcu);  // nothing resident for this range: the host copy is the only one
         if (rc != 0) st = cuda_fail(rc);
@@ -265,11 +298,62 @@ static void cuda_on_host_range_freed(void *device_ctx, const void *start, size_t
     cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
     if (c == nullptr || start == nullptr) return;
     pthread_mutex_lock(&c->mu);
-    mirror_drop_overlapping(c, (uintptr_t)start, length > 0 ? length : 1);
+    mirror_drop_overlapping(c, (uintptr_t)start, length > 0 ? length : 1, false);
     pthread_mutex_unlock(&c->mu);
 }
 
 static void cuda_on_host_ptr_freed(void *device_ctx, const void *ptr) { cuda_on_host_range_freed(device_ctx, ptr, 1); }
+
+// Graph batching (include/marmot/device.h:57-60; the graph executor brackets every bytecode program with these,
+// src/graph/graph_executor.cpp:770,932).  Operators already only enqueue work on the context's stream, so by default
+// a batch needs nothing at its start; at its end a failed program (commit == false) waits for the device so that
+// whatever was enqueued has finished - and a device-side error has surfaced - before the caller reuses the tensors.
+// With MARMOT_CUDA_GRAPH_BATCH=capture the outermost batch is recorded into a CUDA graph instead (mcu_graph_capture_*)
+// and launched once at its end: every operand must then be resident and the workspace warm (run the program once
+// unbatched first), since uploads and allocations cannot be recorded; an operator that needs either fails the batch.
+static marmot_error_t cuda_graph_batch_begin(void *device_ctx) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    pthread_mutex_lock(&c->mu);
+    marmot_error_t st = MARMOT_SUCCESS;
+    if (c->batch_depth == 0 && c->batch_capture) {
+        const int rc = mcu_graph_capture_begin(c->mcu);
+        if (rc != 0) st = cuda_fail(rc);
+        else c->capture_open = true;
+    }
+    if (st == MARMOT_SUCCESS) c->batch_depth++;
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
+
+static marmot_error_t cuda_graph_batch_end(void *device_ctx, bool commit) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    pthread_mutex_lock(&c->mu);
+    marmot_error_t st = MARMOT_SUCCESS;
+    if (c->batch_depth <= 0) {
+        marmot_set_error(MARMOT_ERROR_INVALID_OPERATION, "graph_batch_end without graph_batch_begin");
+        st = MARMOT_ERROR_INVALID_OPERATION;
+    } else if (--c->batch_depth == 0) {
+        if (c->capture_open) {
+            c->capture_open = false;
+            mcu_graph_t *graph = nullptr;
+            int rc = mcu_graph_capture_end(c->mcu, commit ? &graph : nullptr);
+            if (rc == 0 && graph != nullptr) {
+                rc = mcu_graph_launch(graph);
+                const int rc_sync = mcu_synchronize(c->mcu);  // the graph must not be destroyed while it runs
+                if (rc == 0) rc = rc_sync;
+                mcu_graph_destroy(graph);
+            }
+            if (rc != 0) st = cuda_fail(rc);
+        } else if (!commit) {
+            const int rc = mcu_synchronize(c->mcu);
+            if (rc != 0) st = cuda_fail(rc);
+        }
+    }
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
 
 static const marmot_device_ops_t g_cuda_ops = {
     .init = cuda_init,
@@ -281,8 +365,8 @@ static const marmot_device_ops_t g_cuda_ops = {
     .memcpy_from_device = cuda_memcpy_from_device,
     .synchronize = cuda_synchronize,
     .allocator_usage = cuda_allocator_usage,
-    .graph_batch_begin = nullptr,
-    .graph_batch_end = nullptr,
+    .graph_batch_begin = cuda_graph_batch_begin,
+    .graph_batch_end = cuda_graph_batch_end,
     .on_host_ptr_freed = cuda_on_host_ptr_freed,
     .on_host_range_freed = cuda_on_host_range_freed,
 };
@@ -387,6 +471,20 @@ marmot_error_t cuda_matmul_quantized_q8_0(
     const marmot_matmul_epilogue_t *epilogue, marmot_tensor_t *out
 ) {
     return cuda_matmul_quantized(device_ctx, input, weight, nullptr, epilogue, out, nullptr, MARMOT_QUANT_KIND_Q8_0);
+}
+
+// The handler the generated `marmot_cuda_matmul_*_exec` wrappers call (scripts/codegen/templates/backend_dispatch.j2
+// routes every quantized matmul entry of a backend to its one `matmul_quantized` handler): the block format comes
+// from the weight tensor.
+marmot_error_t cuda_matmul_quantized_any(
+    const void *device_ctx, const marmot_tensor_t *input, const marmot_tensor_t *weight,
+    const marmot_matmul_epilogue_t *epilogue, marmot_tensor_t *out
+) {
+    if (weight == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "Tensor argument must not be null");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    return cuda_matmul_quantized(device_ctx, input, weight, nullptr, epilogue, out, nullptr, weight->quant_kind);
 }
 
 marmot_error_t cuda_matmul_quantized_dual_output(
@@ -584,6 +682,20 @@ marmot_error_t cuda_dequantize_q8_0(const void *device_ctx, const marmot_tensor_
     return cuda_dequantize_blockwise(device_ctx, MCU_KIND_Q8_0, input, output);
 }
 
+// The unified dequantize handler of the generated dispatch (the same shape as metal_dequantize_dispatch).
+marmot_error_t cuda_dequantize_dispatch(
+    const void *device_ctx, marmot_quant_kind_t kind, marmot_quant_layout_t layout, const marmot_tensor_t *input,
+    marmot_tensor_t *output
+) {
+    (void)layout;
+    const int k = mcu_kind_of(kind);
+    if (k < 0) {
+        marmot_set_error(MARMOT_ERROR_NOT_IMPLEMENTED, "CUDA dequantize: block format has no kernel (Q4_K, Q6_K, Q8_0 do)");
+        return MARMOT_ERROR_NOT_IMPLEMENTED;
+    }
+    return cuda_dequantize_blockwise(device_ctx, k, input, output);
+}
+
 // ---- quantized row dot (the public marmot_vec_dot; host pointers, as in the reference) ----------------
 // num_blocks counts 32-value blocks in the descriptor's convention for Q8_0 activations and 256-value super-blocks for
 // Q8_K ones, exactly what cpu_vec_dot hands to its dot kernels (src/backends/cpu/ops/vec_dot/vec_dot.c:52-62).
@@ -619,6 +731,281 @@ marmot_error_t cuda_vec_dot(const void *device_ctx, const marmot_vec_dot_descrip
     return rc == 0 ? MARMOT_SUCCESS : cuda_fail(rc);
 }
 
+// ---- decoder operators around the matmuls ---------------------------------------------------------------------
+// Adapters from marmot's descriptors to the C ABI's decoder kernels (mcu_rmsnorm, mcu_rope, mcu_swiglu, mcu_add,
+// mcu_embedding_gather, mcu_paged_attention).  FLOAT32 activations, the shapes the graph builder emits for a
+// Llama-family layer (src/graph/gguf/graph_builder.cpp:1454-2400); anything else is refused, never computed on
+// the host.  Reference counterparts: cpu_rmsnorm_impl / cpu_rmsnorm_gemma_impl
+// (src/backends/cpu/ops/normalization/normalization.c:240-246), cpu_rope (ops/rope/rope_dispatch.c:144-382),
+// cpu_elementwise_binary_impl (ops/elementwise), cpu_embedding_gather (ops/embedding), cpu_paged_attention_impl
+// (ops/paged_attention/paged_attention_ref.c).
+
+static bool cuda_is_dense_f32(const marmot_tensor_t *t) {
+    if (t == nullptr || t->dtype != MARMOT_DTYPE_FLOAT32 || t->shape.ndim == 0) return false;
+    size_t expect = 1;
+    for (size_t i = t->shape.ndim; i-- > 0;) {
+        if (t->shape.shape[i] != 1 && t->shape.strides[i] != expect) return false;
+        expect *= t->shape.shape[i];
+    }
+    return true;
+}
+
+static marmot_error_t cuda_rmsnorm_common(const void *device_ctx, const marmot_rmsnorm_desc_t *desc, float weight_offset) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) {
+        marmot_set_error(MARMOT_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+        return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    }
+    if (desc == nullptr || desc->x == nullptr || desc->out == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "RMSNorm descriptor is incomplete");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    const marmot_tensor_t *x = desc->x;
+    if (!cuda_is_dense_f32(x) || !cuda_is_dense_f32(desc->out) || (desc->residual != nullptr && !cuda_is_dense_f32(desc->residual)) ||
+        (desc->weight != nullptr && desc->weight->dtype != MARMOT_DTYPE_FLOAT32)) {
+        marmot_set_error(MARMOT_ERROR_UNSUPPORTED_DTYPE, "CUDA RMSNorm takes dense FLOAT32 tensors");
+        return MARMOT_ERROR_UNSUPPORTED_DTYPE;
+    }
+    const size_t n = x->shape.shape[x->shape.ndim - 1], total = marmot_tensor_num_elements(x);
+    if (n == 0 || marmot_tensor_num_elements(desc->out) != total ||
+        (desc->residual != nullptr && marmot_tensor_num_elements(desc->residual) != total) ||
+        (desc->weight != nullptr && marmot_tensor_num_elements(desc->weight) != n)) {
+        marmot_set_error(MARMOT_ERROR_DIMENSION_MISMATCH, "RMSNorm shapes do not match");
+        return MARMOT_ERROR_DIMENSION_MISMATCH;
+    }
+    pthread_mutex_lock(&c->mu);
+    const void *xd = nullptr, *rd = nullptr, *wd = nullptr;
+    void *od = nullptr;
+    marmot_error_t st = resident_ro(c, x, total * sizeof(float), &xd);
+    if (st == MARMOT_SUCCESS && desc->residual != nullptr) st = resident_ro(c, desc->residual, total * sizeof(float), &rd);
+    if (st == MARMOT_SUCCESS && desc->weight != nullptr) st = resident_ro(c, desc->weight, n * sizeof(float), &wd);
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, desc->out, total * sizeof(float), &od);
+    if (st == MARMOT_SUCCESS) {
+        const int rc = mcu_rmsnorm(c->mcu, xd, rd, wd, total / n, n, desc->eps, weight_offset, od);
+        if (rc != 0) st = cuda_fail(rc);
+    }
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
+
+marmot_error_t cuda_rmsnorm_impl(const void *device_ctx, const marmot_rmsnorm_desc_t *desc) {
+    return cuda_rmsnorm_common(device_ctx, desc, 0.0f);
+}
+
+marmot_error_t cuda_rmsnorm_gemma_impl(const void *device_ctx, const marmot_rmsnorm_desc_t *desc) {
+    return cuda_rmsnorm_common(device_ctx, desc, 1.0f);
+}
+
+// x [..., rows, dim]: every row is one head of one token and is rotated with the position of its row
+// (the graph reshapes q / k to [tokens * heads, head_dim] and repeats the positions, like the reference's callers).
+marmot_error_t cuda_rope(const void *device_ctx, const marmot_tensor_t *x, const marmot_rope_params_t *params, marmot_tensor_t *out) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) {
+        marmot_set_error(MARMOT_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+        return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    }
+    if (params == nullptr || params->positions == nullptr || x == nullptr || out == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "RoPE needs input, output and a positions tensor");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    if (!cuda_is_dense_f32(x) || !cuda_is_dense_f32(out) || params->positions->dtype != MARMOT_DTYPE_INT32) {
+        marmot_set_error(MARMOT_ERROR_UNSUPPORTED_DTYPE, "CUDA RoPE takes dense FLOAT32 tensors and INT32 positions");
+        return MARMOT_ERROR_UNSUPPORTED_DTYPE;
+    }
+    if (params->scaling_type != MARMOT_ROPE_SCALING_NONE && params->scaling_type != MARMOT_ROPE_SCALING_LINEAR) {
+        marmot_set_error(MARMOT_ERROR_NOT_IMPLEMENTED, "CUDA RoPE covers plain and linearly scaled frequencies only");
+        return MARMOT_ERROR_NOT_IMPLEMENTED;
+    }
+    if (params->rope_type != MARMOT_ROPE_TYPE_NORM && params->rope_type != MARMOT_ROPE_TYPE_NEOX) {
+        marmot_set_error(MARMOT_ERROR_NOT_IMPLEMENTED, "CUDA RoPE covers the NORM and NEOX pairings");
+        return MARMOT_ERROR_NOT_IMPLEMENTED;
+    }
+    if (x->shape.ndim < 2) {
+        marmot_set_error(MARMOT_ERROR_DIMENSION_MISMATCH, "RoPE requires at least 2D tensor");
+        return MARMOT_ERROR_DIMENSION_MISMATCH;
+    }
+    const size_t dim = x->shape.shape[x->shape.ndim - 1], total = marmot_tensor_num_elements(x);
+    if (dim == 0 || dim % 2 != 0 || total == 0 || marmot_tensor_num_elements(out) != total ||
+        marmot_tensor_num_elements(params->positions) != total / dim) {
+        marmot_set_error(MARMOT_ERROR_DIMENSION_MISMATCH, "RoPE shapes do not match");
+        return MARMOT_ERROR_DIMENSION_MISMATCH;
+    }
+    const size_t rows = total / dim;
+    const float freq_scale = params->scaling_type == MARMOT_ROPE_SCALING_LINEAR ? params->freq_scale : 1.0f;
+    pthread_mutex_lock(&c->mu);
+    const void *xd = nullptr, *pd = nullptr;
+    void *od = nullptr;
+    marmot_error_t st = resident_ro(c, x, total * sizeof(float), &xd);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, params->positions, rows * sizeof(int32_t), &pd);
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, out, total * sizeof(float), &od);
+    if (st == MARMOT_SUCCESS) {
+        const int rc = mcu_rope(c->mcu, xd, dim, pd, rows, 1, dim, params->theta, freq_scale,
+                                params->rope_type == MARMOT_ROPE_TYPE_NEOX ? MCU_ROPE_NEOX : MCU_ROPE_NORM, od, dim);
+        if (rc != 0) st = cuda_fail(rc);
+    }
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
+
+// add and swiglu (silu(a) * b) on dense FLOAT32 tensors of equal size.
+marmot_error_t cuda_elementwise_binary_impl(
+    const void *device_ctx, marmot_device_binary_op_t op, const marmot_tensor_t *a, const marmot_tensor_t *b,
+    marmot_tensor_t *out
+) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) {
+        marmot_set_error(MARMOT_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+        return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    }
+    if (op != MARMOT_DEVICE_BINARY_ADD && op != MARMOT_DEVICE_BINARY_SWIGLU) {
+        marmot_set_error(MARMOT_ERROR_NOT_IMPLEMENTED, "CUDA elementwise kernels: add and swiglu");
+        return MARMOT_ERROR_NOT_IMPLEMENTED;
+    }
+    if (a == nullptr || b == nullptr || out == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "Null tensor pointer");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    if (!cuda_is_dense_f32(a) || !cuda_is_dense_f32(b) || !cuda_is_dense_f32(out)) {
+        marmot_set_error(MARMOT_ERROR_UNSUPPORTED_DTYPE, "CUDA elementwise kernels take dense FLOAT32 tensors");
+        return MARMOT_ERROR_UNSUPPORTED_DTYPE;
+    }
+    const size_t n = marmot_tensor_num_elements(a);
+    if (marmot_tensor_num_elements(b) != n || marmot_tensor_num_elements(out) != n) {
+        marmot_set_error(MARMOT_ERROR_DIMENSION_MISMATCH, "elementwise operands must have equal sizes (no broadcasting)");
+        return MARMOT_ERROR_DIMENSION_MISMATCH;
+    }
+    if (n == 0) return MARMOT_SUCCESS;
+    pthread_mutex_lock(&c->mu);
+    const void *ad = nullptr, *bd = nullptr;
+    void *od = nullptr;
+    marmot_error_t st = resident_ro(c, a, n * sizeof(float), &ad);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, b, n * sizeof(float), &bd);
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, out, n * sizeof(float), &od);
+    if (st == MARMOT_SUCCESS) {
+        const int rc = op == MARMOT_DEVICE_BINARY_ADD ? mcu_add(c->mcu, ad, bd, n, od) : mcu_swiglu(c->mcu, ad, bd, n, od);
+        if (rc != 0) st = cuda_fail(rc);
+    }
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
+
+// Rows of a quantized table -> FLOAT32 (bit-exact with the dequantizers); INT32 token ids.
+marmot_error_t cuda_embedding_gather(const void *device_ctx, const marmot_embedding_gather_desc_t *desc) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) {
+        marmot_set_error(MARMOT_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+        return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    }
+    if (desc == nullptr || desc->weights == nullptr || desc->token_ids == nullptr || desc->out == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "Embedding descriptor is incomplete");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    const marmot_tensor_t *w = desc->weights;
+    const int kind = mcu_kind_of(w->quant_kind);
+    if (kind < 0 || w->shape.ndim != 2) {
+        marmot_set_error(MARMOT_ERROR_NOT_IMPLEMENTED, "CUDA embedding gather covers 2D Q4_K, Q6_K and Q8_0 tables");
+        return MARMOT_ERROR_NOT_IMPLEMENTED;
+    }
+    if (desc->token_ids->dtype != MARMOT_DTYPE_INT32 || !cuda_is_dense_f32(desc->out) ||
+        (desc->dtype_out != MARMOT_DTYPE_FLOAT32 && desc->dtype_out != MARMOT_DTYPE_COUNT)) {
+        marmot_set_error(MARMOT_ERROR_UNSUPPORTED_DTYPE, "CUDA embedding gather takes INT32 ids and writes FLOAT32");
+        return MARMOT_ERROR_UNSUPPORTED_DTYPE;
+    }
+    if (desc->scale != 1.0f && desc->scale != 0.0f) {
+        marmot_set_error(MARMOT_ERROR_NOT_IMPLEMENTED, "CUDA embedding gather does not scale its output");
+        return MARMOT_ERROR_NOT_IMPLEMENTED;
+    }
+    const size_t vocab = w->shape.shape[0], dim = w->shape.shape[1], T = marmot_tensor_num_elements(desc->token_ids);
+    if (marmot_tensor_num_elements(desc->out) != T * dim) {
+        marmot_set_error(MARMOT_ERROR_DIMENSION_MISMATCH, "Embedding output shape does not match");
+        return MARMOT_ERROR_DIMENSION_MISMATCH;
+    }
+    if (T == 0) return MARMOT_SUCCESS;
+    if (desc->bounds_check || desc->padding_id >= 0) {
+        // ids are host-visible when the caller asks for checks: reject what the kernel would read out of range
+        const int32_t *ids = (const int32_t *)desc->token_ids->data;
+        for (size_t i = 0; i < T; ++i) {
+            if (ids[i] < 0 || (size_t)ids[i] >= vocab || ids[i] == desc->padding_id) {
+                marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "Embedding token id out of range (padding ids are not supported on CUDA)");
+                return MARMOT_ERROR_INVALID_ARGUMENT;
+            }
+        }
+    }
+    pthread_mutex_lock(&c->mu);
+    const void *wd = nullptr, *id = nullptr;
+    void *od = nullptr;
+    marmot_error_t st = resident_ro(c, w, vocab * mcu_row_bytes(kind, dim), &wd);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, desc->token_ids, T * sizeof(int32_t), &id);
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, desc->out, T * dim * sizeof(float), &od);
+    if (st == MARMOT_SUCCESS) {
+        const int rc = mcu_embedding_gather(c->mcu, kind, wd, dim, id, T, od);
+        if (rc != 0) st = cuda_fail(rc);
+    }
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
+
+// Contract of include/marmot/ops/paged_attention.h:13-56; FLOAT32 q / k / v, FLOAT32 or FLOAT16 pools, no FP8 scales.
+marmot_error_t cuda_paged_attention_impl(const void *device_ctx, const marmot_paged_attention_desc_t *desc) {
+    cuda_ctx_t *c = (cuda_ctx_t *)device_ctx;
+    if (c == nullptr) {
+        marmot_set_error(MARMOT_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+        return MARMOT_ERROR_DEVICE_NOT_AVAILABLE;
+    }
+    if (desc == nullptr || desc->token_meta == nullptr || desc->q == nullptr || desc->k_new == nullptr || desc->v_new == nullptr ||
+        desc->kv_k == nullptr || desc->kv_v == nullptr || desc->block_table == nullptr || desc->out == nullptr) {
+        marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "Paged attention descriptor is incomplete");
+        return MARMOT_ERROR_INVALID_ARGUMENT;
+    }
+    if (desc->pnext != nullptr) {
+        marmot_set_error(MARMOT_ERROR_NOT_IMPLEMENTED, "CUDA paged attention has no FP8 pools with per-block scales");
+        return MARMOT_ERROR_NOT_IMPLEMENTED;
+    }
+    const marmot_dtype_t kv_dt = desc->kv_k->dtype;
+    if (!cuda_is_dense_f32(desc->q) || !cuda_is_dense_f32(desc->k_new) || !cuda_is_dense_f32(desc->v_new) ||
+        !cuda_is_dense_f32(desc->out) || (kv_dt != MARMOT_DTYPE_FLOAT32 && kv_dt != MARMOT_DTYPE_FLOAT16) ||
+        desc->kv_v->dtype != kv_dt || desc->token_meta->dtype != MARMOT_DTYPE_UINT32 ||
+        desc->block_table->dtype != MARMOT_DTYPE_UINT32) {
+        marmot_set_error(MARMOT_ERROR_UNSUPPORTED_DTYPE, "CUDA paged attention: FLOAT32 q/k/v, FLOAT32 or FLOAT16 pools, UINT32 tables");
+        return MARMOT_ERROR_UNSUPPORTED_DTYPE;
+    }
+    const size_t T = desc->token_count, hq = desc->num_q_heads, hkv = desc->num_kv_heads, hd = desc->head_dim, bs = desc->block_size;
+    if (desc->kv_k->shape.ndim != 5 || desc->block_table->shape.ndim != 2 || desc->token_meta->shape.ndim != 2 ||
+        desc->token_meta->shape.shape[0] < T || desc->token_meta->shape.shape[1] != 4 ||
+        marmot_tensor_num_elements(desc->q) < T * hq * hd || marmot_tensor_num_elements(desc->k_new) < T * hkv * hd ||
+        marmot_tensor_num_elements(desc->v_new) < T * hkv * hd || marmot_tensor_num_elements(desc->out) < T * hq * hd ||
+        desc->kv_k->shape.shape[2] != hkv || desc->kv_k->shape.shape[3] != bs || desc->kv_k->shape.shape[4] != hd ||
+        desc->layer_idx >= desc->kv_k->shape.shape[1]) {
+        marmot_set_error(MARMOT_ERROR_DIMENSION_MISMATCH, "Paged attention shapes do not match");
+        return MARMOT_ERROR_DIMENSION_MISMATCH;
+    }
+    if (T == 0) return MARMOT_SUCCESS;
+    const size_t pool_bytes = marmot_tensor_num_elements(desc->kv_k) * (kv_dt == MARMOT_DTYPE_FLOAT16 ? 2 : 4);
+    pthread_mutex_lock(&c->mu);
+    const void *md = nullptr, *qd = nullptr, *kd = nullptr, *vd = nullptr, *td = nullptr;
+    void *pk = nullptr, *pv = nullptr, *od = nullptr;
+    marmot_error_t st = resident_ro(c, desc->token_meta, T * 4 * sizeof(uint32_t), &md);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, desc->q, T * hq * hd * sizeof(float), &qd);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, desc->k_new, T * hkv * hd * sizeof(float), &kd);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, desc->v_new, T * hkv * hd * sizeof(float), &vd);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, desc->block_table, marmot_tensor_num_elements(desc->block_table) * sizeof(uint32_t), &td);
+    // the pools are read and written: current on the device first, then the device copy becomes the newer one
+    const void *tmp = nullptr;
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, desc->kv_k, pool_bytes, &tmp);
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, (marmot_tensor_t *)desc->kv_k, pool_bytes, &pk);
+    if (st == MARMOT_SUCCESS) st = resident_ro(c, desc->kv_v, pool_bytes, &tmp);
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, (marmot_tensor_t *)desc->kv_v, pool_bytes, &pv);
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, desc->out, T * hq * hd * sizeof(float), &od);
+    if (st == MARMOT_SUCCESS) {
+        const int rc = mcu_paged_attention(c->mcu, md, T, qd, kd, vd, pk, pv, kv_dt == MARMOT_DTYPE_FLOAT16 ? MCU_KV_F16 : MCU_KV_F32,
+                                           td, desc->block_table->shape.shape[1], desc->kv_k->shape.shape[1], desc->layer_idx, hq,
+                                           hkv, hd, bs, desc->scale, od);
+        if (rc != 0) st = cuda_fail(rc);
+    }
+    pthread_mutex_unlock(&c->mu);
+    return st;
+}
+
 // ---- kernel query, capabilities, preferences ----------------------------------------------------------
 // Reference counterparts: marmot_cpu_query_kernel / marmot_metal_query_kernel (generated, called from
 // src/core/dispatch/kernel_query.c:35-52), marmot_metal_detect_default_caps and marmot_*_default_preferences
@@ -626,8 +1013,11 @@ marmot_error_t cuda_vec_dot(const void *device_ctx, const marmot_vec_dot_descrip
 // answered with supported = false here, at query time: nothing is ever computed on the host instead
 // (src/core/dispatch/dispatch_execute.c:214-233 would otherwise look for an unfused fallback).
 //
-// The kernel ids below continue marmot's generated enumeration (include/marmot/traits_ids.gen.h); the codegen
-// assigns the real values when it emits the CUDA tables from the .def files, in this order.
+#if !defined(MARMOT_CUDA_GENERATED_QUERY)
+// Inside a marmot build the query is GENERATED from kernels/*.def by scripts/codegen/gen_kernels.py (build_marmot.py
+// compiles this file with MARMOT_CUDA_GENERATED_QUERY); the function below serves the stand-alone host library, which
+// is built against an unmodified marmot whose enumeration has no CUDA entries: its kernel ids continue marmot's
+// generated enumeration (include/marmot/traits_ids.gen.h) and it answers for the same operators as the .def files.
 enum {
     CUDA_KERNEL_MATMUL_Q4_K_F32_NT = MARMOT_KERNEL_COUNT,
     CUDA_KERNEL_MATMUL_Q6_K_F32_NT,
@@ -639,17 +1029,6 @@ enum {
     CUDA_KERNEL_DEQUANTIZE_Q4_K,
     CUDA_KERNEL_DEQUANTIZE_Q6_K,
     CUDA_KERNEL_DEQUANTIZE_Q8_0,
-    CUDA_KERNEL_EMBEDDING_Q4_K,
-    CUDA_KERNEL_EMBEDDING_Q6_K,
-    CUDA_KERNEL_EMBEDDING_Q8_0,
-    CUDA_KERNEL_RMS_NORM_F32,
-    CUDA_KERNEL_RMS_NORM_GEMMA_F32,
-    CUDA_KERNEL_ROPE_F32,
-    CUDA_KERNEL_ADD_F32,
-    CUDA_KERNEL_SWIGLU_F32,
-    CUDA_KERNEL_PAGED_ATTENTION_F32_KV_F32,
-    CUDA_KERNEL_PAGED_ATTENTION_F32_KV_F16,
-    CUDA_KERNEL_ARGMAX_F32,
     CUDA_KERNEL_END,
 };
 
@@ -731,39 +1110,12 @@ marmot_kernel_selection_t marmot_cuda_query_kernel(const marmot_op_signature_t *
         if (slot < 0 || sig->output_dtype != MARMOT_DTYPE_FLOAT32)
             return cuda_unsupported("CUDA dequantize covers Q4_K, Q6_K and Q8_0 to FLOAT32");
         return cuda_supported(CUDA_KERNEL_DEQUANTIZE_Q4_K + slot, caps, 4.0 * sig->dims.elementwise.n_elems, 0.0, 0.0);
-    case MARMOT_OP_EMBEDDING:
-        if (slot < 0 || sig->output_dtype != MARMOT_DTYPE_FLOAT32)
-            return cuda_unsupported("CUDA embedding gather covers Q4_K, Q6_K and Q8_0 tables to FLOAT32");
-        return cuda_supported(CUDA_KERNEL_EMBEDDING_Q4_K + slot, caps, 0.0, 0.0, 0.0);
-    case MARMOT_OP_RMS_NORM:
-    case MARMOT_OP_RMS_NORM_GEMMA:
-        if (!f32_io) return cuda_unsupported("CUDA RMSNorm is FLOAT32");
-        return cuda_supported(sig->op_id == MARMOT_OP_RMS_NORM ? CUDA_KERNEL_RMS_NORM_F32 : CUDA_KERNEL_RMS_NORM_GEMMA_F32,
-                              caps, 8.0 * sig->dims.layernorm.n * sig->dims.layernorm.d, 0.0, 0.0);
-    case MARMOT_OP_ROPE:
-        if (!f32_io) return cuda_unsupported("CUDA RoPE is FLOAT32");
-        return cuda_supported(CUDA_KERNEL_ROPE_F32, caps, 0.0, 0.0, 0.0);
-    case MARMOT_OP_ADD:
-    case MARMOT_OP_SWIGLU:
-        if (!f32_io) return cuda_unsupported("CUDA elementwise kernels are FLOAT32");
-        if (sig->stride_mode != MARMOT_STRIDE_MODE_ANY && sig->stride_mode != MARMOT_STRIDE_MODE_CONTIGUOUS)
-            return cuda_unsupported("CUDA elementwise kernels take contiguous tensors");
-        return cuda_supported(sig->op_id == MARMOT_OP_ADD ? CUDA_KERNEL_ADD_F32 : CUDA_KERNEL_SWIGLU_F32, caps,
-                              12.0 * sig->dims.elementwise.n_elems, 0.0, 0.0);
-    case MARMOT_OP_PAGED_ATTENTION:
-        if (!f32_io) return cuda_unsupported("CUDA paged attention takes FLOAT32 q/k/v");
-        if (sig->weight_dtype == MARMOT_DTYPE_FLOAT16)
-            return cuda_supported(CUDA_KERNEL_PAGED_ATTENTION_F32_KV_F16, caps, 0.0, 0.0, 0.0);
-        if (sig->weight_dtype == MARMOT_DTYPE_FLOAT32)
-            return cuda_supported(CUDA_KERNEL_PAGED_ATTENTION_F32_KV_F32, caps, 0.0, 0.0, 0.0);
-        return cuda_unsupported("CUDA paged attention KV pool must be FLOAT32 or FLOAT16");
-    case MARMOT_OP_REDUCTION_ARGMAX:
-        if (sig->input_dtype != MARMOT_DTYPE_FLOAT32) return cuda_unsupported("CUDA argmax is FLOAT32");
-        return cuda_supported(CUDA_KERNEL_ARGMAX_F32, caps, 0.0, 0.0, 0.0);
     default:
         return cuda_unsupported("no CUDA kernel for this operator");
     }
 }
+
+#endif  // !MARMOT_CUDA_GENERATED_QUERY
 
 marmot_device_caps_t marmot_cuda_detect_default_caps(void) {
     marmot_device_caps_t caps;

@@ -24,7 +24,7 @@ EXPORTS = (
     "mcu_context_set_regime", "mcu_synchronize", "mcu_last_error_message", "mcu_kernel_launch_count",
     "mcu_malloc", "mcu_free", "mcu_memcpy_to_device", "mcu_memcpy_to_host", "mcu_row_bytes", "mcu_dequantize",
     "mcu_quantize_activations", "mcu_linear", "mcu_linear_dual", "mcu_linear_host", "mcu_topk", "mcu_moe_experts",
-    "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_peer_comm_create", "mcu_peer_comm_export",
+    "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_moe_last_buffers", "mcu_peer_comm_create", "mcu_peer_comm_export",
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
     "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
     "mcu_embedding_gather", "mcu_paged_attention", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps", "mcu_vec_dot_host",
@@ -94,6 +94,7 @@ def load_library() -> C.CDLL:
     L.mcu_moe_experts.argtypes = [vp, i32, i32, i32, vp, sz, sz, sz, sz, vp, vp, vp, vp, vp, sz, i32, f32, i32, vp]
     L.mcu_moe_experts_local.argtypes = [vp, i32, i32, i32, vp, sz, sz, sz, sz, sz, sz, vp, vp, vp, vp, vp, sz, i32, f32,
                                         i32, vp]
+    L.mcu_moe_last_buffers.argtypes = [vp, vp]
     L.mcu_peer_comm_create.argtypes = [vp, i32, i32, sz, C.POINTER(vp)]
     L.mcu_peer_comm_export.argtypes = [vp, vp]
     L.mcu_peer_comm_connect.argtypes = [vp, vp]
@@ -331,6 +332,20 @@ class Context:
             scale, _ptr(out)))
         return out
 
+    def moe_last_buffers(self, T: int, k: int, H: int, FF: int) -> dict:
+        """Views of the intermediates the last MoE call left in the workspace (see mcu_moe_last_buffers): for checking
+        the operator stage by stage.  Synchronizes first."""
+        b = _MoeBuffers()
+        self.synchronize()
+        self._check(self.lib.mcu_moe_last_buffers(self.handle, C.byref(b)))
+        view = lambda ptr, shape, ts="<f4": _tensor_from_ptr(self.torch, ptr, shape, self.device, ts)
+        r, E = int(b.routes), int(b.experts)
+        assert r == T * k
+        return {"offsets": view(b.offsets, (E + 1,), "<i4"), "sorted_tok": view(b.sorted_tok, (r,), "<i4"),
+                "sorted_w": view(b.sorted_w, (r,)), "route_pos": view(b.route_pos, (r,), "<i4"),
+                "gate_out": view(b.gate_out, (r, FF)), "up_out": view(b.up_out, (r, FF)),
+                "route_down": view(b.route_down, (r, H)), "grouped": bool(b.grouped)}
+
     def moe_experts_local(self, kinds, hidden, gate, up, down, topk_ids, topk_weights, FF: int, E: int,
                           expert_begin: int, expert_count: int, ffn_type: int = FFN_SWIGLU,
                           weights_scale: float = 1.0, policy: int = ROUTER_RENORMALIZE_SELECTED, out=None):
@@ -391,16 +406,24 @@ class PeerComm:
             self.handle = None
 
 
-def _tensor_from_ptr(torch, ptr: int, shape, device_index: int):
-    """float32 torch view of device memory owned by the library (CUDA array interface)."""
+def _tensor_from_ptr(torch, ptr: int, shape, device_index: int, typestr: str = "<f4"):
+    """torch view (float32 unless `typestr` says otherwise) of device memory owned by the library (CUDA array
+    interface)."""
 
     class _Ext:
         pass
 
     e = _Ext()
-    e.__cuda_array_interface__ = {"shape": tuple(int(v) for v in shape), "typestr": "<f4", "data": (int(ptr), False),
+    e.__cuda_array_interface__ = {"shape": tuple(int(v) for v in shape), "typestr": typestr, "data": (int(ptr), False),
                                   "version": 2}
     return torch.as_tensor(e, device=torch.device("cuda", device_index))
+
+
+class _MoeBuffers(C.Structure):
+    """struct mcu_moe_buffers, include/marmot_cuda.h."""
+    _fields_ = [("offsets", C.c_void_p), ("sorted_tok", C.c_void_p), ("sorted_w", C.c_void_p), ("route_pos", C.c_void_p),
+                ("gate_out", C.c_void_p), ("up_out", C.c_void_p), ("route_down", C.c_void_p), ("routes", C.c_size_t),
+                ("experts", C.c_size_t), ("grouped", C.c_int)]
 
 
 class Graph:
