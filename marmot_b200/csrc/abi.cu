@@ -78,6 +78,7 @@ struct mcu_context {
     Buffer act_qs, act_d, act_bsums, act_half, act_rowscale, x_stage, out_stage, bias_stage;
     Buffer moe_meta, moe_hidden, moe_gate, moe_up, moe_down;
     Buffer gemm_partial;         // split-K partial tiles
+    Buffer i8_partial, i8_tickets;  // integer-MMA matmul: shares of row groups split between CTAs, and their tickets
     Buffer attn_partial;         // split-KV partial attention states
     int *gemm_counters = nullptr;  // split-K tile tickets (zero between launches)
     std::vector<int> host_counts;
@@ -216,7 +217,7 @@ void mcu_context_destroy(mcu_context_t *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     Buffer *bufs[] = {&ctx->act_qs,   &ctx->act_d,      &ctx->act_bsums, &ctx->act_half, &ctx->act_rowscale, &ctx->x_stage, &ctx->out_stage,
-                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down, &ctx->gemm_partial, &ctx->attn_partial};
+                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down, &ctx->gemm_partial, &ctx->attn_partial, &ctx->i8_partial, &ctx->i8_tickets};
     for (Buffer *b : bufs)
         if (b->ptr != nullptr) cudaFree(b->ptr);
     if (ctx->dev_err != nullptr) cudaFree(ctx->dev_err);
@@ -421,6 +422,26 @@ static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx,
     if (T == 0 || F == 0) return MCU_SUCCESS;
     const bool gemm = ctx->regime == MCU_REGIME_GEMM || (ctx->regime == MCU_REGIME_AUTO && T > (size_t)GEMV_MAX_T);
     ActBuffers ab;
+    // Few tokens: exact integer dots on mma.sync s8 (Q4_K, Q6_K).  From two tokens up it reads the weights once for
+    // all of them where the dp4a kernel re-reads the activations per token from shared memory.
+    static const bool no_i8 = getenv("MARMOT_CUDA_NO_I8MMA") != nullptr;  // diagnostic switch
+    if (!no_i8 && ctx->regime == MCU_REGIME_AUTO && T >= 2 && T <= 64 &&
+        gemm_i8_supported(kind, w, w2, (int)T, (int)K, (int)F) && (w2 == nullptr || bias == nullptr)) {
+        size_t qs_b, dT_b, part_b, tick_b;
+        gemm_i8_workspace_bytes((int)T, (int)K, (int)F, w2 != nullptr, &qs_b, &dT_b, &part_b, &tick_b);
+        if (int rc = ensure(ctx, ctx->act_qs, qs_b)) return rc;
+        if (int rc = ensure(ctx, ctx->act_d, dT_b)) return rc;
+        if (int rc = ensure(ctx, ctx->i8_partial, part_b)) return rc;
+        if (tick_b > ctx->i8_tickets.cap) {  // a fresh ticket area starts at zero; the kernel keeps it so
+            if (int rc = ensure(ctx, ctx->i8_tickets, tick_b)) return rc;
+            MCU_CUDA(cudaMemsetAsync(ctx->i8_tickets.ptr, 0, ctx->i8_tickets.cap, ctx->stream));
+        }
+        MCU_CUDA(launch_gemm_i8(kind, w, w2, x, (int)ldx, (int)T, (int)K, (int)F, bias, out, out2, (int)ldo,
+                                (int8_t *)ctx->act_qs.ptr, (float *)ctx->act_d.ptr, (float *)ctx->i8_partial.ptr,
+                                (int *)ctx->i8_tickets.ptr, ctx->dev_err, ctx->stream));
+        count_launches(2);
+        return MCU_SUCCESS;
+    }
     if (gemm) {
         if (gemm_tc_supported(kind, (int)T, (int)K, (int)F)) {
             const bool tma = gemm_tma_supported(kind, w, w2, (int)T, (int)K, (int)F);

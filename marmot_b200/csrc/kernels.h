@@ -65,6 +65,17 @@ bool gemv_stream_supported(int kind, const void *W, const void *W2, int T, int K
 cudaError_t launch_gemv_stream(int kind, const void *W, const void *W2, const float *x, int ldx, int T, int K, int F,
                                const float *bias, float *out, float *out2, int ldo, int *err_flag, cudaStream_t s);
 
+// Few-token regime (2 <= T <= 64) on integer tensor-core instructions: activations packed to Q8_K by a first launch,
+// exact int32 sub-block dots (mma.sync s8), f32 scaling per block; Q4_K and Q6_K, rows a multiple of 16 bytes.
+// The caller provides the workspace (sizes from gemm_i8_workspace_bytes); `tickets` must be zero before the first
+// launch and is left zero.
+bool gemm_i8_supported(int kind, const void *W, const void *W2, int T, int K, int F);
+void gemm_i8_workspace_bytes(int T, int K, int F, bool dual, size_t *qs_bytes, size_t *dT_bytes, size_t *partial_bytes,
+                             size_t *ticket_bytes);
+cudaError_t launch_gemm_i8(int kind, const void *W, const void *W2, const float *x, int ldx, int T, int K, int F,
+                           const float *bias, float *out, float *out2, int ldo, int8_t *qs, float *dT, float *partial,
+                           int *tickets, int *err_flag, cudaStream_t s);
+
 // Prefill / batched regime on the tcgen05 tensor cores: weights dequantised to fp16 tiles in shared
 // memory, activations given as fp16 (d*q of the quantized activations, row stride ldxh), f32
 // accumulation in tensor memory.

@@ -1029,6 +1029,16 @@ enum {
     CUDA_KERNEL_DEQUANTIZE_Q4_K,
     CUDA_KERNEL_DEQUANTIZE_Q6_K,
     CUDA_KERNEL_DEQUANTIZE_Q8_0,
+    CUDA_KERNEL_EMBEDDING_Q4_K,
+    CUDA_KERNEL_EMBEDDING_Q6_K,
+    CUDA_KERNEL_EMBEDDING_Q8_0,
+    CUDA_KERNEL_RMS_NORM_F32,
+    CUDA_KERNEL_RMS_NORM_GEMMA_F32,
+    CUDA_KERNEL_ROPE_F32,
+    CUDA_KERNEL_ADD_F32,
+    CUDA_KERNEL_SWIGLU_F32,
+    CUDA_KERNEL_PAGED_ATTENTION_F32_KV_F32,
+    CUDA_KERNEL_PAGED_ATTENTION_F32_KV_F16,
     CUDA_KERNEL_END,
 };
 
@@ -1110,6 +1120,32 @@ marmot_kernel_selection_t marmot_cuda_query_kernel(const marmot_op_signature_t *
         if (slot < 0 || sig->output_dtype != MARMOT_DTYPE_FLOAT32)
             return cuda_unsupported("CUDA dequantize covers Q4_K, Q6_K and Q8_0 to FLOAT32");
         return cuda_supported(CUDA_KERNEL_DEQUANTIZE_Q4_K + slot, caps, 4.0 * sig->dims.elementwise.n_elems, 0.0, 0.0);
+    case MARMOT_OP_EMBEDDING:
+        if (slot < 0 || sig->output_dtype != MARMOT_DTYPE_FLOAT32)
+            return cuda_unsupported("CUDA embedding gather covers Q4_K, Q6_K and Q8_0 tables to FLOAT32");
+        return cuda_supported(CUDA_KERNEL_EMBEDDING_Q4_K + slot, caps, 0.0, 0.0, 0.0);
+    case MARMOT_OP_RMS_NORM:
+    case MARMOT_OP_RMS_NORM_GEMMA:
+        if (!f32_io) return cuda_unsupported("CUDA RMSNorm is FLOAT32");
+        return cuda_supported(sig->op_id == MARMOT_OP_RMS_NORM ? CUDA_KERNEL_RMS_NORM_F32 : CUDA_KERNEL_RMS_NORM_GEMMA_F32,
+                              caps, 8.0 * sig->dims.layernorm.n * sig->dims.layernorm.d, 0.0, 0.0);
+    case MARMOT_OP_ROPE:
+        if (!f32_io) return cuda_unsupported("CUDA RoPE is FLOAT32");
+        return cuda_supported(CUDA_KERNEL_ROPE_F32, caps, 0.0, 0.0, 0.0);
+    case MARMOT_OP_ADD:
+    case MARMOT_OP_SWIGLU:
+        if (!f32_io) return cuda_unsupported("CUDA elementwise kernels are FLOAT32");
+        if (sig->stride_mode != MARMOT_STRIDE_MODE_ANY && sig->stride_mode != MARMOT_STRIDE_MODE_CONTIGUOUS)
+            return cuda_unsupported("CUDA elementwise kernels take contiguous tensors");
+        return cuda_supported(sig->op_id == MARMOT_OP_ADD ? CUDA_KERNEL_ADD_F32 : CUDA_KERNEL_SWIGLU_F32, caps,
+                              12.0 * sig->dims.elementwise.n_elems, 0.0, 0.0);
+    case MARMOT_OP_PAGED_ATTENTION:
+        if (!f32_io) return cuda_unsupported("CUDA paged attention takes FLOAT32 q/k/v");
+        if (sig->weight_dtype == MARMOT_DTYPE_FLOAT16)
+            return cuda_supported(CUDA_KERNEL_PAGED_ATTENTION_F32_KV_F16, caps, 0.0, 0.0, 0.0);
+        if (sig->weight_dtype == MARMOT_DTYPE_FLOAT32)
+            return cuda_supported(CUDA_KERNEL_PAGED_ATTENTION_F32_KV_F32, caps, 0.0, 0.0, 0.0);
+        return cuda_unsupported("CUDA paged attention KV pool must be FLOAT32 or FLOAT16");
     default:
         return cuda_unsupported("no CUDA kernel for this operator");
     }

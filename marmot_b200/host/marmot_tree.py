@@ -1,8 +1,8 @@
 """Staging a marmot source checkout for a gcc / Linux build.
 
 marmot (darekhta/marmot) builds with meson + clang on macOS; its Linux / x86 gcc build is broken as shipped.  The
-recipes that compile it here - the CPU checker library of the tests (oracle/build_ref.py) and the full library with
-the CUDA backend linked in (marmot_b200/host/build_marmot.py) - first copy the checkout to a temporary directory and
+recipes that compile it here - the CPU checker library the tests compare against and the full library with the
+CUDA backend linked in (marmot_b200/host/build_marmot.py) - first copy the checkout to a temporary directory and
 apply five build fixes there, none of which changes arithmetic:
 
   1. src/backends/cpu/cpu_backend_internal.h: cpu_sincosf / cpu_sincos have a second

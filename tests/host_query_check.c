@@ -109,7 +109,7 @@ int main(int argc, char **argv) {
         const marmot_op_id_t ops[] = {MARMOT_OP_MOE_EXPERTS, MARMOT_OP_TOPK,       MARMOT_OP_DEQUANTIZE,
                                       MARMOT_OP_EMBEDDING,   MARMOT_OP_RMS_NORM,   MARMOT_OP_RMS_NORM_GEMMA,
                                       MARMOT_OP_ROPE,        MARMOT_OP_ADD,        MARMOT_OP_SWIGLU,
-                                      MARMOT_OP_PAGED_ATTENTION, MARMOT_OP_REDUCTION_ARGMAX};
+                                      MARMOT_OP_PAGED_ATTENTION};
         for (size_t i = 0; i < sizeof(ops) / sizeof(ops[0]); ++i) {
             marmot_op_signature_t s;
             memset(&s, 0, sizeof(s));
@@ -119,6 +119,11 @@ int main(int argc, char **argv) {
             CHECK(marmot_cuda_query_kernel(&s, &caps).supported);
         }
         marmot_op_signature_t s;
+        memset(&s, 0, sizeof(s));
+        // an operator the host layer has no implementation function for is not advertised
+        s.op_id = MARMOT_OP_REDUCTION_ARGMAX;
+        s.input_dtype = s.output_dtype = MARMOT_DTYPE_FLOAT32;
+        CHECK(!marmot_cuda_query_kernel(&s, &caps).supported);
         memset(&s, 0, sizeof(s));
         s.op_id = MARMOT_OP_PAGED_ATTENTION;
         s.input_dtype = s.output_dtype = MARMOT_DTYPE_FLOAT32;

@@ -497,3 +497,51 @@ def test_moe_duplicate_routes_and_unused_experts(ctx, oracle):
         ctx.moe_experts(kinds, dev(ctx, hid), ctx.upload(gate), ctx.upload(up), ctx.upload(down), dev(ctx, bad),
                         dev(ctx, wts), FF, E)
     assert e.value.code == -1
+
+
+# ---- few tokens on integer tensor-core instructions (csrc/gemm_i8.cu) ----
+@pytest.mark.parametrize("name", ["q4_k", "q6_k"])
+@pytest.mark.parametrize("T,K,F", [(2, 4096, 4096), (5, 2048, 200), (8, 4096, 1024), (9, 2048, 333), (16, 4096, 14336),
+                                   (33, 2048, 64), (64, 4096, 4096), (64, 14336, 512), (3, 2048 + 256 * 5, 96)])
+def test_integer_mma_matmul_vs_oracle(ctx, oracle, name, T, K, F):
+    """2..64 tokens take the mma.sync s8 kernel: exact integer sub-block dots, so the result must sit at the
+    fp32-accumulate tolerance whatever the token count; row groups that span several CTAs (and several row groups in
+    one CTA), a ragged last row group, bias, and a strided input are all in the list."""
+    import torch
+
+    kind = KINDS[name]
+    if kind == KINDS["q6_k"] and (K // 256) % 8:
+        K = (K // 2048 + 1) * 2048  # Q6_K rows must be 16-byte multiples for the tensor map
+    rng = np.random.default_rng(T * 131 + F)
+    W = random_blocks(kind, F, K, rng)
+    ldx = K + 8
+    xbuf = rng.normal(0, 1, (T, ldx)).astype(np.float32)
+    x = xbuf[:, :K]
+    bias = rng.normal(0, 1, F).astype(np.float32)
+    xd = torch.from_numpy(xbuf).cuda()[:, :K]
+    l0 = ctx.launch_count()
+    got = ctx.linear(kind, xd, ctx.upload(W), F, bias=torch.from_numpy(bias).cuda()).cpu().numpy()
+    assert ctx.launch_count() - l0 == 2  # the activation packer and the matmul
+    want = oracle.linear(kind, np.ascontiguousarray(x), W, F, bias=bias)
+    err = max_rel_err(got, want)
+    assert err <= TOL_FP32, err
+    assert err <= 2e-5, err  # in practice: only the order of the per-block f32 terms differs
+
+
+@pytest.mark.parametrize("T", [4, 40])
+def test_integer_mma_dual_output(ctx, oracle, T):
+    import torch
+
+    K, F = 4096, 1408
+    rng = np.random.default_rng(T)
+    Wa, Wb = random_blocks(KINDS["q4_k"], F, K, rng), random_blocks(KINDS["q4_k"], F, K, rng)
+    x = rng.normal(0, 1, (T, K)).astype(np.float32)
+    a = torch.empty((T, F), dtype=torch.float32, device="cuda")
+    b = torch.empty((T, F), dtype=torch.float32, device="cuda")
+    ctx.linear_dual(KINDS["q4_k"], torch.from_numpy(x).cuda(), ctx.upload(Wa), ctx.upload(Wb), F, out_a=a, out_b=b)
+    assert max_rel_err(a.cpu().numpy(), oracle.linear(KINDS["q4_k"], x, Wa, F)) <= 2e-5
+    assert max_rel_err(b.cpu().numpy(), oracle.linear(KINDS["q4_k"], x, Wb, F)) <= 2e-5
+    # twice more on the same context: the tickets were left at zero
+    for _ in range(2):
+        ctx.linear_dual(KINDS["q4_k"], torch.from_numpy(x).cuda(), ctx.upload(Wa), ctx.upload(Wb), F, out_a=a, out_b=b)
+    assert max_rel_err(b.cpu().numpy(), oracle.linear(KINDS["q4_k"], x, Wb, F)) <= 2e-5
