@@ -61,6 +61,7 @@ enum {
     MCU_REGIME_GEMV = 1,       /* decode kernels for every T (tokens processed eight at a time) */
     MCU_REGIME_GEMM = 2,       /* tensor-core kernel for every T */
     MCU_REGIME_GEMV_PLAIN = 3, /* decode kernels without the shared-memory streaming variant */
+    MCU_REGIME_I8MMA = 4,      /* integer tensor-core kernel wherever it applies (2..64 tokens, Q4_K / Q6_K) */
 };
 
 typedef struct mcu_context mcu_context_t;

@@ -298,7 +298,7 @@ void mcu_graph_destroy(mcu_graph_t *graph) {
 
 int mcu_context_set_regime(mcu_context_t *ctx, int regime) {
     if (ctx == nullptr) return fail(MCU_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
-    if (regime < MCU_REGIME_AUTO || regime > MCU_REGIME_GEMV_PLAIN) return fail(MCU_ERROR_INVALID_ARGUMENT, "bad regime");
+    if (regime < MCU_REGIME_AUTO || regime > MCU_REGIME_I8MMA) return fail(MCU_ERROR_INVALID_ARGUMENT, "bad regime");
     std::lock_guard<std::mutex> lock(ctx->mu);
     ctx->regime = regime;
     return MCU_SUCCESS;
@@ -420,12 +420,20 @@ static void *mapped_host_pointer(const void *host) {
 static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx, const void *w, const void *w2, size_t T,
                          size_t K, size_t F, const float *bias, float *out, float *out2, size_t ldo) {
     if (T == 0 || F == 0) return MCU_SUCCESS;
-    const bool gemm = ctx->regime == MCU_REGIME_GEMM || (ctx->regime == MCU_REGIME_AUTO && T > (size_t)GEMV_MAX_T);
+    const bool gemm = ctx->regime == MCU_REGIME_GEMM ||
+        ((ctx->regime == MCU_REGIME_AUTO || ctx->regime == MCU_REGIME_I8MMA) && T > (size_t)GEMV_MAX_T);
     ActBuffers ab;
-    // Few tokens: exact integer dots on mma.sync s8 (Q4_K, Q6_K).  From two tokens up it reads the weights once for
-    // all of them where the dp4a kernel re-reads the activations per token from shared memory.
+    // A handful of tokens: exact integer dots on mma.sync s8 (Q4_K, Q6_K).  Measured against the neighbours on
+    // K = 4096 (F = 4096 / 14336, microseconds per call): 8 tokens 12.1 / 19.4 here, 15.3 / 33.6 on the dp4a kernel
+    // (which re-reads the activations from shared memory per token); 16 tokens 13.4 / 22.5 here, 12.4 / 25.8 on the
+    // tcgen05 kernel; below five tokens the dp4a kernel's single launch wins, beyond sixteen the integer MMA rate of
+    // this part (about 30 cycles per m16n8k32 and SM sub-partition) does not keep up with the fp16 paths.
     static const bool no_i8 = getenv("MARMOT_CUDA_NO_I8MMA") != nullptr;  // diagnostic switch
-    if (!no_i8 && ctx->regime == MCU_REGIME_AUTO && T >= 2 && T <= 64 &&
+    const size_t w_total = F * mcu_row_bytes(kind, K) * (w2 != nullptr ? 2 : 1);
+    const bool i8_pays = ctx->regime == MCU_REGIME_I8MMA
+        ? (T >= 2 && T <= 64)
+        : (!no_i8 && ctx->regime == MCU_REGIME_AUTO && T >= 5 && T <= 16 && (T <= 12 || w_total >= ((size_t)24 << 20)));
+    if (i8_pays &&
         gemm_i8_supported(kind, w, w2, (int)T, (int)K, (int)F) && (w2 == nullptr || bias == nullptr)) {
         size_t qs_b, dT_b, part_b, tick_b;
         gemm_i8_workspace_bytes((int)T, (int)K, (int)F, w2 != nullptr, &qs_b, &dT_b, &part_b, &tick_b);

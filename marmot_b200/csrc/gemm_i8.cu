@@ -7,19 +7,19 @@
 // as the A operand built in registers straight from the packed block bytes, the tokens as the B operand fetched with
 // `ldmatrix` from the quantized activation tile.  Sub-block sums are scaled by the integer sub-block scales, summed
 // per 256-value block, converted once and scaled by d * d_act in f32 (the reference's vec_dot_q4_k_q8_k /
-// vec_dot_q6_k_q8_k, vec_dot_impl.h:688-732,783-828).  The Q4_K min term sum_j m_j * bsum_j needs no sub-block sums of
-// the activations: a second MMA whose A operand holds m_j in every k position yields m_j * sum_k a_k directly.
+// vec_dot_q6_k_q8_k, vec_dot_impl.h:688-732,783-828).  The Q4_K min term sum_j m_j * bsum_j uses the activation
+// packer's sub-block sums, two products per dp2a.
 // Nothing is rounded to fp16 anywhere, so the results sit at the fp32-accumulate tolerance (about 1e-6 of the
 // reference in practice), not the tensor-core one.
 //
 // Data movement: one launch quantizes the activations (qs [Tpad][K] int8 in the in-block order of act_pack.cuh,
 // scales transposed to [column][Tpad]); the matmul kernel is persistent, one CTA per SM.  Work is cut into stage
-// units (a group of 64 weight rows x I8_WK block columns) laid out row-group major; CTA c takes the contiguous span
+// units (a group of 64 weight rows x WK block columns) laid out row-group major; CTA c takes the contiguous span
 // [SU*c/C, SU*(c+1)/C) of them, so every SM streams the same number of bytes whatever F and K are.  A producer thread
 // feeds a ring of stages with TMA: per stage the raw weight blocks (a [64 rows x one block column] box per column, no
 // repacking: rows of a box are 144 / 240 bytes apart, which spreads the eight rows a warp touches over all banks) and
-// the activation tile of the same columns ([Tpad x 128 B] boxes, 128-byte swizzle for conflict-free ldmatrix).  Eight
-// consumer warps = 4 row tiles x 2 columns.  When a CTA's span ends inside a row group its partial sums go to a
+// the activation tile of the same columns ([Tpad x 128 B] boxes, 128-byte swizzle for conflict-free ldmatrix).  The
+// consumer warps are 4 row tiles x WK columns.  When a CTA's span ends inside a row group its partial sums go to a
 // workspace and the last CTA to finish that row group adds the partials in CTA order (deterministic) - nobody waits
 // for anybody.  Weight boxes are requested before `griddepcontrol.wait` (they never depend on the previous kernel);
 // every mbarrier wait is bounded and ends in an error flag, not a hang.  No TMA multicast.
@@ -34,11 +34,12 @@
 namespace mcu {
 
 constexpr int I8_WM = 4;                     // 16-row tiles per row group
-constexpr int I8_WK = 2;                     // block columns per stage
-constexpr int I8_WARPS = I8_WM * I8_WK;      // consumer warps
 constexpr int I8_ROWS = 16 * I8_WM;          // weight rows per row group
-constexpr int I8_THREADS = (I8_WARPS + 1) * 32;
 constexpr int I8_MAX_STAGES = 8;
+// Block columns per stage (WK, a template parameter): 4 for one or two token tiles (sixteen consumer warps: the
+// integer MMA has a long latency and few of them are in flight per warp), 2 beyond (the activation tiles of a stage
+// grow with the token count).
+__host__ __device__ constexpr int i8_wk(int NT) { return NT <= 2 ? 4 : 2; }
 constexpr int I8_HEADER = 1024;              // barriers; keeps the stages 1024-byte aligned for the swizzled tiles
 
 template <int KIND>
@@ -56,11 +57,12 @@ struct GemmI8Params {
     float *out[2];
     const float *bias;
     const float *dT;   // activation scales [columns][Tpad]
+    const int16_t *bsT; // sums of the 32-value sub-blocks of the activations [columns][Tpad][8] (Q4_K mins)
     float *partial;    // [CTAs][2][I8_WM][Tpad * 16] partial sums of row groups shared between CTAs
     int *tickets;      // [row groups * I8_WM], zero between launches
     int *err;
     int ldo, T, Tpad, F, ncols, NJ, RG, n_mats, SU, stages;
-    int w_bytes, x_bytes, d_bytes, stage_bytes;  // per stage: offsets / sizes of the three parts, stride of a stage
+    int w_bytes, x_bytes, d_bytes, bs_bytes, stage_bytes;  // per stage: offsets / sizes of the three parts, stride of a stage
     int tx_bytes;                                // bytes the copies of one stage deliver
 };
 
@@ -103,8 +105,8 @@ __device__ __forceinline__ uint32_t swz128(uint32_t tile, int row, int chunk) {
 // 144); xa / xb: the activation half tiles (sub-blocks 0,2,4,6 and 1,3,5,7 of the column, in-block order of
 // act_pack.cuh); dcol: the column's activation scales.  acc[nt][i]: rows (g, g, g+8, g+8) x tokens (2t, 2t+1, ...).
 template <int NT>
-__device__ __forceinline__ void unit_q4_k(const uint8_t *wbox, uint32_t xa, uint32_t xb, const float *dcol, int lane,
-                                          float (&acc)[NT][4]) {
+__device__ __forceinline__ void unit_q4_k(const uint8_t *wbox, uint32_t xa, uint32_t xb, const float *dcol,
+                                          const int16_t *bscol, int lane, float (&acc)[NT][4]) {
     const int g = lane >> 2, t = lane & 3;
     const uint8_t *r0 = wbox + g * 144, *r1 = r0 + 8 * 144;
     const uint32_t h0 = *(const uint32_t *)r0, h1 = *(const uint32_t *)r1;
@@ -121,11 +123,11 @@ __device__ __forceinline__ void unit_q4_k(const uint8_t *wbox, uint32_t xa, uint
         sc[1][1] = (b2 & 0x0F0F0F0Fu) | (((b0 >> 6) & 0x03030303u) << 4);
         mn[1][1] = ((b2 >> 4) & 0x0F0F0F0Fu) | (((b1 >> 6) & 0x03030303u) << 4);
     }
-    int p[NT][4], sm[NT][4];
+    int p[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) p[nt][i] = 0, sm[nt][i] = 0;
+        for (int i = 0; i < 4; ++i) p[nt][i] = 0;
     const int mat = lane >> 3, lrow = lane & 7;
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {  // 64-value group: sub-blocks 2jj (low nibbles) and 2jj+1 (high nibbles)
@@ -134,10 +136,6 @@ __device__ __forceinline__ void unit_q4_k(const uint8_t *wbox, uint32_t xa, uint
         const int s0 = 2 * jj, s1 = 2 * jj + 1;
         const int sc00 = (int)((sc[0][s0 >> 2] >> (8 * (s0 & 3))) & 0xFFu), sc01 = (int)((sc[0][s1 >> 2] >> (8 * (s1 & 3))) & 0xFFu);
         const int sc10 = (int)((sc[1][s0 >> 2] >> (8 * (s0 & 3))) & 0xFFu), sc11 = (int)((sc[1][s1 >> 2] >> (8 * (s1 & 3))) & 0xFFu);
-        const uint32_t m00 = ((mn[0][s0 >> 2] >> (8 * (s0 & 3))) & 0xFFu) * 0x01010101u;
-        const uint32_t m01 = ((mn[0][s1 >> 2] >> (8 * (s1 & 3))) & 0xFFu) * 0x01010101u;
-        const uint32_t m10 = ((mn[1][s0 >> 2] >> (8 * (s0 & 3))) & 0xFFu) * 0x01010101u;
-        const uint32_t m11 = ((mn[1][s1 >> 2] >> (8 * (s1 & 3))) & 0xFFu) * 0x01010101u;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             // matrices: (xa, chunk 2jj), (xa, chunk 2jj+1), (xb, chunk 2jj), (xb, chunk 2jj+1)
@@ -150,8 +148,6 @@ __device__ __forceinline__ void unit_q4_k(const uint8_t *wbox, uint32_t xa, uint
             mma_s8_k32(e, (q00 >> 4) & 0x0F0F0F0Fu, (q10 >> 4) & 0x0F0F0F0Fu, (q01 >> 4) & 0x0F0F0F0Fu,
                        (q11 >> 4) & 0x0F0F0F0Fu, b2, b3);
             p[nt][0] += sc01 * e[0], p[nt][1] += sc01 * e[1], p[nt][2] += sc11 * e[2], p[nt][3] += sc11 * e[3];
-            mma_s8_k32(sm[nt], m00, m10, m00, m10, b0, b1);
-            mma_s8_k32(sm[nt], m01, m11, m01, m11, b2, b3);
         }
     }
     const float d0 = half_bits_to_float((uint16_t)(h0 & 0xFFFFu)), dm0 = half_bits_to_float((uint16_t)(h0 >> 16));
@@ -159,10 +155,19 @@ __device__ __forceinline__ void unit_q4_k(const uint8_t *wbox, uint32_t xa, uint
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         const float2 ad = *(const float2 *)(dcol + nt * 8 + 2 * t);
-        acc[nt][0] = fmaf(ad.x, __fsub_rn(__fmul_rn(d0, (float)p[nt][0]), __fmul_rn(dm0, (float)sm[nt][0])), acc[nt][0]);
-        acc[nt][1] = fmaf(ad.y, __fsub_rn(__fmul_rn(d0, (float)p[nt][1]), __fmul_rn(dm0, (float)sm[nt][1])), acc[nt][1]);
-        acc[nt][2] = fmaf(ad.x, __fsub_rn(__fmul_rn(d1, (float)p[nt][2]), __fmul_rn(dm1, (float)sm[nt][2])), acc[nt][2]);
-        acc[nt][3] = fmaf(ad.y, __fsub_rn(__fmul_rn(d1, (float)p[nt][3]), __fmul_rn(dm1, (float)sm[nt][3])), acc[nt][3]);
+        // sum_j m_j * bsum_j (the reference's sumi): eight 16-bit sub-block sums per token against the eight 6-bit mins
+        // of a row, two products per dp2a
+        const int4 bs0 = *(const int4 *)(bscol + (nt * 8 + 2 * t) * 8), bs1 = *(const int4 *)(bscol + (nt * 8 + 2 * t + 1) * 8);
+        int sm[4];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            sm[2 * r] = __dp2a_hi(bs0.w, (int)mn[r][1], __dp2a_lo(bs0.z, (int)mn[r][1], __dp2a_hi(bs0.y, (int)mn[r][0], __dp2a_lo(bs0.x, (int)mn[r][0], 0))));
+            sm[2 * r + 1] = __dp2a_hi(bs1.w, (int)mn[r][1], __dp2a_lo(bs1.z, (int)mn[r][1], __dp2a_hi(bs1.y, (int)mn[r][0], __dp2a_lo(bs1.x, (int)mn[r][0], 0))));
+        }
+        acc[nt][0] = fmaf(ad.x, __fsub_rn(__fmul_rn(d0, (float)p[nt][0]), __fmul_rn(dm0, (float)sm[0])), acc[nt][0]);
+        acc[nt][1] = fmaf(ad.y, __fsub_rn(__fmul_rn(d0, (float)p[nt][1]), __fmul_rn(dm0, (float)sm[1])), acc[nt][1]);
+        acc[nt][2] = fmaf(ad.x, __fsub_rn(__fmul_rn(d1, (float)p[nt][2]), __fmul_rn(dm1, (float)sm[2])), acc[nt][2]);
+        acc[nt][3] = fmaf(ad.y, __fsub_rn(__fmul_rn(d1, (float)p[nt][3]), __fmul_rn(dm1, (float)sm[3])), acc[nt][3]);
     }
 }
 
@@ -230,10 +235,11 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *wbox, int roff, uint32_
 }
 
 template <int KIND, int NT>
-__global__ void __launch_bounds__(I8_THREADS, 1)
+__global__ void __launch_bounds__((I8_WM * i8_wk(NT) + 1) * 32, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
                const __grid_constant__ CUtensorMap map_x, const GemmI8Params p) {
     using Cfg = I8Cfg<KIND>;
+    constexpr int I8_WK = i8_wk(NT), I8_WARPS = I8_WM * I8_WK;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t *full = (uint64_t *)smem;
     uint64_t *empty = full + I8_MAX_STAGES;
@@ -284,6 +290,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant
                     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dd),
                                  "l"(p.dT + (size_t)j * p.Tpad), "r"((uint32_t)(p.Tpad * 4)), "r"(bar)
                                  : "memory");
+                    if (KIND == KIND_Q4_K) {
+                        const uint32_t bb = tm_smem_u32(dst + p.x_bytes + p.d_bytes + k * (p.Tpad * 16));
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(bb),
+                                     "l"(p.bsT + (size_t)j * p.Tpad * 8), "r"((uint32_t)(p.Tpad * 16)), "r"(bar)
+                                     : "memory");
+                    }
                 }
             };
             // the weights never depend on the previous kernel in the stream: ask for the first ring's worth before
@@ -330,7 +342,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant
             const uint8_t *wbox = sb + wk * (I8_ROWS * Cfg::BOX_W) + (wm * 16) * Cfg::BOX_W;
             const uint32_t xa = tm_smem_u32(sb + p.w_bytes + (wk * 2) * (p.Tpad * 128)), xb = xa + p.Tpad * 128;
             const float *dcol = (const float *)(sb + p.w_bytes + p.x_bytes + wk * (p.Tpad * 4));
-            if (KIND == KIND_Q4_K) unit_q4_k<NT>(wbox, xa, xb, dcol, lane, acc);
+            const int16_t *bscol = (const int16_t *)(sb + p.w_bytes + p.x_bytes + p.d_bytes + wk * (p.Tpad * 16));
+            if (KIND == KIND_Q4_K) unit_q4_k<NT>(wbox, xa, xb, dcol, bscol, lane, acc);
             else unit_q6_k<NT>(wbox, (j * Cfg::COL_BYTES) & 15, xa, xb, dcol, lane, acc);
         }
         __syncwarp();
@@ -339,19 +352,22 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant
         // last stage unit of this row group within the span: reduce over the column warps and write
         const bool flush = su + 1 == su1 || (su + 1) / p.NJ != rgg;
         if (!flush) continue;
-        float *redw = (float *)red_buf + (size_t)wm * (NT * 4 * 32);
+        float *redw = (float *)red_buf + (size_t)wm * (I8_WK - 1) * (NT * 4 * 32);
         if (wk != 0) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                for (int k = 0; k < 4; ++k) redw[(nt * 4 + k) * 32 + lane] = acc[nt][k];
+                for (int k = 0; k < 4; ++k) redw[(size_t)(wk - 1) * (NT * 4 * 32) + (nt * 4 + k) * 32 + lane] = acc[nt][k];
         }
         asm volatile("bar.sync 1, %0;" ::"n"(I8_WARPS * 32) : "memory");
         if (wk == 0) {
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
+            for (int w = 0; w < I8_WK - 1; ++w)
 #pragma unroll
-                for (int k = 0; k < 4; ++k) acc[nt][k] = __fadd_rn(acc[nt][k], redw[(nt * 4 + k) * 32 + lane]);
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        acc[nt][k] = __fadd_rn(acc[nt][k], redw[(size_t)w * (NT * 4 * 32) + (nt * 4 + k) * 32 + lane]);
             const int mat = rgg >= p.RG ? 1 : 0, rg = rgg - mat * p.RG;
             const int row_lo = rg * I8_ROWS + wm * 16 + g;
             float *out = p.out[mat];
@@ -413,7 +429,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant
 // ---- activation packing for this kernel: qs [Tpad][kp] (rows T..Tpad-1 are never read: the tensor map ends at T),
 //      scales transposed to dT [columns][Tpad] with zeros for the padding tokens ----
 __global__ void __launch_bounds__(256) quantize_i8_kernel(const float *__restrict__ x, int ldx, int T, int Tpad, int K, int nb,
-                                                         int8_t *__restrict__ qs, float *__restrict__ dT) {
+                                                         int8_t *__restrict__ qs, float *__restrict__ dT,
+                                                         int16_t *__restrict__ bsT) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
@@ -429,17 +446,20 @@ __global__ void __launch_bounds__(256) quantize_i8_kernel(const float *__restric
     const bool vec_ok = (((uintptr_t)x & 15) == 0) && ((ldx & 3) == 0);
     float v[8];
     load_values_q8_k<32>(row, len, vec_ok, lane, v);
-    pack_values_q8_k<32>(v, true, lane, qs + (size_t)t * nb * QK_K + (size_t)j * QK_K, dT + (size_t)j * Tpad + t, nullptr);
+    pack_values_q8_k<32>(v, true, lane, qs + (size_t)t * nb * QK_K + (size_t)j * QK_K, dT + (size_t)j * Tpad + t,
+                         bsT != nullptr ? bsT + ((size_t)j * Tpad + t) * 8 : nullptr);
 }
 
 // ---- host side ----
-static int i8_stage_bytes(int kind, int Tpad, int *w, int *x, int *d) {
+static int i8_stage_bytes(int kind, int Tpad, int *w, int *x, int *d, int *bs) {
     const int box_w = kind == KIND_Q4_K ? I8Cfg<KIND_Q4_K>::BOX_W : I8Cfg<KIND_Q6_K>::BOX_W;
-    *w = I8_WK * I8_ROWS * box_w;
+    const int wk = i8_wk(Tpad / 8);
+    *w = wk * I8_ROWS * box_w;
     *w = (*w + 1023) & ~1023;  // the swizzled activation tiles that follow need 1024-byte alignment
-    *x = I8_WK * 2 * Tpad * 128;
-    *d = I8_WK * Tpad * 4;
-    return (*w + *x + *d + 1023) & ~1023;
+    *x = wk * 2 * Tpad * 128;
+    *d = wk * Tpad * 4;
+    *bs = kind == KIND_Q4_K ? wk * Tpad * 16 : 0;
+    return (*w + *x + *d + *bs + 1023) & ~1023;
 }
 
 bool gemm_i8_supported(int kind, const void *W, const void *W2, int T, int K, int F) {
@@ -459,7 +479,7 @@ void gemm_i8_workspace_bytes(int T, int K, int F, bool dual, size_t *qs_bytes, s
     const int Tpad = (T + 7) & ~7, nb = (K + QK_K - 1) / QK_K;
     const int RG = (F + I8_ROWS - 1) / I8_ROWS;
     *qs_bytes = (size_t)Tpad * nb * QK_K;
-    *dT_bytes = (size_t)nb * Tpad * sizeof(float);
+    *dT_bytes = (size_t)nb * Tpad * (sizeof(float) + 8 * sizeof(int16_t));  // scales, then the sub-block sums
     *partial_bytes = (size_t)device_sm_count() * 2 * I8_WM * (Tpad / 8) * 4 * 32 * sizeof(float);
     *ticket_bytes = (size_t)RG * (dual ? 2 : 1) * I8_WM * sizeof(int);
 }
@@ -475,7 +495,7 @@ static cudaError_t launch_i8(const CUtensorMap &mw0, const CUtensorMap &mw1, con
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
-    cfg.blockDim = dim3(I8_THREADS, 1, 1);
+    cfg.blockDim = dim3((I8_WM * i8_wk(NT) + 1) * 32, 1, 1);
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -509,6 +529,8 @@ cudaError_t launch_gemm_i8(int kind, const void *W, const void *W2, const float 
     if (enc == nullptr) return cudaErrorNotSupported;
     const int Tpad = (T + 7) & ~7, NT = Tpad / 8, nb = (K + QK_K - 1) / QK_K;
     const long row_bytes = (long)nb * block_bytes(kind);
+    const int WK = i8_wk(NT);
+    int16_t *bsT = kind == KIND_Q4_K ? (int16_t *)(dT + (size_t)nb * Tpad) : nullptr;
     {
         cudaLaunchConfig_t cfg = {};
         const int tasks = nb * Tpad;
@@ -520,7 +542,7 @@ cudaError_t launch_gemm_i8(int kind, const void *W, const void *W2, const float 
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, quantize_i8_kernel, x, ldx, T, Tpad, K, nb, qs, dT);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, quantize_i8_kernel, x, ldx, T, Tpad, K, nb, qs, dT, bsT);
         if (e != cudaSuccess) return e;
     }
 
@@ -552,6 +574,7 @@ cudaError_t launch_gemm_i8(int kind, const void *W, const void *W2, const float 
     p.out[1] = out2;
     p.bias = bias;
     p.dT = dT;
+    p.bsT = bsT;
     p.partial = partial;
     p.tickets = tickets;
     p.err = err_flag;
@@ -560,14 +583,14 @@ cudaError_t launch_gemm_i8(int kind, const void *W, const void *W2, const float 
     p.Tpad = Tpad;
     p.F = F;
     p.ncols = nb;
-    p.NJ = (nb + I8_WK - 1) / I8_WK;
+    p.NJ = (nb + WK - 1) / WK;
     p.RG = (F + I8_ROWS - 1) / I8_ROWS;
     p.n_mats = W2 != nullptr ? 2 : 1;
     p.SU = p.RG * p.n_mats * p.NJ;
-    p.stage_bytes = i8_stage_bytes(kind, Tpad, &p.w_bytes, &p.x_bytes, &p.d_bytes);
-    p.tx_bytes = I8_WK * I8_ROWS * box_w + p.x_bytes + p.d_bytes;
+    p.stage_bytes = i8_stage_bytes(kind, Tpad, &p.w_bytes, &p.x_bytes, &p.d_bytes, &p.bs_bytes);
+    p.tx_bytes = WK * I8_ROWS * box_w + p.x_bytes + p.d_bytes + p.bs_bytes;
     if (W2 != nullptr && bias != nullptr) return cudaErrorInvalidValue;  // the dual form has no epilogue
-    const int red_bytes = I8_WM * NT * 4 * 32 * (int)sizeof(float);
+    const int red_bytes = I8_WM * (WK - 1) * NT * 4 * 32 * (int)sizeof(float);
     const int budget = 220 * 1024 - I8_HEADER - red_bytes;
     p.stages = budget / p.stage_bytes;
     if (p.stages > I8_MAX_STAGES) p.stages = I8_MAX_STAGES;

@@ -14,7 +14,7 @@ KIND_Q8_0, KIND_Q4_K, KIND_Q6_K = 5, 9, 11
 KIND_BY_NAME = {"q8_0": KIND_Q8_0, "q4_k": KIND_Q4_K, "q6_k": KIND_Q6_K}
 BLOCK_VALUES = {KIND_Q8_0: 32, KIND_Q4_K: 256, KIND_Q6_K: 256}
 BLOCK_BYTES = {KIND_Q8_0: 34, KIND_Q4_K: 144, KIND_Q6_K: 210}
-REGIME_AUTO, REGIME_GEMV, REGIME_GEMM, REGIME_GEMV_PLAIN = 0, 1, 2, 3
+REGIME_AUTO, REGIME_GEMV, REGIME_GEMM, REGIME_GEMV_PLAIN, REGIME_I8MMA = 0, 1, 2, 3, 4
 ROUTER_SOFTMAX_SELECTED, ROUTER_RENORMALIZE_SELECTED = 0, 2
 FFN_SWIGLU, FFN_GEGLU = 0, 2
 

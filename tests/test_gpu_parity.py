@@ -520,7 +520,11 @@ def test_integer_mma_matmul_vs_oracle(ctx, oracle, name, T, K, F):
     bias = rng.normal(0, 1, F).astype(np.float32)
     xd = torch.from_numpy(xbuf).cuda()[:, :K]
     l0 = ctx.launch_count()
-    got = ctx.linear(kind, xd, ctx.upload(W), F, bias=torch.from_numpy(bias).cuda()).cpu().numpy()
+    ctx.set_regime(4)  # REGIME_I8MMA: this kernel for every token count it covers, not only where it is the fastest
+    try:
+        got = ctx.linear(kind, xd, ctx.upload(W), F, bias=torch.from_numpy(bias).cuda()).cpu().numpy()
+    finally:
+        ctx.set_regime(0)
     assert ctx.launch_count() - l0 == 2  # the activation packer and the matmul
     want = oracle.linear(kind, np.ascontiguousarray(x), W, F, bias=bias)
     err = max_rel_err(got, want)
@@ -538,10 +542,14 @@ def test_integer_mma_dual_output(ctx, oracle, T):
     x = rng.normal(0, 1, (T, K)).astype(np.float32)
     a = torch.empty((T, F), dtype=torch.float32, device="cuda")
     b = torch.empty((T, F), dtype=torch.float32, device="cuda")
-    ctx.linear_dual(KINDS["q4_k"], torch.from_numpy(x).cuda(), ctx.upload(Wa), ctx.upload(Wb), F, out_a=a, out_b=b)
-    assert max_rel_err(a.cpu().numpy(), oracle.linear(KINDS["q4_k"], x, Wa, F)) <= 2e-5
-    assert max_rel_err(b.cpu().numpy(), oracle.linear(KINDS["q4_k"], x, Wb, F)) <= 2e-5
-    # twice more on the same context: the tickets were left at zero
-    for _ in range(2):
+    ctx.set_regime(4)
+    try:
         ctx.linear_dual(KINDS["q4_k"], torch.from_numpy(x).cuda(), ctx.upload(Wa), ctx.upload(Wb), F, out_a=a, out_b=b)
-    assert max_rel_err(b.cpu().numpy(), oracle.linear(KINDS["q4_k"], x, Wb, F)) <= 2e-5
+        assert max_rel_err(a.cpu().numpy(), oracle.linear(KINDS["q4_k"], x, Wa, F)) <= 2e-5
+        assert max_rel_err(b.cpu().numpy(), oracle.linear(KINDS["q4_k"], x, Wb, F)) <= 2e-5
+        # twice more on the same context: the tickets were left at zero
+        for _ in range(2):
+            ctx.linear_dual(KINDS["q4_k"], torch.from_numpy(x).cuda(), ctx.upload(Wa), ctx.upload(Wb), F, out_a=a, out_b=b)
+        assert max_rel_err(b.cpu().numpy(), oracle.linear(KINDS["q4_k"], x, Wb, F)) <= 2e-5
+    finally:
+        ctx.set_regime(0)
