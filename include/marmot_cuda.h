@@ -159,6 +159,40 @@ int mcu_linear_dual(
     size_t K, size_t F, float *out_a_dev, float *out_b_dev, size_t ldo
 );
 
+/* ---- several weights, one activation read, optionally through one of the decoder layer's elementwise steps:
+ *      marmot_matmul_qkv_shared_input with separate wq / wk / wv (include/marmot/ops/matmul.h:74-122,
+ *      src/backends/cpu/ops/matmul/qkv/matmul_qkv.c) generalised to 1..4 weights that may differ in kind and F, plus
+ *      the step that produces the activations in the GGUF graph (src/graph/gguf/graph_builder.cpp:1454-2400):
+ *        MCU_PROLOGUE_ADD_RMSNORM  x' = x + aux (aux may be NULL); the weights multiply
+ *                                  rms_norm(x') * (norm_weight + weight_offset); x' is stored to x_out when that is
+ *                                  set.  x_out must not overlap x or aux.
+ *        MCU_PROLOGUE_SWIGLU       the weights multiply silu(x) * aux (x = gate, aux = up projection)
+ *      Up to 8 tokens with every weight on the streaming path this is ONE launch; otherwise the prologue runs as its
+ *      stand-alone kernel (which needs contiguous rows: ldx = ld_aux = ld_x_out = K) followed by the matmuls. ---- */
+enum { MCU_PROLOGUE_NONE = 0, MCU_PROLOGUE_ADD_RMSNORM = 1, MCU_PROLOGUE_SWIGLU = 2 };
+#define MCU_LINEAR_MAX_JOBS 4
+typedef struct mcu_linear_job {
+    int kind;
+    const void *w_dev;
+    size_t F;
+    const float *bias_dev; /* may be NULL */
+    float *out_dev;
+    size_t ldo;
+} mcu_linear_job_t;
+typedef struct mcu_prologue {
+    int op;
+    const float *aux_dev;
+    size_t ld_aux;
+    const float *norm_weight_dev; /* may be NULL: plain normalisation */
+    float eps, weight_offset;
+    float *x_out_dev; /* may be NULL */
+    size_t ld_x_out;
+} mcu_prologue_t;
+int mcu_linear_multi(
+    mcu_context_t *ctx, const float *x_dev, size_t ldx, size_t T, size_t K, const mcu_prologue_t *prologue,
+    const mcu_linear_job_t *jobs, size_t n_jobs
+);
+
 /* Same as mcu_linear with host activations / bias / output; weights stay device resident (made so once
  * with mcu_malloc + mcu_memcpy_to_device, the residency contract of marmot_tensor_to_device,
  * src/core/tensor/transfer.c:22). */

@@ -78,6 +78,7 @@ struct mcu_context {
     Buffer act_qs, act_d, act_bsums, act_half, act_rowscale, x_stage, out_stage, bias_stage;
     Buffer moe_meta, moe_hidden, moe_gate, moe_up, moe_down;
     Buffer gemm_partial;         // split-K partial tiles
+    Buffer pro_h;                   // activations after a stand-alone prologue kernel (mcu_linear_multi's general form)
     Buffer i8_partial, i8_tickets;  // integer-MMA matmul: shares of row groups split between CTAs, and their tickets
     Buffer attn_partial;         // split-KV partial attention states
     int *gemm_counters = nullptr;  // split-K tile tickets (zero between launches)
@@ -217,7 +218,7 @@ void mcu_context_destroy(mcu_context_t *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     Buffer *bufs[] = {&ctx->act_qs,   &ctx->act_d,      &ctx->act_bsums, &ctx->act_half, &ctx->act_rowscale, &ctx->x_stage, &ctx->out_stage,
-                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down, &ctx->gemm_partial, &ctx->attn_partial, &ctx->i8_partial, &ctx->i8_tickets};
+                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down, &ctx->gemm_partial, &ctx->attn_partial, &ctx->i8_partial, &ctx->i8_tickets, &ctx->pro_h};
     for (Buffer *b : bufs)
         if (b->ptr != nullptr) cudaFree(b->ptr);
     if (ctx->dev_err != nullptr) cudaFree(ctx->dev_err);
@@ -655,6 +656,91 @@ int mcu_linear_dual(mcu_context_t *ctx, int kind, const float *x_dev, size_t ldx
     if (int rc = validate_linear(kind, x_dev, w_b_dev, out_b_dev, T, K, F, ldx, ldo)) return rc;
     std::lock_guard<std::mutex> lock(ctx->mu);
     return linear_locked(ctx, kind, x_dev, ldx, w_a_dev, w_b_dev, T, K, F, nullptr, out_a_dev, out_b_dev, ldo);
+}
+
+int mcu_linear_multi(mcu_context_t *ctx, const float *x_dev, size_t ldx, size_t T, size_t K, const mcu_prologue_t *prologue,
+                     const mcu_linear_job_t *jobs, size_t n_jobs) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (jobs == nullptr || n_jobs == 0 || n_jobs > (size_t)MCU_LINEAR_MAX_JOBS)
+        return fail(MCU_ERROR_INVALID_ARGUMENT, "between 1 and %d jobs", MCU_LINEAR_MAX_JOBS);
+    static_assert(MCU_LINEAR_MAX_JOBS == GEMV_MAX_JOBS, "public and kernel job limits differ");
+    if (T == 0) return MCU_SUCCESS;
+    mcu_prologue_t none = {};
+    const mcu_prologue_t &pr = prologue != nullptr ? *prologue : none;
+    if (pr.op != MCU_PROLOGUE_NONE && pr.op != MCU_PROLOGUE_ADD_RMSNORM && pr.op != MCU_PROLOGUE_SWIGLU)
+        return fail(MCU_ERROR_INVALID_ARGUMENT, "unknown prologue %d", pr.op);
+    if (pr.op == MCU_PROLOGUE_SWIGLU && pr.aux_dev == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "SwiGLU needs the up projection");
+    if (pr.op != MCU_PROLOGUE_NONE) {
+        if ((pr.aux_dev != nullptr && pr.ld_aux < K) || (pr.x_out_dev != nullptr && pr.ld_x_out < K))
+            return fail(MCU_ERROR_DIMENSION_MISMATCH, "row stride smaller than the row");
+        if (pr.ld_aux > (size_t)INT_MAX || pr.ld_x_out > (size_t)INT_MAX) return fail(MCU_ERROR_INVALID_ARGUMENT, "row stride too large");
+        if (pr.op == MCU_PROLOGUE_ADD_RMSNORM && pr.x_out_dev != nullptr &&
+            (pr.x_out_dev == x_dev || pr.x_out_dev == pr.aux_dev))
+            return fail(MCU_ERROR_INVALID_ARGUMENT, "x_out must not overlap the inputs");
+    }
+    GemvJobSpec specs[GEMV_MAX_JOBS];
+    for (size_t j = 0; j < n_jobs; ++j) {
+        const mcu_linear_job_t &jb = jobs[j];
+        if (jb.F == 0) return fail(MCU_ERROR_DIMENSION_MISMATCH, "F must be positive");
+        if (int rc = validate_linear(jb.kind, x_dev, jb.w_dev, jb.out_dev, T, K, jb.F, ldx, jb.ldo)) return rc;
+        specs[j] = GemvJobSpec{jb.kind, jb.w_dev, (int)jb.F, jb.bias_dev, jb.out_dev, (int)jb.ldo};
+    }
+    GemvPrologue gp;
+    gp.op = pr.op;
+    if (pr.op != MCU_PROLOGUE_NONE) {
+        gp.aux = pr.aux_dev;
+        gp.ld_aux = (int)pr.ld_aux;
+        gp.norm_w = pr.norm_weight_dev;
+        gp.eps = pr.eps;
+        gp.w_off = pr.weight_offset;
+        gp.x_out = pr.op == MCU_PROLOGUE_ADD_RMSNORM ? pr.x_out_dev : nullptr;
+        gp.ld_x_out = (int)pr.ld_x_out;
+    }
+    float *h = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        if ((ctx->regime == MCU_REGIME_AUTO || ctx->regime == MCU_REGIME_GEMV) && T <= (size_t)GEMV_MAX_T &&
+            gemv_stream_jobs_supported(specs, (int)n_jobs, (int)T, (int)K, gp)) {
+            MCU_CUDA(launch_gemv_stream_jobs(specs, (int)n_jobs, x_dev, (int)ldx, (int)T, (int)K, gp, ctx->dev_err, ctx->stream));
+            count_launches(1);
+            return MCU_SUCCESS;
+        }
+        if (pr.op != MCU_PROLOGUE_NONE) {
+            if (ldx != K || (pr.aux_dev != nullptr && pr.ld_aux != K) || (gp.x_out != nullptr && pr.ld_x_out != K))
+                return fail(MCU_ERROR_NOT_IMPLEMENTED, "the stand-alone prologue kernels need contiguous rows");
+            if (int rc = ensure(ctx, ctx->pro_h, T * K * sizeof(float))) return rc;
+            h = (float *)ctx->pro_h.ptr;
+        }
+    }
+    // The general form: the prologue as its own kernel into the context's scratch, then the matmuls (pairs of equal
+    // shape share their activation packing).
+    const float *act = x_dev;
+    size_t ld_act = ldx;
+    if (pr.op == MCU_PROLOGUE_ADD_RMSNORM) {
+        if (pr.aux_dev != nullptr && gp.x_out != nullptr) {
+            if (int rc = mcu_add_rmsnorm(ctx, x_dev, pr.aux_dev, pr.norm_weight_dev, T, K, pr.eps, pr.weight_offset, gp.x_out, h))
+                return rc;
+        } else {
+            if (int rc = mcu_rmsnorm(ctx, x_dev, pr.aux_dev, pr.norm_weight_dev, T, K, pr.eps, pr.weight_offset, h)) return rc;
+            if (gp.x_out != nullptr)  // no aux: x' = x
+                MCU_CUDA(cudaMemcpyAsync(gp.x_out, x_dev, T * K * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+        }
+        act = h, ld_act = K;
+    } else if (pr.op == MCU_PROLOGUE_SWIGLU) {
+        if (int rc = mcu_swiglu(ctx, x_dev, pr.aux_dev, T * K, h)) return rc;
+        act = h, ld_act = K;
+    }
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    for (size_t j = 0; j < n_jobs;) {
+        const mcu_linear_job_t &a = jobs[j];
+        const bool pair = j + 1 < n_jobs && jobs[j + 1].kind == a.kind && jobs[j + 1].F == a.F && jobs[j + 1].ldo == a.ldo &&
+            a.bias_dev == nullptr && jobs[j + 1].bias_dev == nullptr;
+        if (int rc = linear_locked(ctx, a.kind, act, ld_act, a.w_dev, pair ? jobs[j + 1].w_dev : nullptr, T, K, a.F, a.bias_dev,
+                                   a.out_dev, pair ? jobs[j + 1].out_dev : nullptr, a.ldo))
+            return rc;
+        j += pair ? 2 : 1;
+    }
+    return MCU_SUCCESS;
 }
 
 int mcu_linear_host(mcu_context_t *ctx, int kind, const float *x_host, size_t ldx, const void *w_dev, size_t T,

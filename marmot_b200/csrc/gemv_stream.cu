@@ -25,20 +25,29 @@ namespace mcu {
 
 constexpr int GS_MAX_STAGES = 8;
 constexpr int GS_ACT_BLOCK = 272;  // 256 int8 + 16 pad: conflict-free 16-byte reads by the lane pairs
-constexpr int GS_HEADER = 256;     // barriers + flags at the start of shared memory
+constexpr int GS_HEADER = 1024;    // barriers, flags and the prologue's reduction scratch at the start of shared memory
+constexpr int GS_RED_OFFSET = 256; // floats: inv[GEMV_MAX_T] then red[GEMV_MAX_T][16]
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
+constexpr int KIND_MIXED = 0;      // template value: the block format is the job's (K-quants only)
+
+// One weight matrix of a launch: rows [0, F) dealt out to the CTAs [cta_begin, next job's cta_begin).
+struct GemvJob {
+    const uint8_t *W;
+    float *out;
+    const float *bias;
+    int F, ldo, kind, row_bytes, rows_per_cta, rows_per_chunk, cta_begin;
+};
 
 struct GemvStreamParams {
-    const uint8_t *W[2];
-    float *out[2];
+    GemvJob job[GEMV_MAX_JOBS];
+    int n_jobs;
     const float *x;
-    const float *bias;
     int *err;
-    int ldx, ldo, K, nb, F;
-    int row_bytes, rows_per_cta, rows_per_chunk;
+    int ldx, K, nb;
     int act_bytes;     // shared memory reserved for the quantized activations (multiple of 128)
     int stages;        // ring depth, <= GS_MAX_STAGES
     int stage_stride;  // bytes between stage buffers (multiple of 128, includes over-read slack)
+    GemvPrologue pro;  // what happens to the activations before they are quantized
 #ifdef MCU_TRACE
     int trace_slot;
 #endif
@@ -156,6 +165,148 @@ __device__ __forceinline__ ActSmem act_layout(uint8_t *base, int T, int nb) {
 __host__ __device__ inline int act_smem_bytes(bool kq, int T, int nb) {
     const int bytes = kq ? T * nb * (GS_ACT_BLOCK + 4 + 16) + 16 : T * (((nb * Q8_0_VALUES + 15) & ~15) + nb * 4);
     return (bytes + 127) & ~127;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Prologues: an elementwise step of the decoder layer applied to the activations on their way into the packer.
+// ---------------------------------------------------------------------------------------------
+// Per-token 1 / rms of x + aux over the K values (RMSNorm's statistic); CTA 0 also stores x + aux to x_out.
+// red: GEMV_MAX_T * 16 floats of scratch, inv_s: GEMV_MAX_T floats; both in shared memory.  Ends with the consumer
+// barrier, after which inv_s is valid.
+template <int T, int NTHREADS>
+__device__ __forceinline__ void pro_rms_stats(const GemvStreamParams &p, int tid, float *red, float *inv_s) {
+    const GemvPrologue &g = p.pro;
+    const int warp = tid >> 5, lane = tid & 31;
+    const bool write_x = g.x_out != nullptr && blockIdx.x == 0;
+    const bool vec = ((((uintptr_t)p.x | (uintptr_t)g.aux | (uintptr_t)g.x_out) & 15) == 0) &&
+        (((p.ldx | g.ld_aux | g.ld_x_out | p.K) & 3) == 0);
+    float s[T];
+#pragma unroll
+    for (int t = 0; t < T; ++t) s[t] = 0.0f;
+    if (vec) {
+        for (int i = tid * 4; i < p.K; i += NTHREADS * 4) {
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                float4 v = __ldg((const float4 *)(p.x + (size_t)t * p.ldx + i));
+                if (g.aux != nullptr) {
+                    const float4 d = __ldg((const float4 *)(g.aux + (size_t)t * g.ld_aux + i));
+                    v.x = __fadd_rn(v.x, d.x), v.y = __fadd_rn(v.y, d.y), v.z = __fadd_rn(v.z, d.z), v.w = __fadd_rn(v.w, d.w);
+                }
+                if (write_x) *(float4 *)(g.x_out + (size_t)t * g.ld_x_out + i) = v;
+                s[t] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+        }
+    } else {
+        for (int i = tid; i < p.K; i += NTHREADS) {
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                float v = __ldg(p.x + (size_t)t * p.ldx + i);
+                if (g.aux != nullptr) v = __fadd_rn(v, __ldg(g.aux + (size_t)t * g.ld_aux + i));
+                if (write_x) g.x_out[(size_t)t * g.ld_x_out + i] = v;
+                s[t] += v * v;
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+        const float w = warp_sum(s[t]);
+        if (lane == 0) red[t * 16 + warp] = w;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(NTHREADS) : "memory");
+    if (tid < T) {
+        float sum = 0.0f;
+        for (int w = 0; w < NTHREADS / 32; ++w) sum += red[tid * 16 + w];
+        inv_s[tid] = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(sum, (float)p.K), g.eps)));
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(NTHREADS) : "memory");
+}
+
+// NV consecutive values of token t from k0 on, through the prologue PRO (a template parameter so that the plain path
+// keeps its registers); zeros past K.  vec: every pointer and stride involved allows 16-byte loads and K % 4 == 0.
+template <int NV, int PRO>
+__device__ __forceinline__ void load_values_pro(const GemvStreamParams &p, bool vec, bool valid, int t, int k0, const float *inv_s,
+                                                float (&v)[NV]) {
+    const GemvPrologue &g = p.pro;
+    const float *xr = p.x + (size_t)t * p.ldx;
+    const float *ar = g.aux != nullptr ? g.aux + (size_t)t * g.ld_aux : nullptr;
+    float b[NV], w[NV];
+    if (vec) {
+#pragma unroll
+        for (int i = 0; i < NV / 4; ++i) {
+            const int k = k0 + 4 * i;
+            const bool in = valid && k < p.K;
+            const float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const float4 xv = in ? __ldg((const float4 *)(xr + k)) : z;
+            const float4 av = in && ar != nullptr ? __ldg((const float4 *)(ar + k)) : z;
+            const float4 wv = in && PRO == GEMV_PRO_ADD_RMSNORM && g.norm_w != nullptr ? __ldg((const float4 *)(g.norm_w + k)) : z;
+            v[4 * i] = xv.x, v[4 * i + 1] = xv.y, v[4 * i + 2] = xv.z, v[4 * i + 3] = xv.w;
+            b[4 * i] = av.x, b[4 * i + 1] = av.y, b[4 * i + 2] = av.z, b[4 * i + 3] = av.w;
+            w[4 * i] = wv.x, w[4 * i + 1] = wv.y, w[4 * i + 2] = wv.z, w[4 * i + 3] = wv.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int k = k0 + i;
+            const bool in = valid && k < p.K;
+            v[i] = in ? __ldg(xr + k) : 0.0f;
+            b[i] = in && ar != nullptr ? __ldg(ar + k) : 0.0f;
+            w[i] = in && PRO == GEMV_PRO_ADD_RMSNORM && g.norm_w != nullptr ? __ldg(g.norm_w + k) : 0.0f;
+        }
+    }
+    const float inv = PRO == GEMV_PRO_ADD_RMSNORM ? inv_s[t] : 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (PRO == GEMV_PRO_ADD_RMSNORM) {  // same operation order as the stand-alone add + rms_norm kernels
+            float y = ar != nullptr ? __fadd_rn(v[i], b[i]) : v[i];
+            y = __fmul_rn(y, inv);
+            if (g.norm_w != nullptr) y = __fmul_rn(y, __fadd_rn(w[i], g.w_off));
+            v[i] = y;
+        } else {  // silu(x) * aux, as the stand-alone SwiGLU kernel
+            v[i] = __fmul_rn(__fdiv_rn(v[i], __fadd_rn(1.0f, expf(-v[i]))), b[i]);
+        }
+    }
+}
+
+__device__ __forceinline__ bool pro_vec_ok(const GemvStreamParams &p) {
+    const GemvPrologue &g = p.pro;
+    return ((((uintptr_t)p.x | (uintptr_t)g.aux | (uintptr_t)g.norm_w) & 15) == 0) && (((p.ldx | g.ld_aux | p.K) & 3) == 0);
+}
+
+// The packers with a prologue: same lane layout as the plain ones, values transformed between the load and the packing.
+template <int LPB, int PRO>
+__device__ __forceinline__ void quantize_all_q8_k_pro(const GemvStreamParams &p, int T, const ActSmem &a, int tid, int n_threads,
+                                                      const float *inv_s) {
+    constexpr int NV = QK_K / LPB;
+    const int lane = tid & 31, sl = lane & (LPB - 1);
+    const int groups = n_threads / LPB, gid = tid / LPB;
+    const int nb = p.nb, tasks = T * nb;
+    const bool vec = pro_vec_ok(p);
+    for (int base = 0; base < tasks; base += groups) {
+        const int task = base + gid;
+        const bool valid = task < tasks;
+        const int t = valid ? task / nb : 0, blk = valid ? task - t * nb : 0;
+        float v[NV];
+        load_values_pro<NV, PRO>(p, vec, valid, t, blk * QK_K + NV * sl, inv_s, v);
+        pack_values_q8_k<LPB>(v, valid, lane, a.qs + (size_t)t * a.tstride + (size_t)blk * GS_ACT_BLOCK, a.d + t * nb + blk,
+                              a.bs32 + ((size_t)t * nb + blk) * 8);
+    }
+}
+
+template <int PRO>
+__device__ __forceinline__ void quantize_all_q8_0_pro(const GemvStreamParams &p, int T, const ActSmem &a, int tid, int n_threads,
+                                                      const float *inv_s) {
+    const int sl = tid & 3;
+    const int groups = n_threads / 4, gid = tid / 4;
+    const int nb = p.nb, tasks = T * nb;
+    const bool vec = pro_vec_ok(p);
+    for (int base = 0; base < tasks; base += groups) {
+        const int task = base + gid;
+        const bool valid = task < tasks;
+        const int t = valid ? task / nb : 0, blk = valid ? task - t * nb : 0;
+        float v[8];
+        load_values_pro<8, PRO>(p, vec, valid, t, blk * Q8_0_VALUES + 8 * sl, inv_s, v);
+        pack_values_q8_0(v, valid, sl, a.qs + (size_t)t * a.tstride + (size_t)blk * Q8_0_VALUES, a.d + t * nb + blk);
+    }
 }
 
 // All (token, block) pairs of the call by the consumer threads: groups of LPB lanes take blocks round robin; the
@@ -617,24 +768,23 @@ __device__ __forceinline__ void rows2_q8_0(const uint8_t *w0, const uint8_t *w1,
 }
 
 // ---------------------------------------------------------------------------------------------
-// The kernel.  TEAMS * TW consumer warps + one producer warp; grid = (CTAs, 1 or 2): blockIdx.y selects the weight
-// matrix of a dual-output call.  A chunk of the ring holds at most TW rows, one per warp of a team.  With one or two
-// tokens a team takes the chunks in pairs (two rows per warp at a time, see rows2_*) and the teams take the pairs in
-// turn; with more tokens there is one team and it takes the chunks one by one.  MINB = 2 keeps the CTA within half
-// of an SM.
+// The kernel.  TW consumer warps + one producer warp; the CTAs [job.cta_begin, next job's cta_begin) work on one weight
+// matrix of the launch.  A chunk of the ring holds at most TW rows, one per warp.  With one or two tokens (Q4_K, and
+// Q8_0 at two) the warps take the chunks in pairs, two rows per warp at a time (see rows2_*); otherwise chunk by chunk.
+// MINB = 2 keeps the CTA within half of an SM.  KIND is the block format of all the launch's matrices, or KIND_MIXED
+// when Q4_K and Q6_K matrices share a launch (the CTA then branches on its job's format).
 // ---------------------------------------------------------------------------------------------
 template <int KIND, int T, int TW, int TEAMS, int MINB>
 __global__ void __launch_bounds__((TW * TEAMS + 1) * 32, MINB) gemv_stream_kernel(const GemvStreamParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
+    static_assert(TEAMS == 1, "one team of consumer warps");
     constexpr bool KQ = KIND != KIND_Q8_0;
-    constexpr int NW = TW * TEAMS;
-    // Row pairs pay where a row's fixed part dominates (Q4_K); the 2-byte aligned formats are bound by their 32-bit
-    // shared-memory reads, which pairing does not reduce (measured: Q6_K 22 -> 27 us at T = 1, F = 28672).
-    constexpr bool PAIRS = (KIND == KIND_Q4_K && T <= 2) || (KIND == KIND_Q8_0 && T == 2);
-    static_assert(PAIRS || TEAMS == 1, "several teams only in the two-row form");
+    constexpr int NW = TW;
     uint64_t *full = (uint64_t *)smem;
     uint64_t *empty = full + GS_MAX_STAGES;
     int *abort_flag = (int *)(empty + GS_MAX_STAGES);
+    float *inv_s = (float *)(smem + GS_RED_OFFSET);
+    float *red = inv_s + GEMV_MAX_T;
     uint8_t *act_base = smem + GS_HEADER;
     uint8_t *stage_base = act_base + p.act_bytes;
     const int S = p.stages;
@@ -642,18 +792,27 @@ __global__ void __launch_bounds__((TW * TEAMS + 1) * 32, MINB) gemv_stream_kerne
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) GS_TRACE_POINT(0);
     if (threadIdx.x == 0) GS_TRACE_CLOCK(9);
-    const uint8_t *W = blockIdx.y == 0 ? p.W[0] : p.W[1];
-    float *out = blockIdx.y == 0 ? p.out[0] : p.out[1];
-    const int r0 = blockIdx.x * p.rows_per_cta;
-    const int r1 = min(p.F, r0 + p.rows_per_cta);
+    // this CTA's job: selects instead of an indexed read of the parameter block
+    GemvJob job = p.job[0];
+#pragma unroll
+    for (int i = 1; i < GEMV_MAX_JOBS; ++i)
+        if (i < p.n_jobs && (int)blockIdx.x >= p.job[i].cta_begin) job = p.job[i];
+    const int kind = KIND == KIND_MIXED ? job.kind : KIND;
+    // Row pairs pay where a row's fixed part dominates (Q4_K); the 2-byte aligned formats are bound by their 32-bit
+    // shared-memory reads, which pairing does not reduce (measured: Q6_K 22 -> 27 us at T = 1, F = 28672).
+    const bool pairs = (kind == KIND_Q4_K && T <= 2) || (kind == KIND_Q8_0 && T == 2);
+    const uint8_t *W = job.W;
+    float *out = job.out;
+    const int r0 = ((int)blockIdx.x - job.cta_begin) * job.rows_per_cta;
+    const int r1 = min(job.F, r0 + job.rows_per_cta);
     const int n_rows = max(0, r1 - r0);
-    const int RC = p.rows_per_chunk;
+    const int RC = job.rows_per_chunk;
     const int n_chunks = (n_rows + RC - 1) / RC;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < S; ++i) {
             mbar_init(&full[i], 1);
-            mbar_init(&empty[i], TW);  // a chunk is read by the warps of one team
+            mbar_init(&empty[i], TW);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -674,9 +833,9 @@ __global__ void __launch_bounds__((TW * TEAMS + 1) * 32, MINB) gemv_stream_kerne
                     break;
                 }
                 const int rows = min(RC, n_rows - c * RC);
-                const uint32_t bytes = (uint32_t)rows * (uint32_t)p.row_bytes;
+                const uint32_t bytes = (uint32_t)rows * (uint32_t)job.row_bytes;
                 mbar_expect_tx(&full[st], bytes);
-                bulk_g2s(stage_base + (size_t)st * p.stage_stride, W + ((size_t)r0 + (size_t)c * RC) * p.row_bytes, bytes,
+                bulk_g2s(stage_base + (size_t)st * p.stage_stride, W + ((size_t)r0 + (size_t)c * RC) * job.row_bytes, bytes,
                          &full[st]);
             }
             GS_TRACE_POINT(6);
@@ -695,19 +854,36 @@ __global__ void __launch_bounds__((TW * TEAMS + 1) * 32, MINB) gemv_stream_kerne
     constexpr int TRACE_SLOT = 0;
 #endif
     GS_TRACE_CLOCK_AT(TRACE_SLOT, 11);
-    if (KQ) {
-        // as many lanes per block as there are threads for: one round of loads when the blocks are few
-        const int tasks = T * p.nb;
-        if (tasks * 32 <= NW * 32) {
-            quantize_all_q8_k<32>(p.x, p.ldx, T, p.K, p.nb, a, threadIdx.x, NW * 32, TRACE_SLOT);
-        } else if (tasks * 16 <= NW * 32 || MINB > 1) {
-            quantize_all_q8_k<16>(p.x, p.ldx, T, p.K, p.nb, a, threadIdx.x, NW * 32, TRACE_SLOT);
+    if (p.pro.op == GEMV_PRO_NONE) {
+        if (KQ) {
+            // as many lanes per block as there are threads for: one round of loads when the blocks are few
+            const int tasks = T * p.nb;
+            if (tasks * 32 <= NW * 32) {
+                quantize_all_q8_k<32>(p.x, p.ldx, T, p.K, p.nb, a, threadIdx.x, NW * 32, TRACE_SLOT);
+            } else if (tasks * 16 <= NW * 32 || MINB > 1) {
+                quantize_all_q8_k<16>(p.x, p.ldx, T, p.K, p.nb, a, threadIdx.x, NW * 32, TRACE_SLOT);
+            } else {
+                // 32 values per lane: only where a thread may use more than 64 registers
+                if constexpr (MINB == 1) quantize_all_q8_k<8>(p.x, p.ldx, T, p.K, p.nb, a, threadIdx.x, NW * 32, TRACE_SLOT);
+            }
         } else {
-            // 32 values per lane: only where a thread may use more than 64 registers
-            if constexpr (MINB == 1) quantize_all_q8_k<8>(p.x, p.ldx, T, p.K, p.nb, a, threadIdx.x, NW * 32, TRACE_SLOT);
+            quantize_all_q8_0(p.x, p.ldx, T, p.K, p.nb, a, threadIdx.x, NW * 32);
+        }
+    } else if (p.pro.op == GEMV_PRO_ADD_RMSNORM) {
+        pro_rms_stats<T, NW * 32>(p, threadIdx.x, red, inv_s);
+        if (KQ) {
+            if (T * p.nb * 32 <= NW * 32) quantize_all_q8_k_pro<32, GEMV_PRO_ADD_RMSNORM>(p, T, a, threadIdx.x, NW * 32, inv_s);
+            else quantize_all_q8_k_pro<16, GEMV_PRO_ADD_RMSNORM>(p, T, a, threadIdx.x, NW * 32, inv_s);
+        } else {
+            quantize_all_q8_0_pro<GEMV_PRO_ADD_RMSNORM>(p, T, a, threadIdx.x, NW * 32, inv_s);
         }
     } else {
-        quantize_all_q8_0(p.x, p.ldx, T, p.K, p.nb, a, threadIdx.x, NW * 32);
+        if (KQ) {
+            if (T * p.nb * 32 <= NW * 32) quantize_all_q8_k_pro<32, GEMV_PRO_SWIGLU>(p, T, a, threadIdx.x, NW * 32, inv_s);
+            else quantize_all_q8_k_pro<16, GEMV_PRO_SWIGLU>(p, T, a, threadIdx.x, NW * 32, inv_s);
+        } else {
+            quantize_all_q8_0_pro<GEMV_PRO_SWIGLU>(p, T, a, threadIdx.x, NW * 32, inv_s);
+        }
     }
     if (threadIdx.x == 0) GS_TRACE_POINT(8);
     GS_TRACE_CLOCK_AT(TRACE_SLOT, 14);
@@ -715,10 +891,10 @@ __global__ void __launch_bounds__((TW * TEAMS + 1) * 32, MINB) gemv_stream_kerne
     GS_TRACE_CLOCK_AT(TRACE_SLOT, 15);
     if (threadIdx.x == 0) GS_TRACE_POINT(3);
 
-    if (PAIRS) {
-        const int team = warp / TW, tw = warp - team * TW;
+    if (pairs) {
+        const int tw = warp;
         const int n_pairs = (n_chunks + 1) / 2;
-        for (int jp = team; jp < n_pairs; jp += TEAMS) {
+        for (int jp = 0; jp < n_pairs; ++jp) {
             const int c0 = 2 * jp, c1 = c0 + 1;
             const bool two = c1 < n_chunks;
             const int st0 = c0 % S, st1 = c1 % S;
@@ -737,16 +913,20 @@ __global__ void __launch_bounds__((TW * TEAMS + 1) * 32, MINB) gemv_stream_kerne
             const int rl0 = (tw - (c0 * RC) % TW + TW) % TW, rl1 = (tw - (c1 * RC) % TW + TW) % TW;
             const bool v0 = rl0 < rows0, v1 = rl1 < rows1;
             if (v0 || v1) {
-                const uint8_t *wa = stage_base + (size_t)st0 * p.stage_stride + (size_t)rl0 * p.row_bytes;
-                const uint8_t *wb = stage_base + (size_t)st1 * p.stage_stride + (size_t)rl1 * p.row_bytes;
+                const uint8_t *wa = stage_base + (size_t)st0 * p.stage_stride + (size_t)rl0 * job.row_bytes;
+                const uint8_t *wb = stage_base + (size_t)st1 * p.stage_stride + (size_t)rl1 * job.row_bytes;
                 if (!v0) wa = wb;  // a lone row is computed twice and stored once
                 if (!v1) wb = wa;
                 float mine[T];
 #pragma unroll
                 for (int t = 0; t < T; ++t) mine[t] = 0.0f;
-                if (KIND == KIND_Q4_K) rows2_q4_k<T>(wa, wb, a, p.nb, lane, mine);
-                else if (KIND == KIND_Q6_K) rows2_q6_k<T>(wa, wb, a, p.nb, lane, mine);
-                else rows2_q8_0<T>(wa, wb, a, p.nb, lane, mine);
+                if (kind == KIND_Q4_K) {
+                    if constexpr (KIND == KIND_Q4_K || KIND == KIND_MIXED) rows2_q4_k<T>(wa, wb, a, p.nb, lane, mine);
+                } else if (kind == KIND_Q6_K) {
+                    if constexpr (KIND == KIND_Q6_K) rows2_q6_k<T>(wa, wb, a, p.nb, lane, mine);
+                } else {
+                    if constexpr (KIND == KIND_Q8_0) rows2_q8_0<T>(wa, wb, a, p.nb, lane, mine);
+                }
 #ifdef MCU_TRACE
                 asm volatile("" ::"f"(mine[0]));
                 if (__float_as_uint(mine[0]) == 0x7fc12345u) return;
@@ -761,7 +941,7 @@ __global__ void __launch_bounds__((TW * TEAMS + 1) * 32, MINB) gemv_stream_kerne
                     v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
                     v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 8));
                     v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 16));
-                    if (store) out[(size_t)t * p.ldo + f] = p.bias != nullptr ? __fadd_rn(v, p.bias[f]) : v;
+                    if (store) out[(size_t)t * job.ldo + f] = job.bias != nullptr ? __fadd_rn(v, job.bias[f]) : v;
                 }
             }
             __syncwarp();
@@ -787,15 +967,19 @@ __global__ void __launch_bounds__((TW * TEAMS + 1) * 32, MINB) gemv_stream_kerne
                 float acc[T];
 #pragma unroll
                 for (int t = 0; t < T; ++t) acc[t] = 0.0f;
-                const uint8_t *wrow = sbuf + (size_t)rl * p.row_bytes;
-                if (KIND == KIND_Q4_K) row_q4_k<T>(wrow, a, p.nb, lane, acc);
-                else if (KIND == KIND_Q6_K) row_q6_k<T>(wrow, a, p.nb, lane, acc);
-                else row_q8_0<T>(wrow, a, p.nb, lane, acc);
+                const uint8_t *wrow = sbuf + (size_t)rl * job.row_bytes;
+                if (kind == KIND_Q4_K) {
+                    if constexpr (KIND == KIND_Q4_K || KIND == KIND_MIXED) row_q4_k<T>(wrow, a, p.nb, lane, acc);
+                } else if (kind == KIND_Q6_K) {
+                    if constexpr (KIND == KIND_Q6_K || KIND == KIND_MIXED) row_q6_k<T>(wrow, a, p.nb, lane, acc);
+                } else {
+                    if constexpr (KIND == KIND_Q8_0) row_q8_0<T>(wrow, a, p.nb, lane, acc);
+                }
                 const int f = r0 + c * RC + rl;
 #pragma unroll
                 for (int t = 0; t < T; ++t) {
                     const float v = warp_sum(acc[t]);
-                    if (lane == 0) out[(size_t)t * p.ldo + f] = p.bias != nullptr ? __fadd_rn(v, p.bias[f]) : v;
+                    if (lane == 0) out[(size_t)t * job.ldo + f] = job.bias != nullptr ? __fadd_rn(v, job.bias[f]) : v;
                 }
             }
             __syncwarp();
@@ -815,7 +999,7 @@ constexpr int NW_SHORT = 14;  // single-token jobs: two CTAs per SM (this launch
 constexpr int NW_LONG = 16;
 
 template <int KIND, int T, int TW, int TEAMS, int MINB>
-static cudaError_t launch_cfg(const GemvStreamParams &p, int grid_x, int grid_y, int smem_bytes, cudaStream_t s) {
+static cudaError_t launch_cfg(const GemvStreamParams &p, int grid_x, int smem_bytes, cudaStream_t s) {
     static int configured = 0;  // largest dynamic shared memory size opted in for this instantiation
     if (smem_bytes > configured) {
         cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<KIND, T, TW, TEAMS, MINB>,
@@ -828,7 +1012,7 @@ static cudaError_t launch_cfg(const GemvStreamParams &p, int grid_x, int grid_y,
         configured = smem_bytes;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid_x, (unsigned)grid_y, 1);
+    cfg.gridDim = dim3((unsigned)grid_x, 1, 1);
     cfg.blockDim = dim3((TW * TEAMS + 1) * 32, 1, 1);
     cfg.dynamicSmemBytes = (size_t)smem_bytes;
     cfg.stream = s;
@@ -842,124 +1026,192 @@ static cudaError_t launch_cfg(const GemvStreamParams &p, int grid_x, int grid_y,
 }
 
 template <int KIND>
-static cudaError_t launch_k(int T, bool short_cfg, const GemvStreamParams &p, int gx, int gy, int smem, cudaStream_t s) {
-    if (short_cfg) return launch_cfg<KIND, 1, NW_SHORT, 1, 2>(p, gx, gy, smem, s);
+static cudaError_t launch_k(int T, bool short_cfg, const GemvStreamParams &p, int gx, int smem, cudaStream_t s) {
+    if (short_cfg) return launch_cfg<KIND, 1, NW_SHORT, 1, 2>(p, gx, smem, s);
     switch (T) {
-    case 1: return launch_cfg<KIND, 1, NW_LONG, 1, 1>(p, gx, gy, smem, s);
-    case 2: return launch_cfg<KIND, 2, NW_LONG, 1, 1>(p, gx, gy, smem, s);
-    case 3: return launch_cfg<KIND, 3, NW_LONG, 1, 1>(p, gx, gy, smem, s);
-    case 4: return launch_cfg<KIND, 4, NW_LONG, 1, 1>(p, gx, gy, smem, s);
-    case 5: return launch_cfg<KIND, 5, NW_LONG, 1, 1>(p, gx, gy, smem, s);
-    case 6: return launch_cfg<KIND, 6, NW_LONG, 1, 1>(p, gx, gy, smem, s);
-    case 7: return launch_cfg<KIND, 7, NW_LONG, 1, 1>(p, gx, gy, smem, s);
-    default: return launch_cfg<KIND, 8, NW_LONG, 1, 1>(p, gx, gy, smem, s);
+    case 1: return launch_cfg<KIND, 1, NW_LONG, 1, 1>(p, gx, smem, s);
+    case 2: return launch_cfg<KIND, 2, NW_LONG, 1, 1>(p, gx, smem, s);
+    case 3: return launch_cfg<KIND, 3, NW_LONG, 1, 1>(p, gx, smem, s);
+    case 4: return launch_cfg<KIND, 4, NW_LONG, 1, 1>(p, gx, smem, s);
+    case 5: return launch_cfg<KIND, 5, NW_LONG, 1, 1>(p, gx, smem, s);
+    case 6: return launch_cfg<KIND, 6, NW_LONG, 1, 1>(p, gx, smem, s);
+    case 7: return launch_cfg<KIND, 7, NW_LONG, 1, 1>(p, gx, smem, s);
+    default: return launch_cfg<KIND, 8, NW_LONG, 1, 1>(p, gx, smem, s);
     }
 }
 
 struct StreamPlan {
     bool ok;
     bool short_cfg;
-    int unit, rows_per_cta, rows_per_chunk, gx, gy, stages, stage_stride, act_bytes, smem;
+    int kind;  // template KIND of the launch
+    int gx, stages, stage_stride, act_bytes, smem, nb;
+    GemvJob job[GEMV_MAX_JOBS];
 };
 
-static StreamPlan plan_stream(int kind, const void *W, const void *W2, int T, int K, int F) {
+// Deals the CTAs of one wave to the jobs in proportion to their bytes (at least one each) and sizes the ring for the
+// largest chunk.  The launch is "short" (half-SM CTAs, everything prefetched at once) when T = 1 and every CTA's share
+// fits in three chunks.
+static StreamPlan plan_stream(const GemvJobSpec *jobs, int n_jobs, int T, int K, const GemvPrologue &pro) {
     StreamPlan pl = {};
-    if (T < 1 || T > GEMV_MAX_T || F < 1) return pl;
-    if (((uintptr_t)W & 15) || ((uintptr_t)W2 & 15)) return pl;  // bulk copies need 16-byte aligned sources
-    const int bv = block_values(kind), nb = (K + bv - 1) / bv;
-    const long row_bytes = (long)nb * block_bytes(kind);
-    if (row_bytes > 64 * 1024) return pl;
-    pl.unit = 16 / gcd_int((int)(row_bytes % 16), 16);  // rows per 16-byte aligned group
-    if (((long)F * row_bytes) & 15) return pl;           // the last chunk of the last CTA must also be a 16-byte multiple
-    pl.act_bytes = act_smem_bytes(kind != KIND_Q8_0, T, nb);
-    pl.gy = W2 != nullptr ? 2 : 1;
+    if (T < 1 || T > GEMV_MAX_T || n_jobs < 1 || n_jobs > GEMV_MAX_JOBS || K < 1) return pl;
+    const bool q8 = jobs[0].kind == KIND_Q8_0;
+    pl.kind = jobs[0].kind;
+    long row_bytes[GEMV_MAX_JOBS];
+    int unit[GEMV_MAX_JOBS];
+    double total = 0.0;
+    for (int j = 0; j < n_jobs; ++j) {
+        const GemvJobSpec &js = jobs[j];
+        if (js.kind != KIND_Q4_K && js.kind != KIND_Q6_K && js.kind != KIND_Q8_0) return pl;
+        if ((js.kind == KIND_Q8_0) != q8) return pl;  // one activation format per launch
+        if (js.kind != pl.kind) pl.kind = KIND_MIXED;
+        if (js.F < 1 || ((uintptr_t)js.W & 15)) return pl;  // bulk copies need 16-byte aligned sources
+        const int bv = block_values(js.kind), nb = (K + bv - 1) / bv;
+        row_bytes[j] = (long)nb * block_bytes(js.kind);
+        if (row_bytes[j] > 64 * 1024) return pl;
+        unit[j] = 16 / gcd_int((int)(row_bytes[j] % 16), 16);  // rows per 16-byte aligned group
+        if (((long)js.F * row_bytes[j]) & 15) return pl;       // the last chunk of the last CTA must also be a 16-byte multiple
+        total += (double)js.F * (double)row_bytes[j];
+    }
+    if (pro.op != GEMV_PRO_NONE && pro.op != GEMV_PRO_ADD_RMSNORM && pro.op != GEMV_PRO_SWIGLU) return pl;
+    if (pro.op == GEMV_PRO_SWIGLU && pro.aux == nullptr) return pl;
+    pl.nb = q8 ? (K + Q8_0_VALUES - 1) / Q8_0_VALUES : (K + QK_K - 1) / QK_K;
+    pl.act_bytes = act_smem_bytes(!q8, T, pl.nb);
     const int sms = device_sm_count();
-    const int ctas = max(1, sms / pl.gy);
-    int rpc = (F + ctas - 1) / ctas;
-    rpc = (rpc + pl.unit - 1) / pl.unit * pl.unit;
-
-    // Single-token jobs whose per-CTA share fits in the ring: half-SM CTAs, everything prefetched at once.
-    {
-        const int nw = NW_SHORT;
-        const int rc = (int)min((long)nw, (long)(40 * 1024) / row_bytes) / pl.unit * pl.unit;
-        if (T == 1 && rc >= 1) {
-            const int chunks = (rpc + rc - 1) / rc;
-            const int stride = (int)((rc * row_bytes + 16 + 127) / 128 * 128);
-            const int smem = GS_HEADER + pl.act_bytes + chunks * stride;
-            if (chunks <= 3 && smem <= 110 * 1024) {
-                pl.ok = true;
-                pl.short_cfg = true;
-                pl.rows_per_cta = rpc;
-                pl.rows_per_chunk = rc;
-                pl.stages = chunks;
-                pl.stage_stride = stride;
-                pl.smem = smem;
-                pl.gx = (F + rpc - 1) / rpc;
-                return pl;
+    if (sms < n_jobs) return pl;
+    int ctas[GEMV_MAX_JOBS], given = 0;
+    for (int j = 0; j < n_jobs; ++j) {
+        ctas[j] = max(1, (int)((double)sms * ((double)jobs[j].F * (double)row_bytes[j]) / total));
+        given += ctas[j];
+    }
+    // hand out what rounding left (or take back what the minimum of one added), largest share per CTA first
+    while (given != sms) {
+        int best = -1;
+        double best_v = 0.0;
+        for (int j = 0; j < n_jobs; ++j) {
+            if (given > sms && ctas[j] <= 1) continue;
+            const double per = (double)jobs[j].F * (double)row_bytes[j] / (double)ctas[j];
+            const double v = given < sms ? per : -per;
+            if (best < 0 || v > best_v) best = j, best_v = v;
+        }
+        if (best < 0) return pl;
+        ctas[best] += given < sms ? 1 : -1;
+        given += given < sms ? 1 : -1;
+    }
+    int rpc[GEMV_MAX_JOBS];
+    for (int j = 0; j < n_jobs; ++j) {
+        rpc[j] = (jobs[j].F + ctas[j] - 1) / ctas[j];
+        rpc[j] = (rpc[j] + unit[j] - 1) / unit[j] * unit[j];
+    }
+    auto fill = [&](const int *rc, int stages, int stride, bool short_cfg) {
+        pl.ok = true;
+        pl.short_cfg = short_cfg;
+        pl.stages = stages;
+        pl.stage_stride = stride;
+        pl.smem = GS_HEADER + pl.act_bytes + stages * stride;
+        int begin = 0;
+        for (int j = 0; j < n_jobs; ++j) {
+            GemvJob &g = pl.job[j];
+            g.W = (const uint8_t *)jobs[j].W;
+            g.out = jobs[j].out;
+            g.bias = jobs[j].bias;
+            g.F = jobs[j].F;
+            g.ldo = jobs[j].ldo;
+            g.kind = jobs[j].kind;
+            g.row_bytes = (int)row_bytes[j];
+            g.rows_per_cta = rpc[j];
+            g.rows_per_chunk = rc[j];
+            g.cta_begin = begin;
+            begin += (jobs[j].F + rpc[j] - 1) / rpc[j];
+        }
+        pl.gx = begin;
+    };
+    // Single-token launches whose per-CTA shares fit in the ring
+    if (T == 1) {
+        int rc[GEMV_MAX_JOBS], chunks = 0, stride = 0;
+        bool ok = true;
+        for (int j = 0; j < n_jobs && ok; ++j) {
+            rc[j] = (int)min((long)NW_SHORT, (long)(40 * 1024) / row_bytes[j]) / unit[j] * unit[j];
+            if (rc[j] < 1) {
+                ok = false;
+                break;
             }
+            chunks = max(chunks, (rpc[j] + rc[j] - 1) / rc[j]);
+            stride = max(stride, (int)((rc[j] * row_bytes[j] + 16 + 127) / 128 * 128));
+        }
+        if (ok && chunks <= 3 && GS_HEADER + pl.act_bytes + chunks * stride <= 110 * 1024) {
+            fill(rc, chunks, stride, true);
+            return pl;
         }
     }
     // General case: one CTA per SM, sixteen consumer warps, as deep a ring as fits.
     {
-        const int nw = NW_LONG;
-        int rc = (int)min((long)nw, (long)(40 * 1024) / row_bytes) / pl.unit * pl.unit;
-        if (rc < 1) {
-            if (row_bytes * pl.unit > 64 * 1024 || pl.unit > nw) return pl;
-            rc = pl.unit;
+        int rc[GEMV_MAX_JOBS], chunks = 0, stride = 0;
+        for (int j = 0; j < n_jobs; ++j) {
+            rc[j] = (int)min((long)NW_LONG, (long)(40 * 1024) / row_bytes[j]) / unit[j] * unit[j];
+            if (rc[j] < 1) {
+                if (row_bytes[j] * unit[j] > 64 * 1024 || unit[j] > NW_LONG) return pl;
+                rc[j] = unit[j];
+            }
+            chunks = max(chunks, (rpc[j] + rc[j] - 1) / rc[j]);
+            stride = max(stride, (int)((rc[j] * row_bytes[j] + 16 + 127) / 128 * 128));
         }
-        const int stride = (int)((rc * row_bytes + 16 + 127) / 128 * 128);
         const int budget = 200 * 1024 - GS_HEADER - pl.act_bytes;
         if (budget < 2 * stride) return pl;
-        const int chunks = (rpc + rc - 1) / rc;
         int stages = min(GS_MAX_STAGES, budget / stride);
         stages = min(stages, max(2, chunks));
-        pl.ok = true;
-        pl.short_cfg = false;
-        pl.rows_per_cta = rpc;
-        pl.rows_per_chunk = rc;
-        pl.stages = stages;
-        pl.stage_stride = stride;
-        pl.smem = GS_HEADER + pl.act_bytes + stages * stride;
-        pl.gx = (F + rpc - 1) / rpc;
+        fill(rc, stages, stride, false);
         return pl;
     }
 }
 
-bool gemv_stream_supported(int kind, const void *W, const void *W2, int T, int K, int F) {
-    return plan_stream(kind, W, W2, T, K, F).ok;
+bool gemv_stream_jobs_supported(const GemvJobSpec *jobs, int n_jobs, int T, int K, const GemvPrologue &pro) {
+    return plan_stream(jobs, n_jobs, T, K, pro).ok;
 }
 
-cudaError_t launch_gemv_stream(int kind, const void *W, const void *W2, const float *x, int ldx, int T, int K, int F,
-                               const float *bias, float *out, float *out2, int ldo, int *err_flag, cudaStream_t s) {
-    const StreamPlan pl = plan_stream(kind, W, W2, T, K, F);
+cudaError_t launch_gemv_stream_jobs(const GemvJobSpec *jobs, int n_jobs, const float *x, int ldx, int T, int K,
+                                    const GemvPrologue &pro, int *err_flag, cudaStream_t s) {
+    const StreamPlan pl = plan_stream(jobs, n_jobs, T, K, pro);
     if (!pl.ok) return cudaErrorInvalidValue;
-    const int bv = block_values(kind), nb = (K + bv - 1) / bv;
-    GemvStreamParams p;
-    p.W[0] = (const uint8_t *)W;
-    p.W[1] = (const uint8_t *)W2;
-    p.out[0] = out;
-    p.out[1] = out2;
+    GemvStreamParams p = {};
+    for (int j = 0; j < n_jobs; ++j) p.job[j] = pl.job[j];
+    p.n_jobs = n_jobs;
     p.x = x;
-    p.bias = bias;
     p.err = err_flag;
     p.ldx = ldx;
-    p.ldo = ldo;
     p.K = K;
-    p.nb = nb;
-    p.F = F;
-    p.row_bytes = nb * block_bytes(kind);
-    p.rows_per_cta = pl.rows_per_cta;
-    p.rows_per_chunk = pl.rows_per_chunk;
+    p.nb = pl.nb;
     p.act_bytes = pl.act_bytes;
     p.stages = pl.stages;
     p.stage_stride = pl.stage_stride;
+    p.pro = pro;
 #ifdef MCU_TRACE
     static int trace_next = 0;
     p.trace_slot = trace_next++;
 #endif
-    if (kind == KIND_Q4_K) return launch_k<KIND_Q4_K>(T, pl.short_cfg, p, pl.gx, pl.gy, pl.smem, s);
-    if (kind == KIND_Q6_K) return launch_k<KIND_Q6_K>(T, pl.short_cfg, p, pl.gx, pl.gy, pl.smem, s);
-    return launch_k<KIND_Q8_0>(T, pl.short_cfg, p, pl.gx, pl.gy, pl.smem, s);
+    if (pl.kind == KIND_Q4_K) return launch_k<KIND_Q4_K>(T, pl.short_cfg, p, pl.gx, pl.smem, s);
+    if (pl.kind == KIND_Q6_K) return launch_k<KIND_Q6_K>(T, pl.short_cfg, p, pl.gx, pl.smem, s);
+    if (pl.kind == KIND_Q8_0) return launch_k<KIND_Q8_0>(T, pl.short_cfg, p, pl.gx, pl.smem, s);
+    return launch_k<KIND_MIXED>(T, pl.short_cfg, p, pl.gx, pl.smem, s);
+}
+
+static int specs_of(int kind, const void *W, const void *W2, int F, const float *bias, float *out, float *out2, int ldo,
+                    GemvJobSpec (&js)[2]) {
+    js[0] = GemvJobSpec{kind, W, F, bias, out, ldo};
+    js[1] = GemvJobSpec{kind, W2, F, bias, out2, ldo};
+    return W2 != nullptr ? 2 : 1;
+}
+
+bool gemv_stream_supported(int kind, const void *W, const void *W2, int T, int K, int F) {
+    GemvJobSpec js[2];
+    const int n = specs_of(kind, W, W2, F, nullptr, nullptr, nullptr, 0, js);
+    return plan_stream(js, n, T, K, GemvPrologue{}).ok;
+}
+
+cudaError_t launch_gemv_stream(int kind, const void *W, const void *W2, const float *x, int ldx, int T, int K, int F,
+                               const float *bias, float *out, float *out2, int ldo, int *err_flag, cudaStream_t s) {
+    GemvJobSpec js[2];
+    const int n = specs_of(kind, W, W2, F, bias, out, out2, ldo, js);
+    return launch_gemv_stream_jobs(js, n, x, ldx, T, K, GemvPrologue{}, err_flag, s);
 }
 
 }  // namespace mcu

@@ -59,8 +59,37 @@ cudaError_t launch_gemv(int kind, const void *W, const void *W2, const ActBuffer
                         const float *bias, float *out, float *out2, int ldo, cudaStream_t s);
 
 // Streaming variant of the decode-regime matmul: activation quantisation fused in, weights streamed through
-// shared memory with bulk asynchronous copies, launched with programmatic stream serialization.
+// shared memory with bulk asynchronous copies, launched with programmatic stream serialization.  One launch serves up
+// to GEMV_MAX_JOBS weight matrices that read the same activations (q / k / v, gate / up): the CTAs are dealt out in
+// proportion to the matrices' bytes.  Before they are quantized the activations can go through one of the decoder
+// layer's elementwise steps, so that step needs no launch of its own:
+//   GEMV_PRO_ADD_RMSNORM  x' = x + aux (aux may be null), h = x' / rms(x') * (norm_w + w_off); the matrices multiply h;
+//                         x' is also written to x_out when that is set (x_out must not alias x: other CTAs still read it)
+//   GEMV_PRO_SWIGLU       the matrices multiply silu(x) * aux
 // *err_flag (device int) receives a non-zero code if a bounded device-side wait ran out.
+constexpr int GEMV_MAX_JOBS = 4;
+enum { GEMV_PRO_NONE = 0, GEMV_PRO_ADD_RMSNORM = 1, GEMV_PRO_SWIGLU = 2 };
+struct GemvPrologue {
+    int op = GEMV_PRO_NONE;
+    const float *aux = nullptr;
+    int ld_aux = 0;
+    const float *norm_w = nullptr;
+    float eps = 0.0f, w_off = 0.0f;
+    float *x_out = nullptr;
+    int ld_x_out = 0;
+};
+struct GemvJobSpec {
+    int kind;
+    const void *W;
+    int F;
+    const float *bias;
+    float *out;
+    int ldo;
+};
+bool gemv_stream_jobs_supported(const GemvJobSpec *jobs, int n_jobs, int T, int K, const GemvPrologue &pro);
+cudaError_t launch_gemv_stream_jobs(const GemvJobSpec *jobs, int n_jobs, const float *x, int ldx, int T, int K,
+                                    const GemvPrologue &pro, int *err_flag, cudaStream_t s);
+// one matrix, or two of the same shape (W2 / out2), no prologue
 bool gemv_stream_supported(int kind, const void *W, const void *W2, int T, int K, int F);
 cudaError_t launch_gemv_stream(int kind, const void *W, const void *W2, const float *x, int ldx, int T, int K, int F,
                                const float *bias, float *out, float *out2, int ldo, int *err_flag, cudaStream_t s);

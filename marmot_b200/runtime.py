@@ -23,7 +23,7 @@ EXPORTS = (
     "mcu_context_create", "mcu_context_destroy", "mcu_context_set_stream", "mcu_context_get_stream",
     "mcu_context_set_regime", "mcu_synchronize", "mcu_last_error_message", "mcu_kernel_launch_count",
     "mcu_malloc", "mcu_free", "mcu_memcpy_to_device", "mcu_memcpy_to_host", "mcu_row_bytes", "mcu_dequantize",
-    "mcu_quantize_activations", "mcu_linear", "mcu_linear_dual", "mcu_linear_host", "mcu_topk", "mcu_moe_experts",
+    "mcu_quantize_activations", "mcu_linear", "mcu_linear_dual", "mcu_linear_multi", "mcu_linear_host", "mcu_topk", "mcu_moe_experts",
     "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_moe_last_buffers", "mcu_peer_comm_create", "mcu_peer_comm_export",
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
     "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
@@ -38,6 +38,21 @@ EXPORTS = (
     "mcu_gguf_open", "mcu_gguf_close", "mcu_gguf_tensor_count", "mcu_gguf_find_tensor", "mcu_gguf_tensor_info",
     "mcu_gguf_meta_u64", "mcu_gguf_meta_f64", "mcu_gguf_meta_str", "mcu_gguf_upload",
 )
+
+
+PROLOGUE_NONE, PROLOGUE_ADD_RMSNORM, PROLOGUE_SWIGLU = 0, 1, 2
+
+
+class LinearJob(C.Structure):
+    """mcu_linear_job_t"""
+    _fields_ = [("kind", C.c_int), ("w_dev", C.c_void_p), ("F", C.c_size_t), ("bias_dev", C.c_void_p),
+                ("out_dev", C.c_void_p), ("ldo", C.c_size_t)]
+
+
+class Prologue(C.Structure):
+    """mcu_prologue_t"""
+    _fields_ = [("op", C.c_int), ("aux_dev", C.c_void_p), ("ld_aux", C.c_size_t), ("norm_weight_dev", C.c_void_p),
+                ("eps", C.c_float), ("weight_offset", C.c_float), ("x_out_dev", C.c_void_p), ("ld_x_out", C.c_size_t)]
 
 
 class MarmotCudaError(RuntimeError):
@@ -88,6 +103,7 @@ def load_library() -> C.CDLL:
     L.mcu_linear.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_linear_dual.argtypes = [vp, i32, vp, sz, vp, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_linear_host.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
+    L.mcu_linear_multi.argtypes = [vp, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_linear_static_scratch.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_topk.argtypes = [vp, vp, sz, sz, sz, sz, vp, vp]
     L.mcu_vec_dot_host.argtypes = [vp, i32, vp, vp, sz, vp]
@@ -210,6 +226,32 @@ class Context:
         self._check(self.lib.mcu_linear_dual(self.handle, kind, _ptr(x), x.stride(0), _ptr(w_a), _ptr(w_b), T, K, F,
                                              _ptr(oa), _ptr(ob), F))
         return oa, ob
+
+    def linear_multi(self, x, jobs, prologue=None):
+        """Several weights over one activation read: jobs = [(kind, w, F, out), ...] (1..4, out [T, F] or wider rows),
+        prologue = None, ("add_rmsnorm", aux or None, norm_weight or None, eps, weight_offset, x_out or None) or
+        ("swiglu", up).  One launch for up to eight tokens on the streaming path."""
+        T, K = x.shape
+        arr = (LinearJob * len(jobs))()
+        for slot, (kind, w, F, out) in zip(arr, jobs):
+            slot.kind, slot.w_dev, slot.F, slot.bias_dev, slot.out_dev, slot.ldo = kind, _ptr(w), F, None, _ptr(out), out.stride(0)
+        pro = None
+        if prologue is not None:
+            pro = Prologue()
+            if prologue[0] == "add_rmsnorm":
+                _, aux, weight, eps, w_off, x_out = prologue
+                pro.op = PROLOGUE_ADD_RMSNORM
+                pro.aux_dev, pro.ld_aux = (_ptr(aux), aux.stride(0)) if aux is not None else (None, 0)
+                pro.norm_weight_dev = _ptr(weight) if weight is not None else None
+                pro.eps, pro.weight_offset = eps, w_off
+                pro.x_out_dev, pro.ld_x_out = (_ptr(x_out), x_out.stride(0)) if x_out is not None else (None, 0)
+            elif prologue[0] == "swiglu":
+                pro.op = PROLOGUE_SWIGLU
+                pro.aux_dev, pro.ld_aux = _ptr(prologue[1]), prologue[1].stride(0)
+            else:
+                raise ValueError(f"unknown prologue {prologue[0]!r}")
+        self._check(self.lib.mcu_linear_multi(self.handle, _ptr(x), x.stride(0), T, K,
+                                              C.byref(pro) if pro is not None else None, arr, len(jobs)))
 
     def linear_host(self, kind: int, x_host: np.ndarray, w, F: int, bias_host: np.ndarray | None = None,
                     out_host: np.ndarray | None = None) -> np.ndarray:

@@ -553,3 +553,134 @@ def test_integer_mma_dual_output(ctx, oracle, T):
         assert max_rel_err(b.cpu().numpy(), oracle.linear(KINDS["q4_k"], x, Wb, F)) <= 2e-5
     finally:
         ctx.set_regime(0)
+
+
+# ---- several weights over one activation read, with the layer's elementwise step as prologue (mcu_linear_multi) ----
+def _multi_case(rng, names, T, K, Fs, ldx=None):
+    import torch
+
+    ldx = ldx or K
+    kinds = [KINDS[n] for n in names]
+    Ws = [random_blocks(k, F, K, rng) for k, F in zip(kinds, Fs)]
+    xbuf = rng.normal(0, 1, (T, ldx)).astype(np.float32)
+    xd = torch.from_numpy(xbuf).cuda()[:, :K]
+    outs = [torch.full((T, F + 5), 7.0, dtype=torch.float32, device="cuda") for F in Fs]  # wider rows: ldo > F
+    return kinds, Ws, np.ascontiguousarray(xbuf[:, :K]), xd, outs
+
+
+@pytest.mark.parametrize("names,T,K,Fs", [
+    (("q4_k", "q4_k", "q6_k"), 1, 2048, (2048, 256, 256)),   # q / k / v of a 1.1B decoder, mixed kinds
+    (("q4_k", "q4_k"), 1, 2048, (5632, 5632)),                # gate / up
+    (("q6_k",), 3, 2048, (777,)),
+    (("q4_k", "q6_k", "q4_k", "q6_k"), 8, 1024, (96, 40, 8, 300)),
+    (("q8_0", "q8_0", "q8_0"), 2, 1024, (512, 64, 64)),
+    (("q4_k", "q4_k", "q4_k"), 1, 4096, (4096, 1024, 1024)),  # q / k / v of an 8B decoder
+])
+@pytest.mark.parametrize("with_aux", [True, False])
+def test_linear_multi_add_rmsnorm_prologue(ctx, oracle, names, T, K, Fs, with_aux):
+    """x' = x + aux, h = rms_norm(x') * w and every matmul of h in ONE launch: results against the oracle's add,
+    rms_norm and linear; x' must come back exactly; the padding of wider output rows must stay untouched."""
+    import torch
+
+    rng = np.random.default_rng(T * 7919 + K + sum(Fs) + with_aux)
+    kinds, Ws, x, xd, outs = _multi_case(rng, names, T, K, Fs)
+    aux = rng.normal(0, 1, (T, K)).astype(np.float32) if with_aux else None
+    w = rng.normal(1, 0.2, K).astype(np.float32)
+    x_out = torch.zeros((T, K), dtype=torch.float32, device="cuda")
+    jobs = [(k, ctx.upload(W), F, o[:, :F]) for k, W, F, o in zip(kinds, Ws, Fs, outs)]
+    l0 = ctx.launch_count()
+    ctx.linear_multi(xd, jobs, ("add_rmsnorm", torch.from_numpy(aux).cuda() if with_aux else None,
+                                torch.from_numpy(w).cuda(), 1e-5, 0.0, x_out))
+    ctx.synchronize()
+    assert ctx.launch_count() - l0 == 1
+    xs = (x + aux).astype(np.float32) if with_aux else x
+    assert np.array_equal(x_out.cpu().numpy(), xs)
+    h = oracle.rmsnorm(xs, w, 1e-5)
+    for k, W, F, o in zip(kinds, Ws, Fs, outs):
+        got = o.cpu().numpy()
+        assert max_rel_err(got[:, :F], oracle.linear(k, h, W, F)) <= TOL_FP32
+        assert np.all(got[:, F:] == 7.0)
+
+
+@pytest.mark.parametrize("name,T,K,F", [("q6_k", 1, 5632, 2048), ("q4_k", 4, 5632, 2048), ("q8_0", 2, 1408, 96),
+                                        ("q4_k", 1, 14336, 4096)])
+def test_linear_multi_swiglu_prologue(ctx, oracle, name, T, K, F):
+    """The down projection reads silu(gate) * up directly."""
+    import torch
+
+    rng = np.random.default_rng(T + K + F)
+    kinds, Ws, gate, gd, outs = _multi_case(rng, (name,), T, K, (F,), ldx=K + 4)
+    up = rng.normal(0, 1, (T, K)).astype(np.float32)
+    l0 = ctx.launch_count()
+    ctx.linear_multi(gd, [(kinds[0], ctx.upload(Ws[0]), F, outs[0][:, :F])], ("swiglu", torch.from_numpy(up).cuda()))
+    ctx.synchronize()
+    assert ctx.launch_count() - l0 == 1
+    want = oracle.linear(kinds[0], oracle.swiglu(gate, up), Ws[0], F)
+    assert max_rel_err(outs[0].cpu().numpy()[:, :F], want) <= TOL_FP32
+
+
+def test_linear_multi_unaligned_rows_and_no_norm_weight(ctx, oracle):
+    """Row strides and K that rule out 16-byte loads, K not a multiple of the block, no norm weight, no x_out."""
+    import torch
+
+    T, K, F = 3, 701, 48  # 48 Q6_K rows of 630 bytes: a whole number of 16-byte pieces, as the bulk copies need
+    rng = np.random.default_rng(5)
+    kinds, Ws, x, xd, outs = _multi_case(rng, ("q4_k", "q6_k"), T, K, (F, F), ldx=K + 1)
+    auxbuf = rng.normal(0, 1, (T, K + 3)).astype(np.float32)
+    ctx.linear_multi(xd, [(k, ctx.upload(W), F, o[:, :F]) for k, W, o in zip(kinds, Ws, outs)],
+                     ("add_rmsnorm", torch.from_numpy(auxbuf).cuda()[:, :K], None, 1e-6, 0.0, None))
+    h = oracle.rmsnorm((x + auxbuf[:, :K]).astype(np.float32), np.ones(K, dtype=np.float32), 1e-6)
+    for k, W, o in zip(kinds, Ws, outs):
+        assert max_rel_err(o.cpu().numpy()[:, :F], oracle.linear(k, h, W, F)) <= TOL_FP32
+
+
+def test_linear_multi_general_form(ctx, oracle):
+    """More than eight tokens, or kinds that do not share an activation format: the prologue runs as its own kernel,
+    the matmuls follow; same results."""
+    import torch
+
+    for names, T in ((("q4_k", "q4_k", "q6_k"), 12), (("q8_0", "q4_k"), 2)):
+        K, Fs = 1024, (128, 128, 72)[:len(names)]
+        rng = np.random.default_rng(T)
+        kinds, Ws, x, xd, outs = _multi_case(rng, names, T, K, Fs)
+        aux = rng.normal(0, 1, (T, K)).astype(np.float32)
+        w = rng.normal(1, 0.2, K).astype(np.float32)
+        x_out = torch.zeros((T, K), dtype=torch.float32, device="cuda")
+        l0 = ctx.launch_count()
+        ctx.linear_multi(xd, [(k, ctx.upload(W), F, o[:, :F]) for k, W, F, o in zip(kinds, Ws, Fs, outs)],
+                         ("add_rmsnorm", torch.from_numpy(aux).cuda(), torch.from_numpy(w).cuda(), 1e-5, 0.0, x_out))
+        assert ctx.launch_count() - l0 > 1
+        xs = (x + aux).astype(np.float32)
+        assert np.array_equal(x_out.cpu().numpy(), xs)
+        h = oracle.rmsnorm(xs, w, 1e-5)
+        for k, W, F, o in zip(kinds, Ws, Fs, outs):
+            tol = TOL_MMA if T > 8 else TOL_FP32
+            assert max_rel_err(o.cpu().numpy()[:, :F], oracle.linear(k, h, W, F)) <= tol
+
+
+def test_linear_multi_without_prologue_equals_singles(ctx):
+    import torch
+
+    rng = np.random.default_rng(11)
+    T, K, Fs = 2, 2048, (300, 64, 1000)
+    kinds, Ws, x, xd, outs = _multi_case(rng, ("q4_k", "q6_k", "q4_k"), T, K, Fs)
+    wd = [ctx.upload(W) for W in Ws]
+    ctx.linear_multi(xd, [(k, w, F, o[:, :F]) for k, w, F, o in zip(kinds, wd, Fs, outs)])
+    for k, w, F, o in zip(kinds, wd, Fs, outs):
+        single = ctx.linear(k, xd, w, F)
+        assert torch.equal(single, o[:, :F])  # same kernel, same arithmetic: bit for bit
+
+
+def test_linear_multi_refusals(ctx):
+    import torch
+    from marmot_b200.runtime import MarmotCudaError
+
+    x = torch.zeros((1, 256), device="cuda")
+    out = torch.zeros((1, 8), device="cuda")
+    w = ctx.upload(np.zeros((8, 144), dtype=np.uint8))
+    with pytest.raises(MarmotCudaError):  # x_out may not be the input: other CTAs still read it
+        ctx.linear_multi(x, [(KIND_Q4_K, w, 8, out)], ("add_rmsnorm", None, None, 1e-5, 0.0, x))
+    with pytest.raises(MarmotCudaError):
+        ctx.linear_multi(x, [(KIND_Q4_K, w, 8, out)] * 5)
+    with pytest.raises(MarmotCudaError):
+        ctx.linear_multi(x, [(1, w, 8, out)])  # Q4_0: no CUDA kernel
