@@ -380,7 +380,7 @@ def time_decode(ctx, dev, rank: int = 0, world: int = 1, dist=None):
             logits = torch.empty((n_seq, dec.local_vocab), dtype=torch.float32, device=dev)
 
             def one_token():
-                dec.step(ids, meta, pos, logits_out=logits)
+                dec.step(ids, meta, pos, logits_out=logits, decode=True)
                 dec.greedy(logits, ids)
                 if advance:  # a sequence's blocks are contiguous here, so kv_slot advances with the position
                     pos.add_(1)

@@ -78,6 +78,7 @@ struct mcu_context {
     Buffer act_qs, act_d, act_bsums, act_half, act_rowscale, x_stage, out_stage, bias_stage;
     Buffer moe_meta, moe_hidden, moe_gate, moe_up, moe_down;
     Buffer gemm_partial;         // split-K partial tiles
+    Buffer attn_tickets;            // fused decode attention: one counter per (token, KV head)
     Buffer pro_h;                   // activations after a stand-alone prologue kernel (mcu_linear_multi's general form)
     Buffer i8_partial, i8_tickets;  // integer-MMA matmul: shares of row groups split between CTAs, and their tickets
     Buffer attn_partial;         // split-KV partial attention states
@@ -134,6 +135,16 @@ int context_attention_scratch(mcu_context *ctx, size_t bytes, void **out) {
     std::lock_guard<std::mutex> lock(ctx->mu);
     if (int rc = ensure(ctx, ctx->attn_partial, bytes)) return rc;
     *out = ctx->attn_partial.ptr;
+    return MCU_SUCCESS;
+}
+// Zero-filled when it is (re)allocated; the attention kernel that uses the tickets leaves them at zero.
+int context_attention_tickets(mcu_context *ctx, size_t bytes, void **out) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (bytes > ctx->attn_tickets.cap) {
+        if (int rc = ensure(ctx, ctx->attn_tickets, bytes)) return rc;
+        MCU_CUDA(cudaMemsetAsync(ctx->attn_tickets.ptr, 0, ctx->attn_tickets.cap, ctx->stream));
+    }
+    *out = ctx->attn_tickets.ptr;
     return MCU_SUCCESS;
 }
 }  // namespace mcu
@@ -218,7 +229,7 @@ void mcu_context_destroy(mcu_context_t *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     Buffer *bufs[] = {&ctx->act_qs,   &ctx->act_d,      &ctx->act_bsums, &ctx->act_half, &ctx->act_rowscale, &ctx->x_stage, &ctx->out_stage,
-                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down, &ctx->gemm_partial, &ctx->attn_partial, &ctx->i8_partial, &ctx->i8_tickets, &ctx->pro_h};
+                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down, &ctx->gemm_partial, &ctx->attn_partial, &ctx->i8_partial, &ctx->i8_tickets, &ctx->pro_h, &ctx->attn_tickets};
     for (Buffer *b : bufs)
         if (b->ptr != nullptr) cudaFree(b->ptr);
     if (ctx->dev_err != nullptr) cudaFree(ctx->dev_err);

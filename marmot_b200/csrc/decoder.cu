@@ -436,14 +436,29 @@ __device__ __forceinline__ void split_half2(float x, float y, uint32_t &hi, uint
     lo = *(const uint32_t *)&t;
 }
 
-template <int HD>
-__global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(PagedParams p, float *partial) {
+// FUSED (decode steps: at most one token per sequence in the call) folds the neighbours of the attention into the
+// same launch.  RoPE: the query heads are rotated on their way into the A fragments, and the warp whose tile holds the
+// token's own position rotates the new K row, converts K and V to f16 and puts them into its tile AND into the pool
+// (no other CTA of the launch reads that pool row: every other position belongs to an earlier step).  Merge: a CTA
+// that is alone on its token writes the output itself; otherwise each CTA writes its chunk state, takes a ticket, and
+// the CTA that draws the last ticket of a (token, KV head) merges the chunk states in chunk order -- the arithmetic of
+// paged_attention_merge_kernel, so both forms give the same bits.
+struct FusedDecode {
+    const int32_t *positions;  // [T], for RoPE
+    int *tickets;              // [T][kv_heads], zero between launches
+    int neox;
+};
+
+template <int HD, bool FUSED>
+__global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(PagedParams p, float *partial, FusedDecode fd,
+                                                                            RopeFreqs freqs) {
     constexpr int ROWB = HD * 2;            // bytes of a K or V row
     constexpr int PIECES = ROWB / 16;       // 16-byte pieces per row
     constexpr int TILEB = PM_TILE * ROWB;
     constexpr int KS = HD / 16;             // k steps of Q K^T
     constexpr int NT = HD / 8;              // n tiles of P V
     extern __shared__ __align__(128) uint8_t pm_smem[];  // [warp][K tile | V tile]; reused for the warps' states
+    __shared__ int s_last;
     MCU_PDL_PROLOGUE();
     const int h = blockIdx.x, t = blockIdx.y, c = blockIdx.z, n_chunks = gridDim.z;
     const uint32_t kv_len = p.meta[t * 4 + 1] + 1u;
@@ -462,6 +477,25 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
     const uint32_t sV = sK + TILEB;
     const uint32_t k0 = p0 + (uint32_t)(warp * PM_TILE);  // this warp's positions [k0, k0 + 32)
     const bool has_tile = k0 < p1;                        // uniform over the warp
+    // FUSED: the token's own row (position kv_len - 1) comes from k_new / v_new, not from the pool
+    const uint32_t new_pos = kv_len - 1u;
+    const int new_row = FUSED && new_pos >= k0 && new_pos < k0 + PM_TILE ? (int)(new_pos - k0) : -1;
+    float *s_q = (float *)(pm_smem + PM_WARPS * 2 * TILEB);  // FUSED: the group's rotated query heads [8][HD]
+    if (FUSED) {
+        const int half = HD / 2;
+        const float posf = (float)fd.positions[t];
+        for (int idx = threadIdx.x; idx < gsize * half; idx += blockDim.x) {
+            const int hh = idx / half, i = idx - hh * half;
+            float sn, cs;
+            sincosf(__fmul_rn(posf, freqs.f[i]), &sn, &cs);
+            const int e = fd.neox ? i : 2 * i, o = fd.neox ? i + half : 2 * i + 1;
+            const float *row = p.q + ((size_t)t * p.n_q_heads + (size_t)h * gsize + hh) * HD;
+            const float xe = row[e], xo = row[o];
+            s_q[hh * HD + e] = __fsub_rn(__fmul_rn(xe, cs), __fmul_rn(xo, sn));
+            s_q[hh * HD + o] = __fadd_rn(__fmul_rn(xe, sn), __fmul_rn(xo, cs));
+        }
+        __syncthreads();
+    }
 
     // stage the tile: lane r looks up the pool block of position k0 + r, the warp copies two rows per step
     uint32_t live = 0;
@@ -476,6 +510,7 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
             const int r = idx / PIECES, pc = idx - r * PIECES;
             const unsigned long long base = __shfl_sync(0xffffffffu, (unsigned long long)row_base, r);
             const uint32_t off = (uint32_t)(r * ROWB + ((pc ^ (r & 7)) << 4));
+            if (r == new_row) continue;  // written below
             if ((live >> r) & 1u) {
                 cp_async16(sK + off, (const __half *)p.kv_k + base + pc * 8);
                 cp_async16(sV + off, (const __half *)p.kv_v + base + pc * 8);
@@ -485,13 +520,42 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
+        if (FUSED && new_row >= 0) {
+            // the new K row rotated, the new V row, both as f16: into this warp's tile and into the pool slot
+            const int half = HD / 2, r = new_row;
+            const float posf = (float)fd.positions[t];
+            const uint32_t kv_slot = p.meta[t * 4 + 2];
+            const size_t dst = (size_t)(kv_slot >> p.block_shift) * s0 + head_off + (size_t)(kv_slot & (uint32_t)(bs - 1)) * s3;
+            const float *krow = p.k_new + ((size_t)t * p.n_kv_heads + h) * HD;
+            const float *vrow = p.v_new + ((size_t)t * p.n_kv_heads + h) * HD;
+            uint8_t *tK = pm_smem + warp * 2 * TILEB, *tV = tK + TILEB;
+            auto tile_off = [&](int d) { return r * ROWB + ((((d >> 3) ^ (r & 7))) << 4) + (d & 7) * 2; };
+            for (int i = lane; i < half; i += 32) {
+                float sn, cs;
+                sincosf(__fmul_rn(posf, freqs.f[i]), &sn, &cs);
+                const int e = fd.neox ? i : 2 * i, o = fd.neox ? i + half : 2 * i + 1;
+                const float xe = krow[e], xo = krow[o];
+                const __half ke = __float2half_rn(__fsub_rn(__fmul_rn(xe, cs), __fmul_rn(xo, sn)));
+                const __half ko = __float2half_rn(__fadd_rn(__fmul_rn(xe, sn), __fmul_rn(xo, cs)));
+                *(__half *)(tK + tile_off(e)) = ke;
+                *(__half *)(tK + tile_off(o)) = ko;
+                ((__half *)p.kv_k)[dst + e] = ke;
+                ((__half *)p.kv_k)[dst + o] = ko;
+            }
+            for (int d = lane; d < HD; d += 32) {
+                const __half vv = __float2half_rn(vrow[d]);
+                *(__half *)(tV + tile_off(d)) = vv;
+                ((__half *)p.kv_v)[dst + d] = vv;
+            }
+        }
     }
 
     // A fragments of Q (row g = query head g of the group): a0 = dims 16s + 2tq, +1; a2 = dims 16s + 8 + 2tq, +1
     uint32_t qhi[KS][2], qlo[KS][2];
     {
         const bool head_ok = g < gsize;
-        const float *qrow = p.q + ((size_t)t * p.n_q_heads + (size_t)h * gsize + (head_ok ? g : 0)) * HD;
+        const float *qrow = FUSED ? s_q + (head_ok ? g : 0) * HD
+                                  : p.q + ((size_t)t * p.n_q_heads + (size_t)h * gsize + (head_ok ? g : 0)) * HD;
 #pragma unroll
         for (int s = 0; s < KS; ++s)
 #pragma unroll
@@ -623,6 +687,10 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
             L += s_l[w * 8 + hh] * e;
             O += s_o[((size_t)w * 8 + hh) * HD + d] * e;
         }
+        if (FUSED && (kv_len <= (uint32_t)PM_CHUNK || n_chunks == 1)) {  // the only chunk of its token: this is the result
+            p.out[((size_t)t * p.n_q_heads + (size_t)h * gsize + hh) * HD + d] = L > 0.0f ? O / L : 0.0f;
+            continue;
+        }
         float *pr = partial + (((size_t)t * p.n_q_heads + (size_t)h * gsize + hh) * n_chunks + c) * (HD + 2);
         if (d == 0) {
             float M = -INFINITY;
@@ -632,6 +700,38 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
             pr[1] = L;
         }
         pr[2 + d] = O;
+    }
+    if (!FUSED || kv_len <= (uint32_t)PM_CHUNK || n_chunks == 1) return;
+    // the last CTA of this (token, KV head) to finish merges the chunk states
+    const int live_chunks = min(n_chunks, (int)((kv_len + (uint32_t)PM_CHUNK - 1u) / (uint32_t)PM_CHUNK));
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int *ticket = fd.tickets + (size_t)t * p.n_kv_heads + h;
+        const int drawn = atomicAdd(ticket, 1);
+        s_last = drawn == live_chunks - 1;
+        if (s_last) *ticket = 0;  // every other CTA has drawn already: ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < gsize * HD; idx += blockDim.x) {
+        const int hh = idx / HD, d = idx - hh * HD;
+        const int qh = h * gsize + hh;
+        const float *pr = partial + ((size_t)t * p.n_q_heads + qh) * n_chunks * (HD + 2);
+        float M = -INFINITY;
+        for (int cc = 0; cc < live_chunks; ++cc) M = fmaxf(M, __ldcg(pr + (size_t)cc * (HD + 2)));
+        float L = 0.0f, o = 0.0f;
+        if (M != -INFINITY) {
+            for (int cc = 0; cc < live_chunks; ++cc) {
+                const float mc = __ldcg(pr + (size_t)cc * (HD + 2));
+                if (mc == -INFINITY) continue;
+                const float e = expf(mc - M);
+                L += __ldcg(pr + (size_t)cc * (HD + 2) + 1) * e;
+                o += __ldcg(pr + (size_t)cc * (HD + 2) + 2 + d) * e;
+            }
+        }
+        p.out[((size_t)t * p.n_q_heads + qh) * HD + d] = L > 0.0f ? o / L : 0.0f;
     }
 }
 
@@ -859,14 +959,14 @@ int mcu_paged_attention(mcu_context_t *ctx, const uint32_t *token_meta_dev, size
     if (mma_path) {
         const size_t smem = (size_t)PM_WARPS * 2 * PM_TILE * head_dim * 2;  // >= the warps' merge states (8 heads each)
         if (head_dim == 64)
-            DEC_CUDA(cudaFuncSetAttribute(paged_attention_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            DEC_CUDA(cudaFuncSetAttribute(paged_attention_mma_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         else
-            DEC_CUDA(cudaFuncSetAttribute(paged_attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            DEC_CUDA(cudaFuncSetAttribute(paged_attention_mma_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         DEC_CUDA(launch_pdl(kv_append_kernel<__half>, ag, dim3(128), s, p, (int)head_dim));
         if (head_dim == 64)
-            DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<64>, qg, dim3(32 * PM_WARPS), smem, s, p, partial));
+            DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<64, false>, qg, dim3(32 * PM_WARPS), smem, s, p, partial, FusedDecode{}, RopeFreqs{}));
         else
-            DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<128>, qg, dim3(32 * PM_WARPS), smem, s, p, partial));
+            DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<128, false>, qg, dim3(32 * PM_WARPS), smem, s, p, partial, FusedDecode{}, RopeFreqs{}));
     } else {
         DEC_CUDA(launch_pdl(kv_append_kernel<float>, ag, dim3(128), s, p, (int)head_dim));
         if (head_dim == 64) DEC_CUDA(launch_pdl(paged_attention_kernel<float, 64>, qg, tb, s, p, (int)chunk, partial));
@@ -877,6 +977,79 @@ int mcu_paged_attention(mcu_context_t *ctx, const uint32_t *token_meta_dev, size
     else
         DEC_CUDA(launch_pdl(paged_attention_merge_kernel<128>, mg, dim3(128), s, p, (int)chunk, (int)n_chunks, (const float *)partial));
     count_launches(3);
+    return MCU_SUCCESS;
+}
+
+
+int mcu_paged_attention_decode(mcu_context_t *ctx, const uint32_t *token_meta_dev, size_t T, float *q_dev, float *k_new_dev,
+                               const float *v_new_dev, void *kv_k_dev, void *kv_v_dev, int kv_dtype,
+                               const uint32_t *block_table_dev, size_t max_blocks_per_seq, size_t n_layers, size_t layer,
+                               size_t n_q_heads, size_t n_kv_heads, size_t head_dim, size_t block_size, float scale,
+                               const int32_t *positions_dev, float rope_theta, float rope_freq_scale, int rope_type,
+                               float *out_dev) {
+    cudaStream_t s;
+    if (int rc = dec_begin(ctx, &s)) return rc;
+    if (T == 0) return MCU_SUCCESS;
+    const bool fused = kv_dtype == MCU_KV_F16 && (head_dim == 64 || head_dim == 128) && n_kv_heads != 0 &&
+        n_q_heads % n_kv_heads == 0 && n_q_heads / n_kv_heads <= (size_t)PA_MAX_GROUP;
+    if (!fused) {  // the three stand-alone steps; they check their own arguments
+        if (int rc = mcu_rope_qk(ctx, q_dev, n_q_heads * head_dim, n_q_heads, k_new_dev, n_kv_heads * head_dim, n_kv_heads,
+                                 positions_dev, T, head_dim, rope_theta, rope_freq_scale, rope_type))
+            return rc;
+        return mcu_paged_attention(ctx, token_meta_dev, T, q_dev, k_new_dev, v_new_dev, kv_k_dev, kv_v_dev, kv_dtype,
+                                   block_table_dev, max_blocks_per_seq, n_layers, layer, n_q_heads, n_kv_heads, head_dim,
+                                   block_size, scale, out_dev);
+    }
+    if (token_meta_dev == nullptr || q_dev == nullptr || k_new_dev == nullptr || v_new_dev == nullptr || kv_k_dev == nullptr ||
+        kv_v_dev == nullptr || block_table_dev == nullptr || out_dev == nullptr || positions_dev == nullptr)
+        return set_error(MCU_ERROR_INVALID_ARGUMENT, "paged_attention descriptor is incomplete");
+    if (((uintptr_t)kv_k_dev | (uintptr_t)kv_v_dev) & 15)
+        return set_error(MCU_ERROR_INVALID_ARGUMENT, "paged_attention KV pools must be 16-byte aligned");
+    if (block_size == 0 || (block_size & (block_size - 1)) != 0)
+        return set_error(MCU_ERROR_INVALID_ARGUMENT, "paged_attention block_size must be a power of two");
+    if (layer >= n_layers) return set_error(MCU_ERROR_DIMENSION_MISMATCH, "paged_attention head / layer configuration invalid");
+    if (rope_type != MCU_ROPE_NORM && rope_type != MCU_ROPE_NEOX) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "unknown RoPE type");
+    PagedParams p;
+    p.meta = token_meta_dev;
+    p.table = block_table_dev;
+    p.q = q_dev;
+    p.k_new = k_new_dev;
+    p.v_new = v_new_dev;
+    p.kv_k = kv_k_dev;
+    p.kv_v = kv_v_dev;
+    p.out = out_dev;
+    p.n_q_heads = (int)n_q_heads;
+    p.n_kv_heads = (int)n_kv_heads;
+    p.max_blocks = (int)max_blocks_per_seq;
+    p.n_layers = (int)n_layers;
+    p.layer = (int)layer;
+    p.block_shift = 0;
+    while (((size_t)1 << p.block_shift) < block_size) ++p.block_shift;
+    p.scale = scale;
+    const size_t max_positions = max_blocks_per_seq * block_size;
+    const size_t n_chunks = (max_positions + PM_CHUNK - 1) / PM_CHUNK;
+    if (n_chunks > 65535) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "paged_attention context bound too long");
+    void *scratch = nullptr, *tickets = nullptr;
+    if (int rc = context_attention_scratch(ctx, T * n_q_heads * n_chunks * (head_dim + 2) * sizeof(float), &scratch)) return rc;
+    if (int rc = context_attention_tickets(ctx, T * n_kv_heads * sizeof(int), &tickets)) return rc;
+    FusedDecode fd;
+    fd.positions = positions_dev;
+    fd.tickets = (int *)tickets;
+    fd.neox = rope_type == MCU_ROPE_NEOX ? 1 : 0;
+    RopeFreqs fr = {};
+    for (size_t i = 0; i < head_dim / 2; ++i)
+        fr.f[i] = powf(rope_theta, -((float)(2 * i) / (float)head_dim)) * rope_freq_scale;  // src/core/helpers/rope.c:111
+    const dim3 qg((unsigned)n_kv_heads, (unsigned)T, (unsigned)n_chunks);
+    // the tiles, then the group's rotated query heads
+    const size_t smem = (size_t)PM_WARPS * 2 * PM_TILE * head_dim * 2 + (size_t)PA_MAX_GROUP * head_dim * sizeof(float);
+    if (head_dim == 64) {
+        DEC_CUDA(cudaFuncSetAttribute(paged_attention_mma_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<64, true>, qg, dim3(32 * PM_WARPS), smem, s, p, (float *)scratch, fd, fr));
+    } else {
+        DEC_CUDA(cudaFuncSetAttribute(paged_attention_mma_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<128, true>, qg, dim3(32 * PM_WARPS), smem, s, p, (float *)scratch, fd, fr));
+    }
+    count_launches(1);
     return MCU_SUCCESS;
 }
 

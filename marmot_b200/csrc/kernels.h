@@ -170,6 +170,7 @@ int context_device(const mcu_context *ctx);
 int *context_err_flag(mcu_context *ctx);
 // workspace of the context for the split-KV attention partials (grows on demand)
 int context_attention_scratch(mcu_context *ctx, size_t bytes, void **out);
+int context_attention_tickets(mcu_context *ctx, size_t bytes, void **out);  // zero-filled counters
 // mcu_linear with the all-reduce fused into the matmul's epilogue; MCU_ERROR_NOT_IMPLEMENTED when the shape or the
 // weights do not allow it (the caller then runs the matmul and the all-reduce kernel separately).
 int linear_fused_allreduce(mcu_context *ctx, int kind, const float *x, size_t ldx, const void *w, size_t T, size_t K,

@@ -249,9 +249,16 @@ class Decoder:
         ids_out.copy_(idxs.gather(1, best).squeeze(1).to(torch.int32))
         return ids_out
 
-    def step(self, ids, meta, positions, logits_out=None):
+    def step(self, ids, meta, positions, logits_out=None, decode=False):
         """One forward pass for T tokens: ids int32 [T], meta u32 [T, 4], positions int32 [T] (device tensors).
-        Returns logits [T, vocab] (tensor parallel: this rank's vocabulary slice [T, local_vocab])."""
+        Returns logits [T, vocab] (tensor parallel: this rank's vocabulary slice [T, local_vocab]).
+
+        decode=True promises at most one token per sequence in the call (a decode step): RoPE, the KV append, the
+        attention and the merge of its context chunks then run as one kernel, and on one GPU every elementwise step
+        (residual add + RMSNorm, SwiGLU) rides in the prologue of the matmul that consumes it -- five launches per layer
+        for up to eight tokens."""
+        if decode and self.group.world == 1 and ids.shape[0] <= 8:
+            return self._step_fused(ids, meta, positions, logits_out)
         ctx, s = self.ctx, self.local
         T = ids.shape[0]
         hq, hkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
@@ -264,7 +271,8 @@ class Decoder:
         scale = float(hd) ** -0.5
         # the residual add that ends a block and the rms_norm that opens the next one run as one kernel
         ctx.rmsnorm(x, self.layers[0]["attn_norm"], s.rms_eps, out=h)
-        side = self._side_contexts()
+        # up to eight tokens q / k / v are one launch; beyond, three matmuls that run side by side on streams of their own
+        side = self._side_contexts() if T > 8 else ()
         main = self._main_stream() if side else None
         for i, lw in enumerate(self.layers):
             if side:
@@ -277,24 +285,60 @@ class Decoder:
                 main.wait_stream(st_k)
                 main.wait_stream(st_v)
             else:
-                ctx.linear(kd[f"l{i}.wq"], h, lw["wq"], hq * hd, out=q)
-                ctx.linear(kd[f"l{i}.wk"], h, lw["wk"], hkv * hd, out=k)
-                ctx.linear(kd[f"l{i}.wv"], h, lw["wv"], hkv * hd, out=v)
-            ctx.rope_qk(q, k, positions, hq, hkv, hd, s.rope_theta)
-            ctx.paged_attention(meta, q, k, v, self.kv_k, self.kv_v, self.block_table, i, hq, hkv, hd, self.block_size,
-                                scale, out=att)
+                ctx.linear_multi(h, [(kd[f"l{i}.wq"], lw["wq"], hq * hd, q), (kd[f"l{i}.wk"], lw["wk"], hkv * hd, k),
+                                     (kd[f"l{i}.wv"], lw["wv"], hkv * hd, v)])
+            if decode:
+                ctx.paged_attention_decode(meta, q, k, v, self.kv_k, self.kv_v, self.block_table, i, hq, hkv, hd,
+                                           self.block_size, scale, positions, s.rope_theta, out=att)
+            else:
+                ctx.rope_qk(q, k, positions, hq, hkv, hd, s.rope_theta)
+                ctx.paged_attention(meta, q, k, v, self.kv_k, self.kv_v, self.block_table, i, hq, hkv, hd, self.block_size,
+                                    scale, out=att)
             self._row_parallel(kd[f"l{i}.wo"], att, lw["wo"], s.d, proj, hq * hd)
             ctx.add_rmsnorm(x, proj, lw["ffn_norm"], s.rms_eps, x, h)
             if s.ffn > 0:
-                if kd[f"l{i}.gate"] == kd[f"l{i}.up"]:
-                    ctx.linear_dual(kd[f"l{i}.gate"], h, lw["gate"], lw["up"], s.ffn, out_a=gate, out_b=up)
-                else:
-                    ctx.linear(kd[f"l{i}.gate"], h, lw["gate"], s.ffn, out=gate)
-                    ctx.linear(kd[f"l{i}.up"], h, lw["up"], s.ffn, out=up)
+                ctx.linear_multi(h, [(kd[f"l{i}.gate"], lw["gate"], s.ffn, gate), (kd[f"l{i}.up"], lw["up"], s.ffn, up)])
                 ctx.swiglu(gate, up, out=gate)
             self._row_parallel(kd[f"l{i}.down"], gate, lw["down"], s.d, proj, s.ffn)
             nxt = self.layers[i + 1]["attn_norm"] if i + 1 < len(self.layers) else self.out_norm
             ctx.add_rmsnorm(x, proj, nxt, s.rms_eps, x, h)
         logits = logits_out if logits_out is not None else self._buf("logits", (T, self.local_vocab))
         ctx.linear(kd["output"], h, self.output, self.local_vocab, out=logits)
+        return logits
+
+    def _step_fused(self, ids, meta, positions, logits_out):
+        """The decode step with every elementwise operator folded into its consumer (see step).  The residual stream
+        alternates between two buffers: a prologue reads x and the pending projection and stores their sum to the other
+        buffer (the CTAs of one launch all read x, so the sum cannot go back in place)."""
+        ctx, s = self.ctx, self.local
+        T = ids.shape[0]
+        hq, hkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
+        kd = self.kinds
+        xs = [self._buf("x", (T, s.d)), self._buf("x2", (T, s.d))]
+        cur = 0
+        ctx.embedding_gather(kd["tok_embd"], self.tok_embd, s.d, ids, out=xs[0])
+        q, k, v = self._buf("q", (T, hq * hd)), self._buf("k", (T, hkv * hd)), self._buf("v", (T, hkv * hd))
+        att, proj = self._buf("att", (T, hq * hd)), self._buf("proj", (T, s.d))
+        gate, up = self._buf("gate", (T, max(s.ffn, 1))), self._buf("up", (T, max(s.ffn, 1)))
+        scale = float(hd) ** -0.5
+        pending = None  # the projection not yet added to the residual stream
+        for i, lw in enumerate(self.layers):
+            ctx.linear_multi(xs[cur], [(kd[f"l{i}.wq"], lw["wq"], hq * hd, q), (kd[f"l{i}.wk"], lw["wk"], hkv * hd, k),
+                                       (kd[f"l{i}.wv"], lw["wv"], hkv * hd, v)],
+                             ("add_rmsnorm", pending, lw["attn_norm"], s.rms_eps, 0.0, xs[1 - cur] if pending is not None else None))
+            if pending is not None:
+                cur = 1 - cur
+            ctx.paged_attention_decode(meta, q, k, v, self.kv_k, self.kv_v, self.block_table, i, hq, hkv, hd,
+                                       self.block_size, scale, positions, s.rope_theta, out=att)
+            ctx.linear(kd[f"l{i}.wo"], att, lw["wo"], s.d, out=proj)
+            pending = proj
+            if s.ffn > 0:
+                ctx.linear_multi(xs[cur], [(kd[f"l{i}.gate"], lw["gate"], s.ffn, gate), (kd[f"l{i}.up"], lw["up"], s.ffn, up)],
+                                 ("add_rmsnorm", pending, lw["ffn_norm"], s.rms_eps, 0.0, xs[1 - cur]))
+                cur = 1 - cur
+                ctx.linear_multi(gate, [(kd[f"l{i}.down"], lw["down"], s.d, proj)], ("swiglu", up))
+                pending = proj
+        logits = logits_out if logits_out is not None else self._buf("logits", (T, self.local_vocab))
+        ctx.linear_multi(xs[cur], [(kd["output"], self.output, self.local_vocab, logits)],
+                         ("add_rmsnorm", pending, self.out_norm, s.rms_eps, 0.0, None))
         return logits

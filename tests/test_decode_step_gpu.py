@@ -34,8 +34,10 @@ def make_weights(rng):
     return w
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("prompt_len,kv_dtype", [(5, torch.float32), (5, torch.float16), (12, torch.float16)])
-def test_prefill_then_greedy_decode(oracle, prompt_len, kv_dtype):
+def test_prefill_then_greedy_decode(oracle, prompt_len, kv_dtype, fused):
+    """fused: the decode steps run in their five-launches-per-layer form (Decoder.step(decode=True))."""
     rng = np.random.default_rng(prompt_len)
     weights = make_weights(rng)
     ctx = Context(0)
@@ -52,7 +54,11 @@ def test_prefill_then_greedy_decode(oracle, prompt_len, kv_dtype):
     tol = TOL_FP32 * 5 if prompt_len <= 8 else 0.25
     for step in range(4):
         meta = dec.token_meta([seq] * len(ids), pos)
-        got = dec.step(torch.from_numpy(ids).cuda(), torch.from_numpy(meta).cuda(), torch.from_numpy(pos).cuda())
+        l0 = ctx.launch_count()
+        got = dec.step(torch.from_numpy(ids).cuda(), torch.from_numpy(meta).cuda(), torch.from_numpy(pos).cuda(),
+                       decode=fused and step > 0)
+        if fused and step > 0 and kv_dtype == torch.float16:
+            assert ctx.launch_count() - l0 == 2 + 5 * SHAPE.layers  # embedding, five per layer, output projection
         got = got.cpu().numpy()
         want = oracle_step(oracle, SHAPE, weights, ids, meta, pos, kv_k, kv_v, table, 16)
         assert cosine(got, want) >= 0.999, (step, cosine(got, want))

@@ -164,6 +164,47 @@ def test_paged_attention_full_size_properties(ctx):
     assert float((got - v_mark.half().float()).abs().max()) <= 1e-3
 
 
+@pytest.mark.parametrize("n_seq,hq,hkv,hd,lo,hi,neox", [(64, 32, 8, 128, 256, 4096, False), (1, 32, 4, 64, 0, 1, False),
+                                                        (5, 4, 4, 64, 100, 300, True), (3, 8, 2, 128, 126, 130, False)])
+def test_decode_attention_in_one_launch_equals_the_three_steps(ctx, n_seq, hq, hkv, hd, lo, hi, neox):
+    """RoPE + append + attention + chunk merge as one kernel (f16 pool) against rope_qk, then paged_attention: the
+    same arithmetic in the same order, so outputs and pools agree bit for bit -- contexts inside one 128-position
+    chunk (the CTA writes the result itself), across many chunks (last-arriver merge), at a chunk boundary, and twice in
+    a row on one context (the tickets are back at zero)."""
+    rng = np.random.default_rng(n_seq * 31 + hd)
+    bs = 16
+    ctx_lens = rng.integers(lo, hi, n_seq)
+    max_blocks = hi // bs + 2
+    n_blocks = int(sum((l + 1 + bs - 1) // bs for l in ctx_lens))
+    table = np.full((n_seq, max_blocks), 0xFFFFFFFF, dtype=np.uint32)
+    nxt, meta = 0, []
+    for s, L in enumerate(ctx_lens):
+        nb = (L + 1 + bs - 1) // bs
+        table[s, :nb] = np.arange(nxt, nxt + nb)
+        nxt += nb
+        meta.append((s, L, int(table[s, L // bs]) * bs + L % bs, 0))
+    meta = np.array(meta, dtype=np.uint32)
+    pool_k = torch.randn((n_blocks, 2, hkv, bs, hd), device="cuda").half()
+    pool_v = torch.randn((n_blocks, 2, hkv, bs, hd), device="cuda").half()
+    q = torch.randn((n_seq, hq * hd), device="cuda")
+    k_new = torch.randn((n_seq, hkv * hd), device="cuda")
+    v_new = torch.randn((n_seq, hkv * hd), device="cuda")
+    pos = dev(ctx_lens.astype(np.int32))
+    theta = 500000.0
+    for _ in range(2):
+        k1, v1 = pool_k.clone(), pool_v.clone()
+        l0 = ctx.launch_count()
+        got = ctx.paged_attention_decode(dev(meta), q.clone(), k_new.clone(), v_new, k1, v1, dev(table), 1, hq, hkv, hd, bs,
+                                         hd ** -0.5, pos, theta, neox=neox)
+        assert ctx.launch_count() - l0 == 1
+        k2, v2 = pool_k.clone(), pool_v.clone()
+        q2, kn2 = q.clone(), k_new.clone()
+        ctx.rope_qk(q2, kn2, pos, hq, hkv, hd, theta, neox=neox)
+        want = ctx.paged_attention(dev(meta), q2, kn2, v_new, k2, v2, dev(table), 1, hq, hkv, hd, bs, hd ** -0.5)
+        assert torch.equal(k1, k2) and torch.equal(v1, v2)
+        assert torch.equal(got, want)
+
+
 def test_graph_capture_replays_a_call_sequence(ctx, oracle):
     """A short chain (RMSNorm -> Q4_K linear -> add -> argmax) recorded once through the C ABI's own capture and replayed
     on new input contents; the calls that wait for the device refuse to be captured and leave the capture intact."""

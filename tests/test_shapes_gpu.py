@@ -123,7 +123,7 @@ def test_tinyllama_shape_prefill_then_greedy_decode(oracle):
                 cap = []
             else:
                 cap = None
-            got = dec.step(dev(ids), dev(meta), dev(pos))[-1:].cpu().numpy()
+            got = dec.step(dev(ids), dev(meta), dev(pos), decode=step > 0)[-1:].cpu().numpy()
             want = oracle_step(oracle, shape, weights, ids, meta, pos, kv_k, kv_v, table, 16, capture=cap, last_only=True)
             if cap is not None:
                 for layer in (0, shape.layers - 1):
@@ -173,7 +173,7 @@ def test_llama3_8b_shape_layer_slice_batched_decode(oracle):
         ctx_len = rng.integers(64, 601, n_seq).astype(np.int32)
         ids = rng.integers(0, shape.vocab, n_seq).astype(np.int32)
         meta = dec.token_meta(np.arange(n_seq), ctx_len)
-        got = dec.step(dev(ids), dev(meta), dev(ctx_len)).cpu().numpy()
+        got = dec.step(dev(ids), dev(meta), dev(ctx_len), decode=True).cpu().numpy()
         cap = []
         yk, yv = kv_k.copy(), kv_v.copy()
         want = oracle_step(oracle, shape, weights, ids, meta, ctx_len, kv_k, kv_v, table, 16, capture=cap)
