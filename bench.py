@@ -338,8 +338,9 @@ def time_tp_decode_matmuls(ctx, dev, rank: int, world: int, dist, T: int = 64):
     return result
 
 
-def time_decode(ctx, dev, rank: int = 0, world: int = 1, dist=None):
-    """Decode tokens/s of the Llama-shape decoders of BASELINE configs 3 and 4 on one GPU, random-init Q4_K_M weights,
+def time_decode(ctx, dev, rank: int = 0, world: int = 1, dist=None, c4_only: bool = False):
+    """Decode tokens/s of the Llama-shape decoders of BASELINE configs 3 and 4, random-init weights (N(0, 0.02) quantised
+    to the Q4_K_M mix of block formats on the device by marmot_b200.synthetic.normal_blocks),
     fp16 paged KV cache with 16-token blocks, the whole step (embedding gather, 7 matmuls + attention + glue per layer,
     output projection, argmax, position update) captured in one CUDA graph and replayed; greedy sampling stays on the
     device.  Config 3: TinyLlama-1.1B shape, batch 1, 128-token prompt, 256 decoded tokens.  Config 4: Llama-3-8B shape,
@@ -431,7 +432,7 @@ def time_decode(ctx, dev, rank: int = 0, world: int = 1, dist=None):
     def row_bytes_q6(K):
         return (K // 256) * 210
 
-    if world == 1:
+    if world == 1 and not c4_only:
         out["tinyllama_1b_batch1"] = run(TINYLLAMA_1B, 1, [128], 128, 256, True)
         torch.cuda.empty_cache()
     lens = np.random.default_rng(4).integers(256, 4097, 64)
@@ -446,12 +447,12 @@ def time_decode(ctx, dev, rank: int = 0, world: int = 1, dist=None):
 def time_moe_c5(ctx, dev, rank: int, world: int, dist):
     """BASELINE config 5: Mixtral-8x7B-shape expert FFN (8 experts, top-2, d=4096, FFN 14336, Q4_K), 2048 tokens,
     softmax top-2 routing of N(0,1) logits; expert parallel over the ranks (contiguous expert ranges, router
-    replicated, outputs summed by the peer all-reduce).  Host-timed: the operator reads the group sizes back once per
-    call, so it cannot be captured in a CUDA graph."""
+    replicated, outputs summed by the peer all-reduce).  At this size the operator takes its grouped path, whose group
+    sizes stay on the device; the calls are timed by the host clock around ten of them with a synchronize at the end."""
     import torch
 
     from marmot_b200 import tensor_parallel as tp
-    from marmot_b200.synthetic import synthetic_blocks_device
+    from marmot_b200.synthetic import normal_blocks
 
     T, H, FF, E, k = 2048, 4096, 14336, 8, 2
     if E % world:
@@ -464,9 +465,9 @@ def time_moe_c5(ctx, dev, rank: int, world: int, dist):
     probs = torch.softmax(torch.randn((T, E), device=dev, generator=gen), dim=1)
     vals, ids = ctx.topk(probs, k)
     gen.manual_seed(1000 + rank)
-    gate = synthetic_blocks_device(torch, KIND_Q4_K, n_local * FF, H, dev, gen)
-    up = synthetic_blocks_device(torch, KIND_Q4_K, n_local * FF, H, dev, gen)
-    down = synthetic_blocks_device(torch, KIND_Q4_K, n_local * H, FF, dev, gen)
+    gate = normal_blocks(torch, KIND_Q4_K, n_local * FF, H, dev, gen).reshape(-1)  # random init: N(0, 0.02), quantised
+    up = normal_blocks(torch, KIND_Q4_K, n_local * FF, H, dev, gen).reshape(-1)
+    down = normal_blocks(torch, KIND_Q4_K, n_local * H, FF, dev, gen).reshape(-1)
     kinds = (KIND_Q4_K,) * 3
     group = tp.Group(rank, world, dist if world > 1 else None)
     comm = tp.make_peer_comm(ctx, group, T * H * 4) if world > 1 else None
@@ -671,12 +672,36 @@ def main():
     if marmot is not None:
         marmot.close()
 
-    tp_section = moe_section = decode_section = None
+    tp_section = moe_section = decode_section = sharded = None
     if not args.no_extra:
         tp_section = time_tp_decode_matmuls(ctx, dev, rank, world, dist)
         moe_section = time_moe_c5(ctx, dev, rank, world, dist)
         if LLAMA8B["kv"] // 128 % world == 0:
             decode_section = time_decode(ctx, dev, rank, world, dist)
+        if world > 1:
+            # The same two sharded workloads on ONE GPU, in this same run (every rank runs its own copy at the same time;
+            # rank 0 reports its own), so that the strong-scaling efficiency has its denominator beside it.
+            one_moe = time_moe_c5(ctx, dev, 0, 1, None)
+            one_dec = time_decode(ctx, dev, 0, 1, None, c4_only=True) if decode_section is not None else None
+            sharded = {"n_gpus": world, "timing": "device events (decode) / host wall clock (MoE), max over ranks; N=1 from this run, rank 0"}
+            if one_dec is not None:
+                a, b = one_dec["llama3_8b_64seq"], decode_section["llama3_8b_64seq"]
+                sharded["llama3_8b_64seq_tensor_parallel"] = {
+                    "n1_ms_per_step": a["ms_per_step"], "n1_tokens_per_s": a["tokens_per_s"], "ms_per_step": b["ms_per_step"],
+                    "tokens_per_s": b["tokens_per_s"], "speedup": round(a["ms_per_step"] / b["ms_per_step"], 3),
+                    "strong_scaling_efficiency": round(a["ms_per_step"] / b["ms_per_step"] / world, 3)}
+                if "llama3_8b_64seq_replicas" in decode_section:
+                    r = decode_section["llama3_8b_64seq_replicas"]
+                    sharded["llama3_8b_64seq_replicas"] = {
+                        "ms_per_step": r["ms_per_step"], "tokens_per_s": r["tokens_per_s"],
+                        "speedup": round(a["ms_per_step"] / r["ms_per_step"], 3),
+                        "strong_scaling_efficiency": round(a["ms_per_step"] / r["ms_per_step"] / world, 3)}
+            if "ms_per_call" in one_moe and "ms_per_call" in moe_section:
+                sharded["moe_mixtral_expert_ffn_expert_parallel"] = {
+                    "n1_ms_per_call": one_moe["ms_per_call"], "ms_per_call": moe_section["ms_per_call"],
+                    "tokens_per_s": round(moe_section["tokens"] / moe_section["ms_per_call"] * 1e3, 1),
+                    "speedup": round(one_moe["ms_per_call"] / moe_section["ms_per_call"], 3),
+                    "strong_scaling_efficiency": round(one_moe["ms_per_call"] / moe_section["ms_per_call"] / world, 3)}
 
     if rank != 0:
         if world > 1:
@@ -717,6 +742,8 @@ def main():
         line["moe_mixtral_expert_ffn"] = moe_section
     if decode_section is not None:
         line["decode"] = decode_section
+    if sharded is not None:
+        line["sharded_scaling"] = sharded
     if not args.no_extra and world == 1:
         line["other_regimes"] = time_other_regimes(ctx, dev)
     if not args.no_cpu_baseline:

@@ -303,14 +303,21 @@ int mcu_paged_attention(
 /* The decode step's form of the same: RoPE of q and k_new (marmot_rope, or the rope_params of marmot_matmul_qkv,
  * include/marmot/ops/matmul.h:83-95), the append, the attention and the merge of the context chunks as ONE launch.
  * q_dev and k_new_dev hold the projections BEFORE RoPE; they may be rotated in place (callers must not reuse them).
+ * rope_table_dev [T][head_dim/2][2] = {cos, sin} of position * frequency from mcu_rope_table, made once per step and
+ * shared by all layers; NULL makes the call compute one itself (one more launch).
  * Precondition: at most one token per sequence in the call (a token's own K/V row is taken from k_new / v_new, every
  * other position from the pool, so rows appended by the same call are not seen by the call's other tokens); prefill
  * chunks use mcu_rope_qk + mcu_paged_attention.  f16 pools run fused; f32 pools run the stand-alone kernels. */
+int mcu_rope_table(
+    mcu_context_t *ctx, const int32_t *positions_dev, size_t T, size_t head_dim, float theta, float freq_scale,
+    float *table_dev
+);
 int mcu_paged_attention_decode(
     mcu_context_t *ctx, const uint32_t *token_meta_dev, size_t T, float *q_dev, float *k_new_dev, const float *v_new_dev,
     void *kv_k_dev, void *kv_v_dev, int kv_dtype, const uint32_t *block_table_dev, size_t max_blocks_per_seq,
     size_t n_layers, size_t layer, size_t n_q_heads, size_t n_kv_heads, size_t head_dim, size_t block_size, float scale,
-    const int32_t *positions_dev, float rope_theta, float rope_freq_scale, int rope_type, float *out_dev
+    const int32_t *positions_dev, float rope_theta, float rope_freq_scale, int rope_type, const float *rope_table_dev,
+    float *out_dev
 );
 
 /* ---- GGUF model files: the reading half of the reference's loader (src/graph/gguf/loader.cpp) and the uploads of

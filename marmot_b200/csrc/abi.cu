@@ -78,6 +78,7 @@ struct mcu_context {
     Buffer act_qs, act_d, act_bsums, act_half, act_rowscale, x_stage, out_stage, bias_stage;
     Buffer moe_meta, moe_hidden, moe_gate, moe_up, moe_down;
     Buffer gemm_partial;         // split-K partial tiles
+    Buffer rope_table;              // {cos, sin} per token and pair when a decode attention call brings none
     Buffer attn_tickets;            // fused decode attention: one counter per (token, KV head)
     Buffer pro_h;                   // activations after a stand-alone prologue kernel (mcu_linear_multi's general form)
     Buffer i8_partial, i8_tickets;  // integer-MMA matmul: shares of row groups split between CTAs, and their tickets
@@ -135,6 +136,12 @@ int context_attention_scratch(mcu_context *ctx, size_t bytes, void **out) {
     std::lock_guard<std::mutex> lock(ctx->mu);
     if (int rc = ensure(ctx, ctx->attn_partial, bytes)) return rc;
     *out = ctx->attn_partial.ptr;
+    return MCU_SUCCESS;
+}
+int context_rope_table(mcu_context *ctx, size_t bytes, void **out) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (int rc = ensure(ctx, ctx->rope_table, bytes)) return rc;
+    *out = ctx->rope_table.ptr;
     return MCU_SUCCESS;
 }
 // Zero-filled when it is (re)allocated; the attention kernel that uses the tickets leaves them at zero.
@@ -229,7 +236,7 @@ void mcu_context_destroy(mcu_context_t *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     Buffer *bufs[] = {&ctx->act_qs,   &ctx->act_d,      &ctx->act_bsums, &ctx->act_half, &ctx->act_rowscale, &ctx->x_stage, &ctx->out_stage,
-                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down, &ctx->gemm_partial, &ctx->attn_partial, &ctx->i8_partial, &ctx->i8_tickets, &ctx->pro_h, &ctx->attn_tickets};
+                      &ctx->bias_stage, &ctx->moe_meta, &ctx->moe_hidden, &ctx->moe_gate, &ctx->moe_up, &ctx->moe_down, &ctx->gemm_partial, &ctx->attn_partial, &ctx->i8_partial, &ctx->i8_tickets, &ctx->pro_h, &ctx->attn_tickets, &ctx->rope_table};
     for (Buffer *b : bufs)
         if (b->ptr != nullptr) cudaFree(b->ptr);
     if (ctx->dev_err != nullptr) cudaFree(ctx->dev_err);
@@ -428,6 +435,64 @@ static void *mapped_host_pointer(const void *host) {
     return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
 }
 
+// What the last staging launch of a multi-matmul call left in the context's fp16 activation buffer: a later matmul
+// of the same call that wants the same block format class and K order reuses it.
+struct Staged {
+    bool valid = false, kq = false;
+    int k_order = -1;
+};
+
+// The tensor-core matmuls (gemm_tc_supported shapes): stage the activations as fp16 (through `src` when the caller
+// folds a gather, GLU or add + RMSNorm into the staging; needs the one-kernel staging), then the GEMM that suits the
+// weights.  ctx->mu is held by the caller.
+static int gemm_locked(mcu_context *ctx, int kind, const float *x, size_t ldx, const void *w, const void *w2, size_t T, size_t K,
+                       size_t F, const float *bias, float *out, float *out2, size_t ldo, const ActSource *src, Staged *st) {
+    const bool tma = gemm_tma_supported(kind, w, w2, (int)T, (int)K, (int)F);
+    const bool warp_mma = gemm_warp_supported(kind, w, w2, (int)T, (int)K, (int)F);
+    const int k_order = warp_mma ? ACT_ORDER_FRAG16 : tma ? ACT_ORDER_QUAD : ACT_ORDER_NATURAL;
+    const bool kq = kind != MCU_KIND_Q8_0;
+    const size_t bv = (size_t)block_values(kind);
+    const size_t kp = (K + bv - 1) / bv * bv;
+    if (st != nullptr && st->valid && st->kq == kq && st->k_order == k_order) {
+        // staged by an earlier matmul of this call
+    } else if (act_half_fused_smem(kind, (int)K) <= 48 * 1024) {
+        if (int rc = ensure(ctx, ctx->act_half, T * kp * sizeof(__half))) return rc;
+        if (int rc = ensure(ctx, ctx->act_rowscale, T * sizeof(float))) return rc;
+        MCU_CUDA(launch_act_half_fused_from(kind, x, (int)ldx, src != nullptr ? *src : ActSource{}, (int)T, (int)K, k_order,
+                                            (__half *)ctx->act_half.ptr, (float *)ctx->act_rowscale.ptr, ctx->stream));
+        count_launches(1);
+        if (st != nullptr) {
+            st->valid = true;
+            st->kq = kq;
+            st->k_order = k_order;
+        }
+    } else {
+        if (src != nullptr) return fail(MCU_ERROR_NOT_IMPLEMENTED, "rows too long for the one-kernel activation staging");
+        ActBuffers ab;
+        if (int rc = pack_activations(ctx, kind, x, ldx, T, K, true, k_order, ab)) return rc;
+        if (st != nullptr) st->valid = false;
+    }
+    int launches = 0;
+    if (warp_mma) {
+        if (int rc = ensure(ctx, ctx->gemm_partial, gemm_warp_workspace_bytes(kind, (int)T, (int)K, (int)F, w2 != nullptr)))
+            return rc;
+        MCU_CUDA(launch_gemm_warp(kind, w, w2, (const __half *)ctx->act_half.ptr, (const float *)ctx->act_rowscale.ptr,
+                                  (int)kp, (int)T, (int)K, (int)F, bias, out, out2, (int)ldo, (float *)ctx->gemm_partial.ptr,
+                                  ctx->gemm_counters, ctx->dev_err, ctx->stream));
+        launches = 1;
+    } else if (tma) {
+        if (int rc = ensure(ctx, ctx->gemm_partial, gemm_tma_workspace_bytes(kind, (int)T, (int)K, (int)F))) return rc;
+        MCU_CUDA(launch_gemm_tma(kind, w, w2, (const __half *)ctx->act_half.ptr, (const float *)ctx->act_rowscale.ptr,
+                                 (int)kp, (int)T, (int)K, (int)F, bias, out, out2, (int)ldo, (float *)ctx->gemm_partial.ptr,
+                                 ctx->gemm_counters, ctx->dev_err, ctx->stream, &launches));
+    } else {
+        MCU_CUDA(launch_gemm_tc(kind, w, w2, (const __half *)ctx->act_half.ptr, (const float *)ctx->act_rowscale.ptr, (int)kp,
+                                (int)T, (int)K, (int)F, bias, out, out2, (int)ldo, ctx->dev_err, ctx->stream, &launches));
+    }
+    count_launches(launches);
+    return MCU_SUCCESS;
+}
+
 // Core of mcu_linear / mcu_linear_dual on device pointers; ctx->mu is held by the caller.
 static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx, const void *w, const void *w2, size_t T,
                          size_t K, size_t F, const float *bias, float *out, float *out2, size_t ldo) {
@@ -463,44 +528,8 @@ static int linear_locked(mcu_context *ctx, int kind, const float *x, size_t ldx,
         return MCU_SUCCESS;
     }
     if (gemm) {
-        if (gemm_tc_supported(kind, (int)T, (int)K, (int)F)) {
-            const bool tma = gemm_tma_supported(kind, w, w2, (int)T, (int)K, (int)F);
-            const bool warp_mma = gemm_warp_supported(kind, w, w2, (int)T, (int)K, (int)F);
-            const int k_order = warp_mma ? ACT_ORDER_FRAG16 : tma ? ACT_ORDER_QUAD : ACT_ORDER_NATURAL;
-            const size_t bv = (size_t)block_values(kind);
-            const size_t kp = (K + bv - 1) / bv * bv;
-            if (act_half_fused_smem(kind, (int)K) <= 48 * 1024) {
-                if (int rc = ensure(ctx, ctx->act_half, T * kp * sizeof(__half))) return rc;
-                if (int rc = ensure(ctx, ctx->act_rowscale, T * sizeof(float))) return rc;
-                MCU_CUDA(launch_act_half_fused(kind, x, (int)ldx, (int)T, (int)K, k_order, (__half *)ctx->act_half.ptr,
-                                               (float *)ctx->act_rowscale.ptr, ctx->stream));
-                count_launches(1);
-            } else if (int rc = pack_activations(ctx, kind, x, ldx, T, K, true, k_order, ab)) {
-                return rc;
-            }
-            int launches = 0;
-            if (warp_mma) {
-                if (int rc = ensure(ctx, ctx->gemm_partial, gemm_warp_workspace_bytes(kind, (int)T, (int)K, (int)F, w2 != nullptr)))
-                    return rc;
-                MCU_CUDA(launch_gemm_warp(kind, w, w2, (const __half *)ctx->act_half.ptr,
-                                          (const float *)ctx->act_rowscale.ptr, (int)kp, (int)T, (int)K, (int)F, bias, out,
-                                          out2, (int)ldo, (float *)ctx->gemm_partial.ptr, ctx->gemm_counters, ctx->dev_err,
-                                          ctx->stream));
-                launches = 1;
-            } else if (tma) {
-                if (int rc = ensure(ctx, ctx->gemm_partial, gemm_tma_workspace_bytes(kind, (int)T, (int)K, (int)F))) return rc;
-                MCU_CUDA(launch_gemm_tma(kind, w, w2, (const __half *)ctx->act_half.ptr,
-                                         (const float *)ctx->act_rowscale.ptr, (int)kp, (int)T, (int)K, (int)F,
-                                         bias, out, out2, (int)ldo, (float *)ctx->gemm_partial.ptr, ctx->gemm_counters,
-                                         ctx->dev_err, ctx->stream, &launches));
-            }
-            else
-                MCU_CUDA(launch_gemm_tc(kind, w, w2, (const __half *)ctx->act_half.ptr,
-                                        (const float *)ctx->act_rowscale.ptr, (int)kp, (int)T, (int)K, (int)F,
-                                        bias, out, out2, (int)ldo, ctx->dev_err, ctx->stream, &launches));
-            count_launches(launches);
-            return MCU_SUCCESS;
-        }
+        if (gemm_tc_supported(kind, (int)T, (int)K, (int)F))
+            return gemm_locked(ctx, kind, x, ldx, w, w2, T, K, F, bias, out, out2, ldo, nullptr, nullptr);
         if (ctx->regime == MCU_REGIME_GEMM)
             return fail(MCU_ERROR_NOT_IMPLEMENTED, "tensor-core GEMM does not cover kind %d T=%zu K=%zu F=%zu", kind, T, K, F);
     }
@@ -716,8 +745,50 @@ int mcu_linear_multi(mcu_context_t *ctx, const float *x_dev, size_t ldx, size_t 
             count_launches(1);
             return MCU_SUCCESS;
         }
+        // More than eight tokens on the tensor cores: one staging launch (the prologue folded into it) feeds every
+        // matmul that wants the same staging; weights of the other block format class get a second one.
+        const bool contiguous = ldx == K && (pr.aux_dev == nullptr || pr.ld_aux == K) && (gp.x_out == nullptr || pr.ld_x_out == K);
+        bool tensor = (ctx->regime == MCU_REGIME_AUTO || ctx->regime == MCU_REGIME_GEMM) && T > 16 &&
+            (pr.op == MCU_PROLOGUE_NONE || contiguous);
+        for (size_t j = 0; j < n_jobs && tensor; ++j)
+            tensor = gemm_tc_supported(jobs[j].kind, (int)T, (int)K, (int)jobs[j].F) &&
+                act_half_fused_smem(jobs[j].kind, (int)K) <= 48 * 1024;
+        if (tensor) {
+            ActSource src;
+            if (pr.op == MCU_PROLOGUE_ADD_RMSNORM) {
+                src.norm = 1;
+                src.add = pr.aux_dev;
+                src.norm_w = pr.norm_weight_dev;
+                src.eps = pr.eps;
+                src.w_off = pr.weight_offset;
+                src.x_out = gp.x_out;
+            } else if (pr.op == MCU_PROLOGUE_SWIGLU) {
+                src.x2 = pr.aux_dev;
+                src.glu = 1;
+            }
+            Staged st;
+            for (size_t j = 0; j < n_jobs;) {
+                const mcu_linear_job_t &a = jobs[j];
+                const bool pair = j + 1 < n_jobs && jobs[j + 1].kind == a.kind && jobs[j + 1].F == a.F && jobs[j + 1].ldo == a.ldo &&
+                    a.bias_dev == nullptr && jobs[j + 1].bias_dev == nullptr;
+                // x_out is written by the first staging launch only (a second one would add aux twice if x_out is x)
+                ActSource use = src;
+                if (st.valid || j > 0) {
+                    if (use.norm && use.x_out != nullptr) {
+                        use.add = nullptr;  // the sum is already in x_out
+                        use.x_out = nullptr;
+                    }
+                }
+                const float *from = (j > 0 && src.norm && src.x_out != nullptr) ? src.x_out : x_dev;
+                if (int rc = gemm_locked(ctx, a.kind, from, ldx, a.w_dev, pair ? jobs[j + 1].w_dev : nullptr, T, K, a.F, a.bias_dev,
+                                         a.out_dev, pair ? jobs[j + 1].out_dev : nullptr, a.ldo, &use, &st))
+                    return rc;
+                j += pair ? 2 : 1;
+            }
+            return MCU_SUCCESS;
+        }
         if (pr.op != MCU_PROLOGUE_NONE) {
-            if (ldx != K || (pr.aux_dev != nullptr && pr.ld_aux != K) || (gp.x_out != nullptr && pr.ld_x_out != K))
+            if (!contiguous)
                 return fail(MCU_ERROR_NOT_IMPLEMENTED, "the stand-alone prologue kernels need contiguous rows");
             if (int rc = ensure(ctx, ctx->pro_h, T * K * sizeof(float))) return rc;
             h = (float *)ctx->pro_h.ptr;

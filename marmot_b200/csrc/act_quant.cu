@@ -208,7 +208,41 @@ act_half_fused_kernel(const float *__restrict__ x, int ldx, ActSource src, int K
     const size_t row_off = (size_t)(src.row_index != nullptr ? src.row_index[t] : t) * ldx;
     const float *xrow = x + row_off;
     const float *urow = GLU != 0 ? src.x2 + row_off : nullptr;
+    const float *arow = nullptr, *nrow = xrow;  // norm: what is added, and where the sum is read back from
+    float norm_inv = 1.0f;
+    if (GLU == 0 && src.norm) {
+        arow = src.add != nullptr ? src.add + row_off : nullptr;
+        float *orow = src.x_out != nullptr ? src.x_out + row_off : nullptr;
+        float sum = 0.0f;
+        for (int i = threadIdx.x; i < K; i += blockDim.x) {
+            const float v = arow != nullptr ? __fadd_rn(xrow[i], arow[i]) : xrow[i];
+            if (orow != nullptr) orow[i] = v;
+            sum += v * v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) red[warp] = sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float s = 0.0f;
+            for (int i = 0; i < 8; ++i) s += red[i];
+            inv_s = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(s, (float)K), src.eps)));
+        }
+        __syncthreads();
+        norm_inv = inv_s;
+        __syncthreads();  // red and inv_s are used again below
+        if (orow != nullptr) {  // the packer reads the sums back (other threads' elements too: all written before
+            nrow = orow;        // the barriers above) instead of adding again
+            arow = nullptr;
+        }
+    }
     auto value = [&](int k) -> float {
+        if (GLU == 0 && src.norm) {
+            const float v = arow != nullptr ? __fadd_rn(nrow[k], arow[k]) : nrow[k];
+            float y = __fmul_rn(v, norm_inv);
+            if (src.norm_w != nullptr) y = __fmul_rn(y, __fadd_rn(src.norm_w[k], src.w_off));
+            return y;
+        }
         const float g = xrow[k];
         if constexpr (GLU == 0) return g;
         float a;

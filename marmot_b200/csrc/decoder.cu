@@ -11,6 +11,7 @@
 #include "common.cuh"
 #include "kernels.h"
 
+#include <climits>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -160,6 +161,19 @@ __global__ void rope_qk_kernel(float *__restrict__ q, size_t ldq, int n_q_heads,
     }
 }
 
+// {cos, sin} of position * frequency for every token and pair, once per decode step: the fused attention kernel of
+// every layer rotates q and the new k with these (the same sincosf of the same product as rope_kernel).
+__global__ void rope_table_kernel(const int32_t *__restrict__ positions, int half, RopeFreqs freqs, float2 *__restrict__ table) {
+    MCU_PDL_PROLOGUE();
+    const int t = blockIdx.x;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf(__fmul_rn(pos, freqs.f[i]), &s, &c);
+        table[(size_t)t * half + i] = make_float2(c, s);
+    }
+}
+
 // ---------------------------------------------------------------- elementwise
 __global__ void swiglu_kernel(const float *__restrict__ a, const float *__restrict__ b, size_t n, float *__restrict__ out) {
     MCU_PDL_PROLOGUE();
@@ -172,15 +186,24 @@ __global__ void add_kernel(const float *__restrict__ a, const float *__restrict_
     if (i < n) out[i] = __fadd_rn(a[i], b[i]);
 }
 
-// argmax over the last axis, first maximum wins; one CTA per row
-__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ x, int n, int32_t *__restrict__ out) {
+// argmax over the last axis, first maximum wins.  grid (rows, slices): each CTA scans one slice of the row; with
+// several slices the CTAs leave their candidates in `cand` and the one that draws the row's last ticket picks the
+// winner (slices in ascending order, strict >, so the first maximum still wins) and puts the ticket back to zero.
+struct ArgmaxCand {
+    float v;
+    int i;
+};
+__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ x, int n, int slice, ArgmaxCand *cand, int *tickets,
+                                                     int32_t *__restrict__ out) {
     MCU_PDL_PROLOGUE();
     __shared__ float bv[8];
     __shared__ int bi[8];
-    const float *xr = x + (size_t)blockIdx.x * n;
+    const int row = blockIdx.x, sp = blockIdx.y, nsp = gridDim.y;
+    const float *xr = x + (size_t)row * n;
+    const int lo = sp * slice, hi = min(n, lo + slice);
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {  // ascending i per thread: strict > keeps the first maximum
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {  // ascending i per thread: strict > keeps the first maximum
         const float v = xr[i];
         if (v > best || idx == 0x7fffffff) {
             best = v;
@@ -201,14 +224,35 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ x
         bi[threadIdx.x >> 5] = idx;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int w = 1; w < 8; ++w)
-            if (bi[w] != 0x7fffffff && (bi[0] == 0x7fffffff || bv[w] > bv[0] || (bv[w] == bv[0] && bi[w] < bi[0]))) {
-                bv[0] = bv[w];
-                bi[0] = bi[w];
-            }
-        out[blockIdx.x] = bi[0] == 0x7fffffff ? 0 : bi[0];
+    if (threadIdx.x != 0) return;
+    for (int w = 1; w < 8; ++w)
+        if (bi[w] != 0x7fffffff && (bi[0] == 0x7fffffff || bv[w] > bv[0] || (bv[w] == bv[0] && bi[w] < bi[0]))) {
+            bv[0] = bv[w];
+            bi[0] = bi[w];
+        }
+    if (nsp == 1) {
+        out[row] = bi[0] == 0x7fffffff ? 0 : bi[0];
+        return;
     }
+    ArgmaxCand *mine = cand + (size_t)row * nsp;
+    mine[sp].v = bv[0];
+    mine[sp].i = bi[0];
+    __threadfence();
+    const int drawn = atomicAdd(tickets + row, 1);
+    if (drawn != nsp - 1) return;
+    tickets[row] = 0;
+    __threadfence();
+    float wv = -INFINITY;
+    int wi = 0x7fffffff;
+    for (int c = 0; c < nsp; ++c) {
+        const float v = __ldcg(&mine[c].v);
+        const int i = __ldcg(&mine[c].i);
+        if (i != 0x7fffffff && (wi == 0x7fffffff || v > wv)) {
+            wv = v;
+            wi = i;
+        }
+    }
+    out[row] = wi == 0x7fffffff ? 0 : wi;
 }
 
 // ---------------------------------------------------------------- paged attention
@@ -396,12 +440,13 @@ __global__ void __launch_bounds__(32 * PA_MAX_GROUP) paged_attention_kernel(Page
 // One CTA per (KV head, token, chunk of 128 positions); each of its four warps owns one tile of 32 positions: it
 // copies the tile's K and V rows into its own shared-memory slice with cp.async (16-byte pieces, XOR-swizzled by row
 // so that ldmatrix reads are conflict-free), and meanwhile builds the A fragments of Q.  The M rows of the MMA are
-// the query heads of the KV head's group (at most 8; rows 8..15 are zero), so a K/V byte is read from HBM once for
+// the query heads of the KV head's group (at most 8), so a K/V byte is read from HBM once for
 // the whole group and scored by one instruction stream.
 //   S = Q K^T : A = Q (heads x dims), B = K rows as they lie in the pool (ldmatrix, no transpose)
 //   O = P V   : A = P straight from the S accumulators, B = V through ldmatrix.trans
-// Q and P are split into an f16 head and an f16 tail (x = hi + lo, two MMAs each), K and V are f16 already, so the
-// products carry about 22 significant bits and the result stays within 1e-6 of f32 arithmetic.
+// Q and P are split into an f16 head and an f16 tail (x = hi + lo): the heads go to rows 0..7 of A, the tails to rows
+// 8..15 (the group has at most eight query heads), so ONE MMA gives both partial products; K and V are f16 already,
+// so the products carry about 22 significant bits and the result stays within 1e-6 of f32 arithmetic.
 // A warp sees exactly one tile, so its softmax needs no running rescale; the four warps' states are merged through
 // shared memory in warp order and written as one partial state per (token, query head, chunk).
 constexpr int PM_WARPS = 4;
@@ -421,11 +466,13 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t &r0, uint3
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                  : "r"(addr));
 }
-// D += A B with the lower eight rows of A zero (a1 = a3 = 0).
-__device__ __forceinline__ void mma_top_rows(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+// D += A B, all sixteen rows of A: rows 0..7 carry the f16 heads of the eight query heads' values, rows 8..15 their
+// f16 tails, so one instruction yields both partial products (c[0..1] = head row g, c[2..3] = tail row g).
+__device__ __forceinline__ void mma_hi_lo(float (&c)[4], uint32_t a_hi0, uint32_t a_lo0, uint32_t a_hi1, uint32_t a_lo1, uint32_t b0,
+                                          uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+                 : "r"(a_hi0), "r"(a_lo0), "r"(a_hi1), "r"(a_lo1), "r"(b0), "r"(b1));
 }
 // (x, y) as an f16 pair plus the f16 pair of what that rounding lost.
 __device__ __forceinline__ void split_half2(float x, float y, uint32_t &hi, uint32_t &lo) {
@@ -444,14 +491,13 @@ __device__ __forceinline__ void split_half2(float x, float y, uint32_t &hi, uint
 // the CTA that draws the last ticket of a (token, KV head) merges the chunk states in chunk order -- the arithmetic of
 // paged_attention_merge_kernel, so both forms give the same bits.
 struct FusedDecode {
-    const int32_t *positions;  // [T], for RoPE
-    int *tickets;              // [T][kv_heads], zero between launches
+    const float2 *rope;  // [T][HD / 2] {cos, sin} of position * frequency, from rope_table_kernel
+    int *tickets;        // [T][kv_heads], zero between launches; null: the chunk states are merged by a kernel of its own
     int neox;
 };
 
 template <int HD, bool FUSED>
-__global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(PagedParams p, float *partial, FusedDecode fd,
-                                                                            RopeFreqs freqs) {
+__global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(PagedParams p, float *partial, FusedDecode fd) {
     constexpr int ROWB = HD * 2;            // bytes of a K or V row
     constexpr int PIECES = ROWB / 16;       // 16-byte pieces per row
     constexpr int TILEB = PM_TILE * ROWB;
@@ -480,23 +526,6 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
     // FUSED: the token's own row (position kv_len - 1) comes from k_new / v_new, not from the pool
     const uint32_t new_pos = kv_len - 1u;
     const int new_row = FUSED && new_pos >= k0 && new_pos < k0 + PM_TILE ? (int)(new_pos - k0) : -1;
-    float *s_q = (float *)(pm_smem + PM_WARPS * 2 * TILEB);  // FUSED: the group's rotated query heads [8][HD]
-    if (FUSED) {
-        const int half = HD / 2;
-        const float posf = (float)fd.positions[t];
-        for (int idx = threadIdx.x; idx < gsize * half; idx += blockDim.x) {
-            const int hh = idx / half, i = idx - hh * half;
-            float sn, cs;
-            sincosf(__fmul_rn(posf, freqs.f[i]), &sn, &cs);
-            const int e = fd.neox ? i : 2 * i, o = fd.neox ? i + half : 2 * i + 1;
-            const float *row = p.q + ((size_t)t * p.n_q_heads + (size_t)h * gsize + hh) * HD;
-            const float xe = row[e], xo = row[o];
-            s_q[hh * HD + e] = __fsub_rn(__fmul_rn(xe, cs), __fmul_rn(xo, sn));
-            s_q[hh * HD + o] = __fadd_rn(__fmul_rn(xe, sn), __fmul_rn(xo, cs));
-        }
-        __syncthreads();
-    }
-
     // stage the tile: lane r looks up the pool block of position k0 + r, the warp copies two rows per step
     uint32_t live = 0;
     if (has_tile) {
@@ -523,7 +552,7 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
         if (FUSED && new_row >= 0) {
             // the new K row rotated, the new V row, both as f16: into this warp's tile and into the pool slot
             const int half = HD / 2, r = new_row;
-            const float posf = (float)fd.positions[t];
+            const float2 *rope = fd.rope + (size_t)t * half;
             const uint32_t kv_slot = p.meta[t * 4 + 2];
             const size_t dst = (size_t)(kv_slot >> p.block_shift) * s0 + head_off + (size_t)(kv_slot & (uint32_t)(bs - 1)) * s3;
             const float *krow = p.k_new + ((size_t)t * p.n_kv_heads + h) * HD;
@@ -531,8 +560,7 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
             uint8_t *tK = pm_smem + warp * 2 * TILEB, *tV = tK + TILEB;
             auto tile_off = [&](int d) { return r * ROWB + ((((d >> 3) ^ (r & 7))) << 4) + (d & 7) * 2; };
             for (int i = lane; i < half; i += 32) {
-                float sn, cs;
-                sincosf(__fmul_rn(posf, freqs.f[i]), &sn, &cs);
+                const float cs = rope[i].x, sn = rope[i].y;
                 const int e = fd.neox ? i : 2 * i, o = fd.neox ? i + half : 2 * i + 1;
                 const float xe = krow[e], xo = krow[o];
                 const __half ke = __float2half_rn(__fsub_rn(__fmul_rn(xe, cs), __fmul_rn(xo, sn)));
@@ -550,18 +578,37 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
         }
     }
 
-    // A fragments of Q (row g = query head g of the group): a0 = dims 16s + 2tq, +1; a2 = dims 16s + 8 + 2tq, +1
+    // A fragments of Q (row g = query head g of the group): a0 = dims 16s + 2tq, +1; a2 = dims 16s + 8 + 2tq, +1.
+    // FUSED: the values are rotated on the way (the partner of a dimension is its neighbour, or lies half a head
+    // away with the NeoX pairing; either way this lane reads it itself).
     uint32_t qhi[KS][2], qlo[KS][2];
     {
         const bool head_ok = g < gsize;
-        const float *qrow = FUSED ? s_q + (head_ok ? g : 0) * HD
-                                  : p.q + ((size_t)t * p.n_q_heads + (size_t)h * gsize + (head_ok ? g : 0)) * HD;
+        const float *qrow = p.q + ((size_t)t * p.n_q_heads + (size_t)h * gsize + (head_ok ? g : 0)) * HD;
+        const float2 *rope = FUSED ? fd.rope + (size_t)t * (HD / 2) : nullptr;
 #pragma unroll
         for (int s = 0; s < KS; ++s)
 #pragma unroll
             for (int hk = 0; hk < 2; ++hk) {
-                float x = head_ok ? qrow[16 * s + 8 * hk + 2 * tq] : 0.0f;
-                float y = head_ok ? qrow[16 * s + 8 * hk + 2 * tq + 1] : 0.0f;
+                const int d = 16 * s + 8 * hk + 2 * tq;
+                float x = head_ok ? qrow[d] : 0.0f;
+                float y = head_ok ? qrow[d + 1] : 0.0f;
+                if (FUSED) {
+                    if (!fd.neox) {  // the pair (d, d + 1)
+                        const float2 cs = rope[d >> 1];
+                        const float xr = __fsub_rn(__fmul_rn(x, cs.x), __fmul_rn(y, cs.y));
+                        y = __fadd_rn(__fmul_rn(x, cs.y), __fmul_rn(y, cs.x));
+                        x = xr;
+                    } else {  // the pairs (d, d +- HD/2) and (d + 1, d + 1 +- HD/2)
+                        constexpr int half = HD / 2;
+                        const bool low = d < half;
+                        const float px = head_ok ? qrow[low ? d + half : d - half] : 0.0f;
+                        const float py = head_ok ? qrow[low ? d + 1 + half : d + 1 - half] : 0.0f;
+                        const float2 c0 = rope[low ? d : d - half], c1 = rope[low ? d + 1 : d + 1 - half];
+                        x = low ? __fsub_rn(__fmul_rn(x, c0.x), __fmul_rn(px, c0.y)) : __fadd_rn(__fmul_rn(px, c0.y), __fmul_rn(x, c0.x));
+                        y = low ? __fsub_rn(__fmul_rn(y, c1.x), __fmul_rn(py, c1.y)) : __fadd_rn(__fmul_rn(py, c1.y), __fmul_rn(y, c1.x));
+                    }
+                }
                 if (p.scale != 1.0f) {
                     x = __fmul_rn(x, p.scale);
                     y = __fmul_rn(y, p.scale);
@@ -577,8 +624,9 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
     if (has_tile) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncwarp();
-        // S[head g][key 8j + 2tq, +1] in sc[j][0..1].  The head and the tail of Q accumulate separately and the four
-        // key tiles alternate, so that consecutive MMAs never wait for one another's accumulator.
+        // S[head g][key 8j + 2tq, +1] = sc[j][0..1] (f16 head of Q) + sc[j][2..3] (its tail).  Even and odd k steps
+        // accumulate separately and the four key tiles alternate, so that consecutive MMAs never wait for one
+        // another's accumulator.
         float sc[4][4], st[4][4];
 #pragma unroll
         for (int j = 0; j < 4; ++j)
@@ -594,18 +642,14 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
                 ldsm_x4(sK + (uint32_t)(r * ROWB + ((pc ^ (r & 7)) << 4)), b[j][0], b[j][1], b[j][2], b[j][3]);
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) mma_top_rows(sc[j], qhi[s][0], qhi[s][1], b[j][0], b[j][1]);
+            for (int j = 0; j < 4; ++j) mma_hi_lo(sc[j], qhi[s][0], qlo[s][0], qhi[s][1], qlo[s][1], b[j][0], b[j][1]);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) mma_top_rows(st[j], qlo[s][0], qlo[s][1], b[j][0], b[j][1]);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) mma_top_rows(sc[j], qhi[s + 1][0], qhi[s + 1][1], b[j][2], b[j][3]);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) mma_top_rows(st[j], qlo[s + 1][0], qlo[s + 1][1], b[j][2], b[j][3]);
+            for (int j = 0; j < 4; ++j) mma_hi_lo(st[j], qhi[s + 1][0], qlo[s + 1][0], qhi[s + 1][1], qlo[s + 1][1], b[j][2], b[j][3]);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            sc[j][0] += st[j][0];
-            sc[j][1] += st[j][1];
+            sc[j][0] = (sc[j][0] + st[j][0]) + (sc[j][2] + st[j][2]);
+            sc[j][1] = (sc[j][1] + st[j][1]) + (sc[j][3] + st[j][3]);
         }
         float mx = -INFINITY;
 #pragma unroll
@@ -645,14 +689,9 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
                     ldsm_x4_trans(sV + (uint32_t)(r * ROWB + ((pc ^ (r & 7)) << 4)), b[h2][0], b[h2][1], b[h2][2], b[h2][3]);
                 }
 #pragma unroll
-                for (int h2 = 0; h2 < 2; ++h2) {
-                    mma_top_rows(o[n + 2 * h2], phi[2 * u], phi[2 * u + 1], b[h2][0], b[h2][1]);
-                    mma_top_rows(o[n + 2 * h2 + 1], phi[2 * u], phi[2 * u + 1], b[h2][2], b[h2][3]);
-                }
-#pragma unroll
-                for (int h2 = 0; h2 < 2; ++h2) {
-                    mma_top_rows(o[n + 2 * h2], plo[2 * u], plo[2 * u + 1], b[h2][0], b[h2][1]);
-                    mma_top_rows(o[n + 2 * h2 + 1], plo[2 * u], plo[2 * u + 1], b[h2][2], b[h2][3]);
+                for (int h2 = 0; h2 < 2; ++h2) {  // o[..][0..1] from the heads of P, o[..][2..3] from the tails
+                    mma_hi_lo(o[n + 2 * h2], phi[2 * u], plo[2 * u], phi[2 * u + 1], plo[2 * u + 1], b[h2][0], b[h2][1]);
+                    mma_hi_lo(o[n + 2 * h2 + 1], phi[2 * u], plo[2 * u], phi[2 * u + 1], plo[2 * u + 1], b[h2][2], b[h2][3]);
                 }
             }
     }
@@ -663,7 +702,7 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
     float *s_e = s_l + PM_WARPS * 8;                                      // weight of a warp's state in the chunk state
 #pragma unroll
     for (int n = 0; n < NT; ++n)
-        *(float2 *)(s_o + ((size_t)warp * 8 + g) * HD + 8 * n + 2 * tq) = make_float2(o[n][0], o[n][1]);
+        *(float2 *)(s_o + ((size_t)warp * 8 + g) * HD + 8 * n + 2 * tq) = make_float2(o[n][0] + o[n][2], o[n][1] + o[n][3]);
     if (tq == 0) {
         s_m[warp * 8 + g] = m;
         s_l[warp * 8 + g] = l;
@@ -687,7 +726,7 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
             L += s_l[w * 8 + hh] * e;
             O += s_o[((size_t)w * 8 + hh) * HD + d] * e;
         }
-        if (FUSED && (kv_len <= (uint32_t)PM_CHUNK || n_chunks == 1)) {  // the only chunk of its token: this is the result
+        if (FUSED && fd.tickets != nullptr && (kv_len <= (uint32_t)PM_CHUNK || n_chunks == 1)) {  // the only chunk of its token: this is the result
             p.out[((size_t)t * p.n_q_heads + (size_t)h * gsize + hh) * HD + d] = L > 0.0f ? O / L : 0.0f;
             continue;
         }
@@ -701,7 +740,7 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
         }
         pr[2 + d] = O;
     }
-    if (!FUSED || kv_len <= (uint32_t)PM_CHUNK || n_chunks == 1) return;
+    if (!FUSED || kv_len <= (uint32_t)PM_CHUNK || n_chunks == 1 || fd.tickets == nullptr) return;
     // the last CTA of this (token, KV head) to finish merges the chunk states
     const int live_chunks = min(n_chunks, (int)((kv_len + (uint32_t)PM_CHUNK - 1u) / (uint32_t)PM_CHUNK));
     __threadfence();
@@ -715,22 +754,55 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // The chunk states' maxima and sums first, all loads at once, into shared memory (the tile buffers are free); then
+    // every (head, dimension) adds up its column with the loads of eight chunks in flight.  Same operations in the same
+    // order as paged_attention_merge_kernel.
+    float *s_cm = (float *)pm_smem;                 // [head][chunk] m, later the chunk's weight exp(m - M)
+    float *s_cl = s_cm + 8 * live_chunks;           // [head][chunk] l
+    float *s_M = s_cl + 8 * live_chunks;            // [head]
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < gsize * live_chunks; idx += blockDim.x) {
+        const int hh = idx / live_chunks, cc = idx - hh * live_chunks;
+        const float *pr = partial + (((size_t)t * p.n_q_heads + h * gsize + hh) * n_chunks + cc) * (HD + 2);
+        s_cm[hh * live_chunks + cc] = __ldcg(pr);
+        s_cl[hh * live_chunks + cc] = __ldcg(pr + 1);
+    }
+    __syncthreads();
+    if (threadIdx.x < gsize) {
+        float M = -INFINITY;
+        for (int cc = 0; cc < live_chunks; ++cc) M = fmaxf(M, s_cm[threadIdx.x * live_chunks + cc]);
+        s_M[threadIdx.x] = M;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < gsize * live_chunks; idx += blockDim.x) {
+        const int hh = idx / live_chunks;
+        const float mc = s_cm[idx], M = s_M[hh];
+        s_cm[idx] = (M == -INFINITY || mc == -INFINITY) ? 0.0f : expf(mc - M);  // weight 0: the merge kernel skips the chunk
+    }
+    __syncthreads();
     for (int idx = threadIdx.x; idx < gsize * HD; idx += blockDim.x) {
         const int hh = idx / HD, d = idx - hh * HD;
         const int qh = h * gsize + hh;
-        const float *pr = partial + ((size_t)t * p.n_q_heads + qh) * n_chunks * (HD + 2);
-        float M = -INFINITY;
-        for (int cc = 0; cc < live_chunks; ++cc) M = fmaxf(M, __ldcg(pr + (size_t)cc * (HD + 2)));
+        const float *pr = partial + ((size_t)t * p.n_q_heads + qh) * n_chunks * (HD + 2) + 2 + d;
+        const float *e = s_cm + hh * live_chunks, *lc = s_cl + hh * live_chunks;
         float L = 0.0f, o = 0.0f;
-        if (M != -INFINITY) {
-            for (int cc = 0; cc < live_chunks; ++cc) {
-                const float mc = __ldcg(pr + (size_t)cc * (HD + 2));
-                if (mc == -INFINITY) continue;
-                const float e = expf(mc - M);
-                L += __ldcg(pr + (size_t)cc * (HD + 2) + 1) * e;
-                o += __ldcg(pr + (size_t)cc * (HD + 2) + 2 + d) * e;
-            }
+        int cc = 0;
+        for (; cc + 8 <= live_chunks; cc += 8) {
+            float vals[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) vals[u] = __ldcg(pr + (size_t)(cc + u) * (HD + 2));
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (e[cc + u] != 0.0f) {
+                    L += lc[cc + u] * e[cc + u];
+                    o += vals[u] * e[cc + u];
+                }
         }
+        for (; cc < live_chunks; ++cc)
+            if (e[cc] != 0.0f) {
+                L += lc[cc] * e[cc];
+                o += __ldcg(pr + (size_t)cc * (HD + 2)) * e[cc];
+            }
         p.out[((size_t)t * p.n_q_heads + qh) * HD + d] = L > 0.0f ? o / L : 0.0f;
     }
 }
@@ -878,7 +950,22 @@ int mcu_argmax(mcu_context_t *ctx, const float *x_dev, size_t rows, size_t n, in
     if (int rc = dec_begin(ctx, &s)) return rc;
     if (rows == 0) return MCU_SUCCESS;
     if (x_dev == nullptr || out_dev == nullptr || n == 0) return set_error(MCU_ERROR_INVALID_ARGUMENT, "null tensor data");
-    DEC_CUDA(launch_pdl(argmax_kernel, dim3((unsigned)rows), dim3(256), s, x_dev, (int)n, out_dev));
+    if (n > (size_t)INT_MAX || rows > 65535u * 1024u) return set_error(MCU_ERROR_INVALID_ARGUMENT, "dimension too large");
+    // slices of at least 2048 values, as many CTAs as fill the device once
+    size_t slices = (n + 2047) / 2048;
+    const size_t want = ((size_t)device_sm_count() + rows - 1) / rows;
+    if (slices > want) slices = want;
+    if (slices > 64) slices = 64;
+    if (slices < 1) slices = 1;
+    const size_t slice = (n + slices - 1) / slices;
+    slices = (n + slice - 1) / slice;
+    void *cand = nullptr, *tickets = nullptr;
+    if (slices > 1) {  // the attention's scratch areas: stream order keeps their users apart, and both leave the tickets at zero
+        if (int rc = context_attention_scratch(ctx, rows * slices * sizeof(ArgmaxCand), &cand)) return rc;
+        if (int rc = context_attention_tickets(ctx, rows * sizeof(int), &tickets)) return rc;
+    }
+    DEC_CUDA(launch_pdl(argmax_kernel, dim3((unsigned)rows, (unsigned)slices), dim3(256), s, x_dev, (int)n, (int)slice,
+                        (ArgmaxCand *)cand, (int *)tickets, out_dev));
     count_launches(1);
     return MCU_SUCCESS;
 }
@@ -964,9 +1051,9 @@ int mcu_paged_attention(mcu_context_t *ctx, const uint32_t *token_meta_dev, size
             DEC_CUDA(cudaFuncSetAttribute(paged_attention_mma_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         DEC_CUDA(launch_pdl(kv_append_kernel<__half>, ag, dim3(128), s, p, (int)head_dim));
         if (head_dim == 64)
-            DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<64, false>, qg, dim3(32 * PM_WARPS), smem, s, p, partial, FusedDecode{}, RopeFreqs{}));
+            DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<64, false>, qg, dim3(32 * PM_WARPS), smem, s, p, partial, FusedDecode{}));
         else
-            DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<128, false>, qg, dim3(32 * PM_WARPS), smem, s, p, partial, FusedDecode{}, RopeFreqs{}));
+            DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<128, false>, qg, dim3(32 * PM_WARPS), smem, s, p, partial, FusedDecode{}));
     } else {
         DEC_CUDA(launch_pdl(kv_append_kernel<float>, ag, dim3(128), s, p, (int)head_dim));
         if (head_dim == 64) DEC_CUDA(launch_pdl(paged_attention_kernel<float, 64>, qg, tb, s, p, (int)chunk, partial));
@@ -981,17 +1068,35 @@ int mcu_paged_attention(mcu_context_t *ctx, const uint32_t *token_meta_dev, size
 }
 
 
+int mcu_rope_table(mcu_context_t *ctx, const int32_t *positions_dev, size_t T, size_t head_dim, float theta, float freq_scale,
+                   float *table_dev) {
+    cudaStream_t s;
+    if (int rc = dec_begin(ctx, &s)) return rc;
+    if (T == 0) return MCU_SUCCESS;
+    if (positions_dev == nullptr || table_dev == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "null tensor data");
+    if (head_dim % 2 != 0 || head_dim / 2 > (size_t)ROPE_MAX_PAIRS || ((uintptr_t)table_dev & 7))
+        return set_error(MCU_ERROR_DIMENSION_MISMATCH, "RoPE table: even head_dim up to 256, 8-byte aligned table");
+    RopeFreqs fr = {};
+    for (size_t i = 0; i < head_dim / 2; ++i)
+        fr.f[i] = powf(theta, -((float)(2 * i) / (float)head_dim)) * freq_scale;  // src/core/helpers/rope.c:111
+    DEC_CUDA(launch_pdl(rope_table_kernel, dim3((unsigned)T), dim3(64), s, positions_dev, (int)(head_dim / 2), fr, (float2 *)table_dev));
+    count_launches(1);
+    return MCU_SUCCESS;
+}
+
 int mcu_paged_attention_decode(mcu_context_t *ctx, const uint32_t *token_meta_dev, size_t T, float *q_dev, float *k_new_dev,
                                const float *v_new_dev, void *kv_k_dev, void *kv_v_dev, int kv_dtype,
                                const uint32_t *block_table_dev, size_t max_blocks_per_seq, size_t n_layers, size_t layer,
                                size_t n_q_heads, size_t n_kv_heads, size_t head_dim, size_t block_size, float scale,
                                const int32_t *positions_dev, float rope_theta, float rope_freq_scale, int rope_type,
-                               float *out_dev) {
+                               const float *rope_table_dev, float *out_dev) {
     cudaStream_t s;
     if (int rc = dec_begin(ctx, &s)) return rc;
     if (T == 0) return MCU_SUCCESS;
+    // (the merge at the end of the fused kernel keeps two floats per query head and chunk in shared memory)
     const bool fused = kv_dtype == MCU_KV_F16 && (head_dim == 64 || head_dim == 128) && n_kv_heads != 0 &&
-        n_q_heads % n_kv_heads == 0 && n_q_heads / n_kv_heads <= (size_t)PA_MAX_GROUP;
+        n_q_heads % n_kv_heads == 0 && n_q_heads / n_kv_heads <= (size_t)PA_MAX_GROUP &&
+        (max_blocks_per_seq * block_size + PM_CHUNK - 1) / PM_CHUNK <= 1024;
     if (!fused) {  // the three stand-alone steps; they check their own arguments
         if (int rc = mcu_rope_qk(ctx, q_dev, n_q_heads * head_dim, n_q_heads, k_new_dev, n_kv_heads * head_dim, n_kv_heads,
                                  positions_dev, T, head_dim, rope_theta, rope_freq_scale, rope_type))
@@ -1029,27 +1134,42 @@ int mcu_paged_attention_decode(mcu_context_t *ctx, const uint32_t *token_meta_de
     const size_t max_positions = max_blocks_per_seq * block_size;
     const size_t n_chunks = (max_positions + PM_CHUNK - 1) / PM_CHUNK;
     if (n_chunks > 65535) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "paged_attention context bound too long");
+    // Few CTAs: the step is a chain of latencies, and the last CTA of a token merging in place saves a launch.  Many
+    // CTAs: the fence and the ticket keep every CTA (and its shared memory) alive for a round trip to L2 longer, which
+    // at 64 sequences x 8 KV heads x ~17 chunks cost 25 % of the kernel (measured); a merge kernel is cheaper there.
+    const bool ticket_merge = n_kv_heads * T * n_chunks <= 4 * (size_t)device_sm_count();
     void *scratch = nullptr, *tickets = nullptr;
     if (int rc = context_attention_scratch(ctx, T * n_q_heads * n_chunks * (head_dim + 2) * sizeof(float), &scratch)) return rc;
-    if (int rc = context_attention_tickets(ctx, T * n_kv_heads * sizeof(int), &tickets)) return rc;
+    if (ticket_merge)
+        if (int rc = context_attention_tickets(ctx, T * n_kv_heads * sizeof(int), &tickets)) return rc;
+    if (rope_table_dev == nullptr) {  // no table from the caller: make one for this call (one more launch)
+        void *tab = nullptr;
+        if (int rc = context_rope_table(ctx, T * (head_dim / 2) * 2 * sizeof(float), &tab)) return rc;
+        if (int rc = mcu_rope_table(ctx, positions_dev, T, head_dim, rope_theta, rope_freq_scale, (float *)tab)) return rc;
+        rope_table_dev = (const float *)tab;
+    }
     FusedDecode fd;
-    fd.positions = positions_dev;
+    fd.rope = (const float2 *)rope_table_dev;
     fd.tickets = (int *)tickets;
     fd.neox = rope_type == MCU_ROPE_NEOX ? 1 : 0;
-    RopeFreqs fr = {};
-    for (size_t i = 0; i < head_dim / 2; ++i)
-        fr.f[i] = powf(rope_theta, -((float)(2 * i) / (float)head_dim)) * rope_freq_scale;  // src/core/helpers/rope.c:111
     const dim3 qg((unsigned)n_kv_heads, (unsigned)T, (unsigned)n_chunks);
-    // the tiles, then the group's rotated query heads
-    const size_t smem = (size_t)PM_WARPS * 2 * PM_TILE * head_dim * 2 + (size_t)PA_MAX_GROUP * head_dim * sizeof(float);
+    const size_t smem = (size_t)PM_WARPS * 2 * PM_TILE * head_dim * 2;
     if (head_dim == 64) {
         DEC_CUDA(cudaFuncSetAttribute(paged_attention_mma_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<64, true>, qg, dim3(32 * PM_WARPS), smem, s, p, (float *)scratch, fd, fr));
+        DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<64, true>, qg, dim3(32 * PM_WARPS), smem, s, p, (float *)scratch, fd));
     } else {
         DEC_CUDA(cudaFuncSetAttribute(paged_attention_mma_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<128, true>, qg, dim3(32 * PM_WARPS), smem, s, p, (float *)scratch, fd, fr));
+        DEC_CUDA(launch_pdl_smem(paged_attention_mma_kernel<128, true>, qg, dim3(32 * PM_WARPS), smem, s, p, (float *)scratch, fd));
     }
     count_launches(1);
+    if (!ticket_merge) {
+        const dim3 mg((unsigned)n_q_heads, (unsigned)T);
+        if (head_dim == 64)
+            DEC_CUDA(launch_pdl(paged_attention_merge_kernel<64>, mg, dim3(64), s, p, (int)PM_CHUNK, (int)n_chunks, (const float *)scratch));
+        else
+            DEC_CUDA(launch_pdl(paged_attention_merge_kernel<128>, mg, dim3(128), s, p, (int)PM_CHUNK, (int)n_chunks, (const float *)scratch));
+        count_launches(1);
+    }
     return MCU_SUCCESS;
 }
 

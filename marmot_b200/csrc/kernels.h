@@ -37,11 +37,18 @@ cudaError_t launch_act_half_fused(int kind, const float *x, int ldx, int T, int 
 // Where the staging kernel takes its rows from, for callers that would otherwise run a gather or a GLU pass first:
 // row t comes from x + row_index[t] * ldx when row_index is set; with x2 set the value is act(x) * x2 (glu 1 = SiLU,
 // 2 = GELU, rounded like the MoE GLU kernel); rows outside [*row_lo, *row_hi) (device-resident) are skipped.
+// With norm set the row is first x + add (add may be null; the sum goes to x_out when that is set, which may be x
+// itself: a CTA owns its row) and the values are rms_norm(row) * (norm_w + w_off), the operations and their order
+// those of the stand-alone add + RMSNorm kernel.
 struct ActSource {
     const float *x2 = nullptr;
     int glu = 0;
     const int32_t *row_index = nullptr;
     const int *row_lo = nullptr, *row_hi = nullptr;
+    int norm = 0;
+    const float *add = nullptr, *norm_w = nullptr;
+    float eps = 0.0f, w_off = 0.0f;
+    float *x_out = nullptr;
 };
 cudaError_t launch_act_half_fused_from(int kind, const float *x, int ldx, const ActSource &src, int T, int K, int k_order,
                                        __half *xh, float *rowscale, cudaStream_t s);
@@ -171,6 +178,7 @@ int *context_err_flag(mcu_context *ctx);
 // workspace of the context for the split-KV attention partials (grows on demand)
 int context_attention_scratch(mcu_context *ctx, size_t bytes, void **out);
 int context_attention_tickets(mcu_context *ctx, size_t bytes, void **out);  // zero-filled counters
+int context_rope_table(mcu_context *ctx, size_t bytes, void **out);
 // mcu_linear with the all-reduce fused into the matmul's epilogue; MCU_ERROR_NOT_IMPLEMENTED when the shape or the
 // weights do not allow it (the caller then runs the matmul and the all-reduce kernel separately).
 int linear_fused_allreduce(mcu_context *ctx, int kind, const float *x, size_t ldx, const void *w, size_t T, size_t K,

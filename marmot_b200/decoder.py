@@ -8,6 +8,8 @@ Used by bench.py (decode tokens/s of BASELINE configs 3 and 4) and by the decode
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 
 import numpy as np
@@ -66,7 +68,7 @@ class Decoder:
         import torch
 
         from . import tensor_parallel as tp
-        from .synthetic import synthetic_blocks_device
+        from .synthetic import normal_blocks
 
         self.ctx, self.shape, self.torch = ctx, shape, torch
         self.block_size, self.max_seqs = block_size, max_seqs
@@ -129,7 +131,7 @@ class Decoder:
                 return None
             if weights is not None:
                 return ctx.upload(cut(name, kind, weights[name]))
-            return synthetic_blocks_device(torch, kind, rows, cols, dev, gen)
+            return normal_blocks(torch, kind, rows, cols, dev, gen).reshape(-1)  # random init: N(0, 0.02), quantised
 
         def vec(name, n):
             if device_weights is not None:
@@ -273,6 +275,7 @@ class Decoder:
         ctx.rmsnorm(x, self.layers[0]["attn_norm"], s.rms_eps, out=h)
         # up to eight tokens q / k / v are one launch; beyond, three matmuls that run side by side on streams of their own
         side = self._side_contexts() if T > 8 else ()
+        fuse_ffn = self.group.world == 1 and T > 16 and s.ffn > 0 and not os.environ.get("MARMOT_DECODER_UNFUSED_FFN")  # diagnostic
         main = self._main_stream() if side else None
         for i, lw in enumerate(self.layers):
             if side:
@@ -288,18 +291,29 @@ class Decoder:
                 ctx.linear_multi(h, [(kd[f"l{i}.wq"], lw["wq"], hq * hd, q), (kd[f"l{i}.wk"], lw["wk"], hkv * hd, k),
                                      (kd[f"l{i}.wv"], lw["wv"], hkv * hd, v)])
             if decode:
+                if i == 0:
+                    rope = ctx.rope_table(positions, hd, s.rope_theta, out=self._buf("rope", (T, hd // 2, 2)))
                 ctx.paged_attention_decode(meta, q, k, v, self.kv_k, self.kv_v, self.block_table, i, hq, hkv, hd,
-                                           self.block_size, scale, positions, s.rope_theta, out=att)
+                                           self.block_size, scale, positions, s.rope_theta, rope_table=rope, out=att)
             else:
                 ctx.rope_qk(q, k, positions, hq, hkv, hd, s.rope_theta)
                 ctx.paged_attention(meta, q, k, v, self.kv_k, self.kv_v, self.block_table, i, hq, hkv, hd, self.block_size,
                                     scale, out=att)
             self._row_parallel(kd[f"l{i}.wo"], att, lw["wo"], s.d, proj, hq * hd)
-            ctx.add_rmsnorm(x, proj, lw["ffn_norm"], s.rms_eps, x, h)
-            if s.ffn > 0:
-                ctx.linear_multi(h, [(kd[f"l{i}.gate"], lw["gate"], s.ffn, gate), (kd[f"l{i}.up"], lw["up"], s.ffn, up)])
-                ctx.swiglu(gate, up, out=gate)
-            self._row_parallel(kd[f"l{i}.down"], gate, lw["down"], s.d, proj, s.ffn)
+            if fuse_ffn:
+                # the residual add + RMSNorm ride in the staging of gate / up, SwiGLU in the staging of down; the sum
+                # goes to the other residual buffer (the prologue's output may not be its input)
+                x_next = self._buf("x2" if x is self._buf("x", (T, s.d)) else "x", (T, s.d))
+                ctx.linear_multi(x, [(kd[f"l{i}.gate"], lw["gate"], s.ffn, gate), (kd[f"l{i}.up"], lw["up"], s.ffn, up)],
+                                 ("add_rmsnorm", proj, lw["ffn_norm"], s.rms_eps, 0.0, x_next))
+                x = x_next
+                ctx.linear_multi(gate, [(kd[f"l{i}.down"], lw["down"], s.d, proj)], ("swiglu", up))
+            else:
+                ctx.add_rmsnorm(x, proj, lw["ffn_norm"], s.rms_eps, x, h)
+                if s.ffn > 0:
+                    ctx.linear_multi(h, [(kd[f"l{i}.gate"], lw["gate"], s.ffn, gate), (kd[f"l{i}.up"], lw["up"], s.ffn, up)])
+                    ctx.swiglu(gate, up, out=gate)
+                self._row_parallel(kd[f"l{i}.down"], gate, lw["down"], s.d, proj, s.ffn)
             nxt = self.layers[i + 1]["attn_norm"] if i + 1 < len(self.layers) else self.out_norm
             ctx.add_rmsnorm(x, proj, nxt, s.rms_eps, x, h)
         logits = logits_out if logits_out is not None else self._buf("logits", (T, self.local_vocab))
@@ -322,6 +336,7 @@ class Decoder:
         gate, up = self._buf("gate", (T, max(s.ffn, 1))), self._buf("up", (T, max(s.ffn, 1)))
         scale = float(hd) ** -0.5
         pending = None  # the projection not yet added to the residual stream
+        rope = ctx.rope_table(positions, hd, s.rope_theta, out=self._buf("rope", (T, hd // 2, 2)))
         for i, lw in enumerate(self.layers):
             ctx.linear_multi(xs[cur], [(kd[f"l{i}.wq"], lw["wq"], hq * hd, q), (kd[f"l{i}.wk"], lw["wk"], hkv * hd, k),
                                        (kd[f"l{i}.wv"], lw["wv"], hkv * hd, v)],
@@ -329,7 +344,7 @@ class Decoder:
             if pending is not None:
                 cur = 1 - cur
             ctx.paged_attention_decode(meta, q, k, v, self.kv_k, self.kv_v, self.block_table, i, hq, hkv, hd,
-                                       self.block_size, scale, positions, s.rope_theta, out=att)
+                                       self.block_size, scale, positions, s.rope_theta, rope_table=rope, out=att)
             ctx.linear(kd[f"l{i}.wo"], att, lw["wo"], s.d, out=proj)
             pending = proj
             if s.ffn > 0:

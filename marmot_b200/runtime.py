@@ -27,7 +27,7 @@ EXPORTS = (
     "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_moe_last_buffers", "mcu_peer_comm_create", "mcu_peer_comm_export",
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
     "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
-    "mcu_embedding_gather", "mcu_paged_attention", "mcu_paged_attention_decode", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps", "mcu_vec_dot_host",
+    "mcu_embedding_gather", "mcu_paged_attention", "mcu_paged_attention_decode", "mcu_rope_table", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps", "mcu_vec_dot_host",
     "mcu_kv_pool_options_init", "mcu_kv_pool_create", "mcu_kv_pool_destroy", "mcu_kv_pool_acquire_seq",
     "mcu_kv_pool_release_seq", "mcu_kv_pool_prepare_append", "mcu_kv_pool_commit_append", "mcu_kv_pool_abort_append",
     "mcu_kv_pool_prepare_prefix_attach", "mcu_kv_pool_commit_prefix_attach", "mcu_kv_pool_abort_prefix_attach",
@@ -131,7 +131,8 @@ def load_library() -> C.CDLL:
     L.mcu_embedding_gather.argtypes = [vp, i32, vp, sz, vp, sz, vp]
     L.mcu_paged_attention.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, i32, vp, sz, sz, sz, sz, sz, sz, sz, f32, vp]
     L.mcu_paged_attention_decode.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, i32, vp, sz, sz, sz, sz, sz, sz, sz, f32, vp, f32,
-                                             f32, i32, vp]
+                                             f32, i32, vp, vp]
+    L.mcu_rope_table.argtypes = [vp, vp, sz, sz, f32, f32, vp]
     _lib = L
     return L
 
@@ -376,11 +377,20 @@ class Context:
             scale, _ptr(out)))
         return out
 
+    def rope_table(self, positions, head_dim: int, theta: float, freq_scale: float = 1.0, out=None):
+        """[T, head_dim/2, 2] float32 {cos, sin} of position * frequency: the rotation every layer of a step applies."""
+        T = positions.shape[0]
+        if out is None:
+            out = self.torch.empty((T, head_dim // 2, 2), dtype=self.torch.float32, device=positions.device)
+        self._check(self.lib.mcu_rope_table(self.handle, _ptr(positions), T, head_dim, theta, freq_scale, _ptr(out)))
+        return out
+
     def paged_attention_decode(self, token_meta, q, k_new, v_new, kv_k, kv_v, block_table, layer: int, n_q_heads: int,
                                n_kv_heads: int, head_dim: int, block_size: int, scale: float, positions, rope_theta: float,
-                               rope_freq_scale: float = 1.0, neox: bool = False, out=None):
+                               rope_freq_scale: float = 1.0, neox: bool = False, rope_table=None, out=None):
         """A decode step's RoPE + append + attention + chunk merge (one launch on float16 pools).  q / k_new are the
-        projections before RoPE and may be rotated in place; at most one token per sequence in the call."""
+        projections before RoPE and may be rotated in place; at most one token per sequence in the call.  rope_table:
+        what rope_table() made for these positions (shared by the layers of a step); None computes one per call."""
         T = q.shape[0]
         if out is None:
             out = self.torch.empty_like(q)
@@ -388,7 +398,8 @@ class Context:
         self._check(self.lib.mcu_paged_attention_decode(
             self.handle, _ptr(token_meta), T, _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(kv_k), _ptr(kv_v), kv_dtype,
             _ptr(block_table), block_table.shape[1], kv_k.shape[1], layer, n_q_heads, n_kv_heads, head_dim, block_size,
-            scale, _ptr(positions), rope_theta, rope_freq_scale, 1 if neox else 0, _ptr(out)))
+            scale, _ptr(positions), rope_theta, rope_freq_scale, 1 if neox else 0,
+            _ptr(rope_table) if rope_table is not None else None, _ptr(out)))
         return out
 
     def moe_last_buffers(self, T: int, k: int, H: int, FF: int) -> dict:

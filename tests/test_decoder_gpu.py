@@ -93,6 +93,11 @@ def test_swiglu_add_argmax_embedding(ctx, oracle):
     x[2, 7] = x[2, 31999] = 99.0
     x[4, :] = -np.inf
     assert np.array_equal(ctx.argmax(dev(x)).cpu().numpy(), oracle.argmax(x))
+    # one long row: many slices, the maximum twice (in different slices), called twice (the tickets return to zero)
+    y = rng.normal(0, 1, (1, 128256)).astype(np.float32)
+    y[0, 70001] = y[0, 127000] = 50.0
+    for _ in range(2):
+        assert int(ctx.argmax(dev(y)).item()) == 70001
     for kind in (KIND_Q4_K, KIND_Q6_K, KIND_Q8_0):
         table = random_blocks(kind, 40, 512, rng)
         ids = np.array([3, 39, 0, 3, 17], dtype=np.int32)
@@ -194,9 +199,10 @@ def test_decode_attention_in_one_launch_equals_the_three_steps(ctx, n_seq, hq, h
     for _ in range(2):
         k1, v1 = pool_k.clone(), pool_v.clone()
         l0 = ctx.launch_count()
+        rope = ctx.rope_table(pos, hd, theta) if _ == 0 else None  # with the caller's table, then with its own
         got = ctx.paged_attention_decode(dev(meta), q.clone(), k_new.clone(), v_new, k1, v1, dev(table), 1, hq, hkv, hd, bs,
-                                         hd ** -0.5, pos, theta, neox=neox)
-        assert ctx.launch_count() - l0 == 1
+                                         hd ** -0.5, pos, theta, neox=neox, rope_table=rope)
+        assert ctx.launch_count() - l0 == (3 if n_seq == 64 else 2)  # the table, the attention, at many CTAs a merge kernel
         k2, v2 = pool_k.clone(), pool_v.clone()
         q2, kn2 = q.clone(), k_new.clone()
         ctx.rope_qk(q2, kn2, pos, hq, hkv, hd, theta, neox=neox)

@@ -684,3 +684,35 @@ def test_linear_multi_refusals(ctx):
         ctx.linear_multi(x, [(KIND_Q4_K, w, 8, out)] * 5)
     with pytest.raises(MarmotCudaError):
         ctx.linear_multi(x, [(1, w, 8, out)])  # Q4_0: no CUDA kernel
+
+
+@pytest.mark.parametrize("names,T,K,Fs", [(("q4_k", "q4_k"), 64, 4096, (1408, 1408)), (("q4_k", "q6_k", "q4_k"), 33, 2048, (256, 128, 512)),
+                                          (("q8_0",), 40, 1024, (256,))])
+def test_linear_multi_tensor_core_form_with_prologues(ctx, oracle, names, T, K, Fs):
+    """More than sixteen tokens: the prologue rides in the fp16 staging kernel and matmuls of one block-format class
+    share one staging launch.  add + RMSNorm, then SwiGLU on the first job's shape."""
+    import torch
+
+    rng = np.random.default_rng(T + K)
+    kinds, Ws, x, xd, outs = _multi_case(rng, names, T, K, Fs)
+    aux = rng.normal(0, 1, (T, K)).astype(np.float32)
+    w = rng.normal(1, 0.2, K).astype(np.float32)
+    x_out = torch.zeros((T, K), dtype=torch.float32, device="cuda")
+    wd = [ctx.upload(W) for W in Ws]
+    l0 = ctx.launch_count()
+    ctx.linear_multi(xd, [(k, wdev, F, o[:, :F]) for k, wdev, F, o in zip(kinds, wd, Fs, outs)],
+                     ("add_rmsnorm", torch.from_numpy(aux).cuda(), torch.from_numpy(w).cuda(), 1e-5, 0.0, x_out))
+    n_launch = ctx.launch_count() - l0
+    xs = (x + aux).astype(np.float32)
+    assert np.array_equal(x_out.cpu().numpy(), xs)
+    h = oracle.rmsnorm(xs, w, 1e-5)
+    for k, W, F, o in zip(kinds, Ws, Fs, outs):
+        got = o.cpu().numpy()
+        assert max_rel_err(got[:, :F], oracle.linear(k, h, W, F)) <= TOL_MMA
+        assert np.all(got[:, F:] == 7.0)
+    if len(set(kinds)) == 1 and len(kinds) == 2:
+        assert n_launch <= 3  # one staging launch, one dual matmul (plus a split-K reduction at most)
+    up = rng.normal(0, 1, (T, K)).astype(np.float32)
+    ctx.linear_multi(xd, [(kinds[0], wd[0], Fs[0], outs[0][:, :Fs[0]])], ("swiglu", torch.from_numpy(up).cuda()))
+    want = oracle.linear(kinds[0], oracle.swiglu(x, up), Ws[0], Fs[0])
+    assert max_rel_err(outs[0].cpu().numpy()[:, :Fs[0]], want) <= TOL_MMA
