@@ -447,7 +447,8 @@ def time_decode(ctx, dev, rank: int = 0, world: int = 1, dist=None, c4_only: boo
 def time_moe_c5(ctx, dev, rank: int, world: int, dist):
     """BASELINE config 5: Mixtral-8x7B-shape expert FFN (8 experts, top-2, d=4096, FFN 14336, Q4_K), 2048 tokens,
     softmax top-2 routing of N(0,1) logits; expert parallel over the ranks (contiguous expert ranges, router
-    replicated, outputs summed by the peer all-reduce).  At this size the operator takes its grouped path, whose group
+    replicated; the routed rows return to the owners of their tokens over peer memory, are combined there in route
+    order and the token slices gathered, mcu_moe_experts_ep).  At this size the operator takes its grouped path, whose group
     sizes stay on the device; the calls are timed by the host clock around ten of them with a synchronize at the end."""
     import torch
 
@@ -470,16 +471,16 @@ def time_moe_c5(ctx, dev, rank: int, world: int, dist):
     down = normal_blocks(torch, KIND_Q4_K, n_local * H, FF, dev, gen).reshape(-1)
     kinds = (KIND_Q4_K,) * 3
     group = tp.Group(rank, world, dist if world > 1 else None)
-    comm = tp.make_peer_comm(ctx, group, T * H * 4) if world > 1 else None
+    # staging slots for the routed rows and the combined token slices: (T * k + T) * H floats
+    comm = tp.make_peer_comm(ctx, group, (T * k + T) * H * 4 + 256) if world > 1 else None
     out = torch.empty((T, H), dtype=torch.float32, device=dev)
+    bounds = [tp.shard_range(E, world, r)[0] for r in range(world)] + [E]
 
     def call():
         if world == 1:
             ctx.moe_experts_local(kinds, hidden, gate, up, down, ids, vals, FF, E, 0, E, out=out)
-        else:
-            ctx.moe_experts_local(kinds, hidden, gate, up, down, ids, vals, FF, E, e_lo, n_local,
-                                  out=comm.staging((T, H)))
-            comm.allreduce(T * H, out)
+        else:  # routed rows back to the token owners over peer memory, combine, gather the token slices
+            comm.moe_experts_ep(kinds, hidden, gate, up, down, ids, vals, FF, E, bounds, out=out)
 
     for _ in range(3):
         call()

@@ -460,6 +460,31 @@ void *mcu_peer_comm_staging(mcu_peer_comm_t *comm);
 int mcu_peer_allreduce(mcu_peer_comm_t *comm, size_t n_floats, float *out_dev);
 void mcu_peer_comm_destroy(mcu_peer_comm_t *comm);
 
+/* Expert-parallel form over a connected peer communicator: rank q holds the matrices of the experts
+ * [expert_bounds[q], expert_bounds[q + 1]) (host array of world + 1 entries, 0 first, E last); hidden, topk_ids and
+ * topk_weights are the same on every rank (replicated router).  Each rank runs its experts' grouped matmuls on the
+ * routes that name them; the routed rows then go back to the owners of their tokens (rank q owns tokens
+ * [q * ceil(T / world), ...)), which combine them in sorted-route order exactly as mcu_moe_experts does, and the
+ * token slices are gathered: out [T][H] on every rank, bit for bit mcu_moe_experts' result.  All peer traffic is
+ * plain loads from the peers' staging slots, which must hold (T * k + T) * H floats; waits are bounded.
+ * MCU_ERROR_NOT_IMPLEMENTED when the shape does not take the grouped path (fewer than 256 routes, mixed gate / up
+ * kinds, ...): use mcu_moe_experts_local and an all-reduce then.  Every rank must make the same call. */
+size_t mcu_peer_comm_capacity(mcu_peer_comm_t *comm);
+int mcu_peer_comm_rank(mcu_peer_comm_t *comm);
+int mcu_peer_comm_world(mcu_peer_comm_t *comm);
+int mcu_moe_experts_ep(
+    mcu_context_t *ctx, mcu_peer_comm_t *comm, int gate_kind, int up_kind, int down_kind, const float *hidden_dev, size_t T,
+    size_t H, size_t FF, size_t E, const int32_t *expert_bounds, const void *gate_dev, const void *up_dev,
+    const void *down_dev, const int32_t *topk_ids_dev, const float *topk_weights_dev, size_t k, int ffn_type,
+    float weights_scale, int router_weight_policy, float *out_dev
+);
+/* The exchange alone: the routed rows [T * k][H] (sorted-route order) are in the communicator's staging slot. */
+int mcu_peer_moe_combine(
+    mcu_peer_comm_t *comm, const int32_t *route_pos_dev, const float *sorted_w_dev, const int32_t *offsets_dev,
+    const int32_t *bad_id_count_dev, const int32_t *expert_bounds, size_t T, size_t k, size_t H, float *out_dev
+);
+
+
 /* Row-parallel quantized linear: this rank's K-slice of the weights times its K-slice of the activations, written
  * straight into the staging buffer, then the all-reduce; out [T][F] contiguous.
  * Two forms, chosen per communicator with mcu_peer_comm_set_fused (every rank must choose the same):

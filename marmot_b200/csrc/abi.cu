@@ -884,7 +884,9 @@ static int moe_experts_impl(mcu_context_t *ctx, int gate_kind, int up_kind, int 
                             size_t T, size_t H, size_t FF, size_t E, size_t e_begin, size_t e_count,
                             const void *gate_dev, const void *up_dev, const void *down_dev,
                             const int32_t *topk_ids_dev, const float *topk_weights_dev, size_t k, int ffn_type,
-                            float weights_scale, int router_weight_policy, float *out_dev) {
+                            float weights_scale, int router_weight_policy, float *out_dev, float *routed_rows_ext = nullptr) {
+    // routed_rows_ext: the rows of the down projection go there ([T * k][H], sorted-route order) and are NOT combined
+    // into out_dev (expert parallelism: the token owners do that); only the grouped path offers it.
     if (int rc = check_ctx(ctx)) return rc;
     if (e_begin + e_count > E) return fail(MCU_ERROR_INVALID_ARGUMENT, "local expert range exceeds the expert count");
     if (hidden_dev == nullptr || gate_dev == nullptr || up_dev == nullptr || down_dev == nullptr ||
@@ -920,7 +922,8 @@ static int moe_experts_impl(mcu_context_t *ctx, int gate_kind, int up_kind, int 
     MCU_CUDA(launch_moe_route(topk_ids_dev, topk_weights_dev, (int)T, (int)k, (int)E, weights_scale, renorm, rb, s));
     count_launches(3);
     float *route_hidden = (float *)ctx->moe_hidden.ptr, *gate_out = (float *)ctx->moe_gate.ptr;
-    float *up_out = (float *)ctx->moe_up.ptr, *route_down = (float *)ctx->moe_down.ptr;
+    float *up_out = (float *)ctx->moe_up.ptr;
+    float *route_down = routed_rows_ext != nullptr ? routed_rows_ext : (float *)ctx->moe_down.ptr;
     // Large batches: one grouped launch per projection over all local experts, sized from the device-resident counts.
     // Nothing is read back, so the call neither waits for the device nor breaks a stream capture.
     static const bool no_grouped = getenv("MARMOT_CUDA_MOE_NO_GROUPED") != nullptr;  // diagnostic switch
@@ -958,12 +961,17 @@ static int moe_experts_impl(mcu_context_t *ctx, int gate_kind, int up_kind, int 
                                             rowscale, s));
         MCU_CUDA(launch_gemm_tma_grouped(down_kind, down_dev, (int)e_count, xh, rowscale, (int)kp_f, (int)routes, (int)FF,
                                          (int)H, cnt, off, route_down, (int)H, ctx->dev_err, s));
-        MCU_CUDA(launch_moe_combine_dev(route_down, rb.sorted_w, rb.route_pos, (int)T, (int)k, (int)H, rb.offsets,
-                                        (int)e_begin, (int)(e_begin + e_count), rb.counts + E, ctx->dev_err, out_dev, H, s));
-        count_launches(6);
+        if (routed_rows_ext == nullptr) {
+            MCU_CUDA(launch_moe_combine_dev(route_down, rb.sorted_w, rb.route_pos, (int)T, (int)k, (int)H, rb.offsets,
+                                            (int)e_begin, (int)(e_begin + e_count), rb.counts + E, ctx->dev_err, out_dev, H, s));
+            count_launches(1);
+        }
+        count_launches(5);
         ctx->moe_last_grouped = 1;
         return MCU_SUCCESS;
     }
+    if (routed_rows_ext != nullptr)
+        return fail(MCU_ERROR_NOT_IMPLEMENTED, "this MoE shape does not take the grouped path: no routed rows to exchange");
     if (stream_is_capturing(s))
         return fail(MCU_ERROR_INVALID_OPERATION,
                     "this MoE shape reads the group sizes back to size the per-expert launches: the call cannot be captured");
@@ -1042,6 +1050,32 @@ int mcu_moe_experts_local(mcu_context_t *ctx, int gate_kind, int up_kind, int do
     return moe_experts_impl(ctx, gate_kind, up_kind, down_kind, hidden_dev, T, H, FF, E, expert_begin, expert_count,
                             gate_dev, up_dev, down_dev, topk_ids_dev, topk_weights_dev, k, ffn_type, weights_scale,
                             router_weight_policy, out_dev);
+}
+
+int mcu_moe_experts_ep(mcu_context_t *ctx, mcu_peer_comm_t *comm, int gate_kind, int up_kind, int down_kind,
+                       const float *hidden_dev, size_t T, size_t H, size_t FF, size_t E, const int32_t *expert_bounds,
+                       const void *gate_dev, const void *up_dev, const void *down_dev, const int32_t *topk_ids_dev,
+                       const float *topk_weights_dev, size_t k, int ffn_type, float weights_scale, int router_weight_policy,
+                       float *out_dev) {
+    if (comm == nullptr || expert_bounds == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "null argument");
+    const int rank = mcu_peer_comm_rank(comm), world = mcu_peer_comm_world(comm);
+    if (expert_bounds[0] != 0 || (size_t)expert_bounds[world] != E)
+        return fail(MCU_ERROR_INVALID_ARGUMENT, "expert bounds must cover the experts 0..E");
+    const size_t rows_bytes = (T * k * H * sizeof(float) + 255) & ~(size_t)255;
+    if (rows_bytes + T * H * sizeof(float) > mcu_peer_comm_capacity(comm))
+        return fail(MCU_ERROR_INVALID_ARGUMENT, "the communicator's staging slot must hold (T * k + T) * H floats");
+    float *rows = (float *)mcu_peer_comm_staging(comm);
+    const size_t e_begin = (size_t)expert_bounds[rank], e_count = (size_t)(expert_bounds[rank + 1] - expert_bounds[rank]);
+    if (int rc = moe_experts_impl(ctx, gate_kind, up_kind, down_kind, hidden_dev, T, H, FF, E, e_begin, e_count, gate_dev, up_dev,
+                                  down_dev, topk_ids_dev, topk_weights_dev, k, ffn_type, weights_scale, router_weight_policy,
+                                  out_dev, rows))
+        return rc;
+    const size_t routes = T * k;
+    const int32_t *counts = (const int32_t *)ctx->moe_meta.ptr;  // counts[E+1] | offsets[E+1] | sorted_tok | sorted_w | route_pos
+    const int32_t *offsets = counts + (E + 1);
+    const float *sorted_w = (const float *)(offsets + (E + 1) + routes);
+    const int32_t *route_pos = (const int32_t *)(sorted_w + routes);
+    return mcu_peer_moe_combine(comm, route_pos, sorted_w, offsets, counts + E, expert_bounds, T, k, H, out_dev);
 }
 
 }  // extern "C"

@@ -24,7 +24,7 @@ EXPORTS = (
     "mcu_context_set_regime", "mcu_synchronize", "mcu_last_error_message", "mcu_kernel_launch_count",
     "mcu_malloc", "mcu_free", "mcu_memcpy_to_device", "mcu_memcpy_to_host", "mcu_row_bytes", "mcu_dequantize",
     "mcu_quantize_activations", "mcu_linear", "mcu_linear_dual", "mcu_linear_multi", "mcu_linear_host", "mcu_topk", "mcu_moe_experts",
-    "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_moe_last_buffers", "mcu_peer_comm_create", "mcu_peer_comm_export",
+    "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_moe_experts_ep", "mcu_peer_moe_combine", "mcu_peer_comm_capacity", "mcu_peer_comm_rank", "mcu_peer_comm_world", "mcu_moe_last_buffers", "mcu_peer_comm_create", "mcu_peer_comm_export",
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
     "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
     "mcu_embedding_gather", "mcu_paged_attention", "mcu_paged_attention_decode", "mcu_rope_table", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps", "mcu_vec_dot_host",
@@ -111,6 +111,9 @@ def load_library() -> C.CDLL:
     L.mcu_moe_experts_local.argtypes = [vp, i32, i32, i32, vp, sz, sz, sz, sz, sz, sz, vp, vp, vp, vp, vp, sz, i32, f32,
                                         i32, vp]
     L.mcu_moe_last_buffers.argtypes = [vp, vp]
+    L.mcu_moe_experts_ep.argtypes = [vp, vp, i32, i32, i32, vp, sz, sz, sz, sz, vp, vp, vp, vp, vp, vp, sz, i32, f32, i32, vp]
+    L.mcu_peer_comm_capacity.argtypes = [vp]
+    L.mcu_peer_comm_capacity.restype = sz
     L.mcu_peer_comm_create.argtypes = [vp, i32, i32, sz, C.POINTER(vp)]
     L.mcu_peer_comm_export.argtypes = [vp, vp]
     L.mcu_peer_comm_connect.argtypes = [vp, vp]
@@ -468,6 +471,22 @@ class PeerComm:
             out = self.ctx.torch.empty((T, F), dtype=self.ctx.torch.float32, device=x.device)
         self.ctx._check(self.ctx.lib.mcu_linear_allreduce(self.ctx.handle, self.handle, kind, _ptr(x), x.stride(0),
                                                           _ptr(w), T, K, F, _ptr(out)))
+        return out
+
+    def moe_experts_ep(self, kinds, hidden, gate, up, down, topk_ids, topk_weights, FF: int, E: int, expert_bounds,
+                       ffn_type: int = FFN_SWIGLU, weights_scale: float = 1.0, policy: int = ROUTER_RENORMALIZE_SELECTED,
+                       out=None):
+        """Expert-parallel MoE FFN: this rank holds the experts [expert_bounds[rank], expert_bounds[rank + 1]); the
+        routed rows return to the owners of their tokens over peer memory and the token slices are gathered (see
+        mcu_moe_experts_ep).  Raises MarmotCudaError with code NOT_IMPLEMENTED for shapes off the grouped path."""
+        T, H = hidden.shape
+        k = topk_ids.shape[1]
+        if out is None:
+            out = self.ctx.torch.empty((T, H), dtype=self.ctx.torch.float32, device=hidden.device)
+        bounds = (C.c_int32 * (self.world + 1))(*[int(b) for b in expert_bounds])
+        self.ctx._check(self.ctx.lib.mcu_moe_experts_ep(
+            self.ctx.handle, self.handle, kinds[0], kinds[1], kinds[2], _ptr(hidden), T, H, FF, E, bounds, _ptr(gate),
+            _ptr(up), _ptr(down), _ptr(topk_ids), _ptr(topk_weights), k, ffn_type, weights_scale, policy, _ptr(out)))
         return out
 
     def close(self):

@@ -178,9 +178,23 @@ class ExpertParallelMoE:
         self.gate, self.up, self.down = backend.upload(g), backend.upload(u), backend.upload(d)
         self.comm = comm
 
-    def __call__(self, hidden, topk_ids, topk_weights, **kw):
+    def __call__(self, hidden, topk_ids, topk_weights, exchange: bool = True, **kw):
+        """exchange: with a peer communicator large enough for (T * k + T) * H floats, the routed rows go back to the
+        token owners and the token slices are gathered (every rank moves about 1 / world of what the all-reduce of
+        whole outputs moves); otherwise, or for shapes off the grouped path, each rank's partial output is summed by an
+        all-reduce."""
         T = hidden.shape[0]
         peer = self.comm is not None and self.group.world > 1
+        if peer and exchange and (T * topk_ids.shape[1] + T) * self.H * 4 + 256 <= self.comm.max_bytes:
+            from .runtime import MarmotCudaError
+
+            bounds = [shard_range(self.E, self.group.world, r)[0] for r in range(self.group.world)] + [self.E]
+            try:
+                return self.comm.moe_experts_ep(self.kinds, hidden, self.gate, self.up, self.down, topk_ids, topk_weights,
+                                                self.FF, self.E, bounds, **kw)
+            except MarmotCudaError as exc:
+                if exc.code != -8:  # NOT_IMPLEMENTED: every rank gets it for the same shape, and all fall through
+                    raise
         out = self.comm.staging((T, self.H)) if peer else None
         y = self.backend.moe_experts_local(self.kinds, hidden, self.gate, self.up, self.down, topk_ids, topk_weights,
                                            self.FF, self.E, self.e_lo, self.e_hi - self.e_lo, out=out, **kw)

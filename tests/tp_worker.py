@@ -51,6 +51,20 @@ def main() -> int:
         ctx.synchronize()
         check(f"allreduce_exact_{rep}", np.array_equal(out.cpu().numpy(), want))
 
+    # a message above the two-phase threshold (reduce-scatter + all-gather in one kernel), ragged length
+    n = 800003
+    parts = [np.random.default_rng(200 + r).normal(0, 1, n).astype(np.float32) for r in range(world)]
+    want = parts[0].copy()
+    for r in range(1, world):
+        want = want + parts[r]
+    for rep in range(3):
+        comm.staging((n,)).copy_(torch.from_numpy(parts[rank]).to(dev))
+        out = torch.full((n + 5,), 3.0, dtype=torch.float32, device=dev)
+        comm.allreduce(n, out)
+        ctx.synchronize()
+        got = out.cpu().numpy()
+        check(f"allreduce_two_phase_exact_{rep}", np.array_equal(got[:n], want) and np.all(got[n:] == 3.0))
+
     rng = np.random.default_rng(42)
     for kind in (KIND_Q4_K, KIND_Q6_K, KIND_Q8_0):
         for T in (1, 5, 48):
@@ -101,10 +115,25 @@ def main() -> int:
     want = ctx.moe_experts(kinds, hidden, ctx.upload(gate), ctx.upload(up), ctx.upload(down4), ids, wts, FF, E).cpu().numpy()
     for name, c in (("nccl", None), ("peer", comm)):
         moe = tp.ExpertParallelMoE(ctx, group, kinds, gate, up, down4, H, FF, E, comm=c)
-        y = moe(hidden, ids, wts)
+        y = moe(hidden, ids, wts, exchange=False)
         ctx.synchronize()
         e = float(max_rel_err(y.cpu().numpy(), want))
         check(f"moe_grouped_{name}", e <= 1e-5, e)  # the same products as on one GPU, summed per rank first
+    # the routed rows return to the token owners, who combine them in the one-GPU order: the same bits, on every rank,
+    # also with a ragged token count and repeated (both parities of the staging slots)
+    moe = tp.ExpertParallelMoE(ctx, group, kinds, gate, up, down4, H, FF, E, comm=comm)
+    for rep in range(3):
+        l0 = ctx.launch_count()
+        y = moe(hidden, ids, wts)
+        ctx.synchronize()
+        check(f"moe_exchange_exact_{rep}", np.array_equal(y.cpu().numpy(), want), float(max_rel_err(y.cpu().numpy(), want)))
+        check(f"moe_exchange_launches_{rep}", ctx.launch_count() - l0 == 9, int(ctx.launch_count() - l0))
+    T2 = 157
+    y = moe(hidden[:T2].contiguous(), ids[:T2].contiguous(), wts[:T2].contiguous())
+    ctx.synchronize()
+    want2 = ctx.moe_experts(kinds, hidden[:T2].contiguous(), ctx.upload(gate), ctx.upload(up), ctx.upload(down4),
+                            ids[:T2].contiguous(), wts[:T2].contiguous(), FF, E).cpu().numpy()
+    check("moe_exchange_ragged", np.array_equal(y.cpu().numpy(), want2))
 
     # a whole decoder step: every rank cuts its share out of the same full-model weights; logits slices and the greedy
     # pick must match the single-GPU decoder on the full weights (only the f32 order of the row-parallel sums differs)
