@@ -152,6 +152,17 @@ int mcu_linear(
     const float *bias_dev, float *out_dev, size_t ldo
 );
 
+/* ---- FLOAT16 activations: the branch of cpu_matmul_quantized_impl taken for f16 inputs
+ *      (matmul_quant_dispatch.c:449-470): no activation packing, out[t][f] = sum_k w(f, k) * (float)x[t][k] in f32 with
+ *      w formed as cpu_vec_dot_{q4_k,q6_k,q8_0}_f16 form it (vec_dot_impl.h:419-447,973-1023,1082-1127; the Q6_K
+ *      function reads the block linearly, not as the dequantizer does, and its golden output pins that).
+ *      x_f16_dev: IEEE half bits; out_dtype MCU_OUT_F32 (float *out_dev) or MCU_OUT_F16 (half bits, no bias). ---- */
+enum { MCU_OUT_F32 = 0, MCU_OUT_F16 = 1 };
+int mcu_linear_f16(
+    mcu_context_t *ctx, int kind, const uint16_t *x_f16_dev, size_t ldx, const void *w_dev, size_t T, size_t K, size_t F,
+    const float *bias_dev, void *out_dev, size_t ldo, int out_dtype
+);
+
 /* ---- two weights, one activation read: cpu_matmul_quantized_dual_output
  *      (matmul_quant_dispatch.c:593-856); gate/up of the FFN and of MoE experts. ---- */
 int mcu_linear_dual(

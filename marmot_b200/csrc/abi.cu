@@ -688,6 +688,24 @@ int mcu_linear(mcu_context_t *ctx, int kind, const float *x_dev, size_t ldx, con
     return linear_locked(ctx, kind, x_dev, ldx, w_dev, nullptr, T, K, F, bias_dev, out_dev, nullptr, ldo);
 }
 
+int mcu_linear_f16(mcu_context_t *ctx, int kind, const uint16_t *x_f16_dev, size_t ldx, const void *w_dev, size_t T, size_t K,
+                   size_t F, const float *bias_dev, void *out_dev, size_t ldo, int out_dtype) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (!kind_supported(kind)) return fail(MCU_ERROR_NOT_IMPLEMENTED, "quant kind %d has no CUDA kernel", kind);
+    if (T == 0 || F == 0) return MCU_SUCCESS;
+    if (int rc = validate_linear(kind, x_f16_dev, w_dev, out_dev, T, K, F, ldx, ldo)) return rc;
+    if (out_dtype != MCU_OUT_F32 && out_dtype != MCU_OUT_F16) return fail(MCU_ERROR_UNSUPPORTED_DTYPE, "output must be f32 or f16");
+    if (out_dtype == MCU_OUT_F16 && bias_dev != nullptr)
+        return fail(MCU_ERROR_NOT_IMPLEMENTED, "bias with an f16 output is not offered");
+    if ((uintptr_t)x_f16_dev & 1) return fail(MCU_ERROR_INVALID_ARGUMENT, "f16 activations must be 2-byte aligned");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    MCU_CUDA(launch_linear_f16(kind, w_dev, (const __half *)x_f16_dev, ldx, (int)T, (int)K, (int)F, bias_dev,
+                               out_dtype == MCU_OUT_F32 ? (float *)out_dev : nullptr,
+                               out_dtype == MCU_OUT_F16 ? (__half *)out_dev : nullptr, ldo, ctx->stream));
+    count_launches(1);
+    return MCU_SUCCESS;
+}
+
 int mcu_linear_dual(mcu_context_t *ctx, int kind, const float *x_dev, size_t ldx, const void *w_a_dev,
                     const void *w_b_dev, size_t T, size_t K, size_t F, float *out_a_dev, float *out_b_dev, size_t ldo) {
     if (int rc = check_ctx(ctx)) return rc;

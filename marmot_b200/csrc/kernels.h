@@ -101,6 +101,11 @@ bool gemv_stream_supported(int kind, const void *W, const void *W2, int T, int K
 cudaError_t launch_gemv_stream(int kind, const void *W, const void *W2, const float *x, int ldx, int T, int K, int F,
                                const float *bias, float *out, float *out2, int ldo, int *err_flag, cudaStream_t s);
 
+// f16 activations, no packing: every weight value formed in f32, products and sums in f32; f32 or f16 out
+// (exactly one of out32 / out16 set).  See linear_f16.cu for the Q6_K reading.
+cudaError_t launch_linear_f16(int kind, const void *W, const __half *x, size_t ldx, int T, int K, int F, const float *bias,
+                              float *out32, __half *out16, size_t ldo, cudaStream_t s);
+
 // Few-token regime (2 <= T <= 64) on integer tensor-core instructions: activations packed to Q8_K by a first launch,
 // exact int32 sub-block dots (mma.sync s8), f32 scaling per block; Q4_K and Q6_K, rows a multiple of 16 bytes.
 // The caller provides the workspace (sizes from gemm_i8_workspace_bytes); `tickets` must be zero before the first

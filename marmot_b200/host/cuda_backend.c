@@ -407,10 +407,16 @@ static marmot_error_t cuda_matmul_quantized(
         marmot_set_error(MARMOT_ERROR_NOT_IMPLEMENTED, "CUDA quantized matmul: unsupported quant kind");
         return MARMOT_ERROR_NOT_IMPLEMENTED;
     }
-    if (!profile.input_is_fp32 || !profile.output_is_fp32) {
-        marmot_set_error(MARMOT_ERROR_UNSUPPORTED_DTYPE, "CUDA quantized matmul takes FLOAT32 activations and output");
+    // FLOAT32 in and out: activations packed on the device (mcu_linear).  FLOAT16 in: the reference's unpacked f32
+    // arithmetic (mcu_linear_f16), FLOAT32 or FLOAT16 out, one weight.
+    const bool half_in = profile.input_is_fp16;
+    if (!(profile.input_is_fp32 && profile.output_is_fp32) &&
+        !(half_in && (profile.output_is_fp32 || profile.output_is_fp16) && weight_b == nullptr)) {
+        marmot_set_error(MARMOT_ERROR_UNSUPPORTED_DTYPE,
+                         "CUDA quantized matmul takes FLOAT32 in and out, or FLOAT16 in with FLOAT32 / FLOAT16 out");
         return MARMOT_ERROR_UNSUPPORTED_DTYPE;
     }
+    const size_t in_elem = half_in ? 2 : 4, out_elem = profile.output_is_fp16 ? 2 : 4;
     if (input->shape.strides[1] != 1 || out_a->shape.strides[1] != 1) {
         marmot_set_error(MARMOT_ERROR_INVALID_ARGUMENT, "CUDA quantized matmul needs unit inner strides");
         return MARMOT_ERROR_INVALID_ARGUMENT;
@@ -429,7 +435,7 @@ static marmot_error_t cuda_matmul_quantized(
     pthread_mutex_lock(&c->mu);
     const void *x = nullptr, *wa = nullptr, *wb = nullptr, *bias = nullptr;
     void *ya = nullptr, *yb = nullptr;
-    st = resident_ro(c, input, ((T - 1) * ldx + K) * sizeof(float), &x);
+    st = resident_ro(c, input, ((T - 1) * ldx + K) * in_elem, &x);
     if (st == MARMOT_SUCCESS) st = resident_ro(c, weight_a, w_bytes, &wa);
     if (st == MARMOT_SUCCESS && weight_b != nullptr) st = resident_ro(c, weight_b, w_bytes, &wb);
     if (st == MARMOT_SUCCESS && epilogue != nullptr && epilogue->bias != nullptr) {
@@ -440,12 +446,13 @@ static marmot_error_t cuda_matmul_quantized(
             st = resident_ro(c, epilogue->bias, F * sizeof(float), &bias);
         }
     }
-    if (st == MARMOT_SUCCESS) st = resident_rw(c, out_a, ((T - 1) * ldo + F) * sizeof(float), &ya);
+    if (st == MARMOT_SUCCESS) st = resident_rw(c, out_a, ((T - 1) * ldo + F) * out_elem, &ya);
     if (st == MARMOT_SUCCESS && out_b != nullptr) st = resident_rw(c, out_b, ((T - 1) * ldo + F) * sizeof(float), &yb);
     if (st == MARMOT_SUCCESS) {
-        const int rc = weight_b == nullptr
-            ? mcu_linear(c->mcu, kind, x, ldx, wa, T, K, F, bias, ya, ldo)
-            : mcu_linear_dual(c->mcu, kind, x, ldx, wa, wb, T, K, F, ya, yb, ldo);
+        const int rc = half_in ? mcu_linear_f16(c->mcu, kind, x, ldx, wa, T, K, F, bias, ya, ldo,
+                                                profile.output_is_fp16 ? MCU_OUT_F16 : MCU_OUT_F32)
+            : weight_b == nullptr ? mcu_linear(c->mcu, kind, x, ldx, wa, T, K, F, bias, ya, ldo)
+                                  : mcu_linear_dual(c->mcu, kind, x, ldx, wa, wb, T, K, F, ya, yb, ldo);
         if (rc != 0) st = cuda_fail(rc);
     }
     pthread_mutex_unlock(&c->mu);
@@ -1097,7 +1104,10 @@ marmot_kernel_selection_t marmot_cuda_query_kernel(const marmot_op_signature_t *
     case MARMOT_OP_MATMUL:
     case MARMOT_OP_LINEAR: {
         if (slot < 0) return cuda_unsupported("CUDA matmul covers Q4_K, Q6_K and Q8_0 weights");
-        if (!f32_io) return cuda_unsupported("CUDA quantized matmul takes FLOAT32 activations and writes FLOAT32");
+        const bool f16_in = sig->input_dtype == MARMOT_DTYPE_FLOAT16 &&
+            (sig->output_dtype == MARMOT_DTYPE_FLOAT32 || sig->output_dtype == MARMOT_DTYPE_FLOAT16);
+        if (!f32_io && !f16_in)
+            return cuda_unsupported("CUDA quantized matmul takes FLOAT32 in and out, or FLOAT16 in with FLOAT32 / FLOAT16 out");
         if (sig->matmul_layout != MARMOT_MATMUL_LAYOUT_NT) return cuda_unsupported("CUDA quantized matmul is NT only");
         if (sig->weight_layout != MARMOT_WEIGHT_LAYOUT_SEPARATE) return cuda_unsupported("packed weight layouts are CPU caches");
         if ((sig->epilogue_flags & ~(uint32_t)MARMOT_EPILOGUE_BIAS) != 0 || sig->activation != MARMOT_DEVICE_UNARY_IDENTITY)

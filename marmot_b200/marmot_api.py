@@ -188,6 +188,20 @@ class MarmotLibrary:
             for t in (to, tw, tx):
                 self.lib.marmot_tensor_destroy(t)
 
+    def linear_f16(self, kind: int, x16: np.ndarray, W: np.ndarray, F: int, half_out: bool = False) -> np.ndarray:
+        """marmot_linear with FLOAT16 activations [T, K] (float16 array); FLOAT32 result, or FLOAT16 with half_out."""
+        x16 = np.ascontiguousarray(x16, dtype=np.float16)
+        T, K = x16.shape
+        tx = self._tensor((T, K), DT_F16, x16)
+        tw = self._qtensor((F, K), kind, W)
+        to = self._tensor((T, F), DT_F16 if half_out else DT_F32)
+        try:
+            self._check(self.lib.marmot_linear(self.ctx, tx, tw, None, to), "marmot_linear")
+            return self._read(to, (T, F), np.float16 if half_out else np.float32)
+        finally:
+            for t in (to, tw, tx):
+                self.lib.marmot_tensor_destroy(t)
+
     def quantize(self, kind: int, w: np.ndarray) -> np.ndarray:
         """Row-wise weight quantisation: w [rows, K] f32 -> packed rows (uint8)."""
         w = np.ascontiguousarray(w, dtype=np.float32)

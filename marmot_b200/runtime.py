@@ -23,7 +23,7 @@ EXPORTS = (
     "mcu_context_create", "mcu_context_destroy", "mcu_context_set_stream", "mcu_context_get_stream",
     "mcu_context_set_regime", "mcu_synchronize", "mcu_last_error_message", "mcu_kernel_launch_count",
     "mcu_malloc", "mcu_free", "mcu_memcpy_to_device", "mcu_memcpy_to_host", "mcu_row_bytes", "mcu_dequantize",
-    "mcu_quantize_activations", "mcu_linear", "mcu_linear_dual", "mcu_linear_multi", "mcu_linear_host", "mcu_topk", "mcu_moe_experts",
+    "mcu_quantize_activations", "mcu_linear", "mcu_linear_dual", "mcu_linear_multi", "mcu_linear_f16", "mcu_linear_host", "mcu_topk", "mcu_moe_experts",
     "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_moe_experts_ep", "mcu_peer_moe_combine", "mcu_peer_comm_capacity", "mcu_peer_comm_rank", "mcu_peer_comm_world", "mcu_moe_last_buffers", "mcu_peer_comm_create", "mcu_peer_comm_export",
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
     "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
@@ -104,6 +104,7 @@ def load_library() -> C.CDLL:
     L.mcu_linear_dual.argtypes = [vp, i32, vp, sz, vp, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_linear_host.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_linear_multi.argtypes = [vp, vp, sz, sz, sz, vp, vp, sz]
+    L.mcu_linear_f16.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz, i32]
     L.mcu_linear_static_scratch.argtypes = [vp, i32, vp, sz, vp, sz, sz, sz, vp, vp, sz]
     L.mcu_topk.argtypes = [vp, vp, sz, sz, sz, sz, vp, vp]
     L.mcu_vec_dot_host.argtypes = [vp, i32, vp, vp, sz, vp]
@@ -232,6 +233,18 @@ class Context:
         self._check(self.lib.mcu_linear_dual(self.handle, kind, _ptr(x), x.stride(0), _ptr(w_a), _ptr(w_b), T, K, F,
                                              _ptr(oa), _ptr(ob), F))
         return oa, ob
+
+    def linear_f16(self, kind: int, x16, w, F: int, bias=None, out_dtype=None):
+        """float16 activations [T, K] (no packing, f32 arithmetic on weight values formed as the reference's f16 row
+        dots form them); float32 out unless out_dtype is torch.float16."""
+        T, K = x16.shape
+        tc = self.torch
+        assert x16.dtype == tc.float16
+        half_out = out_dtype == tc.float16
+        out = tc.empty((T, F), dtype=tc.float16 if half_out else tc.float32, device=x16.device)
+        self._check(self.lib.mcu_linear_f16(self.handle, kind, _ptr(x16), x16.stride(0), _ptr(w), T, K, F,
+                                            _ptr(bias) if bias is not None else None, _ptr(out), F, 1 if half_out else 0))
+        return out
 
     def linear_multi(self, x, jobs, prologue=None):
         """Several weights over one activation read: jobs = [(kind, w, F, out), ...] (1..4, out [T, F] or wider rows),

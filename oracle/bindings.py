@@ -51,6 +51,8 @@ class Oracle:
             f.restype = C.c_float
         L.mo_linear.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
                                 C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+        L.mo_linear_f16.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
+                                    C.c_void_p, C.c_void_p, C.c_size_t]
         L.mo_topk.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p]
         L.mo_moe_experts.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
                                      C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -98,6 +100,17 @@ class Oracle:
         b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
         rc = self.lib.mo_linear(kind, _p(x), K, _p(W), T, K, F, None if b is None else _p(b), _p(out), F,
                                 threads or os.cpu_count() or 1)
+        assert rc == 0
+        return out
+
+    def linear_f16(self, kind: int, x16: np.ndarray, W: np.ndarray, F: int, bias: np.ndarray | None = None) -> np.ndarray:
+        """x16 [T, K] float16 (or its uint16 bits): the reference's f16-activation matmul, f32 out."""
+        x16 = np.ascontiguousarray(x16).view(np.uint16)
+        T, K = x16.shape
+        W = np.ascontiguousarray(W, dtype=np.uint8)
+        out = np.empty((T, F), dtype=np.float32)
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        rc = self.lib.mo_linear_f16(kind, _p(x16), K, _p(W), T, K, F, None if b is None else _p(b), _p(out), F)
         assert rc == 0
         return out
 

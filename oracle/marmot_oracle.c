@@ -341,6 +341,91 @@ int mo_linear(
     return 0;
 }
 
+/*
+ * The f16-activation form (matmul_quant_dispatch.c:449-470 -> cpu_quant_matmul_dispatch_fp16_tile): no activation
+ * packing; every output is ONE running f32 sum over the row, total += w_val * (float)x[k], in k order, with the
+ * weight value formed as in cpu_vec_dot_q4_k_f16 (vec_dot_impl.h:973-1023), cpu_vec_dot_q8_0_f16 (:419-447) and
+ * cpu_vec_dot_q6_k_f16 (:1082-1127).  The Q6_K function does NOT read the block as the dequantizer does: value idx of
+ * a block takes the scale sc[idx / 128], the nibble idx of ql counted linearly (even idx low, odd idx high) and the
+ * two bits (idx % 4) of qh[idx / 4].  The reference's golden output (g_matmul_q6_k_output_from_f16) pins that reading,
+ * so it is restated as it stands.  Bias: out += bias.
+ */
+static float dot_f16_q4_k(const blk_q4_k *w, const uint16_t *x, size_t nb, size_t K) {
+    float total = 0.0f;
+    for (size_t b = 0; b < nb; ++b) {
+        const uint8_t *q = w[b].qs;
+        const float d = h2f(w[b].d), dmin = h2f(w[b].dmin);
+        const uint16_t *a = x + b * QK_K;
+        const size_t len = K - b * QK_K < QK_K ? K - b * QK_K : QK_K;
+        size_t at = 0;
+        for (int g = 0; g < 4 && at < len; ++g) {
+            uint8_t sc, mn;
+            k4_scale_min(2 * g, w[b].scales, &sc, &mn);
+            const float d1 = d * (float)sc, m1 = dmin * (float)mn;
+            k4_scale_min(2 * g + 1, w[b].scales, &sc, &mn);
+            const float d2 = d * (float)sc, m2 = dmin * (float)mn;
+            for (int l = 0; l < 32 && at < len; ++l, ++at) {
+                const float wv = d1 * (float)(q[l] & 0xF) - m1;
+                total += wv * h2f(a[at]);
+            }
+            for (int l = 0; l < 32 && at < len; ++l, ++at) {
+                const float wv = d2 * (float)(q[l] >> 4) - m2;
+                total += wv * h2f(a[at]);
+            }
+            q += 32;
+        }
+    }
+    return total;
+}
+static float dot_f16_q6_k(const blk_q6_k *w, const uint16_t *x, size_t nb, size_t K) {
+    float total = 0.0f;
+    for (size_t b = 0; b < nb; ++b) {
+        const float d = h2f(w[b].d);
+        const uint16_t *a = x + b * QK_K;
+        const size_t len = K - b * QK_K < QK_K ? K - b * QK_K : QK_K;
+        for (size_t idx = 0; idx < len; ++idx) {
+            const float scale = d * (float)w[b].scales[idx / 128];
+            const uint8_t lo = (idx % 2 == 0) ? (uint8_t)(w[b].ql[idx / 2] & 0xF) : (uint8_t)(w[b].ql[idx / 2] >> 4);
+            const uint8_t hi = (uint8_t)((w[b].qh[idx / 4] >> ((idx % 4) * 2)) & 0x3);
+            const int8_t sq = (int8_t)((int8_t)(lo | (hi << 4)) - 32);
+            const float wv = scale * (float)sq;
+            total += wv * h2f(a[idx]);
+        }
+    }
+    return total;
+}
+static float dot_f16_q8_0(const blk_q8_0 *w, const uint16_t *x, size_t nb, size_t K) {
+    float total = 0.0f;
+    for (size_t b = 0; b < nb; ++b) {
+        const float sw = h2f(w[b].d);
+        const uint16_t *a = x + b * Q8_0_VALUES;
+        const size_t len = K - b * Q8_0_VALUES < Q8_0_VALUES ? K - b * Q8_0_VALUES : Q8_0_VALUES;
+        for (size_t i = 0; i < len; ++i) total += ((float)w[b].qs[i]) * sw * h2f(a[i]);
+    }
+    return total;
+}
+int mo_linear_f16(
+    int kind, const uint16_t *x, size_t ldx, const void *W, size_t T, size_t K, size_t F, const float *bias, float *out,
+    size_t ldo
+) {
+    const size_t bv = mo_block_values(kind), bb = mo_block_bytes(kind);
+    if (bv == 0 || x == NULL || W == NULL || out == NULL) return -1;
+    const size_t nb = (K + bv - 1) / bv;
+    const uint8_t *wb = (const uint8_t *)W;
+    for (size_t f = 0; f < F; ++f) {
+        const uint8_t *row = wb + f * nb * bb;
+        for (size_t t = 0; t < T; ++t) {
+            const uint16_t *xr = x + t * ldx;
+            float acc = kind == MO_KIND_Q4_K ? dot_f16_q4_k((const blk_q4_k *)row, xr, nb, K)
+                : kind == MO_KIND_Q6_K     ? dot_f16_q6_k((const blk_q6_k *)row, xr, nb, K)
+                                           : dot_f16_q8_0((const blk_q8_0 *)row, xr, nb, K);
+            if (bias != NULL) acc += bias[f];
+            out[t * ldo + f] = acc;
+        }
+    }
+    return 0;
+}
+
 /* ---- MoE ---- */
 
 /* cpu_topk_impl, ops/moe/moe_ops.c:789-889: insertion top-k, equal values keep the lower column first. */

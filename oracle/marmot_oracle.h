@@ -67,6 +67,11 @@ int mo_linear(
     int kind, const float *x, size_t ldx, const void *W, size_t T, size_t K, size_t F, const float *bias, float *out,
     size_t ldo, int n_threads
 );
+/* f16 activations, no packing: one running f32 sum per output (cpu_vec_dot_*_f16, vec_dot_impl.h) */
+int mo_linear_f16(
+    int kind, const uint16_t *x, size_t ldx, const void *W, size_t T, size_t K, size_t F, const float *bias, float *out,
+    size_t ldo
+);
 
 /* top-k per row, ties -> lower index */
 void mo_topk(const float *x, size_t rows, size_t cols, size_t ldx, size_t k, float *values, int32_t *indices);

@@ -47,7 +47,8 @@ static void put(FILE *f, const char *name, const void *p, size_t n) {
 #define MATMUL(l, U) do { \
     uint64_t dims[3] = {MATMUL_##U##_N, MATMUL_##U##_K, MATMUL_##U##_M}; \
     put(f, "matmul_" #l "_dims", dims, sizeof(dims)); \
-    PUT(g_matmul_##l##_input_f32); PUT(g_matmul_##l##_weight); PUT(g_matmul_##l##_output_from_f32); } while (0)
+    PUT(g_matmul_##l##_input_f32); PUT(g_matmul_##l##_weight); PUT(g_matmul_##l##_output_from_f32); \
+    PUT(g_matmul_##l##_input_f16); PUT(g_matmul_##l##_output_from_f16); } while (0)
 int main(int argc, char **argv) {
     FILE *f = fopen(argv[1], "wb");
     MATMUL(q4_k, Q4_K); MATMUL(q6_k, Q6_K); MATMUL(q8_0, Q8_0);
@@ -63,7 +64,7 @@ int main(int argc, char **argv) {
 }
 """
 
-F32_KEYS = ("input_f32", "output_from_f32", "expected", "dequant", "test_input")
+F32_KEYS = ("input_f32", "output_from_f32", "output_from_f16", "expected", "dequant", "test_input")  # input_f16 stays raw bytes
 
 
 def dump_reference_goldens(ref_root: Path) -> dict[str, np.ndarray]:

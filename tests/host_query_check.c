@@ -81,7 +81,11 @@ int main(int argc, char **argv) {
     // what has no CUDA kernel is refused at query time, with a reason
     {
         marmot_op_signature_t s = linear_sig(MARMOT_QSCHEME_Q4_K, 1, 4096, 4096);
-        s.input_dtype = MARMOT_DTYPE_FLOAT16;
+        s.input_dtype = MARMOT_DTYPE_FLOAT16;  // FLOAT16 activations are served (f32 or f16 out) ...
+        CHECK(marmot_cuda_query_kernel(&s, &caps).supported);
+        s.output_dtype = MARMOT_DTYPE_FLOAT16;
+        CHECK(marmot_cuda_query_kernel(&s, &caps).supported);
+        s.input_dtype = MARMOT_DTYPE_FLOAT32;  // ... FLOAT32 activations with a FLOAT16 output are not
         marmot_kernel_selection_t sel = marmot_cuda_query_kernel(&s, &caps);
         CHECK(!sel.supported && sel.fallback_reason != nullptr && sel.kernel_id == MARMOT_KERNEL_INVALID);
         s = linear_sig(MARMOT_QSCHEME_NONE, 1, 4096, 4096);

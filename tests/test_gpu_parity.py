@@ -716,3 +716,41 @@ def test_linear_multi_tensor_core_form_with_prologues(ctx, oracle, names, T, K, 
     ctx.linear_multi(xd, [(kinds[0], wd[0], Fs[0], outs[0][:, :Fs[0]])], ("swiglu", torch.from_numpy(up).cuda()))
     want = oracle.linear(kinds[0], oracle.swiglu(x, up), Ws[0], Fs[0])
     assert max_rel_err(outs[0].cpu().numpy()[:, :Fs[0]], want) <= TOL_MMA
+
+
+# ---- float16 activations (mcu_linear_f16): the reference's no-packing branch ----
+@pytest.mark.parametrize("name", NAMES)
+def test_linear_f16_llama_golden(ctx, llama_goldens, name):
+    import torch
+
+    kind = KINDS[name]
+    N, K, M = (int(v) for v in llama_goldens[f"matmul_{name}_dims"])
+    x16 = llama_goldens[f"matmul_{name}_input_f16"].view(np.float16).reshape(N, K)
+    want = llama_goldens[f"matmul_{name}_output_from_f16"].reshape(N, M)
+    got = ctx.linear_f16(kind, torch.from_numpy(x16.copy()).cuda(), ctx.upload(llama_goldens[f"matmul_{name}_weight"]), M)
+    assert max_rel_err(got.cpu().numpy(), want) <= 1e-5
+
+
+@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("T,K,F", [(1, 4096, 64), (3, 700, 13), (12, 2048, 40), (64, 1024, 9)])
+def test_linear_f16_vs_oracle(ctx, oracle, name, T, K, F):
+    """Against the oracle's restatement of cpu_vec_dot_*_f16 (one running f32 sum per output; here the sum is a
+    shuffle tree): ragged K, strided rows, bias, f16 output."""
+    import torch
+
+    kind = KINDS[name]
+    rng = np.random.default_rng(T * 31 + K + F)
+    W = random_blocks(kind, F, K, rng)
+    xbuf = rng.normal(0, 1, (T, K + 3)).astype(np.float16)
+    x16 = np.ascontiguousarray(xbuf[:, :K])
+    bias = rng.normal(0, 1, F).astype(np.float32)
+    wd = ctx.upload(W)
+    xd = torch.from_numpy(xbuf).cuda()[:, :K]
+    got = ctx.linear_f16(kind, xd, wd, F, bias=torch.from_numpy(bias).cuda()).cpu().numpy()
+    want = oracle.linear_f16(kind, x16, W, F, bias=bias)
+    assert max_rel_err(got, want) <= TOL_FP32
+    assert max_rel_err(got, want) <= 2e-5  # in practice: the order of the f32 additions
+    half = ctx.linear_f16(kind, xd, wd, F, out_dtype=torch.float16).cpu().numpy().astype(np.float32)
+    plain = oracle.linear_f16(kind, x16, W, F)
+    finite = np.abs(plain) < 6e4
+    assert np.max(np.abs(half - plain)[finite] / np.maximum(np.abs(plain[finite]), 1.0)) <= 2e-3  # one f16 rounding

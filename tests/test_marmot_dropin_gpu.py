@@ -50,6 +50,24 @@ def test_marmot_linear(libs, kind, T, K, F):
 
 
 @pytest.mark.parametrize("kind", [KIND_Q4_K, KIND_Q6_K, KIND_Q8_0])
+@pytest.mark.parametrize("T,K,F,half_out", [(1, 4096, 256, False), (6, 1024, 96, True), (20, 512, 64, False)])
+def test_marmot_linear_with_float16_activations(libs, kind, T, K, F, half_out):
+    """FLOAT16 inputs take the reference's unpacked branch (no Q8 packing, f32 arithmetic per weight value): the CUDA
+    context against the CPU context, f32 and f16 outputs."""
+    cpu, cuda = libs
+    rng = np.random.default_rng(T + kind + K)
+    W = random_blocks(kind, F, K, rng)
+    x16 = rng.normal(0, 1, (T, K)).astype(np.float16)
+    got = cuda.linear_f16(kind, x16, W, F, half_out).astype(np.float32)
+    want = cpu.linear_f16(kind, x16, W, F, half_out).astype(np.float32)
+    if half_out:
+        ok = np.isfinite(want)
+        assert np.max(np.abs(got - want)[ok] / np.maximum(np.abs(want[ok]), 1.0)) <= 2e-3  # one f16 place
+    else:
+        assert max_rel_err(got, want) <= 2e-5
+
+
+@pytest.mark.parametrize("kind", [KIND_Q4_K, KIND_Q6_K, KIND_Q8_0])
 def test_marmot_dequantize_is_bit_exact(libs, kind):
     cpu, cuda = libs
     rng = np.random.default_rng(kind)

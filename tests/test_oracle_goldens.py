@@ -99,3 +99,19 @@ def test_against_reference_library_live(oracle, reference_lib, name):
         x = rng.normal(0, 1, (T, K)).astype(np.float32)
         assert np.array_equal(bits(reference_lib.dequantize(kind, W, F * K)), bits(oracle.dequantize(kind, W, F * K)))
         assert np.array_equal(bits(reference_lib.linear(kind, x, W, F)), bits(oracle.linear(kind, x, W, F)))
+
+
+@pytest.mark.parametrize("name", ["q4_k", "q6_k", "q8_0"])
+def test_linear_f16_oracle_against_the_reference_goldens(oracle, llama_goldens, name):
+    """The f16-activation matmul restated from cpu_vec_dot_*_f16 reproduces g_matmul_*_output_from_f16 (bit for bit
+    for Q4_K and Q8_0; the Q6_K golden differs in the last place, as the reference library's own output does)."""
+    from tests.util import KINDS
+
+    N, K, M = (int(v) for v in llama_goldens[f"matmul_{name}_dims"])
+    x16 = llama_goldens[f"matmul_{name}_input_f16"].view(np.uint16).reshape(N, K)
+    got = oracle.linear_f16(KINDS[name], x16, llama_goldens[f"matmul_{name}_weight"], M)
+    want = llama_goldens[f"matmul_{name}_output_from_f16"].reshape(N, M)
+    if name == "q6_k":
+        assert np.max(np.abs(got - want) / np.abs(want)) <= 1e-6
+    else:
+        assert np.array_equal(got, want)
