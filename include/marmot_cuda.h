@@ -506,6 +506,10 @@ int mcu_peer_moe_combine(
  * Measured on 2 GPUs at T = 64 the two-kernel form is the faster one (25 vs 32 us for a 4096x2048 shard), which
  * is why it is the default. */
 int mcu_peer_comm_set_fused(mcu_peer_comm_t *comm, int enabled);
+/* One staging slot instead of two alternating ones: every collective then ends with a "finished reading" exchange, and a
+ * captured CUDA graph may hold any number of collectives (with two slots: an even number).  Costs one more flag round trip
+ * per collective; synchronizes the context's stream; every rank must choose the same. */
+int mcu_peer_comm_set_one_slot(mcu_peer_comm_t *comm, int enabled);
 int mcu_linear_allreduce(
     mcu_context_t *ctx, mcu_peer_comm_t *comm, int kind, const float *x_dev, size_t ldx, const void *w_dev, size_t T,
     size_t K, size_t F, float *out_dev

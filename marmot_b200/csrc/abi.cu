@@ -945,7 +945,11 @@ static int moe_experts_impl(mcu_context_t *ctx, int gate_kind, int up_kind, int 
     // Large batches: one grouped launch per projection over all local experts, sized from the device-resident counts.
     // Nothing is read back, so the call neither waits for the device nor breaks a stream capture.
     static const bool no_grouped = getenv("MARMOT_CUDA_MOE_NO_GROUPED") != nullptr;  // diagnostic switch
-    const bool grouped = !no_grouped && routes >= 256 && gate_kind == up_kind &&
+    // Fewer routes normally take per-expert launches sized from counts read back on the host (small groups then get the
+    // GEMV kernels); a call that is being recorded into a CUDA graph cannot read anything back, so it takes the grouped
+    // launches whatever its size.
+    const bool grouped = !no_grouped && (routes >= 256 || stream_is_capturing(s) || routed_rows_ext != nullptr) &&
+        gate_kind == up_kind &&
         gemm_tma_grouped_supported(gate_kind, gate_dev, (int)H, (int)FF) &&
         gemm_tma_grouped_supported(up_kind, up_dev, (int)H, (int)FF) &&
         gemm_tma_grouped_supported(down_kind, down_dev, (int)FF, (int)H) &&

@@ -10,8 +10,10 @@
 // Two parities are enough: a rank can only pass the wait of call n+1 after every peer has started call n+1,
 // i.e. finished reading call n, and it overwrites parity n & 1 again in call n+2 at the earliest.
 // The epoch lives in device memory (read by every CTA at its start, advanced by the last CTA to finish), so a
-// captured CUDA graph can be replayed; the staging pointer a producer writes to is fixed at capture, which is
-// why a graph must hold an even number of all-reduces per communicator.
+// captured CUDA graph can be replayed; the staging pointer a producer writes to is fixed at capture, so with the two
+// alternating slots a graph must hold an even number of collectives per communicator.  mcu_peer_comm_set_one_slot
+// lifts that: one slot, and every kernel ends with a second flag exchange ("finished reading"), after which nothing
+// can still be reading what the next producer overwrites.
 // A wait that runs out (a peer that never arrives) sets the context's error flag and skips the sum; the
 // kernel always terminates.
 #include "../../include/marmot_cuda.h"
@@ -46,6 +48,11 @@ struct PeerParams {
     size_t n;         // floats
     float *out;
     int *err;
+    // One-slot mode (mcu_peer_comm_set_one_slot): always parity 0, and the kernel ends only when every peer has finished
+    // reading this rank's slot, so that whatever writes the slot next -- however many all-reduces a replayed CUDA graph
+    // holds -- cannot overtake a reader.  done[r]: rank r's array of "finished reading" epochs, one entry per rank.
+    int one_slot;
+    uint32_t *done[PEER_MAX_WORLD];
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
@@ -62,6 +69,33 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
+// The end of every collective kernel of this file: the last CTA of the grid to get here (ticket) publishes the epoch
+// for the next launch.  In one-slot mode it first tells every peer that this rank has finished reading, and waits,
+// bounded, until every peer has said the same.
+__device__ __forceinline__ void peer_finish(const PeerParams &p, uint32_t epoch) {
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    __threadfence();
+    if (atomicAdd(p.ctr + 1, 1u) != gridDim.x - 1) return;
+    p.ctr[1] = 0;
+    if (p.one_slot) {
+        __threadfence_system();
+        for (int r = 0; r < p.world; ++r) st_release_sys(p.done[r] + (size_t)p.rank * 16, epoch);
+        for (int r = 0; r < p.world; ++r) {
+            const unsigned long long t0 = global_ns();
+            while ((int32_t)(ld_acquire_sys(p.done[p.rank] + (size_t)r * 16) - epoch) < 0) {
+                if (global_ns() - t0 > PEER_WAIT_NS) {
+                    atomicExch(p.err, 25);
+                    break;
+                }
+                __nanosleep(200);
+            }
+        }
+    }
+    __threadfence();
+    *(volatile uint32_t *)p.ctr = epoch;
+}
+
 __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const PeerParams p) {
     __shared__ int ok_s;
     __shared__ uint32_t epoch_s;
@@ -71,7 +105,7 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const PeerParams
     }
     __syncthreads();
     const uint32_t epoch = epoch_s;
-    const int parity = epoch & 1u;
+    const int parity = p.one_slot ? 0 : (int)(epoch & 1u);
     const size_t slot_offset = PEER_FLAG_BYTES + (size_t)parity * p.capacity;
     if (blockIdx.x == 0 && threadIdx.x < p.world) {
         // this rank's partial result was written by earlier work on this stream
@@ -114,16 +148,7 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const PeerParams
         for (int r = 1; r < p.world; ++r) acc = __fadd_rn(acc, __ldcg((const float *)(p.base[r] + slot_offset) + i));
         p.out[i] = acc;
     }
-    // the last CTA to get here publishes the epoch for the next launch (every CTA has read it by now)
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(p.ctr + 1, 1u) == gridDim.x - 1) {
-            p.ctr[1] = 0;
-            __threadfence();
-            *(volatile uint32_t *)p.ctr = epoch;
-        }
-    }
+    peer_finish(p, epoch);
 }
 
 
@@ -137,7 +162,8 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const PeerParams
 // the occupancy of this kernel.  The flags of the two phases live side by side: [parity][phase][rank].
 constexpr size_t PEER_CTR2_OFFSET = PEER_CTR_OFFSET + 128;    // phase-1 ticket of the owning rank
 constexpr size_t PEER_PHASE2_OFFSET = PEER_CTR_OFFSET + 256;  // [parity][rank] u32, 64 bytes apart
-static_assert(PEER_PHASE2_OFFSET + 2 * PEER_MAX_WORLD * 64 <= PEER_FUSE_FLAG_OFFSET, "layout");
+constexpr size_t PEER_DONE_OFFSET = PEER_PHASE2_OFFSET + 2 * PEER_MAX_WORLD * 64;  // [rank] u32, 64 bytes apart (one-slot mode)
+static_assert(PEER_DONE_OFFSET + PEER_MAX_WORLD * 64 <= PEER_FUSE_FLAG_OFFSET, "layout");
 
 __device__ __forceinline__ bool peer_wait_flag(const uint32_t *f, uint32_t epoch, int *err, int code) {
     const unsigned long long t0 = global_ns();
@@ -167,7 +193,7 @@ __global__ void __launch_bounds__(512) allreduce_rs_ag_kernel(const PeerParams2 
     }
     __syncthreads();
     const uint32_t epoch = epoch_s;
-    const int parity = epoch & 1u;
+    const int parity = p.one_slot ? 0 : (int)(epoch & 1u);
     const size_t slot_offset = PEER_FLAG_BYTES + (size_t)parity * p.capacity;
     if (blockIdx.x == 0 && threadIdx.x < p.world) {
         __threadfence_system();  // this rank's partial result was written by earlier work on this stream
@@ -228,15 +254,7 @@ __global__ void __launch_bounds__(512) allreduce_rs_ag_kernel(const PeerParams2 
             }
         }
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(p.ctr + 1, 1u) == gridDim.x - 1) {
-            p.ctr[1] = 0;
-            __threadfence();
-            *(volatile uint32_t *)p.ctr = epoch;
-        }
-    }
+    peer_finish(p, epoch);
 }
 
 
@@ -271,7 +289,7 @@ __global__ void __launch_bounds__(512) moe_ep_combine_kernel(const PeerMoeParams
     }
     __syncthreads();
     const uint32_t epoch = epoch_s;
-    const int parity = epoch & 1u;
+    const int parity = p.one_slot ? 0 : (int)(epoch & 1u);
     const size_t slot_offset = PEER_FLAG_BYTES + (size_t)parity * p.capacity;
     if (blockIdx.x == 0 && threadIdx.x < p.world) {
         __threadfence_system();  // this rank's routed rows were written by the down projection earlier on this stream
@@ -349,15 +367,7 @@ __global__ void __launch_bounds__(512) moe_ep_combine_kernel(const PeerMoeParams
         const float4 *from = (const float4 *)(p.base[src] + slot_offset + m.result_offset);
         for (size_t i = (size_t)lo * H4 + tid; i < (size_t)max(hi, lo) * H4; i += stride) out4[i] = __ldcg(from + i);
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(p.ctr + 1, 1u) == gridDim.x - 1) {
-            p.ctr[1] = 0;
-            __threadfence();
-            *(volatile uint32_t *)p.ctr = epoch;
-        }
-    }
+    peer_finish(p, epoch);
 }
 
 }  // namespace mcu
@@ -372,6 +382,7 @@ struct mcu_peer_comm {
     uint8_t *mapped[PEER_MAX_WORLD] = {};
     bool connected = false;
     bool fused = false;  // mcu_linear_allreduce as one kernel (see mcu_peer_comm_set_fused)
+    bool one_slot = false;  // see PeerParams::one_slot
     uint32_t epoch = 0;
 };
 
@@ -454,8 +465,16 @@ int mcu_peer_comm_set_fused(mcu_peer_comm_t *c, int enabled) {
 
 void *mcu_peer_comm_staging(mcu_peer_comm_t *c) {
     if (c == nullptr) return nullptr;
-    // slot of the NEXT all-reduce
-    return c->local + PEER_FLAG_BYTES + (size_t)((c->epoch + 1) & 1u) * c->capacity;
+    // slot of the NEXT collective: the two slots take turns, unless the communicator keeps to one
+    return c->local + PEER_FLAG_BYTES + (c->one_slot ? 0 : (size_t)((c->epoch + 1) & 1u) * c->capacity);
+}
+
+int mcu_peer_comm_set_one_slot(mcu_peer_comm_t *c, int enabled) {
+    if (c == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "null argument");
+    PEER_CUDA(cudaSetDevice(context_device(c->ctx)));
+    PEER_CUDA(cudaStreamSynchronize((cudaStream_t)mcu_context_get_stream(c->ctx)));  // nothing of the other mode in flight here
+    c->one_slot = enabled != 0;
+    return MCU_SUCCESS;
 }
 
 int mcu_peer_allreduce(mcu_peer_comm_t *c, size_t n_floats, float *out_dev) {
@@ -473,6 +492,8 @@ int mcu_peer_allreduce(mcu_peer_comm_t *c, size_t n_floats, float *out_dev) {
         p.base[r] = c->mapped[r];
         p.flag_base[r] = c->mapped[r];
     }
+    for (int r = 0; r < c->world; ++r) p.done[r] = (uint32_t *)(c->mapped[r] + PEER_DONE_OFFSET);
+    p.one_slot = c->one_slot ? 1 : 0;
     p.rank = c->rank;
     p.world = c->world;
     p.ctr = (uint32_t *)(c->local + PEER_CTR_OFFSET);
@@ -520,7 +541,7 @@ int mcu_linear_allreduce(mcu_context_t *ctx, mcu_peer_comm_t *c, int kind, const
     if (T * F * sizeof(float) > c->capacity)
         return set_error(MCU_ERROR_INVALID_ARGUMENT, "result larger than the communicator's staging buffer");
     if (!c->connected) return set_error(MCU_ERROR_INVALID_OPERATION, "peer communicator is not connected");
-    if (c->fused && c->world > 1 && gemm_tma_can_fuse(kind, (int)T, (int)F) && ((uintptr_t)out_dev & 15) == 0) {
+    if (c->fused && !c->one_slot && c->world > 1 && gemm_tma_can_fuse(kind, (int)T, (int)F) && ((uintptr_t)out_dev & 15) == 0) {
         // one kernel: the matmul's epilogue publishes its tiles and pulls the peers' tiles
         const uint32_t parity = (c->epoch + 1) & 1u;
         PeerFuse f;
@@ -583,7 +604,9 @@ int mcu_peer_moe_combine(mcu_peer_comm_t *c, const int32_t *route_pos_dev, const
         m.pp.base.base[r] = c->mapped[r];
         m.pp.base.flag_base[r] = c->mapped[r];
         m.pp.phase2[r] = (uint32_t *)(c->mapped[r] + PEER_PHASE2_OFFSET);
+        m.pp.base.done[r] = (uint32_t *)(c->mapped[r] + PEER_DONE_OFFSET);
     }
+    m.pp.base.one_slot = c->one_slot ? 1 : 0;
     m.pp.base.rank = c->rank;
     m.pp.base.world = c->world;
     m.pp.base.ctr = (uint32_t *)(c->local + PEER_CTR_OFFSET);

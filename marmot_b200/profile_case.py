@@ -3,6 +3,8 @@ self-ending command that a profiler (ncu) or a quick timing wraps.
 
     python -m marmot_b200.profile_case --kind q4_k -T 1 -K 4096 -F 4096 --copies 16 --iters 3
     python -m marmot_b200.profile_case --op attention --seqs 64 --ctx 2048 --layers 4 --iters 2 --time
+    python -m marmot_b200.profile_case --op attention --decode --seqs 1 --ctx 250 --q-heads 32 --kv-heads 4 --head-dim 64
+    python -m marmot_b200.profile_case --op layer --layers 22 --iters 2 --time      (the decode step's five kernels)
 
 The weights rotate over ``--copies`` distinct matrices so that a memory-bound kernel reads from HBM rather
 than from L2.  With ``--time`` the calls are also captured in a CUDA graph and replayed, and the average
@@ -17,7 +19,7 @@ import numpy as np
 from .runtime import KIND_BY_NAME, KIND_Q4_K, KIND_Q6_K, Context, row_bytes
 from .synthetic import synthetic_blocks, synthetic_blocks_device
 
-REGIMES = {"auto": 0, "gemv": 1, "gemm": 2, "gemv_plain": 3}
+REGIMES = {"auto": 0, "gemv": 1, "gemm": 2, "gemv_plain": 3, "i8mma": 4}
 
 
 def attention_case(args) -> None:
@@ -46,9 +48,16 @@ def attention_case(args) -> None:
     v = torch.randn((args.seqs, hkv * hd), device=dev, generator=gen)
     out = torch.empty_like(q)
 
+    pos = torch.full((args.seqs,), args.ctx, dtype=torch.int32, device=dev)
+    rope = ctx.rope_table(pos, hd, 500000.0)
+
     def one_pass():
         for layer in range(L):
-            ctx.paged_attention(meta, q, k, v, kv_k, kv_v, table, layer, hq, hkv, hd, bs, hd ** -0.5, out=out)
+            if args.decode:  # RoPE + append + attention + merge in one launch (two at many CTAs)
+                ctx.paged_attention_decode(meta, q, k, v, kv_k, kv_v, table, layer, hq, hkv, hd, bs, hd ** -0.5, pos,
+                                           500000.0, rope_table=rope, out=out)
+            else:
+                ctx.paged_attention(meta, q, k, v, kv_k, kv_v, table, layer, hq, hkv, hd, bs, hd ** -0.5, out=out)
 
     stream = torch.cuda.Stream(dev)
     ctx.set_stream(stream.cuda_stream)
@@ -74,7 +83,8 @@ def attention_case(args) -> None:
             e1.record(stream)
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / (reps * L)
-        print(f"{us:.2f} us per call (append + attention + merge), {nbytes / us / 1e3:.0f} GB/s of pool bytes")
+        what = "RoPE + append + attention + merge" if args.decode else "append + attention + merge"
+        print(f"{us:.2f} us per call ({what}), {nbytes / us / 1e3:.0f} GB/s of pool bytes")
     ctx.set_stream(0)
     ctx.close()
 
@@ -127,9 +137,81 @@ def moe_case(args) -> None:
     ctx.close()
 
 
+def layer_case(args) -> None:
+    """The five launches of one decoder layer in a fused decode step, TinyLlama-1.1B shape by default (d 2048, FFN 5632,
+    32 / 4 heads of 64; Q4_K with Q6_K for v and down), -T tokens of one context length each, `--layers` layers with
+    weights of their own in turn: q/k/v with add + RMSNorm prologue, decode attention, o projection, gate/up with
+    add + RMSNorm prologue, down with SwiGLU prologue."""
+    import torch
+
+    from .synthetic import synthetic_blocks_device
+
+    dev = torch.device("cuda", 0)
+    ctx = Context(0)
+    d, ffn, hq, hkv, hd, L, T, bs = args.K if args.K != 4096 else 2048, args.F if args.F != 4096 else 5632, 32, 4, 64, args.layers, args.T, 16
+    gen = torch.Generator(device=dev).manual_seed(1)
+    mk = lambda kind, F, K: [synthetic_blocks_device(torch, kind, F, K, dev, gen) for _ in range(L)]
+    wq, wk, wv, wo = mk(KIND_Q4_K, d, d), mk(KIND_Q4_K, hkv * hd, d), mk(KIND_Q6_K, hkv * hd, d), mk(KIND_Q4_K, d, d)
+    wg, wu, wd = mk(KIND_Q4_K, ffn, d), mk(KIND_Q4_K, ffn, d), mk(KIND_Q6_K, d, ffn)
+    xa, xb = torch.randn((T, d), device=dev, generator=gen), torch.empty((T, d), device=dev)
+    nw = torch.ones(d, device=dev)
+    q, k, v = (torch.empty((T, n), device=dev) for n in (d, hkv * hd, hkv * hd))
+    att, proj = torch.empty((T, d), device=dev), torch.randn((T, d), device=dev, generator=gen) * 0.01
+    gate, up = torch.empty((T, ffn), device=dev), torch.empty((T, ffn), device=dev)
+    per_seq = (args.ctx + 1 + bs - 1) // bs
+    kv_k = (torch.randn((T * per_seq, L, hkv, bs, hd), device=dev, generator=gen) * 0.1).half()
+    kv_v = (torch.randn((T * per_seq, L, hkv, bs, hd), device=dev, generator=gen) * 0.1).half()
+    table = torch.arange(T * per_seq, dtype=torch.int32, device=dev).view(T, per_seq).contiguous()
+    meta = np.zeros((T, 4), dtype=np.uint32)
+    meta[:, 0], meta[:, 1], meta[:, 2] = np.arange(T), args.ctx, np.arange(T) * per_seq * bs + args.ctx
+    meta = torch.from_numpy(meta.view(np.int32)).to(dev)
+    pos = torch.full((T,), args.ctx, dtype=torch.int32, device=dev)
+    rope = ctx.rope_table(pos, hd, 10000.0)
+
+    def one_pass():
+        for i in range(L):
+            ctx.linear_multi(xa, [(KIND_Q4_K, wq[i], d, q), (KIND_Q4_K, wk[i], hkv * hd, k), (KIND_Q6_K, wv[i], hkv * hd, v)],
+                             ("add_rmsnorm", proj, nw, 1e-5, 0.0, xb))
+            ctx.paged_attention_decode(meta, q, k, v, kv_k, kv_v, table, i, hq, hkv, hd, bs, hd ** -0.5, pos, 10000.0,
+                                       rope_table=rope, out=att)
+            ctx.linear(KIND_Q4_K, att, wo[i], d, out=proj)
+            ctx.linear_multi(xb, [(KIND_Q4_K, wg[i], ffn, gate), (KIND_Q4_K, wu[i], ffn, up)],
+                             ("add_rmsnorm", proj, nw, 1e-5, 0.0, xa))
+            ctx.linear_multi(gate, [(KIND_Q6_K, wd[i], d, proj)], ("swiglu", up))
+
+    stream = torch.cuda.Stream(dev)
+    ctx.set_stream(stream.cuda_stream)
+    with torch.cuda.stream(stream):
+        for _ in range(args.iters):
+            one_pass()
+    torch.cuda.synchronize()
+    wbytes = sum(int(w[0].numel()) for w in (wq, wk, wv, wo, wg, wu, wd))
+    print(f"layer d={d} ffn={ffn} T={T} ctx={args.ctx}: {L} layers, {args.iters} passes, {ctx.launch_count()} kernel launches, "
+          f"{wbytes} weight bytes per layer")
+    if args.time:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 20
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * L)
+        print(f"{us:.2f} us per layer (5 launches), {wbytes / us / 1e3:.0f} GB/s of weight bytes")
+    ctx.set_stream(0)
+    ctx.close()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--op", default="linear", choices=["linear", "attention", "moe"])
+    ap.add_argument("--op", default="linear", choices=["linear", "attention", "moe", "layer"])
+    ap.add_argument("--decode", action="store_true", help="attention: the one-launch decode form (RoPE + append + merge folded in)")
     ap.add_argument("--experts", type=int, default=8, help="moe: experts")
     ap.add_argument("--top-k", type=int, default=2, help="moe: routes per token")
     ap.add_argument("--seqs", type=int, default=64, help="attention: sequences (one new token each)")
@@ -152,6 +234,8 @@ def main() -> None:
         return attention_case(args)
     if args.op == "moe":
         return moe_case(args)
+    if args.op == "layer":
+        return layer_case(args)
 
     import torch
 

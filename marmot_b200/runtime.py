@@ -26,7 +26,7 @@ EXPORTS = (
     "mcu_quantize_activations", "mcu_linear", "mcu_linear_dual", "mcu_linear_multi", "mcu_linear_f16", "mcu_linear_host", "mcu_topk", "mcu_moe_experts",
     "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_moe_experts_ep", "mcu_peer_moe_combine", "mcu_peer_comm_capacity", "mcu_peer_comm_rank", "mcu_peer_comm_world", "mcu_moe_last_buffers", "mcu_peer_comm_create", "mcu_peer_comm_export",
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
-    "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
+    "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_peer_comm_set_one_slot", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
     "mcu_embedding_gather", "mcu_paged_attention", "mcu_paged_attention_decode", "mcu_rope_table", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps", "mcu_vec_dot_host",
     "mcu_kv_pool_options_init", "mcu_kv_pool_create", "mcu_kv_pool_destroy", "mcu_kv_pool_acquire_seq",
     "mcu_kv_pool_release_seq", "mcu_kv_pool_prepare_append", "mcu_kv_pool_commit_append", "mcu_kv_pool_abort_append",
@@ -125,6 +125,7 @@ def load_library() -> C.CDLL:
     L.mcu_peer_comm_destroy.restype = None
     L.mcu_linear_allreduce.argtypes = [vp, vp, i32, vp, sz, vp, sz, sz, sz, vp]
     L.mcu_peer_comm_set_fused.argtypes = [vp, i32]
+    L.mcu_peer_comm_set_one_slot.argtypes = [vp, i32]
     L.mcu_rmsnorm.argtypes = [vp, vp, vp, vp, sz, sz, f32, f32, vp]
     L.mcu_rope.argtypes = [vp, vp, sz, vp, sz, sz, sz, f32, f32, i32, vp, sz]
     L.mcu_swiglu.argtypes = [vp, vp, vp, sz, vp]
@@ -466,6 +467,11 @@ class PeerComm:
     def set_fused(self, enabled: bool):
         """One-kernel form of linear_allreduce (matmul epilogue + all-reduce); every rank must choose the same."""
         self.ctx._check(self.ctx.lib.mcu_peer_comm_set_fused(self.handle, 1 if enabled else 0))
+
+    def set_one_slot(self, enabled: bool):
+        """One staging slot and a closing "finished reading" exchange per collective: a captured CUDA graph may then hold
+        any number of collectives (an even number with the default two slots); every rank must choose the same."""
+        self.ctx._check(self.ctx.lib.mcu_peer_comm_set_one_slot(self.handle, 1 if enabled else 0))
 
     def staging(self, shape):
         """The buffer the next all-reduce sums, as a float32 torch tensor of `shape` (a view, no copy)."""

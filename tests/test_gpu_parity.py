@@ -427,7 +427,8 @@ def test_moe_grouped_path_vs_oracle(ctx, oracle, kinds):
 
 def test_moe_grouped_path_records_into_a_graph(ctx):
     """With 256 routes or more nothing is read back, so the whole expert block can be captured once and replayed on new
-    token contents and new routing; a small batch says that it cannot be captured and leaves the capture usable."""
+    token contents and new routing; a small batch, which eagerly reads its group sizes back, takes the grouped launches
+    too while it is being recorded."""
     import torch
 
     from marmot_b200 import MarmotCudaError
@@ -451,8 +452,8 @@ def test_moe_grouped_path_records_into_a_graph(ctx):
         with torch.cuda.stream(stream):
             ctx.graph_capture_begin()
             run()
-            with pytest.raises(MarmotCudaError, match="cannot be captured"):
-                ctx.moe_experts_local(kinds, hd_[:8], gd, ud, dd, idd[:8], vd[:8], FF, E, 0, E, out=out[:8])
+            small = torch.zeros((8, H), dtype=torch.float32, device="cuda")
+            ctx.moe_experts_local(kinds, hd_[:8], gd, ud, dd, idd[:8], vd[:8], FF, E, 0, E, out=small)
             graph = ctx.graph_capture_end()
             hd_.copy_(dev(ctx, rng.normal(0, 1, (T, H)).astype(np.float32)))
             idd.copy_(dev(ctx, ((order + 1) % E).astype(np.int32)))
@@ -463,6 +464,10 @@ def test_moe_grouped_path_records_into_a_graph(ctx):
             run()
             ctx.synchronize()
             assert torch.equal(replayed, out)
+            # the small call: recorded on the tensor-core path, eager on the per-expert GEMV path
+            eager = ctx.moe_experts_local(kinds, hd_[:8], gd, ud, dd, idd[:8], vd[:8], FF, E, 0, E)
+            ctx.synchronize()
+            assert max_rel_err(small.cpu().numpy(), eager.cpu().numpy()) <= TOL_MOE
             graph.close()
     finally:
         ctx.set_stream(0)

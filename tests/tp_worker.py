@@ -65,6 +65,43 @@ def main() -> int:
         got = out.cpu().numpy()
         check(f"allreduce_two_phase_exact_{rep}", np.array_equal(got[:n], want) and np.all(got[n:] == 3.0))
 
+    # one-slot mode: a CUDA graph with an ODD number of collectives (small and large), replayed; back to two slots after
+    comm.set_one_slot(True)
+    stream = torch.cuda.Stream(dev)
+    ctx.set_stream(stream.cuda_stream)
+    sizes = (100003, 800003, 4099)
+    srcs = [torch.from_numpy(np.random.default_rng(300 + 10 * i + rank).normal(0, 1, m).astype(np.float32)).to(dev)
+            for i, m in enumerate(sizes)]
+    wants = []
+    for i, m in enumerate(sizes):
+        acc = np.random.default_rng(300 + 10 * i).normal(0, 1, m).astype(np.float32)
+        for r in range(1, world):
+            acc = acc + np.random.default_rng(300 + 10 * i + r).normal(0, 1, m).astype(np.float32)
+        wants.append(acc)
+    outs = [torch.zeros(m, dtype=torch.float32, device=dev) for m in sizes]
+
+    def three_collectives():
+        for src, o in zip(srcs, outs):
+            comm.staging((src.numel(),)).copy_(src)
+            comm.allreduce(src.numel(), o)
+
+    with torch.cuda.stream(stream):
+        three_collectives()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            three_collectives()
+        for rep in range(3):
+            for o in outs:
+                o.zero_()
+            g.replay()
+            torch.cuda.synchronize()
+            check(f"one_slot_graph_replay_{rep}", all(np.array_equal(o.cpu().numpy(), w) for o, w in zip(outs, wants)))
+    ctx.synchronize()
+    ctx.set_stream(0)
+    comm.set_one_slot(False)
+    dist.barrier()
+
     rng = np.random.default_rng(42)
     for kind in (KIND_Q4_K, KIND_Q6_K, KIND_Q8_0):
         for T in (1, 5, 48):
