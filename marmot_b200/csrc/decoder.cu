@@ -585,30 +585,54 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
     {
         const bool head_ok = g < gsize;
         const float *qrow = p.q + ((size_t)t * p.n_q_heads + (size_t)h * gsize + (head_ok ? g : 0)) * HD;
-        const float2 *rope = FUSED ? fd.rope + (size_t)t * (HD / 2) : nullptr;
+        // All loads first, without a branch between them (a branch per pair would serialise sixteen trips to L2: measured,
+        // +50 % on the whole kernel), then the rotation, then the split.
+        float2 qv[KS][2];
+#pragma unroll
+        for (int s = 0; s < KS; ++s)
+#pragma unroll
+            for (int hk = 0; hk < 2; ++hk)
+                qv[s][hk] = head_ok ? *(const float2 *)(qrow + 16 * s + 8 * hk + 2 * tq) : make_float2(0.0f, 0.0f);
+        if (FUSED) {
+            const float2 *rope = fd.rope + (size_t)t * (HD / 2);
+            if (!fd.neox) {  // the pair (d, d + 1) is one float2
+                float2 cs[KS][2];
+#pragma unroll
+                for (int s = 0; s < KS; ++s)
+#pragma unroll
+                    for (int hk = 0; hk < 2; ++hk) cs[s][hk] = __ldg(rope + ((16 * s + 8 * hk + 2 * tq) >> 1));
+#pragma unroll
+                for (int s = 0; s < KS; ++s)
+#pragma unroll
+                    for (int hk = 0; hk < 2; ++hk) {
+                        const float x = qv[s][hk].x, y = qv[s][hk].y, c = cs[s][hk].x, sn = cs[s][hk].y;
+                        qv[s][hk].x = __fsub_rn(__fmul_rn(x, c), __fmul_rn(y, sn));
+                        qv[s][hk].y = __fadd_rn(__fmul_rn(x, sn), __fmul_rn(y, c));
+                    }
+            } else {  // the pairs (d, d +- HD/2): the partner of k step s is k step s +- KS/2 of this same lane
+                float4 cs[KS / 2][2];  // {cos, sin} of the two pairs (d, d + 1) of the low half
+#pragma unroll
+                for (int s = 0; s < KS / 2; ++s)
+#pragma unroll
+                    for (int hk = 0; hk < 2; ++hk) cs[s][hk] = __ldg((const float4 *)(rope + 16 * s + 8 * hk + 2 * tq));
+#pragma unroll
+                for (int s = 0; s < KS / 2; ++s)
+#pragma unroll
+                    for (int hk = 0; hk < 2; ++hk) {
+                        const float2 lo = qv[s][hk], hi = qv[s + KS / 2][hk];
+                        const float4 c = cs[s][hk];
+                        qv[s][hk].x = __fsub_rn(__fmul_rn(lo.x, c.x), __fmul_rn(hi.x, c.y));
+                        qv[s][hk].y = __fsub_rn(__fmul_rn(lo.y, c.z), __fmul_rn(hi.y, c.w));
+                        qv[s + KS / 2][hk].x = __fadd_rn(__fmul_rn(lo.x, c.y), __fmul_rn(hi.x, c.x));
+                        qv[s + KS / 2][hk].y = __fadd_rn(__fmul_rn(lo.y, c.w), __fmul_rn(hi.y, c.z));
+                    }
+            }
+        }
 #pragma unroll
         for (int s = 0; s < KS; ++s)
 #pragma unroll
             for (int hk = 0; hk < 2; ++hk) {
-                const int d = 16 * s + 8 * hk + 2 * tq;
-                float x = head_ok ? qrow[d] : 0.0f;
-                float y = head_ok ? qrow[d + 1] : 0.0f;
-                if (FUSED) {
-                    if (!fd.neox) {  // the pair (d, d + 1)
-                        const float2 cs = rope[d >> 1];
-                        const float xr = __fsub_rn(__fmul_rn(x, cs.x), __fmul_rn(y, cs.y));
-                        y = __fadd_rn(__fmul_rn(x, cs.y), __fmul_rn(y, cs.x));
-                        x = xr;
-                    } else {  // the pairs (d, d +- HD/2) and (d + 1, d + 1 +- HD/2)
-                        constexpr int half = HD / 2;
-                        const bool low = d < half;
-                        const float px = head_ok ? qrow[low ? d + half : d - half] : 0.0f;
-                        const float py = head_ok ? qrow[low ? d + 1 + half : d + 1 - half] : 0.0f;
-                        const float2 c0 = rope[low ? d : d - half], c1 = rope[low ? d + 1 : d + 1 - half];
-                        x = low ? __fsub_rn(__fmul_rn(x, c0.x), __fmul_rn(px, c0.y)) : __fadd_rn(__fmul_rn(px, c0.y), __fmul_rn(x, c0.x));
-                        y = low ? __fsub_rn(__fmul_rn(y, c1.x), __fmul_rn(py, c1.y)) : __fadd_rn(__fmul_rn(py, c1.y), __fmul_rn(y, c1.x));
-                    }
-                }
+                float x = qv[s][hk].x, y = qv[s][hk].y;
                 if (p.scale != 1.0f) {
                     x = __fmul_rn(x, p.scale);
                     y = __fmul_rn(y, p.scale);
@@ -807,26 +831,50 @@ __global__ void __launch_bounds__(32 * PM_WARPS) paged_attention_mma_kernel(Page
     }
 }
 
-// out[t][qh][:] from the chunk states; grid (query heads, tokens), HD threads.
+// out[t][qh][:] from the chunk states; grid (query heads, tokens), HD threads.  The chunks' maxima and sums go to shared
+// memory first (one load per thread, all in flight together), then every thread adds up its column eight chunks at a
+// time; chunk order throughout, so the result does not depend on how the work was cut.
 template <int HD>
 __global__ void paged_attention_merge_kernel(PagedParams p, int chunk, int n_chunks, const float *partial) {
+    extern __shared__ float mg_s[];  // m [live], then weight exp(m - M) in place; l [live]
     MCU_PDL_PROLOGUE();
     const int qh = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
     const uint32_t kv_len = p.meta[t * 4 + 1] + 1u;
     const int live = min(n_chunks, (int)((kv_len + (uint32_t)chunk - 1u) / (uint32_t)chunk));
     const float *pr = partial + ((size_t)t * p.n_q_heads + qh) * n_chunks * (HD + 2);
-    float M = -INFINITY;
-    for (int c = 0; c < live; ++c) M = fmaxf(M, pr[(size_t)c * (HD + 2)]);
-    float L = 0.0f, o = 0.0f;
-    if (M != -INFINITY) {
-        for (int c = 0; c < live; ++c) {
-            const float mc = pr[(size_t)c * (HD + 2)];
-            if (mc == -INFINITY) continue;
-            const float e = expf(mc - M);
-            L += pr[(size_t)c * (HD + 2) + 1] * e;
-            o += pr[(size_t)c * (HD + 2) + 2 + d] * e;
-        }
+    float *s_e = mg_s, *s_l = mg_s + n_chunks;
+    for (int c = d; c < live; c += HD) {
+        s_e[c] = pr[(size_t)c * (HD + 2)];
+        s_l[c] = pr[(size_t)c * (HD + 2) + 1];
     }
+    __syncthreads();
+    float M = -INFINITY;
+    for (int c = 0; c < live; ++c) M = fmaxf(M, s_e[c]);
+    __syncthreads();
+    for (int c = d; c < live; c += HD) {
+        const float mc = s_e[c];
+        s_e[c] = (M == -INFINITY || mc == -INFINITY) ? 0.0f : expf(mc - M);  // 0: the chunk adds nothing
+    }
+    __syncthreads();
+    float L = 0.0f, o = 0.0f;
+    const float *col = pr + 2 + d;
+    int c = 0;
+    for (; c + 8 <= live; c += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = col[(size_t)(c + u) * (HD + 2)];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (s_e[c + u] != 0.0f) {
+                L += s_l[c + u] * s_e[c + u];
+                o += v[u] * s_e[c + u];
+            }
+    }
+    for (; c < live; ++c)
+        if (s_e[c] != 0.0f) {
+            L += s_l[c] * s_e[c];
+            o += col[(size_t)c * (HD + 2)] * s_e[c];
+        }
     p.out[((size_t)t * p.n_q_heads + qh) * HD + d] = L > 0.0f ? o / L : 0.0f;
 }
 
@@ -999,6 +1047,7 @@ int mcu_paged_attention(mcu_context_t *ctx, const uint32_t *token_meta_dev, size
         return set_error(MCU_ERROR_UNSUPPORTED_DTYPE, "paged_attention KV pool must be FLOAT32 or FLOAT16");
     if (((uintptr_t)kv_k_dev | (uintptr_t)kv_v_dev) & 15)
         return set_error(MCU_ERROR_INVALID_ARGUMENT, "paged_attention KV pools must be 16-byte aligned");
+    if ((uintptr_t)q_dev & 7) return set_error(MCU_ERROR_INVALID_ARGUMENT, "paged_attention q must be 8-byte aligned");
     if (head_dim != 64 && head_dim != 128)
         return set_error(MCU_ERROR_NOT_IMPLEMENTED, "paged_attention supports head_dim 64 and 128");
     if (block_size == 0 || (block_size & (block_size - 1)) != 0)
@@ -1034,7 +1083,7 @@ int mcu_paged_attention(mcu_context_t *ctx, const uint32_t *token_meta_dev, size
            n_kv_heads * T * ((max_positions + chunk - 1) / chunk) < 2 * (size_t)device_sm_count())
         chunk /= 2;
     const size_t n_chunks = (max_positions + chunk - 1) / chunk;
-    if (n_chunks > 65535) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "paged_attention context bound too long");
+    if (n_chunks > 6000) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "paged_attention context bound too long");  // (the merge keeps two floats per chunk in shared memory)
     void *scratch = nullptr;
     if (int rc = context_attention_scratch(ctx, T * n_q_heads * n_chunks * (head_dim + 2) * sizeof(float), &scratch))
         return rc;
@@ -1060,9 +1109,9 @@ int mcu_paged_attention(mcu_context_t *ctx, const uint32_t *token_meta_dev, size
         else DEC_CUDA(launch_pdl(paged_attention_kernel<float, 128>, qg, tb, s, p, (int)chunk, partial));
     }
     if (head_dim == 64)
-        DEC_CUDA(launch_pdl(paged_attention_merge_kernel<64>, mg, dim3(64), s, p, (int)chunk, (int)n_chunks, (const float *)partial));
+        DEC_CUDA(launch_pdl_smem(paged_attention_merge_kernel<64>, mg, dim3(64), 2 * n_chunks * sizeof(float), s, p, (int)chunk, (int)n_chunks, (const float *)partial));
     else
-        DEC_CUDA(launch_pdl(paged_attention_merge_kernel<128>, mg, dim3(128), s, p, (int)chunk, (int)n_chunks, (const float *)partial));
+        DEC_CUDA(launch_pdl_smem(paged_attention_merge_kernel<128>, mg, dim3(128), 2 * n_chunks * sizeof(float), s, p, (int)chunk, (int)n_chunks, (const float *)partial));
     count_launches(3);
     return MCU_SUCCESS;
 }
@@ -1113,6 +1162,8 @@ int mcu_paged_attention_decode(mcu_context_t *ctx, const uint32_t *token_meta_de
     if (block_size == 0 || (block_size & (block_size - 1)) != 0)
         return set_error(MCU_ERROR_INVALID_ARGUMENT, "paged_attention block_size must be a power of two");
     if (layer >= n_layers) return set_error(MCU_ERROR_DIMENSION_MISMATCH, "paged_attention head / layer configuration invalid");
+    if (((uintptr_t)q_dev & 7) || ((uintptr_t)rope_table_dev & 15))
+        return set_error(MCU_ERROR_INVALID_ARGUMENT, "paged_attention q must be 8-byte aligned, the RoPE table 16-byte aligned");
     if (rope_type != MCU_ROPE_NORM && rope_type != MCU_ROPE_NEOX) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "unknown RoPE type");
     PagedParams p;
     p.meta = token_meta_dev;
@@ -1133,7 +1184,7 @@ int mcu_paged_attention_decode(mcu_context_t *ctx, const uint32_t *token_meta_de
     p.scale = scale;
     const size_t max_positions = max_blocks_per_seq * block_size;
     const size_t n_chunks = (max_positions + PM_CHUNK - 1) / PM_CHUNK;
-    if (n_chunks > 65535) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "paged_attention context bound too long");
+    if (n_chunks > 6000) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "paged_attention context bound too long");  // (the merge keeps two floats per chunk in shared memory)
     // Few CTAs: the step is a chain of latencies, and the last CTA of a token merging in place saves a launch.  Many
     // CTAs: the fence and the ticket keep every CTA (and its shared memory) alive for a round trip to L2 longer, which
     // at 64 sequences x 8 KV heads x ~17 chunks cost 25 % of the kernel (measured); a merge kernel is cheaper there.
@@ -1165,9 +1216,9 @@ int mcu_paged_attention_decode(mcu_context_t *ctx, const uint32_t *token_meta_de
     if (!ticket_merge) {
         const dim3 mg((unsigned)n_q_heads, (unsigned)T);
         if (head_dim == 64)
-            DEC_CUDA(launch_pdl(paged_attention_merge_kernel<64>, mg, dim3(64), s, p, (int)PM_CHUNK, (int)n_chunks, (const float *)scratch));
+            DEC_CUDA(launch_pdl_smem(paged_attention_merge_kernel<64>, mg, dim3(64), 2 * n_chunks * sizeof(float), s, p, (int)PM_CHUNK, (int)n_chunks, (const float *)scratch));
         else
-            DEC_CUDA(launch_pdl(paged_attention_merge_kernel<128>, mg, dim3(128), s, p, (int)PM_CHUNK, (int)n_chunks, (const float *)scratch));
+            DEC_CUDA(launch_pdl_smem(paged_attention_merge_kernel<128>, mg, dim3(128), 2 * n_chunks * sizeof(float), s, p, (int)PM_CHUNK, (int)n_chunks, (const float *)scratch));
         count_launches(1);
     }
     return MCU_SUCCESS;

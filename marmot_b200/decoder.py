@@ -275,7 +275,7 @@ class Decoder:
         ctx.rmsnorm(x, self.layers[0]["attn_norm"], s.rms_eps, out=h)
         # up to eight tokens q / k / v are one launch; beyond, three matmuls that run side by side on streams of their own
         side = self._side_contexts() if T > 8 else ()
-        fuse_ffn = self.group.world == 1 and T > 16 and s.ffn > 0 and not os.environ.get("MARMOT_DECODER_UNFUSED_FFN")  # diagnostic
+        fuse_ffn = T > 16 and s.ffn > 0 and not os.environ.get("MARMOT_DECODER_UNFUSED_FFN")  # (diagnostic switch)
         main = self._main_stream() if side else None
         for i, lw in enumerate(self.layers):
             if side:
