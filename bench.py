@@ -10,9 +10,10 @@ each GEMV in the pass is one call of the library's ``mcu_linear``.
 Printed on rank 0 as one JSON line:
   value     GB/s of algorithmic bytes (packed weights + x + y = 9 469 952 B per GEMV) over the timed
             region, inputs resident in HBM, summed over ranks
-  e2e       the same through ``mcu_linear_host``: activations start in pinned host memory and the
-            result lands in pinned host memory inside the timed region (weights stay resident; the
-            activations are copied to the device, the kernel writes the result over PCIe in place)
+  e2e       the same through the reference's public API on its CUDA context (``marmot_linear`` after
+            ``marmot_init(MARMOT_BACKEND_CUDA)`` in libmarmot_b200.so; ``mcu_linear_host`` when that library
+            is not built): activations start in host memory and the result lands in host memory inside the
+            timed region, weights stay resident
   roofline  the GEMV kernel against the measured HBM copy bandwidth
   cpu_baseline  the reference CPU backend (or the oracle port) on the host cores, bounded sample
 
@@ -40,7 +41,7 @@ W_BYTES = F_DIM * (K_DIM // 256) * 144
 ALG_BYTES = W_BYTES + T_TOK * K_DIM * 4 + T_TOK * F_DIM * 4  # 9 469 952
 METRIC = "q4k_gemv_hbm_gbps"
 UNIT = "GB/s"
-NCU_TRAFFIC_BYTES = 9_476_864  # DRAM bytes of one launch, from the committed ncu capture of this shape
+NCU_TRAFFIC_BYTES = 9_519_872  # DRAM bytes of one launch, from the committed ncu capture of this shape
 WORKLOAD = "Q4_K GEMV T=1 K=4096 F=4096 (BASELINE config 1), rotation of distinct weight matrices"
 
 
@@ -733,7 +734,7 @@ def main():
                      "traffic": NCU_TRAFFIC_BYTES, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of "
                      "one launch of this kernel and shape (profiles/gemv_stream_q4k_T1_K4096_F4096.md)",
                      "peak_source": peak_kind, "frac_of_nominal_8TBs": achieved / 8000.0,
-                     "algorithmic_bytes": ALG_BYTES, "kernel": "gemv_stream_kernel<Q4_K, T=1, NW=14, MINB=2>",
+                     "algorithmic_bytes": ALG_BYTES, "kernel": "gemv_stream_kernel<Q4_K, T=1, TW=14, TEAMS=1, MINB=2>",
                      "us_per_launch": per_launch_s * 1e6},
         "clocks": clocks,
     }

@@ -168,16 +168,22 @@ def layer_case(args) -> None:
     pos = torch.full((T,), args.ctx, dtype=torch.int32, device=dev)
     rope = ctx.rope_table(pos, hd, 10000.0)
 
+    steps = {
+        "qkv": lambda i: ctx.linear_multi(xa, [(KIND_Q4_K, wq[i], d, q), (KIND_Q4_K, wk[i], hkv * hd, k),
+                                               (KIND_Q6_K, wv[i], hkv * hd, v)], ("add_rmsnorm", proj, nw, 1e-5, 0.0, xb)),
+        "attn": lambda i: ctx.paged_attention_decode(meta, q, k, v, kv_k, kv_v, table, i, hq, hkv, hd, bs, hd ** -0.5, pos,
+                                                     10000.0, rope_table=rope, out=att),
+        "wo": lambda i: ctx.linear(KIND_Q4_K, att, wo[i], d, out=proj),
+        "gateup": lambda i: ctx.linear_multi(xb, [(KIND_Q4_K, wg[i], ffn, gate), (KIND_Q4_K, wu[i], ffn, up)],
+                                             ("add_rmsnorm", proj, nw, 1e-5, 0.0, xa)),
+        "down": lambda i: ctx.linear_multi(gate, [(KIND_Q6_K, wd[i], d, proj)], ("swiglu", up)),
+    }
+    chosen = [steps[n] for n in (args.only.split(",") if args.only else steps)]  # --only: a chain of one kind of kernel
+
     def one_pass():
         for i in range(L):
-            ctx.linear_multi(xa, [(KIND_Q4_K, wq[i], d, q), (KIND_Q4_K, wk[i], hkv * hd, k), (KIND_Q6_K, wv[i], hkv * hd, v)],
-                             ("add_rmsnorm", proj, nw, 1e-5, 0.0, xb))
-            ctx.paged_attention_decode(meta, q, k, v, kv_k, kv_v, table, i, hq, hkv, hd, bs, hd ** -0.5, pos, 10000.0,
-                                       rope_table=rope, out=att)
-            ctx.linear(KIND_Q4_K, att, wo[i], d, out=proj)
-            ctx.linear_multi(xb, [(KIND_Q4_K, wg[i], ffn, gate), (KIND_Q4_K, wu[i], ffn, up)],
-                             ("add_rmsnorm", proj, nw, 1e-5, 0.0, xa))
-            ctx.linear_multi(gate, [(KIND_Q6_K, wd[i], d, proj)], ("swiglu", up))
+            for step in chosen:
+                step(i)
 
     stream = torch.cuda.Stream(dev)
     ctx.set_stream(stream.cuda_stream)
@@ -203,7 +209,7 @@ def layer_case(args) -> None:
             e1.record(stream)
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / (reps * L)
-        print(f"{us:.2f} us per layer (5 launches), {wbytes / us / 1e3:.0f} GB/s of weight bytes")
+        print(f"{us:.2f} us per layer ({args.only or 'all five launches'}), {wbytes / us / 1e3:.0f} GB/s of the layer's weight bytes")
     ctx.set_stream(0)
     ctx.close()
 
@@ -211,6 +217,7 @@ def layer_case(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--op", default="linear", choices=["linear", "attention", "moe", "layer"])
+    ap.add_argument("--only", default="", help="layer: comma-separated subset of qkv,attn,wo,gateup,down")
     ap.add_argument("--decode", action="store_true", help="attention: the one-launch decode form (RoPE + append + merge folded in)")
     ap.add_argument("--experts", type=int, default=8, help="moe: experts")
     ap.add_argument("--top-k", type=int, default=2, help="moe: routes per token")
