@@ -362,6 +362,45 @@ int mcu_gguf_upload(
     void *dst_dev
 );
 
+/* ---- one decode step (one token) of a Llama-family decoder as ONE persistent kernel.  The op sequence of
+ *      src/graph/gguf/graph_builder.cpp:1454-2400 for a single token -- per layer: add + rms_norm, q/k/v, rope, paged
+ *      attention with KV append, o projection, add + rms_norm, gate/up, swiglu, down; then add + rms_norm and the output
+ *      projection -- with the CTAs resident for the whole step (cooperative launch), grid-wide barriers between the
+ *      dependent phases and the weight stream running across them.  The plan fixes every pointer: the caller puts the
+ *      embedded token into x0, the token's {seq slot, position, kv slot, flags} into token_meta and the {cos, sin} table of
+ *      its position (mcu_rope_table) into rope_table, runs the plan, and finds the logits in `logits`.  Q4_K / Q6_K
+ *      weights, float16 KV pool, head_dim 64 or 128; the matmul arithmetic is that of mcu_linear_multi (same device
+ *      functions), the attention is f32 on the f16 pool.  Bounded waits: a barrier that runs out sets the error reported by
+ *      mcu_synchronize.  The launch can be recorded into a CUDA graph. ---- */
+typedef struct mcu_decode_layer {
+    int kind_q, kind_k, kind_v, kind_o, kind_gate, kind_up, kind_down;
+    const void *wq, *wk, *wv, *wo, *gate, *up, *down;
+    const float *attn_norm, *ffn_norm;
+} mcu_decode_layer_t;
+typedef struct mcu_decode_plan_desc {
+    size_t n_layers, d, ffn, n_q_heads, n_kv_heads, head_dim, vocab;
+    float rms_eps, attn_scale;
+    int rope_type;
+    const mcu_decode_layer_t *layers; /* host array [n_layers] */
+    const float *out_norm;
+    int kind_output;
+    const void *output;
+    float *x0, *x1;                           /* residual stream, two buffers [d] */
+    float *q, *k, *v, *att, *proj, *gate, *up; /* scratch: [d], [kv], [kv], [d], [d], [ffn], [ffn] */
+    float *logits;                            /* [vocab] */
+    const uint32_t *token_meta;               /* [4] */
+    const uint32_t *block_table;
+    size_t max_blocks_per_seq;
+    void *kv_k, *kv_v;
+    int kv_dtype;
+    size_t block_size;
+    const float *rope_table; /* [head_dim / 2][2] */
+} mcu_decode_plan_desc_t;
+typedef struct mcu_decode_plan mcu_decode_plan_t;
+int mcu_decode_plan_create(mcu_context_t *ctx, const mcu_decode_plan_desc_t *desc, mcu_decode_plan_t **out_plan);
+int mcu_decode_plan_run(mcu_decode_plan_t *plan);
+void mcu_decode_plan_destroy(mcu_decode_plan_t *plan);
+
 /* ---- paged KV-cache pool: marmot_kv_pool_* (include/marmot/inference/kv_pool.h:65-101, implementation
  *      src/inference/kv_pool/kv_pool.cpp).  Same bookkeeping, decision for decision (slot and block order, reference
  *      counts and copy on write for shared prefixes, retained blocks, swap with the exchange path, error codes); the K

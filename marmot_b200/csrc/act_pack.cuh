@@ -4,6 +4,13 @@
 
 #include "common.cuh"
 
+// How the packers read activations (and the prologues' operands).  Read-only cache loads by default; a kernel that
+// reads what OTHER CTAs of the same launch wrote earlier (the persistent decode step) defines this as __ldcg before
+// including the header, because the non-coherent path may serve a line cached before the write.
+#ifndef MCU_ACT_LOAD
+#define MCU_ACT_LOAD(ptr) __ldg(ptr)
+#endif
+
 namespace mcu {
 
 // Q8_K packer, matmul_quant_pack.c:106-142 of the reference.  LPB lanes share one 256-value block, lane `sl` of the
@@ -20,12 +27,12 @@ __device__ __forceinline__ void load_values_q8_k(const float *row, int len, bool
     } else if (vec_ok && len == QK_K) {
 #pragma unroll
         for (int i = 0; i < NV / 4; ++i) {
-            const float4 a = __ldg((const float4 *)(row + NV * sl + 4 * i));
+            const float4 a = MCU_ACT_LOAD((const float4 *)(row + NV * sl + 4 * i));
             v[4 * i] = a.x, v[4 * i + 1] = a.y, v[4 * i + 2] = a.z, v[4 * i + 3] = a.w;
         }
     } else {
 #pragma unroll
-        for (int i = 0; i < NV; ++i) v[i] = NV * sl + i < len ? __ldg(row + NV * sl + i) : 0.0f;
+        for (int i = 0; i < NV; ++i) v[i] = NV * sl + i < len ? MCU_ACT_LOAD(row + NV * sl + i) : 0.0f;
     }
 }
 
@@ -97,11 +104,11 @@ __device__ __forceinline__ void load_values_q8_0(const float *row, int len, bool
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.0f;
     } else if (vec_ok && len == Q8_0_VALUES) {
-        const float4 a = __ldg((const float4 *)(row + 8 * sl)), b = __ldg((const float4 *)(row + 8 * sl + 4));
+        const float4 a = MCU_ACT_LOAD((const float4 *)(row + 8 * sl)), b = MCU_ACT_LOAD((const float4 *)(row + 8 * sl + 4));
         v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
     } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = 8 * sl + i < len ? __ldg(row + 8 * sl + i) : 0.0f;
+        for (int i = 0; i < 8; ++i) v[i] = 8 * sl + i < len ? MCU_ACT_LOAD(row + 8 * sl + i) : 0.0f;
     }
 }
 

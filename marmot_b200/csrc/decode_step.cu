@@ -1,0 +1,745 @@
+// One decode step of a Llama-family decoder (one token) as ONE persistent kernel.
+//
+// The five-launch layer (gemv_stream.cu with prologues, the decode attention of decoder.cu) is bound by what happens at
+// every kernel boundary: the weight stream drains, the next kernel's consumers wait for the previous grid to retire,
+// then load and pack their activations.  Here the CTAs stay resident for the whole step (cooperative launch, one CTA per
+// SM) and walk a table of PHASES -- per layer: q/k/v, attention, o projection, gate/up, down; at the end the output
+// projection -- separated by grid-wide barriers on a counter in global memory:
+//   * the producer thread of a CTA runs through the CTA's weight chunks of ALL phases in order, limited only by free
+//     ring slots, so HBM keeps streaming across the barriers and during the activation packing;
+//   * the consumer warps do per phase what the streaming GEMV does per launch (prologue + packing of the activations,
+//     row dots on the ring, stores), with the same device functions, hence the same bits;
+//   * attention for the single token runs on up to four warps per CTA, one 32-position tile of one KV head each, in f32
+//     on the f16 pool (scores with one position per lane, P V with two dimensions per lane), RoPE of q and of the new K
+//     row from the step's table, the new K / V rows appended by the warp that holds the token's own position; the last
+//     tile of a KV head to finish (ticket) merges the tiles in tile order.
+// Every wait is bounded: a barrier or ring wait that runs out sets the error flag and an abort word that all CTAs
+// poll, and the kernel returns.
+#define MCU_ACT_LOAD(ptr) __ldcg(ptr)  // activations are written by other CTAs of this same launch
+#include "gemv_stream_dev.cuh"
+
+#include "../../include/marmot_cuda.h"
+
+#include <cuda_fp16.h>
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+namespace mcu {
+
+constexpr int DS_TW = 15;                      // consumer warps
+constexpr int DS_THREADS = (DS_TW + 1) * 32;   // + the producer warp
+constexpr int DS_MAX_JOBS = 3;
+constexpr int DS_ATTN_WARPS = 4;
+constexpr int DS_CHUNK_BYTES = 20 * 1024;      // target size of a ring chunk
+constexpr int DS_STAGE_STRIDE = 21 * 1024;     // a chunk + over-read slack, multiple of 128
+constexpr int DS_STAGES = 7;
+constexpr int DS_ACT_BYTES = 20 * 1024;        // packed activations of one token: K up to 17408 values
+constexpr int DS_ATTN_SCRATCH = 10 * 128;      // floats per attention warp: 8 rotated query heads + the new K and V rows, head_dim <= 128
+constexpr uint32_t DS_SPIN_LIMIT = 1u << 22;
+
+enum { DS_PHASE_GEMV = 0, DS_PHASE_ATTN = 1 };
+
+struct DsJob {
+    const uint8_t *W;
+    float *out;
+    int F, kind, row_bytes, rows_per_cta, rows_per_chunk, cta_begin;
+};
+
+struct DsPhase {
+    int type;
+    int n_jobs;
+    DsJob job[DS_MAX_JOBS];
+    const float *x;  // activations of the token [K]
+    int K, nb;
+    GemvPrologue pro;
+    int layer;       // attention: which layer of the pool
+};
+
+struct DsParams {
+    const DsPhase *phases;
+    int n_phases;
+    uint32_t *sync;  // [0] arrivals of the grid barrier, [1] abort word, [2..] tickets of the attention (one per KV head)
+    int *err;
+    // attention
+    const uint32_t *meta;   // [4]: seq slot, position, kv slot, flags
+    const uint32_t *table;  // [seqs][max_blocks]
+    const float *q, *k_new, *v_new;
+    __half *kv_k, *kv_v;
+    const float2 *rope;     // [head_dim / 2] {cos, sin}
+    float *att;             // [n_q_heads * head_dim]
+    float *partial;         // [n_q_heads][max_tiles][head_dim + 2]
+    int n_q_heads, n_kv_heads, head_dim, max_blocks, n_layers, block_shift, max_tiles, neox;
+    float scale;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One thread per CTA: this CTA has finished phase `phase` (all its stores are done: the caller synchronised the CTA).
+__device__ __forceinline__ void grid_arrive(uint32_t *sync) {
+    __threadfence();
+    atomicAdd(sync, 1u);
+}
+// Bounded wait until every CTA has finished phase `phase`; false on abort.
+__device__ __forceinline__ bool grid_wait(const DsParams &p, int phase) {
+    const uint32_t want = (uint32_t)(phase + 1) * gridDim.x;
+    for (uint32_t i = 0; i < DS_SPIN_LIMIT; ++i) {
+        if (ld_acquire_gpu(p.sync) >= want) return true;
+        if ((i & 63u) == 63u && ld_acquire_gpu(p.sync + 1) != 0u) return false;
+        __nanosleep(20);
+    }
+    atomicExch(p.err, 31);
+    atomicExch(p.sync + 1, 1u);
+    return false;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Attention of the one token for KV head h, positions [k0, k0 + 32): by one warp.  s_q: this warp's scratch, rotated and
+// scaled query heads of the group [gsize][HD], then the new K and V rows [2][HD] when the tile holds the token's own
+// position.  Writes the tile's state {m, l, acc[HD]} per query head to `partial`.
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+__device__ __forceinline__ void attention_tile(const DsParams &p, int layer, int h, int tile, uint32_t kv_len, float *s_q) {
+    constexpr int HALF = HD / 2, DPL = HD / 32;  // dimensions per lane in the P V product
+    const int lane = threadIdx.x & 31;
+    const int gsize = p.n_q_heads / p.n_kv_heads;
+    const uint32_t k0 = (uint32_t)tile * 32u, new_pos = kv_len - 1u;
+    const size_t bs = (size_t)1 << p.block_shift;
+    const size_t s3 = HD, s2 = bs * s3, s1 = (size_t)p.n_kv_heads * s2, s0 = (size_t)p.n_layers * s1;
+    const size_t head_off = (size_t)layer * s1 + (size_t)h * s2;
+    float *s_kn = s_q + 8 * HD, *s_vn = s_kn + HD;
+    // rotated, scaled query heads
+    for (int idx = lane; idx < gsize * HALF; idx += 32) {
+        const int g = idx / HALF, i = idx - g * HALF;
+        const float2 cs = p.rope[i];
+        const int e = p.neox ? i : 2 * i, o = p.neox ? i + HALF : 2 * i + 1;
+        const float *row = p.q + (size_t)(h * gsize + g) * HD;
+        const float xe = __ldcg(row + e), xo = __ldcg(row + o);  // written by other CTAs in the previous phase
+        float re = __fsub_rn(__fmul_rn(xe, cs.x), __fmul_rn(xo, cs.y)), ro = __fadd_rn(__fmul_rn(xe, cs.y), __fmul_rn(xo, cs.x));
+        if (p.scale != 1.0f) {
+            re = __fmul_rn(re, p.scale);
+            ro = __fmul_rn(ro, p.scale);
+        }
+        s_q[g * HD + e] = re;
+        s_q[g * HD + o] = ro;
+    }
+    const bool has_new = new_pos >= k0 && new_pos < k0 + 32u;
+    if (has_new) {  // the token's own K (rotated) and V rows, rounded to f16 as the pool stores them, and into the pool
+        const uint32_t kv_slot = p.meta[2];
+        const size_t dst = (size_t)(kv_slot >> p.block_shift) * s0 + head_off + (size_t)(kv_slot & (uint32_t)(bs - 1)) * s3;
+        const float *krow = p.k_new + (size_t)h * HD, *vrow = p.v_new + (size_t)h * HD;
+        for (int i = lane; i < HALF; i += 32) {
+            const float2 cs = p.rope[i];
+            const int e = p.neox ? i : 2 * i, o = p.neox ? i + HALF : 2 * i + 1;
+            const float xe = __ldcg(krow + e), xo = __ldcg(krow + o);
+            const __half ke = __float2half_rn(__fsub_rn(__fmul_rn(xe, cs.x), __fmul_rn(xo, cs.y)));
+            const __half ko = __float2half_rn(__fadd_rn(__fmul_rn(xe, cs.y), __fmul_rn(xo, cs.x)));
+            p.kv_k[dst + e] = ke;
+            p.kv_k[dst + o] = ko;
+            s_kn[e] = __half2float(ke);
+            s_kn[o] = __half2float(ko);
+        }
+        for (int d = lane; d < HD; d += 32) {
+            const __half vv = __float2half_rn(__ldcg(vrow + d));
+            p.kv_v[dst + d] = vv;
+            s_vn[d] = __half2float(vv);
+        }
+    }
+    __syncwarp();
+    // scores: lane = position
+    const uint32_t pos = k0 + (uint32_t)lane;
+    const uint32_t seq = p.meta[0];
+    uint32_t tb = 0xFFFFFFFFu;
+    if (pos < kv_len && (pos >> p.block_shift) < (uint32_t)p.max_blocks) tb = p.table[(size_t)seq * p.max_blocks + (pos >> p.block_shift)];
+    const bool live = tb != 0xFFFFFFFFu;
+    const size_t row_base = live ? (size_t)tb * s0 + head_off + (size_t)(pos & (uint32_t)(bs - 1)) * s3 : 0;
+    float sc[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) sc[g] = 0.0f;
+    if (live) {
+        const bool mine_new = pos == new_pos;
+#pragma unroll 2
+        for (int c = 0; c < HD / 8; ++c) {
+            float kf[8];
+            if (mine_new) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) kf[j] = s_kn[8 * c + j];
+            } else {
+                const uint4 raw = *(const uint4 *)(p.kv_k + row_base + 8 * c);
+                const __half2 *h2 = (const __half2 *)&raw;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(h2[j]);
+                    kf[2 * j] = f.x, kf[2 * j + 1] = f.y;
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                if (g >= gsize) break;
+                const float4 qa = *(const float4 *)(s_q + g * HD + 8 * c), qb = *(const float4 *)(s_q + g * HD + 8 * c + 4);
+                sc[g] += qa.x * kf[0] + qa.y * kf[1] + qa.z * kf[2] + qa.w * kf[3] + qb.x * kf[4] + qb.y * kf[5] + qb.z * kf[6] +
+                    qb.w * kf[7];
+            }
+        }
+    }
+    // per head: tile maximum, weights, sum
+    float pw[8], mx[8], sum[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        float m = live ? sc[g] : -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float w = (live && m != -INFINITY) ? expf(sc[g] - m) : 0.0f;
+        float s = w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        pw[g] = w, mx[g] = m, sum[g] = s;
+    }
+    // O = P V: lane = DPL consecutive dimensions; positions in order
+    float acc[8][DPL];
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) acc[g][d] = 0.0f;
+    const uint32_t live_mask = __ballot_sync(0xffffffffu, live);
+    for (int r = 0; r < 32; ++r) {
+        if (!((live_mask >> r) & 1u)) continue;  // uniform
+        const unsigned long long rb = __shfl_sync(0xffffffffu, (unsigned long long)row_base, r);
+        float vf[DPL];
+        if (k0 + (uint32_t)r == new_pos) {
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) vf[d] = s_vn[lane * DPL + d];
+        } else if constexpr (DPL == 2) {
+            const float2 f = __half22float2(*(const __half2 *)(p.kv_v + rb + lane * 2));
+            vf[0] = f.x, vf[1] = f.y;
+        } else {
+            const uint2 raw = *(const uint2 *)(p.kv_v + rb + lane * 4);
+            const float2 a = __half22float2(*(const __half2 *)&raw.x), b = __half22float2(*(const __half2 *)&raw.y);
+            vf[0] = a.x, vf[1] = a.y, vf[2] = b.x, vf[3] = b.y;
+        }
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            if (g >= gsize) break;
+            const float w = __shfl_sync(0xffffffffu, pw[g], r);
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) acc[g][d] += w * vf[d];
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        if (g >= gsize) break;
+        float *pr = p.partial + ((size_t)(h * gsize + g) * p.max_tiles + tile) * (HD + 2);
+        if (lane == 0) {
+            pr[0] = mx[g];
+            pr[1] = sum[g];
+        }
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) pr[2 + lane * DPL + d] = acc[g][d];
+    }
+}
+
+// The tiles of KV head h merged in tile order into att (by one warp): the arithmetic of the attention merge kernel.
+template <int HD>
+__device__ __forceinline__ void attention_merge(const DsParams &p, int h, int n_tiles) {
+    constexpr int DPL = HD / 32;
+    const int lane = threadIdx.x & 31;
+    const int gsize = p.n_q_heads / p.n_kv_heads;
+    for (int g = 0; g < gsize; ++g) {
+        const int qh = h * gsize + g;
+        const float *pr = p.partial + (size_t)qh * p.max_tiles * (HD + 2);
+        float M = -INFINITY;
+        for (int c = 0; c < n_tiles; ++c) M = fmaxf(M, __ldcg(pr + (size_t)c * (HD + 2)));
+        float L = 0.0f, o[DPL];
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) o[d] = 0.0f;
+        if (M != -INFINITY) {
+            for (int c = 0; c < n_tiles; ++c) {
+                const float mc = __ldcg(pr + (size_t)c * (HD + 2));
+                if (mc == -INFINITY) continue;
+                const float e = expf(mc - M);
+                L += __ldcg(pr + (size_t)c * (HD + 2) + 1) * e;
+#pragma unroll
+                for (int d = 0; d < DPL; ++d) o[d] += __ldcg(pr + (size_t)c * (HD + 2) + 2 + lane * DPL + d) * e;
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) p.att[(size_t)qh * HD + lane * DPL + d] = L > 0.0f ? o[d] / L : 0.0f;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ const DsJob &job_of(const DsPhase &ph, int cta) {
+    int j = 0;
+    for (int i = 1; i < ph.n_jobs; ++i)
+        if (cta >= ph.job[i].cta_begin) j = i;
+    return ph.job[j];
+}
+
+__global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = (uint64_t *)smem;
+    uint64_t *empty = full + GS_MAX_STAGES;
+    float *inv_s = (float *)(smem + GS_RED_OFFSET);
+    float *red = inv_s + GEMV_MAX_T;
+    uint8_t *act_base = smem + GS_HEADER;
+    float *attn_scratch = (float *)(act_base + DS_ACT_BYTES);  // [DS_ATTN_WARPS][DS_ATTN_SCRATCH]
+    uint8_t *stage_base = (uint8_t *)(attn_scratch + DS_ATTN_WARPS * DS_ATTN_SCRATCH);
+    constexpr int S = DS_STAGES;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, cta = blockIdx.x;
+    (void)inv_s;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], DS_TW);  // every consumer warp releases every chunk
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == DS_TW) {
+        // ---------------- producer: the weight chunks of all phases, in order ----------------
+        if (lane == 0) {
+            int cbase = 0;
+            for (int ph_i = 0; ph_i < p.n_phases; ++ph_i) {
+                const DsPhase &ph = p.phases[ph_i];
+                if (ph.type != DS_PHASE_GEMV) continue;
+                const DsJob &job = job_of(ph, cta);
+                const int r0 = (cta - job.cta_begin) * job.rows_per_cta;
+                const int n_rows = max(0, min(job.F, r0 + job.rows_per_cta) - r0);
+                const int RC = job.rows_per_chunk, n_chunks = (n_rows + RC - 1) / RC;
+                for (int c = 0; c < n_chunks; ++c) {
+                    const int gc = cbase + c, st = gc % S, round = gc / S;
+                    if (round > 0 && !mbar_wait(&empty[st], (uint32_t)((round - 1) & 1))) {
+                        atomicExch(p.err, 32);
+                        atomicExch(p.sync + 1, 1u);
+                        return;
+                    }
+                    const int rows = min(RC, n_rows - c * RC);
+                    const uint32_t bytes = (uint32_t)rows * (uint32_t)job.row_bytes;
+                    mbar_expect_tx(&full[st], bytes);
+                    bulk_g2s(stage_base + (size_t)st * DS_STAGE_STRIDE, job.W + ((size_t)r0 + (size_t)c * RC) * job.row_bytes, bytes,
+                             &full[st]);
+                }
+                cbase += n_chunks;
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    constexpr int NTH = DS_TW * 32;
+    int cbase = 0;
+    bool ok = true;
+    for (int ph_i = 0; ph_i < p.n_phases && ok; ++ph_i) {
+        const DsPhase &ph = p.phases[ph_i];
+        if (ph_i > 0) {  // the previous phase's results, from every CTA
+            if (threadIdx.x == 0) red[0] = grid_wait(p, ph_i - 1) ? 1.0f : 0.0f;
+            asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
+            ok = red[0] != 0.0f;
+            asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
+            if (!ok) break;
+        }
+        if (ph.type == DS_PHASE_ATTN) {
+            const uint32_t kv_len = p.meta[1] + 1u;
+            const int n_tiles = min(p.max_tiles, (int)((kv_len + 31u) / 32u));
+            if (warp < DS_ATTN_WARPS) {
+                float *scratch = attn_scratch + warp * DS_ATTN_SCRATCH;
+                for (int item = cta * DS_ATTN_WARPS + warp; item < p.n_kv_heads * n_tiles; item += (int)gridDim.x * DS_ATTN_WARPS) {
+                    const int h = item / n_tiles, tile = item - h * n_tiles;
+                    if (p.head_dim == 64) attention_tile<64>(p, ph.layer, h, tile, kv_len, scratch);
+                    else attention_tile<128>(p, ph.layer, h, tile, kv_len, scratch);
+                    __threadfence();
+                    __syncwarp();
+                    uint32_t drawn = 0;
+                    if (lane == 0) drawn = atomicAdd(p.sync + 2 + h, 1u);
+                    drawn = __shfl_sync(0xffffffffu, drawn, 0);
+                    if (drawn == (uint32_t)n_tiles - 1u) {  // the head's last tile: merge, and leave the ticket at zero
+                        if (lane == 0) p.sync[2 + h] = 0u;
+                        __threadfence();
+                        if (p.head_dim == 64) attention_merge<64>(p, h, n_tiles);
+                        else attention_merge<128>(p, h, n_tiles);
+                    }
+                    __syncwarp();
+                }
+            }
+        } else {
+            const DsJob &job = job_of(ph, cta);
+            const int kind = job.kind;
+            const int r0 = (cta - job.cta_begin) * job.rows_per_cta;
+            const int n_rows = max(0, min(job.F, r0 + job.rows_per_cta) - r0);
+            const int RC = job.rows_per_chunk, n_chunks = (n_rows + RC - 1) / RC;
+            const ActSmem a = act_layout<true>(act_base, 1, ph.nb);
+            // the activations, through the phase's prologue
+            const ProArgs pa{ph.x, ph.K, ph.K, ph.nb, ph.pro};
+            if (ph.pro.op == GEMV_PRO_ADD_RMSNORM) {
+                if (ph.nb <= DS_TW) quantize_q8_k_addnorm_once<32, NTH>(pa, 1, a, threadIdx.x, red);
+                else quantize_q8_k_addnorm_once<16, NTH>(pa, 1, a, threadIdx.x, red);
+            } else if (ph.pro.op == GEMV_PRO_SWIGLU) {
+                if (ph.nb <= DS_TW) quantize_all_q8_k_pro<32, GEMV_PRO_SWIGLU>(pa, 1, a, threadIdx.x, NTH, inv_s);
+                else quantize_all_q8_k_pro<16, GEMV_PRO_SWIGLU>(pa, 1, a, threadIdx.x, NTH, inv_s);
+            } else {
+                if (ph.nb <= DS_TW) quantize_all_q8_k<32>(ph.x, ph.K, 1, ph.K, ph.nb, a, threadIdx.x, NTH);
+                else quantize_all_q8_k<16>(ph.x, ph.K, 1, ph.K, ph.nb, a, threadIdx.x, NTH);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
+            if (kind == KIND_Q4_K) {
+                // two rows per warp: chunks in pairs
+                for (int jp = 0; 2 * jp < n_chunks; ++jp) {
+                    const int c0 = 2 * jp, c1 = c0 + 1;
+                    const bool two = c1 < n_chunks;
+                    const int g0 = cbase + c0, g1 = cbase + c1;
+                    bool ready = mbar_wait(&full[g0 % S], (uint32_t)((g0 / S) & 1));
+                    if (ready && two) ready = mbar_wait(&full[g1 % S], (uint32_t)((g1 / S) & 1));
+                    if (!ready) {
+                        if (lane == 0) {
+                            atomicExch(p.err, 33);
+                            atomicExch(p.sync + 1, 1u);
+                        }
+                        break;  // the abort word is set: every warp leaves after the barrier below
+                    }
+                    const int rows0 = min(RC, n_rows - c0 * RC), rows1 = two ? min(RC, n_rows - c1 * RC) : 0;
+                    const int rl0 = (warp - (c0 * RC) % DS_TW + DS_TW) % DS_TW, rl1 = (warp - (c1 * RC) % DS_TW + DS_TW) % DS_TW;
+                    const bool v0 = rl0 < rows0, v1 = rl1 < rows1;
+                    if (v0 || v1) {
+                        const uint8_t *wa = stage_base + (size_t)(g0 % S) * DS_STAGE_STRIDE + (size_t)rl0 * job.row_bytes;
+                        const uint8_t *wb = stage_base + (size_t)(g1 % S) * DS_STAGE_STRIDE + (size_t)rl1 * job.row_bytes;
+                        if (!v0) wa = wb;
+                        if (!v1) wb = wa;
+                        float mine[1] = {0.0f};
+                        rows2_q4_k<1>(wa, wb, a, ph.nb, lane, mine);
+                        float v = mine[0];
+                        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+                        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+                        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 8));
+                        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 16));
+                        const int f = lane == 0 ? r0 + c0 * RC + rl0 : r0 + c1 * RC + rl1;
+                        if (lane == 0 ? v0 : (lane == 1 && v1)) job.out[f] = v;
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&empty[g0 % S]);
+                        if (two) mbar_arrive(&empty[g1 % S]);
+                    }
+                }
+            } else {
+                for (int c = 0; c < n_chunks; ++c) {
+                    const int gc = cbase + c, st = gc % S;
+                    if (!mbar_wait(&full[st], (uint32_t)((gc / S) & 1))) {
+                        if (lane == 0) {
+                            atomicExch(p.err, 33);
+                            atomicExch(p.sync + 1, 1u);
+                        }
+                        break;
+                    }
+                    const int rows = min(RC, n_rows - c * RC);
+                    const int rl = (warp - (c * RC) % DS_TW + DS_TW) % DS_TW;
+                    if (rl < rows) {
+                        float acc[1] = {0.0f};
+                        row_q6_k<1>(stage_base + (size_t)st * DS_STAGE_STRIDE + (size_t)rl * job.row_bytes, a, ph.nb, lane, acc);
+                        const float v = warp_sum(acc[0]);
+                        if (lane == 0) job.out[r0 + c * RC + rl] = v;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[st]);
+                }
+            }
+            cbase += n_chunks;
+        }
+        // this CTA is through the phase (or one of its warps gave up: then all leave together)
+        asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
+        if (ld_acquire_gpu(p.sync + 1) != 0u) {
+            ok = false;
+            break;
+        }
+        if (threadIdx.x == 0) grid_arrive(p.sync);
+    }
+    // CTA 0 waits for everybody's last arrival and leaves the counter at zero for the next launch (nobody else waits on
+    // it any more)
+    if (threadIdx.x == 0 && cta == 0 && ok && grid_wait(p, p.n_phases - 1)) {
+        p.sync[0] = 0u;
+        __threadfence();
+    }
+}
+
+}  // namespace mcu
+
+// ---------------------------------------------------------------------------------------------
+// Host side: the plan (phase table on the device) and its launch
+// ---------------------------------------------------------------------------------------------
+using namespace mcu;
+
+struct mcu_decode_plan {
+    mcu_context_t *ctx = nullptr;
+    DsParams params{};
+    DsPhase *phases_dev = nullptr;
+    uint32_t *sync_dev = nullptr;
+    float *partial_dev = nullptr;
+    int grid = 0, smem = 0;
+};
+
+#define DS_CUDA(expr)                                                                   \
+    do {                                                                                \
+        cudaError_t e__ = (expr);                                                       \
+        if (e__ != cudaSuccess) {                                                       \
+            char msg__[256];                                                            \
+            snprintf(msg__, sizeof(msg__), "%s: %s", #expr, cudaGetErrorString(e__));   \
+            return set_error(MCU_ERROR_INVALID_OPERATION, msg__);                       \
+        }                                                                               \
+    } while (0)
+
+static int ds_gcd(int a, int b) { return b == 0 ? a : ds_gcd(b, a % b); }
+
+// One matmul phase: the CTAs dealt to its jobs in proportion to their bytes, chunk sizes chosen for the ring.
+static int ds_gemv_phase(DsPhase &ph, int sms, const float *x, int K, const GemvPrologue &pro, int n_jobs, const int *kinds,
+                         const void *const *W, const int *F, float *const *out) {
+    ph = DsPhase{};
+    ph.type = DS_PHASE_GEMV;
+    ph.n_jobs = n_jobs;
+    ph.x = x;
+    ph.K = K;
+    ph.nb = (K + QK_K - 1) / QK_K;
+    ph.pro = pro;
+    if (act_smem_bytes(true, 1, ph.nb) > DS_ACT_BYTES) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "decode plan: rows too long");
+    if (pro.op == GEMV_PRO_ADD_RMSNORM && ph.nb > 2 * DS_TW) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "decode plan: hidden size too large");
+    double bytes[DS_MAX_JOBS], total = 0.0;
+    int unit[DS_MAX_JOBS], rb[DS_MAX_JOBS];
+    for (int j = 0; j < n_jobs; ++j) {
+        if (kinds[j] != KIND_Q4_K && kinds[j] != KIND_Q6_K) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "decode plan: Q4_K / Q6_K weights only");
+        if (((uintptr_t)W[j] & 15) || F[j] < 1) return set_error(MCU_ERROR_INVALID_ARGUMENT, "decode plan: weights must be 16-byte aligned");
+        rb[j] = ph.nb * block_bytes(kinds[j]);
+        unit[j] = 16 / ds_gcd(rb[j] % 16, 16);
+        if (((long)F[j] * rb[j]) & 15) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "decode plan: weight matrix is not a whole number of 16-byte pieces");
+        if ((long)unit[j] * rb[j] > DS_CHUNK_BYTES || unit[j] > DS_TW) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "decode plan: rows too long for the ring");
+        bytes[j] = (double)F[j] * rb[j];
+        total += bytes[j];
+    }
+    if (sms < n_jobs) return set_error(MCU_ERROR_INVALID_OPERATION, "decode plan: fewer SMs than weight matrices");
+    int ctas[DS_MAX_JOBS], given = 0;
+    for (int j = 0; j < n_jobs; ++j) {
+        ctas[j] = (int)((double)sms * bytes[j] / total);
+        if (ctas[j] < 1) ctas[j] = 1;
+        given += ctas[j];
+    }
+    while (given != sms) {  // hand out what rounding left (or take back), largest share per CTA first
+        int best = -1;
+        double best_v = 0.0;
+        for (int j = 0; j < n_jobs; ++j) {
+            if (given > sms && ctas[j] <= 1) continue;
+            const double per = bytes[j] / ctas[j], v = given < sms ? per : -per;
+            if (best < 0 || v > best_v) best = j, best_v = v;
+        }
+        if (best < 0) return set_error(MCU_ERROR_INVALID_OPERATION, "decode plan: cannot deal the CTAs");
+        ctas[best] += given < sms ? 1 : -1;
+        given += given < sms ? 1 : -1;
+    }
+    int begin = 0;
+    for (int j = 0; j < n_jobs; ++j) {
+        DsJob &g = ph.job[j];
+        g.W = (const uint8_t *)W[j];
+        g.out = out[j];
+        g.F = F[j];
+        g.kind = kinds[j];
+        g.row_bytes = rb[j];
+        int rpc = (F[j] + ctas[j] - 1) / ctas[j];
+        g.rows_per_cta = (rpc + unit[j] - 1) / unit[j] * unit[j];
+        int rc = DS_CHUNK_BYTES / rb[j];
+        if (rc > DS_TW) rc = DS_TW;
+        rc = rc / unit[j] * unit[j];
+        g.rows_per_chunk = rc;
+        g.cta_begin = begin;
+        begin += ctas[j];  // every CTA of the grid belongs to a job, also those whose row range is empty
+    }
+    return MCU_SUCCESS;
+}
+
+extern "C" {
+
+int mcu_decode_plan_create(mcu_context_t *ctx, const mcu_decode_plan_desc_t *d, mcu_decode_plan_t **out) {
+    if (out == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    if (ctx == nullptr) return set_error(MCU_ERROR_DEVICE_NOT_AVAILABLE, "CUDA context is not initialised");
+    if (d == nullptr || d->layers == nullptr || d->n_layers == 0) return set_error(MCU_ERROR_INVALID_ARGUMENT, "decode plan: empty description");
+    const void *ptrs[] = {d->x0, d->x1, d->q, d->k, d->v, d->att, d->proj, d->gate, d->up, d->logits, d->token_meta, d->block_table,
+                          d->kv_k, d->kv_v, d->rope_table, d->out_norm, d->output};
+    for (const void *p : ptrs)
+        if (p == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "decode plan: a buffer is missing");
+    if (d->head_dim != 64 && d->head_dim != 128) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "decode plan: head_dim 64 or 128");
+    if (d->n_kv_heads == 0 || d->n_q_heads % d->n_kv_heads != 0 || d->n_q_heads / d->n_kv_heads > 8)
+        return set_error(MCU_ERROR_NOT_IMPLEMENTED, "decode plan: up to 8 query heads per KV head");
+    if (d->kv_dtype != MCU_KV_F16) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "decode plan: float16 KV pool");
+    if (d->block_size == 0 || (d->block_size & (d->block_size - 1)) != 0) return set_error(MCU_ERROR_INVALID_ARGUMENT, "decode plan: block_size must be a power of two");
+    if (d->n_q_heads * d->head_dim != d->d || d->ffn == 0) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "decode plan: heads * head_dim must equal the hidden size");
+    if (((uintptr_t)d->kv_k | (uintptr_t)d->kv_v | (uintptr_t)d->rope_table) & 15) return set_error(MCU_ERROR_INVALID_ARGUMENT, "decode plan: pools and RoPE table must be 16-byte aligned");
+    DS_CUDA(cudaSetDevice(context_device(ctx)));
+    const int sms = device_sm_count();
+    const int L = (int)d->n_layers, D = (int)d->d, FF = (int)d->ffn, HKV = (int)(d->n_kv_heads * d->head_dim);
+    std::vector<DsPhase> phases;
+    phases.reserve(5 * (size_t)L + 1);
+    float *xs[2] = {d->x0, d->x1};
+    int cur = 0;
+    const float *pending = nullptr;
+    auto add_norm = [&](const float *norm_w, bool store) {
+        GemvPrologue g;
+        g.op = GEMV_PRO_ADD_RMSNORM;
+        g.aux = pending;
+        g.ld_aux = D;
+        g.norm_w = norm_w;
+        g.eps = d->rms_eps;
+        g.w_off = 0.0f;
+        g.x_out = store && pending != nullptr ? xs[1 - cur] : nullptr;
+        g.ld_x_out = D;
+        return g;
+    };
+    for (int i = 0; i < L; ++i) {
+        const mcu_decode_layer_t &lw = d->layers[i];
+        {
+            DsPhase ph;
+            const int kinds[3] = {lw.kind_q, lw.kind_k, lw.kind_v};
+            const void *W[3] = {lw.wq, lw.wk, lw.wv};
+            const int F[3] = {D, HKV, HKV};
+            float *o[3] = {d->q, d->k, d->v};
+            const GemvPrologue g = add_norm(lw.attn_norm, true);
+            if (int rc = ds_gemv_phase(ph, sms, xs[cur], D, g, 3, kinds, W, F, o)) return rc;
+            phases.push_back(ph);
+            if (pending != nullptr) cur = 1 - cur;
+        }
+        {
+            DsPhase ph{};
+            ph.type = DS_PHASE_ATTN;
+            ph.layer = i;
+            phases.push_back(ph);
+        }
+        {
+            DsPhase ph;
+            const int kinds[1] = {lw.kind_o};
+            const void *W[1] = {lw.wo};
+            const int F[1] = {D};
+            float *o[1] = {d->proj};
+            if (int rc = ds_gemv_phase(ph, sms, d->att, D, GemvPrologue{}, 1, kinds, W, F, o)) return rc;
+            phases.push_back(ph);
+            pending = d->proj;
+        }
+        {
+            DsPhase ph;
+            const int kinds[2] = {lw.kind_gate, lw.kind_up};
+            const void *W[2] = {lw.gate, lw.up};
+            const int F[2] = {FF, FF};
+            float *o[2] = {d->gate, d->up};
+            const GemvPrologue g = add_norm(lw.ffn_norm, true);
+            if (int rc = ds_gemv_phase(ph, sms, xs[cur], D, g, 2, kinds, W, F, o)) return rc;
+            phases.push_back(ph);
+            cur = 1 - cur;
+        }
+        {
+            DsPhase ph;
+            const int kinds[1] = {lw.kind_down};
+            const void *W[1] = {lw.down};
+            const int F[1] = {D};
+            float *o[1] = {d->proj};
+            GemvPrologue g;
+            g.op = GEMV_PRO_SWIGLU;
+            g.aux = d->up;
+            g.ld_aux = FF;
+            if (int rc = ds_gemv_phase(ph, sms, d->gate, FF, g, 1, kinds, W, F, o)) return rc;
+            phases.push_back(ph);
+            pending = d->proj;
+        }
+    }
+    {
+        DsPhase ph;
+        const int kinds[1] = {d->kind_output};
+        const void *W[1] = {d->output};
+        const int F[1] = {(int)d->vocab};
+        float *o[1] = {d->logits};
+        const GemvPrologue g = add_norm(d->out_norm, false);
+        if (int rc = ds_gemv_phase(ph, sms, xs[cur], D, g, 1, kinds, W, F, o)) return rc;
+        phases.push_back(ph);
+    }
+    mcu_decode_plan *pl = new (std::nothrow) mcu_decode_plan;
+    if (pl == nullptr) return set_error(MCU_ERROR_OUT_OF_MEMORY, "decode plan allocation failed");
+    pl->ctx = ctx;
+    pl->grid = sms;
+    pl->smem = GS_HEADER + DS_ACT_BYTES + DS_ATTN_WARPS * DS_ATTN_SCRATCH * (int)sizeof(float) + DS_STAGES * DS_STAGE_STRIDE;
+    const size_t max_positions = d->max_blocks_per_seq * d->block_size;
+    const int max_tiles = (int)((max_positions + 31) / 32);
+    const size_t sync_words = 2 + d->n_kv_heads;
+    cudaError_t e = cudaMalloc((void **)&pl->phases_dev, phases.size() * sizeof(DsPhase));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->sync_dev, sync_words * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->partial_dev, d->n_q_heads * (size_t)max_tiles * (d->head_dim + 2) * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemcpy(pl->phases_dev, phases.data(), phases.size() * sizeof(DsPhase), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemset(pl->sync_dev, 0, sync_words * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pl->smem);
+    int per_sm = 0;
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel, DS_THREADS, pl->smem);
+    if (e != cudaSuccess || per_sm < 1) {
+        const int rc = set_error(MCU_ERROR_INVALID_OPERATION, e != cudaSuccess ? cudaGetErrorString(e) : "decode step kernel does not fit an SM");
+        mcu_decode_plan_destroy(pl);
+        return rc;
+    }
+    DsParams &p = pl->params;
+    p.phases = pl->phases_dev;
+    p.n_phases = (int)phases.size();
+    p.sync = pl->sync_dev;
+    p.err = context_err_flag(ctx);
+    p.meta = d->token_meta;
+    p.table = d->block_table;
+    p.q = d->q;
+    p.k_new = d->k;
+    p.v_new = d->v;
+    p.kv_k = (__half *)d->kv_k;
+    p.kv_v = (__half *)d->kv_v;
+    p.rope = (const float2 *)d->rope_table;
+    p.att = d->att;
+    p.partial = pl->partial_dev;
+    p.n_q_heads = (int)d->n_q_heads;
+    p.n_kv_heads = (int)d->n_kv_heads;
+    p.head_dim = (int)d->head_dim;
+    p.max_blocks = (int)d->max_blocks_per_seq;
+    p.n_layers = (int)d->n_layers;
+    p.block_shift = 0;
+    while (((size_t)1 << p.block_shift) < d->block_size) ++p.block_shift;
+    p.max_tiles = max_tiles;
+    p.neox = d->rope_type == MCU_ROPE_NEOX ? 1 : 0;
+    p.scale = d->attn_scale;
+    *out = pl;
+    return MCU_SUCCESS;
+}
+
+int mcu_decode_plan_run(mcu_decode_plan_t *pl) {
+    if (pl == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "null plan");
+    DS_CUDA(cudaSetDevice(context_device(pl->ctx)));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)pl->grid, 1, 1);
+    cfg.blockDim = dim3(DS_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)pl->smem;
+    cfg.stream = (cudaStream_t)mcu_context_get_stream(pl->ctx);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident at once: they wait on one another
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DS_CUDA(cudaLaunchKernelEx(&cfg, decode_step_kernel, pl->params));
+    count_launches(1);
+    return MCU_SUCCESS;
+}
+
+void mcu_decode_plan_destroy(mcu_decode_plan_t *pl) {
+    if (pl == nullptr) return;
+    cudaSetDevice(context_device(pl->ctx));
+    cudaStreamSynchronize((cudaStream_t)mcu_context_get_stream(pl->ctx));
+    if (pl->phases_dev != nullptr) cudaFree(pl->phases_dev);
+    if (pl->sync_dev != nullptr) cudaFree(pl->sync_dev);
+    if (pl->partial_dev != nullptr) cudaFree(pl->partial_dev);
+    delete pl;
+}
+
+}  // extern "C"

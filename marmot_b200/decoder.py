@@ -172,6 +172,7 @@ class Decoder:
             table = np.arange(n_blocks, dtype=np.uint32).reshape(max_seqs, self.max_blocks)
             self.block_table = torch.from_numpy(table).to(dev)
         self._bufs = {}
+        self._plans = {}  # one-token step plans (persistent kernel), per set of caller tensors
         self._side = None
 
     def _side_contexts(self):
@@ -323,12 +324,68 @@ class Decoder:
         ctx.linear(kd["output"], h, self.output, self.local_vocab, out=logits)
         return logits
 
+    def _one_token_plan(self, meta, positions, logits):
+        """The persistent-kernel plan for a one-token step on these very tensors (mcu_decode_plan), or None when the
+        model does not suit it (formats other than Q4_K / Q6_K, float32 pool, ...).  Plans are kept per tensor set."""
+        import ctypes as C
+
+        from .runtime import DecodeLayer, DecodePlan, DecodePlanDesc, MarmotCudaError, _ptr
+
+        if os.environ.get("MARMOT_DECODER_NO_STEP_KERNEL"):  # diagnostic switch: the five-launch layer instead
+            return None
+        key = (meta.data_ptr(), positions.data_ptr(), logits.data_ptr())
+        if key in self._plans:
+            return self._plans[key]
+        s, kd = self.local, self.kinds
+        hq, hkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
+        plan = None
+        if self.kv_k.dtype == self.torch.float16 and s.ffn > 0 and hq * hd == s.d:
+            L = len(self.layers)
+            layers = (DecodeLayer * L)()
+            for i, (slot, lw) in enumerate(zip(layers, self.layers)):
+                for name in ("q", "k", "v", "o"):
+                    setattr(slot, f"kind_{name}", kd[f"l{i}.w{name}"])
+                    setattr(slot, f"w{name}", _ptr(lw[f"w{name}"]))
+                for name in ("gate", "up", "down"):
+                    setattr(slot, f"kind_{name}", kd[f"l{i}.{name}"])
+                    setattr(slot, name, _ptr(lw[name]))
+                slot.attn_norm, slot.ffn_norm = _ptr(lw["attn_norm"]), _ptr(lw["ffn_norm"])
+            buf = lambda name, n: self._buf(name, (1, n))
+            rope = self._buf("rope", (1, hd // 2, 2))
+            d = DecodePlanDesc()
+            d.n_layers, d.d, d.ffn, d.n_q_heads, d.n_kv_heads, d.head_dim, d.vocab = L, s.d, s.ffn, hq, hkv, hd, self.local_vocab
+            d.rms_eps, d.attn_scale, d.rope_type = s.rms_eps, float(hd) ** -0.5, 0
+            d.layers, d.out_norm, d.kind_output, d.output = layers, _ptr(self.out_norm), kd["output"], _ptr(self.output)
+            d.x0, d.x1 = _ptr(buf("x", s.d)), _ptr(buf("x2", s.d))
+            d.q, d.k, d.v = _ptr(buf("q", hq * hd)), _ptr(buf("k", hkv * hd)), _ptr(buf("v", hkv * hd))
+            d.att, d.proj = _ptr(buf("att", hq * hd)), _ptr(buf("proj", s.d))
+            d.gate, d.up, d.logits = _ptr(buf("gate", s.ffn)), _ptr(buf("up", s.ffn)), _ptr(logits)
+            d.token_meta, d.block_table, d.max_blocks_per_seq = _ptr(meta), _ptr(self.block_table), self.block_table.shape[1]
+            d.kv_k, d.kv_v, d.kv_dtype, d.block_size, d.rope_table = _ptr(self.kv_k), _ptr(self.kv_v), 1, self.block_size, _ptr(rope)
+            try:
+                plan = DecodePlan(self.ctx, d, keep=(layers, meta, positions, logits))
+            except MarmotCudaError as exc:
+                if exc.code != -8:  # NOT_IMPLEMENTED: this model takes the five-launch layer
+                    raise
+        self._plans[key] = plan
+        return plan
+
     def _step_fused(self, ids, meta, positions, logits_out):
-        """The decode step with every elementwise operator folded into its consumer (see step).  The residual stream
-        alternates between two buffers: a prologue reads x and the pending projection and stores their sum to the other
-        buffer (the CTAs of one launch all read x, so the sum cannot go back in place)."""
+        """The decode step with every elementwise operator folded into its consumer (see step).  One token: a single
+        persistent kernel walks all layers (mcu_decode_plan; embedding gather and RoPE table before it).  Otherwise five
+        launches per layer; the residual stream alternates between two buffers: a prologue reads x and the pending
+        projection and stores their sum to the other buffer (the CTAs of one launch all read x, so the sum cannot go
+        back in place)."""
         ctx, s = self.ctx, self.local
         T = ids.shape[0]
+        if T == 1:
+            logits = logits_out if logits_out is not None else self._buf("logits", (1, self.local_vocab))
+            plan = self._one_token_plan(meta, positions, logits)
+            if plan is not None:
+                ctx.embedding_gather(self.kinds["tok_embd"], self.tok_embd, s.d, ids, out=self._buf("x", (1, s.d)))
+                ctx.rope_table(positions, s.head_dim, s.rope_theta, out=self._buf("rope", (1, s.head_dim // 2, 2)))
+                plan.run()
+                return logits
         hq, hkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
         kd = self.kinds
         xs = [self._buf("x", (T, s.d)), self._buf("x2", (T, s.d))]

@@ -27,7 +27,8 @@ EXPORTS = (
     "mcu_linear_static_scratch", "mcu_moe_experts_local", "mcu_moe_experts_ep", "mcu_peer_moe_combine", "mcu_peer_comm_capacity", "mcu_peer_comm_rank", "mcu_peer_comm_world", "mcu_moe_last_buffers", "mcu_peer_comm_create", "mcu_peer_comm_export",
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
     "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_peer_comm_set_one_slot", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
-    "mcu_embedding_gather", "mcu_paged_attention", "mcu_paged_attention_decode", "mcu_rope_table", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps", "mcu_vec_dot_host",
+    "mcu_embedding_gather", "mcu_paged_attention", "mcu_paged_attention_decode", "mcu_rope_table", "mcu_decode_plan_create", "mcu_decode_plan_run",
+    "mcu_decode_plan_destroy", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps", "mcu_vec_dot_host",
     "mcu_kv_pool_options_init", "mcu_kv_pool_create", "mcu_kv_pool_destroy", "mcu_kv_pool_acquire_seq",
     "mcu_kv_pool_release_seq", "mcu_kv_pool_prepare_append", "mcu_kv_pool_commit_append", "mcu_kv_pool_abort_append",
     "mcu_kv_pool_prepare_prefix_attach", "mcu_kv_pool_commit_prefix_attach", "mcu_kv_pool_abort_prefix_attach",
@@ -53,6 +54,42 @@ class Prologue(C.Structure):
     """mcu_prologue_t"""
     _fields_ = [("op", C.c_int), ("aux_dev", C.c_void_p), ("ld_aux", C.c_size_t), ("norm_weight_dev", C.c_void_p),
                 ("eps", C.c_float), ("weight_offset", C.c_float), ("x_out_dev", C.c_void_p), ("ld_x_out", C.c_size_t)]
+
+
+class DecodeLayer(C.Structure):
+    """mcu_decode_layer_t"""
+    _fields_ = [(n, C.c_int) for n in ("kind_q", "kind_k", "kind_v", "kind_o", "kind_gate", "kind_up", "kind_down")] + \
+               [(n, C.c_void_p) for n in ("wq", "wk", "wv", "wo", "gate", "up", "down", "attn_norm", "ffn_norm")]
+
+
+class DecodePlanDesc(C.Structure):
+    """mcu_decode_plan_desc_t"""
+    _fields_ = [(n, C.c_size_t) for n in ("n_layers", "d", "ffn", "n_q_heads", "n_kv_heads", "head_dim", "vocab")] + \
+               [("rms_eps", C.c_float), ("attn_scale", C.c_float), ("rope_type", C.c_int), ("layers", C.POINTER(DecodeLayer)),
+                ("out_norm", C.c_void_p), ("kind_output", C.c_int), ("output", C.c_void_p)] + \
+               [(n, C.c_void_p) for n in ("x0", "x1", "q", "k", "v", "att", "proj", "gate", "up", "logits", "token_meta",
+                                          "block_table")] + \
+               [("max_blocks_per_seq", C.c_size_t), ("kv_k", C.c_void_p), ("kv_v", C.c_void_p), ("kv_dtype", C.c_int),
+                ("block_size", C.c_size_t), ("rope_table", C.c_void_p)]
+
+
+class DecodePlan:
+    """mcu_decode_plan: one decode step of one token as a single persistent kernel; every pointer is fixed at creation
+    (the tensors named in the description must stay alive and in place)."""
+
+    def __init__(self, ctx: "Context", desc: DecodePlanDesc, keep):
+        self.ctx, self._keep = ctx, keep
+        h = C.c_void_p()
+        ctx._check(ctx.lib.mcu_decode_plan_create(ctx.handle, C.byref(desc), C.byref(h)))
+        self.handle = h
+
+    def run(self):
+        self.ctx._check(self.ctx.lib.mcu_decode_plan_run(self.handle))
+
+    def close(self):
+        if self.handle:
+            self.ctx.lib.mcu_decode_plan_destroy(self.handle)
+            self.handle = None
 
 
 class MarmotCudaError(RuntimeError):
@@ -138,6 +175,10 @@ def load_library() -> C.CDLL:
     L.mcu_paged_attention_decode.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, i32, vp, sz, sz, sz, sz, sz, sz, sz, f32, vp, f32,
                                              f32, i32, vp, vp]
     L.mcu_rope_table.argtypes = [vp, vp, sz, sz, f32, f32, vp]
+    L.mcu_decode_plan_create.argtypes = [vp, vp, C.POINTER(vp)]
+    L.mcu_decode_plan_run.argtypes = [vp]
+    L.mcu_decode_plan_destroy.argtypes = [vp]
+    L.mcu_decode_plan_destroy.restype = None
     _lib = L
     return L
 

@@ -37,7 +37,8 @@ def make_weights(rng):
 @pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("prompt_len,kv_dtype", [(5, torch.float32), (5, torch.float16), (12, torch.float16)])
 def test_prefill_then_greedy_decode(oracle, prompt_len, kv_dtype, fused):
-    """fused: the decode steps run in their five-launches-per-layer form (Decoder.step(decode=True))."""
+    """fused: the decode steps run as Decoder.step(decode=True): one persistent kernel per one-token step on a float16
+    pool (five launches per layer otherwise)."""
     rng = np.random.default_rng(prompt_len)
     weights = make_weights(rng)
     ctx = Context(0)
@@ -58,7 +59,7 @@ def test_prefill_then_greedy_decode(oracle, prompt_len, kv_dtype, fused):
         got = dec.step(torch.from_numpy(ids).cuda(), torch.from_numpy(meta).cuda(), torch.from_numpy(pos).cuda(),
                        decode=fused and step > 0)
         if fused and step > 0 and kv_dtype == torch.float16:
-            assert ctx.launch_count() - l0 == 3 + 5 * SHAPE.layers  # embedding, RoPE table, five per layer, output projection
+            assert ctx.launch_count() - l0 == 3  # embedding gather, RoPE table, the persistent step kernel
         got = got.cpu().numpy()
         want = oracle_step(oracle, SHAPE, weights, ids, meta, pos, kv_k, kv_v, table, 16)
         assert cosine(got, want) >= 0.999, (step, cosine(got, want))
@@ -146,5 +147,64 @@ def test_decoder_loaded_from_gguf_equals_direct_weights(tmp_path, tie_output):
             meta = torch.from_numpy(direct.token_meta([1] * n, pos_np)).cuda()
             pos = torch.from_numpy(pos_np).cuda()
             assert torch.equal(loaded.step(ids, meta, pos), direct.step(ids, meta, pos))
+    finally:
+        ctx.close()
+
+
+@pytest.mark.parametrize("prompt_len", [3, 40])
+def test_one_token_step_kernel_matches_the_five_launch_layer(monkeypatch, prompt_len):
+    """Decoder.step(decode=True) for one token runs ONE persistent kernel (mcu_decode_plan); with the diagnostic switch it
+    runs five launches per layer.  Same weights, same prompt: the matmuls share their device functions, the attention is
+    f32 in one and split-f16 MMAs in the other, so logits agree to rounding, the greedy tokens are the same, and the
+    K/V rows both wrote into their pools agree (bit for bit in the first layer).  Contexts inside one 32-position tile and across two; also replayed
+    from a CUDA graph."""
+    rng = np.random.default_rng(prompt_len)
+    weights = make_weights(rng)
+    ctx = Context(0)
+    try:
+        decs = [Decoder(ctx, SHAPE, max_seqs=2, max_ctx=64, block_size=16, kv_dtype=torch.float16, weights=weights) for _ in range(2)]
+        ids = torch.from_numpy(rng.integers(0, SHAPE.vocab, prompt_len).astype(np.int32)).cuda()
+        pos_np = np.arange(prompt_len, dtype=np.int32)
+        for d in decs:
+            d.step(ids, torch.from_numpy(d.token_meta([1] * prompt_len, pos_np)).cuda(), torch.from_numpy(pos_np).cuda())
+        tok = torch.tensor([7], dtype=torch.int32, device="cuda")
+        for step in range(8):
+            p = np.array([prompt_len + step], dtype=np.int32)
+            meta, pos = torch.from_numpy(decs[0].token_meta([1], p)).cuda(), torch.from_numpy(p).cuda()
+            l0 = ctx.launch_count()
+            got = decs[0].step(tok, meta, pos, decode=True).clone()
+            assert ctx.launch_count() - l0 == 3
+            monkeypatch.setenv("MARMOT_DECODER_NO_STEP_KERNEL", "1")
+            want = decs[1].step(tok, meta, pos, decode=True).clone()
+            monkeypatch.delenv("MARMOT_DECODER_NO_STEP_KERNEL")
+            ctx.synchronize()
+            assert max_rel_err(got.cpu().numpy(), want.cpu().numpy()) <= 1e-4, step
+            assert int(got.argmax()) == int(want.argmax())
+            tok = want.argmax(dim=1).to(torch.int32)
+        # layer 0's rows come from identical arithmetic; deeper layers inherit the attention's last-place differences,
+        # which an f16 rounding can turn into one unit in the last place
+        for a, b in ((decs[0].kv_k, decs[1].kv_k), (decs[0].kv_v, decs[1].kv_v)):
+            assert torch.equal(a[:, 0], b[:, 0])
+            assert float((a.float() - b.float()).abs().max()) <= 2e-3 * float(b.float().abs().max())
+        # the same plan from a CUDA graph: fixed tensors, new contents
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        ctx.set_stream(stream.cuda_stream)
+        p = np.array([prompt_len + 8], dtype=np.int32)
+        meta, pos = torch.from_numpy(decs[0].token_meta([1], p)).cuda(), torch.from_numpy(p).cuda()
+        logits = torch.empty((1, SHAPE.vocab), dtype=torch.float32, device="cuda")
+        with torch.cuda.stream(stream):
+            decs[0].step(tok, meta, pos, logits_out=logits, decode=True)  # builds the plan for these tensors
+            torch.cuda.synchronize()
+            eager = logits.clone()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                decs[0].step(tok, meta, pos, logits_out=logits, decode=True)
+            logits.zero_()
+            g.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(logits, eager)  # same position, same pool rows rewritten with the same values
+        ctx.synchronize()
+        ctx.set_stream(0)
     finally:
         ctx.close()
