@@ -399,6 +399,12 @@ typedef struct mcu_decode_plan_desc {
 typedef struct mcu_decode_plan mcu_decode_plan_t;
 int mcu_decode_plan_create(mcu_context_t *ctx, const mcu_decode_plan_desc_t *desc, mcu_decode_plan_t **out_plan);
 int mcu_decode_plan_run(mcu_decode_plan_t *plan);
+/* Timeline of the last run, the device's nanosecond clock as CTA 0 saw it: at the start of every phase (per layer:
+ * q/k/v, attention, o projection, gate/up, down; then the output projection) and at the end (n_phases + 1 values),
+ * then per phase two more: activations packed (matmul phases; 0 otherwise) and phase work done, before the grid
+ * barrier.  3 * n_phases + 1 values.  Waits for the stream.  With out == NULL or capacity too small only *n_out is
+ * set. */
+int mcu_decode_plan_phase_times(mcu_decode_plan_t *plan, unsigned long long *out, size_t capacity, size_t *n_out);
 void mcu_decode_plan_destroy(mcu_decode_plan_t *plan);
 
 /* ---- paged KV-cache pool: marmot_kv_pool_* (include/marmot/inference/kv_pool.h:65-101, implementation

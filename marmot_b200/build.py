@@ -12,7 +12,7 @@ CSRC = PKG / "csrc"
 OUT = PKG / "libmarmot_cuda.so"
 OBJ_DIR = PKG / "build"
 
-SOURCES = ["abi.cu", "act_quant.cu", "dequant.cu", "gemv.cu", "gemv_stream.cu", "gemm_tc.cu", "gemm_tma.cu", "gemm_warp.cu", "gemm_i8.cu", "linear_f16.cu", "moe.cu", "static_scratch.cu", "peer.cu", "decoder.cu", "decode_step.cu", "kv_pool.cu", "gguf.cu"]
+SOURCES = ["abi.cu", "act_quant.cu", "dequant.cu", "gemv.cu", "gemv_stream.cu", "gemv_stream_addnorm.cu", "gemv_stream_swiglu.cu", "gemm_tc.cu", "gemm_tma.cu", "gemm_warp.cu", "gemm_i8.cu", "linear_f16.cu", "moe.cu", "static_scratch.cu", "peer.cu", "decoder.cu", "decode_step.cu", "kv_pool.cu", "gguf.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

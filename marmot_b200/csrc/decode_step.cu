@@ -9,10 +9,11 @@
 //     ring slots, so HBM keeps streaming across the barriers and during the activation packing;
 //   * the consumer warps do per phase what the streaming GEMV does per launch (prologue + packing of the activations,
 //     row dots on the ring, stores), with the same device functions, hence the same bits;
-//   * attention for the single token runs on up to four warps per CTA, one 32-position tile of one KV head each, in f32
-//     on the f16 pool (scores with one position per lane, P V with two dimensions per lane), RoPE of q and of the new K
-//     row from the step's table, the new K / V rows appended by the warp that holds the token's own position; the last
-//     tile of a KV head to finish (ticket) merges the tiles in tile order.
+//   * attention for the single token: one CTA per query head, in f32 on the f16 pool -- RoPE of the query head and of the
+//     new K row from the step's table, the new K / V rows appended, every warp a running softmax state over its
+//     32-position tiles (scores with one position per lane, P V with head_dim / 32 dimensions per lane), the states
+//     merged through shared memory.  Made for the short contexts of single-sequence decoding: with thousands of
+//     cached positions a few dozen SMs read the whole cache of a layer, and the five-launch layer is the faster one.
 // Every wait is bounded: a barrier or ring wait that runs out sets the error flag and an abort word that all CTAs
 // poll, and the kernel returns.
 #define MCU_ACT_LOAD(ptr) __ldcg(ptr)  // activations are written by other CTAs of this same launch
@@ -29,15 +30,18 @@
 
 namespace mcu {
 
-constexpr int DS_TW = 15;                      // consumer warps
+#ifndef DS_TW_N
+#define DS_TW_N 15
+#endif
+constexpr int DS_TW = DS_TW_N;                 // consumer warps
+constexpr int DS_AW = DS_TW < 15 ? DS_TW : 15; // of them, the warps that take attention tiles (their states share the activation area)
 constexpr int DS_THREADS = (DS_TW + 1) * 32;   // + the producer warp
 constexpr int DS_MAX_JOBS = 3;
-constexpr int DS_ATTN_WARPS = 4;
-constexpr int DS_CHUNK_BYTES = 20 * 1024;      // target size of a ring chunk
-constexpr int DS_STAGE_STRIDE = 21 * 1024;     // a chunk + over-read slack, multiple of 128
-constexpr int DS_STAGES = 7;
+constexpr int DS_CHUNK_BYTES = (DS_TW > 15 ? 36 : 20) * 1024;    // target size of a ring chunk (a row per consumer warp)
+constexpr int DS_STAGE_STRIDE = DS_CHUNK_BYTES + 1024;           // a chunk + over-read slack, multiple of 128
+constexpr int DS_STAGES = DS_TW > 15 ? 4 : 7;
 constexpr int DS_ACT_BYTES = 20 * 1024;        // packed activations of one token: K up to 17408 values
-constexpr int DS_ATTN_SCRATCH = 10 * 128;      // floats per attention warp: 8 rotated query heads + the new K and V rows, head_dim <= 128
+constexpr int DS_ATTN_EXTRA_BYTES = 20 * 1024; // behind the activation area: with it the attention phase's queries and softmax states
 constexpr uint32_t DS_SPIN_LIMIT = 1u << 22;
 
 enum { DS_PHASE_GEMV = 0, DS_PHASE_ATTN = 1 };
@@ -61,7 +65,7 @@ struct DsPhase {
 struct DsParams {
     const DsPhase *phases;
     int n_phases;
-    uint32_t *sync;  // [0] arrivals of the grid barrier, [1] abort word, [2..] tickets of the attention (one per KV head)
+    uint32_t *sync;  // [0] arrivals of the grid barrier, [1] abort word (one aligned 8-byte word)
     int *err;
     // attention
     const uint32_t *meta;   // [4]: seq slot, position, kv slot, flags
@@ -70,29 +74,32 @@ struct DsParams {
     __half *kv_k, *kv_v;
     const float2 *rope;     // [head_dim / 2] {cos, sin}
     float *att;             // [n_q_heads * head_dim]
-    float *partial;         // [n_q_heads][max_tiles][head_dim + 2]
-    int n_q_heads, n_kv_heads, head_dim, max_blocks, n_layers, block_shift, max_tiles, neox;
+    int n_q_heads, n_kv_heads, head_dim, max_blocks, n_layers, block_shift, neox;
     float scale;
+    unsigned long long *stamps;  // nanosecond clock of CTA 0: [n_phases + 1] phase starts and the end, then per phase
+                                 // {activations packed (matmul phases), phase work done}; or null
 };
 
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
 }
 
-// One thread per CTA: this CTA has finished phase `phase` (all its stores are done: the caller synchronised the CTA).
+// One thread per CTA: this CTA has finished a phase (the caller synchronised the CTA, so the release covers every
+// warp's stores).
 __device__ __forceinline__ void grid_arrive(uint32_t *sync) {
-    __threadfence();
-    atomicAdd(sync, 1u);
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(sync) : "memory");
 }
-// Bounded wait until every CTA has finished phase `phase`; false on abort.
+// Bounded wait until every CTA has finished phase `phase`; false on abort.  Arrivals and the abort word sit in one
+// aligned 8-byte word, so one load per poll reads both.
 __device__ __forceinline__ bool grid_wait(const DsParams &p, int phase) {
     const uint32_t want = (uint32_t)(phase + 1) * gridDim.x;
     for (uint32_t i = 0; i < DS_SPIN_LIMIT; ++i) {
-        if (ld_acquire_gpu(p.sync) >= want) return true;
-        if ((i & 63u) == 63u && ld_acquire_gpu(p.sync + 1) != 0u) return false;
-        __nanosleep(20);
+        unsigned long long v;
+        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p.sync) : "memory");
+        if ((uint32_t)(v >> 32) != 0u) return false;
+        if ((uint32_t)v >= want) return true;
     }
     atomicExch(p.err, 31);
     atomicExch(p.sync + 1, 1u);
@@ -100,177 +107,205 @@ __device__ __forceinline__ bool grid_wait(const DsParams &p, int phase) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Attention of the one token for KV head h, positions [k0, k0 + 32): by one warp.  s_q: this warp's scratch, rotated and
-// scaled query heads of the group [gsize][HD], then the new K and V rows [2][HD] when the tile holds the token's own
-// position.  Writes the tile's state {m, l, acc[HD]} per query head to `partial`.
+// Attention of the one token for query head qh, by the consumer warps of one CTA.  `sm` overlays the activation area:
+// the rotated and scaled query head [HD] (f32), the token's own K (rotated) and V rows as the pool stores them
+// [2][HD] (f16), then one softmax state {m, l, acc[HD]} per warp.
+//   1. RoPE of the query head and of the new K row; the CTA of a group's first query head also appends the new K and V
+//      rows to the pool (the others use their own copy, so no CTA waits for another);
+//   2. warp w takes the 32-position tiles w, w + W, ...: one position per lane for the scores (its K row in registers),
+//      HD / 32 dimensions per lane for P V (the V rows in registers, sixteen at a time), a running maximum and sum;
+//   3. warp 0 merges the warps' states in tile order.
+// A single token's attention is a chain of latencies, not a stream: one query head per CTA and one tile per warp keep
+// the chain short (K and V are read once per query head of the group, from L2), and nothing counts on L1 -- with
+// this much shared memory configured it is a few tens of kilobytes.  Loops stay rolled where they can: every piece of
+// code runs once per layer, so its size is part of what the step waits for.
 // ---------------------------------------------------------------------------------------------
+#define DS_DBG(k) do { if (dbg != nullptr && threadIdx.x == 0) dbg[k] = global_ns(); } while (0)
 template <int HD>
-__device__ __forceinline__ void attention_tile(const DsParams &p, int layer, int h, int tile, uint32_t kv_len, float *s_q) {
-    constexpr int HALF = HD / 2, DPL = HD / 32;  // dimensions per lane in the P V product
-    const int lane = threadIdx.x & 31;
-    const int gsize = p.n_q_heads / p.n_kv_heads;
-    const uint32_t k0 = (uint32_t)tile * 32u, new_pos = kv_len - 1u;
+__device__ __forceinline__ void attention_head(const DsParams &p, int layer, int qh, float *sm, unsigned long long *dbg) {
+    constexpr int HALF = HD / 2, DPL = HD / 32, NTH = DS_TW * 32, SW = HD + 2;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gsize = p.n_q_heads / p.n_kv_heads, h = qh / gsize;
+    float *s_q = sm;
+    __half *s_kn = (__half *)(sm + HD), *s_vn = s_kn + HD;
+    float *s_state = sm + 2 * HD;
+    const uint32_t seq = p.meta[0], new_pos = p.meta[1], kv_slot = p.meta[2], kv_len = new_pos + 1u;
     const size_t bs = (size_t)1 << p.block_shift;
     const size_t s3 = HD, s2 = bs * s3, s1 = (size_t)p.n_kv_heads * s2, s0 = (size_t)p.n_layers * s1;
     const size_t head_off = (size_t)layer * s1 + (size_t)h * s2;
-    float *s_kn = s_q + 8 * HD, *s_vn = s_kn + HD;
-    // rotated, scaled query heads
-    for (int idx = lane; idx < gsize * HALF; idx += 32) {
-        const int g = idx / HALF, i = idx - g * HALF;
-        const float2 cs = p.rope[i];
+
+    // ---- 1. rotations: threads [0, HALF) the query pairs, [64, 64 + HALF) the K pairs, [128, 128 + HD) the V values ----
+    {
+        const bool q_thread = tid < HALF, k_thread = tid >= 64 && tid < 64 + HALF, v_thread = tid >= 128 && tid < 128 + HD;
+        const bool writer = qh == h * gsize;  // appends the rows to the pool
+        const int i = q_thread ? tid : tid - 64;
         const int e = p.neox ? i : 2 * i, o = p.neox ? i + HALF : 2 * i + 1;
-        const float *row = p.q + (size_t)(h * gsize + g) * HD;
-        const float xe = __ldcg(row + e), xo = __ldcg(row + o);  // written by other CTAs in the previous phase
-        float re = __fsub_rn(__fmul_rn(xe, cs.x), __fmul_rn(xo, cs.y)), ro = __fadd_rn(__fmul_rn(xe, cs.y), __fmul_rn(xo, cs.x));
-        if (p.scale != 1.0f) {
-            re = __fmul_rn(re, p.scale);
-            ro = __fmul_rn(ro, p.scale);
+        float xe = 0.0f, xo = 0.0f, vx = 0.0f;
+        float2 cs = make_float2(1.0f, 0.0f);
+        if (q_thread || k_thread) {  // written by other CTAs in the previous phase
+            const float *row = q_thread ? p.q + (size_t)qh * HD : p.k_new + (size_t)h * HD;
+            xe = __ldcg(row + e);
+            xo = __ldcg(row + o);
+            cs = p.rope[i];
         }
-        s_q[g * HD + e] = re;
-        s_q[g * HD + o] = ro;
-    }
-    const bool has_new = new_pos >= k0 && new_pos < k0 + 32u;
-    if (has_new) {  // the token's own K (rotated) and V rows, rounded to f16 as the pool stores them, and into the pool
-        const uint32_t kv_slot = p.meta[2];
+        if (v_thread) vx = __ldcg(p.v_new + (size_t)h * HD + (tid - 128));
         const size_t dst = (size_t)(kv_slot >> p.block_shift) * s0 + head_off + (size_t)(kv_slot & (uint32_t)(bs - 1)) * s3;
-        const float *krow = p.k_new + (size_t)h * HD, *vrow = p.v_new + (size_t)h * HD;
-        for (int i = lane; i < HALF; i += 32) {
-            const float2 cs = p.rope[i];
-            const int e = p.neox ? i : 2 * i, o = p.neox ? i + HALF : 2 * i + 1;
-            const float xe = __ldcg(krow + e), xo = __ldcg(krow + o);
-            const __half ke = __float2half_rn(__fsub_rn(__fmul_rn(xe, cs.x), __fmul_rn(xo, cs.y)));
-            const __half ko = __float2half_rn(__fadd_rn(__fmul_rn(xe, cs.y), __fmul_rn(xo, cs.x)));
-            p.kv_k[dst + e] = ke;
-            p.kv_k[dst + o] = ko;
-            s_kn[e] = __half2float(ke);
-            s_kn[o] = __half2float(ko);
+        float re = __fsub_rn(__fmul_rn(xe, cs.x), __fmul_rn(xo, cs.y)), ro = __fadd_rn(__fmul_rn(xe, cs.y), __fmul_rn(xo, cs.x));
+        if (q_thread) {
+            if (p.scale != 1.0f) {
+                re = __fmul_rn(re, p.scale);
+                ro = __fmul_rn(ro, p.scale);
+            }
+            s_q[e] = re;
+            s_q[o] = ro;
         }
-        for (int d = lane; d < HD; d += 32) {
-            const __half vv = __float2half_rn(__ldcg(vrow + d));
-            p.kv_v[dst + d] = vv;
-            s_vn[d] = __half2float(vv);
+        if (k_thread) {
+            const __half ke = __float2half_rn(re), ko = __float2half_rn(ro);
+            s_kn[e] = ke;
+            s_kn[o] = ko;
+            if (writer) {
+                p.kv_k[dst + e] = ke;
+                p.kv_k[dst + o] = ko;
+            }
+        }
+        if (v_thread) {
+            const __half vv = __float2half_rn(vx);
+            s_vn[tid - 128] = vv;
+            if (writer) p.kv_v[dst + (tid - 128)] = vv;
         }
     }
-    __syncwarp();
-    // scores: lane = position
-    const uint32_t pos = k0 + (uint32_t)lane;
-    const uint32_t seq = p.meta[0];
-    uint32_t tb = 0xFFFFFFFFu;
-    if (pos < kv_len && (pos >> p.block_shift) < (uint32_t)p.max_blocks) tb = p.table[(size_t)seq * p.max_blocks + (pos >> p.block_shift)];
-    const bool live = tb != 0xFFFFFFFFu;
-    const size_t row_base = live ? (size_t)tb * s0 + head_off + (size_t)(pos & (uint32_t)(bs - 1)) * s3 : 0;
-    float sc[8];
+    DS_DBG(0);
+    asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
+    DS_DBG(1);
+
+    // ---- 2. tiles ----
+    const int n_tiles = (int)((kv_len + 31u) / 32u);
+    if (warp < DS_AW) {
+        float m_run = -INFINITY, l_run = 0.0f, acc[DPL];
 #pragma unroll
-    for (int g = 0; g < 8; ++g) sc[g] = 0.0f;
-    if (live) {
-        const bool mine_new = pos == new_pos;
-#pragma unroll 2
-        for (int c = 0; c < HD / 8; ++c) {
-            float kf[8];
-            if (mine_new) {
+        for (int d = 0; d < DPL; ++d) acc[d] = 0.0f;
+#pragma unroll 1
+        for (int tile = warp; tile < n_tiles; tile += DS_AW) {
+            const uint32_t k0 = (uint32_t)tile * 32u, pos = k0 + (uint32_t)lane;
+            uint32_t tb = 0xFFFFFFFFu;
+            if (pos < kv_len && (pos >> p.block_shift) < (uint32_t)p.max_blocks) tb = p.table[(size_t)seq * p.max_blocks + (pos >> p.block_shift)];
+            const bool live = tb != 0xFFFFFFFFu;
+            const size_t row_base = live ? (size_t)tb * s0 + head_off + (size_t)(pos & (uint32_t)(bs - 1)) * s3 : 0;
+            const uint32_t live_mask = __ballot_sync(0xffffffffu, live);
+            const int new_row = (new_pos >= k0 && new_pos < k0 + 32u) ? (int)(new_pos - k0) : -1;  // taken from shared memory
+            uint32_t vraw[16][DPL / 2];
+            auto load_v = [&](int half) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) kf[j] = s_kn[8 * c + j];
-            } else {
-                const uint4 raw = *(const uint4 *)(p.kv_k + row_base + 8 * c);
-                const __half2 *h2 = (const __half2 *)&raw;
+                for (int j = 0; j < 16; ++j) {
+                    const int r = 16 * half + j;
+                    const unsigned long long rb = __shfl_sync(0xffffffffu, (unsigned long long)row_base, r);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2 f = __half22float2(h2[j]);
-                    kf[2 * j] = f.x, kf[2 * j + 1] = f.y;
+                    for (int d = 0; d < DPL / 2; ++d) vraw[j][d] = 0u;
+                    if (r == new_row) {
+#pragma unroll
+                        for (int d = 0; d < DPL / 2; ++d) vraw[j][d] = *(const uint32_t *)(s_vn + lane * DPL + 2 * d);
+                    } else if ((live_mask >> r) & 1u) {
+                        if constexpr (DPL == 2) {
+                            vraw[j][0] = *(const uint32_t *)(p.kv_v + rb + lane * 2);
+                        } else {
+                            const uint2 t = *(const uint2 *)(p.kv_v + rb + lane * 4);
+                            vraw[j][0] = t.x, vraw[j][1] = t.y;
+                        }
+                    }
+                }
+            };
+            float w;
+            {
+                uint4 kraw[HD / 8];
+#pragma unroll
+                for (int c = 0; c < HD / 8; ++c) kraw[c] = make_uint4(0u, 0u, 0u, 0u);
+                if (lane == new_row) {
+#pragma unroll
+                    for (int c = 0; c < HD / 8; ++c) kraw[c] = *(const uint4 *)(s_kn + 8 * c);
+                } else if (live) {
+#pragma unroll
+                    for (int c = 0; c < HD / 8; ++c) kraw[c] = *(const uint4 *)(p.kv_k + row_base + 8 * c);
+                }
+                if constexpr (HD == 64) load_v(0);  // in flight with the K rows where the registers allow
+                float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+                for (int c = 0; c < HD / 8; ++c) {
+                    const __half2 *h2 = (const __half2 *)&kraw[c];
+                    const float4 qa = *(const float4 *)(s_q + 8 * c), qb = *(const float4 *)(s_q + 8 * c + 4);
+                    const float2 k0f = __half22float2(h2[0]), k1f = __half22float2(h2[1]), k2f = __half22float2(h2[2]), k3f = __half22float2(h2[3]);
+                    sa += qa.x * k0f.x + qa.y * k0f.y + qa.z * k1f.x + qa.w * k1f.y;
+                    sb += qb.x * k2f.x + qb.y * k2f.y + qb.z * k3f.x + qb.w * k3f.y;
+                }
+                const float sc = sa + sb;
+                float m = live ? sc : -INFINITY;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                const float m_new = fmaxf(m_run, m);  // finite: the token's own position is always there... in some tile
+                float alpha = 1.0f;
+                w = 0.0f;
+                if (m_new != -INFINITY) {  // uniform
+                    alpha = m_run == -INFINITY ? 0.0f : __expf(m_run - m_new);
+                    w = live ? __expf(sc - m_new) : 0.0f;
+                }
+                float sum = w;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                l_run = l_run * alpha + sum;
+#pragma unroll
+                for (int d = 0; d < DPL; ++d) acc[d] *= alpha;
+                m_run = m_new;
+            }
+            // O += P V, positions in order
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                if (HD != 64 || half == 1) load_v(half);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float wr = __shfl_sync(0xffffffffu, w, 16 * half + j);  // zero for a position that is not there
+#pragma unroll
+                    for (int d = 0; d < DPL / 2; ++d) {
+                        const float2 f = __half22float2(*(const __half2 *)&vraw[j][d]);
+                        acc[2 * d] += wr * f.x;
+                        acc[2 * d + 1] += wr * f.y;
+                    }
                 }
             }
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                if (g >= gsize) break;
-                const float4 qa = *(const float4 *)(s_q + g * HD + 8 * c), qb = *(const float4 *)(s_q + g * HD + 8 * c + 4);
-                sc[g] += qa.x * kf[0] + qa.y * kf[1] + qa.z * kf[2] + qa.w * kf[3] + qb.x * kf[4] + qb.y * kf[5] + qb.z * kf[6] +
-                    qb.w * kf[7];
-            }
         }
-    }
-    // per head: tile maximum, weights, sum
-    float pw[8], mx[8], sum[8];
-#pragma unroll
-    for (int g = 0; g < 8; ++g) {
-        float m = live ? sc[g] : -INFINITY;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        const float w = (live && m != -INFINITY) ? expf(sc[g] - m) : 0.0f;
-        float s = w;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        pw[g] = w, mx[g] = m, sum[g] = s;
-    }
-    // O = P V: lane = DPL consecutive dimensions; positions in order
-    float acc[8][DPL];
-#pragma unroll
-    for (int g = 0; g < 8; ++g)
-#pragma unroll
-        for (int d = 0; d < DPL; ++d) acc[g][d] = 0.0f;
-    const uint32_t live_mask = __ballot_sync(0xffffffffu, live);
-    for (int r = 0; r < 32; ++r) {
-        if (!((live_mask >> r) & 1u)) continue;  // uniform
-        const unsigned long long rb = __shfl_sync(0xffffffffu, (unsigned long long)row_base, r);
-        float vf[DPL];
-        if (k0 + (uint32_t)r == new_pos) {
-#pragma unroll
-            for (int d = 0; d < DPL; ++d) vf[d] = s_vn[lane * DPL + d];
-        } else if constexpr (DPL == 2) {
-            const float2 f = __half22float2(*(const __half2 *)(p.kv_v + rb + lane * 2));
-            vf[0] = f.x, vf[1] = f.y;
-        } else {
-            const uint2 raw = *(const uint2 *)(p.kv_v + rb + lane * 4);
-            const float2 a = __half22float2(*(const __half2 *)&raw.x), b = __half22float2(*(const __half2 *)&raw.y);
-            vf[0] = a.x, vf[1] = a.y, vf[2] = b.x, vf[3] = b.y;
-        }
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            if (g >= gsize) break;
-            const float w = __shfl_sync(0xffffffffu, pw[g], r);
-#pragma unroll
-            for (int d = 0; d < DPL; ++d) acc[g][d] += w * vf[d];
-        }
-    }
-#pragma unroll
-    for (int g = 0; g < 8; ++g) {
-        if (g >= gsize) break;
-        float *pr = p.partial + ((size_t)(h * gsize + g) * p.max_tiles + tile) * (HD + 2);
+        float *st = s_state + (size_t)warp * SW;
         if (lane == 0) {
-            pr[0] = mx[g];
-            pr[1] = sum[g];
+            st[0] = m_run;
+            st[1] = l_run;
         }
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) pr[2 + lane * DPL + d] = acc[g][d];
+        for (int d = 0; d < DPL; ++d) st[2 + lane * DPL + d] = acc[d];
     }
-}
+    DS_DBG(2);
+    asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
+    DS_DBG(3);
 
-// The tiles of KV head h merged in tile order into att (by one warp): the arithmetic of the attention merge kernel.
-template <int HD>
-__device__ __forceinline__ void attention_merge(const DsParams &p, int h, int n_tiles) {
-    constexpr int DPL = HD / 32;
-    const int lane = threadIdx.x & 31;
-    const int gsize = p.n_q_heads / p.n_kv_heads;
-    for (int g = 0; g < gsize; ++g) {
-        const int qh = h * gsize + g;
-        const float *pr = p.partial + (size_t)qh * p.max_tiles * (HD + 2);
+    // ---- 3. merge ----
+    if (warp == 0) {
+        const int n_used = min(n_tiles, DS_AW);  // the warps that hold a state
         float M = -INFINITY;
-        for (int c = 0; c < n_tiles; ++c) M = fmaxf(M, __ldcg(pr + (size_t)c * (HD + 2)));
+        for (int t = 0; t < n_used; ++t) M = fmaxf(M, s_state[(size_t)t * SW]);
         float L = 0.0f, o[DPL];
 #pragma unroll
         for (int d = 0; d < DPL; ++d) o[d] = 0.0f;
         if (M != -INFINITY) {
-            for (int c = 0; c < n_tiles; ++c) {
-                const float mc = __ldcg(pr + (size_t)c * (HD + 2));
+            for (int t = 0; t < n_used; ++t) {
+                const float *st = s_state + (size_t)t * SW;
+                const float mc = st[0];
                 if (mc == -INFINITY) continue;
-                const float e = expf(mc - M);
-                L += __ldcg(pr + (size_t)c * (HD + 2) + 1) * e;
+                const float e = __expf(mc - M);
+                L += st[1] * e;
 #pragma unroll
-                for (int d = 0; d < DPL; ++d) o[d] += __ldcg(pr + (size_t)c * (HD + 2) + 2 + lane * DPL + d) * e;
+                for (int d = 0; d < DPL; ++d) o[d] += st[2 + lane * DPL + d] * e;
             }
         }
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) p.att[(size_t)qh * HD + lane * DPL + d] = L > 0.0f ? o[d] / L : 0.0f;
+        for (int d = 0; d < DPL; ++d) p.att[(size_t)qh * HD + lane * DPL + d] = L > 0.0f ? __fdividef(o[d], L) : 0.0f;
     }
+    DS_DBG(4);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -290,8 +325,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
     float *inv_s = (float *)(smem + GS_RED_OFFSET);
     float *red = inv_s + GEMV_MAX_T;
     uint8_t *act_base = smem + GS_HEADER;
-    float *attn_scratch = (float *)(act_base + DS_ACT_BYTES);  // [DS_ATTN_WARPS][DS_ATTN_SCRATCH]
-    uint8_t *stage_base = (uint8_t *)(attn_scratch + DS_ATTN_WARPS * DS_ATTN_SCRATCH);
+    uint8_t *stage_base = act_base + DS_ACT_BYTES + DS_ATTN_EXTRA_BYTES;
     constexpr int S = DS_STAGES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, cta = blockIdx.x;
     (void)inv_s;
@@ -348,28 +382,13 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
             asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
             if (!ok) break;
         }
+        if (cta == 0 && threadIdx.x == 0 && p.stamps != nullptr) p.stamps[ph_i] = global_ns();
+        if (ph_i + 1 < p.n_phases && threadIdx.x < (int)((sizeof(DsPhase) + 127) / 128))  // the next descriptor, towards L1
+            asm volatile("prefetch.global.L2 [%0];" ::"l"((const char *)(p.phases + ph_i + 1) + 128 * threadIdx.x));
         if (ph.type == DS_PHASE_ATTN) {
-            const uint32_t kv_len = p.meta[1] + 1u;
-            const int n_tiles = min(p.max_tiles, (int)((kv_len + 31u) / 32u));
-            if (warp < DS_ATTN_WARPS) {
-                float *scratch = attn_scratch + warp * DS_ATTN_SCRATCH;
-                for (int item = cta * DS_ATTN_WARPS + warp; item < p.n_kv_heads * n_tiles; item += (int)gridDim.x * DS_ATTN_WARPS) {
-                    const int h = item / n_tiles, tile = item - h * n_tiles;
-                    if (p.head_dim == 64) attention_tile<64>(p, ph.layer, h, tile, kv_len, scratch);
-                    else attention_tile<128>(p, ph.layer, h, tile, kv_len, scratch);
-                    __threadfence();
-                    __syncwarp();
-                    uint32_t drawn = 0;
-                    if (lane == 0) drawn = atomicAdd(p.sync + 2 + h, 1u);
-                    drawn = __shfl_sync(0xffffffffu, drawn, 0);
-                    if (drawn == (uint32_t)n_tiles - 1u) {  // the head's last tile: merge, and leave the ticket at zero
-                        if (lane == 0) p.sync[2 + h] = 0u;
-                        __threadfence();
-                        if (p.head_dim == 64) attention_merge<64>(p, h, n_tiles);
-                        else attention_merge<128>(p, h, n_tiles);
-                    }
-                    __syncwarp();
-                }
+            if (cta < p.n_q_heads) {  // one CTA per query head; the others go straight to the barrier
+                if (p.head_dim == 64) attention_head<64>(p, ph.layer, cta, (float *)act_base, cta == 0 && p.stamps != nullptr ? p.stamps + 3 * p.n_phases + 1 + 8 * ph_i : nullptr);
+                else attention_head<128>(p, ph.layer, cta, (float *)act_base, nullptr);
             }
         } else {
             const DsJob &job = job_of(ph, cta);
@@ -391,6 +410,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
                 else quantize_all_q8_k<16>(ph.x, ph.K, 1, ph.K, ph.nb, a, threadIdx.x, NTH);
             }
             asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
+            if (cta == 0 && threadIdx.x == 0 && p.stamps != nullptr) p.stamps[p.n_phases + 1 + 2 * ph_i] = global_ns();
             if (kind == KIND_Q4_K) {
                 // two rows per warp: chunks in pairs
                 for (int jp = 0; 2 * jp < n_chunks; ++jp) {
@@ -454,17 +474,15 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
             }
             cbase += n_chunks;
         }
-        // this CTA is through the phase (or one of its warps gave up: then all leave together)
+        // this CTA is through the phase; a warp that gave up has set the abort word, which every CTA reads in its next wait
         asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
-        if (ld_acquire_gpu(p.sync + 1) != 0u) {
-            ok = false;
-            break;
-        }
+        if (cta == 0 && threadIdx.x == 0 && p.stamps != nullptr) p.stamps[p.n_phases + 2 + 2 * ph_i] = global_ns();
         if (threadIdx.x == 0) grid_arrive(p.sync);
     }
     // CTA 0 waits for everybody's last arrival and leaves the counter at zero for the next launch (nobody else waits on
     // it any more)
     if (threadIdx.x == 0 && cta == 0 && ok && grid_wait(p, p.n_phases - 1)) {
+        if (p.stamps != nullptr) p.stamps[p.n_phases] = global_ns();
         p.sync[0] = 0u;
         __threadfence();
     }
@@ -482,7 +500,7 @@ struct mcu_decode_plan {
     DsParams params{};
     DsPhase *phases_dev = nullptr;
     uint32_t *sync_dev = nullptr;
-    float *partial_dev = nullptr;
+    unsigned long long *stamps_dev = nullptr;
     int grid = 0, smem = 0;
 };
 
@@ -581,6 +599,7 @@ int mcu_decode_plan_create(mcu_context_t *ctx, const mcu_decode_plan_desc_t *d, 
     if (((uintptr_t)d->kv_k | (uintptr_t)d->kv_v | (uintptr_t)d->rope_table) & 15) return set_error(MCU_ERROR_INVALID_ARGUMENT, "decode plan: pools and RoPE table must be 16-byte aligned");
     DS_CUDA(cudaSetDevice(context_device(ctx)));
     const int sms = device_sm_count();
+    if ((int)d->n_q_heads > sms) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "decode plan: more query heads than SMs");
     const int L = (int)d->n_layers, D = (int)d->d, FF = (int)d->ffn, HKV = (int)(d->n_kv_heads * d->head_dim);
     std::vector<DsPhase> phases;
     phases.reserve(5 * (size_t)L + 1);
@@ -668,13 +687,12 @@ int mcu_decode_plan_create(mcu_context_t *ctx, const mcu_decode_plan_desc_t *d, 
     if (pl == nullptr) return set_error(MCU_ERROR_OUT_OF_MEMORY, "decode plan allocation failed");
     pl->ctx = ctx;
     pl->grid = sms;
-    pl->smem = GS_HEADER + DS_ACT_BYTES + DS_ATTN_WARPS * DS_ATTN_SCRATCH * (int)sizeof(float) + DS_STAGES * DS_STAGE_STRIDE;
-    const size_t max_positions = d->max_blocks_per_seq * d->block_size;
-    const int max_tiles = (int)((max_positions + 31) / 32);
-    const size_t sync_words = 2 + d->n_kv_heads;
+    pl->smem = GS_HEADER + DS_ACT_BYTES + DS_ATTN_EXTRA_BYTES + DS_STAGES * DS_STAGE_STRIDE;
+    const size_t sync_words = 2;
     cudaError_t e = cudaMalloc((void **)&pl->phases_dev, phases.size() * sizeof(DsPhase));
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->sync_dev, sync_words * sizeof(uint32_t));
-    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->partial_dev, d->n_q_heads * (size_t)max_tiles * (d->head_dim + 2) * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->stamps_dev, (11 * phases.size() + 1) * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemset(pl->stamps_dev, 0, (11 * phases.size() + 1) * sizeof(unsigned long long));
     if (e == cudaSuccess) e = cudaMemcpy(pl->phases_dev, phases.data(), phases.size() * sizeof(DsPhase), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemset(pl->sync_dev, 0, sync_words * sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pl->smem);
@@ -699,7 +717,6 @@ int mcu_decode_plan_create(mcu_context_t *ctx, const mcu_decode_plan_desc_t *d, 
     p.kv_v = (__half *)d->kv_v;
     p.rope = (const float2 *)d->rope_table;
     p.att = d->att;
-    p.partial = pl->partial_dev;
     p.n_q_heads = (int)d->n_q_heads;
     p.n_kv_heads = (int)d->n_kv_heads;
     p.head_dim = (int)d->head_dim;
@@ -707,9 +724,9 @@ int mcu_decode_plan_create(mcu_context_t *ctx, const mcu_decode_plan_desc_t *d, 
     p.n_layers = (int)d->n_layers;
     p.block_shift = 0;
     while (((size_t)1 << p.block_shift) < d->block_size) ++p.block_shift;
-    p.max_tiles = max_tiles;
     p.neox = d->rope_type == MCU_ROPE_NEOX ? 1 : 0;
     p.scale = d->attn_scale;
+    p.stamps = pl->stamps_dev;
     *out = pl;
     return MCU_SUCCESS;
 }
@@ -732,13 +749,24 @@ int mcu_decode_plan_run(mcu_decode_plan_t *pl) {
     return MCU_SUCCESS;
 }
 
+int mcu_decode_plan_phase_times(mcu_decode_plan_t *pl, unsigned long long *out, size_t capacity, size_t *n_out) {
+    if (pl == nullptr || n_out == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "null plan");
+    const size_t n = 11 * (size_t)pl->params.n_phases + 1;
+    *n_out = n;
+    if (out == nullptr || capacity < n) return MCU_SUCCESS;  // the count alone
+    DS_CUDA(cudaSetDevice(context_device(pl->ctx)));
+    DS_CUDA(cudaStreamSynchronize((cudaStream_t)mcu_context_get_stream(pl->ctx)));
+    DS_CUDA(cudaMemcpy(out, pl->stamps_dev, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    return MCU_SUCCESS;
+}
+
 void mcu_decode_plan_destroy(mcu_decode_plan_t *pl) {
     if (pl == nullptr) return;
     cudaSetDevice(context_device(pl->ctx));
     cudaStreamSynchronize((cudaStream_t)mcu_context_get_stream(pl->ctx));
     if (pl->phases_dev != nullptr) cudaFree(pl->phases_dev);
     if (pl->sync_dev != nullptr) cudaFree(pl->sync_dev);
-    if (pl->partial_dev != nullptr) cudaFree(pl->partial_dev);
+    if (pl->stamps_dev != nullptr) cudaFree(pl->stamps_dev);
     delete pl;
 }
 

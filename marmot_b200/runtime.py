@@ -3,6 +3,7 @@ operation is one call through the C ABI declared in include/marmot_cuda.h."""
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 import numpy as np
@@ -28,7 +29,7 @@ EXPORTS = (
     "mcu_peer_comm_connect", "mcu_peer_comm_staging", "mcu_peer_allreduce", "mcu_peer_comm_destroy",
     "mcu_linear_allreduce", "mcu_peer_comm_set_fused", "mcu_peer_comm_set_one_slot", "mcu_rmsnorm", "mcu_rope", "mcu_swiglu", "mcu_add", "mcu_argmax",
     "mcu_embedding_gather", "mcu_paged_attention", "mcu_paged_attention_decode", "mcu_rope_table", "mcu_decode_plan_create", "mcu_decode_plan_run",
-    "mcu_decode_plan_destroy", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps", "mcu_vec_dot_host",
+    "mcu_decode_plan_destroy", "mcu_decode_plan_phase_times", "mcu_add_rmsnorm", "mcu_rope_qk", "mcu_device_caps", "mcu_vec_dot_host",
     "mcu_kv_pool_options_init", "mcu_kv_pool_create", "mcu_kv_pool_destroy", "mcu_kv_pool_acquire_seq",
     "mcu_kv_pool_release_seq", "mcu_kv_pool_prepare_append", "mcu_kv_pool_commit_append", "mcu_kv_pool_abort_append",
     "mcu_kv_pool_prepare_prefix_attach", "mcu_kv_pool_commit_prefix_attach", "mcu_kv_pool_abort_prefix_attach",
@@ -86,6 +87,14 @@ class DecodePlan:
     def run(self):
         self.ctx._check(self.ctx.lib.mcu_decode_plan_run(self.handle))
 
+    def phase_times(self):
+        """Nanosecond stamps of the last run: the start of every phase, then the end."""
+        n = C.c_size_t()
+        self.ctx._check(self.ctx.lib.mcu_decode_plan_phase_times(self.handle, None, 0, C.byref(n)))
+        buf = (C.c_ulonglong * n.value)()
+        self.ctx._check(self.ctx.lib.mcu_decode_plan_phase_times(self.handle, buf, n.value, C.byref(n)))
+        return list(buf)
+
     def close(self):
         if self.handle:
             self.ctx.lib.mcu_decode_plan_destroy(self.handle)
@@ -111,12 +120,13 @@ def load_library() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
+    path = Path(os.environ.get("MARMOT_CUDA_LIB") or LIB_PATH)  # another build of the library, for A/B measurements
+    if not path.exists():
         raise FileNotFoundError(
-            f"{LIB_PATH} is missing: build it with `python -m marmot_b200.build` (needs nvcc); "
+            f"{path} is missing: build it with `python -m marmot_b200.build` (needs nvcc); "
             "marmot_b200 has no CPU or PyTorch fallback"
         )
-    L = C.CDLL(str(LIB_PATH))
+    L = C.CDLL(str(path))
     vp, sz, i32, f32 = C.c_void_p, C.c_size_t, C.c_int, C.c_float
     L.mcu_context_create.argtypes = [i32, C.POINTER(vp)]
     L.mcu_context_destroy.argtypes = [vp]
@@ -178,6 +188,7 @@ def load_library() -> C.CDLL:
     L.mcu_decode_plan_create.argtypes = [vp, vp, C.POINTER(vp)]
     L.mcu_decode_plan_run.argtypes = [vp]
     L.mcu_decode_plan_destroy.argtypes = [vp]
+    L.mcu_decode_plan_phase_times.argtypes = [vp, vp, sz, vp]
     L.mcu_decode_plan_destroy.restype = None
     _lib = L
     return L
