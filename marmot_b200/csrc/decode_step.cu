@@ -60,7 +60,13 @@ struct DsPhase {
     int K, nb;
     GemvPrologue pro;
     int layer;       // attention: which layer of the pool
+    const void *next_norm_w;  // the next phase's norm weights (used once per step, so they come from HBM): requested now
+    int next_norm_bytes;
 };
+
+constexpr int DS_PH_WORDS = (int)(sizeof(DsPhase) / 4);
+constexpr int DS_PH_STRIDE = (DS_PH_WORDS + 3) / 4 * 4;  // words between the two descriptor slots in shared memory
+static_assert(sizeof(DsPhase) % 8 == 0 && DS_PH_WORDS <= DS_TW * 32, "a descriptor is copied by one word per consumer thread");
 
 struct DsParams {
     const DsPhase *phases;
@@ -174,12 +180,18 @@ __device__ __forceinline__ void attention_head(const DsParams &p, int layer, int
             if (writer) p.kv_v[dst + (tid - 128)] = vv;
         }
     }
+    const int n_tiles = (int)((kv_len + 31u) / 32u);
+    auto block_of = [&](int tile) -> uint32_t {  // the pool block of this lane's position in the tile, or none
+        const uint32_t pos = (uint32_t)tile * 32u + (uint32_t)lane;
+        if (pos < kv_len && (pos >> p.block_shift) < (uint32_t)p.max_blocks) return p.table[(size_t)seq * p.max_blocks + (pos >> p.block_shift)];
+        return 0xFFFFFFFFu;
+    };
+    uint32_t tb_next = warp < DS_AW && warp < n_tiles ? block_of(warp) : 0xFFFFFFFFu;  // in flight across the barrier
     DS_DBG(0);
     asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
     DS_DBG(1);
 
     // ---- 2. tiles ----
-    const int n_tiles = (int)((kv_len + 31u) / 32u);
     if (warp < DS_AW) {
         float m_run = -INFINITY, l_run = 0.0f, acc[DPL];
 #pragma unroll
@@ -187,17 +199,18 @@ __device__ __forceinline__ void attention_head(const DsParams &p, int layer, int
 #pragma unroll 1
         for (int tile = warp; tile < n_tiles; tile += DS_AW) {
             const uint32_t k0 = (uint32_t)tile * 32u, pos = k0 + (uint32_t)lane;
-            uint32_t tb = 0xFFFFFFFFu;
-            if (pos < kv_len && (pos >> p.block_shift) < (uint32_t)p.max_blocks) tb = p.table[(size_t)seq * p.max_blocks + (pos >> p.block_shift)];
+            const uint32_t tb = tb_next;
+            if (tile + DS_AW < n_tiles) tb_next = block_of(tile + DS_AW);
             const bool live = tb != 0xFFFFFFFFu;
             const size_t row_base = live ? (size_t)tb * s0 + head_off + (size_t)(pos & (uint32_t)(bs - 1)) * s3 : 0;
             const uint32_t live_mask = __ballot_sync(0xffffffffu, live);
             const int new_row = (new_pos >= k0 && new_pos < k0 + 32u) ? (int)(new_pos - k0) : -1;  // taken from shared memory
-            uint32_t vraw[16][DPL / 2];
+            constexpr int VR = HD == 64 ? 32 : 16;  // V rows in registers at a time
+            uint32_t vraw[VR][DPL / 2];
             auto load_v = [&](int half) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int r = 16 * half + j;
+                for (int j = 0; j < VR; ++j) {
+                    const int r = VR * half + j;
                     const unsigned long long rb = __shfl_sync(0xffffffffu, (unsigned long long)row_base, r);
 #pragma unroll
                     for (int d = 0; d < DPL / 2; ++d) vraw[j][d] = 0u;
@@ -226,7 +239,7 @@ __device__ __forceinline__ void attention_head(const DsParams &p, int layer, int
 #pragma unroll
                     for (int c = 0; c < HD / 8; ++c) kraw[c] = *(const uint4 *)(p.kv_k + row_base + 8 * c);
                 }
-                if constexpr (HD == 64) load_v(0);  // in flight with the K rows where the registers allow
+                if constexpr (VR == 32) load_v(0);  // in flight with the K rows where the registers allow
                 float sa = 0.0f, sb = 0.0f;
 #pragma unroll
                 for (int c = 0; c < HD / 8; ++c) {
@@ -257,11 +270,11 @@ __device__ __forceinline__ void attention_head(const DsParams &p, int layer, int
             }
             // O += P V, positions in order
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                if (HD != 64 || half == 1) load_v(half);
+            for (int half = 0; half < 32 / VR; ++half) {
+                if constexpr (VR != 32) load_v(half);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float wr = __shfl_sync(0xffffffffu, w, 16 * half + j);  // zero for a position that is not there
+                for (int j = 0; j < VR; ++j) {
+                    const float wr = __shfl_sync(0xffffffffu, w, VR * half + j);  // zero for a position that is not there
 #pragma unroll
                     for (int d = 0; d < DPL / 2; ++d) {
                         const float2 f = __half22float2(*(const __half2 *)&vraw[j][d]);
@@ -283,7 +296,7 @@ __device__ __forceinline__ void attention_head(const DsParams &p, int layer, int
     asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
     DS_DBG(3);
 
-    // ---- 3. merge ----
+    // ---- 3. merge, in warp order ----
     if (warp == 0) {
         const int n_used = min(n_tiles, DS_AW);  // the warps that hold a state
         float M = -INFINITY;
@@ -370,11 +383,16 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
     }
 
     // ---------------- consumers ----------------
+    // The phase descriptors come through shared memory, the next one fetched while the current phase runs: read from
+    // global memory at the start of a phase, its two or three lines were as many dependent trips to L2 (1.3 us).
     constexpr int NTH = DS_TW * 32;
+    uint32_t *s_ph = (uint32_t *)(stage_base + (size_t)DS_STAGES * DS_STAGE_STRIDE);
+    if (threadIdx.x < DS_PH_WORDS) s_ph[threadIdx.x] = __ldg((const uint32_t *)p.phases + threadIdx.x);
+    asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
     int cbase = 0;
     bool ok = true;
     for (int ph_i = 0; ph_i < p.n_phases && ok; ++ph_i) {
-        const DsPhase &ph = p.phases[ph_i];
+        const DsPhase &ph = *(const DsPhase *)(s_ph + (ph_i & 1) * DS_PH_STRIDE);
         if (ph_i > 0) {  // the previous phase's results, from every CTA
             if (threadIdx.x == 0) red[0] = grid_wait(p, ph_i - 1) ? 1.0f : 0.0f;
             asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
@@ -383,8 +401,11 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
             if (!ok) break;
         }
         if (cta == 0 && threadIdx.x == 0 && p.stamps != nullptr) p.stamps[ph_i] = global_ns();
-        if (ph_i + 1 < p.n_phases && threadIdx.x < (int)((sizeof(DsPhase) + 127) / 128))  // the next descriptor, towards L1
-            asm volatile("prefetch.global.L2 [%0];" ::"l"((const char *)(p.phases + ph_i + 1) + 128 * threadIdx.x));
+        uint32_t next_word = 0u;  // of the next descriptor; stored at the end of this phase
+        const bool fetch_next = ph_i + 1 < p.n_phases && threadIdx.x < DS_PH_WORDS;
+        if (fetch_next) next_word = __ldg((const uint32_t *)(p.phases + ph_i + 1) + threadIdx.x);
+        if (cta == (ph_i % (int)gridDim.x) && (int)threadIdx.x * 128 < ph.next_norm_bytes)  // one CTA asks, a different one every phase
+            asm volatile("prefetch.global.L2 [%0];" ::"l"((const char *)ph.next_norm_w + 128 * threadIdx.x));
         if (ph.type == DS_PHASE_ATTN) {
             if (cta < p.n_q_heads) {  // one CTA per query head; the others go straight to the barrier
                 if (p.head_dim == 64) attention_head<64>(p, ph.layer, cta, (float *)act_base, cta == 0 && p.stamps != nullptr ? p.stamps + 3 * p.n_phases + 1 + 8 * ph_i : nullptr);
@@ -474,6 +495,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
             }
             cbase += n_chunks;
         }
+        if (fetch_next) s_ph[((ph_i + 1) & 1) * DS_PH_STRIDE + threadIdx.x] = next_word;  // last read two phases ago
         // this CTA is through the phase; a warp that gave up has set the abort word, which every CTA reads in its next wait
         asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
         if (cta == 0 && threadIdx.x == 0 && p.stamps != nullptr) p.stamps[p.n_phases + 2 + 2 * ph_i] = global_ns();
@@ -683,11 +705,18 @@ int mcu_decode_plan_create(mcu_context_t *ctx, const mcu_decode_plan_desc_t *d, 
         if (int rc = ds_gemv_phase(ph, sms, xs[cur], D, g, 1, kinds, W, F, o)) return rc;
         phases.push_back(ph);
     }
+    for (size_t i = 0; i + 1 < phases.size(); ++i) {
+        const DsPhase &nx = phases[i + 1];
+        if (nx.type == DS_PHASE_GEMV && nx.pro.op == GEMV_PRO_ADD_RMSNORM && nx.pro.norm_w != nullptr) {
+            phases[i].next_norm_w = nx.pro.norm_w;
+            phases[i].next_norm_bytes = nx.K * (int)sizeof(float);
+        }
+    }
     mcu_decode_plan *pl = new (std::nothrow) mcu_decode_plan;
     if (pl == nullptr) return set_error(MCU_ERROR_OUT_OF_MEMORY, "decode plan allocation failed");
     pl->ctx = ctx;
     pl->grid = sms;
-    pl->smem = GS_HEADER + DS_ACT_BYTES + DS_ATTN_EXTRA_BYTES + DS_STAGES * DS_STAGE_STRIDE;
+    pl->smem = GS_HEADER + DS_ACT_BYTES + DS_ATTN_EXTRA_BYTES + DS_STAGES * DS_STAGE_STRIDE + 2 * DS_PH_STRIDE * (int)sizeof(uint32_t);
     const size_t sync_words = 2;
     cudaError_t e = cudaMalloc((void **)&pl->phases_dev, phases.size() * sizeof(DsPhase));
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->sync_dev, sync_words * sizeof(uint32_t));

@@ -172,7 +172,7 @@ __device__ __noinline__ void pro_rms_stats(const ProArgs p, int tid, float *red,
     if (tid < T) {
         float sum = 0.0f;
         for (int w = 0; w < NTHREADS / 32; ++w) sum += red[tid * 16 + w];
-        inv_s[tid] = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(sum, (float)p.K), g.eps)));
+        inv_s[tid] = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)p.K), g.eps)))  /* = 1 / sqrt: both correctly rounded */;
     }
     asm volatile("bar.sync 1, %0;" ::"n"(NTHREADS) : "memory");
 }
@@ -303,7 +303,7 @@ __device__ __noinline__ void quantize_q8_k_addnorm_once(const ProArgs p, int T, 
     asm volatile("bar.sync 1, %0;" ::"n"(NTHREADS) : "memory");
     float sum = 0.0f;
     for (int b = 0; b < nb; ++b) sum += red[t * nb + b];
-    const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(sum, (float)p.K), g.eps)));
+    const float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)p.K), g.eps)))  /* = 1 / sqrt: both correctly rounded */;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         float y = __fmul_rn(v[i], inv);
