@@ -37,20 +37,28 @@ constexpr int DS_TW = DS_TW_N;                 // consumer warps
 constexpr int DS_AW = DS_TW < 15 ? DS_TW : 15; // of them, the warps that take attention tiles (their states share the activation area)
 constexpr int DS_THREADS = (DS_TW + 1) * 32;   // + the producer warp
 constexpr int DS_MAX_JOBS = 3;
-constexpr int DS_CHUNK_BYTES = (DS_TW > 15 ? 36 : 20) * 1024;    // target size of a ring chunk (a row per consumer warp)
+constexpr int DS_CHUNK_BYTES = 36 * 1024;                        // target size of a ring chunk (one or two rows per consumer warp)
 constexpr int DS_STAGE_STRIDE = DS_CHUNK_BYTES + 1024;           // a chunk + over-read slack, multiple of 128
-constexpr int DS_STAGES = DS_TW > 15 ? 4 : 7;
+constexpr int DS_STAGES = 4;
+constexpr int DS_HALF_NB = 8;                  // Q4_K rows of at most this many blocks: two row pairs per warp (rows2_q4_k<1, 8>)
 constexpr int DS_ACT_BYTES = 20 * 1024;        // packed activations of one token: K up to 17408 values
 constexpr int DS_ATTN_EXTRA_BYTES = 20 * 1024; // behind the activation area: with it the attention phase's queries and softmax states
 constexpr uint32_t DS_SPIN_LIMIT = 1u << 22;
 
 enum { DS_PHASE_GEMV = 0, DS_PHASE_ATTN = 1 };
 
+// W2 != null: a gated pair (gate = W, up = W2, both Q4_K): the CTA streams its rows of both matrices, chunks
+// alternating, a warp takes row r of both in one pass and stores silu(gate . x) * (up . x) -- the activation of the
+// down projection, which then needs no prologue.
 struct DsJob {
-    const uint8_t *W;
+    const uint8_t *W, *W2;
     float *out;
     int F, kind, row_bytes, rows_per_cta, rows_per_chunk, cta_begin;
 };
+__device__ __forceinline__ int job_chunks(const DsJob &job, int n_rows) {
+    const int n_rc = (n_rows + job.rows_per_chunk - 1) / job.rows_per_chunk;
+    return job.W2 != nullptr ? 2 * n_rc : n_rc;
+}
 
 struct DsPhase {
     int type;
@@ -362,7 +370,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
                 const DsJob &job = job_of(ph, cta);
                 const int r0 = (cta - job.cta_begin) * job.rows_per_cta;
                 const int n_rows = max(0, min(job.F, r0 + job.rows_per_cta) - r0);
-                const int RC = job.rows_per_chunk, n_chunks = (n_rows + RC - 1) / RC;
+                const int RC = job.rows_per_chunk, n_chunks = job_chunks(job, n_rows);
+                const bool glu = job.W2 != nullptr;
                 for (int c = 0; c < n_chunks; ++c) {
                     const int gc = cbase + c, st = gc % S, round = gc / S;
                     if (round > 0 && !mbar_wait(&empty[st], (uint32_t)((round - 1) & 1))) {
@@ -370,11 +379,12 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
                         atomicExch(p.sync + 1, 1u);
                         return;
                     }
-                    const int rows = min(RC, n_rows - c * RC);
+                    const int k = glu ? c >> 1 : c;  // row chunk
+                    const uint8_t *mat = glu && (c & 1) ? job.W2 : job.W;
+                    const int rows = min(RC, n_rows - k * RC);
                     const uint32_t bytes = (uint32_t)rows * (uint32_t)job.row_bytes;
                     mbar_expect_tx(&full[st], bytes);
-                    bulk_g2s(stage_base + (size_t)st * DS_STAGE_STRIDE, job.W + ((size_t)r0 + (size_t)c * RC) * job.row_bytes, bytes,
-                             &full[st]);
+                    bulk_g2s(stage_base + (size_t)st * DS_STAGE_STRIDE, mat + ((size_t)r0 + (size_t)k * RC) * job.row_bytes, bytes, &full[st]);
                 }
                 cbase += n_chunks;
             }
@@ -416,7 +426,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
             const int kind = job.kind;
             const int r0 = (cta - job.cta_begin) * job.rows_per_cta;
             const int n_rows = max(0, min(job.F, r0 + job.rows_per_cta) - r0);
-            const int RC = job.rows_per_chunk, n_chunks = (n_rows + RC - 1) / RC;
+            const int RC = job.rows_per_chunk, n_chunks = job_chunks(job, n_rows);
             const ActSmem a = act_layout<true>(act_base, 1, ph.nb);
             // the activations, through the phase's prologue
             const ProArgs pa{ph.x, ph.K, ph.K, ph.nb, ph.pro};
@@ -433,7 +443,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
             asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
             if (cta == 0 && threadIdx.x == 0 && p.stamps != nullptr) p.stamps[p.n_phases + 1 + 2 * ph_i] = global_ns();
             if (kind == KIND_Q4_K) {
-                // two rows per warp: chunks in pairs
+                // Chunks in pairs, a row of each per warp and pass (of a gated pair: the same row of gate and up); with
+                // short rows each half of the warp takes such a pair.
+                const bool glu = job.W2 != nullptr, halves = ph.nb <= DS_HALF_NB;
+                const int half = halves ? lane >> 4 : 0, hl = halves ? lane & 15 : lane;
                 for (int jp = 0; 2 * jp < n_chunks; ++jp) {
                     const int c0 = 2 * jp, c1 = c0 + 1;
                     const bool two = c1 < n_chunks;
@@ -445,25 +458,33 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
                             atomicExch(p.err, 33);
                             atomicExch(p.sync + 1, 1u);
                         }
-                        break;  // the abort word is set: every warp leaves after the barrier below
+                        break;  // the abort word is set: every CTA leaves at its next grid wait
                     }
-                    const int rows0 = min(RC, n_rows - c0 * RC), rows1 = two ? min(RC, n_rows - c1 * RC) : 0;
-                    const int rl0 = (warp - (c0 * RC) % DS_TW + DS_TW) % DS_TW, rl1 = (warp - (c1 * RC) % DS_TW + DS_TW) % DS_TW;
+                    const int k0 = glu ? jp : c0, k1 = glu ? jp : c1;  // row chunks held by the two ring chunks
+                    const int rows0 = min(RC, n_rows - k0 * RC), rows1 = two ? min(RC, n_rows - k1 * RC) : 0;
+                    const int rl0 = (warp - (k0 * RC) % DS_TW + DS_TW) % DS_TW + DS_TW * half;
+                    const int rl1 = (warp - (k1 * RC) % DS_TW + DS_TW) % DS_TW + DS_TW * half;
                     const bool v0 = rl0 < rows0, v1 = rl1 < rows1;
-                    if (v0 || v1) {
-                        const uint8_t *wa = stage_base + (size_t)(g0 % S) * DS_STAGE_STRIDE + (size_t)rl0 * job.row_bytes;
-                        const uint8_t *wb = stage_base + (size_t)(g1 % S) * DS_STAGE_STRIDE + (size_t)rl1 * job.row_bytes;
-                        if (!v0) wa = wb;
-                        if (!v1) wb = wa;
+                    if (__any_sync(0xffffffffu, v0 || v1)) {
+                        const uint8_t *base0 = stage_base + (size_t)(g0 % S) * DS_STAGE_STRIDE;
+                        const uint8_t *base1 = two ? stage_base + (size_t)(g1 % S) * DS_STAGE_STRIDE : base0;
+                        const uint8_t *wa = v0 ? base0 + (size_t)rl0 * job.row_bytes : (v1 ? base1 + (size_t)rl1 * job.row_bytes : base0);
+                        const uint8_t *wb = v1 ? base1 + (size_t)rl1 * job.row_bytes : wa;
                         float mine[1] = {0.0f};
-                        rows2_q4_k<1>(wa, wb, a, ph.nb, lane, mine);
+                        if (halves) rows2_q4_k<1, 8>(wa, wb, a, ph.nb, hl, mine);
+                        else rows2_q4_k<1>(wa, wb, a, ph.nb, hl, mine);
                         float v = mine[0];
                         v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
                         v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
                         v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 8));
-                        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 16));
-                        const int f = lane == 0 ? r0 + c0 * RC + rl0 : r0 + c1 * RC + rl1;
-                        if (lane == 0 ? v0 : (lane == 1 && v1)) job.out[f] = v;
+                        if (!halves) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 16));
+                        const float other = __shfl_down_sync(0xffffffffu, v, 1);  // at lane 0 of a (half) warp: the second row's
+                        if (glu) {
+                            if (hl == 0 && v0) job.out[r0 + k0 * RC + rl0] = __fmul_rn(__fdividef(v, __fadd_rn(1.0f, __expf(-v))), other);
+                        } else {
+                            if (hl == 0 && v0) job.out[r0 + k0 * RC + rl0] = v;
+                            if (hl == 1 && v1) job.out[r0 + k1 * RC + rl1] = v;
+                        }
                     }
                     __syncwarp();
                     if (lane == 0) {
@@ -540,7 +561,7 @@ static int ds_gcd(int a, int b) { return b == 0 ? a : ds_gcd(b, a % b); }
 
 // One matmul phase: the CTAs dealt to its jobs in proportion to their bytes, chunk sizes chosen for the ring.
 static int ds_gemv_phase(DsPhase &ph, int sms, const float *x, int K, const GemvPrologue &pro, int n_jobs, const int *kinds,
-                         const void *const *W, const int *F, float *const *out) {
+                         const void *const *W, const int *F, float *const *out, const void *const *W2 = nullptr) {
     ph = DsPhase{};
     ph.type = DS_PHASE_GEMV;
     ph.n_jobs = n_jobs;
@@ -559,7 +580,9 @@ static int ds_gemv_phase(DsPhase &ph, int sms, const float *x, int K, const Gemv
         unit[j] = 16 / ds_gcd(rb[j] % 16, 16);
         if (((long)F[j] * rb[j]) & 15) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "decode plan: weight matrix is not a whole number of 16-byte pieces");
         if ((long)unit[j] * rb[j] > DS_CHUNK_BYTES || unit[j] > DS_TW) return set_error(MCU_ERROR_NOT_IMPLEMENTED, "decode plan: rows too long for the ring");
-        bytes[j] = (double)F[j] * rb[j];
+        const bool glu = W2 != nullptr && W2[j] != nullptr;
+        if (glu && (kinds[j] != KIND_Q4_K || ((uintptr_t)W2[j] & 15))) return set_error(MCU_ERROR_INVALID_ARGUMENT, "decode plan: a gated pair is two aligned Q4_K matrices");
+        bytes[j] = (double)F[j] * rb[j] * (glu ? 2.0 : 1.0);
         total += bytes[j];
     }
     if (sms < n_jobs) return set_error(MCU_ERROR_INVALID_OPERATION, "decode plan: fewer SMs than weight matrices");
@@ -585,6 +608,7 @@ static int ds_gemv_phase(DsPhase &ph, int sms, const float *x, int K, const Gemv
     for (int j = 0; j < n_jobs; ++j) {
         DsJob &g = ph.job[j];
         g.W = (const uint8_t *)W[j];
+        g.W2 = W2 != nullptr ? (const uint8_t *)W2[j] : nullptr;
         g.out = out[j];
         g.F = F[j];
         g.kind = kinds[j];
@@ -592,7 +616,8 @@ static int ds_gemv_phase(DsPhase &ph, int sms, const float *x, int K, const Gemv
         int rpc = (F[j] + ctas[j] - 1) / ctas[j];
         g.rows_per_cta = (rpc + unit[j] - 1) / unit[j] * unit[j];
         int rc = DS_CHUNK_BYTES / rb[j];
-        if (rc > DS_TW) rc = DS_TW;
+        const int cap = kinds[j] == KIND_Q4_K && ph.nb <= DS_HALF_NB ? 2 * DS_TW : DS_TW;  // rows a pass of the warps takes
+        if (rc > cap) rc = cap;
         rc = rc / unit[j] * unit[j];
         g.rows_per_chunk = rc;
         g.cta_begin = begin;
@@ -669,7 +694,18 @@ int mcu_decode_plan_create(mcu_context_t *ctx, const mcu_decode_plan_desc_t *d, 
             phases.push_back(ph);
             pending = d->proj;
         }
-        {
+        const bool gated = lw.kind_gate == KIND_Q4_K && lw.kind_up == KIND_Q4_K;  // silu(gate) * up formed where the rows are
+        if (gated) {
+            DsPhase ph;
+            const int kinds[1] = {KIND_Q4_K};
+            const void *W[1] = {lw.gate}, *W2[1] = {lw.up};
+            const int F[1] = {FF};
+            float *o[1] = {d->gate};
+            const GemvPrologue g = add_norm(lw.ffn_norm, true);
+            if (int rc = ds_gemv_phase(ph, sms, xs[cur], D, g, 1, kinds, W, F, o, W2)) return rc;
+            phases.push_back(ph);
+            cur = 1 - cur;
+        } else {
             DsPhase ph;
             const int kinds[2] = {lw.kind_gate, lw.kind_up};
             const void *W[2] = {lw.gate, lw.up};
@@ -687,9 +723,11 @@ int mcu_decode_plan_create(mcu_context_t *ctx, const mcu_decode_plan_desc_t *d, 
             const int F[1] = {D};
             float *o[1] = {d->proj};
             GemvPrologue g;
-            g.op = GEMV_PRO_SWIGLU;
-            g.aux = d->up;
-            g.ld_aux = FF;
+            if (!gated) {
+                g.op = GEMV_PRO_SWIGLU;
+                g.aux = d->up;
+                g.ld_aux = FF;
+            }
             if (int rc = ds_gemv_phase(ph, sms, d->gate, FF, g, 1, kinds, W, F, o)) return rc;
             phases.push_back(ph);
             pending = d->proj;

@@ -601,11 +601,13 @@ __device__ __forceinline__ void q4k_scales_of_half(const uint4 &hdr, int h, uint
     mn4 = h == 0 ? (hdr.z & 0x3F3F3F3Fu) : (((hdr.w >> 4) & 0x0F0F0F0Fu) | (((hdr.z >> 6) & 0x03030303u) << 4));
 }
 
-template <int T>
+// SUBS = 8: the two halves of a warp work on a row pair each (w0 / w1 are per-lane values, `lane` the lane within the
+// half), eight blocks per round -- for rows of at most eight blocks, where sixteen lanes would have nothing to do.
+template <int T, int SUBS = 16>
 __device__ __forceinline__ void rows2_q4_k(const uint8_t *w0, const uint8_t *w1, const ActSmem &a, int nb, int lane,
                                            float (&mine)[T]) {
     const int sub = lane >> 1, h = lane & 1;
-    for (int b0 = 0; b0 < nb; b0 += 16) {
+    for (int b0 = 0; b0 < nb; b0 += SUBS) {
         const int blk = b0 + sub;
         const bool ok = blk < nb;
         int p[2][T], s[2][T];
