@@ -14,6 +14,12 @@
 //     32-position tiles (scores with one position per lane, P V with head_dim / 32 dimensions per lane), the states
 //     merged through shared memory.  Made for the short contexts of single-sequence decoding: with thousands of
 //     cached positions a few dozen SMs read the whole cache of a layer, and the five-launch layer is the faster one.
+// What the phases cost is latency, not bandwidth, and the kernel is built around that: the phase descriptors travel
+// through shared memory one phase ahead (read from global memory at the start of a phase their lines were dependent
+// trips to L2), the next phase's norm weights are requested a phase ahead (used once per step, they come from HBM),
+// nothing relies on L1 (with ~190 KB of shared memory configured it is a few tens of kilobytes: per-thread stack frames
+// and re-read V rows went to L2 every time), gate and up are one gated job so that silu(gate) * up is formed where the
+// two dot products meet, and rows of at most eight blocks are taken two pairs per warp.
 // Every wait is bounded: a barrier or ring wait that runs out sets the error flag and an abort word that all CTAs
 // poll, and the kernel returns.
 #define MCU_ACT_LOAD(ptr) __ldcg(ptr)  // activations are written by other CTAs of this same launch
@@ -134,9 +140,8 @@ __device__ __forceinline__ bool grid_wait(const DsParams &p, int phase) {
 // this much shared memory configured it is a few tens of kilobytes.  Loops stay rolled where they can: every piece of
 // code runs once per layer, so its size is part of what the step waits for.
 // ---------------------------------------------------------------------------------------------
-#define DS_DBG(k) do { if (dbg != nullptr && threadIdx.x == 0) dbg[k] = global_ns(); } while (0)
 template <int HD>
-__device__ __forceinline__ void attention_head(const DsParams &p, int layer, int qh, float *sm, unsigned long long *dbg) {
+__device__ __forceinline__ void attention_head(const DsParams &p, int layer, int qh, float *sm) {
     constexpr int HALF = HD / 2, DPL = HD / 32, NTH = DS_TW * 32, SW = HD + 2;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gsize = p.n_q_heads / p.n_kv_heads, h = qh / gsize;
@@ -195,9 +200,7 @@ __device__ __forceinline__ void attention_head(const DsParams &p, int layer, int
         return 0xFFFFFFFFu;
     };
     uint32_t tb_next = warp < DS_AW && warp < n_tiles ? block_of(warp) : 0xFFFFFFFFu;  // in flight across the barrier
-    DS_DBG(0);
     asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
-    DS_DBG(1);
 
     // ---- 2. tiles ----
     if (warp < DS_AW) {
@@ -300,9 +303,7 @@ __device__ __forceinline__ void attention_head(const DsParams &p, int layer, int
 #pragma unroll
         for (int d = 0; d < DPL; ++d) st[2 + lane * DPL + d] = acc[d];
     }
-    DS_DBG(2);
     asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
-    DS_DBG(3);
 
     // ---- 3. merge, in warp order ----
     if (warp == 0) {
@@ -326,7 +327,6 @@ __device__ __forceinline__ void attention_head(const DsParams &p, int layer, int
 #pragma unroll
         for (int d = 0; d < DPL; ++d) p.att[(size_t)qh * HD + lane * DPL + d] = L > 0.0f ? __fdividef(o[d], L) : 0.0f;
     }
-    DS_DBG(4);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -418,8 +418,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
             asm volatile("prefetch.global.L2 [%0];" ::"l"((const char *)ph.next_norm_w + 128 * threadIdx.x));
         if (ph.type == DS_PHASE_ATTN) {
             if (cta < p.n_q_heads) {  // one CTA per query head; the others go straight to the barrier
-                if (p.head_dim == 64) attention_head<64>(p, ph.layer, cta, (float *)act_base, cta == 0 && p.stamps != nullptr ? p.stamps + 3 * p.n_phases + 1 + 8 * ph_i : nullptr);
-                else attention_head<128>(p, ph.layer, cta, (float *)act_base, nullptr);
+                if (p.head_dim == 64) attention_head<64>(p, ph.layer, cta, (float *)act_base);
+                else attention_head<128>(p, ph.layer, cta, (float *)act_base);
             }
         } else {
             const DsJob &job = job_of(ph, cta);
@@ -758,8 +758,8 @@ int mcu_decode_plan_create(mcu_context_t *ctx, const mcu_decode_plan_desc_t *d, 
     const size_t sync_words = 2;
     cudaError_t e = cudaMalloc((void **)&pl->phases_dev, phases.size() * sizeof(DsPhase));
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->sync_dev, sync_words * sizeof(uint32_t));
-    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->stamps_dev, (11 * phases.size() + 1) * sizeof(unsigned long long));
-    if (e == cudaSuccess) e = cudaMemset(pl->stamps_dev, 0, (11 * phases.size() + 1) * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->stamps_dev, (3 * phases.size() + 1) * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemset(pl->stamps_dev, 0, (3 * phases.size() + 1) * sizeof(unsigned long long));
     if (e == cudaSuccess) e = cudaMemcpy(pl->phases_dev, phases.data(), phases.size() * sizeof(DsPhase), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemset(pl->sync_dev, 0, sync_words * sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pl->smem);
@@ -818,7 +818,7 @@ int mcu_decode_plan_run(mcu_decode_plan_t *pl) {
 
 int mcu_decode_plan_phase_times(mcu_decode_plan_t *pl, unsigned long long *out, size_t capacity, size_t *n_out) {
     if (pl == nullptr || n_out == nullptr) return set_error(MCU_ERROR_INVALID_ARGUMENT, "null plan");
-    const size_t n = 11 * (size_t)pl->params.n_phases + 1;
+    const size_t n = 3 * (size_t)pl->params.n_phases + 1;
     *n_out = n;
     if (out == nullptr || capacity < n) return MCU_SUCCESS;  // the count alone
     DS_CUDA(cudaSetDevice(context_device(pl->ctx)));

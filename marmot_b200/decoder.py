@@ -333,6 +333,10 @@ class Decoder:
 
         if os.environ.get("MARMOT_DECODER_NO_STEP_KERNEL"):  # diagnostic switch: the five-launch layer instead
             return None
+        # The kernel's attention gives a query head one CTA: right for the contexts of single-sequence decoding, slower
+        # than the five-launch layer's attention once a layer's cache runs to thousands of positions.
+        if self.max_blocks * self.block_size > int(os.environ.get("MARMOT_DECODER_STEP_KERNEL_MAX_CTX", "2560")):
+            return None
         key = (meta.data_ptr(), positions.data_ptr(), logits.data_ptr())
         if key in self._plans:
             return self._plans[key]

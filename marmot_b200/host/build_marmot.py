@@ -246,8 +246,10 @@ def build(marmot_root: Path | None = None, jobs: int | None = None, keep_generat
             msg = "\n".join(f"{src}: {err}" for src, err in failed)
             raise RuntimeError(f"{len(failed)} translation units failed to compile:\n{msg}")
         tmp = stage / OUT.name
+        # -Bsymbolic: the library's own marmot_* calls bind to its own definitions, also in a process where another
+        # marmot build was loaded with global symbols first (a CPU-only one would otherwise answer the dispatch)
         subprocess.run(["gcc", "-shared", "-o", str(tmp), *objs, f"-L{PKG}", "-lmarmot_cuda", "-Wl,-rpath,$ORIGIN", "-lm",
-                        "-pthread", "-Wl,--allow-shlib-undefined"], check=True)
+                        "-pthread", "-Wl,--allow-shlib-undefined", "-Wl,-Bsymbolic"], check=True)
         shutil.copyfile(tmp, OUT)
     finally:
         shutil.rmtree(stage, ignore_errors=True)

@@ -5,6 +5,7 @@ self-ending command that a profiler (ncu) or a quick timing wraps.
     python -m marmot_b200.profile_case --op attention --seqs 64 --ctx 2048 --layers 4 --iters 2 --time
     python -m marmot_b200.profile_case --op attention --decode --seqs 1 --ctx 250 --q-heads 32 --kv-heads 4 --head-dim 64
     python -m marmot_b200.profile_case --op layer --layers 22 --iters 2 --time      (the decode step's five kernels)
+    python -m marmot_b200.profile_case --op step --ctx 250 --iters 3 --time         (one-token step: the persistent kernel)
 
 The weights rotate over ``--copies`` distinct matrices so that a memory-bound kernel reads from HBM rather
 than from L2.  With ``--time`` the calls are also captured in a CUDA graph and replayed, and the average
@@ -137,6 +138,77 @@ def moe_case(args) -> None:
     ctx.close()
 
 
+def step_case(args) -> None:
+    """One-token decode steps of the TinyLlama-1.1B shape (random-init weights, 128-token prompt prefilled, the token at
+    position `--ctx`) through Decoder.step: the persistent decode-step kernel.  Prints the kernel's own timeline (CTA 0's
+    clock at every phase start; per matmul phase also when the activations were packed and when the rows were done),
+    medians over the layers, and with --time the device time per step in CUDA-graph replay."""
+    import torch
+
+    from .decoder import TINYLLAMA_1B, Decoder
+
+    dev = torch.device("cuda", 0)
+    ctx = Context(0)
+    shape = TINYLLAMA_1B
+    n_prompt = min(128, args.ctx)
+    dec = Decoder(ctx, shape, max_seqs=1, max_ctx=max(args.ctx, n_prompt) + 64, block_size=16, kv_dtype=torch.float16, seed=5)
+    stream = torch.cuda.Stream(dev)
+    ctx.set_stream(stream.cuda_stream)
+    rng = np.random.default_rng(3)
+    with torch.cuda.stream(stream):
+        ids = torch.from_numpy(rng.integers(0, shape.vocab, n_prompt).astype(np.int32)).to(dev)
+        pos = np.arange(n_prompt, dtype=np.int32)
+        dec.step(ids, torch.from_numpy(dec.token_meta([0] * n_prompt, pos)).to(dev), torch.from_numpy(pos).to(dev))
+        ids = torch.from_numpy(rng.integers(0, shape.vocab, 1).astype(np.int32)).to(dev)
+        pos_np = np.asarray([args.ctx], dtype=np.int32)
+        pos = torch.from_numpy(pos_np).to(dev)
+        meta = torch.from_numpy(dec.token_meta(np.arange(1), pos_np)).to(dev)
+        logits = torch.empty((1, dec.local_vocab), dtype=torch.float32, device=dev)
+
+        def one():
+            dec.step(ids, meta, pos, logits_out=logits, decode=True)
+
+        l0 = ctx.launch_count()
+        one()
+        launches = ctx.launch_count() - l0
+        for _ in range(max(1, args.iters) - 1):
+            one()
+        torch.cuda.synchronize()
+        plan = next((pl for pl in dec._plans.values() if pl is not None), None)
+        print(f"step d={shape.d} ffn={shape.ffn} layers={shape.layers} ctx={args.ctx}: {launches} kernel launches per step, "
+              f"{'persistent kernel' if plan is not None else 'five launches per layer'}")
+        if plan is not None:
+            t = np.array(plan.phase_times(), dtype=np.int64)
+            n = (len(t) - 1) // 3
+            L = shape.layers
+            dur = np.diff(t[:n + 1]) / 1e3
+            det = (t[n + 1:].reshape(n, 2) - t[:n, None]) / 1e3
+            names = ["q/k/v", "attention", "o proj", "gate/up", "down"]
+            per, pk, wk = dur[:5 * L].reshape(L, 5), det[:5 * L, 0].reshape(L, 5), det[:5 * L, 1].reshape(L, 5)
+            print("phase        us   packed at   rows done at   (medians over the layers, CTA 0)")
+            for i, name in enumerate(names):
+                packed = f"{np.median(pk[:, i]):9.2f}" if i != 1 else "        -"
+                print(f"{name:10s} {np.median(per[:, i]):5.2f}   {packed}   {np.median(wk[:, i]):9.2f}")
+            print(f"{'output':10s} {dur[5 * L]:5.2f}   {det[5 * L, 0]:9.2f}   {det[5 * L, 1]:9.2f}")
+            print(f"kernel, first phase start to end: {(t[n] - t[0]) / 1e3:.1f} us")
+        if args.time:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                one()
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(100):
+                g.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            print(f"{e0.elapsed_time(e1) * 10:.1f} us per step in graph replay")
+    ctx.synchronize()
+    ctx.set_stream(0)
+
+
 def layer_case(args) -> None:
     """The five launches of one decoder layer in a fused decode step, TinyLlama-1.1B shape by default (d 2048, FFN 5632,
     32 / 4 heads of 64; Q4_K with Q6_K for v and down), -T tokens of one context length each, `--layers` layers with
@@ -216,7 +288,7 @@ def layer_case(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--op", default="linear", choices=["linear", "attention", "moe", "layer"])
+    ap.add_argument("--op", default="linear", choices=["linear", "attention", "moe", "layer", "step"])
     ap.add_argument("--only", default="", help="layer: comma-separated subset of qkv,attn,wo,gateup,down")
     ap.add_argument("--decode", action="store_true", help="attention: the one-launch decode form (RoPE + append + merge folded in)")
     ap.add_argument("--experts", type=int, default=8, help="moe: experts")
@@ -243,6 +315,8 @@ def main() -> None:
         return moe_case(args)
     if args.op == "layer":
         return layer_case(args)
+    if args.op == "step":
+        return step_case(args)
 
     import torch
 
