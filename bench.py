@@ -734,7 +734,7 @@ def main():
                      "traffic": NCU_TRAFFIC_BYTES, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of "
                      "one launch of this kernel and shape (profiles/gemv_stream_q4k_T1_K4096_F4096.md)",
                      "peak_source": peak_kind, "frac_of_nominal_8TBs": achieved / 8000.0,
-                     "algorithmic_bytes": ALG_BYTES, "kernel": "gemv_stream_kernel<Q4_K, T=1, TW=14, TEAMS=1, MINB=2>",
+                     "algorithmic_bytes": ALG_BYTES, "kernel": "gemv_stream_kernel<Q4_K, T=1, TW=14, TEAMS=1, MINB=2, PRO=none>",
                      "us_per_launch": per_launch_s * 1e6},
         "clocks": clocks,
     }
