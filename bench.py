@@ -152,7 +152,7 @@ def workload_config(copies: int) -> dict:
 
 def time_other_regimes(ctx, dev):
     """Short CUDA-graph timings of the other regimes of the path (not the headline): large-F GEMVs of the three
-    formats, the batched-decode shape and the Q8_0 prefill GEMM of BASELINE config 2.  Each entry is one
+    formats (F = 28672, and the 128256-row output projection of the Llama-3 shape), the batched-decode shape and the Q8_0 prefill GEMM of BASELINE config 2.  Each entry is one
     `mcu_linear` call (activation quantisation included), rotating over weight copies larger than L2."""
     import torch
 
@@ -167,6 +167,7 @@ def time_other_regimes(ctx, dev):
     ctx.set_stream(stream.cuda_stream)
     rng = np.random.default_rng(11)
     for name, T, K, F, copies in [("q4_k", 1, 4096, 28672, 4), ("q6_k", 1, 4096, 28672, 4), ("q8_0", 1, 4096, 28672, 4),
+                                  ("q4_k", 1, 4096, 128256, 2), ("q6_k", 1, 4096, 128256, 1),  # Llama-3 output projection
                                   ("q4_k", 8, 4096, 14336, 8), ("q4_k", 64, 4096, 14336, 4),
                                   ("q8_0", 512, 4096, 14336, 2), ("q4_k", 512, 4096, 14336, 2)]:
         kind = KIND_BY_NAME[name]

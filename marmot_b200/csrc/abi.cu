@@ -757,7 +757,20 @@ int mcu_linear_multi(mcu_context_t *ctx, const float *x_dev, size_t ldx, size_t 
     float *h = nullptr;
     {
         std::lock_guard<std::mutex> lock(ctx->mu);
-        if ((ctx->regime == MCU_REGIME_AUTO || ctx->regime == MCU_REGIME_GEMV) && T <= (size_t)GEMV_MAX_T &&
+        const bool contiguous = ldx == K && (pr.aux_dev == nullptr || pr.ld_aux == K) && (gp.x_out == nullptr || pr.ld_x_out == K);
+        // Five to eight tokens over large K-quant matrices: the dp4a kernel is bound by its integer dots there (8 tokens,
+        // 2 x 14336 x 4096 Q4_K: 73 us with the prologue folded in, 29 us on the integer-MMA kernel), so the prologue runs
+        // as a kernel of its own and the matmuls take mcu_linear's regimes.  Small matrices keep the one-launch form.
+        size_t w_total = 0;
+        bool k_quants = true;
+        for (size_t j = 0; j < n_jobs; ++j) {
+            w_total += jobs[j].F * mcu_row_bytes(jobs[j].kind, K);
+            k_quants = k_quants && (jobs[j].kind == KIND_Q4_K || jobs[j].kind == KIND_Q6_K);
+        }
+        static const bool no_i8 = getenv("MARMOT_CUDA_NO_I8MMA") != nullptr;  // diagnostic switch, as in linear_locked
+        const bool integer_mma_pays = ctx->regime == MCU_REGIME_AUTO && !no_i8 && T >= 5 && k_quants &&
+            w_total >= ((size_t)24 << 20) && (pr.op == MCU_PROLOGUE_NONE || contiguous);
+        if (!integer_mma_pays && (ctx->regime == MCU_REGIME_AUTO || ctx->regime == MCU_REGIME_GEMV) && T <= (size_t)GEMV_MAX_T &&
             gemv_stream_jobs_supported(specs, (int)n_jobs, (int)T, (int)K, gp)) {
             MCU_CUDA(launch_gemv_stream_jobs(specs, (int)n_jobs, x_dev, (int)ldx, (int)T, (int)K, gp, ctx->dev_err, ctx->stream));
             count_launches(1);
@@ -765,7 +778,6 @@ int mcu_linear_multi(mcu_context_t *ctx, const float *x_dev, size_t ldx, size_t 
         }
         // More than eight tokens on the tensor cores: one staging launch (the prologue folded into it) feeds every
         // matmul that wants the same staging; weights of the other block format class get a second one.
-        const bool contiguous = ldx == K && (pr.aux_dev == nullptr || pr.ld_aux == K) && (gp.x_out == nullptr || pr.ld_x_out == K);
         bool tensor = (ctx->regime == MCU_REGIME_AUTO || ctx->regime == MCU_REGIME_GEMM) && T > 16 &&
             (pr.op == MCU_PROLOGUE_NONE || contiguous);
         for (size_t j = 0; j < n_jobs && tensor; ++j)

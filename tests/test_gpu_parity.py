@@ -639,6 +639,31 @@ def test_linear_multi_unaligned_rows_and_no_norm_weight(ctx, oracle):
         assert max_rel_err(o.cpu().numpy()[:, :F], oracle.linear(k, h, W, F)) <= TOL_FP32
 
 
+def test_linear_multi_large_matrices_at_a_handful_of_tokens(ctx, oracle):
+    """Five to eight tokens over tens of megabytes of K-quant weights: the prologue runs as a kernel of its own and the
+    matmuls take the integer-MMA regime (the dp4a kernel is bound by its dots there); same results as the oracle."""
+    import torch
+
+    T, K, F = 6, 4096, 5632  # 2 x 5632 x 2304 B = 26 MB
+    rng = np.random.default_rng(606)
+    kinds, Ws, x, xd, outs = _multi_case(rng, ("q4_k", "q4_k"), T, K, (F, F))
+    aux = rng.normal(0, 1, (T, K)).astype(np.float32)
+    w = rng.normal(1, 0.2, K).astype(np.float32)
+    x_out = torch.zeros((T, K), dtype=torch.float32, device="cuda")
+    jobs = [(k, ctx.upload(W), F, o[:, :F]) for k, W, o in zip(kinds, Ws, outs)]
+    l0 = ctx.launch_count()
+    ctx.linear_multi(xd, jobs, ("add_rmsnorm", torch.from_numpy(aux).cuda(), torch.from_numpy(w).cuda(), 1e-5, 0.0, x_out))
+    ctx.synchronize()
+    assert ctx.launch_count() - l0 > 1  # not the one-launch form
+    xs = (x + aux).astype(np.float32)
+    assert np.array_equal(x_out.cpu().numpy(), xs)
+    h = oracle.rmsnorm(xs, w, 1e-5)
+    for k, W, o in zip(kinds, Ws, outs):
+        got = o.cpu().numpy()
+        assert max_rel_err(got[:, :F], oracle.linear(k, h, W, F)) <= TOL_FP32
+        assert np.all(got[:, F:] == 7.0)
+
+
 def test_linear_multi_general_form(ctx, oracle):
     """More than eight tokens, or kinds that do not share an activation format: the prologue runs as its own kernel,
     the matmuls follow; same results."""
