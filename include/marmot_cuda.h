@@ -112,6 +112,9 @@ uint64_t mcu_kernel_launch_count(const mcu_context_t *ctx);
 /* ---- device memory: alloc / free / memcpy slots of marmot_device_ops (include/marmot/device.h:47-56) ---- */
 int mcu_malloc(mcu_context_t *ctx, size_t bytes, void **out_dev);
 int mcu_free(mcu_context_t *ctx, void *dev);
+/* mcu_memcpy_to_device returns when src_host may be reused; the copy itself is ordered on the context's stream before
+ * everything enqueued after it (copies of up to 64 KB go through page-locked slots of the context and do not wait for
+ * the device; larger ones do).  mcu_memcpy_to_host returns with the bytes in dst_host. */
 int mcu_memcpy_to_device(mcu_context_t *ctx, void *dst_dev, const void *src_host, size_t bytes);
 int mcu_memcpy_to_host(mcu_context_t *ctx, void *dst_host, const void *src_dev, size_t bytes);
 

@@ -68,6 +68,9 @@ struct Buffer {
 
 using namespace mcu;
 
+constexpr int PIN_SLOTS = 16;
+constexpr size_t PIN_SLOT_BYTES = 64 * 1024;
+
 struct mcu_context {
     int device = 0;
     cudaStream_t own_stream = nullptr;
@@ -88,6 +91,14 @@ struct mcu_context {
     size_t moe_last_routes = 0, moe_last_experts = 0;  // shape of the last MoE call (mcu_moe_last_buffers)
     int moe_last_grouped = 0;
     int *dev_err = nullptr;  // set by kernels whose bounded device-side waits ran out
+    int *err_host = nullptr; // page-locked word the flag is copied into on a synchronize
+    // Small host <-> device copies go through page-locked slots owned by the context: an upload is a host memcpy into a
+    // slot plus an asynchronous copy (the caller's buffer is free on return and nothing waits for the copy engine), a
+    // download lands in a slot and is copied out after the one synchronize it needs anyway.
+    uint8_t *pin_ring = nullptr;
+    cudaEvent_t pin_event[PIN_SLOTS] = {};
+    bool pin_used[PIN_SLOTS] = {};
+    int pin_next = 0;
 };
 
 static bool stream_is_capturing(cudaStream_t s) {
@@ -118,9 +129,22 @@ static int ensure(mcu_context *ctx, Buffer &b, size_t bytes) {
 }
 
 // After a synchronize: did a kernel give up on a bounded wait?
-static int check_device_error(mcu_context *ctx) {
-    int flag = 0;
-    MCU_CUDA(cudaMemcpy(&flag, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
+// Wait for the stream `s` of the context and report a device-side error flag, if one was set.  The flag travels with
+// the wait (an asynchronous copy into a page-locked word enqueued ahead of the synchronize): a separate blocking copy
+// of four bytes cost ten microseconds on every synchronising call.
+static int sync_and_check(mcu_context *ctx, cudaStream_t s) {
+    if (ctx->err_host == nullptr) {
+        MCU_CUDA(cudaStreamSynchronize(s));
+        int flag = 0;
+        MCU_CUDA(cudaMemcpy(&flag, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
+        if (flag == 0) return MCU_SUCCESS;
+        cudaMemset(ctx->dev_err, 0, sizeof(int));
+        if (flag == 40) return fail(MCU_ERROR_INVALID_ARGUMENT, "MoE expert id is out of range (found by an earlier call)");
+        return fail(MCU_ERROR_INVALID_OPERATION, "a device-side wait timed out (code %d)", flag);
+    }
+    MCU_CUDA(cudaMemcpyAsync(ctx->err_host, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost, s));
+    MCU_CUDA(cudaStreamSynchronize(s));
+    const int flag = *(volatile int *)ctx->err_host;
     if (flag != 0) {
         cudaMemset(ctx->dev_err, 0, sizeof(int));
         if (flag == 40) return fail(MCU_ERROR_INVALID_ARGUMENT, "MoE expert id is out of range (found by an earlier call)");
@@ -216,6 +240,11 @@ int mcu_context_create(int device, mcu_context_t **out) {
     ctx->stream = ctx->own_stream;
     e = cudaMalloc(&ctx->dev_err, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->dev_err, 0, sizeof(int));
+    if (e == cudaSuccess && cudaHostAlloc((void **)&ctx->err_host, sizeof(int), cudaHostAllocDefault) != cudaSuccess) {
+        (void)cudaGetLastError();
+        ctx->err_host = nullptr;  // the flag is then fetched with a blocking copy
+    }
+    if (ctx->err_host != nullptr) *ctx->err_host = 0;
     if (e == cudaSuccess) e = cudaMalloc(&ctx->gemm_counters, GEMM_TMA_MAX_TILE_COUNTERS * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->gemm_counters, 0, GEMM_TMA_MAX_TILE_COUNTERS * sizeof(int));
     if (e != cudaSuccess) {
@@ -240,6 +269,12 @@ void mcu_context_destroy(mcu_context_t *ctx) {
     for (Buffer *b : bufs)
         if (b->ptr != nullptr) cudaFree(b->ptr);
     if (ctx->dev_err != nullptr) cudaFree(ctx->dev_err);
+    if (ctx->err_host != nullptr) cudaFreeHost(ctx->err_host);
+    if (ctx->pin_ring != nullptr) {
+        for (int i = 0; i < PIN_SLOTS; ++i)
+            if (ctx->pin_event[i] != nullptr) cudaEventDestroy(ctx->pin_event[i]);
+        cudaFreeHost(ctx->pin_ring);
+    }
     if (ctx->gemm_counters != nullptr) cudaFree(ctx->gemm_counters);
     if (ctx->own_stream != nullptr) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
@@ -326,8 +361,7 @@ int mcu_context_set_regime(mcu_context_t *ctx, int regime) {
 int mcu_synchronize(mcu_context_t *ctx) {
     if (int rc = check_ctx(ctx)) return rc;
     if (stream_is_capturing(ctx->stream)) return fail(MCU_ERROR_INVALID_OPERATION, "cannot synchronize during stream capture");
-    MCU_CUDA(cudaStreamSynchronize(ctx->stream));
-    return check_device_error(ctx);
+    return sync_and_check(ctx, ctx->stream);
 }
 
 int mcu_malloc(mcu_context_t *ctx, size_t bytes, void **out_dev) {
@@ -346,10 +380,46 @@ int mcu_free(mcu_context_t *ctx, void *dev) {
     return MCU_SUCCESS;
 }
 
+// The next page-locked slot, free for reuse (its last copy has completed), or nullptr when the ring cannot be had.
+static uint8_t *pin_slot(mcu_context *ctx, int *slot_out) {
+    if (ctx->pin_ring == nullptr) {
+        if (cudaHostAlloc((void **)&ctx->pin_ring, PIN_SLOTS * PIN_SLOT_BYTES, cudaHostAllocDefault) != cudaSuccess) {
+            (void)cudaGetLastError();
+            ctx->pin_ring = nullptr;
+            return nullptr;
+        }
+        for (int i = 0; i < PIN_SLOTS; ++i)
+            if (cudaEventCreateWithFlags(&ctx->pin_event[i], cudaEventDisableTiming) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return nullptr;
+            }
+    }
+    const int i = ctx->pin_next;
+    if (ctx->pin_event[i] == nullptr) return nullptr;
+    if (ctx->pin_used[i] && cudaEventSynchronize(ctx->pin_event[i]) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    ctx->pin_next = (i + 1) % PIN_SLOTS;
+    *slot_out = i;
+    return ctx->pin_ring + (size_t)i * PIN_SLOT_BYTES;
+}
+
 int mcu_memcpy_to_device(mcu_context_t *ctx, void *dst_dev, const void *src_host, size_t bytes) {
     if (int rc = check_ctx(ctx)) return rc;
     if (bytes == 0) return MCU_SUCCESS;
     if (dst_dev == nullptr || src_host == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "null pointer");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (bytes <= PIN_SLOT_BYTES && !stream_is_capturing(ctx->stream)) {
+        int slot = 0;
+        if (uint8_t *pin = pin_slot(ctx, &slot)) {
+            memcpy(pin, src_host, bytes);
+            MCU_CUDA(cudaMemcpyAsync(dst_dev, pin, bytes, cudaMemcpyHostToDevice, ctx->stream));
+            MCU_CUDA(cudaEventRecord(ctx->pin_event[slot], ctx->stream));
+            ctx->pin_used[slot] = true;
+            return MCU_SUCCESS;  // ordered before everything enqueued on the context's stream after it
+        }
+    }
     MCU_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
     MCU_CUDA(cudaStreamSynchronize(ctx->stream));
     return MCU_SUCCESS;
@@ -359,6 +429,17 @@ int mcu_memcpy_to_host(mcu_context_t *ctx, void *dst_host, const void *src_dev, 
     if (int rc = check_ctx(ctx)) return rc;
     if (bytes == 0) return MCU_SUCCESS;
     if (dst_host == nullptr || src_dev == nullptr) return fail(MCU_ERROR_INVALID_ARGUMENT, "null pointer");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (bytes <= PIN_SLOT_BYTES && !stream_is_capturing(ctx->stream)) {
+        int slot = 0;
+        if (uint8_t *pin = pin_slot(ctx, &slot)) {
+            MCU_CUDA(cudaMemcpyAsync(pin, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+            MCU_CUDA(cudaStreamSynchronize(ctx->stream));
+            ctx->pin_used[slot] = false;
+            memcpy(dst_host, pin, bytes);
+            return MCU_SUCCESS;
+        }
+    }
     MCU_CUDA(cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     MCU_CUDA(cudaStreamSynchronize(ctx->stream));
     return MCU_SUCCESS;
@@ -674,8 +755,7 @@ int mcu_vec_dot_host(mcu_context_t *ctx, int weight_kind, const void *weights_ho
                          nullptr, 1, s));
     count_launches(1);
     MCU_CUDA(cudaMemcpyAsync(result_host, ctx->out_stage.ptr, sizeof(float), cudaMemcpyDeviceToHost, s));
-    MCU_CUDA(cudaStreamSynchronize(s));  // the host vectors above must outlive the copies
-    return check_device_error(ctx);
+    return sync_and_check(ctx, s);  // the host vectors above must outlive the copies
 }
 
 int mcu_linear(mcu_context_t *ctx, int kind, const float *x_dev, size_t ldx, const void *w_dev, size_t T, size_t K,
@@ -893,8 +973,7 @@ int mcu_linear_host(mcu_context_t *ctx, int kind, const float *x_host, size_t ld
     if (out_map == nullptr)
         MCU_CUDA(cudaMemcpy2DAsync(out_host, ldo * sizeof(float), od, F * sizeof(float), F * sizeof(float), T,
                                    cudaMemcpyDeviceToHost, ctx->stream));
-    MCU_CUDA(cudaStreamSynchronize(ctx->stream));
-    return check_device_error(ctx);
+    return sync_and_check(ctx, ctx->stream);
 }
 
 int mcu_topk(mcu_context_t *ctx, const float *x_dev, size_t rows, size_t cols, size_t ldx, size_t k, float *values_dev,

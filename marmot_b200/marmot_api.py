@@ -319,10 +319,17 @@ class MarmotLibrary:
         out = np.empty((T, F), dtype=np.float32)
         keep = (tw, tx, to)
 
+        out_p, out_bytes = _p(out), out.nbytes
+        lib, ctx, check = self.lib, self.ctx, self._check
+        in_bytes = T * K * 4
+
         def run(x: np.ndarray) -> np.ndarray:
-            self._check(self.lib.marmot_tensor_copy_from_host_buffer(self.ctx, tx, _p(x), x.nbytes), "copy_from")
-            self._check(self.lib.marmot_linear(self.ctx, tx, tw, None, to), "marmot_linear")
-            self._check(self.lib.marmot_tensor_copy_to_host_buffer(self.ctx, to, _p(out), out.nbytes), "copy_to")
+            # x: C-contiguous float32 [T, K]; its address is taken without building a ctypes view of the array (that
+            # alone costs several microseconds per call, as much as the upload)
+            assert x.nbytes == in_bytes and x.dtype == np.float32 and x.flags.c_contiguous
+            check(lib.marmot_tensor_copy_from_host_buffer(ctx, tx, C.c_void_p(x.__array_interface__["data"][0]), in_bytes), "copy_from")
+            check(lib.marmot_linear(ctx, tx, tw, None, to), "marmot_linear")
+            check(lib.marmot_tensor_copy_to_host_buffer(ctx, to, out_p, out_bytes), "copy_to")
             return out
 
         run.tensors = keep
