@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 SHAPE = DecoderShape(layers=2, d=256, ffn=512, n_heads=4, n_kv_heads=2, head_dim=64, vocab=512, rope_theta=10000.0)
 
 
-def make_weights(rng):
+def make_weights(rng, SHAPE=SHAPE):
     """Block scales small enough that activations stay of order one (weight std about 1/sqrt(K)), as in a trained
     model: with the default block-space scales the attention scores reach the thousands, the softmax saturates and a
     1e-3 perturbation of a score flips whole attention rows."""
@@ -206,5 +206,52 @@ def test_one_token_step_kernel_matches_the_five_launch_layer(monkeypatch, prompt
             assert torch.equal(logits, eager)  # same position, same pool rows rewritten with the same values
         ctx.synchronize()
         ctx.set_stream(0)
+    finally:
+        ctx.close()
+
+
+@pytest.mark.parametrize("shape,ctx_len", [
+    # head_dim 128, four query heads on one KV head, FFN of six blocks
+    (DecoderShape(layers=2, d=512, ffn=1536, n_heads=4, n_kv_heads=1, head_dim=128, vocab=512, rope_theta=500000.0), 70),
+    # the row lengths of an 8B model: 16 blocks of hidden size (more blocks than consumer warps), 32 / 8 heads of 128
+    (DecoderShape(layers=1, d=4096, ffn=4352, n_heads=32, n_kv_heads=8, head_dim=128, vocab=256, rope_theta=500000.0), 33),
+    # eight query heads per KV head at head_dim 64, a context of more tiles than attention warps (16 > 15)
+    (DecoderShape(layers=1, d=512, ffn=768, n_heads=8, n_kv_heads=1, head_dim=64, vocab=256, rope_theta=10000.0), 500),
+])
+def test_one_token_step_kernel_on_other_shapes(monkeypatch, shape, ctx_len):
+    """The persistent decode-step kernel against the five-launch layer on shapes that take its other code paths."""
+    rng = np.random.default_rng(shape.d + ctx_len)
+    weights = make_weights(rng, shape)
+    ctx = Context(0)
+    try:
+        decs = [Decoder(ctx, shape, max_seqs=1, max_ctx=ctx_len + 16, block_size=16, kv_dtype=torch.float16, weights=weights)
+                for _ in range(2)]
+        n = min(ctx_len, 96)  # a prompt, then the pool filled up to ctx_len with the same random rows in both decoders
+        ids = torch.from_numpy(rng.integers(0, shape.vocab, n).astype(np.int32)).cuda()
+        pos_np = np.arange(n, dtype=np.int32)
+        for d in decs:
+            d.step(ids, torch.from_numpy(d.token_meta([0] * n, pos_np)).cuda(), torch.from_numpy(pos_np).cuda())
+        fill_k = (torch.randn(decs[0].kv_k.shape, device="cuda") * 0.5).half()
+        fill_v = (torch.randn(decs[0].kv_v.shape, device="cuda") * 0.5).half()
+        blocks_done = n // 16  # whole blocks the prompt wrote stay as they are
+        for d in decs:
+            d.kv_k[blocks_done + 1:] = fill_k[blocks_done + 1:]
+            d.kv_v[blocks_done + 1:] = fill_v[blocks_done + 1:]
+        tok = torch.tensor([3], dtype=torch.int32, device="cuda")
+        for step in range(3):
+            p = np.array([ctx_len + step], dtype=np.int32)
+            meta, pos = torch.from_numpy(decs[0].token_meta([0], p)).cuda(), torch.from_numpy(p).cuda()
+            l0 = ctx.launch_count()
+            got = decs[0].step(tok, meta, pos, decode=True).clone()
+            assert ctx.launch_count() - l0 == 3  # embedding gather, RoPE table, the persistent kernel
+            monkeypatch.setenv("MARMOT_DECODER_NO_STEP_KERNEL", "1")
+            want = decs[1].step(tok, meta, pos, decode=True).clone()
+            monkeypatch.delenv("MARMOT_DECODER_NO_STEP_KERNEL")
+            ctx.synchronize()
+            assert max_rel_err(got.cpu().numpy(), want.cpu().numpy()) <= 2e-4, step
+            assert int(got.argmax()) == int(want.argmax())
+            tok = want.argmax(dim=1).to(torch.int32)
+        for a, b in ((decs[0].kv_k, decs[1].kv_k), (decs[0].kv_v, decs[1].kv_v)):
+            assert torch.equal(a[:, 0], b[:, 0])
     finally:
         ctx.close()
