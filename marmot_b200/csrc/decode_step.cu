@@ -46,7 +46,7 @@ constexpr int DS_MAX_JOBS = 3;
 constexpr int DS_CHUNK_BYTES = 36 * 1024;                        // target size of a ring chunk (one or two rows per consumer warp)
 constexpr int DS_STAGE_STRIDE = DS_CHUNK_BYTES + 1024;           // a chunk + over-read slack, multiple of 128
 constexpr int DS_STAGES = 4;
-constexpr int DS_HALF_NB = 8;                  // Q4_K rows of at most this many blocks: two row pairs per warp (rows2_q4_k<1, 8>)
+constexpr int DS_HALF_NB = 8;                  // rows of at most this many blocks: each half of a warp takes its own (rows2_q4_k<1, 8>, row_q6_k<1, 8>)
 constexpr int DS_ACT_BYTES = 20 * 1024;        // packed activations of one token: K up to 17408 values
 constexpr int DS_ATTN_EXTRA_BYTES = 20 * 1024; // behind the activation area: with it the attention phase's queries and softmax states
 constexpr uint32_t DS_SPIN_LIMIT = 1u << 22;
@@ -493,6 +493,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
                     }
                 }
             } else {
+                // Q6_K: a row per warp and chunk; with short rows each half of the warp takes a row
+                const bool halves = ph.nb <= DS_HALF_NB;
+                const int half = halves ? lane >> 4 : 0, hl = halves ? lane & 15 : lane;
                 for (int c = 0; c < n_chunks; ++c) {
                     const int gc = cbase + c, st = gc % S;
                     if (!mbar_wait(&full[st], (uint32_t)((gc / S) & 1))) {
@@ -503,12 +506,20 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
                         break;
                     }
                     const int rows = min(RC, n_rows - c * RC);
-                    const int rl = (warp - (c * RC) % DS_TW + DS_TW) % DS_TW;
-                    if (rl < rows) {
+                    const int rl = (warp - (c * RC) % DS_TW + DS_TW) % DS_TW + DS_TW * half;
+                    const bool valid = rl < rows;
+                    if (__any_sync(0xffffffffu, valid)) {
+                        const uint8_t *wrow = stage_base + (size_t)st * DS_STAGE_STRIDE + (size_t)(valid ? rl : 0) * job.row_bytes;
                         float acc[1] = {0.0f};
-                        row_q6_k<1>(stage_base + (size_t)st * DS_STAGE_STRIDE + (size_t)rl * job.row_bytes, a, ph.nb, lane, acc);
-                        const float v = warp_sum(acc[0]);
-                        if (lane == 0) job.out[r0 + c * RC + rl] = v;
+                        if (halves) row_q6_k<1, 8>(wrow, a, ph.nb, hl, acc);
+                        else row_q6_k<1>(wrow, a, ph.nb, hl, acc);
+                        float v = acc[0];  // the order of warp_sum (with halves, its first step would add zeros)
+                        if (!halves) v += __shfl_xor_sync(0xffffffffu, v, 16);
+                        v += __shfl_xor_sync(0xffffffffu, v, 8);
+                        v += __shfl_xor_sync(0xffffffffu, v, 4);
+                        v += __shfl_xor_sync(0xffffffffu, v, 2);
+                        v += __shfl_xor_sync(0xffffffffu, v, 1);
+                        if (hl == 0 && valid) job.out[r0 + c * RC + rl] = v;
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty[st]);
@@ -616,7 +627,7 @@ static int ds_gemv_phase(DsPhase &ph, int sms, const float *x, int K, const Gemv
         int rpc = (F[j] + ctas[j] - 1) / ctas[j];
         g.rows_per_cta = (rpc + unit[j] - 1) / unit[j] * unit[j];
         int rc = DS_CHUNK_BYTES / rb[j];
-        const int cap = kinds[j] == KIND_Q4_K && ph.nb <= DS_HALF_NB ? 2 * DS_TW : DS_TW;  // rows a pass of the warps takes
+        const int cap = ph.nb <= DS_HALF_NB ? 2 * DS_TW : DS_TW;  // rows a pass of the warps takes
         if (rc > cap) rc = cap;
         rc = rc / unit[j] * unit[j];
         g.rows_per_chunk = rc;

@@ -503,11 +503,12 @@ __device__ __forceinline__ void row_q4_k(const uint8_t *wrow, const ActSmem &a, 
     }
 }
 
-// Q6_K: two lanes per super-block; lane h owns the 128-value half h.
-template <int T>
+// Q6_K: two lanes per super-block; lane h owns the 128-value half h.  SUBS = 8: each half of the warp works on a row of
+// its own (wrow is a per-lane value, `lane` the lane within the half), for rows of at most eight blocks.
+template <int T, int SUBS = 16>
 __device__ __forceinline__ void row_q6_k(const uint8_t *wrow, const ActSmem &a, int nb, int lane, float (&acc)[T]) {
     const int sub = lane >> 1, h = lane & 1;
-    for (int b0 = 0; b0 < nb; b0 += 16) {
+    for (int b0 = 0; b0 < nb; b0 += SUBS) {
         const int blk = b0 + sub;
         const bool ok = blk < nb;
         int p[T];
