@@ -30,6 +30,7 @@
 #include <cuda_fp16.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -49,7 +50,7 @@ constexpr int DS_STAGES = 4;
 constexpr int DS_HALF_NB = 8;                  // rows of at most this many blocks: each half of a warp takes its own (rows2_q4_k<1, 8>, row_q6_k<1, 8>)
 constexpr int DS_ACT_BYTES = 20 * 1024;        // packed activations of one token: K up to 17408 values
 constexpr int DS_ATTN_EXTRA_BYTES = 20 * 1024; // behind the activation area: with it the attention phase's queries and softmax states
-constexpr uint32_t DS_SPIN_LIMIT = 1u << 22;
+constexpr uint32_t DS_SPIN_LIMIT = 1u << 22;        // polls of the grid barrier before a CTA gives up (seconds)
 
 enum { DS_PHASE_GEMV = 0, DS_PHASE_ATTN = 1 };
 
@@ -96,6 +97,8 @@ struct DsParams {
     float *att;             // [n_q_heads * head_dim]
     int n_q_heads, n_kv_heads, head_dim, max_blocks, n_layers, block_shift, neox;
     float scale;
+    uint32_t spin_limit;         // polls of the grid barrier before a CTA gives up
+    int skip_arrive_phase;       // test hook: CTA 1 does not arrive after this phase, so that the others' waits run out (-1: off)
     unsigned long long *stamps;  // nanosecond clock of CTA 0: [n_phases + 1] phase starts and the end, then per phase
                                  // {activations packed (matmul phases), phase work done}; or null
 };
@@ -115,7 +118,7 @@ __device__ __forceinline__ void grid_arrive(uint32_t *sync) {
 // aligned 8-byte word, so one load per poll reads both.
 __device__ __forceinline__ bool grid_wait(const DsParams &p, int phase) {
     const uint32_t want = (uint32_t)(phase + 1) * gridDim.x;
-    for (uint32_t i = 0; i < DS_SPIN_LIMIT; ++i) {
+    for (uint32_t i = 0; i < p.spin_limit; ++i) {
         unsigned long long v;
         asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p.sync) : "memory");
         if ((uint32_t)(v >> 32) != 0u) return false;
@@ -374,10 +377,17 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
                 const bool glu = job.W2 != nullptr;
                 for (int c = 0; c < n_chunks; ++c) {
                     const int gc = cbase + c, st = gc % S, round = gc / S;
-                    if (round > 0 && !mbar_wait(&empty[st], (uint32_t)((round - 1) & 1))) {
-                        atomicExch(p.err, 32);
-                        atomicExch(p.sync + 1, 1u);
-                        return;
+                    if (round > 0) {  // a free slot; gives up when the consumers have (abort word) or after its own limit
+                        bool got = false;
+                        for (uint32_t i = 0; i < SPIN_LIMIT && !got; ++i) {
+                            got = mbar_try_wait(&empty[st], (uint32_t)((round - 1) & 1));
+                            if (!got && (i & 255u) == 255u && *(volatile uint32_t *)(p.sync + 1) != 0u) return;
+                        }
+                        if (!got) {
+                            atomicExch(p.err, 32);
+                            atomicExch(p.sync + 1, 1u);
+                            return;
+                        }
                     }
                     const int k = glu ? c >> 1 : c;  // row chunk
                     const uint8_t *mat = glu && (c & 1) ? job.W2 : job.W;
@@ -531,15 +541,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
         // this CTA is through the phase; a warp that gave up has set the abort word, which every CTA reads in its next wait
         asm volatile("bar.sync 1, %0;" ::"n"(NTH) : "memory");
         if (cta == 0 && threadIdx.x == 0 && p.stamps != nullptr) p.stamps[p.n_phases + 2 + 2 * ph_i] = global_ns();
-        if (threadIdx.x == 0) grid_arrive(p.sync);
+        if (threadIdx.x == 0 && !(ph_i == p.skip_arrive_phase && cta == 1)) grid_arrive(p.sync);
     }
-    // CTA 0 waits for everybody's last arrival and leaves the counter at zero for the next launch (nobody else waits on
-    // it any more)
-    if (threadIdx.x == 0 && cta == 0 && ok && grid_wait(p, p.n_phases - 1)) {
-        if (p.stamps != nullptr) p.stamps[p.n_phases] = global_ns();
-        p.sync[0] = 0u;
-        __threadfence();
-    }
+    // the end of the step on CTA 0's clock (the counter is zeroed by the host before every launch)
+    if (threadIdx.x == 0 && cta == 0 && ok && p.stamps != nullptr && grid_wait(p, p.n_phases - 1)) p.stamps[p.n_phases] = global_ns();
 }
 
 }  // namespace mcu
@@ -805,6 +810,11 @@ int mcu_decode_plan_create(mcu_context_t *ctx, const mcu_decode_plan_desc_t *d, 
     p.neox = d->rope_type == MCU_ROPE_NEOX ? 1 : 0;
     p.scale = d->attn_scale;
     p.stamps = pl->stamps_dev;
+    // Test hooks (host-side fault injection: no kernel traps or spins without a bound): a short barrier limit, and one
+    // CTA that skips one arrival so that the other CTAs' waits run out and the step ends with the error flag set.
+    const char *lim = getenv("MARMOT_DECODE_PLAN_SPIN_LIMIT"), *skip = getenv("MARMOT_DECODE_PLAN_TEST_SKIP_ARRIVE");
+    p.spin_limit = lim != nullptr && atoi(lim) > 0 ? (uint32_t)atoi(lim) : DS_SPIN_LIMIT;
+    p.skip_arrive_phase = skip != nullptr ? atoi(skip) : -1;
     *out = pl;
     return MCU_SUCCESS;
 }
@@ -822,6 +832,8 @@ int mcu_decode_plan_run(mcu_decode_plan_t *pl) {
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    // arrivals and abort word start from zero, also after a step that gave up
+    DS_CUDA(cudaMemsetAsync(pl->sync_dev, 0, 2 * sizeof(uint32_t), cfg.stream));
     DS_CUDA(cudaLaunchKernelEx(&cfg, decode_step_kernel, pl->params));
     count_launches(1);
     return MCU_SUCCESS;

@@ -255,3 +255,45 @@ def test_one_token_step_kernel_on_other_shapes(monkeypatch, shape, ctx_len):
             assert torch.equal(a[:, 0], b[:, 0])
     finally:
         ctx.close()
+
+
+def test_step_kernel_barrier_wait_runs_out_and_the_context_stays_usable(monkeypatch):
+    """Failure detection without a GPU fault: a host-side hook makes one CTA skip one arrival at the grid barrier, so the
+    other CTAs' bounded waits run out (a short limit for the test); the kernel returns with the error flag set, the next
+    synchronize reports it, and the same context and decoder then run the step correctly."""
+    from marmot_b200.runtime import MarmotCudaError
+
+    rng = np.random.default_rng(77)
+    weights = make_weights(rng)
+    ctx = Context(0)
+    try:
+        decs = [Decoder(ctx, SHAPE, max_seqs=1, max_ctx=64, block_size=16, kv_dtype=torch.float16, weights=weights) for _ in range(2)]
+        n = 5
+        ids = torch.from_numpy(rng.integers(0, SHAPE.vocab, n).astype(np.int32)).cuda()
+        pos_np = np.arange(n, dtype=np.int32)
+        for d in decs:
+            d.step(ids, torch.from_numpy(d.token_meta([0] * n, pos_np)).cuda(), torch.from_numpy(pos_np).cuda())
+        ctx.synchronize()
+        tok = torch.tensor([9], dtype=torch.int32, device="cuda")
+        p = np.array([n], dtype=np.int32)
+        meta, pos = torch.from_numpy(decs[0].token_meta([0], p)).cuda(), torch.from_numpy(p).cuda()
+        monkeypatch.setenv("MARMOT_DECODE_PLAN_SPIN_LIMIT", str(1 << 15))
+        monkeypatch.setenv("MARMOT_DECODE_PLAN_TEST_SKIP_ARRIVE", "3")  # after the fourth phase (gate/up of layer 0)
+        decs[0].step(tok, meta, pos, decode=True)
+        with pytest.raises(MarmotCudaError, match="timed out"):
+            ctx.synchronize()
+        monkeypatch.delenv("MARMOT_DECODE_PLAN_SPIN_LIMIT")
+        monkeypatch.delenv("MARMOT_DECODE_PLAN_TEST_SKIP_ARRIVE")
+        for plan in decs[0]._plans.values():  # a plan keeps the hooks it was created with
+            if plan is not None:
+                plan.close()
+        decs[0]._plans.clear()
+        got = decs[0].step(tok, meta, pos, decode=True).clone()
+        ctx.synchronize()
+        monkeypatch.setenv("MARMOT_DECODER_NO_STEP_KERNEL", "1")
+        want = decs[1].step(tok, meta, pos, decode=True).clone()
+        ctx.synchronize()
+        assert max_rel_err(got.cpu().numpy(), want.cpu().numpy()) <= 1e-4
+        assert int(got.argmax()) == int(want.argmax())
+    finally:
+        ctx.close()
