@@ -457,9 +457,11 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
                 // short rows each half of the warp takes such a pair.
                 const bool glu = job.W2 != nullptr, halves = ph.nb <= DS_HALF_NB;
                 const int half = halves ? lane >> 4 : 0, hl = halves ? lane & 15 : lane;
-                for (int jp = 0; 2 * jp < n_chunks; ++jp) {
-                    const int c0 = 2 * jp, c1 = c0 + 1;
-                    const bool two = c1 < n_chunks;
+                // all rows in one pass of the warps: every chunk on its own, a row per (half-)warp, no pairs
+                const bool single = !glu && n_rows <= DS_TW * (halves ? 2 : 1);
+                for (int c0 = 0; c0 < n_chunks; c0 += single ? 1 : 2) {
+                    const int c1 = c0 + 1, jp = c0 >> 1;
+                    const bool two = !single && c1 < n_chunks;
                     const int g0 = cbase + c0, g1 = cbase + c1;
                     bool ready = mbar_wait(&full[g0 % S], (uint32_t)((g0 / S) & 1));
                     if (ready && two) ready = mbar_wait(&full[g1 % S], (uint32_t)((g1 / S) & 1));
@@ -475,7 +477,22 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DsPara
                     const int rl0 = (warp - (k0 * RC) % DS_TW + DS_TW) % DS_TW + DS_TW * half;
                     const int rl1 = (warp - (k1 * RC) % DS_TW + DS_TW) % DS_TW + DS_TW * half;
                     const bool v0 = rl0 < rows0, v1 = rl1 < rows1;
-                    if (__any_sync(0xffffffffu, v0 || v1)) {
+                    if (!two && !glu) {
+                        // a lone chunk: one row per warp (or half of a warp) instead of a pair made of the row and itself
+                        if (__any_sync(0xffffffffu, v0)) {
+                            const uint8_t *wrow = stage_base + (size_t)(g0 % S) * DS_STAGE_STRIDE + (size_t)(v0 ? rl0 : 0) * job.row_bytes;
+                            float acc[1] = {0.0f};
+                            if (halves) row_q4_k<1, 8>(wrow, a, ph.nb, hl, acc);
+                            else row_q4_k<1>(wrow, a, ph.nb, hl, acc);
+                            float v = acc[0];
+                            if (!halves) v += __shfl_xor_sync(0xffffffffu, v, 16);
+                            v += __shfl_xor_sync(0xffffffffu, v, 8);
+                            v += __shfl_xor_sync(0xffffffffu, v, 4);
+                            v += __shfl_xor_sync(0xffffffffu, v, 2);
+                            v += __shfl_xor_sync(0xffffffffu, v, 1);
+                            if (hl == 0 && v0) job.out[r0 + k0 * RC + rl0] = v;
+                        }
+                    } else if (__any_sync(0xffffffffu, v0 || v1)) {
                         const uint8_t *base0 = stage_base + (size_t)(g0 % S) * DS_STAGE_STRIDE;
                         const uint8_t *base1 = two ? stage_base + (size_t)(g1 % S) * DS_STAGE_STRIDE : base0;
                         const uint8_t *wa = v0 ? base0 + (size_t)rl0 * job.row_bytes : (v1 ? base1 + (size_t)rl1 * job.row_bytes : base0);

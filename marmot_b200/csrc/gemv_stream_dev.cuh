@@ -428,10 +428,11 @@ __device__ __forceinline__ void quantize_all_q8_0(const float *x, int ldx, int T
 // Q4_K: two lanes per super-block; lane h owns sub-blocks 4h .. 4h+3 (qs bytes [64h, 64h+64)).
 // High nibbles are used in place (byte & 0xF0 = 16*q): their dot is 16 times too large, which the
 // exact arithmetic shift at the end undoes.
-template <int T>
+// SUBS = 8: each half of the warp works on a row of its own (wrow per lane, `lane` within the half), rows of <= 8 blocks.
+template <int T, int SUBS = 16>
 __device__ __forceinline__ void row_q4_k(const uint8_t *wrow, const ActSmem &a, int nb, int lane, float (&acc)[T]) {
     const int sub = lane >> 1, h = lane & 1;
-    for (int b0 = 0; b0 < nb; b0 += 16) {
+    for (int b0 = 0; b0 < nb; b0 += SUBS) {
         const int blk = b0 + sub;
         const bool ok = blk < nb;
         int p[T], s[T];
