@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 SHAPE = DecoderShape(layers=2, d=256, ffn=512, n_heads=4, n_kv_heads=2, head_dim=64, vocab=512, rope_theta=10000.0)
 
 
-def make_weights(rng, SHAPE=SHAPE):
+def make_weights(rng, SHAPE=SHAPE, kinds=None):
     """Block scales small enough that activations stay of order one (weight std about 1/sqrt(K)), as in a trained
     model: with the default block-space scales the attention scores reach the thousands, the softmax saturates and a
     1e-3 perturbation of a score flips whole attention rows."""
@@ -25,6 +25,7 @@ def make_weights(rng, SHAPE=SHAPE):
     w = {}
     for i in range(SHAPE.layers):
         for name, kind, rows, cols in LAYER_WEIGHTS:
+            kind = (kinds or {}).get(f"l{i}.{name}", kind)
             w[f"l{i}.{name}"] = random_blocks(kind, rows(SHAPE), cols(SHAPE), rng, d_sigma=sig)
         w[f"l{i}.attn_norm"] = rng.normal(1, 0.1, SHAPE.d).astype(np.float32)
         w[f"l{i}.ffn_norm"] = rng.normal(1, 0.1, SHAPE.d).astype(np.float32)
@@ -217,15 +218,19 @@ def test_one_token_step_kernel_matches_the_five_launch_layer(monkeypatch, prompt
     (DecoderShape(layers=1, d=4096, ffn=4352, n_heads=32, n_kv_heads=8, head_dim=128, vocab=256, rope_theta=500000.0), 33),
     # eight query heads per KV head at head_dim 64, a context of more tiles than attention warps (16 > 15)
     (DecoderShape(layers=1, d=512, ffn=768, n_heads=8, n_kv_heads=1, head_dim=64, vocab=256, rope_theta=10000.0), 500),
+    # other block formats per tensor: an up projection in Q6_K (gate and up as two jobs, SwiGLU as down's prologue),
+    # down in Q4_K with rows of three blocks, v in Q4_K
+    (DecoderShape(layers=2, d=256, ffn=768, n_heads=4, n_kv_heads=2, head_dim=64, vocab=512, rope_theta=10000.0), 21),
 ])
 def test_one_token_step_kernel_on_other_shapes(monkeypatch, shape, ctx_len):
     """The persistent decode-step kernel against the five-launch layer on shapes that take its other code paths."""
     rng = np.random.default_rng(shape.d + ctx_len)
-    weights = make_weights(rng, shape)
+    kinds = {"l0.up": KIND_Q6_K, "l1.down": KIND_Q4_K, "l0.wv": KIND_Q4_K, "l1.gate": KIND_Q6_K} if ctx_len == 21 else None
+    weights = make_weights(rng, shape, kinds)
     ctx = Context(0)
     try:
-        decs = [Decoder(ctx, shape, max_seqs=1, max_ctx=ctx_len + 16, block_size=16, kv_dtype=torch.float16, weights=weights)
-                for _ in range(2)]
+        decs = [Decoder(ctx, shape, max_seqs=1, max_ctx=ctx_len + 16, block_size=16, kv_dtype=torch.float16, weights=weights,
+                        kinds=kinds) for _ in range(2)]
         n = min(ctx_len, 96)  # a prompt, then the pool filled up to ctx_len with the same random rows in both decoders
         ids = torch.from_numpy(rng.integers(0, shape.vocab, n).astype(np.int32)).cuda()
         pos_np = np.arange(n, dtype=np.int32)

@@ -664,6 +664,24 @@ def test_linear_multi_large_matrices_at_a_handful_of_tokens(ctx, oracle):
         assert np.all(got[:, F:] == 7.0)
 
 
+def test_linear_multi_swiglu_over_a_large_matrix_at_a_handful_of_tokens(ctx, oracle):
+    """The down projection of an 8B model for six tokens: SwiGLU as a kernel of its own, the matmul on the integer MMAs."""
+    import torch
+
+    T, K, F = 6, 14336, 4096  # 33 MB of Q4_K
+    rng = np.random.default_rng(607)
+    kinds, Ws, gate, gd, outs = _multi_case(rng, ("q4_k",), T, K, (F,))
+    up = rng.normal(0, 1, (T, K)).astype(np.float32)
+    l0 = ctx.launch_count()
+    ctx.linear_multi(gd, [(kinds[0], ctx.upload(Ws[0]), F, outs[0][:, :F])], ("swiglu", torch.from_numpy(up).cuda()))
+    ctx.synchronize()
+    assert ctx.launch_count() - l0 > 1
+    want = oracle.linear(kinds[0], oracle.swiglu(gate, up), Ws[0], F)
+    got = outs[0].cpu().numpy()
+    assert max_rel_err(got[:, :F], want) <= TOL_FP32
+    assert np.all(got[:, F:] == 7.0)
+
+
 def test_linear_multi_general_form(ctx, oracle):
     """More than eight tokens, or kinds that do not share an activation format: the prologue runs as its own kernel,
     the matmuls follow; same results."""
