@@ -181,8 +181,11 @@ int mcu_linear_dual(
  *                                  rms_norm(x') * (norm_weight + weight_offset); x' is stored to x_out when that is
  *                                  set.  x_out must not overlap x or aux.
  *        MCU_PROLOGUE_SWIGLU       the weights multiply silu(x) * aux (x = gate, aux = up projection)
- *      Up to 8 tokens with every weight on the streaming path this is ONE launch; otherwise the prologue runs as its
- *      stand-alone kernel (which needs contiguous rows: ldx = ld_aux = ld_x_out = K) followed by the matmuls. ---- */
+ *      Up to 8 tokens with every weight on the streaming path this is ONE launch -- except for 5 to 8 tokens over 24 MB
+ *      or more of Q4_K / Q6_K weights, where the integer-MMA kernel behind a stand-alone prologue kernel is faster than
+ *      the one launch; more than 16 tokens: the prologue rides in the tensor-core path's activation staging; otherwise the
+ *      prologue runs as its stand-alone kernel (which needs contiguous rows: ldx = ld_aux = ld_x_out = K) followed by
+ *      the matmuls. ---- */
 enum { MCU_PROLOGUE_NONE = 0, MCU_PROLOGUE_ADD_RMSNORM = 1, MCU_PROLOGUE_SWIGLU = 2 };
 #define MCU_LINEAR_MAX_JOBS 4
 typedef struct mcu_linear_job {
